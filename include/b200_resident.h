@@ -1,0 +1,245 @@
+/*
+ * b200_resident.h — C ABI of the B200 (sm_100a) resident backend for goinfer's ragged batched
+ * decode / varlen-prefill step.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns an int status and never
+ * throws, aborts or calls back into the host. A cgo-free Go host binds these with dlopen/dlsym; the
+ * Python package binds them with ctypes. Host buffers passed in stay the caller's and are only read
+ * (or written, for outputs) during the call.
+ *
+ * Each declaration cites the interface of the reference (townsendmerino/goinfer, paths relative to its
+ * root) that it stands in for.
+ */
+#ifndef B200_RESIDENT_H
+#define B200_RESIDENT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes -------------------------------------------------------------------------------- */
+#define B200_OK            0
+#define B200_DECLINED      1 /* the model cannot be built resident (decoder.DeclineResident, decoder/residency.go:240-255) */
+#define B200_KV_POOL_FULL  2 /* decoder.ErrKVPoolFull: every row's blocks were mapped first and nothing was written (decoder/mc3_batch.go:492-498) */
+#define B200_BAD_ARGUMENT  3
+#define B200_CUDA_ERROR    4
+#define B200_TIMEOUT       5 /* a bounded device-side wait gave up; the context stays usable */
+#define B200_NCCL_ERROR    6
+
+/* ---- tensor names (b200_upload_tensor `which`) ----------------------------------------------------
+ * The weights a dense or routed-expert decoder layer carries, as decoder.BackendView.Weights() hands
+ * them to a resident build (decoder/backend_view.go:120-302). */
+#define B200_T_EMBED       0  /* [vocab, hidden]  F32 | F16                                   */
+#define B200_T_FINAL_NORM  1  /* [hidden]         F32                                         */
+#define B200_T_LM_HEAD     2  /* [vocab, hidden]  F32 | F16 | Q4K                             */
+#define B200_T_ATTN_NORM   3  /* [hidden]         F32                                         */
+#define B200_T_WQ          4  /* [n_heads*head_dim, hidden]                                   */
+#define B200_T_WK          5  /* [n_kv_heads*head_dim, hidden]                                */
+#define B200_T_WV          6
+#define B200_T_WO          7  /* [hidden, n_heads*head_dim]                                   */
+#define B200_T_Q_NORM      8  /* [head_dim] F32, per-head RMSNorm of q (decoder/program_cpu.go:351-364) */
+#define B200_T_K_NORM      9
+#define B200_T_FFN_NORM    10
+#define B200_T_GATE        11 /* [ffn, hidden]                                                */
+#define B200_T_UP          12
+#define B200_T_DOWN        13 /* [hidden, ffn]                                                */
+#define B200_T_ROUTER      14 /* [n_experts, hidden] F32 only (decoder/weightmat.go:61-64)    */
+#define B200_T_EXP_GATE    15 /* [moe_ffn, hidden] per expert                                 */
+#define B200_T_EXP_UP      16
+#define B200_T_EXP_DOWN    17 /* [hidden, moe_ffn] per expert                                 */
+
+/* ---- weight kinds --------------------------------------------------------------------------------- */
+#define B200_K_F32 0
+#define B200_K_F16 1
+#define B200_K_Q4K 2 /* GGUF Q4_K super-blocks, 144 bytes per 256 weights, row-major [rows][cols/256][144]
+                        (decoder/gguf.go:1508-1537; device twin backend/cuda/actgroup.cu:311-355). A Q4K
+                        matrix multiplies per-32-group int8 activations (backend/cuda/actgroup.cu:32-54). */
+
+/* ---- draw kinds ----------------------------------------------------------------------------------- */
+#define B200_DRAW_LOGITS 0 /* no draw: the row's logits are returned (BatchSeq.Draw == nil)          */
+#define B200_DRAW_GREEDY 1 /* BatchDraw.Greedy: first maximal index (internal/runtime/sampling/sampler.go:485-518) */
+#define B200_DRAW_MINP   2 /* min-p retained set + CDF walk with the caller's uniform `u`
+                              (sampler.go:586-724, drawFiltered :442-458)                            */
+
+/* ---- kernel classes (b200_model_cfg.kernel_class) -------------------------------------------------
+ * The reference separates exact kernels from fast, non-bit-identical ones by a row floor
+ * (resident.Caps.HasFastPrefill / FastPrefillFloor, decoder/resident/forward.go:119-146). */
+#define B200_CLASS_AUTO  0 /* exact integer-dot kernels below fast_floor rows, tcgen05 fp16 GEMM from it */
+#define B200_CLASS_EXACT 1 /* exact kernels at every row count                                        */
+
+typedef struct b200_ctx b200_ctx;
+typedef struct b200_model b200_model;
+
+/* Model shape and runtime plan. Mirrors what a resident build reads through BackendView: Dims(),
+ * NormEps(), AttnScale(), HasQKNorm(), AttnLogitSoftcap(), MoE() (decoder/backend_view.go:17-76). */
+typedef struct {
+    int32_t hidden, n_layers, n_heads, n_kv_heads, head_dim, ffn, vocab;
+    int32_t rotary_dim;      /* rotated dims per head (== head_dim for full rotary)                    */
+    int32_t qk_norm;         /* 1: per-head RMSNorm of q and k before RoPE                             */
+    int32_t n_experts, top_k, norm_topk, moe_ffn; /* n_experts == 0: dense gated FFN                   */
+    int32_t kv_block_rows;   /* positions per KV block (16 or 64)                                      */
+    int32_t kv_pool_blocks;  /* blocks in the pool, the null block 0 included                          */
+    int32_t n_slots;         /* KV slots (KVSubsystem.KVSlots, decoder/resident/subsystems.go)         */
+    int32_t ctx_cap;         /* Caps.ContextCap: positions per slot                                    */
+    int32_t max_rows;        /* most packed rows one step carries                                      */
+    int32_t tp_rank, tp_size;/* tensor-parallel rank/size; 1 = replica                                 */
+    int32_t kernel_class;    /* B200_CLASS_*                                                           */
+    int32_t fast_floor;      /* rows from which the fast class runs (0 = library default)              */
+    int32_t kv_dtype;        /* 0 = fp16 paged cache (the only kind this backend builds); 1 = f32, which
+                                this backend declines (decoder.DeclineResident) and only the CPU oracle runs */
+    float rms_eps, rope_theta;
+    float attn_scale;        /* 0 = 1/sqrt(head_dim)                                                   */
+    float attn_softcap;      /* 0 = off; else cap*tanh(s/cap) (decoder/attention.go:287-295)           */
+    float final_softcap;     /* 0 = off                                                                */
+    float embed_scale;       /* 0 or 1 = none (decoder/cpu_batch.go:176-186)                           */
+} b200_model_cfg;
+
+/* Per-sequence draw of a step (resident.BatchDraw, decoder/resident/forward.go:43-52). */
+typedef struct {
+    int32_t kind;        /* B200_DRAW_*                                                               */
+    float temperature;   /* min-p only; <= 0 reads as 1                                               */
+    float min_p;         /* min-p only; > 1 is clamped to 1 (sampler.go:129-139)                      */
+    float _pad;
+    double u;            /* min-p only: the uniform in [0,1) the host sampler drew for this token     */
+} b200_draw;
+
+/* resident.Caps (decoder/resident/forward.go:119-146). */
+typedef struct {
+    int32_t context_cap, kv_slots, batch_lo, batch_hi; /* BatchStepRange = (batch_lo, batch_hi)       */
+    int32_t has_fast_prefill, fast_prefill_floor, tail_min_rows, batch_greedy_draw;
+    int64_t weight_bytes, kv_bytes, scratch_bytes;
+} b200_caps;
+
+/* decoder.ResidentBatchStats (decoder/mc3_batch.go:82-94) plus device-side counters. */
+typedef struct {
+    int64_t steps, rows, prefill_rows, kernel_launches, kv_blocks_in_use, kv_pool_full;
+    double last_step_device_ms;
+} b200_stats_t;
+
+/* ---- context -------------------------------------------------------------------------------------- */
+/* Opens device `device_ordinal`. `stream` is a cudaStream_t the library launches on; NULL makes the
+ * library create its own. Replaces gpudev.Open (backend/cuda/internal/gpudev/cuda.go:177-181). */
+int b200_open(int device_ordinal, void* stream, b200_ctx** out);
+void b200_close(b200_ctx* ctx);
+/* Text of the last non-OK status on this context (the Go shim turns it into an error value). */
+const char* b200_last_error(b200_ctx* ctx);
+/* Counts kernels launched by this library on the context since open (bench accounting). */
+int64_t b200_launch_count(b200_ctx* ctx);
+
+/* ---- model build: ResidencyBackend.BuildResident (decoder/residency.go:208-210) -------------------- */
+int b200_model_create(b200_ctx* ctx, const b200_model_cfg* cfg, b200_model** out);
+/* Copies one tensor to the device. `layer` is -1 for model-level tensors; `expert` is -1 unless `which`
+ * is an expert tensor. The host buffer stays the caller's. */
+int b200_upload_tensor(b200_model* m, int which, int layer, int expert, int kind,
+                       int rows, int cols, const void* host, size_t bytes);
+/* Fills one Q4_K tensor on the device with seeded N(0, sigma) weights quantized by the library's
+ * deterministic quantizer (no host copy). The reference has no fp32->Q4_K quantizer (it only reads
+ * GGUF, decoder/gguf.go:1508-1537); this exists for synthetic-weight workloads. */
+int b200_synth_tensor(b200_model* m, int which, int layer, int expert, int kind,
+                      int rows, int cols, float sigma, uint64_t seed);
+/* Per-layer RoPE inverse frequencies (BackendView.RopeInvFreq, decoder/residency.go:604-619). `layer`
+ * -1 sets every layer. Without a call the table is theta^(-2d/rotary_dim) (decoder/ropescale.go:285-290). */
+int b200_set_rope_inv_freq(b200_model* m, int layer, const double* inv_freq, int n);
+/* Plans the KV pool and scratch, fuses projection groups, fills Caps. */
+int b200_model_finalize(b200_model* m, b200_caps* out);
+void b200_model_free(b200_model* m);
+
+/* ---- KVSubsystem (decoder/resident/subsystems.go; backend/cuda/kvpool.go:16-76) --------------------- */
+int b200_kv_slots(b200_model* m);
+/* Releases a slot's blocks and rewinds it to position 0 (ResidentForward.Reset on that slot). */
+int b200_reset_slot(b200_model* m, int slot);
+int b200_reset(b200_model* m);
+/* Copies a slot's block table (ctx_cap / kv_block_rows entries, 0 = unmapped) to `out`. */
+int b200_block_table(b200_model* m, int slot, int32_t* out, int n);
+/* Fills the KV rows [0, n_pos) of a slot in every layer with seeded N(0, sigma) fp16 values (synthetic
+ * prefix contexts for a decode benchmark) and maps their blocks. */
+int b200_synth_kv(b200_model* m, int slot, int n_pos, float sigma, uint64_t seed);
+/* ResidentForward.UploadKV (decoder/resident/forward.go:5-33): rows [base, base+n) of one layer, f32
+ * [n][n_kv_heads*head_dim], rounded to the cache's fp16. */
+int b200_upload_kv(b200_model* m, int slot, int layer, int base, int n, const float* keys, const float* vals);
+
+/* ---- the step: DecodeSubsystem.StepBatch / StepRagged (decoder/resident/subsystems.go:102-117;
+ *      wire types decoder/resident/forward.go:35-84; existing implementation backend/cuda/batchstep.go:49-182)
+ *
+ * n_seqs sequences; sequence i owns n_rows[i] packed rows at positions pos[i], pos[i]+1, ... of KV slot
+ * slot[i] (slots distinct). prefill_prompt_len[i] > 0 marks a prefill chunk (at most one, first, no draw,
+ * inside its prompt; prefill_last[i] iff it ends it). Inputs are either `embs` (packed rows x hidden f32,
+ * the reference's host embedResident rows) or `token_ids` (device table gather; allowed where the lookup
+ * is a plain table row, decoder/residency.go:1053-1131); exactly one is non-NULL.
+ * draws may be NULL (all rows return logits). mask_index[i] >= 0 selects row mask_index[i] of `logit_mask`
+ * ([n_masks][ceil(vocab/32)] words, bit set = token allowed; cleared => logit = -inf before the draw,
+ * constrain/constrain.go:233-267).
+ *
+ * Outputs: logits_out receives, packed in order, one [vocab] row for every row that returns logits
+ * (every row of a sequence without a draw; for a draw sequence every row but its last; for a prefill chunk only the
+ * final row of a Last pass). ids_out[i] is the drawn id or -1. n_logit_rows_out, if not NULL, receives
+ * the number of rows written.
+ * StepBatch is this call with n_rows[i] == 1 for all i. */
+int b200_step_ragged(b200_model* m, int n_seqs, const int32_t* slot, const int32_t* pos,
+                     const int32_t* n_rows, const int32_t* prefill_prompt_len,
+                     const uint8_t* prefill_last, const float* embs, const int32_t* token_ids,
+                     const b200_draw* draws, const int32_t* mask_index, const uint32_t* logit_mask,
+                     int n_masks, float* logits_out, int32_t* ids_out, int32_t* n_logit_rows_out);
+
+/* ResidentForward.Forward / DecodeSubsystem.ForwardArgmax / ForwardNoLogits on one slot
+ * (decoder/resident/forward.go:5-33): one row at `pos`. out_kind: 0 logits, 1 argmax id, 2 nothing. */
+int b200_forward(b200_model* m, int slot, const float* emb, int token_id, int pos, int out_kind,
+                 float* logits_out, int32_t* id_out);
+/* PrefillSubsystem.PrefillLast: n rows from start_pos on one slot, logits of the last row. */
+int b200_prefill_last(b200_model* m, int slot, int n, const float* embs, const int32_t* token_ids,
+                      int start_pos, float* logits_out);
+
+/* Timed decode steps with everything already on the device (benchmark leg "value"): runs `steps`
+ * greedy StepBatch iterations over the given sequences, feeding each drawn id back as the next token,
+ * and returns the device time of the whole loop in milliseconds. */
+int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, const int32_t* pos0,
+                            const int32_t* first_ids, int steps, int advance_pos,
+                            int32_t* ids_out /*[steps][n_seqs] or NULL*/, float* ms_out);
+
+int b200_stats(b200_model* m, b200_stats_t* out);
+
+/* ---- operator-level entry points (host buffers in, host buffers out) -------------------------------
+ * The reference exposes its matmul as Backend.MatmulBT(a, b, dst, M, K, N) (decoder/backend.go:23-32)
+ * and tests kernels against host twins (backend/cuda/kernels/actgroup_kernel_test.go). These run the
+ * same device kernels the step uses on caller-supplied data. */
+/* Per-32 int8 activation quantizer (backend/cuda/actgroup.cu:32-54): x [rows][k] -> codes int8
+ * [rows][k], scales [rows][2*k/32] (k/32 scales then k/32 group sums). */
+int b200_op_quant_g32(b200_ctx* ctx, const float* x, int rows, int k, int8_t* codes, float* scales);
+/* Q4_K super-blocks -> f32 weights, w = d*sc*q - dmin*m (backend/cuda/kernels/ks_a1_test.go:117-131). */
+int b200_op_q4k_dequant(b200_ctx* ctx, const uint8_t* w, int rows, int cols, float* out);
+/* dst[M][N] = a[M][K] . W^T, W Q4_K [N][K]; activations quantized per 32 (actgroup.cu:311-355).
+ * klass: 0 = library choice by M, 1 = exact kernels, 2 = fast (tcgen05 fp16) kernel. */
+int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, int K, int N, int klass,
+                       float* dst);
+/* fp32 -> Q4_K with the library's quantizer; out is rows*cols/256*144 bytes. */
+int b200_op_q4k_quantize(b200_ctx* ctx, const float* w, int rows, int cols, uint8_t* out);
+/* RMSNorm rows (decoder/rmsnorm.go:29-92). */
+int b200_op_rmsnorm(b200_ctx* ctx, const float* x, const float* w, int rows, int dim, float eps, float* out);
+/* softmax -> top-k router (decoder/mlp.go:130-184, 370-440): logits [rows][n_experts] -> idx, wts [rows][k]. */
+int b200_op_route(b200_ctx* ctx, const float* logits, int rows, int n_experts, int k, int norm_topk,
+                  int32_t* idx, float* wts);
+/* Draw over logits rows with optional masks (sampler.go:485-518, 586-724). */
+int b200_op_draw(b200_ctx* ctx, const float* logits, int rows, int vocab, const b200_draw* draws,
+                 const int32_t* mask_index, const uint32_t* logit_mask, int n_masks, int32_t* ids);
+/* Paged decode attention over caller-supplied contiguous K/V (f32 rounded to fp16 on upload):
+ * q [rows][n_heads*head_dim]; row r attends keys [0, n_keys[r]) of its own K/V
+ * (decoder/forwardn.go:295-501, acc64 branch). */
+int b200_op_attention(b200_ctx* ctx, const float* q, const float* k, const float* v, const int32_t* n_keys,
+                      int rows, int max_keys, int n_heads, int n_kv_heads, int head_dim, float scale,
+                      float softcap, int block_rows, float* out);
+
+/* Device-resident micro-benchmarks: average device milliseconds per launch over `iters` launches after
+ * `warmup`, of the kernel the step would pick (or `klass`), on synthetic resident data. */
+int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_weight_copies,
+                          int warmup, int iters, float* ms_out);
+int b200_bench_attention(b200_ctx* ctx, int rows, int ctx_lo, int ctx_hi, int n_heads, int n_kv_heads,
+                         int head_dim, int block_rows, uint64_t seed, int warmup, int iters,
+                         float* ms_out, double* kv_bytes_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_RESIDENT_H */
