@@ -1,0 +1,113 @@
+// common.cuh — context, error handling and the launcher table shared by the library's .cu files.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/b200_resident.h"
+
+struct b200_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    std::string err;
+    int64_t launches = 0;  // kernels this library launched on the context
+    int sm_count = 148;
+};
+
+#define B200_FAIL(ctx, code, ...)                         \
+    do {                                                  \
+        char buf_[512];                                   \
+        snprintf(buf_, sizeof buf_, __VA_ARGS__);         \
+        (ctx)->err = buf_;                                \
+        return (code);                                    \
+    } while (0)
+
+#define CUDA_TRY(ctx, expr)                                                                              \
+    do {                                                                                                 \
+        cudaError_t e_ = (expr);                                                                         \
+        if (e_ != cudaSuccess) B200_FAIL(ctx, B200_CUDA_ERROR, "%s: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, __LINE__); \
+    } while (0)
+
+#define ST_TRY(expr)            \
+    do {                        \
+        int st_ = (expr);       \
+        if (st_ != B200_OK) return st_; \
+    } while (0)
+
+// Counts the launch and reports a launch-time error.
+#define LAUNCH_CHECK(ctx)                                                                               \
+    do {                                                                                                \
+        (ctx)->launches++;                                                                              \
+        cudaError_t e_ = cudaGetLastError();                                                            \
+        if (e_ != cudaSuccess) B200_FAIL(ctx, B200_CUDA_ERROR, "launch failed: %s (%s:%d)", cudaGetErrorString(e_), __FILE__, __LINE__); \
+    } while (0)
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// ---- device buffers a Q4_K matmul reads: int8 codes [T][K] and scales [T][2*K/32] ----
+struct ActQ {
+    int8_t* codes = nullptr;
+    float* scales = nullptr;
+};
+
+// ---- paged KV view of one layer ----
+// Pool layout: [block][kv_head][row in block][head_dim] fp16 for K, the same for V. One (block, kv head)
+// tile is block_rows*head_dim*2 contiguous bytes.
+struct KVView {
+    __half* k = nullptr;
+    __half* v = nullptr;
+    const int32_t* table = nullptr;  // [n_slots][max_blocks]
+    int max_blocks = 0, block_rows = 16, n_kv = 0, hd = 0;
+};
+
+// ---- launchers (each returns a B200_* status) ----
+// elementwise.cu
+int launch_embed_gather(b200_ctx*, const void* table, int kind, const int32_t* ids, int T, int H, float scale, float* h);
+// h += delta (delta may be null), then RMSNorm(h)*w -> normed f32 (may be null) and/or per-32 int8 (aq.codes may be null).
+int launch_add_rmsnorm_quant(b200_ctx*, float* h, const float* delta, const float* w, int T, int H, float eps,
+                             float* normed, ActQ aq, const int32_t* gather_rows);
+int launch_quant_g32(b200_ctx*, const float* x, int T, int K, ActQ aq);
+int launch_swiglu_quant(b200_ctx*, const float* gate_up, int T, int F, int ld, float* mid_f32, ActQ aq);
+int launch_add(b200_ctx*, float* h, const float* delta, size_t n);
+// q (in place, f32), k,v -> paged fp16 store; optional per-head RMSNorm, NeoX RoPE with f64 cos/sin.
+int launch_qknorm_rope_kvstore(b200_ctx*, float* qkv, int ld, int T, int nH, int nKV, int hd, int rot_half,
+                               const double* inv_freq, const float* q_norm, const float* k_norm, float eps,
+                               const int32_t* row_slot, const int32_t* row_pos, KVView kv);
+int launch_fold_experts(b200_ctx*, const float* eo, const float* wts, const int32_t* slot_of, int T, int k, int H, float* out);
+int launch_softcap(b200_ctx*, float* x, size_t n, float cap);
+
+// gemm.cu
+// dst[T][N] (ld = ldd) = act . W^T for a Q4_K matrix; klass 0 auto, 1 exact, 2 fast.
+int launch_q4k_matmul(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, int klass);
+// grouped form: expert e owns assignment rows [offs[e], offs[e+1]); assignment a reads activation row
+// rows[a] and writes dst row a. Wptrs[e] is expert e's matrix.
+int launch_q4k_matmul_grouped(b200_ctx*, const uint8_t* const* Wptrs, int n_experts, int N, int K, ActQ aq,
+                              const int32_t* offs, const int32_t* rows, int max_rows_per_expert, float* dst, int ldd);
+int launch_f16w_matmul(b200_ctx*, const __half* W, int N, int K, const float* x, int T, float* dst, int ldd,
+                       __half* split_scratch /* 2*T*K halves */);
+int launch_f32w_matmul(b200_ctx*, const float* W, int N, int K, const float* x, int T, float* dst, int ldd);
+int launch_q4k_dequant(b200_ctx*, const uint8_t* W, size_t n_blocks, float* out);
+int launch_q4k_quantize(b200_ctx*, const float* w, size_t n_blocks, uint8_t* out);
+int launch_synth_normal_f32(b200_ctx*, float* out, size_t n, float sigma, uint64_t seed);
+int launch_synth_q4k(b200_ctx*, uint8_t* out, size_t n_blocks, float sigma, uint64_t seed);
+int launch_synth_f16(b200_ctx*, __half* out, size_t n, float sigma, uint64_t seed);
+
+// attention.cu
+struct AttnScratch {
+    float* partial = nullptr;  // [T][nH][max_splits][hd+2]
+    int max_splits = 0;
+};
+size_t attn_scratch_floats(int T, int nH, int hd, int max_splits);
+int attn_split_keys();
+int launch_paged_attention(b200_ctx*, const float* q, int ldq, int T, int nH, int nKV, int hd, float scale, float softcap,
+                           const int32_t* row_slot, const int32_t* row_pos, int max_keys, KVView kv, AttnScratch sc,
+                           float* out, ActQ aq);
+
+// sample.cu
+int launch_mask_logits(b200_ctx*, float* logits, int R, int V, const int32_t* row_mask, const uint32_t* masks);
+int launch_draw(b200_ctx*, const float* logits, int R, int V, const b200_draw* draws, int32_t* ids, float* scratch);
+int launch_route(b200_ctx*, const float* logits, int T, int nE, int k, int norm, int32_t* idx, float* wts);
+int launch_group_experts(b200_ctx*, const int32_t* idx, int T, int k, int nE, int32_t* offs, int32_t* rows);

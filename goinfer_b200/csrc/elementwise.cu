@@ -1,0 +1,286 @@
+// elementwise.cu — the HBM-bound row kernels of the step: embedding gather, residual + RMSNorm + per-32
+// int8 activation quantization, SwiGLU + quantization, per-head QK RMSNorm + NeoX RoPE + paged fp16 KV
+// store, expert fold. Each is one pass over its rows; arithmetic follows the reference's CPU path:
+//   RMSNorm      decoder/rmsnorm.go:29-92      (f64 sum of squares, y = (x*inv)*w)
+//   quantizer    backend/cuda/actgroup.cu:32-54 (sc = max/127, inv = sc>0 ? 1/sc : 0, RNE, clamp +-127, asum = sc*sum)
+//   SwiGLU       decoder/mlp.go:269-290, silu in f64 decoder/rmsnorm.go:204-207
+//   QK norm      decoder/program_cpu.go:351-364
+//   RoPE         decoder/rope.go:28-64 (split-half, cos/sin and the rotation in f64)
+//   residual     decoder/model_forward.go:98-119
+//   expert fold  decoder/mlp.go:729-745 (out += w*src, rank order, no contraction)
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Quantizes one group of 32 values held one per lane. Lane 0 writes the scale and the group sum.
+__device__ __forceinline__ void quant_group_warp(float y, int8_t* codes_g, float* sc_out, float* asum_out, int lane) {
+    float ma = fabsf(y);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, o));
+    float sc = __fdiv_rn(ma, 127.f);
+    float inv = sc > 0.f ? __fdiv_rn(1.f, sc) : 0.f;
+    int q = __float2int_rn(__fmul_rn(y, inv));
+    q = max(-127, min(127, q));
+    int sum = q;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    codes_g[lane] = (int8_t)q;
+    if (lane == 0) {
+        *sc_out = sc;
+        *asum_out = __fmul_rn(sc, (float)sum);
+    }
+}
+
+__global__ void embed_gather_kernel(const void* __restrict__ table, int kind, const int32_t* __restrict__ ids, int H,
+                                    float scale, float* __restrict__ h) {
+    int r = blockIdx.x;
+    size_t id = (size_t)ids[r];
+    float* out = h + (size_t)r * H;
+    if (kind == B200_K_F32) {
+        const float* row = (const float*)table + id * H;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = scale != 1.f ? __fmul_rn(row[i], scale) : row[i];
+    } else {
+        const __half* row = (const __half*)table + id * H;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = __half2float(row[i]);
+            out[i] = scale != 1.f ? __fmul_rn(v, scale) : v;
+        }
+    }
+}
+
+// One block per output row. Dynamic shared memory: H floats (the normed row) + 8 doubles.
+__global__ void __launch_bounds__(256) add_rmsnorm_quant_kernel(float* __restrict__ h, const float* __restrict__ delta,
+                                                                const float* __restrict__ w, int H, float eps,
+                                                                float* __restrict__ normed, int8_t* __restrict__ codes,
+                                                                float* __restrict__ scales,
+                                                                const int32_t* __restrict__ gather_rows) {
+    extern __shared__ double smem_d[];
+    double* red = smem_d;                 // 8 doubles
+    float* row = (float*)(smem_d + 8);    // H floats
+    const int j = blockIdx.x;
+    const int r = gather_rows ? gather_rows[j] : j;
+    float* hr = h + (size_t)r * H;
+    double ss = 0;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float x = hr[i];
+        if (delta) {
+            x = __fadd_rn(x, delta[(size_t)r * H + i]);
+            hr[i] = x;
+        }
+        row[i] = x;
+        ss += (double)x * (double)x;
+    }
+    ss = warp_sum_f64(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    double tot = 0;
+#pragma unroll
+    for (int k = 0; k < 8; k++) tot += red[k];
+    const float inv = (float)(1.0 / sqrt(tot / (double)H + (double)eps));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nG = H >> 5;
+    for (int g = warp; g < nG; g += 8) {
+        int i = g * 32 + lane;
+        float y = __fmul_rn(__fmul_rn(row[i], inv), w[i]);
+        if (normed) normed[(size_t)j * H + i] = y;
+        if (codes) quant_group_warp(y, codes + (size_t)j * H + g * 32, scales + (size_t)j * 2 * nG + g,
+                                    scales + (size_t)j * 2 * nG + nG + g, lane);
+    }
+    // tail for H not a multiple of 32 (f32-weight models only; no quantized output there)
+    for (int i = nG * 32 + threadIdx.x; i < H; i += blockDim.x)
+        if (normed) normed[(size_t)j * H + i] = __fmul_rn(__fmul_rn(row[i], inv), w[i]);
+}
+
+__global__ void __launch_bounds__(256) quant_g32_kernel(const float* __restrict__ x, int K, int8_t* __restrict__ codes,
+                                                        float* __restrict__ scales) {
+    const int r = blockIdx.y, lane = threadIdx.x & 31, nG = K >> 5;
+    const int g = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (g >= nG) return;
+    float y = x[(size_t)r * K + g * 32 + lane];
+    quant_group_warp(y, codes + (size_t)r * K + g * 32, scales + (size_t)r * 2 * nG + g, scales + (size_t)r * 2 * nG + nG + g, lane);
+}
+
+__device__ __forceinline__ float silu_f64(float x) {
+    double x64 = (double)x;
+    return (float)(x64 / (1.0 + exp(-x64)));
+}
+
+// gate at gate_up[r*ld + f], up at gate_up[r*ld + F + f].
+__global__ void __launch_bounds__(256) swiglu_quant_kernel(const float* __restrict__ gate_up, int F, int ld,
+                                                           float* __restrict__ mid, int8_t* __restrict__ codes,
+                                                           float* __restrict__ scales) {
+    const int r = blockIdx.y, lane = threadIdx.x & 31, nG = F >> 5;
+    const int g = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (g >= nG) return;
+    const int f = g * 32 + lane;
+    const float gt = gate_up[(size_t)r * ld + f], up = gate_up[(size_t)r * ld + F + f];
+    float y = __fmul_rn(silu_f64(gt), up);
+    if (mid) mid[(size_t)r * F + f] = y;
+    if (codes) quant_group_warp(y, codes + (size_t)r * F + g * 32, scales + (size_t)r * 2 * nG + g, scales + (size_t)r * 2 * nG + nG + g, lane);
+}
+
+// plain SwiGLU for widths that are not a multiple of 32 (f32-weight models)
+__global__ void swiglu_plain_kernel(const float* __restrict__ gate_up, int F, int ld, float* __restrict__ mid) {
+    const int r = blockIdx.y;
+    const int f = blockIdx.x * blockDim.x + threadIdx.x;
+    if (f < F) mid[(size_t)r * F + f] = __fmul_rn(silu_f64(gate_up[(size_t)r * ld + f]), gate_up[(size_t)r * ld + F + f]);
+}
+
+__global__ void add_kernel(float* __restrict__ h, const float* __restrict__ d, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) h[i] = __fadd_rn(h[i], d[i]);
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+// One block per packed row. Shared: cos/sin of the row's position (f64), one head buffer per warp.
+__global__ void __launch_bounds__(256) qknorm_rope_kvstore_kernel(
+    float* __restrict__ qkv, int ld, int nH, int nKV, int hd, int half, const double* __restrict__ inv_freq,
+    const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, const int32_t* __restrict__ row_slot,
+    const int32_t* __restrict__ row_pos, __half* __restrict__ kpool, __half* __restrict__ vpool,
+    const int32_t* __restrict__ table, int max_blocks, int block_rows) {
+    extern __shared__ double smem_d[];
+    double* cs = smem_d;                         // [half] cos, [half] sin
+    float* hb = (float*)(smem_d + 2 * half);     // [8][hd]
+    const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = row_pos[r], slot = row_slot[r];
+    for (int d = threadIdx.x; d < half; d += blockDim.x) {
+        double th = (double)pos * inv_freq[d];
+        double s, c;
+        sincos(th, &s, &c);
+        cs[d] = c;
+        cs[half + d] = s;
+    }
+    __syncthreads();
+    const int blk = table[(size_t)slot * max_blocks + pos / block_rows];
+    const int rib = pos % block_rows;
+    float* buf = hb + warp * hd;
+    float* rowp = qkv + (size_t)r * ld;
+    for (int hh = warp; hh < nH + 2 * nKV; hh += 8) {
+        const bool is_q = hh < nH, is_k = !is_q && hh < nH + nKV;
+        float* src = rowp + (size_t)hh * hd;
+        double ss = 0;
+        for (int e = lane; e < hd; e += 32) {
+            float x = src[e];
+            buf[e] = x;
+            ss += (double)x * (double)x;
+        }
+        const float* nw = is_q ? q_norm : (is_k ? k_norm : nullptr);
+        if (nw) {  // per-head RMSNorm before RoPE
+            ss = warp_sum_f64(ss);
+            float inv = (float)(1.0 / sqrt(ss / (double)hd + (double)eps));
+            __syncwarp();
+            for (int e = lane; e < hd; e += 32) buf[e] = __fmul_rn(__fmul_rn(buf[e], inv), nw[e]);
+        }
+        __syncwarp();
+        if (is_q || is_k) {
+            for (int d = lane; d < half; d += 32) {
+                double x1 = buf[d], x2 = buf[half + d], c = cs[d], s = cs[half + d];
+                float y1 = (float)(x1 * c - x2 * s), y2 = (float)(x2 * c + x1 * s);
+                buf[d] = y1;
+                buf[half + d] = y2;
+            }
+            __syncwarp();
+        }
+        if (is_q) {
+            for (int e = lane; e < hd; e += 32) src[e] = buf[e];
+        } else {
+            const int kvh = is_k ? hh - nH : hh - nH - nKV;
+            __half* dst = (is_k ? kpool : vpool) + (((size_t)blk * nKV + kvh) * block_rows + rib) * hd;
+            for (int e = lane; e < hd; e += 32) dst[e] = __float2half_rn(buf[e]);
+        }
+        __syncwarp();
+    }
+}
+
+// eo rows are in expert-sorted slot order; slot_of[row*k + rank] names the slot (-1: empty rank).
+__global__ void fold_experts_kernel(const float* __restrict__ eo, const float* __restrict__ wts,
+                                    const int32_t* __restrict__ slot_of, int k, int H, float* __restrict__ out) {
+    const int r = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= H) return;
+    float acc = 0.f;
+    for (int j = 0; j < k; j++) {
+        const int s = slot_of[(size_t)r * k + j];
+        if (s >= 0) acc = __fadd_rn(acc, __fmul_rn(wts[(size_t)r * k + j], eo[(size_t)s * H + i]));
+    }
+    out[(size_t)r * H + i] = acc;
+}
+
+}  // namespace
+
+int launch_embed_gather(b200_ctx* ctx, const void* table, int kind, const int32_t* ids, int T, int H, float scale, float* h) {
+    embed_gather_kernel<<<T, 256, 0, ctx->stream>>>(table, kind, ids, H, (scale == 0.f ? 1.f : scale), h);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_add_rmsnorm_quant(b200_ctx* ctx, float* h, const float* delta, const float* w, int T, int H, float eps,
+                             float* normed, ActQ aq, const int32_t* gather_rows) {
+    if (aq.codes && (H % 32)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "quantized rows need a width that is a multiple of 32");
+    size_t smem = 8 * sizeof(double) + (size_t)H * sizeof(float);
+    add_rmsnorm_quant_kernel<<<T, 256, smem, ctx->stream>>>(h, delta, w, H, eps, normed, aq.codes, aq.scales, gather_rows);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_quant_g32(b200_ctx* ctx, const float* x, int T, int K, ActQ aq) {
+    if (K % 32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K must be a multiple of 32");
+    dim3 grid(ceil_div(K / 32, 8), T);
+    quant_g32_kernel<<<grid, 256, 0, ctx->stream>>>(x, K, aq.codes, aq.scales);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_swiglu_quant(b200_ctx* ctx, const float* gate_up, int T, int F, int ld, float* mid, ActQ aq) {
+    if (aq.codes) {
+        if (F % 32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "F must be a multiple of 32");
+        dim3 grid(ceil_div(F / 32, 8), T);
+        swiglu_quant_kernel<<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales);
+    } else {
+        dim3 grid(ceil_div(F, 256), T);
+        swiglu_plain_kernel<<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid);
+    }
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_add(b200_ctx* ctx, float* h, const float* delta, size_t n) {
+    add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(h, delta, n);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_softcap(b200_ctx* ctx, float* x, size_t n, float cap) {
+    softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(x, n, cap);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_qknorm_rope_kvstore(b200_ctx* ctx, float* qkv, int ld, int T, int nH, int nKV, int hd, int rot_half,
+                               const double* inv_freq, const float* q_norm, const float* k_norm, float eps,
+                               const int32_t* row_slot, const int32_t* row_pos, KVView kv) {
+    if (hd > 256 || 2 * rot_half > hd) B200_FAIL(ctx, B200_BAD_ARGUMENT, "head_dim up to 256, rotary_dim <= head_dim");
+    size_t smem = 2 * (size_t)rot_half * sizeof(double) + 8 * (size_t)hd * sizeof(float);
+    qknorm_rope_kvstore_kernel<<<T, 256, smem, ctx->stream>>>(qkv, ld, nH, nKV, hd, rot_half, inv_freq, q_norm, k_norm, eps,
+                                                              row_slot, row_pos, kv.k, kv.v, kv.table, kv.max_blocks,
+                                                              kv.block_rows);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_fold_experts(b200_ctx* ctx, const float* eo, const float* wts, const int32_t* slot_of, int T, int k, int H,
+                        float* out) {
+    dim3 grid(ceil_div(H, 256), T);
+    fold_experts_kernel<<<grid, 256, 0, ctx->stream>>>(eo, wts, slot_of, k, H, out);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}

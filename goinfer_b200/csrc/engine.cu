@@ -1,0 +1,970 @@
+// engine.cu — the resident model and its ragged step behind the C ABI of include/b200_resident.h.
+//
+// What the reference does on the host per step — the slot/position arrays, the per-slot block tables and
+// their upload (backend/cuda/batchstep.go:306-381, kvpool.go:16-76), the coalescer's per-token embedding
+// rows (decoder/mc3_batch.go:358-366) — lives on the device here: a step uploads one small packed
+// descriptor (per-sequence slot, position, row count, token ids), and prepare_step_kernel maps KV blocks
+// from the device free list, builds the row->sequence / row->position arrays and the sequence offsets.
+// The host keeps only counters (rows stored and blocks mapped per slot, free blocks), which is enough to
+// refuse a step with B200_KV_POOL_FULL before anything is launched (decoder/mc3_batch.go:492-498).
+//
+// Layer program (decoder/program.go:143-166): norm -> QKV -> [QK norm] -> RoPE -> KV append -> attention
+// -> O -> residual -> norm -> gated FFN | routed experts -> residual; final norm + LM head on the rows that
+// return logits or draw (decoder/forwardn.go:800-831).
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "common.cuh"
+
+namespace {
+
+struct DevMat {
+    int kind = -1, rows = 0, cols = 0;
+    void* p = nullptr;
+    size_t bytes = 0;
+    bool present() const { return kind >= 0 && p; }
+};
+
+size_t mat_bytes(int kind, size_t rows, size_t cols) {
+    if (kind == B200_K_F32) return rows * cols * 4;
+    if (kind == B200_K_F16) return rows * cols * 2;
+    return rows * cols / 256 * 144;
+}
+
+struct LayerW {
+    float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+    DevMat wq, wk, wv, wo, gate, up, down, router;
+    std::vector<DevMat> eg, eu, ed;
+    DevMat qkv, gu;                         // fused at finalize
+    std::vector<DevMat> egu;                // per expert gate|up
+    const uint8_t** d_egu_ptrs = nullptr;   // device arrays of expert matrix pointers
+    const uint8_t** d_ed_ptrs = nullptr;
+    double* inv_freq = nullptr;             // device, [rot_half]
+    std::vector<double> h_inv_freq;
+};
+
+__global__ void init_pool_kernel(int32_t* free_stack, int32_t* free_count, int blocks, int32_t* table, size_t table_n,
+                                 int32_t* slot_mapped, int n_slots) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // take pops the last entry: ascending ids 1..blocks-1 (backend/cuda/kvpool.go:50-64)
+    if (i < (size_t)blocks - 1) free_stack[i] = (int32_t)(blocks - 1 - i);
+    if (i < table_n) table[i] = 0;
+    if (i < (size_t)n_slots) slot_mapped[i] = 0;
+    if (i == 0) *free_count = blocks - 1;
+}
+
+__global__ void reset_slot_kernel(int32_t* free_stack, int32_t* free_count, int32_t* table, int max_blocks,
+                                  int32_t* slot_mapped, int slot) {
+    // single thread: unref in table order, each freed block appended (kvpool.go:58-64)
+    int n = slot_mapped[slot], fc = *free_count;
+    int32_t* t = table + (size_t)slot * max_blocks;
+    for (int b = 0; b < n; b++) {
+        if (t[b]) free_stack[fc++] = t[b];
+        t[b] = 0;
+    }
+    *free_count = fc;
+    slot_mapped[slot] = 0;
+}
+
+// Descriptor layout (int32 words): [0] n_seqs, [1] T, then slot[S], pos[S], nrows[S] with S = n_seqs.
+// One block. Thread 0 maps blocks in sequence order; then all threads expand rows.
+__global__ void __launch_bounds__(256) prepare_step_kernel(const int32_t* __restrict__ desc, int32_t* __restrict__ pos_dev,
+                                                           int use_pos_dev, int32_t* __restrict__ table, int max_blocks,
+                                                           int block_rows, int32_t* __restrict__ slot_mapped,
+                                                           int32_t* __restrict__ free_stack, int32_t* __restrict__ free_count,
+                                                           int32_t* __restrict__ seq_row0, int32_t* __restrict__ row_slot,
+                                                           int32_t* __restrict__ row_pos, int32_t* __restrict__ status) {
+    const int S = desc[0], T = desc[1];
+    const int32_t* slot = desc + 2;
+    const int32_t* pos = use_pos_dev ? pos_dev : desc + 2 + S;
+    const int32_t* nrows = desc + 2 + 2 * S;
+    if (threadIdx.x == 0) {
+        int run = 0, fc = *free_count, bad = 0;
+        for (int i = 0; i < S; i++) {
+            seq_row0[i] = run;
+            run += nrows[i];
+            const int need = (pos[i] + nrows[i] + block_rows - 1) / block_rows;
+            int32_t* t = table + (size_t)slot[i] * max_blocks;
+            int mapped = slot_mapped[slot[i]];
+            for (int b = mapped; b < need; b++) {
+                if (fc <= 0 || b >= max_blocks) { bad = 1; break; }  // the host counters rule this out
+                t[b] = free_stack[--fc];
+            }
+            if (need > mapped) slot_mapped[slot[i]] = need;
+        }
+        seq_row0[S] = run;
+        *free_count = fc;
+        if (bad || run != T) *status = 1;
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < T; r += blockDim.x) {
+        int lo = 0, hi = S;  // last i with seq_row0[i] <= r
+        while (hi - lo > 1) {
+            int mid = (lo + hi) >> 1;
+            if (seq_row0[mid] <= r) lo = mid; else hi = mid;
+        }
+        row_slot[r] = slot[lo];
+        row_pos[r] = pos[lo] + (r - seq_row0[lo]);
+    }
+}
+
+// decode loop feedback: next token = drawn id, position + 1
+__global__ void advance_kernel(int32_t* tokens, const int32_t* ids, int32_t* pos_dev, int S, int advance_pos,
+                               int32_t* ids_log) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= S) return;
+    tokens[i] = ids[i];
+    if (ids_log) ids_log[i] = ids[i];
+    if (advance_pos) pos_dev[i] += 1;
+}
+
+__global__ void synth_kv_kernel(__half* kpool, __half* vpool, const int32_t* table_row, int n_pos, int nKV, int hd,
+                                int block_rows, float sigma, uint64_t seed) {
+    // element index over [pos][kvh][e]
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t n = (size_t)n_pos * nKV * hd;
+    if (i >= n) return;
+    int e = (int)(i % hd), kvh = (int)((i / hd) % nKV), pos = (int)(i / ((size_t)hd * nKV));
+    int blk = table_row[pos / block_rows];
+    size_t off = (((size_t)blk * nKV + kvh) * block_rows + (pos % block_rows)) * hd + e;
+    // two cheap hashed uniforms -> approximately normal (sum of uniforms), enough for synthetic contexts
+    uint64_t z = seed * 0x9E3779B97F4A7C15ull + i;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    float u = 0.f;
+    for (int k = 0; k < 4; k++) u += (float)((z >> (16 * k)) & 0xFFFF) * (1.f / 65536.f);
+    float g = (u - 2.f) * 1.7320508f;  // variance 4/12 -> 1
+    kpool[off] = __float2half_rn(sigma * g);
+    vpool[off] = __float2half_rn(sigma * (float)(((z >> 7) & 0xFFFF) * (1.f / 65536.f) - 0.5f) * 3.4641016f);
+}
+
+__global__ void upload_kv_kernel(__half* kpool, __half* vpool, const int32_t* table_row, const float* keys, const float* vals,
+                                 int base, int n, int nKV, int hd, int block_rows) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t tot = (size_t)n * nKV * hd;
+    if (i >= tot) return;
+    int e = (int)(i % hd), kvh = (int)((i / hd) % nKV), pos = base + (int)(i / ((size_t)hd * nKV));
+    int blk = table_row[pos / block_rows];
+    size_t off = (((size_t)blk * nKV + kvh) * block_rows + (pos % block_rows)) * hd + e;
+    kpool[off] = __float2half_rn(keys[i]);
+    vpool[off] = __float2half_rn(vals[i]);
+}
+
+}  // namespace
+
+struct b200_model {
+    b200_ctx* ctx = nullptr;
+    b200_model_cfg c{};
+    bool finalized = false;
+    DevMat embed, head;
+    float* final_norm = nullptr;
+    std::vector<LayerW> layers;
+    int rot_half = 0;
+
+    // KV
+    std::vector<__half*> kpool, vpool;  // per layer
+    int32_t *table = nullptr, *free_stack = nullptr, *free_count = nullptr, *slot_mapped = nullptr, *status = nullptr;
+    int max_blocks = 0;
+    std::vector<int> h_slot_len, h_slot_mapped;
+    int h_free = 0;
+
+    // step buffers (device)
+    int MR = 0, MLR = 0;  // max rows, max logit rows per head chunk
+    int32_t *d_desc = nullptr, *d_pos = nullptr, *d_tokens = nullptr, *d_seq_row0 = nullptr, *d_row_slot = nullptr,
+            *d_row_pos = nullptr, *d_head_rows = nullptr, *d_row_mask = nullptr, *d_ids = nullptr, *d_ids_log = nullptr;
+    b200_draw* d_draws = nullptr;
+    uint32_t* d_masks = nullptr;
+    size_t masks_cap = 0;
+    float *h = nullptr, *normed = nullptr, *qkv = nullptr, *ctxb = nullptr, *att = nullptr, *gu = nullptr, *mid = nullptr,
+          *hn = nullptr, *logits = nullptr;
+    ActQ aq_h, aq_ctx, aq_mid;
+    __half* split = nullptr;
+    AttnScratch asc;
+    // MoE
+    float *rl = nullptr, *rw = nullptr, *egu_out = nullptr, *eo = nullptr;
+    int32_t *ridx = nullptr, *eoffs = nullptr, *erows = nullptr;
+    ActQ aq_emid;
+    // pinned host staging
+    int32_t* p_desc = nullptr;
+    float* p_logits = nullptr;
+    size_t p_logits_cap = 0;
+    int32_t* p_ids = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    b200_stats_t stats{};
+    size_t weight_bytes = 0, kv_bytes = 0, scratch_bytes = 0;
+    std::vector<void*> allocs;
+
+    int dalloc(void** p, size_t bytes, size_t* tally) {
+        cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+        if (e != cudaSuccess) B200_FAIL(ctx, B200_CUDA_ERROR, "cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
+        allocs.push_back(*p);
+        if (tally) *tally += bytes;
+        return B200_OK;
+    }
+    void dfree(void* p) {
+        if (!p) return;
+        auto it = std::find(allocs.begin(), allocs.end(), p);
+        if (it != allocs.end()) allocs.erase(it);
+        cudaFree(p);
+    }
+};
+
+namespace {
+
+DevMat* tensor_slot(b200_model* m, int which, int layer, int expert, float*** vec, int* veclen) {
+    *vec = nullptr;
+    const b200_model_cfg& c = m->c;
+    if (which == B200_T_EMBED) return &m->embed;
+    if (which == B200_T_LM_HEAD) return &m->head;
+    if (which == B200_T_FINAL_NORM) { *vec = &m->final_norm; *veclen = c.hidden; return nullptr; }
+    if (layer < 0 || layer >= c.n_layers) return nullptr;
+    LayerW& L = m->layers[layer];
+    switch (which) {
+        case B200_T_ATTN_NORM: *vec = &L.attn_norm; *veclen = c.hidden; return nullptr;
+        case B200_T_FFN_NORM: *vec = &L.ffn_norm; *veclen = c.hidden; return nullptr;
+        case B200_T_Q_NORM: *vec = &L.q_norm; *veclen = c.head_dim; return nullptr;
+        case B200_T_K_NORM: *vec = &L.k_norm; *veclen = c.head_dim; return nullptr;
+        case B200_T_WQ: return &L.wq;
+        case B200_T_WK: return &L.wk;
+        case B200_T_WV: return &L.wv;
+        case B200_T_WO: return &L.wo;
+        case B200_T_GATE: return &L.gate;
+        case B200_T_UP: return &L.up;
+        case B200_T_DOWN: return &L.down;
+        case B200_T_ROUTER: return &L.router;
+        case B200_T_EXP_GATE: return expert >= 0 && expert < (int)L.eg.size() ? &L.eg[expert] : nullptr;
+        case B200_T_EXP_UP: return expert >= 0 && expert < (int)L.eu.size() ? &L.eu[expert] : nullptr;
+        case B200_T_EXP_DOWN: return expert >= 0 && expert < (int)L.ed.size() ? &L.ed[expert] : nullptr;
+    }
+    return nullptr;
+}
+
+// expected [rows, cols] of a matrix tensor
+bool expected_shape(const b200_model_cfg& c, int which, int* rows, int* cols) {
+    const int qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim;
+    switch (which) {
+        case B200_T_EMBED: case B200_T_LM_HEAD: *rows = c.vocab; *cols = c.hidden; return true;
+        case B200_T_WQ: *rows = qd; *cols = c.hidden; return true;
+        case B200_T_WK: case B200_T_WV: *rows = kvd; *cols = c.hidden; return true;
+        case B200_T_WO: *rows = c.hidden; *cols = qd; return true;
+        case B200_T_GATE: case B200_T_UP: *rows = c.ffn; *cols = c.hidden; return true;
+        case B200_T_DOWN: *rows = c.hidden; *cols = c.ffn; return true;
+        case B200_T_ROUTER: *rows = c.n_experts; *cols = c.hidden; return true;
+        case B200_T_EXP_GATE: case B200_T_EXP_UP: *rows = c.moe_ffn; *cols = c.hidden; return true;
+        case B200_T_EXP_DOWN: *rows = c.hidden; *cols = c.moe_ffn; return true;
+    }
+    return false;
+}
+
+int prep_mat(b200_model* m, int which, int layer, int expert, int kind, int rows, int cols, DevMat** out) {
+    b200_ctx* ctx = m->ctx;
+    float** vecp;
+    int veclen = 0;
+    float*** vp = &vecp;
+    DevMat* mat = tensor_slot(m, which, layer, expert, vp, &veclen);
+    if (!mat) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tensor %d (layer %d, expert %d) is not a matrix of this model", which, layer, expert);
+    int er, ec;
+    if (!expected_shape(m->c, which, &er, &ec) || er != rows || ec != cols)
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "tensor %d: shape [%d,%d], expected [%d,%d]", which, rows, cols, er, ec);
+    if (kind == B200_K_Q4K && cols % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs cols %% 256 == 0");
+    if (which == B200_T_ROUTER && kind != B200_K_F32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the router stays f32");
+    if (which == B200_T_EMBED && kind == B200_K_Q4K) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the embedding table is f32 or f16");
+    if (mat->p) { m->dfree(mat->p); m->weight_bytes -= mat->bytes; }
+    mat->kind = kind; mat->rows = rows; mat->cols = cols;
+    mat->bytes = mat_bytes(kind, rows, cols);
+    ST_TRY(m->dalloc(&mat->p, mat->bytes, &m->weight_bytes));
+    *out = mat;
+    return B200_OK;
+}
+
+// concatenates matrices of one kind and width row-wise into a new buffer and frees the parts
+int fuse_rows(b200_model* m, std::vector<DevMat*> parts, DevMat* out) {
+    b200_ctx* ctx = m->ctx;
+    size_t bytes = 0;
+    int rows = 0;
+    for (auto* p : parts) {
+        if (!p->present() || p->kind != parts[0]->kind || p->cols != parts[0]->cols)
+            B200_FAIL(ctx, B200_DECLINED, "projection group with mixed kinds or a missing tensor");
+        bytes += p->bytes;
+        rows += p->rows;
+    }
+    out->kind = parts[0]->kind; out->cols = parts[0]->cols; out->rows = rows; out->bytes = bytes;
+    ST_TRY(m->dalloc(&out->p, bytes, &m->weight_bytes));
+    size_t off = 0;
+    for (auto* p : parts) {
+        CUDA_TRY(ctx, cudaMemcpyAsync((char*)out->p + off, p->p, p->bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+        off += p->bytes;
+    }
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    for (auto* p : parts) { m->dfree(p->p); m->weight_bytes -= p->bytes; p->p = nullptr; }
+    return B200_OK;
+}
+
+// dst[T][N] = x . W^T, picking the kernel by the weight kind
+int matmul(b200_model* m, const DevMat& W, const float* xf, ActQ xq, int T, float* dst, int ldd) {
+    b200_ctx* ctx = m->ctx;
+    if (W.kind == B200_K_Q4K) return launch_q4k_matmul(ctx, (const uint8_t*)W.p, W.rows, W.cols, xq, T, dst, ldd, m->c.kernel_class);
+    if (W.kind == B200_K_F16) return launch_f16w_matmul(ctx, (const __half*)W.p, W.rows, W.cols, xf, T, dst, ldd, m->split);
+    return launch_f32w_matmul(ctx, (const float*)W.p, W.rows, W.cols, xf, T, dst, ldd);
+}
+
+int run_layers(b200_model* m, int T, int max_keys) {
+    b200_ctx* ctx = m->ctx;
+    const b200_model_cfg& c = m->c;
+    const int H = c.hidden, nH = c.n_heads, nKV = c.n_kv_heads, hd = c.head_dim, qd = nH * hd, ldq = (nH + 2 * nKV) * hd;
+    const float scale = c.attn_scale != 0.f ? c.attn_scale : (float)(1.0 / std::sqrt((double)hd));
+    const ActQ none{};
+    const float* delta = nullptr;  // pending residual add, fused into the next norm
+    for (int l = 0; l < c.n_layers; l++) {
+        LayerW& L = m->layers[l];
+        const bool q_in = L.qkv.kind == B200_K_Q4K;
+        ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, delta, L.attn_norm, T, H, c.rms_eps, q_in ? nullptr : m->normed,
+                                        q_in ? m->aq_h : none, nullptr));
+        ST_TRY(matmul(m, L.qkv, m->normed, m->aq_h, T, m->qkv, ldq));
+        KVView kv{m->kpool[l], m->vpool[l], m->table, m->max_blocks, c.kv_block_rows, nKV, hd};
+        ST_TRY(launch_qknorm_rope_kvstore(ctx, m->qkv, ldq, T, nH, nKV, hd, m->rot_half, L.inv_freq,
+                                          c.qk_norm ? L.q_norm : nullptr, c.qk_norm ? L.k_norm : nullptr, c.rms_eps,
+                                          m->d_row_slot, m->d_row_pos, kv));
+        const bool o_q = L.wo.kind == B200_K_Q4K;
+        ST_TRY(launch_paged_attention(ctx, m->qkv, ldq, T, nH, nKV, hd, scale, c.attn_softcap, m->d_row_slot, m->d_row_pos,
+                                      max_keys, kv, m->asc, m->ctxb, o_q ? m->aq_ctx : none));
+        ST_TRY(matmul(m, L.wo, m->ctxb, m->aq_ctx, T, m->att, H));
+        if (c.n_experts == 0) {
+            const bool g_q = L.gu.kind == B200_K_Q4K, d_q = L.down.kind == B200_K_Q4K;
+            ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, m->att, L.ffn_norm, T, H, c.rms_eps, g_q ? nullptr : m->normed,
+                                            g_q ? m->aq_h : none, nullptr));
+            ST_TRY(matmul(m, L.gu, m->normed, m->aq_h, T, m->gu, 2 * c.ffn));
+            ST_TRY(launch_swiglu_quant(ctx, m->gu, T, c.ffn, 2 * c.ffn, d_q ? nullptr : m->mid, d_q ? m->aq_mid : none));
+            ST_TRY(matmul(m, L.down, m->mid, m->aq_mid, T, m->att, H));
+        } else {
+            // routed experts (decoder/mlp.go:36-120): f32 router on the f32 normed row, top-k, grouped expert GEMMs,
+            // fold in routing-rank order
+            const int nE = c.n_experts, kk = c.top_k, F = c.moe_ffn;
+            ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, m->att, L.ffn_norm, T, H, c.rms_eps, m->normed, m->aq_h, nullptr));
+            ST_TRY(launch_f32w_matmul(ctx, (const float*)L.router.p, nE, H, m->normed, T, m->rl, nE));
+            ST_TRY(launch_route(ctx, m->rl, T, nE, kk, c.norm_topk, m->ridx, m->rw));
+            ST_TRY(launch_group_experts(ctx, m->ridx, T, kk, nE, m->eoffs, m->erows));
+            const int32_t* rows_tok = m->erows;
+            const int32_t* slot_of = m->erows + (size_t)T * kk;
+            if (L.egu[0].kind != B200_K_Q4K) B200_FAIL(ctx, B200_DECLINED, "routed experts run as Q4_K only");
+            ST_TRY(launch_q4k_matmul_grouped(ctx, L.d_egu_ptrs, nE, 2 * F, H, m->aq_h, m->eoffs, rows_tok, T, m->egu_out, 2 * F));
+            ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, nullptr, m->aq_emid));
+            ST_TRY(launch_q4k_matmul_grouped(ctx, L.d_ed_ptrs, nE, H, F, m->aq_emid, m->eoffs, nullptr, T, m->eo, H));
+            ST_TRY(launch_fold_experts(ctx, m->eo, m->rw, slot_of, T, kk, H, m->att));
+        }
+        delta = m->att;
+    }
+    if (delta) ST_TRY(launch_add(ctx, m->h, delta, (size_t)T * H));
+    return B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_open(int device_ordinal, void* stream, b200_ctx** out) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || device_ordinal < 0 || device_ordinal >= n) return B200_CUDA_ERROR;
+    if (cudaSetDevice(device_ordinal) != cudaSuccess) return B200_CUDA_ERROR;
+    auto* ctx = new b200_ctx();
+    ctx->device = device_ordinal;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device_ordinal) == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
+    if (stream) {
+        ctx->stream = (cudaStream_t)stream;
+    } else {
+        if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) { delete ctx; return B200_CUDA_ERROR; }
+        ctx->own_stream = true;
+    }
+    *out = ctx;
+    return B200_OK;
+}
+
+void b200_close(b200_ctx* ctx) {
+    if (!ctx) return;
+    if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+const char* b200_last_error(b200_ctx* ctx) { return ctx ? ctx->err.c_str() : "no context"; }
+int64_t b200_launch_count(b200_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int b200_model_create(b200_ctx* ctx, const b200_model_cfg* cfg, b200_model** out) {
+    const b200_model_cfg& c = *cfg;
+    if (c.hidden <= 0 || c.n_layers <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.head_dim <= 0 || c.vocab <= 0 ||
+        c.n_heads % c.n_kv_heads || c.n_slots <= 0 || c.ctx_cap <= 0 || c.kv_block_rows <= 0 || c.kv_pool_blocks < 2)
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad model configuration");
+    if (c.kv_dtype != 0) B200_FAIL(ctx, B200_DECLINED, "only the fp16 paged KV cache is built");
+    if (c.tp_size > 1) B200_FAIL(ctx, B200_DECLINED, "tensor parallel shards are built by the multi-GPU driver, not this entry point");
+    if (c.head_dim > 256) B200_FAIL(ctx, B200_DECLINED, "head_dim above 256");
+    const int G = c.n_heads / c.n_kv_heads;
+    const bool fast_attn = (c.head_dim == 64 || c.head_dim == 128) && (G == 1 || G == 2 || G == 4 || G == 8);
+    if (!fast_attn && c.head_dim > 64) B200_FAIL(ctx, B200_DECLINED, "attention shape head_dim=%d group=%d is not built", c.head_dim, G);
+    if (c.n_experts > 512) B200_FAIL(ctx, B200_DECLINED, "more than 512 experts");
+    auto* m = new b200_model();
+    m->ctx = ctx;
+    m->c = c;
+    if (m->c.rotary_dim <= 0) m->c.rotary_dim = c.head_dim;
+    m->rot_half = m->c.rotary_dim / 2;
+    m->layers.resize(c.n_layers);
+    for (auto& L : m->layers) {
+        L.h_inv_freq.resize(m->rot_half);
+        for (int d = 0; d < m->rot_half; d++)  // decoder/ropescale.go:285-290
+            L.h_inv_freq[d] = std::pow((double)c.rope_theta, -(double)(2 * d) / (double)(2 * m->rot_half));
+        if (c.n_experts > 0) { L.eg.resize(c.n_experts); L.eu.resize(c.n_experts); L.ed.resize(c.n_experts); }
+    }
+    *out = m;
+    return B200_OK;
+}
+
+int b200_upload_tensor(b200_model* m, int which, int layer, int expert, int kind, int rows, int cols, const void* host,
+                       size_t bytes) {
+    b200_ctx* ctx = m->ctx;
+    if (m->finalized) B200_FAIL(ctx, B200_BAD_ARGUMENT, "model already finalized");
+    float** vecp = nullptr;
+    int veclen = 0;
+    DevMat* probe = tensor_slot(m, which, layer, expert, &vecp, &veclen);
+    if (vecp) {
+        if (kind != B200_K_F32 || (size_t)rows * cols != (size_t)veclen || bytes != (size_t)veclen * 4)
+            B200_FAIL(ctx, B200_BAD_ARGUMENT, "norm tensor %d must be f32[%d]", which, veclen);
+        if (!*vecp) ST_TRY(m->dalloc((void**)vecp, bytes, &m->weight_bytes));
+        CUDA_TRY(ctx, cudaMemcpy(*vecp, host, bytes, cudaMemcpyHostToDevice));
+        return B200_OK;
+    }
+    (void)probe;
+    DevMat* mat;
+    ST_TRY(prep_mat(m, which, layer, expert, kind, rows, cols, &mat));
+    if (bytes != mat->bytes) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tensor %d: %zu bytes, expected %zu", which, bytes, mat->bytes);
+    CUDA_TRY(ctx, cudaMemcpy(mat->p, host, bytes, cudaMemcpyHostToDevice));
+    return B200_OK;
+}
+
+int b200_synth_tensor(b200_model* m, int which, int layer, int expert, int kind, int rows, int cols, float sigma, uint64_t seed) {
+    b200_ctx* ctx = m->ctx;
+    if (m->finalized) B200_FAIL(ctx, B200_BAD_ARGUMENT, "model already finalized");
+    DevMat* mat;
+    ST_TRY(prep_mat(m, which, layer, expert, kind, rows, cols, &mat));
+    const size_t n = (size_t)rows * cols;
+    if (kind == B200_K_Q4K) return launch_synth_q4k(ctx, (uint8_t*)mat->p, n / 256, sigma, seed);
+    if (kind == B200_K_F16) return launch_synth_f16(ctx, (__half*)mat->p, n, sigma, seed);
+    return launch_synth_normal_f32(ctx, (float*)mat->p, n, sigma, seed);
+}
+
+int b200_set_rope_inv_freq(b200_model* m, int layer, const double* f, int n) {
+    if (n != m->rot_half) B200_FAIL(m->ctx, B200_BAD_ARGUMENT, "inv_freq needs %d entries", m->rot_half);
+    for (int l = 0; l < m->c.n_layers; l++)
+        if (layer < 0 || l == layer) {
+            m->layers[l].h_inv_freq.assign(f, f + n);
+            if (m->layers[l].inv_freq)
+                CUDA_TRY(m->ctx, cudaMemcpy(m->layers[l].inv_freq, f, n * sizeof(double), cudaMemcpyHostToDevice));
+        }
+    return B200_OK;
+}
+
+int b200_model_finalize(b200_model* m, b200_caps* out) {
+    b200_ctx* ctx = m->ctx;
+    const b200_model_cfg& c = m->c;
+    if (m->finalized) B200_FAIL(ctx, B200_BAD_ARGUMENT, "model already finalized");
+    const int H = c.hidden, nH = c.n_heads, nKV = c.n_kv_heads, hd = c.head_dim;
+    if (!m->embed.present() || !m->head.present() || !m->final_norm) B200_FAIL(ctx, B200_DECLINED, "embedding, head or final norm missing");
+    for (int l = 0; l < c.n_layers; l++) {
+        LayerW& L = m->layers[l];
+        if (!L.attn_norm || !L.ffn_norm || (c.qk_norm && (!L.q_norm || !L.k_norm))) B200_FAIL(ctx, B200_DECLINED, "layer %d: norm weights missing", l);
+        if (!L.wo.present()) B200_FAIL(ctx, B200_DECLINED, "layer %d: o projection missing", l);
+        ST_TRY(fuse_rows(m, {&L.wq, &L.wk, &L.wv}, &L.qkv));
+        if (c.n_experts == 0) {
+            if (!L.down.present()) B200_FAIL(ctx, B200_DECLINED, "layer %d: down projection missing", l);
+            ST_TRY(fuse_rows(m, {&L.gate, &L.up}, &L.gu));
+        } else {
+            if (!L.router.present()) B200_FAIL(ctx, B200_DECLINED, "layer %d: router missing", l);
+            L.egu.resize(c.n_experts);
+            std::vector<const uint8_t*> pg(c.n_experts), pd(c.n_experts);
+            for (int e = 0; e < c.n_experts; e++) {
+                if (!L.ed[e].present()) B200_FAIL(ctx, B200_DECLINED, "layer %d expert %d: down missing", l, e);
+                ST_TRY(fuse_rows(m, {&L.eg[e], &L.eu[e]}, &L.egu[e]));
+                pg[e] = (const uint8_t*)L.egu[e].p;
+                pd[e] = (const uint8_t*)L.ed[e].p;
+            }
+            ST_TRY(m->dalloc((void**)&L.d_egu_ptrs, c.n_experts * sizeof(void*), &m->weight_bytes));
+            ST_TRY(m->dalloc((void**)&L.d_ed_ptrs, c.n_experts * sizeof(void*), &m->weight_bytes));
+            CUDA_TRY(ctx, cudaMemcpy(L.d_egu_ptrs, pg.data(), c.n_experts * sizeof(void*), cudaMemcpyHostToDevice));
+            CUDA_TRY(ctx, cudaMemcpy(L.d_ed_ptrs, pd.data(), c.n_experts * sizeof(void*), cudaMemcpyHostToDevice));
+        }
+        ST_TRY(m->dalloc((void**)&L.inv_freq, std::max(1, m->rot_half) * sizeof(double), &m->weight_bytes));
+        CUDA_TRY(ctx, cudaMemcpy(L.inv_freq, L.h_inv_freq.data(), m->rot_half * sizeof(double), cudaMemcpyHostToDevice));
+    }
+    // KV pool
+    m->max_blocks = ceil_div(c.ctx_cap, c.kv_block_rows);
+    const size_t per_layer = (size_t)c.kv_pool_blocks * nKV * c.kv_block_rows * hd * sizeof(__half);
+    size_t free_b = 0, total_b = 0;
+    cudaMemGetInfo(&free_b, &total_b);
+    if (2 * per_layer * c.n_layers + ((size_t)1 << 30) > free_b)
+        B200_FAIL(ctx, B200_DECLINED, "KV pool of %.1f GB does not fit the %.1f GB free on the device",
+                  2.0 * per_layer * c.n_layers / 1e9, free_b / 1e9);
+    m->kpool.resize(c.n_layers);
+    m->vpool.resize(c.n_layers);
+    for (int l = 0; l < c.n_layers; l++) {
+        ST_TRY(m->dalloc((void**)&m->kpool[l], per_layer, &m->kv_bytes));
+        ST_TRY(m->dalloc((void**)&m->vpool[l], per_layer, &m->kv_bytes));
+        // block 0 is the all-zero null block (backend/cuda/kvpool.go:16-27)
+        const size_t blk_bytes = (size_t)nKV * c.kv_block_rows * hd * sizeof(__half);
+        CUDA_TRY(ctx, cudaMemsetAsync(m->kpool[l], 0, blk_bytes, ctx->stream));
+        CUDA_TRY(ctx, cudaMemsetAsync(m->vpool[l], 0, blk_bytes, ctx->stream));
+    }
+    ST_TRY(m->dalloc((void**)&m->table, (size_t)c.n_slots * m->max_blocks * 4, &m->kv_bytes));
+    ST_TRY(m->dalloc((void**)&m->free_stack, (size_t)c.kv_pool_blocks * 4, &m->kv_bytes));
+    ST_TRY(m->dalloc((void**)&m->free_count, 4, nullptr));
+    ST_TRY(m->dalloc((void**)&m->slot_mapped, (size_t)c.n_slots * 4, nullptr));
+    ST_TRY(m->dalloc((void**)&m->status, 4, nullptr));
+    CUDA_TRY(ctx, cudaMemsetAsync(m->status, 0, 4, ctx->stream));
+    m->h_slot_len.assign(c.n_slots, 0);
+    m->h_slot_mapped.assign(c.n_slots, 0);
+    // step buffers
+    const int MR = m->MR = std::max(1, c.max_rows);
+    const int MLR = m->MLR = std::min(MR, std::max(c.n_slots, 64));
+    size_t* sb = &m->scratch_bytes;
+    const int qd = nH * hd, ldq = (nH + 2 * nKV) * hd;
+    const int F = c.n_experts ? 0 : c.ffn;
+    ST_TRY(m->dalloc((void**)&m->d_desc, (size_t)(2 + 3 * MR) * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->d_pos, (size_t)MR * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->d_tokens, (size_t)MR * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->d_seq_row0, (size_t)(MR + 1) * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->d_row_slot, (size_t)MR * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->d_row_pos, (size_t)MR * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->d_head_rows, (size_t)MR * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->d_row_mask, (size_t)MR * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->d_ids, (size_t)MR * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->d_draws, (size_t)MR * sizeof(b200_draw), sb));
+    ST_TRY(m->dalloc((void**)&m->h, (size_t)MR * H * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->normed, (size_t)MR * H * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->qkv, (size_t)MR * ldq * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->ctxb, (size_t)MR * qd * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->att, (size_t)MR * H * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->aq_h.codes, (size_t)MR * H, sb));
+    ST_TRY(m->dalloc((void**)&m->aq_h.scales, (size_t)MR * 2 * ceil_div(H, 32) * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->aq_ctx.codes, (size_t)MR * qd, sb));
+    ST_TRY(m->dalloc((void**)&m->aq_ctx.scales, (size_t)MR * 2 * ceil_div(qd, 32) * 4, sb));
+    if (F) {
+        ST_TRY(m->dalloc((void**)&m->gu, (size_t)MR * 2 * F * 4, sb));
+        ST_TRY(m->dalloc((void**)&m->mid, (size_t)MR * F * 4, sb));
+        ST_TRY(m->dalloc((void**)&m->aq_mid.codes, (size_t)MR * F, sb));
+        ST_TRY(m->dalloc((void**)&m->aq_mid.scales, (size_t)MR * 2 * ceil_div(F, 32) * 4, sb));
+    } else {
+        const int nE = c.n_experts, kk = c.top_k, EF = c.moe_ffn;
+        ST_TRY(m->dalloc((void**)&m->rl, (size_t)MR * nE * 4, sb));
+        ST_TRY(m->dalloc((void**)&m->rw, (size_t)MR * kk * 4, sb));
+        ST_TRY(m->dalloc((void**)&m->ridx, (size_t)MR * kk * 4, sb));
+        ST_TRY(m->dalloc((void**)&m->eoffs, (size_t)(nE + 1) * 4, sb));
+        ST_TRY(m->dalloc((void**)&m->erows, (size_t)2 * MR * kk * 4, sb));
+        ST_TRY(m->dalloc((void**)&m->egu_out, (size_t)MR * kk * 2 * EF * 4, sb));
+        ST_TRY(m->dalloc((void**)&m->eo, (size_t)MR * kk * H * 4, sb));
+        ST_TRY(m->dalloc((void**)&m->aq_emid.codes, (size_t)MR * kk * EF, sb));
+        ST_TRY(m->dalloc((void**)&m->aq_emid.scales, (size_t)MR * kk * 2 * ceil_div(EF, 32) * 4, sb));
+    }
+    m->asc.max_splits = ceil_div(c.ctx_cap, attn_split_keys());
+    ST_TRY(m->dalloc((void**)&m->asc.partial, attn_scratch_floats(MR, nH, hd, m->asc.max_splits) * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->hn, (size_t)MLR * H * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->logits, (size_t)MLR * c.vocab * 4, sb));
+    ST_TRY(m->dalloc((void**)&m->split, (size_t)2 * MLR * H * 2, sb));
+    CUDA_TRY(ctx, cudaMallocHost((void**)&m->p_desc, (size_t)(2 + 3 * MR) * 4 + (size_t)MR * (4 + 4 + 4 + sizeof(b200_draw))));
+    CUDA_TRY(ctx, cudaMallocHost((void**)&m->p_ids, (size_t)MR * 4));
+    CUDA_TRY(ctx, cudaEventCreate(&m->ev0));
+    CUDA_TRY(ctx, cudaEventCreate(&m->ev1));
+    m->finalized = true;
+    ST_TRY(b200_reset(m));
+    if (out) {
+        memset(out, 0, sizeof *out);
+        out->context_cap = c.ctx_cap;
+        out->kv_slots = c.n_slots;
+        out->batch_lo = 2;  // BatchStepRange = (2, KVSlots), backend/cuda/batchstep.go:36-44
+        out->batch_hi = c.n_slots;
+        out->has_fast_prefill = 0;
+        out->fast_prefill_floor = 0;
+        out->tail_min_rows = 1;
+        out->batch_greedy_draw = 1;
+        out->weight_bytes = (int64_t)m->weight_bytes;
+        out->kv_bytes = (int64_t)m->kv_bytes;
+        out->scratch_bytes = (int64_t)m->scratch_bytes;
+    }
+    return B200_OK;
+}
+
+void b200_model_free(b200_model* m) {
+    if (!m) return;
+    cudaStreamSynchronize(m->ctx->stream);
+    for (void* p : m->allocs) cudaFree(p);
+    if (m->p_desc) cudaFreeHost(m->p_desc);
+    if (m->p_ids) cudaFreeHost(m->p_ids);
+    if (m->p_logits) cudaFreeHost(m->p_logits);
+    if (m->ev0) cudaEventDestroy(m->ev0);
+    if (m->ev1) cudaEventDestroy(m->ev1);
+    delete m;
+}
+
+int b200_kv_slots(b200_model* m) { return m->c.n_slots; }
+
+int b200_reset_slot(b200_model* m, int slot) {
+    b200_ctx* ctx = m->ctx;
+    if (!m->finalized || slot < 0 || slot >= m->c.n_slots) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad slot %d", slot);
+    reset_slot_kernel<<<1, 1, 0, ctx->stream>>>(m->free_stack, m->free_count, m->table, m->max_blocks, m->slot_mapped, slot);
+    LAUNCH_CHECK(ctx);
+    m->h_free += m->h_slot_mapped[slot];
+    m->h_slot_mapped[slot] = 0;
+    m->h_slot_len[slot] = 0;
+    return B200_OK;
+}
+
+int b200_reset(b200_model* m) {
+    b200_ctx* ctx = m->ctx;
+    if (!m->finalized) B200_FAIL(ctx, B200_BAD_ARGUMENT, "model not finalized");
+    const size_t tn = (size_t)m->c.n_slots * m->max_blocks;
+    const size_t n = std::max<size_t>(std::max<size_t>(tn, m->c.kv_pool_blocks), m->c.n_slots);
+    init_pool_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(m->free_stack, m->free_count, m->c.kv_pool_blocks,
+                                                                           m->table, tn, m->slot_mapped, m->c.n_slots);
+    LAUNCH_CHECK(ctx);
+    std::fill(m->h_slot_len.begin(), m->h_slot_len.end(), 0);
+    std::fill(m->h_slot_mapped.begin(), m->h_slot_mapped.end(), 0);
+    m->h_free = m->c.kv_pool_blocks - 1;
+    return B200_OK;
+}
+
+int b200_block_table(b200_model* m, int slot, int32_t* out, int n) {
+    b200_ctx* ctx = m->ctx;
+    if (!m->finalized || slot < 0 || slot >= m->c.n_slots) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad slot %d", slot);
+    const int k = std::min(n, m->max_blocks);
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpy(out, m->table + (size_t)slot * m->max_blocks, (size_t)k * 4, cudaMemcpyDeviceToHost));
+    for (int i = k; i < n; i++) out[i] = 0;
+    return B200_OK;
+}
+
+}  // extern "C"
+
+namespace {
+
+// host-side block accounting for rows [0, end) of a slot; returns blocks still to map
+int blocks_needed(const b200_model* m, int slot, int end) {
+    return std::max(0, ceil_div(end, m->c.kv_block_rows) - m->h_slot_mapped[slot]);
+}
+
+// Maps the blocks of rows [0, end) of one slot on the device (used by the KV upload/synthesis entry points).
+int map_slot_rows(b200_model* m, int slot, int end) {
+    b200_ctx* ctx = m->ctx;
+    const int need = blocks_needed(m, slot, end);
+    if (need > m->h_free) { m->stats.kv_pool_full++; B200_FAIL(ctx, B200_KV_POOL_FULL, "kv pool full: %d blocks needed, %d free", need, m->h_free); }
+    if (need == 0) return B200_OK;
+    int32_t* d = m->p_desc;
+    d[0] = 1; d[1] = 1; d[2] = slot; d[3] = end - 1; d[4] = 1;
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->d_desc, d, 5 * 4, cudaMemcpyHostToDevice, ctx->stream));
+    prepare_step_kernel<<<1, 256, 0, ctx->stream>>>(m->d_desc, m->d_pos, 0, m->table, m->max_blocks, m->c.kv_block_rows,
+                                                    m->slot_mapped, m->free_stack, m->free_count, m->d_seq_row0, m->d_row_slot,
+                                                    m->d_row_pos, m->status);
+    LAUNCH_CHECK(ctx);
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));  // p_desc is reused by the next call
+    m->h_free -= need;
+    m->h_slot_mapped[slot] += need;
+    return B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_synth_kv(b200_model* m, int slot, int n_pos, float sigma, uint64_t seed) {
+    b200_ctx* ctx = m->ctx;
+    const b200_model_cfg& c = m->c;
+    if (!m->finalized || slot < 0 || slot >= c.n_slots || n_pos < 0 || n_pos > c.ctx_cap) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad slot or length");
+    if (n_pos == 0) return B200_OK;
+    ST_TRY(map_slot_rows(m, slot, n_pos));
+    const size_t n = (size_t)n_pos * c.n_kv_heads * c.head_dim;
+    for (int l = 0; l < c.n_layers; l++) {
+        synth_kv_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(m->kpool[l], m->vpool[l],
+                                                                              m->table + (size_t)slot * m->max_blocks, n_pos,
+                                                                              c.n_kv_heads, c.head_dim, c.kv_block_rows, sigma,
+                                                                              seed * 1315423911ull + (uint64_t)l);
+        LAUNCH_CHECK(ctx);
+    }
+    m->h_slot_len[slot] = std::max(m->h_slot_len[slot], n_pos);
+    return B200_OK;
+}
+
+int b200_upload_kv(b200_model* m, int slot, int layer, int base, int n, const float* keys, const float* vals) {
+    b200_ctx* ctx = m->ctx;
+    const b200_model_cfg& c = m->c;
+    if (!m->finalized || slot < 0 || slot >= c.n_slots || layer < 0 || layer >= c.n_layers || base < 0 || n <= 0 || base + n > c.ctx_cap)
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad slot, layer or range");
+    ST_TRY(map_slot_rows(m, slot, base + n));
+    const size_t cnt = (size_t)n * c.n_kv_heads * c.head_dim;
+    float *dk = nullptr, *dv = nullptr;
+    CUDA_TRY(ctx, cudaMalloc(&dk, cnt * 4));
+    CUDA_TRY(ctx, cudaMalloc(&dv, cnt * 4));
+    CUDA_TRY(ctx, cudaMemcpyAsync(dk, keys, cnt * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(dv, vals, cnt * 4, cudaMemcpyHostToDevice, ctx->stream));
+    upload_kv_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, ctx->stream>>>(m->kpool[layer], m->vpool[layer],
+                                                                             m->table + (size_t)slot * m->max_blocks, dk, dv, base, n,
+                                                                             c.n_kv_heads, c.head_dim, c.kv_block_rows);
+    LAUNCH_CHECK(ctx);
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    cudaFree(dk);
+    cudaFree(dv);
+    m->h_slot_len[slot] = std::max(m->h_slot_len[slot], base + n);
+    return B200_OK;
+}
+
+int b200_step_ragged(b200_model* m, int n_seqs, const int32_t* slot, const int32_t* pos, const int32_t* n_rows,
+                     const int32_t* prefill_prompt_len, const uint8_t* prefill_last, const float* embs, const int32_t* token_ids,
+                     const b200_draw* draws, const int32_t* mask_index, const uint32_t* logit_mask, int n_masks, float* logits_out,
+                     int32_t* ids_out, int32_t* n_logit_rows_out) {
+    b200_ctx* ctx = m->ctx;
+    const b200_model_cfg& c = m->c;
+    if (!m->finalized) B200_FAIL(ctx, B200_BAD_ARGUMENT, "model not finalized");
+    if (n_seqs <= 0 || (!embs) == (!token_ids)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "a step takes exactly one of embs / token_ids");
+    const int H = c.hidden, V = c.vocab;
+    // ---- checks on the sequences alone (backend/cuda/batchstep.go:184-211) and the block budget ----
+    int T = 0, need = 0, max_keys = 0;
+    {
+        std::vector<char> seen(c.n_slots, 0);
+        for (int i = 0; i < n_seqs; i++) {
+            if (slot[i] < 0 || slot[i] >= c.n_slots || seen[slot[i]]) B200_FAIL(ctx, B200_BAD_ARGUMENT, "sequence %d: slot %d out of range or repeated", i, slot[i]);
+            seen[slot[i]] = 1;
+            if (n_rows[i] <= 0 || pos[i] < 0 || pos[i] + n_rows[i] > c.ctx_cap)
+                B200_FAIL(ctx, B200_BAD_ARGUMENT, "sequence %d: rows [%d,%d) outside the context cap %d", i, pos[i], pos[i] + n_rows[i], c.ctx_cap);
+            if (pos[i] > m->h_slot_len[slot[i]]) B200_FAIL(ctx, B200_BAD_ARGUMENT, "sequence %d: position %d past the slot's %d stored rows", i, pos[i], m->h_slot_len[slot[i]]);
+            const int pl = prefill_prompt_len ? prefill_prompt_len[i] : 0;
+            if (pl > 0) {
+                const bool last = prefill_last && prefill_last[i];
+                const bool has_draw = draws && draws[i].kind != B200_DRAW_LOGITS;
+                if (i != 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "a step takes one prefill chunk and it goes first");
+                if (has_draw) B200_FAIL(ctx, B200_BAD_ARGUMENT, "a prefill chunk carries no draw");
+                if (pl < pos[i] + n_rows[i]) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the chunk ends at %d, past its prompt's %d", pos[i] + n_rows[i], pl);
+                if (last != (pos[i] + n_rows[i] == pl)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the chunk ends at %d of a %d-row prompt with Last %d", pos[i] + n_rows[i], pl, (int)last);
+            }
+            T += n_rows[i];
+            need += blocks_needed(m, slot[i], pos[i] + n_rows[i]);
+            max_keys = std::max(max_keys, pos[i] + n_rows[i]);
+        }
+    }
+    if (T > m->MR) B200_FAIL(ctx, B200_BAD_ARGUMENT, "%d rows exceed max_rows %d", T, m->MR);
+    if (token_ids)
+        for (int r = 0; r < T; r++)
+            if (token_ids[r] < 0 || token_ids[r] >= V) B200_FAIL(ctx, B200_BAD_ARGUMENT, "token id %d out of range", token_ids[r]);
+    if (need > m->h_free) { m->stats.kv_pool_full++; B200_FAIL(ctx, B200_KV_POOL_FULL, "kv pool full: %d blocks needed, %d free", need, m->h_free); }
+
+    // ---- rows that reach the LM head: logits rows first, then the drawn rows ----
+    std::vector<int> head_rows, head_seq;
+    int n_out = 0;
+    {
+        std::vector<int> draw_rows, draw_seq;
+        int r0 = 0;
+        for (int i = 0; i < n_seqs; i++) {
+            const int pl = prefill_prompt_len ? prefill_prompt_len[i] : 0;
+            const int dk = draws ? draws[i].kind : B200_DRAW_LOGITS;
+            const int lastr = r0 + n_rows[i] - 1;
+            if (pl > 0) {
+                if (prefill_last && prefill_last[i]) { head_rows.push_back(lastr); head_seq.push_back(i); }
+            } else {
+                for (int r = r0; r < lastr; r++) { head_rows.push_back(r); head_seq.push_back(i); }
+                if (dk == B200_DRAW_LOGITS) { head_rows.push_back(lastr); head_seq.push_back(i); }
+                else { draw_rows.push_back(lastr); draw_seq.push_back(i); }
+            }
+            r0 += n_rows[i];
+        }
+        n_out = (int)head_rows.size();
+        head_rows.insert(head_rows.end(), draw_rows.begin(), draw_rows.end());
+        head_seq.insert(head_seq.end(), draw_seq.begin(), draw_seq.end());
+    }
+    const int R = (int)head_rows.size();
+
+    // ---- upload the step descriptor ----
+    int32_t* d = m->p_desc;
+    d[0] = n_seqs; d[1] = T;
+    memcpy(d + 2, slot, (size_t)n_seqs * 4);
+    memcpy(d + 2 + n_seqs, pos, (size_t)n_seqs * 4);
+    memcpy(d + 2 + 2 * n_seqs, n_rows, (size_t)n_seqs * 4);
+    CUDA_TRY(ctx, cudaEventRecord(m->ev0, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->d_desc, d, (size_t)(2 + 3 * n_seqs) * 4, cudaMemcpyHostToDevice, ctx->stream));
+    int32_t* p_tail = d + 2 + 3 * m->MR;  // head_rows[MR], row_mask[MR], tokens[MR], draws[MR]
+    int32_t* p_head = p_tail;
+    int32_t* p_mask = p_tail + m->MR;
+    int32_t* p_tok = p_tail + 2 * m->MR;
+    b200_draw* p_draw = (b200_draw*)(p_tail + 3 * m->MR);
+    for (int j = 0; j < R; j++) {
+        p_head[j] = head_rows[j];
+        p_mask[j] = (mask_index && logit_mask && mask_index[head_seq[j]] >= 0 && mask_index[head_seq[j]] < n_masks) ? mask_index[head_seq[j]] : -1;
+        p_draw[j] = (j >= n_out) ? draws[head_seq[j]] : b200_draw{B200_DRAW_LOGITS, 0, 0, 0, 0};
+    }
+    bool any_mask = false;
+    for (int j = 0; j < R; j++) any_mask |= p_mask[j] >= 0;
+    if (R) {
+        CUDA_TRY(ctx, cudaMemcpyAsync(m->d_head_rows, p_head, (size_t)R * 4, cudaMemcpyHostToDevice, ctx->stream));
+        CUDA_TRY(ctx, cudaMemcpyAsync(m->d_row_mask, p_mask, (size_t)R * 4, cudaMemcpyHostToDevice, ctx->stream));
+        CUDA_TRY(ctx, cudaMemcpyAsync(m->d_draws, p_draw, (size_t)R * sizeof(b200_draw), cudaMemcpyHostToDevice, ctx->stream));
+    }
+    if (any_mask) {
+        const size_t mb = (size_t)n_masks * ((V + 31) / 32) * 4;
+        if (mb > m->masks_cap) {
+            if (m->d_masks) m->dfree(m->d_masks);
+            ST_TRY(m->dalloc((void**)&m->d_masks, mb, &m->scratch_bytes));
+            m->masks_cap = mb;
+        }
+        CUDA_TRY(ctx, cudaMemcpyAsync(m->d_masks, logit_mask, mb, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    if (token_ids) {
+        memcpy(p_tok, token_ids, (size_t)T * 4);
+        CUDA_TRY(ctx, cudaMemcpyAsync(m->d_tokens, p_tok, (size_t)T * 4, cudaMemcpyHostToDevice, ctx->stream));
+    } else {
+        CUDA_TRY(ctx, cudaMemcpyAsync(m->h, embs, (size_t)T * H * 4, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    // ---- device: map blocks, build row arrays, run the layers ----
+    prepare_step_kernel<<<1, 256, 0, ctx->stream>>>(m->d_desc, m->d_pos, 0, m->table, m->max_blocks, c.kv_block_rows,
+                                                    m->slot_mapped, m->free_stack, m->free_count, m->d_seq_row0, m->d_row_slot,
+                                                    m->d_row_pos, m->status);
+    LAUNCH_CHECK(ctx);
+    // the host counters follow what the kernel does
+    for (int i = 0; i < n_seqs; i++) {
+        const int nb = blocks_needed(m, slot[i], pos[i] + n_rows[i]);
+        m->h_free -= nb;
+        m->h_slot_mapped[slot[i]] += nb;
+        m->h_slot_len[slot[i]] = std::max(m->h_slot_len[slot[i]], pos[i] + n_rows[i]);
+    }
+    if (token_ids) ST_TRY(launch_embed_gather(ctx, m->embed.p, m->embed.kind, m->d_tokens, T, H, c.embed_scale, m->h));
+    ST_TRY(run_layers(m, T, max_keys));
+    // ---- head, in chunks of MLR rows ----
+    if ((size_t)std::max(n_out, 1) * V * 4 > m->p_logits_cap) {
+        if (m->p_logits) cudaFreeHost(m->p_logits);
+        m->p_logits_cap = (size_t)std::max(n_out, 1) * V * 4;
+        CUDA_TRY(ctx, cudaMallocHost((void**)&m->p_logits, m->p_logits_cap));
+    }
+    for (int j0 = 0; j0 < R; j0 += m->MLR) {
+        const int rn = std::min(m->MLR, R - j0);
+        const bool hq = m->head.kind == B200_K_Q4K;
+        ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, nullptr, m->final_norm, rn, H, c.rms_eps, hq ? nullptr : m->hn,
+                                        hq ? m->aq_h : ActQ{}, m->d_head_rows + j0));
+        ST_TRY(matmul(m, m->head, m->hn, m->aq_h, rn, m->logits, V));
+        if (c.final_softcap > 0.f) ST_TRY(launch_softcap(ctx, m->logits, (size_t)rn * V, c.final_softcap));
+        if (any_mask) ST_TRY(launch_mask_logits(ctx, m->logits, rn, V, m->d_row_mask + j0, m->d_masks));
+        const int out_here = std::max(0, std::min(n_out, j0 + rn) - j0);
+        if (out_here && logits_out)
+            CUDA_TRY(ctx, cudaMemcpyAsync(m->p_logits + (size_t)j0 * V, m->logits, (size_t)out_here * V * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        if (j0 + rn > n_out) ST_TRY(launch_draw(ctx, m->logits, rn, V, m->d_draws + j0, m->d_ids + j0, nullptr));
+    }
+    if (R > n_out) CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids, m->d_ids, (size_t)R * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaEventRecord(m->ev1, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (n_out && logits_out) memcpy(logits_out, m->p_logits, (size_t)n_out * V * 4);
+    if (ids_out) {
+        for (int i = 0; i < n_seqs; i++) ids_out[i] = -1;
+        for (int j = n_out; j < R; j++) ids_out[head_seq[j]] = m->p_ids[j];
+    }
+    if (n_logit_rows_out) *n_logit_rows_out = n_out;
+    float ms = 0;
+    cudaEventElapsedTime(&ms, m->ev0, m->ev1);
+    m->stats.steps++;
+    m->stats.rows += T;
+    if (prefill_prompt_len && prefill_prompt_len[0] > 0) m->stats.prefill_rows += n_rows[0];
+    m->stats.last_step_device_ms = ms;
+    return B200_OK;
+}
+
+int b200_forward(b200_model* m, int slot, const float* emb, int token_id, int pos, int out_kind, float* logits_out, int32_t* id_out) {
+    const int32_t one = 1, s = slot, p = pos, tok = token_id;
+    b200_draw dr{out_kind == 1 ? B200_DRAW_GREEDY : B200_DRAW_LOGITS, 0, 0, 0, 0};
+    int32_t id = -1;
+    // ForwardNoLogits still runs the LM head here; its result is simply not copied out
+    int st = b200_step_ragged(m, 1, &s, &p, &one, nullptr, nullptr, emb, emb ? nullptr : &tok, &dr, nullptr, nullptr, 0,
+                              out_kind == 0 ? logits_out : nullptr, &id, nullptr);
+    if (id_out) *id_out = id;
+    return st;
+}
+
+int b200_prefill_last(b200_model* m, int slot, int n, const float* embs, const int32_t* token_ids, int start_pos, float* logits_out) {
+    const int32_t s = slot, p = start_pos, nr = n, pl = start_pos + n;
+    const uint8_t last = 1;
+    return b200_step_ragged(m, 1, &s, &p, &nr, &pl, &last, embs, token_ids, nullptr, nullptr, nullptr, 0, logits_out, nullptr, nullptr);
+}
+
+int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, const int32_t* pos0, const int32_t* first_ids, int steps,
+                            int advance_pos, int32_t* ids_out, float* ms_out) {
+    b200_ctx* ctx = m->ctx;
+    const b200_model_cfg& c = m->c;
+    if (!m->finalized || n_seqs <= 0 || n_seqs > m->MR || n_seqs > m->MLR || steps <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad decode loop arguments");
+    const int H = c.hidden, V = c.vocab, S = n_seqs;
+    int need = 0, max_keys = 0;
+    {
+        std::vector<char> seen(c.n_slots, 0);
+        for (int i = 0; i < S; i++) {
+            if (slot[i] < 0 || slot[i] >= c.n_slots || seen[slot[i]]) B200_FAIL(ctx, B200_BAD_ARGUMENT, "slot %d out of range or repeated", slot[i]);
+            seen[slot[i]] = 1;
+            const int end = pos0[i] + (advance_pos ? steps : 1);
+            if (pos0[i] < 0 || end > c.ctx_cap || pos0[i] > m->h_slot_len[slot[i]]) B200_FAIL(ctx, B200_BAD_ARGUMENT, "sequence %d outside its slot", i);
+            if (first_ids[i] < 0 || first_ids[i] >= V) B200_FAIL(ctx, B200_BAD_ARGUMENT, "token id out of range");
+            need += blocks_needed(m, slot[i], end);
+            max_keys = std::max(max_keys, end);
+        }
+    }
+    if (need > m->h_free) { m->stats.kv_pool_full++; B200_FAIL(ctx, B200_KV_POOL_FULL, "kv pool full: %d blocks needed, %d free", need, m->h_free); }
+    if (ids_out && !m->d_ids_log) ST_TRY(m->dalloc((void**)&m->d_ids_log, (size_t)m->MR * 4, &m->scratch_bytes));
+    int32_t* d = m->p_desc;
+    d[0] = S; d[1] = S;
+    memcpy(d + 2, slot, (size_t)S * 4);
+    memcpy(d + 2 + S, pos0, (size_t)S * 4);
+    for (int i = 0; i < S; i++) d[2 + 2 * S + i] = 1;
+    int32_t* p_tail = d + 2 + 3 * m->MR;
+    b200_draw* p_draw = (b200_draw*)(p_tail + 3 * m->MR);
+    for (int i = 0; i < S; i++) { p_tail[i] = i; p_tail[2 * m->MR + i] = first_ids[i]; p_draw[i] = b200_draw{B200_DRAW_GREEDY, 0, 0, 0, 0}; }
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->d_desc, d, (size_t)(2 + 3 * S) * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->d_pos, pos0, (size_t)S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->d_head_rows, p_tail, (size_t)S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->d_tokens, p_tail + 2 * m->MR, (size_t)S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->d_draws, p_draw, (size_t)S * sizeof(b200_draw), cudaMemcpyHostToDevice, ctx->stream));
+    std::vector<int32_t> log;
+    if (ids_out) log.resize((size_t)steps * S);
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    CUDA_TRY(ctx, cudaEventRecord(m->ev0, ctx->stream));
+    for (int st = 0; st < steps; st++) {
+        prepare_step_kernel<<<1, 256, 0, ctx->stream>>>(m->d_desc, m->d_pos, 1, m->table, m->max_blocks, c.kv_block_rows,
+                                                        m->slot_mapped, m->free_stack, m->free_count, m->d_seq_row0,
+                                                        m->d_row_slot, m->d_row_pos, m->status);
+        LAUNCH_CHECK(ctx);
+        ST_TRY(launch_embed_gather(ctx, m->embed.p, m->embed.kind, m->d_tokens, S, H, c.embed_scale, m->h));
+        ST_TRY(run_layers(m, S, max_keys));
+        const bool hq = m->head.kind == B200_K_Q4K;
+        ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, nullptr, m->final_norm, S, H, c.rms_eps, hq ? nullptr : m->hn,
+                                        hq ? m->aq_h : ActQ{}, m->d_head_rows));
+        ST_TRY(matmul(m, m->head, m->hn, m->aq_h, S, m->logits, V));
+        if (c.final_softcap > 0.f) ST_TRY(launch_softcap(ctx, m->logits, (size_t)S * V, c.final_softcap));
+        ST_TRY(launch_draw(ctx, m->logits, S, V, m->d_draws, m->d_ids, nullptr));
+        advance_kernel<<<ceil_div(S, 256), 256, 0, ctx->stream>>>(m->d_tokens, m->d_ids, m->d_pos, S, advance_pos, ids_out ? m->d_ids_log : nullptr);
+        LAUNCH_CHECK(ctx);
+        if (ids_out) CUDA_TRY(ctx, cudaMemcpyAsync(log.data() + (size_t)st * S, m->d_ids_log, (size_t)S * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    CUDA_TRY(ctx, cudaEventRecord(m->ev1, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    float ms = 0;
+    cudaEventElapsedTime(&ms, m->ev0, m->ev1);
+    if (ms_out) *ms_out = ms;
+    if (ids_out) memcpy(ids_out, log.data(), log.size() * 4);
+    for (int i = 0; i < S; i++) {
+        const int end = pos0[i] + (advance_pos ? steps : 1);
+        const int nb = blocks_needed(m, slot[i], end);
+        m->h_free -= nb;
+        m->h_slot_mapped[slot[i]] += nb;
+        m->h_slot_len[slot[i]] = std::max(m->h_slot_len[slot[i]], end);
+    }
+    m->stats.steps += steps;
+    m->stats.rows += (int64_t)steps * S;
+    m->stats.last_step_device_ms = ms / steps;
+    return B200_OK;
+}
+
+int b200_stats(b200_model* m, b200_stats_t* out) {
+    *out = m->stats;
+    out->kernel_launches = m->ctx->launches;
+    out->kv_blocks_in_use = m->c.kv_pool_blocks - 1 - m->h_free;
+    return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,480 @@
+// gemm.cu — weight matmuls of the step.
+//
+// Q4_K x per-32-int8 activations, exact class (backend/cuda/actgroup.cu:311-355 rowQ4K's arithmetic):
+//   dst[t][n] = sum over groups g, ascending:  fma(idot_g, (d*sc_g)*aS[t][g], .) then fma(-(dmin*m_g), asum[t][g], .)
+// with idot_g the exact int32 dot of 32 weight codes and 32 activation codes. The integer dots run on the
+// tensor cores (mma.sync m16n8k32 u8 x s8), the per-group rescale on the CUDA cores. Weights are the MMA's
+// 16-row operand, packed tokens its 8-column operand, so one warp streams 16 weight rows once for up to
+// 8*NT tokens. With SPLITK (small token counts, HBM-bound) the 8 warps of a CTA take super-blocks
+// round-robin and fold their partials in warp order; without it every (row, token) sum is one ascending
+// chain, the same order the CPU oracle uses, so the result is bit-identical to it.
+//
+// f16 weights (LM head): mma.sync m16n8k16 with the f32 activation split into f16 hi + lo parts, fp32
+// accumulate. f32 weights (router, f32 test models): f64 accumulate on the CUDA cores.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ unsigned q4k_byte(int k, unsigned s0, unsigned s1, unsigned s2) {
+    unsigned w = k < 4 ? s0 : (k < 8 ? s1 : s2);
+    return (w >> ((k & 3) << 3)) & 0xffu;
+}
+
+// 6-bit scale and minimum of sub-block j from the 12 packed bytes (ggml get_scale_min_k4;
+// backend/cuda/kernels/ks_a1_test.go:62-67).
+__device__ __forceinline__ void q4k_scale_min(int j, unsigned s0, unsigned s1, unsigned s2, int* sc, int* m) {
+    if (j < 4) {
+        *sc = (int)(q4k_byte(j, s0, s1, s2) & 63u);
+        *m = (int)(q4k_byte(j + 4, s0, s1, s2) & 63u);
+    } else {
+        unsigned hi = q4k_byte(j + 4, s0, s1, s2);
+        *sc = (int)((hi & 0x0Fu) | ((q4k_byte(j - 4, s0, s1, s2) >> 6) << 4));
+        *m = (int)((hi >> 4) | ((q4k_byte(j, s0, s1, s2) >> 6) << 4));
+    }
+}
+
+__device__ __forceinline__ float h2f_bits(unsigned short b) { return __half2float(__ushort_as_half(b)); }
+
+#define MAGIC_I 0x4B400000
+#define MAGIC_F 12582912.0f
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// grid.x: 16-row weight tiles (8 per CTA without SPLITK, 1 per CTA with it); grid.y: token tiles of 8*NT;
+// grid.z: experts when GROUPED.
+template <int NT, bool SPLITK, bool GROUPED>
+__global__ void __launch_bounds__(256) q4k_gemm_mma_kernel(const uint8_t* __restrict__ W, const uint8_t* const* __restrict__ Wptrs,
+                                                           int N, int nSB, const int8_t* __restrict__ codes,
+                                                           const float* __restrict__ scales, int T,
+                                                           const int32_t* __restrict__ offs, const int32_t* __restrict__ rows,
+                                                           float* __restrict__ dst, int ldd) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tig = lane & 3;
+    const int n0 = SPLITK ? blockIdx.x * 16 : (blockIdx.x * 8 + warp) * 16;
+    if (!SPLITK && n0 >= N) return;
+    int t_base, t_end;
+    const uint8_t* Wm = W;
+    if (GROUPED) {
+        const int e = blockIdx.z;
+        t_base = offs[e] + blockIdx.y * 8 * NT;
+        t_end = offs[e + 1];
+        if (t_base >= t_end) return;
+        Wm = Wptrs[e];
+    } else {
+        t_base = blockIdx.y * 8 * NT;
+        t_end = T;
+    }
+    const int K = nSB * 256, nG = nSB * 8;
+    const int r0 = min(n0 + gid, N - 1), r1 = min(n0 + gid + 8, N - 1);
+    const uint8_t* w0 = Wm + (size_t)r0 * nSB * 144;
+    const uint8_t* w1 = Wm + (size_t)r1 * nSB * 144;
+
+    const int8_t* ab[NT];   // activation codes of the token this lane feeds the MMA with
+    const float* sc0[NT];   // scale rows of the two tokens this lane's accumulators belong to
+    const float* sc1[NT];
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        int tb = min(t_base + 8 * j + gid, t_end - 1);
+        int tc0 = min(t_base + 8 * j + 2 * tig, t_end - 1), tc1 = min(t_base + 8 * j + 2 * tig + 1, t_end - 1);
+        if (GROUPED && rows) { tb = rows[tb]; tc0 = rows[tc0]; tc1 = rows[tc1]; }
+        ab[j] = codes + (size_t)tb * K + 8 * tig;
+        sc0[j] = scales + (size_t)tc0 * 2 * nG;
+        sc1[j] = scales + (size_t)tc1 * 2 * nG;
+        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    }
+
+    const int b_begin = SPLITK ? warp : 0, b_step = SPLITK ? 8 : 1;
+    for (int b = b_begin; b < nSB; b += b_step) {
+        const uint4 h0 = *reinterpret_cast<const uint4*>(w0 + (size_t)b * 144);
+        const uint4 h1 = *reinterpret_cast<const uint4*>(w1 + (size_t)b * 144);
+        // this lane decodes sub-blocks 2*tig and 2*tig+1 of its two rows; the quad shares them by shuffle
+        float my_ds[2][2], my_nm[2][2];
+        {
+            int s, m;
+            const float d0 = h2f_bits((unsigned short)(h0.x & 0xffffu)), dm0 = h2f_bits((unsigned short)(h0.x >> 16));
+            const float d1 = h2f_bits((unsigned short)(h1.x & 0xffffu)), dm1 = h2f_bits((unsigned short)(h1.x >> 16));
+            q4k_scale_min(2 * tig, h0.y, h0.z, h0.w, &s, &m);
+            my_ds[0][0] = __fmul_rn(d0, (float)s); my_nm[0][0] = -__fmul_rn(dm0, (float)m);
+            q4k_scale_min(2 * tig + 1, h0.y, h0.z, h0.w, &s, &m);
+            my_ds[0][1] = __fmul_rn(d0, (float)s); my_nm[0][1] = -__fmul_rn(dm0, (float)m);
+            q4k_scale_min(2 * tig, h1.y, h1.z, h1.w, &s, &m);
+            my_ds[1][0] = __fmul_rn(d1, (float)s); my_nm[1][0] = -__fmul_rn(dm1, (float)m);
+            q4k_scale_min(2 * tig + 1, h1.y, h1.z, h1.w, &s, &m);
+            my_ds[1][1] = __fmul_rn(d1, (float)s); my_nm[1][1] = -__fmul_rn(dm1, (float)m);
+        }
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            const int src = (lane & ~3) | p;
+            const float ds0lo = __shfl_sync(0xffffffffu, my_ds[0][0], src), ds0hi = __shfl_sync(0xffffffffu, my_ds[0][1], src);
+            const float ds1lo = __shfl_sync(0xffffffffu, my_ds[1][0], src), ds1hi = __shfl_sync(0xffffffffu, my_ds[1][1], src);
+            const float nm0lo = __shfl_sync(0xffffffffu, my_nm[0][0], src), nm0hi = __shfl_sync(0xffffffffu, my_nm[0][1], src);
+            const float nm1lo = __shfl_sync(0xffffffffu, my_nm[1][0], src), nm1hi = __shfl_sync(0xffffffffu, my_nm[1][1], src);
+            // code words 2*tig, 2*tig+1 of the pair: low nibbles = sub-block 2p, high = 2p+1. The k order inside a
+            // group is permuted the same way for weights and activations, which an integer dot does not see.
+            const uint2 q0 = *reinterpret_cast<const uint2*>(w0 + (size_t)b * 144 + 16 + 32 * p + 8 * tig);
+            const uint2 q1 = *reinterpret_cast<const uint2*>(w1 + (size_t)b * 144 + 16 + 32 * p + 8 * tig);
+            const unsigned al0 = q0.x & 0x0F0F0F0Fu, al1 = q1.x & 0x0F0F0F0Fu, al2 = q0.y & 0x0F0F0F0Fu, al3 = q1.y & 0x0F0F0F0Fu;
+            const unsigned ah0 = (q0.x >> 4) & 0x0F0F0F0Fu, ah1 = (q1.x >> 4) & 0x0F0F0F0Fu, ah2 = (q0.y >> 4) & 0x0F0F0F0Fu,
+                           ah3 = (q1.y >> 4) & 0x0F0F0F0Fu;
+            const int g = 8 * b + 2 * p;
+#pragma unroll
+            for (int j = 0; j < NT; j++) {
+                const int2 blo = *reinterpret_cast<const int2*>(ab[j] + 256 * b + 64 * p);
+                const int2 bhi = *reinterpret_cast<const int2*>(ab[j] + 256 * b + 64 * p + 32);
+                int cl[4] = {MAGIC_I, MAGIC_I, MAGIC_I, MAGIC_I}, ch[4] = {MAGIC_I, MAGIC_I, MAGIC_I, MAGIC_I};
+                mma_u8s8(cl, al0, al1, al2, al3, (unsigned)blo.x, (unsigned)blo.y);
+                mma_u8s8(ch, ah0, ah1, ah2, ah3, (unsigned)bhi.x, (unsigned)bhi.y);
+                const float2 aS0 = *reinterpret_cast<const float2*>(sc0[j] + g);       // token 2*tig: scales of groups g, g+1
+                const float2 aS1 = *reinterpret_cast<const float2*>(sc1[j] + g);       // token 2*tig+1
+                const float2 as0 = *reinterpret_cast<const float2*>(sc0[j] + nG + g);  // group sums
+                const float2 as1 = *reinterpret_cast<const float2*>(sc1[j] + nG + g);
+                float f;
+                // (row gid, token 2*tig)
+                f = acc[j][0];
+                f = __fmaf_rn(__fsub_rn(__int_as_float(cl[0]), MAGIC_F), __fmul_rn(ds0lo, aS0.x), f);
+                f = __fmaf_rn(__fsub_rn(__int_as_float(ch[0]), MAGIC_F), __fmul_rn(ds0hi, aS0.y), f);
+                f = __fmaf_rn(nm0lo, as0.x, f);
+                acc[j][0] = __fmaf_rn(nm0hi, as0.y, f);
+                // (row gid, token 2*tig+1)
+                f = acc[j][1];
+                f = __fmaf_rn(__fsub_rn(__int_as_float(cl[1]), MAGIC_F), __fmul_rn(ds0lo, aS1.x), f);
+                f = __fmaf_rn(__fsub_rn(__int_as_float(ch[1]), MAGIC_F), __fmul_rn(ds0hi, aS1.y), f);
+                f = __fmaf_rn(nm0lo, as1.x, f);
+                acc[j][1] = __fmaf_rn(nm0hi, as1.y, f);
+                // (row gid+8, token 2*tig)
+                f = acc[j][2];
+                f = __fmaf_rn(__fsub_rn(__int_as_float(cl[2]), MAGIC_F), __fmul_rn(ds1lo, aS0.x), f);
+                f = __fmaf_rn(__fsub_rn(__int_as_float(ch[2]), MAGIC_F), __fmul_rn(ds1hi, aS0.y), f);
+                f = __fmaf_rn(nm1lo, as0.x, f);
+                acc[j][2] = __fmaf_rn(nm1hi, as0.y, f);
+                // (row gid+8, token 2*tig+1)
+                f = acc[j][3];
+                f = __fmaf_rn(__fsub_rn(__int_as_float(cl[3]), MAGIC_F), __fmul_rn(ds1lo, aS1.x), f);
+                f = __fmaf_rn(__fsub_rn(__int_as_float(ch[3]), MAGIC_F), __fmul_rn(ds1hi, aS1.y), f);
+                f = __fmaf_rn(nm1lo, as1.x, f);
+                acc[j][3] = __fmaf_rn(nm1hi, as1.y, f);
+            }
+        }
+    }
+
+    if (SPLITK) {
+        // fold the 8 warps' partials in warp order (fixed, so a row's value does not depend on the batch)
+        __shared__ float red[8][NT][4][32];
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) red[warp][j][i][lane] = acc[j][i];
+        __syncthreads();
+        if (warp != 0) return;
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float s = red[0][j][i][lane];
+#pragma unroll
+                for (int w = 1; w < 8; w++) s = __fadd_rn(s, red[w][j][i][lane]);
+                acc[j][i] = s;
+            }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        const int t0 = t_base + 8 * j + 2 * tig, t1 = t0 + 1;
+        const int na = n0 + gid, nb = n0 + gid + 8;
+        if (t0 < t_end) {
+            if (na < N) dst[(size_t)t0 * ldd + na] = acc[j][0];
+            if (nb < N) dst[(size_t)t0 * ldd + nb] = acc[j][2];
+        }
+        if (t1 < t_end) {
+            if (na < N) dst[(size_t)t1 * ldd + na] = acc[j][1];
+            if (nb < N) dst[(size_t)t1 * ldd + nb] = acc[j][3];
+        }
+    }
+}
+
+// ---- f16 weights ----
+__global__ void split_f16_kernel(const float* __restrict__ x, size_t n, __half* __restrict__ hi, __half* __restrict__ lo) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = x[i];
+    __half h = __float2half_rn(v);
+    hi[i] = h;
+    lo[i] = __float2half_rn(__fsub_rn(v, __half2float(h)));
+}
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// dst[t][n] = sum_k W[n][k] * x[t][k], W f16, x as f16 hi + lo. K a multiple of 32. One warp per 16 weight rows.
+template <int NT>
+__global__ void __launch_bounds__(256) f16w_gemm_mma_kernel(const __half* __restrict__ W, int N, int K,
+                                                            const __half* __restrict__ xhi, const __half* __restrict__ xlo,
+                                                            int T, float* __restrict__ dst, int ldd) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tig = lane & 3;
+    const int n0 = (blockIdx.x * 8 + warp) * 16;
+    if (n0 >= N) return;
+    const int t_base = blockIdx.y * 8 * NT;
+    const __half* w0 = W + (size_t)min(n0 + gid, N - 1) * K + 8 * tig;
+    const __half* w1 = W + (size_t)min(n0 + gid + 8, N - 1) * K + 8 * tig;
+    const __half* bh[NT];
+    const __half* bl[NT];
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        size_t t = (size_t)min(t_base + 8 * j + gid, T - 1);
+        bh[j] = xhi + t * K + 8 * tig;
+        bl[j] = xlo + t * K + 8 * tig;
+        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    }
+    for (int k = 0; k < K; k += 32) {
+        // halves [k+8*tig, +8) of both rows; the k order inside the 32-chunk is permuted alike for W and x
+        const uint4 a = *reinterpret_cast<const uint4*>(w0 + k);
+        const uint4 b = *reinterpret_cast<const uint4*>(w1 + k);
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+            const uint4 xh = *reinterpret_cast<const uint4*>(bh[j] + k);
+            const uint4 xl = *reinterpret_cast<const uint4*>(bl[j] + k);
+            mma_f16(acc[j], a.x, b.x, a.y, b.y, xh.x, xh.y);
+            mma_f16(acc[j], a.z, b.z, a.w, b.w, xh.z, xh.w);
+            mma_f16(acc[j], a.x, b.x, a.y, b.y, xl.x, xl.y);
+            mma_f16(acc[j], a.z, b.z, a.w, b.w, xl.z, xl.w);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        const int t0 = t_base + 8 * j + 2 * tig, t1 = t0 + 1;
+        const int na = n0 + gid, nb = n0 + gid + 8;
+        if (t0 < T) {
+            if (na < N) dst[(size_t)t0 * ldd + na] = acc[j][0];
+            if (nb < N) dst[(size_t)t0 * ldd + nb] = acc[j][2];
+        }
+        if (t1 < T) {
+            if (na < N) dst[(size_t)t1 * ldd + na] = acc[j][1];
+            if (nb < N) dst[(size_t)t1 * ldd + nb] = acc[j][3];
+        }
+    }
+}
+
+// generic fallback: one warp per output, f64 accumulate (any K; f16 or f32 weights)
+template <typename WT>
+__global__ void __launch_bounds__(256) dense_matmul_f64_kernel(const WT* __restrict__ W, int N, int K, const float* __restrict__ x,
+                                                               float* __restrict__ dst, int ldd) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), t = blockIdx.y;
+    if (n >= N) return;
+    const WT* w = W + (size_t)n * K;
+    const float* xr = x + (size_t)t * K;
+    double s = 0;
+    for (int k = lane; k < K; k += 32) s += (double)xr[k] * (double)(float)w[k];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) dst[(size_t)t * ldd + n] = (float)s;
+}
+
+// ---- Q4_K block utilities ----
+__global__ void q4k_dequant_kernel(const uint8_t* __restrict__ W, size_t n_blocks, float* __restrict__ out) {
+    const size_t blk = blockIdx.x;
+    if (blk >= n_blocks) return;
+    const uint8_t* b = W + blk * 144;
+    const uint4 h = *reinterpret_cast<const uint4*>(b);
+    const float d = h2f_bits((unsigned short)(h.x & 0xffffu)), dmin = h2f_bits((unsigned short)(h.x >> 16));
+    const int e = threadIdx.x;  // 0..255
+    const int j = e >> 5, p = e >> 6, l = e & 31;
+    int sc, m;
+    q4k_scale_min(j, h.y, h.z, h.w, &sc, &m);
+    const uint8_t q = b[16 + 32 * p + l];
+    const int code = (j & 1) ? (q >> 4) : (q & 0x0F);
+    out[blk * 256 + e] = __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)code), __fmul_rn(dmin, (float)m));
+}
+
+// One thread per super-block; the arithmetic is the host quantizer's, operation for operation.
+__device__ void q4k_quantize_block_dev(const float* __restrict__ w, uint8_t* __restrict__ blk) {
+    float scale[8], mn[8];
+    float max_scale = 0.f, max_min = 0.f;
+    for (int j = 0; j < 8; j++) {
+        float lo = w[32 * j], hi = w[32 * j];
+        for (int i = 1; i < 32; i++) {
+            lo = fminf(lo, w[32 * j + i]);
+            hi = fmaxf(hi, w[32 * j + i]);
+        }
+        float m = lo < 0.f ? -lo : 0.f;
+        float s = __fdiv_rn(__fadd_rn(hi, m), 15.f);
+        if (s < 0.f) s = 0.f;
+        scale[j] = s;
+        mn[j] = m;
+        max_scale = fmaxf(max_scale, s);
+        max_min = fmaxf(max_min, m);
+    }
+    const __half hd = __float2half_rn(__fdiv_rn(max_scale, 63.f)), hm = __float2half_rn(__fdiv_rn(max_min, 63.f));
+    const float d = __half2float(hd), dmin = __half2float(hm);
+    int sc[8], m6[8];
+    for (int j = 0; j < 8; j++) {
+        sc[j] = d > 0.f ? max(0, min(63, __float2int_rn(__fdiv_rn(scale[j], d)))) : 0;
+        m6[j] = dmin > 0.f ? max(0, min(63, __float2int_rn(__fdiv_rn(mn[j], dmin)))) : 0;
+    }
+    uint8_t hdr[16];
+    const unsigned short hdb = __half_as_ushort(hd), hmb = __half_as_ushort(hm);
+    hdr[0] = hdb & 0xff; hdr[1] = hdb >> 8; hdr[2] = hmb & 0xff; hdr[3] = hmb >> 8;
+    for (int i = 4; i < 16; i++) hdr[i] = 0;
+    for (int j = 0; j < 8; j++) {
+        if (j < 4) {
+            hdr[4 + j] |= (uint8_t)(sc[j] & 63);
+            hdr[4 + j + 4] |= (uint8_t)(m6[j] & 63);
+        } else {
+            hdr[4 + j + 4] |= (uint8_t)((sc[j] & 0x0F) | ((m6[j] & 0x0F) << 4));
+            hdr[4 + j - 4] |= (uint8_t)((sc[j] >> 4) << 6);
+            hdr[4 + j] |= (uint8_t)((m6[j] >> 4) << 6);
+        }
+    }
+    for (int i = 0; i < 16; i++) blk[i] = hdr[i];
+    for (int p = 0; p < 4; p++) {
+        const float dsl = __fmul_rn(d, (float)sc[2 * p]), dml = __fmul_rn(dmin, (float)m6[2 * p]);
+        const float dsh = __fmul_rn(d, (float)sc[2 * p + 1]), dmh = __fmul_rn(dmin, (float)m6[2 * p + 1]);
+        const float il = dsl > 0.f ? __fdiv_rn(1.f, dsl) : 0.f, ih = dsh > 0.f ? __fdiv_rn(1.f, dsh) : 0.f;
+        for (int l = 0; l < 32; l++) {
+            int cl = __float2int_rn(__fmul_rn(__fadd_rn(w[64 * p + l], dml), il));
+            int ch = __float2int_rn(__fmul_rn(__fadd_rn(w[64 * p + 32 + l], dmh), ih));
+            cl = max(0, min(15, cl));
+            ch = max(0, min(15, ch));
+            blk[16 + 32 * p + l] = (uint8_t)(cl | (ch << 4));
+        }
+    }
+}
+
+__global__ void q4k_quantize_kernel(const float* __restrict__ w, size_t n_blocks, uint8_t* __restrict__ out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_blocks) q4k_quantize_block_dev(w + i * 256, out + i * 144);
+}
+
+// counter-based normal generator (splitmix64 hash -> Box-Muller)
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__device__ __forceinline__ float normal_at(uint64_t seed, uint64_t i) {
+    uint64_t r = mix64(seed * 0xD1342543DE82EF95ull + i);
+    float u1 = ((float)((r >> 40) + 1)) * (1.0f / 16777217.0f);
+    float u2 = ((float)((r >> 8) & 0xFFFFFF)) * (1.0f / 16777216.0f);
+    return sqrtf(-2.f * logf(u1)) * cospif(2.f * u2);
+}
+
+__global__ void synth_f32_kernel(float* out, size_t n, float sigma, uint64_t seed) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = sigma * normal_at(seed, i);
+}
+__global__ void synth_f16_kernel(__half* out, size_t n, float sigma, uint64_t seed) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2half_rn(sigma * normal_at(seed, i));
+}
+__global__ void synth_q4k_kernel(uint8_t* out, size_t n_blocks, float sigma, uint64_t seed) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_blocks) return;
+    float w[256];
+    for (int e = 0; e < 256; e++) w[e] = sigma * normal_at(seed, i * 256 + e);
+    q4k_quantize_block_dev(w, out + i * 144);
+}
+
+template <int NT, bool SPLITK>
+int run_q4k(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, int T, float* dst, int ldd) {
+    dim3 grid(SPLITK ? ceil_div(N, 16) : ceil_div(N, 128), ceil_div(T, 8 * NT));
+    q4k_gemm_mma_kernel<NT, SPLITK, false><<<grid, 256, 0, ctx->stream>>>(W, nullptr, N, nSB, aq.codes, aq.scales, T, nullptr,
+                                                                         nullptr, dst, ldd);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+}  // namespace
+
+int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, int klass) {
+    if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
+    (void)klass;
+    const int nSB = K / 256;
+    // Rows up to 8 are HBM-bound: split K over the CTA's warps. Beyond that one ascending chain per output.
+    if (T <= 8) return run_q4k<1, true>(ctx, W, N, nSB, aq, T, dst, ldd);
+    if (T <= 16) return run_q4k<2, false>(ctx, W, N, nSB, aq, T, dst, ldd);
+    if (T <= 32) return run_q4k<4, false>(ctx, W, N, nSB, aq, T, dst, ldd);
+    return run_q4k<8, false>(ctx, W, N, nSB, aq, T, dst, ldd);
+}
+
+int launch_q4k_matmul_grouped(b200_ctx* ctx, const uint8_t* const* Wptrs, int n_experts, int N, int K, ActQ aq,
+                              const int32_t* offs, const int32_t* rows, int max_rows_per_expert, float* dst, int ldd) {
+    if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
+    dim3 grid(ceil_div(N, 128), ceil_div(max_rows_per_expert, 16), n_experts);
+    q4k_gemm_mma_kernel<2, false, true><<<grid, 256, 0, ctx->stream>>>(nullptr, Wptrs, N, K / 256, aq.codes, aq.scales, 0, offs,
+                                                                       rows, dst, ldd);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+// split_scratch: 2*T*K halves (the activation's f16 hi and lo parts), owned by the caller.
+int launch_f16w_matmul(b200_ctx* ctx, const __half* W, int N, int K, const float* x, int T, float* dst, int ldd,
+                       __half* split_scratch) {
+    if (K % 32) {
+        dim3 grid(ceil_div(N, 8), T);
+        dense_matmul_f64_kernel<__half><<<grid, 256, 0, ctx->stream>>>(W, N, K, x, dst, ldd);
+        LAUNCH_CHECK(ctx);
+        return B200_OK;
+    }
+    size_t n = (size_t)T * K;
+    __half* hi = split_scratch;
+    __half* lo = split_scratch + n;
+    split_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(x, n, hi, lo);
+    LAUNCH_CHECK(ctx);
+    if (T <= 8) {
+        dim3 grid(ceil_div(N, 128), ceil_div(T, 8));
+        f16w_gemm_mma_kernel<1><<<grid, 256, 0, ctx->stream>>>(W, N, K, hi, lo, T, dst, ldd);
+    } else if (T <= 32) {
+        dim3 grid(ceil_div(N, 128), ceil_div(T, 32));
+        f16w_gemm_mma_kernel<4><<<grid, 256, 0, ctx->stream>>>(W, N, K, hi, lo, T, dst, ldd);
+    } else {
+        dim3 grid(ceil_div(N, 128), ceil_div(T, 64));
+        f16w_gemm_mma_kernel<8><<<grid, 256, 0, ctx->stream>>>(W, N, K, hi, lo, T, dst, ldd);
+    }
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_f32w_matmul(b200_ctx* ctx, const float* W, int N, int K, const float* x, int T, float* dst, int ldd) {
+    dim3 grid(ceil_div(N, 8), T);
+    dense_matmul_f64_kernel<float><<<grid, 256, 0, ctx->stream>>>(W, N, K, x, dst, ldd);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_q4k_dequant(b200_ctx* ctx, const uint8_t* W, size_t n_blocks, float* out) {
+    q4k_dequant_kernel<<<(unsigned)n_blocks, 256, 0, ctx->stream>>>(W, n_blocks, out);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_q4k_quantize(b200_ctx* ctx, const float* w, size_t n_blocks, uint8_t* out) {
+    q4k_quantize_kernel<<<(unsigned)((n_blocks + 127) / 128), 128, 0, ctx->stream>>>(w, n_blocks, out);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_synth_normal_f32(b200_ctx* ctx, float* out, size_t n, float sigma, uint64_t seed) {
+    synth_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(out, n, sigma, seed);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+int launch_synth_f16(b200_ctx* ctx, __half* out, size_t n, float sigma, uint64_t seed) {
+    synth_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(out, n, sigma, seed);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+int launch_synth_q4k(b200_ctx* ctx, uint8_t* out, size_t n_blocks, float sigma, uint64_t seed) {
+    synth_q4k_kernel<<<(unsigned)((n_blocks + 63) / 64), 64, 0, ctx->stream>>>(out, n_blocks, sigma, seed);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}

@@ -1,0 +1,270 @@
+// ops.cu — operator-level C entry points (host buffers in and out) and device-resident micro-benchmarks.
+// They run the same kernels the step uses, the way the reference tests its kernels against host twins
+// (backend/cuda/kernels/actgroup_kernel_test.go, moe_route_test.go, gemv_bw_test.go).
+#include <algorithm>
+#include <cmath>
+#include <vector>
+
+#include "common.cuh"
+
+namespace {
+
+struct Tmp {  // device allocations freed at scope exit
+    std::vector<void*> ps;
+    ~Tmp() {
+        for (void* p : ps) cudaFree(p);
+    }
+    template <typename T>
+    cudaError_t get(T** p, size_t n) {
+        cudaError_t e = cudaMalloc((void**)p, std::max<size_t>(n * sizeof(T), 16));
+        if (e == cudaSuccess) ps.push_back(*p);
+        return e;
+    }
+};
+
+#define TMP_GET(ctx, tmp, ptr, n) CUDA_TRY(ctx, (tmp).get(&(ptr), (n)))
+#define H2D(ctx, dst, src, bytes) CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (ctx)->stream))
+#define D2H(ctx, dst, src, bytes) CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (ctx)->stream))
+#define SYNC(ctx) CUDA_TRY(ctx, cudaStreamSynchronize((ctx)->stream))
+
+__global__ void fill_i32_kernel(int32_t* p, size_t n, int32_t v) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+__global__ void iota_blocks_kernel(int32_t* table, int rows, int max_blocks, const int32_t* n_keys, int block_rows) {
+    // row r owns blocks 1 + r*max_blocks + b (contiguous identity mapping)
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * max_blocks) return;
+    int r = i / max_blocks, b = i % max_blocks;
+    table[i] = (b * block_rows < n_keys[r]) ? 1 + r * max_blocks + b : 0;
+}
+__global__ void scatter_kv_kernel(const float* k, const float* v, __half* kpool, __half* vpool, const int32_t* table, int rows,
+                                  int max_keys, int max_blocks, int nKV, int hd, int block_rows, const int32_t* n_keys) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t per_row = (size_t)max_keys * nKV * hd;
+    if (i >= (size_t)rows * per_row) return;
+    int r = (int)(i / per_row);
+    size_t j = i % per_row;
+    int e = (int)(j % hd), kvh = (int)((j / hd) % nKV), key = (int)(j / ((size_t)hd * nKV));
+    if (key >= n_keys[r]) return;
+    int blk = table[(size_t)r * max_blocks + key / block_rows];
+    size_t off = (((size_t)blk * nKV + kvh) * block_rows + key % block_rows) * hd + e;
+    kpool[off] = __float2half_rn(k[i]);
+    vpool[off] = __float2half_rn(v[i]);
+}
+__global__ void ctx_minus1_kernel(const int32_t* n_keys, int32_t* row_pos, int32_t* row_slot, int rows) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < rows) { row_pos[i] = n_keys[i] - 1; row_slot[i] = i; }
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_op_quant_g32(b200_ctx* ctx, const float* x, int rows, int k, int8_t* codes, float* scales) {
+    Tmp t;
+    float* dx; ActQ aq;
+    const size_t n = (size_t)rows * k, ns = (size_t)rows * 2 * (k / 32);
+    TMP_GET(ctx, t, dx, n); TMP_GET(ctx, t, aq.codes, n); TMP_GET(ctx, t, aq.scales, ns);
+    H2D(ctx, dx, x, n * 4);
+    ST_TRY(launch_quant_g32(ctx, dx, rows, k, aq));
+    D2H(ctx, codes, aq.codes, n); D2H(ctx, scales, aq.scales, ns * 4);
+    SYNC(ctx);
+    return B200_OK;
+}
+
+int b200_op_q4k_dequant(b200_ctx* ctx, const uint8_t* w, int rows, int cols, float* out) {
+    if (cols % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "cols %% 256");
+    Tmp t;
+    const size_t nb = (size_t)rows * cols / 256;
+    uint8_t* dw; float* dout;
+    TMP_GET(ctx, t, dw, nb * 144); TMP_GET(ctx, t, dout, nb * 256);
+    H2D(ctx, dw, w, nb * 144);
+    ST_TRY(launch_q4k_dequant(ctx, dw, nb, dout));
+    D2H(ctx, out, dout, nb * 256 * 4);
+    SYNC(ctx);
+    return B200_OK;
+}
+
+int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, int K, int N, int klass, float* dst) {
+    if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K %% 256");
+    Tmp t;
+    const size_t wb = (size_t)N * K / 256 * 144;
+    uint8_t* dw; float *da, *dd; ActQ aq;
+    TMP_GET(ctx, t, dw, wb); TMP_GET(ctx, t, da, (size_t)M * K); TMP_GET(ctx, t, dd, (size_t)M * N);
+    TMP_GET(ctx, t, aq.codes, (size_t)M * K); TMP_GET(ctx, t, aq.scales, (size_t)M * 2 * (K / 32));
+    H2D(ctx, dw, w, wb); H2D(ctx, da, a, (size_t)M * K * 4);
+    ST_TRY(launch_quant_g32(ctx, da, M, K, aq));
+    ST_TRY(launch_q4k_matmul(ctx, dw, N, K, aq, M, dd, N, klass));
+    D2H(ctx, dst, dd, (size_t)M * N * 4);
+    SYNC(ctx);
+    return B200_OK;
+}
+
+int b200_op_q4k_quantize(b200_ctx* ctx, const float* w, int rows, int cols, uint8_t* out) {
+    if (cols % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "cols %% 256");
+    Tmp t;
+    const size_t nb = (size_t)rows * cols / 256;
+    float* dw; uint8_t* dq;
+    TMP_GET(ctx, t, dw, nb * 256); TMP_GET(ctx, t, dq, nb * 144);
+    H2D(ctx, dw, w, nb * 256 * 4);
+    ST_TRY(launch_q4k_quantize(ctx, dw, nb, dq));
+    D2H(ctx, out, dq, nb * 144);
+    SYNC(ctx);
+    return B200_OK;
+}
+
+int b200_op_rmsnorm(b200_ctx* ctx, const float* x, const float* w, int rows, int dim, float eps, float* out) {
+    Tmp t;
+    float *dx, *dw, *dout;
+    TMP_GET(ctx, t, dx, (size_t)rows * dim); TMP_GET(ctx, t, dw, (size_t)dim); TMP_GET(ctx, t, dout, (size_t)rows * dim);
+    H2D(ctx, dx, x, (size_t)rows * dim * 4); H2D(ctx, dw, w, (size_t)dim * 4);
+    ST_TRY(launch_add_rmsnorm_quant(ctx, dx, nullptr, dw, rows, dim, eps, dout, ActQ{}, nullptr));
+    D2H(ctx, out, dout, (size_t)rows * dim * 4);
+    SYNC(ctx);
+    return B200_OK;
+}
+
+int b200_op_route(b200_ctx* ctx, const float* logits, int rows, int n_experts, int k, int norm_topk, int32_t* idx, float* wts) {
+    Tmp t;
+    float *dl, *dw; int32_t* di;
+    TMP_GET(ctx, t, dl, (size_t)rows * n_experts); TMP_GET(ctx, t, dw, (size_t)rows * k); TMP_GET(ctx, t, di, (size_t)rows * k);
+    H2D(ctx, dl, logits, (size_t)rows * n_experts * 4);
+    ST_TRY(launch_route(ctx, dl, rows, n_experts, k, norm_topk, di, dw));
+    D2H(ctx, idx, di, (size_t)rows * k * 4); D2H(ctx, wts, dw, (size_t)rows * k * 4);
+    SYNC(ctx);
+    return B200_OK;
+}
+
+int b200_op_draw(b200_ctx* ctx, const float* logits, int rows, int vocab, const b200_draw* draws, const int32_t* mask_index,
+                 const uint32_t* logit_mask, int n_masks, int32_t* ids) {
+    Tmp t;
+    float* dl; b200_draw* dd; int32_t *dm, *di; uint32_t* dmk;
+    const size_t words = (vocab + 31) / 32;
+    TMP_GET(ctx, t, dl, (size_t)rows * vocab); TMP_GET(ctx, t, dd, (size_t)rows); TMP_GET(ctx, t, dm, (size_t)rows);
+    TMP_GET(ctx, t, di, (size_t)rows); TMP_GET(ctx, t, dmk, std::max<size_t>(1, (size_t)n_masks * words));
+    H2D(ctx, dl, logits, (size_t)rows * vocab * 4); H2D(ctx, dd, draws, (size_t)rows * sizeof(b200_draw));
+    if (mask_index && logit_mask && n_masks > 0) {
+        H2D(ctx, dm, mask_index, (size_t)rows * 4); H2D(ctx, dmk, logit_mask, (size_t)n_masks * words * 4);
+        ST_TRY(launch_mask_logits(ctx, dl, rows, vocab, dm, dmk));
+    }
+    ST_TRY(launch_draw(ctx, dl, rows, vocab, dd, di, nullptr));
+    D2H(ctx, ids, di, (size_t)rows * 4);
+    SYNC(ctx);
+    return B200_OK;
+}
+
+int b200_op_attention(b200_ctx* ctx, const float* q, const float* k, const float* v, const int32_t* n_keys, int rows, int max_keys,
+                      int n_heads, int n_kv_heads, int head_dim, float scale, float softcap, int block_rows, float* out) {
+    if (rows <= 0 || max_keys <= 0 || block_rows <= 0 || n_heads % n_kv_heads) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad attention shape");
+    Tmp t;
+    const int max_blocks = ceil_div(max_keys, block_rows);
+    const size_t pool_blocks = 1 + (size_t)rows * max_blocks;
+    const size_t pool_elems = pool_blocks * n_kv_heads * block_rows * head_dim;
+    const size_t kvn = (size_t)rows * max_keys * n_kv_heads * head_dim, qn = (size_t)rows * n_heads * head_dim;
+    float *dq, *dk, *dv, *dout; __half *kp, *vp; int32_t *tbl, *nk, *rpos, *rslot;
+    AttnScratch sc;
+    sc.max_splits = ceil_div(max_keys, attn_split_keys());
+    TMP_GET(ctx, t, dq, qn); TMP_GET(ctx, t, dk, kvn); TMP_GET(ctx, t, dv, kvn); TMP_GET(ctx, t, dout, qn);
+    TMP_GET(ctx, t, kp, pool_elems); TMP_GET(ctx, t, vp, pool_elems);
+    TMP_GET(ctx, t, tbl, (size_t)rows * max_blocks); TMP_GET(ctx, t, nk, (size_t)rows); TMP_GET(ctx, t, rpos, (size_t)rows);
+    TMP_GET(ctx, t, rslot, (size_t)rows);
+    TMP_GET(ctx, t, sc.partial, attn_scratch_floats(rows, n_heads, head_dim, sc.max_splits));
+    H2D(ctx, dq, q, qn * 4); H2D(ctx, dk, k, kvn * 4); H2D(ctx, dv, v, kvn * 4); H2D(ctx, nk, n_keys, (size_t)rows * 4);
+    CUDA_TRY(ctx, cudaMemsetAsync(kp, 0, pool_elems * 2, ctx->stream));
+    CUDA_TRY(ctx, cudaMemsetAsync(vp, 0, pool_elems * 2, ctx->stream));
+    iota_blocks_kernel<<<ceil_div(rows * max_blocks, 256), 256, 0, ctx->stream>>>(tbl, rows, max_blocks, nk, block_rows);
+    LAUNCH_CHECK(ctx);
+    scatter_kv_kernel<<<(unsigned)((kvn + 255) / 256), 256, 0, ctx->stream>>>(dk, dv, kp, vp, tbl, rows, max_keys, max_blocks,
+                                                                              n_kv_heads, head_dim, block_rows, nk);
+    LAUNCH_CHECK(ctx);
+    ctx_minus1_kernel<<<ceil_div(rows, 256), 256, 0, ctx->stream>>>(nk, rpos, rslot, rows);
+    LAUNCH_CHECK(ctx);
+    KVView kv{kp, vp, tbl, max_blocks, block_rows, n_kv_heads, head_dim};
+    const float sc_ = scale != 0.f ? scale : (float)(1.0 / std::sqrt((double)head_dim));
+    ST_TRY(launch_paged_attention(ctx, dq, n_heads * head_dim, rows, n_heads, n_kv_heads, head_dim, sc_, softcap, rslot, rpos,
+                                  max_keys, kv, sc, dout, ActQ{}));
+    D2H(ctx, out, dout, qn * 4);
+    SYNC(ctx);
+    return B200_OK;
+}
+
+int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_weight_copies, int warmup, int iters, float* ms_out) {
+    if (K % 256 || M <= 0 || N <= 0 || n_weight_copies <= 0 || iters <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad bench shape");
+    Tmp t;
+    const size_t wb = (size_t)N * K / 256 * 144;
+    uint8_t* dw; float *da, *dd; ActQ aq;
+    // several copies of the matrix, cycled, so a launch never finds its weights in L2
+    TMP_GET(ctx, t, dw, wb * n_weight_copies); TMP_GET(ctx, t, da, (size_t)M * K); TMP_GET(ctx, t, dd, (size_t)M * N);
+    TMP_GET(ctx, t, aq.codes, (size_t)M * K); TMP_GET(ctx, t, aq.scales, (size_t)M * 2 * (K / 32));
+    for (int c = 0; c < n_weight_copies; c++) ST_TRY(launch_synth_q4k(ctx, dw + (size_t)c * wb, wb / 144, 0.02f, 17 + c));
+    ST_TRY(launch_synth_normal_f32(ctx, da, (size_t)M * K, 1.f, 5));
+    ST_TRY(launch_quant_g32(ctx, da, M, K, aq));
+    cudaEvent_t e0, e1;
+    CUDA_TRY(ctx, cudaEventCreate(&e0)); CUDA_TRY(ctx, cudaEventCreate(&e1));
+    for (int i = 0; i < warmup; i++) ST_TRY(launch_q4k_matmul(ctx, dw + (size_t)(i % n_weight_copies) * wb, N, K, aq, M, dd, N, klass));
+    CUDA_TRY(ctx, cudaEventRecord(e0, ctx->stream));
+    for (int i = 0; i < iters; i++) ST_TRY(launch_q4k_matmul(ctx, dw + (size_t)(i % n_weight_copies) * wb, N, K, aq, M, dd, N, klass));
+    CUDA_TRY(ctx, cudaEventRecord(e1, ctx->stream));
+    SYNC(ctx);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    *ms_out = ms / iters;
+    return B200_OK;
+}
+
+int b200_bench_attention(b200_ctx* ctx, int rows, int ctx_lo, int ctx_hi, int n_heads, int n_kv_heads, int head_dim,
+                         int block_rows, uint64_t seed, int warmup, int iters, float* ms_out, double* kv_bytes_out) {
+    if (rows <= 0 || ctx_lo <= 0 || ctx_hi < ctx_lo || iters <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad bench shape");
+    Tmp t;
+    std::vector<int32_t> nk(rows);
+    uint64_t z = seed * 0x9E3779B97F4A7C15ull + 1;
+    double tot_keys = 0;
+    for (int r = 0; r < rows; r++) {
+        z ^= z << 13; z ^= z >> 7; z ^= z << 17;
+        nk[r] = ctx_lo + (int)(z % (uint64_t)(ctx_hi - ctx_lo + 1));
+        tot_keys += nk[r];
+    }
+    const int max_keys = ctx_hi, max_blocks = ceil_div(max_keys, block_rows);
+    const size_t pool_blocks = 1 + (size_t)rows * max_blocks;
+    const size_t pool_elems = pool_blocks * n_kv_heads * block_rows * head_dim;
+    const size_t qn = (size_t)rows * n_heads * head_dim;
+    size_t free_b = 0, total_b = 0;
+    cudaMemGetInfo(&free_b, &total_b);
+    if (pool_elems * 4 + ((size_t)2 << 30) > free_b) B200_FAIL(ctx, B200_BAD_ARGUMENT, "attention bench pool does not fit the device");
+    float *dq, *dout; __half *kp, *vp; int32_t *tbl, *dnk, *rpos, *rslot;
+    AttnScratch sc;
+    sc.max_splits = ceil_div(max_keys, attn_split_keys());
+    TMP_GET(ctx, t, dq, qn); TMP_GET(ctx, t, dout, qn); TMP_GET(ctx, t, kp, pool_elems); TMP_GET(ctx, t, vp, pool_elems);
+    TMP_GET(ctx, t, tbl, (size_t)rows * max_blocks); TMP_GET(ctx, t, dnk, (size_t)rows); TMP_GET(ctx, t, rpos, (size_t)rows);
+    TMP_GET(ctx, t, rslot, (size_t)rows);
+    TMP_GET(ctx, t, sc.partial, attn_scratch_floats(rows, n_heads, head_dim, sc.max_splits));
+    H2D(ctx, dnk, nk.data(), (size_t)rows * 4);
+    ST_TRY(launch_synth_normal_f32(ctx, dq, qn, 1.f, seed + 1));
+    ST_TRY(launch_synth_f16(ctx, kp, pool_elems, 0.5f, seed + 2));
+    ST_TRY(launch_synth_f16(ctx, vp, pool_elems, 0.5f, seed + 3));
+    iota_blocks_kernel<<<ceil_div(rows * max_blocks, 256), 256, 0, ctx->stream>>>(tbl, rows, max_blocks, dnk, block_rows);
+    LAUNCH_CHECK(ctx);
+    ctx_minus1_kernel<<<ceil_div(rows, 256), 256, 0, ctx->stream>>>(dnk, rpos, rslot, rows);
+    LAUNCH_CHECK(ctx);
+    KVView kv{kp, vp, tbl, max_blocks, block_rows, n_kv_heads, head_dim};
+    const float scale = (float)(1.0 / std::sqrt((double)head_dim));
+    cudaEvent_t e0, e1;
+    CUDA_TRY(ctx, cudaEventCreate(&e0)); CUDA_TRY(ctx, cudaEventCreate(&e1));
+    for (int i = 0; i < warmup; i++)
+        ST_TRY(launch_paged_attention(ctx, dq, n_heads * head_dim, rows, n_heads, n_kv_heads, head_dim, scale, 0.f, rslot, rpos, max_keys, kv, sc, dout, ActQ{}));
+    CUDA_TRY(ctx, cudaEventRecord(e0, ctx->stream));
+    for (int i = 0; i < iters; i++)
+        ST_TRY(launch_paged_attention(ctx, dq, n_heads * head_dim, rows, n_heads, n_kv_heads, head_dim, scale, 0.f, rslot, rpos, max_keys, kv, sc, dout, ActQ{}));
+    CUDA_TRY(ctx, cudaEventRecord(e1, ctx->stream));
+    SYNC(ctx);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    *ms_out = ms / iters;
+    if (kv_bytes_out) *kv_bytes_out = tot_keys * 2.0 * n_kv_heads * head_dim * 2.0;
+    return B200_OK;
+}
+
+}  // extern "C"

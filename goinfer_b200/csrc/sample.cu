@@ -1,0 +1,267 @@
+// sample.cu — device-side draws, logit masks and the routed-expert bookkeeping.
+//
+//   mask      constrain/constrain.go:233-267 maskID: a rejected token's logit becomes -inf before the draw
+//   greedy    internal/runtime/sampling/sampler.go:485-518 Argmax: first maximal index
+//   min-p     sampler.go:586-647 (candidates logit >= max + T*ln(minP)), :654-724 finishFilter (order by
+//             (prob desc, id asc), cut p < minP*p0, drop zeros, renormalise), :442-458 drawFiltered (first
+//             prefix whose cumulative probability exceeds the caller's uniform u)
+//   route     decoder/mlp.go:130-184 routeExperts (softmax path), :370-411 softmaxF32, :415-440 topK
+#include "common.cuh"
+
+namespace {
+
+__global__ void mask_logits_kernel(float* __restrict__ logits, int V, const int32_t* __restrict__ row_mask,
+                                   const uint32_t* __restrict__ masks) {
+    const int r = blockIdx.y;
+    const int mi = row_mask[r];
+    if (mi < 0) return;
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= V) return;
+    const int words = (V + 31) / 32;
+    if (!((masks[(size_t)mi * words + (t >> 5)] >> (t & 31)) & 1u)) logits[(size_t)r * V + t] = -INFINITY;
+}
+
+constexpr int kDrawThreads = 1024;
+
+__device__ __forceinline__ double block_sum_f64(double v, double* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double t = 0;
+    for (int w = 0; w < kDrawThreads / 32; w++) t += red[w];
+    return t;
+}
+
+__device__ __forceinline__ long long block_sum_i64(long long v, long long* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    long long t = 0;
+    for (int w = 0; w < kDrawThreads / 32; w++) t += red[w];
+    return t;
+}
+
+// One block per row.
+__global__ void __launch_bounds__(kDrawThreads) draw_kernel(const float* __restrict__ logits, int V,
+                                                            const b200_draw* __restrict__ draws, int32_t* __restrict__ ids) {
+    __shared__ float s_val[kDrawThreads / 32];
+    __shared__ int s_idx[kDrawThreads / 32];
+    __shared__ double s_red[kDrawThreads / 32];
+    __shared__ float s_max;
+    __shared__ int s_arg;
+    const int r = blockIdx.x;
+    const float* l = logits + (size_t)r * V;
+    const b200_draw dr = draws[r];
+    if (dr.kind == B200_DRAW_LOGITS) {
+        if (threadIdx.x == 0) ids[r] = -1;
+        return;
+    }
+    // first maximum
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += kDrawThreads) {
+        float v = l[i];
+        if (v > best || bi == 0x7fffffff) {
+            if (v > best || bi == 0x7fffffff) { best = v; bi = i; }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float b = s_val[0];
+        int k = s_idx[0];
+        for (int w = 1; w < kDrawThreads / 32; w++)
+            if (s_val[w] > b || (s_val[w] == b && s_idx[w] < k)) { b = s_val[w]; k = s_idx[w]; }
+        s_max = b;
+        s_arg = k;
+    }
+    __syncthreads();
+    if (dr.kind == B200_DRAW_GREEDY) {
+        if (threadIdx.x == 0) ids[r] = s_arg;
+        return;
+    }
+    // min-p
+    const double texp = dr.temperature > 0.f ? (double)dr.temperature : 1.0;
+    const double minp = dr.min_p > 1.f ? 1.0 : (double)dr.min_p;
+    const double maxL = (double)s_max;
+    const double thr = minp > 0 ? maxL + texp * log(minp) : -INFINITY;
+    // e of a retained token, else 0: candidate by logit, not cut by minP*p0 (p0 = e of the top token = 1), nonzero
+    auto e_of = [&](int i) -> double {
+        const double li = (double)l[i];
+        if (!(li >= thr)) return 0.0;
+        const double e = exp((li - maxL) / texp);
+        if (minp > 0 && e < minp * 1.0) return 0.0;
+        return e;
+    };
+    double part = 0;
+    for (int i = threadIdx.x; i < V; i += kDrawThreads) part += e_of(i);
+    const double total = block_sum_f64(part, s_red);
+    if (!(total > 0)) {
+        if (threadIdx.x == 0) ids[r] = s_arg;
+        return;
+    }
+    const double target = dr.u * total;
+    // largest key X (bit pattern of a positive double) with mass{e >= X} > target
+    long long lo = 1, hi = __double_as_longlong(1.0) + 1;
+    while (hi - lo > 1) {
+        const long long mid = lo + (hi - lo) / 2;
+        const double x = __longlong_as_double(mid);
+        double p2 = 0;
+        for (int i = threadIdx.x; i < V; i += kDrawThreads) {
+            const double e = e_of(i);
+            if (e >= x) p2 += e;
+        }
+        const double g = block_sum_f64(p2, s_red);
+        if (g > target) lo = mid; else hi = mid;
+    }
+    const double X = __longlong_as_double(lo);
+    // mass strictly above X, and the ties at X
+    double pa = 0;
+    long long ties = 0;
+    for (int i = threadIdx.x; i < V; i += kDrawThreads) {
+        const double e = e_of(i);
+        if (e > X) pa += e;
+        if (e == X) ties++;
+    }
+    const double above = block_sum_f64(pa, s_red);
+    const long long n_ties = block_sum_i64(ties, (long long*)s_red);
+    if (n_ties == 0) {  // u at or past the retained mass: the reference returns the last retained token
+        if (threadIdx.x == 0) ids[r] = s_arg;
+        return;
+    }
+    // ties share one e: after t of them the running mass is above + t*X; take the first t that exceeds target
+    long long t = (long long)floor((target - above) / X) + 1;
+    if (t < 1) t = 1;
+    if (t > n_ties) t = n_ties;
+    // t-th smallest id among the ties: bisection on the id
+    int ilo = -1, ihi = V - 1;  // count(id <= ilo) < t <= count(id <= ihi)
+    while (ihi - ilo > 1) {
+        const int mid = ilo + (ihi - ilo) / 2;
+        long long c = 0;
+        for (int i = threadIdx.x; i <= mid; i += kDrawThreads)
+            if (e_of(i) == X) c++;
+        const long long cnt = block_sum_i64(c, (long long*)s_red);
+        if (cnt >= t) ihi = mid; else ilo = mid;
+    }
+    if (threadIdx.x == 0) ids[r] = ihi;
+}
+
+// One warp per row. n_experts <= 512.
+__global__ void __launch_bounds__(32) route_kernel(const float* __restrict__ logits, int nE, int k, int norm,
+                                                   int32_t* __restrict__ idx, float* __restrict__ wts) {
+    __shared__ float p[512];
+    __shared__ double e64[512];
+    const int r = blockIdx.x, lane = threadIdx.x;
+    const float* lg = logits + (size_t)r * nE;
+    float mx = -INFINITY;
+    for (int i = lane; i < nE; i += 32) mx = fmaxf(mx, lg[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    for (int i = lane; i < nE; i += 32) {
+        const double e = exp((double)__fsub_rn(lg[i], mx));
+        e64[i] = e;
+        p[i] = (float)e;
+    }
+    __syncwarp();
+    double sum = 0;
+    if (lane == 0)
+        for (int i = 0; i < nE; i++) sum += e64[i];  // index order, as the reference sums
+    sum = __shfl_sync(0xffffffffu, sum, 0);
+    const float inv = (float)(1.0 / sum);
+    for (int i = lane; i < nE; i += 32) p[i] = __fmul_rn(p[i], inv);
+    __syncwarp();
+    float wsum = 0.f;
+    for (int j = 0; j < k; j++) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = lane; i < nE; i += 32) {
+            const float v = p[i];
+            if (v > best) { best = v; bi = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (bi == 0x7fffffff) {  // fewer than k finite scores
+            if (lane == 0) { idx[(size_t)r * k + j] = -1; wts[(size_t)r * k + j] = 0.f; }
+            continue;
+        }
+        if (lane == 0) {
+            idx[(size_t)r * k + j] = bi;
+            wts[(size_t)r * k + j] = best;
+            p[bi] = -INFINITY;  // used
+        }
+        wsum = __fadd_rn(wsum, best);
+        __syncwarp();
+    }
+    if (norm && wsum > 0.f && lane == 0)
+        for (int j = 0; j < k; j++)
+            if (idx[(size_t)r * k + j] >= 0) wts[(size_t)r * k + j] = __fdiv_rn(wts[(size_t)r * k + j], wsum);
+}
+
+// One block; thread e owns expert e. offs[nE+1]; rows_tok[s] = token row of sorted slot s; slot_of[a] = sorted
+// slot of assignment a = row*k + rank (-1 when the rank is empty).
+__global__ void group_experts_kernel(const int32_t* __restrict__ idx, int n_assign, int k, int nE, int32_t* __restrict__ offs,
+                                     int32_t* __restrict__ rows_tok, int32_t* __restrict__ slot_of) {
+    extern __shared__ int s_cnt[];
+    const int e = threadIdx.x;
+    int c = 0;
+    if (e < nE)
+        for (int a = 0; a < n_assign; a++) c += idx[a] == e;
+    if (e < nE) s_cnt[e] = c;
+    __syncthreads();
+    if (e == 0) {
+        int run = 0;
+        for (int i = 0; i < nE; i++) { offs[i] = run; run += s_cnt[i]; }
+        offs[nE] = run;
+    }
+    __syncthreads();
+    if (e < nE) {
+        int s = offs[e];
+        for (int a = 0; a < n_assign; a++)
+            if (idx[a] == e) { rows_tok[s] = a / k; slot_of[a] = s; s++; }
+    }
+    for (int a = e; a < n_assign; a += blockDim.x)
+        if (idx[a] < 0) slot_of[a] = -1;
+}
+
+}  // namespace
+
+int launch_mask_logits(b200_ctx* ctx, float* logits, int R, int V, const int32_t* row_mask, const uint32_t* masks) {
+    mask_logits_kernel<<<dim3(ceil_div(V, 256), R), 256, 0, ctx->stream>>>(logits, V, row_mask, masks);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_draw(b200_ctx* ctx, const float* logits, int R, int V, const b200_draw* draws, int32_t* ids, float*) {
+    draw_kernel<<<R, kDrawThreads, 0, ctx->stream>>>(logits, V, draws, ids);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_route(b200_ctx* ctx, const float* logits, int T, int nE, int k, int norm, int32_t* idx, float* wts) {
+    if (nE > 512) B200_FAIL(ctx, B200_DECLINED, "router: more than 512 experts");
+    route_kernel<<<T, 32, 0, ctx->stream>>>(logits, nE, k, norm, idx, wts);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_group_experts(b200_ctx* ctx, const int32_t* idx, int T, int k, int nE, int32_t* offs, int32_t* rows) {
+    // rows holds rows_tok[T*k] followed by slot_of[T*k]
+    group_experts_kernel<<<1, max(32, ((nE + 31) / 32) * 32), nE * sizeof(int), ctx->stream>>>(idx, T * k, k, nE, offs, rows,
+                                                                                            rows + (size_t)T * k);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}

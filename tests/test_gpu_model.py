@@ -1,0 +1,214 @@
+"""GPU parity of the whole ragged step through the C ABI against the CPU oracle on identical seeded
+inputs: logits within max-abs 2e-2 / rel 1e-2, block tables bit-exact, the first 32 greedy ids equal.
+The cases follow the reference's step tests (backend/cuda/batchstep_test.go:29,157,289,455) and its golden
+forward tests (decoder/llama_tiny_test.go:22-80, decoder/qwen3moe_test.go)."""
+import numpy as np
+import pytest
+
+from goinfer_b200 import abi, synth
+from goinfer_b200.resident import (BatchDraw, BatchSeq, ErrKVPoolFull, RaggedPrefill, RaggedSeq, Resident,
+                                   ResidentError)
+from helpers import cfg_from_hf, close_logits, load_golden, upload_hf
+
+pytestmark = pytest.mark.gpu
+
+
+def build_pair(oracle_lib, shape_name, n_slots=4, ctx_cap=256, seed=0, n_layers=0, kv_block_rows=16, max_rows=0,
+               kv_pool_blocks=0):
+    s = synth.SHAPES[shape_name]
+    mk = lambda: synth.make_cfg(s, n_slots, ctx_cap, kv_block_rows, kv_pool_blocks, max_rows, abi.CLASS_EXACT, n_layers)
+    g, o = Resident(mk()), oracle_lib.OracleResident(mk())
+    synth.load_host_weights([g, o], s, seed, n_layers)
+    g.finalize()
+    o.finalize()
+    return g, o, s
+
+
+def greedy_margin_ok(logits, gid, oid, tol=4e-2):
+    """Ids differ only at a near-tie (the reference's own rule for real checkpoints, docs/benchmarks.md:1132-1133)."""
+    return gid == oid or abs(float(logits[gid]) - float(logits[oid])) <= tol
+
+
+@pytest.mark.parametrize("shape", ["tiny-dense", "tiny-qknorm", "tiny-moe"])
+def test_ragged_prefill_then_32_greedy_steps(oracle_lib, shape):
+    g, o, s = build_pair(oracle_lib, shape, n_slots=4, ctx_cap=160)
+    rng = np.random.default_rng(0)
+    lens = [17, 64, 3, 40]
+    prompts = [rng.integers(0, s.vocab, n).tolist() for n in lens]
+    toks = []
+    for slot, p in enumerate(prompts):
+        lg, lo = g.PrefillLast(None, 0, slot, p), o.PrefillLast(None, 0, slot, p)
+        ok, err = close_logits(lg, lo)
+        assert ok, (shape, slot, err)
+        assert np.array_equal(g.BlockTable(slot), o.BlockTable(slot))
+        toks.append(int(np.argmax(lo)))
+        assert greedy_margin_ok(lo, int(np.argmax(lg)), toks[-1])
+    pos = list(lens)
+    agree = 0
+    for step in range(32):
+        # teacher forcing on the oracle's ids; logits compared every step, ids by the near-tie rule
+        seqs = [BatchSeq(i, pos[i], None, toks[i]) for i in range(4)]
+        og, oo = g.StepBatch(seqs), o.StepBatch(seqs)
+        for i in range(4):
+            ok, err = close_logits(og[i].Logits, oo[i].Logits)
+            assert ok, (shape, step, i, err)
+            gi, oi = int(np.argmax(og[i].Logits)), int(np.argmax(oo[i].Logits))
+            assert greedy_margin_ok(oo[i].Logits, gi, oi)
+            agree += gi == oi
+            toks[i] = oi
+            pos[i] += 1
+    assert agree >= 0.97 * 128, agree
+    for slot in range(4):
+        assert np.array_equal(g.BlockTable(slot), o.BlockTable(slot))
+
+
+def test_free_running_greedy_ids_agree_for_32_steps(oracle_lib):
+    """No teacher forcing: both sides feed back their own drawn ids through the on-device greedy draw."""
+    g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=2, ctx_cap=96, seed=3)
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(0, s.vocab, n).tolist() for n in (9, 30)]
+    ids = {}
+    for name, r in (("g", g), ("o", o)):
+        tok = [int(np.argmax(r.PrefillLast(None, 0, i, p))) for i, p in enumerate(prompts)]
+        pos, out = [len(p) for p in prompts], []
+        for _ in range(32):
+            res = r.StepBatch([BatchSeq(i, pos[i], None, tok[i], BatchDraw(Greedy=True)) for i in range(2)])
+            tok = [x.ID for x in res]
+            assert all(x.Logits is None for x in res)
+            out.append(tok)
+            pos = [p + 1 for p in pos]
+        ids[name] = out
+    assert ids["g"] == ids["o"]
+
+
+def test_step_ragged_chunk_rides_with_decode_rows(oracle_lib):
+    """A prefill chunk and decode rows in one step; every row equals its own sequence's pass
+    (TestCUDAStepRagged_rowsMatchTheirShapes, _prefillChunkMatchesItsPass)."""
+    g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=4, ctx_cap=128, seed=5, max_rows=96)
+    rng = np.random.default_rng(2)
+    p0 = rng.integers(0, s.vocab, 50).tolist()
+    p1 = rng.integers(0, s.vocab, 20).tolist()
+    for r in (g, o):
+        r.PrefillLast(None, 0, 1, p1)
+        r.PrefillLast(None, 0, 2, p1[:7])
+    def step(r):
+        a = r.StepRagged([RaggedSeq(0, 0, None, p0[:32], None, RaggedPrefill(50, False)),
+                          RaggedSeq(1, 20, None, [5]), RaggedSeq(2, 7, None, [6, 7, 8], BatchDraw(Greedy=True))])
+        b = r.StepRagged([RaggedSeq(0, 32, None, p0[32:], None, RaggedPrefill(50, True)), RaggedSeq(1, 21, None, [9])])
+        return a, b
+    (ga, gb), (oa, ob) = step(g), step(o)
+    assert ga[0].Logits == [None] * 32 and ga[2].Logits[-1] is None
+    for x, y in ((ga[1].Logits[0], oa[1].Logits[0]), (ga[2].Logits[0], oa[2].Logits[0]), (ga[2].Logits[1], oa[2].Logits[1]),
+                 (gb[0].Logits[-1], ob[0].Logits[-1]), (gb[1].Logits[0], ob[1].Logits[0])):
+        ok, err = close_logits(x, y)
+        assert ok, err
+    assert ga[2].ID == oa[2].ID
+    # the chunked prompt equals the same prompt in one pass on another slot (same kernel class: > 8 rows)
+    whole = g.PrefillLast(None, 0, 3, p0)
+    ok, err = close_logits(gb[0].Logits[-1], whole, atol=1e-4, rtol=1e-4)
+    assert ok, err
+
+
+def test_batch_rows_are_bit_identical_to_their_own_forward(oracle_lib):
+    """StepBatch rows == the sequence's own Forward bit for bit while both run the small-batch kernel class
+    (decoder/resident/subsystems.go:102-110; TestCUDAStepBatch_matchesForward)."""
+    g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=8, ctx_cap=64, seed=7)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, s.vocab, n).tolist() for n in (5, 12, 33, 7)]
+    for i, p in enumerate(prompts):
+        g.PrefillLast(None, 0, i, p)
+        g.PrefillLast(None, 0, i + 4, p)
+    batch = g.StepBatch([BatchSeq(i, len(prompts[i]), None, 11 + i) for i in range(4)])
+    for i in range(4):
+        solo = g.Forward(None, len(prompts[i]), slot=i + 4, token=11 + i)
+        assert np.array_equal(batch[i].Logits, solo)
+
+
+def test_kv_pool_full_writes_nothing_and_bad_steps_are_refused(oracle_lib):
+    g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=3, ctx_cap=64, seed=9, kv_pool_blocks=1 + 3)
+    for r in (g, o):
+        r.PrefillLast(None, 0, 0, list(range(1, 33)))            # 2 blocks of 16
+        with pytest.raises(ErrKVPoolFull):
+            r.PrefillLast(None, 0, 1, list(range(1, 40)))        # needs 3, 1 free
+        assert r.BlockTable(1).sum() == 0                        # nothing was mapped
+        r.PrefillLast(None, 0, 1, list(range(1, 10)))            # 1 block still fits
+        with pytest.raises(ErrKVPoolFull):
+            r.StepBatch([BatchSeq(0, 32, None, 3), BatchSeq(1, 9, None, 4)])   # slot 0 needs a third block
+        r.ResetSlot(0)
+        assert r.StepBatch([BatchSeq(1, 9, None, 4), BatchSeq(2, 0, None, 5)])[0].Logits is not None
+    assert np.array_equal(g.BlockTable(2), o.BlockTable(2))      # a freed block is reused in the same order
+    assert np.array_equal(g.BlockTable(1), o.BlockTable(1))
+    for bad in ([BatchSeq(0, 0, None, 1), BatchSeq(0, 0, None, 1)],          # repeated slot
+                [BatchSeq(2, 5, None, 1)],                                   # past the slot's stored rows
+                [BatchSeq(1, 64, None, 1)]):                                 # past the context cap
+        with pytest.raises(ResidentError):
+            g.StepBatch(bad)
+    with pytest.raises(ResidentError):
+        g.StepRagged([RaggedSeq(1, 10, None, [1]), RaggedSeq(2, 1, None, [1, 2], None, RaggedPrefill(3, True))])  # chunk not first
+
+
+def test_min_p_draw_and_logit_mask_in_a_step(oracle_lib):
+    g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=2, ctx_cap=32, seed=11)
+    words = (s.vocab + 31) // 32
+    mask = np.zeros(words, np.uint32)
+    mask[1] = 0x00F0                                             # only ids 36..39 allowed
+    for r in (g, o):
+        r.PrefillLast(None, 0, 0, [1, 2, 3])
+        r.PrefillLast(None, 0, 1, [4, 5])
+    seqs = [BatchSeq(0, 3, None, 7, BatchDraw(Greedy=False, Temperature=0.8, MinP=0.02, U=0.37)),
+            BatchSeq(1, 2, None, 8, BatchDraw(Greedy=True), mask)]
+    a, b = g.StepBatch(seqs), o.StepBatch(seqs)
+    assert [x.ID for x in a] == [x.ID for x in b]
+    assert 36 <= a[1].ID <= 39
+    lg = g.StepBatch([BatchSeq(1, 3, None, 9, None, mask)])[0].Logits
+    assert np.isinf(lg[:36]).all() and np.isfinite(lg[36:40]).all() and np.isinf(lg[40:]).all()
+
+
+@pytest.mark.parametrize("name", ["llama_tiny", "qwen3moe_tiny"])
+def test_reference_goldens_on_the_gpu(name):
+    """The reference's HF goldens with their f32 weights on the GPU (fp16 KV cache, so a looser bar than the
+    oracle's own pin): argmax equal, logits within 2e-3."""
+    hf, w, gold = load_golden(name)
+    r = Resident(cfg_from_hf(hf))
+    upload_hf(r, hf, w)
+    r.finalize()
+    ids = (gold["prompt_ids"] if name == "llama_tiny" else gold["ids"]).tolist()
+    lg = r.PrefillLast(None, 0, 0, ids)
+    assert int(np.argmax(lg)) == int(gold["argmax"])
+    if name == "llama_tiny":
+        np.testing.assert_allclose(lg, gold["last_logits"], atol=2e-3, rtol=0)
+        tok, pos, out = int(gold["argmax"]), len(ids), [int(gold["argmax"])]
+        for _ in range(len(gold["continuation_ids"]) - 1):
+            tok = r.ForwardArgmax(None, pos, 0, tok)
+            out.append(tok)
+            pos += 1
+        assert out == gold["continuation_ids"].tolist()
+    else:
+        np.testing.assert_allclose(lg[gold["top_k_ids"]], gold["top_k_logits"], atol=2e-3, rtol=0)
+
+
+def test_c1_shape_ragged_prompts_and_greedy_decode(oracle_lib):
+    """BASELINE configuration 1 at reduced depth (4 of 22 layers keeps the CPU oracle within a minute): the
+    1.1B-shape Llama in Q4_K, 4 ragged prompts of {17, 64, 128, 300} tokens from seed 0, then greedy steps."""
+    g, o, s = build_pair(oracle_lib, "c1-1.1b", n_slots=4, ctx_cap=352, seed=0, n_layers=4, max_rows=320)
+    rng = np.random.default_rng(0)
+    lens = [17, 64, 128, 300]
+    prompts = [rng.integers(0, 32000, n).tolist() for n in lens]
+    toks = []
+    for i, p in enumerate(prompts):
+        lg, lo = g.PrefillLast(None, 0, i, p), o.PrefillLast(None, 0, i, p)
+        ok, err = close_logits(lg, lo)
+        assert ok, (i, err)
+        toks.append(int(np.argmax(lo)))
+    pos = list(lens)
+    for step in range(8):
+        seqs = [BatchSeq(i, pos[i], None, toks[i]) for i in range(4)]
+        og, oo = g.StepBatch(seqs), o.StepBatch(seqs)
+        for i in range(4):
+            ok, err = close_logits(og[i].Logits, oo[i].Logits)
+            assert ok, (step, i, err)
+            assert greedy_margin_ok(oo[i].Logits, int(np.argmax(og[i].Logits)), int(np.argmax(oo[i].Logits)))
+            toks[i] = int(np.argmax(oo[i].Logits))
+            pos[i] += 1
+    for i in range(4):
+        assert np.array_equal(g.BlockTable(i), o.BlockTable(i))

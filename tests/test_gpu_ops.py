@@ -1,0 +1,198 @@
+"""GPU parity of the kernels, one operator at a time, through the C ABI against the CPU oracle.
+
+Integer artefacts (Q4_K unpacking, activation codes, quantized blocks, routing indices, drawn ids) are
+compared bit for bit; floating point to the tolerance written beside each check. The cases follow the
+reference's own kernel tests: backend/cuda/kernels/actgroup_kernel_test.go:141-206 (quantizers, exact),
+:305-364 (Q4_K GEMV incl. a saturated block, rel-err 1e-5 vs a float64 sum), moe_route_test.go:29-110,
+backend/cuda/argmax_tiebreak_test.go:22."""
+import numpy as np
+import pytest
+
+from goinfer_b200 import abi, q4k
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from goinfer_b200.ops import Ops
+    return Ops(0)
+
+
+def test_quant_g32_bit_exact(ops, oracle_lib):
+    rng = np.random.default_rng(0)
+    x = rng.normal(0, 1, (7, 1024)).astype(np.float32)
+    x[0, :32] = 0.0                     # zero group: scale 0, inv 0
+    x[1, 5] = 900.0                     # outlier group
+    x[2, 32:64] = -1.0                  # saturated negatives
+    x[3] *= 1e-30                       # tiny magnitudes
+    x[4, ::2] = 0.5 * 3 / 127           # exact .5 ties -> round half to even
+    c0, s0 = oracle_lib.op_quant_g32(x)
+    c1, s1 = ops.quant_g32(x)
+    assert np.array_equal(c0, c1)
+    assert np.array_equal(s0.view(np.uint32), s1.view(np.uint32))
+
+
+def test_q4k_dequant_bit_exact_on_random_blocks(ops, oracle_lib):
+    rng = np.random.default_rng(1)
+    raw = q4k.random_blocks(rng, 16, 1024)
+    raw[:144 * 2][4:] = 0xFF            # a saturated block: every scale, minimum and code at its maximum
+    a = oracle_lib.op_q4k_dequant(raw, 16, 1024)
+    b = ops.q4k_dequant(raw, 16, 1024)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    assert np.array_equal(b, q4k.dequantize(raw, 16, 1024))
+
+
+def test_q4k_quantizer_bit_exact(ops, oracle_lib):
+    rng = np.random.default_rng(2)
+    w = rng.normal(0, 0.02, (48, 768)).astype(np.float32)
+    w[0, :256] = 0.0                    # all-zero super-block
+    w[1, :32] = 0.25                    # constant positive sub-block
+    w[2, :64] = -np.abs(w[2, :64])      # all-negative sub-blocks
+    a = oracle_lib.op_q4k_quantize(w)
+    assert np.array_equal(a, ops.q4k_quantize(w))
+    assert np.array_equal(a, q4k.quantize(w))
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 70, 256])
+def test_q4k_matmul_exact_class(ops, oracle_lib, M):
+    rng = np.random.default_rng(10 + M)
+    N, K = 200, 1024                    # N not a multiple of 16 or 128: ragged row tiles
+    raw = q4k.quantize(rng.normal(0, 0.02, (N, K)).astype(np.float32))
+    a = rng.normal(0, 1, (M, K)).astype(np.float32)
+    a[0, :32] = 0
+    want = oracle_lib.op_q4k_matmul(raw, a, N)
+    got = ops.q4k_matmul(raw, a, N, klass=1)
+    if M > 8:
+        # one ascending chain per output, the oracle's order: bit-identical
+        assert np.array_equal(want.view(np.uint32), got.view(np.uint32))
+    ref = oracle_lib.op_q4k_matmul_f64(raw, a, N)
+    scale = np.abs(ref).max()
+    assert np.abs(got - ref).max() <= 1e-5 * scale          # the reference's own GEMV bar
+    assert np.abs(got - want).max() <= 2e-6 * scale
+
+
+def test_q4k_matmul_saturated_and_random_bytes(ops, oracle_lib):
+    rng = np.random.default_rng(3)
+    N, K = 32, 512
+    raw = q4k.random_blocks(rng, N, K).reshape(N, K // 256, 144)
+    raw[0, :, 4:] = 0xFF                # saturated rows: actgroup_kernel_test.go:293-295,311-315
+    raw = raw.reshape(-1)
+    for M in (2, 12):
+        a = rng.normal(0, 1, (M, K)).astype(np.float32)
+        a[0, :] = -1.0
+        ref = oracle_lib.op_q4k_matmul_f64(raw, a, N)
+        got = ops.q4k_matmul(raw, a, N, klass=1)
+        assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max()
+
+
+def test_q4k_batch_rows_equal_single_rows_within_class(ops):
+    """Rows of a batched product equal the same rows alone wherever the kernel class is the same
+    (decoder/resident/subsystems.go:102-110 asks this of StepBatch against Forward)."""
+    rng = np.random.default_rng(4)
+    N, K = 64, 512
+    raw = q4k.quantize(rng.normal(0, 0.02, (N, K)).astype(np.float32))
+    a = rng.normal(0, 1, (8, K)).astype(np.float32)
+    full = ops.q4k_matmul(raw, a, N, klass=1)
+    for r in range(8):
+        assert np.array_equal(full[r], ops.q4k_matmul(raw, a[r:r + 1], N, klass=1)[0])
+    b = rng.normal(0, 1, (40, K)).astype(np.float32)
+    big = ops.q4k_matmul(raw, b, N, klass=1)
+    assert np.array_equal(big[:12], ops.q4k_matmul(raw, b[:12], N, klass=1))
+
+
+def test_rmsnorm(ops, oracle_lib):
+    rng = np.random.default_rng(5)
+    x = rng.normal(0, 3, (5, 2048)).astype(np.float32)
+    w = (1 + rng.normal(0, 0.1, 2048)).astype(np.float32)
+    a = oracle_lib.op_rmsnorm(x, w, 1e-6)
+    b = ops.rmsnorm(x, w, 1e-6)
+    np.testing.assert_allclose(b, a, rtol=3e-7, atol=0)   # 1 ulp: the f64 sum is folded in another order
+
+
+def test_route_indices_bit_exact(ops, oracle_lib):
+    rng = np.random.default_rng(6)
+    for nE, k, norm in ((8, 2, True), (128, 8, True), (128, 8, False), (64, 6, True)):
+        lg = rng.normal(0, 1, (33, nE)).astype(np.float32)
+        lg[0, :] = 0.25                       # all tied: lowest indices win, in order
+        lg[1, 3] = lg[1, 9] = 7.0             # a tie at the top
+        i0, w0 = oracle_lib.op_route(lg, k, norm)
+        i1, w1 = ops.route(lg, k, norm)
+        assert np.array_equal(i0, i1)
+        assert np.array_equal(w0.view(np.uint32), w1.view(np.uint32))
+
+
+def test_greedy_draw_first_maximum_and_masks(ops, oracle_lib):
+    rng = np.random.default_rng(7)
+    V = 32000
+    lg = rng.normal(0, 1, (6, V)).astype(np.float32)
+    lg[0, 100] = lg[0, 20000] = 9.0           # exact tie: index 100
+    lg[1, :] = -1.5                           # all equal: index 0
+    lg[2, V - 1] = 50.0
+    draws = [abi.Draw(abi.DRAW_GREEDY, 0, 0, 0, 0)] * 6
+    masks = np.full((2, (V + 31) // 32), 0xFFFFFFFF, np.uint32)
+    masks[0, 100 // 32] &= ~np.uint32(1 << (100 % 32))      # forbid id 100 for row 0
+    masks[1, :] = 0
+    masks[1, 7] = 1 << 3                                    # only id 227 allowed for row 3
+    mi = np.array([0, -1, -1, 1, -1, -1], np.int32)
+    want = oracle_lib.op_draw(lg, draws, mi, masks)
+    got = ops.draw(lg, draws, mi, masks)
+    assert np.array_equal(want, got)
+    assert got[0] == 20000 and got[1] == 0 and got[2] == V - 1 and got[3] == 227
+
+
+def test_minp_draw_matches_the_retained_set_walk(ops, oracle_lib):
+    rng = np.random.default_rng(8)
+    V = 4096
+    lg = (rng.normal(0, 2, (40, V))).astype(np.float32)
+    lg[5, 10] = lg[5, 11] = lg[5].max() + 1   # tied top tokens
+    draws = []
+    for r in range(40):
+        draws.append(abi.Draw(abi.DRAW_MINP, [0.7, 1.0, 1.3][r % 3], [0.05, 0.2, 0.01, 1.5][r % 4], 0, float(rng.random())))
+    want = oracle_lib.op_draw(lg, draws)
+    got = ops.draw(lg, draws)
+    assert np.array_equal(want, got)
+    # every drawn id lies in the oracle's retained set
+    for r in range(40):
+        ids, probs = oracle_lib.op_minp_set(lg[r], draws[r].temperature, draws[r].min_p)
+        assert got[r] in ids and abs(probs.sum() - 1) < 1e-12
+
+
+@pytest.mark.parametrize("nH,nKV,hd", [(32, 8, 128), (32, 4, 64), (4, 2, 64), (4, 2, 16), (8, 2, 8), (8, 8, 128)])
+def test_paged_attention_matches_the_f64_oracle(ops, oracle_lib, nH, nKV, hd):
+    rng = np.random.default_rng(hd + nH)
+    rows, max_keys = 6, 1300
+    n_keys = np.array([1, 15, 16, 17, 700, 1300], np.int32)   # block edges, split edges (512), ragged
+    q = rng.normal(0, 1, (rows, nH * hd)).astype(np.float32)
+    k = rng.normal(0, 1, (rows, max_keys, nKV * hd)).astype(np.float32)
+    v = rng.normal(0, 1, (rows, max_keys, nKV * hd)).astype(np.float32)
+    scale = 1.0 / np.sqrt(hd)
+    for cap in (0.0, 30.0):
+        want = oracle_lib.op_attention(q, k, v, n_keys, nH, nKV, hd, scale, cap)
+        got = ops.attention(q, k, v, n_keys, nH, nKV, hd, scale, cap, block_rows=16)
+        np.testing.assert_allclose(got, want, atol=2e-5, rtol=1e-4)   # fp32 online softmax vs f64
+    got64 = ops.attention(q, k, v, n_keys, nH, nKV, hd, scale, 0.0, block_rows=64)
+    np.testing.assert_allclose(got64, want if cap == 0.0 else oracle_lib.op_attention(q, k, v, n_keys, nH, nKV, hd, scale, 0.0),
+                               atol=2e-5, rtol=1e-4)
+
+
+def test_attention_properties_at_full_context(ops):
+    """Size-independent properties at the benchmark's largest context (8192 keys, 8 kv heads of 128):
+    constant V gives that constant back; the output is linear in V; keys past n_keys do not matter."""
+    rng = np.random.default_rng(9)
+    nH, nKV, hd, rows, max_keys = 32, 8, 128, 3, 8192
+    n_keys = np.array([8192, 4097, 129], np.int32)
+    q = rng.normal(0, 1, (rows, nH * hd)).astype(np.float32)
+    k = rng.normal(0, 1, (rows, max_keys, nKV * hd)).astype(np.float32)
+    v1 = rng.normal(0, 1, (rows, max_keys, nKV * hd)).astype(np.float16).astype(np.float32)
+    const = np.broadcast_to(rng.normal(0, 1, (1, 1, nKV * hd)).astype(np.float16).astype(np.float32), v1.shape)
+    o_const = ops.attention(q, k, const, n_keys, nH, nKV, hd)
+    want = np.repeat(const[0, 0].reshape(nKV, 1, hd), nH // nKV, axis=1).reshape(-1)
+    np.testing.assert_allclose(o_const, np.broadcast_to(want, o_const.shape), atol=2e-3, rtol=0)
+    o1 = ops.attention(q, k, v1, n_keys, nH, nKV, hd)
+    o2 = ops.attention(q, k, 2 * v1, n_keys, nH, nKV, hd)
+    np.testing.assert_allclose(o2, 2 * o1, atol=1e-5, rtol=1e-5)
+    k2 = k.copy()
+    for r in range(rows):
+        k2[r, n_keys[r]:] = 1e4          # poison the keys outside the causal range
+    assert np.array_equal(ops.attention(q, k2, v1, n_keys, nH, nKV, hd), o1)
