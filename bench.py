@@ -1,0 +1,306 @@
+#!/usr/bin/env python
+"""Benchmark of the ragged batched decode step on B200.
+
+Workload (BASELINE configuration 3, the one the headline metric is quoted on): dense 8B shape (hidden 4096, 36 layers,
+32 query / 8 KV heads of 128, per-head QK RMSNorm, SwiGLU 12288, vocab 151936, RoPE theta 1e6), random-init N(0, 0.02)
+weights quantized to Q4_K with per-32 int8 activations, f16 embedding and LM head; a ragged batch of 256 sequences with
+prefix contexts uniform in [128, 8192] (seed 2) held in a paged fp16 KV cache of 16-token blocks (about 160 GB, so every
+step streams far more than the 126 MB L2); one step = one greedy decode token for every sequence.
+
+  python bench.py --gpus N --steps K --warmup W          this build (one replica per GPU, no collective)
+  python bench.py --impl reference --steps K --warmup W  the CPU restatement of the reference path on the host cores
+
+One JSON line on stdout (rank 0). `value` is tok/s with everything resident in HBM and the drawn ids fed back on the
+device; `e2e` is the same metric through the C ABI's step call with host buffers (embedding rows in, ids out, every step).
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "ragged-batch decode tok/s (Q4_K, 8B shape, B=256)"
+B, CTX_LO, CTX_HI, SEED = 256, 128, 8192, 2
+SAMPLE_SEQS, SAMPLE_LAYERS = 32, 2
+
+
+def contexts():
+    return np.random.default_rng(SEED).integers(CTX_LO, CTX_HI + 1, B).astype(np.int32)
+
+
+def workload_config(n_gpus):
+    return {"workload": "c3: 8B-shape Q4_K (W4A8 per-32), B=256 ragged decode, contexts U[128,8192] seed 2, paged fp16 KV "
+                        "16-token blocks", "global_batch": B * n_gpus, "parallelism": f"replicas x{n_gpus} (no collective)",
+            "l2": "inputs (about 160 GB of KV and 6.4 GB of weights per step) are far larger than the 126 MB L2",
+            "kernel_class": "fast (fp32 flash-decode attention)"}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+def cpu_sample(steps, warmup):
+    """The oracle (CPU restatement of the reference's decodeMultiStep) on a bounded sample of the workload: the first
+    SAMPLE_SEQS sequences of the batch at their drawn contexts, SAMPLE_LAYERS of the 36 layers plus the full LM head.
+    Layer time is scaled by 36/SAMPLE_LAYERS and the batch by B/SAMPLE_SEQS (CPU cost is linear in both)."""
+    from goinfer_b200 import abi, q4k, synth
+    from oracle import binding as ob
+    s = synth.SHAPES["c3-8b"]
+    ctx = contexts()[:SAMPLE_SEQS]
+    cap = int(ctx.max()) + warmup + steps + 2
+    cfg = synth.make_cfg(s, SAMPLE_SEQS, cap, 16, 0, SAMPLE_SEQS, abi.CLASS_EXACT, SAMPLE_LAYERS)
+    o = ob.OracleResident(cfg)
+    rng = np.random.default_rng(7)
+    H, qd, kvd = s.hidden, s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
+    tile = rng.normal(0, 0.02, (1024, H)).astype(np.float16)
+    table = np.ascontiguousarray(np.tile(tile, (s.vocab // 1024 + 1, 1))[:s.vocab])
+    o.upload(abi.T_EMBED, table)
+    o.upload(abi.T_LM_HEAD, table)
+    o.upload(abi.T_FINAL_NORM, np.ones(H, np.float32))
+    for l in range(SAMPLE_LAYERS):
+        o.upload(abi.T_ATTN_NORM, np.ones(H, np.float32), l)
+        o.upload(abi.T_FFN_NORM, np.ones(H, np.float32), l)
+        o.upload(abi.T_Q_NORM, np.ones(s.head_dim, np.float32), l)
+        o.upload(abi.T_K_NORM, np.ones(s.head_dim, np.float32), l)
+        for which, rows, cols in ((abi.T_WQ, qd, H), (abi.T_WK, kvd, H), (abi.T_WV, kvd, H), (abi.T_WO, H, qd),
+                                  (abi.T_GATE, s.ffn, H), (abi.T_UP, s.ffn, H), (abi.T_DOWN, H, s.ffn)):
+            # random valid blocks (how the reference's own tests build Q4_K tensors); values do not matter for time
+            o.upload(which, q4k.random_blocks(rng, rows, cols, 1, 4), l, -1, abi.K_Q4K, rows, cols)
+    o.finalize()
+    kv = rng.normal(0, 0.5, (int(ctx.max()), kvd)).astype(np.float32)
+    for i, n in enumerate(ctx):
+        for l in range(SAMPLE_LAYERS):
+            o.UploadKV(i, l, 0, kv[:n], kv[:n])
+    lay, head = C.c_double(0), C.c_double(0)
+    from goinfer_b200.resident import BatchDraw, BatchSeq
+    toks = rng.integers(0, s.vocab, SAMPLE_SEQS).tolist()
+    times = []
+    for it in range(warmup + steps):
+        seqs = [BatchSeq(i, int(ctx[i]) + it, None, toks[i], BatchDraw(Greedy=True)) for i in range(SAMPLE_SEQS)]
+        toks = [x.ID for x in o.StepBatch(seqs)]
+        ob.lib().oracle_last_timing(C.byref(lay), C.byref(head))
+        if it >= warmup:
+            times.append((lay.value, head.value))
+    lay_s = float(np.mean([t[0] for t in times]))
+    head_s = float(np.mean([t[1] for t in times]))
+    full_step_s = (B / SAMPLE_SEQS) * (lay_s * s.n_layers / SAMPLE_LAYERS + head_s)
+    return {"value": B / full_step_s, "unit": "tok/s", "cores": ob.threads(), "kind": "port",
+            "sample": f"{SAMPLE_SEQS} of the {B} sequences at their drawn contexts, {SAMPLE_LAYERS} of 36 layers + the LM head; "
+                      f"measured {lay_s:.3f} s layers + {head_s:.3f} s head per sample step, scaled by 36/{SAMPLE_LAYERS} and "
+                      f"{B}/{SAMPLE_SEQS}; CPU restatement of goinfer's CPU path (its Go binary and aikit kernels cannot be built here)",
+            "ms_per_step": full_step_s * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cb = cpu_sample(args.steps, args.warmup)
+    line = {"metric": METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x Q4_K integer dots, f32/f64 accumulate", "data": "synthetic",
+            "config": workload_config(args.gpus), "impl": "reference",
+            "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+class Clocks:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.p, self.path = gpu_index, None, f"/tmp/clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if not self.p:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        self.p.wait()
+        sm, mx, reasons = [], [], set()
+        for ln in open(self.path):
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_gpu(args):
+    import torch
+    from goinfer_b200 import abi, synth
+    from goinfer_b200.resident import Resident
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    stream = torch.cuda.Stream()
+    K, W = args.steps, max(args.warmup, 0)
+    s = synth.SHAPES["c3-8b"]
+    ctx = contexts()
+    growth = 2 * (K + W) + 8                       # positions each sequence may advance over both timed loops
+    cap = int(ctx.max()) + growth
+    blocks = 1 + int(np.ceil((ctx + growth) / 16).sum())
+    cfg = synth.make_cfg(s, B, cap, 16, blocks, B, abi.CLASS_AUTO)
+    with torch.cuda.stream(stream):
+        r = Resident(cfg, device=local, stream=stream.cuda_stream)
+        synth.load_device_weights(r, s, seed=SEED)
+        caps = r.finalize()
+        for i in range(B):
+            r.SynthKV(i, int(ctx[i]), 0.5, 1000 + i)
+        lib, m, bctx = r.drv.lib, r.m, r.drv.ctx
+        slot = np.arange(B, dtype=np.int32)
+        pos = ctx.copy()
+        first = np.random.default_rng(SEED + 1).integers(0, s.vocab, B).astype(np.int32)
+        ms = C.c_float(0)
+        p32 = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))
+
+        def check(st):
+            if st != abi.OK:
+                raise RuntimeError(f"b200 status {st}: {r.drv.last_error()}")
+
+        def barrier():
+            torch.cuda.synchronize()
+            if world > 1:
+                import torch.distributed as dist
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        # ---- resident leg: `value` ----
+        if W:
+            check(lib.b200_decode_loop_device(m, B, p32(slot), p32(pos), p32(first), W, 1, None, C.byref(ms)))
+            pos += W
+        lib.b200_profile(bctx, 1)                   # per-launch events on the attention split kernel only
+        clocks = Clocks(local)
+        barrier()
+        clocks.start()
+        launches0 = lib.b200_launch_count(bctx)
+        check(lib.b200_decode_loop_device(m, B, p32(slot), p32(pos), p32(first), K, 1, None, C.byref(ms)))
+        barrier()
+        launches = int(lib.b200_launch_count(bctx) - launches0)
+        clk = clocks.stop()
+        dev_ms = float(ms.value)
+        tag_ms = (C.c_double * 8)()
+        tag_n = (C.c_int64 * 8)()
+        lib.b200_profile_read(bctx, tag_ms, tag_n, 8)
+        lib.b200_profile(bctx, 0)
+        keys_per_step = [float((pos + 1 + i).sum()) for i in range(K)]      # keys read per layer at timed step i
+        pos += K
+        attn_bytes_per_launch = float(np.mean(keys_per_step)) * 2 * s.n_kv_heads * s.head_dim * 2
+        attn_ms_per_launch = tag_ms[0] / max(1, tag_n[0])
+
+        # ---- end-to-end leg: the C ABI step call with host buffers, H2D and D2H inside the timed region ----
+        embs = torch.empty((B, s.hidden), dtype=torch.float32).normal_(0, 0.02).pin_memory()
+        e_np = embs.numpy()
+        ones = np.ones(B, np.int32)
+        draws = (abi.Draw * B)(*[abi.Draw(abi.DRAW_GREEDY, 0, 0, 0, 0)] * B)
+        ids = np.zeros(B, np.int32)
+
+        def step_host():
+            check(lib.b200_step_ragged(m, B, p32(slot), p32(pos), p32(ones), None, None,
+                                       e_np.ctypes.data_as(C.POINTER(C.c_float)), None, draws, None, None, 0, None, p32(ids), None))
+            pos[:] += 1
+
+        for _ in range(min(W, 3)):
+            step_host()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            step_host()
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([dev_ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_s = float(t[0]), float(t[1]) / 1e3
+    if rank != 0:
+        return
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = attn_bytes_per_launch / (attn_ms_per_launch * 1e-3) / 1e9 if attn_ms_per_launch > 0 else 0.0
+    traffic = None
+    try:
+        traffic = json.load(open(os.path.join(ROOT, "profiles", "attn_split_traffic.json"))).get("dram_bytes_per_launch_scaled")
+    except (OSError, ValueError):
+        pass
+    h2d = B * s.hidden * 4 + (2 + 3 * B) * 4 + B * 4 + B * 24
+    line = {
+        "metric": METRIC, "value": world * B * K / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8 x s8 integer dots (Q4_K x per-32 int8), fp32 accumulate; fp16 KV", "data": "synthetic",
+        "config": workload_config(world),
+        "e2e": {"value": world * B * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": B * 4,
+                "ms_per_step": e2e_s / K * 1e3},
+        "gpu_launches": launches,
+        "clocks": clk,
+        "roofline": {"kernel": "attn_split_kernel<128,4> (paged flash-decode attention)", "bound": "hbm",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": "of measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "of fallback",
+                     "frac_of_8tbs_nominal": achieved / 8000.0, "traffic": traffic,
+                     "algorithmic_bytes_per_launch": attn_bytes_per_launch, "ms_per_launch": attn_ms_per_launch,
+                     "launches_timed": int(tag_n[0]), "share_of_step": tag_ms[0] / dev_ms if dev_ms else None},
+        "memory": {"weights_gb": caps.weight_bytes / 1e9, "kv_gb": caps.kv_bytes / 1e9, "scratch_gb": caps.scratch_bytes / 1e9},
+    }
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = {k: v for k, v in cpu_sample(2, 1).items() if k != "ms_per_step"}
+    if world == 1 and not args.no_gemv:
+        from goinfer_b200.ops import Ops
+        ops = Ops(local)
+        rows = []
+        for M in (1, 2, 4, 8, 16, 32):
+            t = ops.bench_q4k_matmul(M, 4096, 12288, 0, 8, 3, 20)
+            gb = 12288 * 4096 * 144 / 256 / 1e9
+            rows.append({"rows": M, "ms": t, "weight_GBps": gb / (t * 1e-3), "frac_of_measured_peak": gb / (t * 1e-3) / peak})
+        line["q4k_gemv_12288x4096"] = rows
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-gemv", action="store_true", help="skip the Q4_K small-batch matmul sweep")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -246,21 +246,119 @@ __global__ void __launch_bounds__(32) attn_generic_kernel(const float* __restric
     }
 }
 
+// ---- exact class: f64 dot, softmax and AV fold, the CPU path's own arithmetic (decoder/forwardn.go:379-499) ----
+// scores[(r*nH + h)*ld + key] = f32(sum_d q_d*k_d in f64, d ascending)
+__global__ void __launch_bounds__(128) attn_exact_scores_kernel(const float* __restrict__ q, int ldq, int nH, int nKV, int hd,
+                                                                double scale, double cap, const int32_t* __restrict__ row_slot,
+                                                                const int32_t* __restrict__ row_pos,
+                                                                const __half* __restrict__ kpool, const int32_t* __restrict__ table,
+                                                                int max_blocks, int block_rows, float* __restrict__ scores, int ld) {
+    const int h = blockIdx.y, r = blockIdx.z;
+    const int key = blockIdx.x * 128 + threadIdx.x;
+    if (key > row_pos[r]) return;
+    const int kvh = h / (nH / nKV);
+    const int blk = table[(size_t)row_slot[r] * max_blocks + key / block_rows];
+    const __half* kr = kpool + (((size_t)blk * nKV + kvh) * block_rows + key % block_rows) * hd;
+    const float* qh = q + (size_t)r * ldq + (size_t)h * hd;
+    double d = 0;
+    for (int i = 0; i < hd; i++) d = __dadd_rn(d, __dmul_rn((double)qh[i], (double)__half2float(kr[i])));
+    (void)scale; (void)cap;
+    scores[((size_t)r * nH + h) * ld + key] = (float)d;  // the f32-rounded dot; scale and cap are applied in f64 below
+}
+
+// per (head, row): x = cap(f64(dot)*scale); max over the unrounded x; e = exp(f64(f32 x) - max) stored as f32; f64 sum of
+// the unrounded e; w = f32(f64(f32 e) / sum) -- the rounding points of decoder/forwardn.go:437-470
+__device__ __forceinline__ double exact_score(float dot, double scale, double cap) {
+    double x = __dmul_rn((double)dot, scale);
+    if (cap != 0.0) x = cap * tanh(x / cap);
+    return x;
+}
+__global__ void __launch_bounds__(256) attn_exact_softmax_kernel(const int32_t* __restrict__ row_pos, int nH, double scale,
+                                                                 double cap, float* __restrict__ scores, int ld) {
+    __shared__ double red[8];
+    const int h = blockIdx.x, r = blockIdx.y, nkeys = row_pos[r] + 1;
+    float* s = scores + ((size_t)r * nH + h) * ld;
+    double mx = -INFINITY;
+    for (int t = threadIdx.x; t < nkeys; t += 256) mx = fmax(mx, exact_score(s[t], scale, cap));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int w = 1; w < 8; w++) mx = fmax(mx, red[w]);
+    __syncthreads();
+    double sum = 0;
+    for (int t = threadIdx.x; t < nkeys; t += 256) {
+        const double e = exp((double)(float)exact_score(s[t], scale, cap) - mx);
+        s[t] = (float)e;
+        sum += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    sum = 0;
+    for (int w = 0; w < 8; w++) sum += red[w];
+    const double inv = 1.0 / sum;
+    for (int t = threadIdx.x; t < nkeys; t += 256) s[t] = (float)((double)s[t] * inv);
+}
+
+// per (head, row), one thread per dim: ctx_d = f32( sum over keys ascending of w_t * v_t[d] in f64 )
+__global__ void attn_exact_av_kernel(const float* __restrict__ scores, int ld, int nH, int nKV, int hd,
+                                     const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
+                                     const __half* __restrict__ vpool, const int32_t* __restrict__ table, int max_blocks,
+                                     int block_rows, float* __restrict__ out) {
+    const int h = blockIdx.x, r = blockIdx.y, d = threadIdx.x;
+    if (d >= hd) return;
+    const int kvh = h / (nH / nKV), nkeys = row_pos[r] + 1;
+    const float* w = scores + ((size_t)r * nH + h) * ld;
+    const int32_t* tbl = table + (size_t)row_slot[r] * max_blocks;
+    double acc = 0;
+    for (int k0 = 0; k0 < nkeys; k0 += block_rows) {
+        const __half* vb = vpool + (((size_t)tbl[k0 / block_rows] * nKV + kvh) * block_rows) * hd + d;
+        const int n = min(block_rows, nkeys - k0);
+        for (int i = 0; i < n; i++) acc = __dadd_rn(acc, __dmul_rn((double)w[k0 + i], (double)__half2float(vb[(size_t)i * hd])));
+    }
+    out[(size_t)r * nH * hd + (size_t)h * hd + d] = (float)acc;
+}
+
 template <int HD, int G>
 int run_split(b200_ctx* ctx, const float* q, int ldq, int T, int nH, int nKV, float scale, float cap, const int32_t* row_slot,
               const int32_t* row_pos, int max_keys, KVView kv, AttnScratch sc, float* out, ActQ aq) {
     const int nsp = ceil_div(max_keys, kSplitKeys);
     if (nsp > sc.max_splits) B200_FAIL(ctx, B200_BAD_ARGUMENT, "attention scratch too small for %d keys", max_keys);
     dim3 grid(nsp, nKV, T);
-    attn_split_kernel<HD, G><<<grid, 128, 0, ctx->stream>>>(q, ldq, nH, nKV, scale, cap, row_slot, row_pos, kv.k, kv.v, kv.table,
-                                                           kv.max_blocks, kv.block_rows, sc.partial, sc.max_splits);
+    {
+        ProfScope ps(ctx, PROF_ATTN_SPLIT);
+        attn_split_kernel<HD, G><<<grid, 128, 0, ctx->stream>>>(q, ldq, nH, nKV, scale, cap, row_slot, row_pos, kv.k, kv.v,
+                                                               kv.table, kv.max_blocks, kv.block_rows, sc.partial, sc.max_splits);
+    }
     LAUNCH_CHECK(ctx);
-    attn_combine_kernel<HD><<<dim3(nH, T), HD, 0, ctx->stream>>>(sc.partial, nH, sc.max_splits, row_pos, out, aq.codes, aq.scales);
+    {
+        ProfScope ps(ctx, PROF_ATTN_COMBINE);
+        attn_combine_kernel<HD><<<dim3(nH, T), HD, 0, ctx->stream>>>(sc.partial, nH, sc.max_splits, row_pos, out, aq.codes, aq.scales);
+    }
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }
 
 }  // namespace
+
+int launch_paged_attention_exact(b200_ctx* ctx, const float* q, int ldq, int T, int nH, int nKV, int hd, double scale,
+                                 double softcap, const int32_t* row_slot, const int32_t* row_pos, int max_keys, KVView kv,
+                                 float* scores, int ld, float* out, ActQ aq) {
+    if (max_keys > ld) B200_FAIL(ctx, B200_BAD_ARGUMENT, "exact attention scratch holds %d keys, %d asked", ld, max_keys);
+    attn_exact_scores_kernel<<<dim3(ceil_div(max_keys, 128), nH, T), 128, 0, ctx->stream>>>(
+        q, ldq, nH, nKV, hd, scale, softcap, row_slot, row_pos, kv.k, kv.table, kv.max_blocks, kv.block_rows, scores, ld);
+    LAUNCH_CHECK(ctx);
+    attn_exact_softmax_kernel<<<dim3(nH, T), 256, 0, ctx->stream>>>(row_pos, nH, scale, softcap, scores, ld);
+    LAUNCH_CHECK(ctx);
+    attn_exact_av_kernel<<<dim3(nH, T), ((hd + 31) / 32) * 32, 0, ctx->stream>>>(scores, ld, nH, nKV, hd, row_slot, row_pos, kv.v,
+                                                                                 kv.table, kv.max_blocks, kv.block_rows, out);
+    LAUNCH_CHECK(ctx);
+    if (aq.codes) return launch_quant_g32(ctx, out, T, nH * hd, aq);
+    return B200_OK;
+}
 
 int attn_split_keys() { return kSplitKeys; }
 

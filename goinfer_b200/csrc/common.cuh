@@ -5,8 +5,18 @@
 #include <stdint.h>
 
 #include <string>
+#include <vector>
 
 #include "../../include/b200_resident.h"
+
+// Kernel classes the per-launch profiler tells apart.
+enum ProfTag { PROF_ATTN_SPLIT = 0, PROF_ATTN_COMBINE, PROF_Q4K_GEMM, PROF_HEAD_GEMM, PROF_NORM_QUANT, PROF_ROPE_KV,
+               PROF_SWIGLU, PROF_OTHER, PROF_TAGS };
+
+struct ProfRec {
+    int tag;
+    cudaEvent_t e0, e1;
+};
 
 struct b200_ctx {
     int device = 0;
@@ -15,6 +25,37 @@ struct b200_ctx {
     std::string err;
     int64_t launches = 0;  // kernels this library launched on the context
     int sm_count = 148;
+    // per-launch CUDA-event timing of the tagged kernel classes (off unless b200_profile sets a mask)
+    unsigned prof_mask = 0;
+    std::vector<ProfRec> prof_recs;
+    std::vector<cudaEvent_t> prof_pool;
+    cudaEvent_t prof_event() {
+        if (!prof_pool.empty()) { cudaEvent_t e = prof_pool.back(); prof_pool.pop_back(); return e; }
+        cudaEvent_t e;
+        cudaEventCreate(&e);
+        return e;
+    }
+};
+
+// Brackets one kernel launch with events when its class is being profiled.
+struct ProfScope {
+    b200_ctx* ctx;
+    ProfRec rec;
+    bool on;
+    ProfScope(b200_ctx* c, int tag) : ctx(c), on((c->prof_mask >> tag) & 1u) {
+        if (on) {
+            rec.tag = tag;
+            rec.e0 = c->prof_event();
+            rec.e1 = c->prof_event();
+            cudaEventRecord(rec.e0, c->stream);
+        }
+    }
+    ~ProfScope() {
+        if (on) {
+            cudaEventRecord(rec.e1, ctx->stream);
+            ctx->prof_recs.push_back(rec);
+        }
+    }
 };
 
 #define B200_FAIL(ctx, code, ...)                         \
@@ -89,6 +130,9 @@ int launch_q4k_matmul_grouped(b200_ctx*, const uint8_t* const* Wptrs, int n_expe
 int launch_f16w_matmul(b200_ctx*, const __half* W, int N, int K, const float* x, int T, float* dst, int ldd,
                        __half* split_scratch /* 2*T*K halves */);
 int launch_f32w_matmul(b200_ctx*, const float* W, int N, int K, const float* x, int T, float* dst, int ldd);
+// grouped f32 form (f32 test models with routed experts): same indirection as the Q4_K grouped matmul
+int launch_f32w_matmul_grouped(b200_ctx*, const float* const* Wptrs, int n_experts, int N, int K, const float* x,
+                               const int32_t* offs, const int32_t* rows, int max_rows_per_expert, float* dst, int ldd);
 int launch_q4k_dequant(b200_ctx*, const uint8_t* W, size_t n_blocks, float* out);
 int launch_q4k_quantize(b200_ctx*, const float* w, size_t n_blocks, uint8_t* out);
 int launch_synth_normal_f32(b200_ctx*, float* out, size_t n, float sigma, uint64_t seed);
@@ -105,6 +149,11 @@ int attn_split_keys();
 int launch_paged_attention(b200_ctx*, const float* q, int ldq, int T, int nH, int nKV, int hd, float scale, float softcap,
                            const int32_t* row_slot, const int32_t* row_pos, int max_keys, KVView kv, AttnScratch sc,
                            float* out, ActQ aq);
+
+// exact class: f64 arithmetic in the CPU path's own order; scores is [T*nH][ld] f32 scratch, ld >= max_keys
+int launch_paged_attention_exact(b200_ctx*, const float* q, int ldq, int T, int nH, int nKV, int hd, double scale,
+                                 double softcap, const int32_t* row_slot, const int32_t* row_pos, int max_keys, KVView kv,
+                                 float* scores, int ld, float* out, ActQ aq);
 
 // sample.cu
 int launch_mask_logits(b200_ctx*, float* logits, int R, int V, const int32_t* row_mask, const uint32_t* masks);

@@ -227,6 +227,7 @@ int launch_add_rmsnorm_quant(b200_ctx* ctx, float* h, const float* delta, const 
                              float* normed, ActQ aq, const int32_t* gather_rows) {
     if (aq.codes && (H % 32)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "quantized rows need a width that is a multiple of 32");
     size_t smem = 8 * sizeof(double) + (size_t)H * sizeof(float);
+    ProfScope ps(ctx, PROF_NORM_QUANT);
     add_rmsnorm_quant_kernel<<<T, 256, smem, ctx->stream>>>(h, delta, w, H, eps, normed, aq.codes, aq.scales, gather_rows);
     LAUNCH_CHECK(ctx);
     return B200_OK;
@@ -241,6 +242,7 @@ int launch_quant_g32(b200_ctx* ctx, const float* x, int T, int K, ActQ aq) {
 }
 
 int launch_swiglu_quant(b200_ctx* ctx, const float* gate_up, int T, int F, int ld, float* mid, ActQ aq) {
+    ProfScope ps(ctx, PROF_SWIGLU);
     if (aq.codes) {
         if (F % 32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "F must be a multiple of 32");
         dim3 grid(ceil_div(F / 32, 8), T);
@@ -270,6 +272,7 @@ int launch_qknorm_rope_kvstore(b200_ctx* ctx, float* qkv, int ld, int T, int nH,
                                const int32_t* row_slot, const int32_t* row_pos, KVView kv) {
     if (hd > 256 || 2 * rot_half > hd) B200_FAIL(ctx, B200_BAD_ARGUMENT, "head_dim up to 256, rotary_dim <= head_dim");
     size_t smem = 2 * (size_t)rot_half * sizeof(double) + 8 * (size_t)hd * sizeof(float);
+    ProfScope ps(ctx, PROF_ROPE_KV);
     qknorm_rope_kvstore_kernel<<<T, 256, smem, ctx->stream>>>(qkv, ld, nH, nKV, hd, rot_half, inv_freq, q_norm, k_norm, eps,
                                                               row_slot, row_pos, kv.k, kv.v, kv.table, kv.max_blocks,
                                                               kv.block_rows);

@@ -183,8 +183,9 @@ struct b200_model {
     ActQ aq_h, aq_ctx, aq_mid;
     __half* split = nullptr;
     AttnScratch asc;
+    float* exact_scores = nullptr;  // exact class: [MR*nH][ctx_cap]
     // MoE
-    float *rl = nullptr, *rw = nullptr, *egu_out = nullptr, *eo = nullptr;
+    float *rl = nullptr, *rw = nullptr, *egu_out = nullptr, *eo = nullptr, *emid = nullptr;
     int32_t *ridx = nullptr, *eoffs = nullptr, *erows = nullptr;
     ActQ aq_emid;
     // pinned host staging
@@ -329,8 +330,15 @@ int run_layers(b200_model* m, int T, int max_keys) {
                                           c.qk_norm ? L.q_norm : nullptr, c.qk_norm ? L.k_norm : nullptr, c.rms_eps,
                                           m->d_row_slot, m->d_row_pos, kv));
         const bool o_q = L.wo.kind == B200_K_Q4K;
-        ST_TRY(launch_paged_attention(ctx, m->qkv, ldq, T, nH, nKV, hd, scale, c.attn_softcap, m->d_row_slot, m->d_row_pos,
-                                      max_keys, kv, m->asc, m->ctxb, o_q ? m->aq_ctx : none));
+        if (m->exact_scores) {
+            const double scale_d = c.attn_scale != 0.f ? (double)c.attn_scale : 1.0 / std::sqrt((double)hd);
+            ST_TRY(launch_paged_attention_exact(ctx, m->qkv, ldq, T, nH, nKV, hd, scale_d, (double)c.attn_softcap, m->d_row_slot,
+                                                m->d_row_pos, max_keys, kv, m->exact_scores, c.ctx_cap, m->ctxb,
+                                                o_q ? m->aq_ctx : none));
+        } else {
+            ST_TRY(launch_paged_attention(ctx, m->qkv, ldq, T, nH, nKV, hd, scale, c.attn_softcap, m->d_row_slot, m->d_row_pos,
+                                          max_keys, kv, m->asc, m->ctxb, o_q ? m->aq_ctx : none));
+        }
         ST_TRY(matmul(m, L.wo, m->ctxb, m->aq_ctx, T, m->att, H));
         if (c.n_experts == 0) {
             const bool g_q = L.gu.kind == B200_K_Q4K, d_q = L.down.kind == B200_K_Q4K;
@@ -343,16 +351,24 @@ int run_layers(b200_model* m, int T, int max_keys) {
             // routed experts (decoder/mlp.go:36-120): f32 router on the f32 normed row, top-k, grouped expert GEMMs,
             // fold in routing-rank order
             const int nE = c.n_experts, kk = c.top_k, F = c.moe_ffn;
-            ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, m->att, L.ffn_norm, T, H, c.rms_eps, m->normed, m->aq_h, nullptr));
+            ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, m->att, L.ffn_norm, T, H, c.rms_eps, m->normed,
+                                            (H % 32 == 0) ? m->aq_h : none, nullptr));
             ST_TRY(launch_f32w_matmul(ctx, (const float*)L.router.p, nE, H, m->normed, T, m->rl, nE));
             ST_TRY(launch_route(ctx, m->rl, T, nE, kk, c.norm_topk, m->ridx, m->rw));
             ST_TRY(launch_group_experts(ctx, m->ridx, T, kk, nE, m->eoffs, m->erows));
             const int32_t* rows_tok = m->erows;
             const int32_t* slot_of = m->erows + (size_t)T * kk;
-            if (L.egu[0].kind != B200_K_Q4K) B200_FAIL(ctx, B200_DECLINED, "routed experts run as Q4_K only");
-            ST_TRY(launch_q4k_matmul_grouped(ctx, L.d_egu_ptrs, nE, 2 * F, H, m->aq_h, m->eoffs, rows_tok, T, m->egu_out, 2 * F));
-            ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, nullptr, m->aq_emid));
-            ST_TRY(launch_q4k_matmul_grouped(ctx, L.d_ed_ptrs, nE, H, F, m->aq_emid, m->eoffs, nullptr, T, m->eo, H));
+            if (L.egu[0].kind == B200_K_Q4K) {
+                ST_TRY(launch_q4k_matmul_grouped(ctx, L.d_egu_ptrs, nE, 2 * F, H, m->aq_h, m->eoffs, rows_tok, T, m->egu_out, 2 * F));
+                ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, nullptr, m->aq_emid));
+                ST_TRY(launch_q4k_matmul_grouped(ctx, L.d_ed_ptrs, nE, H, F, m->aq_emid, m->eoffs, nullptr, T, m->eo, H));
+            } else if (L.egu[0].kind == B200_K_F32) {
+                ST_TRY(launch_f32w_matmul_grouped(ctx, (const float* const*)L.d_egu_ptrs, nE, 2 * F, H, m->normed, m->eoffs, rows_tok, T, m->egu_out, 2 * F));
+                ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, m->emid, ActQ{}));
+                ST_TRY(launch_f32w_matmul_grouped(ctx, (const float* const*)L.d_ed_ptrs, nE, H, F, m->emid, m->eoffs, nullptr, T, m->eo, H));
+            } else {
+                B200_FAIL(ctx, B200_DECLINED, "routed experts run as Q4_K or f32");
+            }
             ST_TRY(launch_fold_experts(ctx, m->eo, m->rw, slot_of, T, kk, H, m->att));
         }
         delta = m->att;
@@ -400,9 +416,6 @@ int b200_model_create(b200_ctx* ctx, const b200_model_cfg* cfg, b200_model** out
     if (c.kv_dtype != 0) B200_FAIL(ctx, B200_DECLINED, "only the fp16 paged KV cache is built");
     if (c.tp_size > 1) B200_FAIL(ctx, B200_DECLINED, "tensor parallel shards are built by the multi-GPU driver, not this entry point");
     if (c.head_dim > 256) B200_FAIL(ctx, B200_DECLINED, "head_dim above 256");
-    const int G = c.n_heads / c.n_kv_heads;
-    const bool fast_attn = (c.head_dim == 64 || c.head_dim == 128) && (G == 1 || G == 2 || G == 4 || G == 8);
-    if (!fast_attn && c.head_dim > 64) B200_FAIL(ctx, B200_DECLINED, "attention shape head_dim=%d group=%d is not built", c.head_dim, G);
     if (c.n_experts > 512) B200_FAIL(ctx, B200_DECLINED, "more than 512 experts");
     auto* m = new b200_model();
     m->ctx = ctx;
@@ -561,11 +574,17 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
         ST_TRY(m->dalloc((void**)&m->erows, (size_t)2 * MR * kk * 4, sb));
         ST_TRY(m->dalloc((void**)&m->egu_out, (size_t)MR * kk * 2 * EF * 4, sb));
         ST_TRY(m->dalloc((void**)&m->eo, (size_t)MR * kk * H * 4, sb));
+        if (m->layers[0].egu[0].kind != B200_K_Q4K) ST_TRY(m->dalloc((void**)&m->emid, (size_t)MR * kk * EF * 4, sb));
         ST_TRY(m->dalloc((void**)&m->aq_emid.codes, (size_t)MR * kk * EF, sb));
         ST_TRY(m->dalloc((void**)&m->aq_emid.scales, (size_t)MR * kk * 2 * ceil_div(EF, 32) * 4, sb));
     }
-    m->asc.max_splits = ceil_div(c.ctx_cap, attn_split_keys());
-    ST_TRY(m->dalloc((void**)&m->asc.partial, attn_scratch_floats(MR, nH, hd, m->asc.max_splits) * 4, sb));
+    const bool fast_attn = (hd == 64 || hd == 128) && ((nH / nKV) == 1 || (nH / nKV) == 2 || (nH / nKV) == 4 || (nH / nKV) == 8);
+    if (c.kernel_class == B200_CLASS_EXACT || (!fast_attn && hd > 64)) {
+        ST_TRY(m->dalloc((void**)&m->exact_scores, (size_t)MR * nH * c.ctx_cap * 4, sb));
+    } else {
+        m->asc.max_splits = ceil_div(c.ctx_cap, attn_split_keys());
+        ST_TRY(m->dalloc((void**)&m->asc.partial, attn_scratch_floats(MR, nH, hd, m->asc.max_splits) * 4, sb));
+    }
     ST_TRY(m->dalloc((void**)&m->hn, (size_t)MLR * H * 4, sb));
     ST_TRY(m->dalloc((void**)&m->logits, (size_t)MLR * c.vocab * 4, sb));
     ST_TRY(m->dalloc((void**)&m->split, (size_t)2 * MLR * H * 2, sb));
@@ -581,8 +600,9 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
         out->kv_slots = c.n_slots;
         out->batch_lo = 2;  // BatchStepRange = (2, KVSlots), backend/cuda/batchstep.go:36-44
         out->batch_hi = c.n_slots;
-        out->has_fast_prefill = 0;
-        out->fast_prefill_floor = 0;
+        // the fast class (fp32 flash attention, split-K small-batch matmul) is not bit-identical to the exact one
+        out->has_fast_prefill = c.kernel_class == B200_CLASS_EXACT ? 0 : 1;
+        out->fast_prefill_floor = c.kernel_class == B200_CLASS_EXACT ? 0 : 1;
         out->tail_min_rows = 1;
         out->batch_greedy_draw = 1;
         out->weight_bytes = (int64_t)m->weight_bytes;
@@ -957,6 +977,38 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
     m->stats.steps += steps;
     m->stats.rows += (int64_t)steps * S;
     m->stats.last_step_device_ms = ms / steps;
+    return B200_OK;
+}
+
+// Debug tap: the residual stream after the last layer of the latest step, [rows][hidden].
+int b200_debug_read_hidden(b200_model* m, float* out, int n) {
+    CUDA_TRY(m->ctx, cudaStreamSynchronize(m->ctx->stream));
+    const float* src = m->h;
+    if (const char* w = getenv("B200_DEBUG_TAP")) {  // qkv | ctx | att: the last layer's buffers
+        if (!strcmp(w, "qkv")) src = m->qkv;
+        if (!strcmp(w, "ctx")) src = m->ctxb;
+        if (!strcmp(w, "att")) src = m->att;
+    }
+    CUDA_TRY(m->ctx, cudaMemcpy(out, src, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    return B200_OK;
+}
+
+int b200_profile(b200_ctx* ctx, unsigned tag_mask) {
+    ctx->prof_mask = tag_mask;
+    return B200_OK;
+}
+
+int b200_profile_read(b200_ctx* ctx, double* ms_by_tag, int64_t* launches_by_tag, int n_tags) {
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int i = 0; i < n_tags; i++) { ms_by_tag[i] = 0; launches_by_tag[i] = 0; }
+    for (auto& r : ctx->prof_recs) {
+        float ms = 0;
+        cudaEventElapsedTime(&ms, r.e0, r.e1);
+        if (r.tag < n_tags) { ms_by_tag[r.tag] += ms; launches_by_tag[r.tag]++; }
+        ctx->prof_pool.push_back(r.e0);
+        ctx->prof_pool.push_back(r.e1);
+    }
+    ctx->prof_recs.clear();
     return B200_OK;
 }
 

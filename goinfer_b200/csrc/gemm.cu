@@ -279,6 +279,23 @@ __global__ void __launch_bounds__(256) dense_matmul_f64_kernel(const WT* __restr
     if (lane == 0) dst[(size_t)t * ldd + n] = (float)s;
 }
 
+__global__ void __launch_bounds__(256) dense_matmul_f64_grouped_kernel(const float* const* __restrict__ Wptrs, int N, int K,
+                                                                       const float* __restrict__ x,
+                                                                       const int32_t* __restrict__ offs,
+                                                                       const int32_t* __restrict__ rows,
+                                                                       float* __restrict__ dst, int ldd) {
+    const int lane = threadIdx.x & 31, e = blockIdx.z;
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), a = offs[e] + blockIdx.y;
+    if (n >= N || a >= offs[e + 1]) return;
+    const float* w = Wptrs[e] + (size_t)n * K;
+    const float* xr = x + (size_t)(rows ? rows[a] : a) * K;
+    double s = 0;
+    for (int k = lane; k < K; k += 32) s += (double)xr[k] * (double)w[k];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) dst[(size_t)a * ldd + n] = (float)s;
+}
+
 // ---- Q4_K block utilities ----
 __global__ void q4k_dequant_kernel(const uint8_t* __restrict__ W, size_t n_blocks, float* __restrict__ out) {
     const size_t blk = blockIdx.x;
@@ -387,6 +404,7 @@ __global__ void synth_q4k_kernel(uint8_t* out, size_t n_blocks, float sigma, uin
 template <int NT, bool SPLITK>
 int run_q4k(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, int T, float* dst, int ldd) {
     dim3 grid(SPLITK ? ceil_div(N, 16) : ceil_div(N, 128), ceil_div(T, 8 * NT));
+    ProfScope ps(ctx, PROF_Q4K_GEMM);
     q4k_gemm_mma_kernel<NT, SPLITK, false><<<grid, 256, 0, ctx->stream>>>(W, nullptr, N, nSB, aq.codes, aq.scales, T, nullptr,
                                                                          nullptr, dst, ldd);
     LAUNCH_CHECK(ctx);
@@ -397,10 +415,11 @@ int run_q4k(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, int T, flo
 
 int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, int klass) {
     if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
-    (void)klass;
     const int nSB = K / 256;
-    // Rows up to 8 are HBM-bound: split K over the CTA's warps. Beyond that one ascending chain per output.
-    if (T <= 8) return run_q4k<1, true>(ctx, W, N, nSB, aq, T, dst, ldd);
+    // Rows up to 8 are HBM-bound: split K over the CTA's warps (unless the exact class asks for the one ascending
+    // chain per output that every larger batch uses, so a row's bits do not depend on its batch).
+    if (T <= 8) return klass == B200_CLASS_EXACT ? run_q4k<1, false>(ctx, W, N, nSB, aq, T, dst, ldd)
+                                                  : run_q4k<1, true>(ctx, W, N, nSB, aq, T, dst, ldd);
     if (T <= 16) return run_q4k<2, false>(ctx, W, N, nSB, aq, T, dst, ldd);
     if (T <= 32) return run_q4k<4, false>(ctx, W, N, nSB, aq, T, dst, ldd);
     return run_q4k<8, false>(ctx, W, N, nSB, aq, T, dst, ldd);
@@ -410,6 +429,7 @@ int launch_q4k_matmul_grouped(b200_ctx* ctx, const uint8_t* const* Wptrs, int n_
                               const int32_t* offs, const int32_t* rows, int max_rows_per_expert, float* dst, int ldd) {
     if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
     dim3 grid(ceil_div(N, 128), ceil_div(max_rows_per_expert, 16), n_experts);
+    ProfScope ps(ctx, PROF_Q4K_GEMM);
     q4k_gemm_mma_kernel<2, false, true><<<grid, 256, 0, ctx->stream>>>(nullptr, Wptrs, N, K / 256, aq.codes, aq.scales, 0, offs,
                                                                        rows, dst, ldd);
     LAUNCH_CHECK(ctx);
@@ -430,6 +450,7 @@ int launch_f16w_matmul(b200_ctx* ctx, const __half* W, int N, int K, const float
     __half* lo = split_scratch + n;
     split_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(x, n, hi, lo);
     LAUNCH_CHECK(ctx);
+    ProfScope ps(ctx, PROF_HEAD_GEMM);
     if (T <= 8) {
         dim3 grid(ceil_div(N, 128), ceil_div(T, 8));
         f16w_gemm_mma_kernel<1><<<grid, 256, 0, ctx->stream>>>(W, N, K, hi, lo, T, dst, ldd);
@@ -447,6 +468,14 @@ int launch_f16w_matmul(b200_ctx* ctx, const __half* W, int N, int K, const float
 int launch_f32w_matmul(b200_ctx* ctx, const float* W, int N, int K, const float* x, int T, float* dst, int ldd) {
     dim3 grid(ceil_div(N, 8), T);
     dense_matmul_f64_kernel<float><<<grid, 256, 0, ctx->stream>>>(W, N, K, x, dst, ldd);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_f32w_matmul_grouped(b200_ctx* ctx, const float* const* Wptrs, int n_experts, int N, int K, const float* x,
+                               const int32_t* offs, const int32_t* rows, int max_rows_per_expert, float* dst, int ldd) {
+    dim3 grid(ceil_div(N, 8), max_rows_per_expert, n_experts);
+    dense_matmul_f64_grouped_kernel<<<grid, 256, 0, ctx->stream>>>(Wptrs, N, K, x, offs, rows, dst, ldd);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }

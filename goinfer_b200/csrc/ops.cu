@@ -155,7 +155,8 @@ int b200_op_draw(b200_ctx* ctx, const float* logits, int rows, int vocab, const 
 }
 
 int b200_op_attention(b200_ctx* ctx, const float* q, const float* k, const float* v, const int32_t* n_keys, int rows, int max_keys,
-                      int n_heads, int n_kv_heads, int head_dim, float scale, float softcap, int block_rows, float* out) {
+                      int n_heads, int n_kv_heads, int head_dim, float scale, float softcap, int block_rows, int klass,
+                      float* out) {
     if (rows <= 0 || max_keys <= 0 || block_rows <= 0 || n_heads % n_kv_heads) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad attention shape");
     Tmp t;
     const int max_blocks = ceil_div(max_keys, block_rows);
@@ -182,8 +183,16 @@ int b200_op_attention(b200_ctx* ctx, const float* q, const float* k, const float
     LAUNCH_CHECK(ctx);
     KVView kv{kp, vp, tbl, max_blocks, block_rows, n_kv_heads, head_dim};
     const float sc_ = scale != 0.f ? scale : (float)(1.0 / std::sqrt((double)head_dim));
-    ST_TRY(launch_paged_attention(ctx, dq, n_heads * head_dim, rows, n_heads, n_kv_heads, head_dim, sc_, softcap, rslot, rpos,
-                                  max_keys, kv, sc, dout, ActQ{}));
+    if (klass == B200_CLASS_EXACT) {
+        float* scores;
+        TMP_GET(ctx, t, scores, (size_t)rows * n_heads * max_keys);
+        const double sd = scale != 0.f ? (double)scale : 1.0 / std::sqrt((double)head_dim);
+        ST_TRY(launch_paged_attention_exact(ctx, dq, n_heads * head_dim, rows, n_heads, n_kv_heads, head_dim, sd, (double)softcap,
+                                            rslot, rpos, max_keys, kv, scores, max_keys, dout, ActQ{}));
+    } else {
+        ST_TRY(launch_paged_attention(ctx, dq, n_heads * head_dim, rows, n_heads, n_kv_heads, head_dim, sc_, softcap, rslot, rpos,
+                                      max_keys, kv, sc, dout, ActQ{}));
+    }
     D2H(ctx, out, dout, qn * 4);
     SYNC(ctx);
     return B200_OK;

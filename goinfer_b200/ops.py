@@ -82,7 +82,7 @@ class Ops:
                                           0 if mk is None else mk.shape[0], _p(ids, C.c_int32)))
         return ids
 
-    def attention(self, q, k, v, n_keys, n_heads, n_kv_heads, head_dim, scale=0.0, softcap=0.0, block_rows=16):
+    def attention(self, q, k, v, n_keys, n_heads, n_kv_heads, head_dim, scale=0.0, softcap=0.0, block_rows=16, klass=0):
         q = np.ascontiguousarray(q, np.float32)
         k = np.ascontiguousarray(k, np.float32)
         v = np.ascontiguousarray(v, np.float32)
@@ -91,7 +91,7 @@ class Ops:
         out = np.empty_like(q)
         self._check(self.lib.b200_op_attention(self.ctx, _p(q, C.c_float), _p(k, C.c_float), _p(v, C.c_float), _p(nk, C.c_int32),
                                                rows, max_keys, n_heads, n_kv_heads, head_dim, C.c_float(scale), C.c_float(softcap),
-                                               block_rows, _p(out, C.c_float)))
+                                               block_rows, klass, _p(out, C.c_float)))
         return out
 
     def bench_q4k_matmul(self, M, K, N, klass=0, n_weight_copies=8, warmup=3, iters=20) -> float:

@@ -67,8 +67,11 @@ extern "C" {
 /* ---- kernel classes (b200_model_cfg.kernel_class) -------------------------------------------------
  * The reference separates exact kernels from fast, non-bit-identical ones by a row floor
  * (resident.Caps.HasFastPrefill / FastPrefillFloor, decoder/resident/forward.go:119-146). */
-#define B200_CLASS_AUTO  0 /* exact integer-dot kernels below fast_floor rows, tcgen05 fp16 GEMM from it */
-#define B200_CLASS_EXACT 1 /* exact kernels at every row count                                        */
+#define B200_CLASS_AUTO  0 /* fast class: fp32 flash-decode attention, split-K Q4_K matmul at up to 8 rows.
+                              Integer dots stay exact; f32 sums are folded in another order than the CPU path's. */
+#define B200_CLASS_EXACT 1 /* exact class: attention in f64 in the CPU path's own order (decoder/forwardn.go:379-499)
+                              and one ascending f32 chain per matmul output at every row count, so a row's bits do
+                              not depend on its batch (decoder/resident/subsystems.go:102-110)             */
 
 typedef struct b200_ctx b200_ctx;
 typedef struct b200_model b200_model;
@@ -200,6 +203,17 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
                             int32_t* ids_out /*[steps][n_seqs] or NULL*/, float* ms_out);
 
 int b200_stats(b200_model* m, b200_stats_t* out);
+/* Debug tap for parity work: copies the first n floats of the residual stream ([rows][hidden]) as the latest
+ * step left it after its last layer. */
+int b200_debug_read_hidden(b200_model* m, float* out, int n);
+
+/* Per-launch CUDA-event timing of kernel classes, on the stream the kernels are launched on (the role of
+ * the reference's per-phase decodeTiming clocks, decoder/policy_decode.go:10-14). tag_mask bit i enables
+ * class i: 0 attention split, 1 attention combine, 2 Q4_K matmul, 3 LM-head matmul, 4 norm+quant,
+ * 5 RoPE+KV store, 6 SwiGLU+quant. b200_profile_read synchronizes, sums milliseconds and launches per class
+ * since the last read, and clears the records. */
+int b200_profile(b200_ctx* ctx, unsigned tag_mask);
+int b200_profile_read(b200_ctx* ctx, double* ms_by_tag, int64_t* launches_by_tag, int n_tags);
 
 /* ---- operator-level entry points (host buffers in, host buffers out) -------------------------------
  * The reference exposes its matmul as Backend.MatmulBT(a, b, dst, M, K, N) (decoder/backend.go:23-32)
@@ -229,7 +243,7 @@ int b200_op_draw(b200_ctx* ctx, const float* logits, int rows, int vocab, const 
  * (decoder/forwardn.go:295-501, acc64 branch). */
 int b200_op_attention(b200_ctx* ctx, const float* q, const float* k, const float* v, const int32_t* n_keys,
                       int rows, int max_keys, int n_heads, int n_kv_heads, int head_dim, float scale,
-                      float softcap, int block_rows, float* out);
+                      float softcap, int block_rows, int klass /* 0 fast fp32, 1 exact f64 */, float* out);
 
 /* Device-resident micro-benchmarks: average device milliseconds per launch over `iters` launches after
  * `warmup`, of the kernel the step would pick (or `klass`), on synthetic resident data. */

@@ -76,6 +76,12 @@ class OracleResident(Resident):
         return out
 
 
+def last_tap(which: int, n: int) -> np.ndarray:
+    out = np.zeros(n, np.float32)
+    lib().oracle_last_tap(which, out.ctypes.data_as(C.POINTER(C.c_float)), n)
+    return out
+
+
 def _p(a, t):
     return a.ctypes.data_as(C.POINTER(t)) if a is not None else None
 

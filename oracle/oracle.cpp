@@ -27,6 +27,9 @@
 #ifdef _OPENMP
 #include <omp.h>
 #endif
+#ifdef __AVX2__
+#include <immintrin.h>
+#endif
 
 namespace {
 
@@ -187,6 +190,23 @@ void q4k_quantize_block(const float* w, uint8_t* blk) {
         for (int l = 0; l < 32; l++) qs[32 * p + l] = (uint8_t)(code[64 * p + l] | (code[64 * p + 32 + l] << 4));
 }
 
+// exact int32 dot of 32 unsigned weight codes (0..15) and 32 signed activation codes (-127..127)
+inline int dot32_u8s8(const uint8_t* w, const int8_t* a) {
+#ifdef __AVX2__
+    const __m256i vw = _mm256_loadu_si256((const __m256i*)w), va = _mm256_loadu_si256((const __m256i*)a);
+    const __m256i p16 = _mm256_maddubs_epi16(vw, va);  // pairs: |2*15*127| fits int16
+    const __m256i p32 = _mm256_madd_epi16(p16, _mm256_set1_epi16(1));
+    __m128i s = _mm_add_epi32(_mm256_castsi256_si128(p32), _mm256_extracti128_si256(p32, 1));
+    s = _mm_add_epi32(s, _mm_shuffle_epi32(s, 0x4E));
+    s = _mm_add_epi32(s, _mm_shuffle_epi32(s, 0xB1));
+    return _mm_cvtsi128_si32(s);
+#else
+    int d = 0;
+    for (int l = 0; l < 32; l++) d += (int)w[l] * (int)a[l];
+    return d;
+#endif
+}
+
 // ---- weights ----
 struct Mat {
     int kind = -1, rows = 0, cols = 0;
@@ -226,9 +246,7 @@ void matmul(const Mat& W, const float* a, int T, float* dst) {
                             const int8_t* ca = &codes[(size_t)t * K + 256 * b + 64 * p];
                             const float* aS = &scales[(size_t)t * 2 * nG];
                             const float* asum = aS + nG;
-                            int lo = 0, hi = 0;
-                            for (int l = 0; l < 32; l++) lo += (int)cw[l] * (int)ca[l];
-                            for (int l = 0; l < 32; l++) hi += (int)cw[32 + l] * (int)ca[32 + l];
+                            const int lo = dot32_u8s8(cw, ca), hi = dot32_u8s8(cw + 32, ca + 32);
                             float f = acc[t];
                             f = std::fmaf((float)lo, dsLo * aS[g], f);
                             f = std::fmaf((float)hi, dsHi * aS[g + 1], f);
@@ -243,19 +261,25 @@ void matmul(const Mat& W, const float* a, int T, float* dst) {
         }
         return;
     }
-#pragma omp parallel for schedule(static)
-    for (int n = 0; n < N; n++) {
-        for (int t = 0; t < T; t++) {
-            const float* x = a + (size_t)t * K;
-            double s = 0;
+#pragma omp parallel
+    {
+        std::vector<float> wide(W.kind == B200_K_F16 ? K : 0);  // one f16 row widened once for all T rows
+#pragma omp for schedule(static)
+        for (int n = 0; n < N; n++) {
+            const float* w;
             if (W.kind == B200_K_F32) {
-                const float* w = &W.f32[(size_t)n * K];
-                for (int k = 0; k < K; k++) s += (double)x[k] * (double)w[k];
+                w = &W.f32[(size_t)n * K];
             } else {
-                const uint16_t* w = &W.f16[(size_t)n * K];
-                for (int k = 0; k < K; k++) s += (double)x[k] * (double)f16_to_f32(w[k]);
+                const uint16_t* h = &W.f16[(size_t)n * K];
+                for (int k = 0; k < K; k++) wide[k] = f16_to_f32(h[k]);
+                w = wide.data();
             }
-            dst[(size_t)t * N + n] = (float)s;
+            for (int t = 0; t < T; t++) {
+                const float* x = a + (size_t)t * K;
+                double s = 0;
+                for (int k = 0; k < K; k++) s += (double)x[k] * (double)w[k];
+                dst[(size_t)t * N + n] = (float)s;
+            }
         }
     }
 }
@@ -596,6 +620,9 @@ int oracle_upload_kv(oracle_model* m, int slot, int layer, int base, int n, cons
     for (int i = 0; i < need; i++)
         if (!s.table[i]) { s.table[i] = m->free_blocks.back(); m->free_blocks.pop_back(); }
     if (s.k[layer].size() < (size_t)(base + n) * kvDim) {
+        const size_t room = std::min((size_t)m->c.ctx_cap, (size_t)(base + n) + 64) * kvDim;  // headroom for the appends that follow
+        s.k[layer].reserve(room);
+        s.v[layer].reserve(room);
         s.k[layer].resize((size_t)(base + n) * kvDim);
         s.v[layer].resize((size_t)(base + n) * kvDim);
     }
@@ -607,10 +634,29 @@ int oracle_upload_kv(oracle_model* m, int slot, int layer, int base, int n, cons
 }
 
 // Debug taps: per-layer hidden after each layer of the last step (tests localise a mismatch with them).
-static std::vector<float> g_tap;
+static std::vector<float> g_tap, g_tap_q, g_tap_ctx, g_tap_att;
+static double g_layers_s = 0, g_head_s = 0;  // wall time of the latest step's layer loop and head
+static double now_s() {
+#ifdef _OPENMP
+    return omp_get_wtime();
+#else
+    return (double)clock() / CLOCKS_PER_SEC;
+#endif
+}
+void oracle_last_timing(double* layers_s, double* head_s) {
+    *layers_s = g_layers_s;
+    *head_s = g_head_s;
+}
 int oracle_last_hidden(float* out, int n) {
     for (int i = 0; i < n && i < (int)g_tap.size(); i++) out[i] = g_tap[i];
     return (int)g_tap.size();
+}
+// which: 0 residual stream after the last layer, 1 the last layer's q after RoPE [T][n_heads*head_dim],
+// 2 its attention context, 3 its FFN output.
+int oracle_last_tap(int which, float* out, int n) {
+    const std::vector<float>& t = which == 1 ? g_tap_q : which == 2 ? g_tap_ctx : which == 3 ? g_tap_att : g_tap;
+    for (int i = 0; i < n && i < (int)t.size(); i++) out[i] = t[i];
+    return (int)t.size();
 }
 
 // The step: decoder/cpu_batch.go:166-197 decodeMultiStep + decoder/program_cpu_n.go:406-563 walkMulti
@@ -679,6 +725,7 @@ int oracle_step_ragged(oracle_model* m, int n_seqs, const int32_t* slot, const i
             if (c.embed_scale != 0.f && c.embed_scale != 1.f) for (int j = 0; j < H; j++) hr[j] *= c.embed_scale;
         }
     }
+    const double t_layers0 = now_s();
     for (int l = 0; l < c.n_layers; l++) {
         Layer& L = m->layers[l];
         rmsnorm(norm.data(), h.data(), L.attn_norm.data(), T, H, c.rms_eps);
@@ -697,7 +744,15 @@ int oracle_step_ragged(oracle_model* m, int n_seqs, const int32_t* slot, const i
         for (int r = 0; r < T; r++) {
             Slot& s = m->slots[slot[rseq[r]]];
             size_t need_sz = (size_t)(rpos[r] + 1) * kvDim;
-            if (s.k[l].size() < need_sz) { s.k[l].resize(need_sz); s.v[l].resize(need_sz); }
+            if (s.k[l].size() < need_sz) {
+                if (s.k[l].capacity() < need_sz) {  // grow geometrically up to the slot's cap: an append must not copy the cache
+                    const size_t want = std::min((size_t)c.ctx_cap * kvDim, std::max(need_sz, 2 * s.k[l].capacity()));
+                    s.k[l].reserve(want);
+                    s.v[l].reserve(want);
+                }
+                s.k[l].resize(need_sz);
+                s.v[l].resize(need_sz);
+            }
             for (int i = 0; i < kvDim; i++) {
                 s.k[l][(size_t)rpos[r] * kvDim + i] = m->kv_round(k[(size_t)r * kvDim + i]);
                 s.v[l][(size_t)rpos[r] * kvDim + i] = m->kv_round(v[(size_t)r * kvDim + i]);
@@ -744,8 +799,11 @@ int oracle_step_ragged(oracle_model* m, int n_seqs, const int32_t* slot, const i
             }
         }
         for (size_t i = 0; i < (size_t)T * H; i++) h[i] += att[i];
+        if (l == c.n_layers - 1) { g_tap_q = q; g_tap_ctx = ctx; g_tap_att = att; }
     }
     g_tap = h;
+    g_layers_s = now_s() - t_layers0;
+    const double t_head0 = now_s();
     // final norm + LM head for the rows that return logits or draw (decoder/forwardn.go:800-831)
     std::vector<int> out_rows;   // rows whose logits are returned
     std::vector<int> draw_rows;  // per sequence: row that is drawn or -1
@@ -799,6 +857,7 @@ int oracle_step_ragged(oracle_model* m, int n_seqs, const int32_t* slot, const i
         }
         if (ids_out) ids_out[i] = id;
     }
+    g_head_s = now_s() - t_head0;
     return B200_OK;
 }
 

@@ -14,9 +14,14 @@ pytestmark = pytest.mark.gpu
 
 
 def build_pair(oracle_lib, shape_name, n_slots=4, ctx_cap=256, seed=0, n_layers=0, kv_block_rows=16, max_rows=0,
-               kv_pool_blocks=0):
+               kv_pool_blocks=0, klass=abi.CLASS_EXACT):
+    """The GPU resident and the oracle with the same host-built weights. The exact kernel class is the default:
+    per-32 int8 activation quantization is discontinuous, so an implementation that differs from the oracle in
+    the last bit of an attention output flips activation codes and the difference grows with depth (about 1% of
+    the FFN output per layer once one code has flipped); only the exact class is held to the logit tolerance at
+    depth. The fast class is held to it on shallow models and to the reference's own GPU-vs-CPU bars at depth."""
     s = synth.SHAPES[shape_name]
-    mk = lambda: synth.make_cfg(s, n_slots, ctx_cap, kv_block_rows, kv_pool_blocks, max_rows, abi.CLASS_EXACT, n_layers)
+    mk = lambda: synth.make_cfg(s, n_slots, ctx_cap, kv_block_rows, kv_pool_blocks, max_rows, klass, n_layers)
     g, o = Resident(mk()), oracle_lib.OracleResident(mk())
     synth.load_host_weights([g, o], s, seed, n_layers)
     g.finalize()
@@ -122,6 +127,41 @@ def test_batch_rows_are_bit_identical_to_their_own_forward(oracle_lib):
     for i in range(4):
         solo = g.Forward(None, len(prompts[i]), slot=i + 4, token=11 + i)
         assert np.array_equal(batch[i].Logits, solo)
+
+
+def test_exact_class_prefill_rows_equal_token_by_token(oracle_lib):
+    """ForwardN rows are bit-identical to sequential Forward (decoder/resident/forward.go:5-33; the CPU path's own
+    contract, decoder/program_cpu_n.go:10-12): a 40-row prefill against 40 single-row steps on another slot."""
+    g, o, s = build_pair(oracle_lib, "tiny-qknorm", n_slots=2, ctx_cap=64, seed=13)
+    p = np.random.default_rng(5).integers(0, s.vocab, 40).tolist()
+    a = g.PrefillLast(None, 0, 0, p)
+    for i, t in enumerate(p):
+        b = g.Forward(None, i, slot=1, token=t)
+    assert np.array_equal(a, b)
+
+
+def test_fast_class_meets_the_reference_gpu_vs_cpu_bars(oracle_lib):
+    """The fast class (fp32 flash-decode attention, split-K small-batch matmul) against the oracle: within the logit
+    tolerance on a shallow model, and at depth within the bars the reference itself holds its GPU backends to
+    against its CPU path (cosine >= 0.995, rel-L2 <= 0.10: decoder/selftest_gpu.go:30-35)."""
+    g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=2, ctx_cap=96, seed=21, klass=abi.CLASS_AUTO)
+    p = np.random.default_rng(6).integers(0, s.vocab, 50).tolist()
+    ok, err = close_logits(g.PrefillLast(None, 0, 0, p), o.PrefillLast(None, 0, 0, p))
+    assert ok, err
+    for step in range(8):
+        ok, err = close_logits(g.Forward(None, 50 + step, 0, token=step + 1), o.Forward(None, 50 + step, 0, token=step + 1))
+        assert ok, (step, err)
+    g.Close()
+    g, o, s = build_pair(oracle_lib, "c1-1.1b", n_slots=2, ctx_cap=96, seed=1, n_layers=6, max_rows=64, klass=abi.CLASS_AUTO)
+    p = np.random.default_rng(7).integers(0, s.vocab, 40).tolist()
+    lg, lo = g.PrefillLast(None, 0, 0, p).astype(np.float64), o.PrefillLast(None, 0, 0, p).astype(np.float64)
+    for step in range(4):
+        cos = float(lg @ lo / (np.linalg.norm(lg) * np.linalg.norm(lo)))
+        rel = float(np.linalg.norm(lg - lo) / np.linalg.norm(lo))
+        assert cos >= 0.995 and rel <= 0.10, (step, cos, rel)
+        t = int(np.argmax(lo))
+        lg = g.Forward(None, 40 + step, 0, token=t).astype(np.float64)
+        lo = o.Forward(None, 40 + step, 0, token=t).astype(np.float64)
 
 
 def test_kv_pool_full_writes_nothing_and_bad_steps_are_refused(oracle_lib):

@@ -35,8 +35,9 @@ def test_quant_g32_bit_exact(ops, oracle_lib):
 
 def test_q4k_dequant_bit_exact_on_random_blocks(ops, oracle_lib):
     rng = np.random.default_rng(1)
-    raw = q4k.random_blocks(rng, 16, 1024)
-    raw[:144 * 2][4:] = 0xFF            # a saturated block: every scale, minimum and code at its maximum
+    raw = q4k.random_blocks(rng, 16, 1024).reshape(-1, 144)
+    raw[:2, 4:] = 0xFF                  # saturated blocks: every scale, minimum and code at its maximum
+    raw = raw.reshape(-1)
     a = oracle_lib.op_q4k_dequant(raw, 16, 1024)
     b = ops.q4k_dequant(raw, 16, 1024)
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
@@ -63,13 +64,16 @@ def test_q4k_matmul_exact_class(ops, oracle_lib, M):
     a[0, :32] = 0
     want = oracle_lib.op_q4k_matmul(raw, a, N)
     got = ops.q4k_matmul(raw, a, N, klass=1)
-    if M > 8:
-        # one ascending chain per output, the oracle's order: bit-identical
-        assert np.array_equal(want.view(np.uint32), got.view(np.uint32))
+    # exact class: one ascending chain per output, the oracle's order: bit-identical at every row count
+    assert np.array_equal(want.view(np.uint32), got.view(np.uint32))
     ref = oracle_lib.op_q4k_matmul_f64(raw, a, N)
     scale = np.abs(ref).max()
     assert np.abs(got - ref).max() <= 1e-5 * scale          # the reference's own GEMV bar
-    assert np.abs(got - want).max() <= 2e-6 * scale
+    fast = ops.q4k_matmul(raw, a, N, klass=0)               # fast class: split-K up to 8 rows
+    assert np.abs(fast - ref).max() <= 1e-5 * scale
+    assert np.abs(fast - want).max() <= 2e-6 * scale
+    if M > 8:
+        assert np.array_equal(fast, got)
 
 
 def test_q4k_matmul_saturated_and_random_bytes(ops, oracle_lib):
@@ -94,11 +98,14 @@ def test_q4k_batch_rows_equal_single_rows_within_class(ops):
     raw = q4k.quantize(rng.normal(0, 0.02, (N, K)).astype(np.float32))
     a = rng.normal(0, 1, (8, K)).astype(np.float32)
     full = ops.q4k_matmul(raw, a, N, klass=1)
-    for r in range(8):
-        assert np.array_equal(full[r], ops.q4k_matmul(raw, a[r:r + 1], N, klass=1)[0])
+    for klass in (0, 1):
+        full = ops.q4k_matmul(raw, a, N, klass=klass)
+        for r in range(8):
+            assert np.array_equal(full[r], ops.q4k_matmul(raw, a[r:r + 1], N, klass=klass)[0])
     b = rng.normal(0, 1, (40, K)).astype(np.float32)
     big = ops.q4k_matmul(raw, b, N, klass=1)
     assert np.array_equal(big[:12], ops.q4k_matmul(raw, b[:12], N, klass=1))
+    assert np.array_equal(big[:3], ops.q4k_matmul(raw, b[:3], N, klass=1))   # exact class: across the 8-row boundary too
 
 
 def test_rmsnorm(ops, oracle_lib):
@@ -115,7 +122,7 @@ def test_route_indices_bit_exact(ops, oracle_lib):
     for nE, k, norm in ((8, 2, True), (128, 8, True), (128, 8, False), (64, 6, True)):
         lg = rng.normal(0, 1, (33, nE)).astype(np.float32)
         lg[0, :] = 0.25                       # all tied: lowest indices win, in order
-        lg[1, 3] = lg[1, 9] = 7.0             # a tie at the top
+        lg[1, 3] = lg[1, nE - 2] = 7.0        # a tie at the top
         i0, w0 = oracle_lib.op_route(lg, k, norm)
         i1, w1 = ops.route(lg, k, norm)
         assert np.array_equal(i0, i1)
@@ -170,10 +177,14 @@ def test_paged_attention_matches_the_f64_oracle(ops, oracle_lib, nH, nKV, hd):
     for cap in (0.0, 30.0):
         want = oracle_lib.op_attention(q, k, v, n_keys, nH, nKV, hd, scale, cap)
         got = ops.attention(q, k, v, n_keys, nH, nKV, hd, scale, cap, block_rows=16)
-        np.testing.assert_allclose(got, want, atol=2e-5, rtol=1e-4)   # fp32 online softmax vs f64
-    got64 = ops.attention(q, k, v, n_keys, nH, nKV, hd, scale, 0.0, block_rows=64)
-    np.testing.assert_allclose(got64, want if cap == 0.0 else oracle_lib.op_attention(q, k, v, n_keys, nH, nKV, hd, scale, 0.0),
-                               atol=2e-5, rtol=1e-4)
+        np.testing.assert_allclose(got, want, atol=2e-5, rtol=1e-4)   # fast class: fp32 online softmax vs f64
+        exact = ops.attention(q, k, v, n_keys, nH, nKV, hd, scale, cap, block_rows=16, klass=1)
+        # exact class: the oracle's own f64 order; only libm's last-ulp exp/tanh can move a rounding
+        assert (exact.view(np.uint32) != want.view(np.uint32)).mean() < 1e-3
+        np.testing.assert_allclose(exact, want, atol=0, rtol=3e-7)
+    want0 = oracle_lib.op_attention(q, k, v, n_keys, nH, nKV, hd, scale, 0.0)
+    np.testing.assert_allclose(ops.attention(q, k, v, n_keys, nH, nKV, hd, scale, 0.0, block_rows=64), want0, atol=2e-5, rtol=1e-4)
+    np.testing.assert_allclose(ops.attention(q, k, v, n_keys, nH, nKV, hd, scale, 0.0, block_rows=64, klass=1), want0, atol=0, rtol=3e-7)
 
 
 def test_attention_properties_at_full_context(ops):
