@@ -39,7 +39,7 @@ def workload_config(n_gpus):
     return {"workload": "c3: 8B-shape Q4_K (W4A8 per-32), B=256 ragged decode, contexts U[128,8192] seed 2, paged fp16 KV "
                         "16-token blocks", "global_batch": B * n_gpus, "parallelism": f"replicas x{n_gpus} (no collective)",
             "l2": "inputs (about 160 GB of KV and 6.4 GB of weights per step) are far larger than the 126 MB L2",
-            "kernel_class": "fast (fp32 flash-decode attention)"}
+            "kernel_class": "fast (tensor-core flash-decode attention, fp32 softmax and accumulate)"}
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -112,7 +112,7 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------------------------------
 class Clocks:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
@@ -125,19 +125,25 @@ class Clocks:
         except OSError:
             self.p = None
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summary of the samples taken between the two wall-clock times (the timed region)."""
         if not self.p:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.p.terminate()
         self.p.wait()
-        sm, mx, reasons = [], [], set()
+        import datetime
+        sm, mx, pw, reasons = [], [], [], set()
         for ln in open(self.path):
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
             try:
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                if t_begin is not None and not (t_begin - 0.05 <= ts <= t_end + 0.05):
+                    continue
                 sm.append(float(f[1]))
                 mx.append(float(f[2]))
+                pw.append(float(f[3]))
             except ValueError:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
@@ -145,7 +151,7 @@ class Clocks:
                     reasons.add(name)
         os.unlink(self.path)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
 def run_gpu(args):
@@ -164,7 +170,7 @@ def run_gpu(args):
     K, W = args.steps, max(args.warmup, 0)
     s = synth.SHAPES["c3-8b"]
     ctx = contexts()
-    growth = 2 * (K + W) + 8                       # positions each sequence may advance over both timed loops
+    growth = 2 * (K + W) + 12                      # positions each sequence may advance over the timed loops
     cap = int(ctx.max()) + growth
     blocks = 1 + int(np.ceil((ctx + growth) / 16).sum())
     cfg = synth.make_cfg(s, B, cap, 16, blocks, B, abi.CLASS_AUTO)
@@ -193,18 +199,19 @@ def run_gpu(args):
             torch.cuda.synchronize()
 
         # ---- resident leg: `value` ----
+        clocks = Clocks(local)
+        clocks.start()
         if W:
             check(lib.b200_decode_loop_device(m, B, p32(slot), p32(pos), p32(first), W, 1, None, C.byref(ms)))
             pos += W
         lib.b200_profile(bctx, 1)                   # per-launch events on the attention split kernel only
-        clocks = Clocks(local)
         barrier()
-        clocks.start()
+        wall0 = time.time()
         launches0 = lib.b200_launch_count(bctx)
         check(lib.b200_decode_loop_device(m, B, p32(slot), p32(pos), p32(first), K, 1, None, C.byref(ms)))
         barrier()
+        wall1 = time.time()
         launches = int(lib.b200_launch_count(bctx) - launches0)
-        clk = clocks.stop()
         dev_ms = float(ms.value)
         tag_ms = (C.c_double * 8)()
         tag_n = (C.c_int64 * 8)()
@@ -213,7 +220,8 @@ def run_gpu(args):
         keys_per_step = [float((pos + 1 + i).sum()) for i in range(K)]      # keys read per layer at timed step i
         pos += K
         attn_bytes_per_launch = float(np.mean(keys_per_step)) * 2 * s.n_kv_heads * s.head_dim * 2
-        attn_ms_per_launch = tag_ms[0] / max(1, tag_n[0])
+        attn_ms_total, attn_launches = float(tag_ms[0]), int(tag_n[0])
+        attn_ms_per_launch = attn_ms_total / max(1, attn_launches)
 
         # ---- end-to-end leg: the C ABI step call with host buffers, H2D and D2H inside the timed region ----
         embs = torch.empty((B, s.hidden), dtype=torch.float32).normal_(0, 0.02).pin_memory()
@@ -235,6 +243,17 @@ def run_gpu(args):
             step_host()
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
+        clk = clocks.stop(wall0, wall1)
+
+        # ---- per-class breakdown of one more resident step (every kernel class bracketed by events; not part of `value`) ----
+        lib.b200_profile(bctx, 0xFF)
+        check(lib.b200_decode_loop_device(m, B, p32(slot), p32(pos), p32(first), 2, 1, None, C.byref(ms)))
+        pos += 2
+        lib.b200_profile_read(bctx, tag_ms, tag_n, 8)
+        lib.b200_profile(bctx, 0)
+        names = ("attn_split", "attn_combine", "q4k_matmul", "head_matmul", "norm_quant", "rope_kvstore", "swiglu_quant", "other")
+        breakdown = {n: {"ms_per_step": tag_ms[i] / 2, "launches_per_step": int(tag_n[i] // 2)} for i, n in enumerate(names) if tag_n[i]}
+        breakdown["step_ms_with_events"] = float(ms.value) / 2
 
     if world > 1:
         import torch.distributed as dist
@@ -265,12 +284,13 @@ def run_gpu(args):
                 "ms_per_step": e2e_s / K * 1e3},
         "gpu_launches": launches,
         "clocks": clk,
-        "roofline": {"kernel": "attn_split_kernel<128,4> (paged flash-decode attention)", "bound": "hbm",
+        "roofline": {"kernel": "attn_mma_kernel<128,4> (paged tensor-core flash-decode attention)", "bound": "hbm",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": "of measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "of fallback",
                      "frac_of_8tbs_nominal": achieved / 8000.0, "traffic": traffic,
                      "algorithmic_bytes_per_launch": attn_bytes_per_launch, "ms_per_launch": attn_ms_per_launch,
-                     "launches_timed": int(tag_n[0]), "share_of_step": tag_ms[0] / dev_ms if dev_ms else None},
+                     "launches_timed": attn_launches, "share_of_step": attn_ms_total / dev_ms if dev_ms else None},
+        "breakdown": breakdown,
         "memory": {"weights_gb": caps.weight_bytes / 1e9, "kv_gb": caps.kv_bytes / 1e9, "scratch_gb": caps.scratch_bytes / 1e9},
     }
     if world == 1 and not args.no_cpu:

@@ -13,6 +13,8 @@
 // (optionally) quantizes the context row per 32 for the O projection.
 // attn_generic_kernel: any head_dim up to 64 and any group size, one warp per (row, head); used for tiny test
 // models and as the independent implementation the parity tests cross-check the fast kernel with.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -168,13 +170,202 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
     }
 }
 
+
+// ---- tensor-core flash-decode (fast class) ----
+// One CTA per (key split, kv head, row), 4 warps; each warp walks 16-key tiles of its own (a KV block, or a 16-row slab
+// of one, is contiguous per kv head: 16*HD fp16) through a private 3-stage cp.async ring in shared memory, 16-byte
+// chunks XOR-swizzled by the key row so ldmatrix reads are conflict-free. Scores S[head][key] = Q K^T run as
+// mma.sync m16n8k16 with the group's query heads in the 16-row operand (f32 q split into f16 hi + lo parts, so the
+// product keeps fp32-level accuracy over the fp16 keys); the context is accumulated transposed, O^T[dim][head] = V^T P^T,
+// so that the score fragment of a lane is already the B fragment of the second product and the 8-column operand holds
+// the (up to 8) heads of the group. Online softmax in fp32 registers; P is also split hi + lo. G <= 8.
+__device__ __forceinline__ void ldsm_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_f16f32(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp16(unsigned smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_dst), "l"(gsrc));
+}
+// f32 pair -> f16 hi pair and f16 lo pair (x = hi + lo up to 2^-22 relative)
+__device__ __forceinline__ void split_hi_lo(float x, float y, unsigned& hi, unsigned& lo) {
+    const __half2 h = __floats2half2_rn(x, y);
+    const float2 hf = __half22float2(h);
+    const __half2 l = __floats2half2_rn(x - hf.x, y - hf.y);
+    hi = *reinterpret_cast<const unsigned*>(&h);
+    lo = *reinterpret_cast<const unsigned*>(&l);
+}
+
+constexpr int kMmaStages = 3;
+
+template <int HD, int G>
+__global__ void __launch_bounds__(128) attn_mma_kernel(const float* __restrict__ q, int ldq, int nH, int nKV, float scale, float cap,
+                                                       const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
+                                                       const __half* __restrict__ kpool, const __half* __restrict__ vpool,
+                                                       const int32_t* __restrict__ table, int max_blocks, int block_rows,
+                                                       float* __restrict__ partial, int max_splits, int split_keys) {
+    constexpr int KS = HD / 16, CPR = HD / 8, ROWB = HD * 2, TILE = 16 * ROWB, CPL = 16 * CPR / 32;
+    extern __shared__ __align__(128) uint8_t attn_smem[];
+    const int r = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
+    const int nkeys = row_pos[r] + 1;
+    const int k0 = split * split_keys;
+    if (k0 >= nkeys) return;
+    const int k1 = min(nkeys, k0 + split_keys);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tig = lane & 3;
+    const int32_t* tbl = table + (size_t)row_slot[r] * max_blocks;
+    uint8_t* wsm = attn_smem + (size_t)warp * kMmaStages * 2 * TILE;
+    const unsigned wsm_s = (unsigned)__cvta_generic_to_shared(wsm);
+
+    // Q fragments: row gid = head gid of the group (zero rows beyond the group), dims 16ks+2tig(+1) and 16ks+8+2tig(+1)
+    unsigned qh0[KS], qh2[KS], ql0[KS], ql2[KS];
+    {
+        const float* qp = q + (size_t)r * ldq + (size_t)(kvh * G + (gid < G ? gid : 0)) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            float2 a = *reinterpret_cast<const float2*>(qp + 16 * ks + 2 * tig);
+            float2 b = *reinterpret_cast<const float2*>(qp + 16 * ks + 8 + 2 * tig);
+            if (gid >= G) { a.x = a.y = b.x = b.y = 0.f; }
+            split_hi_lo(a.x, a.y, qh0[ks], ql0[ks]);
+            split_hi_lo(b.x, b.y, qh2[ks], ql2[ks]);
+        }
+    }
+    float o[KS][4];
+#pragma unroll
+    for (int mt = 0; mt < KS; mt++) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+
+    const int c_first = k0 / 16 + warp, c_end = (k1 + 15) / 16;   // this warp's tiles: c_first, c_first+4, ...
+    const int n_tiles = c_first < c_end ? (c_end - c_first + 3) / 4 : 0;
+    auto issue = [&](int it) {
+        if (it < n_tiles) {
+            const int key0 = (c_first + 4 * it) * 16;
+            const int blk = tbl[key0 / block_rows];
+            const size_t off = (((size_t)blk * nKV + kvh) * block_rows + (key0 % block_rows)) * HD;
+            const uint8_t* ksrc = reinterpret_cast<const uint8_t*>(kpool + off);
+            const uint8_t* vsrc = reinterpret_cast<const uint8_t*>(vpool + off);
+            const unsigned dst = wsm_s + (unsigned)((it % kMmaStages) * 2 * TILE);
+#pragma unroll
+            for (int i = 0; i < CPL; i++) {
+                const int ci = lane + 32 * i, row = ci / CPR, c = ci % CPR;
+                const unsigned d = (unsigned)(row * ROWB + ((c ^ (row & 7)) << 4));
+                cp16(dst + d, ksrc + ci * 16);
+                cp16(dst + TILE + d, vsrc + ci * 16);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+#pragma unroll
+    for (int s = 0; s < kMmaStages - 1; s++) issue(s);
+
+    // per-lane ldmatrix geometry (same for K and V tiles)
+    const int lrow = (lane & 7) + ((lane >> 4) << 3), lsel = (lane >> 3) & 1;
+    for (int it = 0; it < n_tiles; it++) {
+        issue(it + kMmaStages - 1);
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(kMmaStages - 1));
+        __syncwarp();
+        const unsigned kb = wsm_s + (unsigned)((it % kMmaStages) * 2 * TILE), vb = kb + TILE;
+        const int key0 = (c_first + 4 * it) * 16;
+        // S0 = keys 0-7 of the tile, S1 = keys 8-15; hi and lo parts accumulate apart to shorten the dependency chains
+        float s0h[4] = {0, 0, 0, 0}, s0l[4] = {0, 0, 0, 0}, s1h[4] = {0, 0, 0, 0}, s1l[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            unsigned b0, b1, b2, b3;
+            ldsm_x4(kb + (unsigned)(lrow * ROWB + (((2 * ks + lsel) ^ (lrow & 7)) << 4)), b0, b1, b2, b3);
+            mma_f16f32(s0h, qh0[ks], 0u, qh2[ks], 0u, b0, b1);
+            mma_f16f32(s1h, qh0[ks], 0u, qh2[ks], 0u, b2, b3);
+            mma_f16f32(s0l, ql0[ks], 0u, ql2[ks], 0u, b0, b1);
+            mma_f16f32(s1l, ql0[ks], 0u, ql2[ks], 0u, b2, b3);
+        }
+        float sv[4];
+        sv[0] = s0h[0] + s0l[0]; sv[1] = s0h[1] + s0l[1]; sv[2] = s1h[0] + s1l[0]; sv[3] = s1h[1] + s1l[1];
+        const int kk[4] = {key0 + 2 * tig, key0 + 2 * tig + 1, key0 + 8 + 2 * tig, key0 + 9 + 2 * tig};
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            sv[i] = kk[i] < k1 ? score_of(sv[i], scale, cap) : -INFINITY;
+            mx = fmaxf(mx, sv[i]);
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float alpha = __expf(m_run - m_new);
+        float pv[4], ps = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            pv[i] = __expf(sv[i] - m_new);   // exp(-inf) = 0 for masked keys
+            ps += pv[i];
+        }
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        l_run = l_run * alpha + ps;
+        m_run = m_new;
+        unsigned ph0, pl0, ph1, pl1;
+        split_hi_lo(pv[0], pv[1], ph0, pl0);
+        split_hi_lo(pv[2], pv[3], ph1, pl1);
+        // rescale the context columns of heads 2*tig and 2*tig+1
+        const float a0 = __shfl_sync(0xffffffffu, alpha, (2 * tig) * 4), a1 = __shfl_sync(0xffffffffu, alpha, (2 * tig + 1) * 4);
+#pragma unroll
+        for (int mt = 0; mt < KS; mt++) {
+            o[mt][0] *= a0; o[mt][1] *= a1; o[mt][2] *= a0; o[mt][3] *= a1;
+            unsigned v0, v1, v2, v3;
+            ldsm_x4_t(vb + (unsigned)(lrow * ROWB + (((2 * mt + lsel) ^ (lrow & 7)) << 4)), v0, v1, v2, v3);
+            mma_f16f32(o[mt], v0, v1, v2, v3, ph0, ph1);
+            mma_f16f32(o[mt], v0, v1, v2, v3, pl0, pl1);
+        }
+        __syncwarp();
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    __syncthreads();
+    // merge the 4 warps (reusing the ring): sm_acc[warp][head][dim], sm_m/sm_l[warp][head]
+    float* sm_acc = reinterpret_cast<float*>(attn_smem);
+    float* sm_m = sm_acc + 4 * G * HD;
+    float* sm_l = sm_m + 4 * G;
+    if (tig == 0 && gid < G) {
+        sm_m[warp * G + gid] = m_run;
+        sm_l[warp * G + gid] = l_run;
+    }
+#pragma unroll
+    for (int mt = 0; mt < KS; mt++) {
+        const int h0 = 2 * tig, h1 = 2 * tig + 1, d0 = 16 * mt + gid;
+        if (h0 < G) { sm_acc[(warp * G + h0) * HD + d0] = o[mt][0]; sm_acc[(warp * G + h0) * HD + d0 + 8] = o[mt][2]; }
+        if (h1 < G) { sm_acc[(warp * G + h1) * HD + d0] = o[mt][1]; sm_acc[(warp * G + h1) * HD + d0 + 8] = o[mt][3]; }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * HD; idx += 128) {
+        const int g = idx / HD, e = idx % HD;
+        float M = sm_m[g];  // warp 0 always holds a tile
+#pragma unroll
+        for (int w = 1; w < 4; w++) M = fmaxf(M, sm_m[w * G + g]);
+        float tot = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float f = __expf(sm_m[w * G + g] - M);
+            tot += sm_acc[(w * G + g) * HD + e] * f;
+            l += sm_l[w * G + g] * f;
+        }
+        float* out = partial + (((size_t)r * nH + kvh * G + g) * max_splits + split) * (HD + 2);
+        out[e] = tot;
+        if (e == 0) {
+            out[HD] = M;
+            out[HD + 1] = l;
+        }
+    }
+}
+
 // grid (nH, T), HD threads. Merges a row's splits in split order; optional per-32 quantization.
 template <int HD>
-__global__ void attn_combine_kernel(const float* __restrict__ partial, int nH, int max_splits,
+__global__ void attn_combine_kernel(const float* __restrict__ partial, int nH, int max_splits, int split_keys,
                                     const int32_t* __restrict__ row_pos, float* __restrict__ out, int8_t* __restrict__ codes,
                                     float* __restrict__ scales) {
     const int h = blockIdx.x, r = blockIdx.y, e = threadIdx.x;
-    const int nsp = (row_pos[r] + 1 + kSplitKeys - 1) / kSplitKeys;
+    const int nsp = (row_pos[r] + 1 + split_keys - 1) / split_keys;
     const float* p = partial + ((size_t)r * nH + h) * max_splits * (HD + 2);
     float M = -INFINITY;
     for (int s = 0; s < nsp; s++) M = fmaxf(M, p[(size_t)s * (HD + 2) + HD]);
@@ -336,7 +527,35 @@ int run_split(b200_ctx* ctx, const float* q, int ldq, int T, int nH, int nKV, fl
     LAUNCH_CHECK(ctx);
     {
         ProfScope ps(ctx, PROF_ATTN_COMBINE);
-        attn_combine_kernel<HD><<<dim3(nH, T), HD, 0, ctx->stream>>>(sc.partial, nH, sc.max_splits, row_pos, out, aq.codes, aq.scales);
+        attn_combine_kernel<HD><<<dim3(nH, T), HD, 0, ctx->stream>>>(sc.partial, nH, sc.max_splits, kSplitKeys, row_pos, out, aq.codes, aq.scales);
+    }
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+constexpr int kMmaSplitKeys = 1024;
+
+template <int HD, int G>
+int run_mma(b200_ctx* ctx, const float* q, int ldq, int T, int nH, int nKV, float scale, float cap, const int32_t* row_slot,
+            const int32_t* row_pos, int max_keys, KVView kv, AttnScratch sc, float* out, ActQ aq) {
+    const int nsp = ceil_div(max_keys, kMmaSplitKeys);
+    if (nsp > sc.max_splits) B200_FAIL(ctx, B200_BAD_ARGUMENT, "attention scratch too small for %d keys", max_keys);
+    constexpr int smem = 4 * kMmaStages * 2 * 16 * HD * 2;
+    static bool attr_set = false;
+    if (!attr_set) {
+        CUDA_TRY(ctx, cudaFuncSetAttribute(attn_mma_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_set = true;
+    }
+    dim3 grid(nsp, nKV, T);
+    {
+        ProfScope ps(ctx, PROF_ATTN_SPLIT);
+        attn_mma_kernel<HD, G><<<grid, 128, smem, ctx->stream>>>(q, ldq, nH, nKV, scale, cap, row_slot, row_pos, kv.k, kv.v, kv.table,
+                                                                kv.max_blocks, kv.block_rows, sc.partial, sc.max_splits, kMmaSplitKeys);
+    }
+    LAUNCH_CHECK(ctx);
+    {
+        ProfScope ps(ctx, PROF_ATTN_COMBINE);
+        attn_combine_kernel<HD><<<dim3(nH, T), HD, 0, ctx->stream>>>(sc.partial, nH, sc.max_splits, kMmaSplitKeys, row_pos, out, aq.codes, aq.scales);
     }
     LAUNCH_CHECK(ctx);
     return B200_OK;
@@ -368,6 +587,15 @@ int launch_paged_attention(b200_ctx* ctx, const float* q, int ldq, int T, int nH
                            const int32_t* row_slot, const int32_t* row_pos, int max_keys, KVView kv, AttnScratch sc, float* out,
                            ActQ aq) {
     const int G = nH / nKV;
+    // tensor-core kernel: 16-key tiles must be contiguous, i.e. the block size a multiple of 16
+    static const bool use_mma = !getenv("B200_ATTN_SIMT");
+    if (use_mma && kv.block_rows % 16 == 0) {
+#define MMA_CASE(HD_, G_) \
+    if (hd == HD_ && G == G_) return run_mma<HD_, G_>(ctx, q, ldq, T, nH, nKV, scale, softcap, row_slot, row_pos, max_keys, kv, sc, out, aq)
+        MMA_CASE(128, 1); MMA_CASE(128, 2); MMA_CASE(128, 4); MMA_CASE(128, 8);
+        MMA_CASE(64, 1); MMA_CASE(64, 2); MMA_CASE(64, 4); MMA_CASE(64, 8);
+#undef MMA_CASE
+    }
 #define SPLIT_CASE(HD_, G_) \
     if (hd == HD_ && G == G_) return run_split<HD_, G_>(ctx, q, ldq, T, nH, nKV, scale, softcap, row_slot, row_pos, max_keys, kv, sc, out, aq)
     SPLIT_CASE(128, 1); SPLIT_CASE(128, 2); SPLIT_CASE(128, 4); SPLIT_CASE(128, 8);

@@ -522,10 +522,11 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
     for (int l = 0; l < c.n_layers; l++) {
         ST_TRY(m->dalloc((void**)&m->kpool[l], per_layer, &m->kv_bytes));
         ST_TRY(m->dalloc((void**)&m->vpool[l], per_layer, &m->kv_bytes));
-        // block 0 is the all-zero null block (backend/cuda/kvpool.go:16-27)
-        const size_t blk_bytes = (size_t)nKV * c.kv_block_rows * hd * sizeof(__half);
-        CUDA_TRY(ctx, cudaMemsetAsync(m->kpool[l], 0, blk_bytes, ctx->stream));
-        CUDA_TRY(ctx, cudaMemsetAsync(m->vpool[l], 0, blk_bytes, ctx->stream));
+        // Block 0 is the all-zero null block (backend/cuda/kvpool.go:16-27). The whole pool starts zeroed: the attention
+        // kernels load whole 16-key tiles and weight the rows past a sequence's end by zero, so every row must hold
+        // finite values from the start (a reused block holds a previous sequence's finite rows).
+        CUDA_TRY(ctx, cudaMemsetAsync(m->kpool[l], 0, per_layer, ctx->stream));
+        CUDA_TRY(ctx, cudaMemsetAsync(m->vpool[l], 0, per_layer, ctx->stream));
     }
     ST_TRY(m->dalloc((void**)&m->table, (size_t)c.n_slots * m->max_blocks * 4, &m->kv_bytes));
     ST_TRY(m->dalloc((void**)&m->free_stack, (size_t)c.kv_pool_blocks * 4, &m->kv_bytes));

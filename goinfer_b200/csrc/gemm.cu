@@ -45,6 +45,15 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], unsigned a0, unsigned a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// d = a*b + c with c a separate (constant) operand: the magic-number bias costs no moves
+__device__ __forceinline__ void mma_u8s8_c(int (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1,
+                                           int c) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
+}
+
 // grid.x: 16-row weight tiles (8 per CTA without SPLITK, 1 per CTA with it); grid.y: token tiles of 8*NT;
 // grid.z: experts when GROUPED.
 template <int NT, bool SPLITK, bool GROUPED>
@@ -194,6 +203,199 @@ __global__ void __launch_bounds__(256) q4k_gemm_mma_kernel(const uint8_t* __rest
             if (nb < N) dst[(size_t)t1 * ldd + nb] = acc[j][3];
         }
     }
+}
+
+
+// ---- tiled exact-class kernel for more than 8 rows ----
+// CTA = 8 warps x 16 weight rows against BT = 8*NT tokens. Per super-block the tokens' 256 activation codes and their
+// 8 scales / 8 group sums are staged in shared memory by cp.async (two stages), each token's codes padded to 288 bytes
+// so the 8-byte fragment loads of a half-warp fall in distinct banks. Weights stream from global memory straight into
+// registers, one super-block ahead. Arithmetic and its order are q4k_gemm_mma_kernel's: one ascending chain per output.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gsrc));
+}
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gsrc) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(d), "l"(gsrc));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N_>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N_)); }
+
+struct WRegs {
+    uint4 h0, h1;
+    uint2 q0[4], q1[4];
+};
+
+__device__ __forceinline__ void load_wregs(WRegs& w, const uint8_t* w0, const uint8_t* w1, int b, int tig) {
+    w.h0 = *reinterpret_cast<const uint4*>(w0 + (size_t)b * 144);
+    w.h1 = *reinterpret_cast<const uint4*>(w1 + (size_t)b * 144);
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+        w.q0[p] = *reinterpret_cast<const uint2*>(w0 + (size_t)b * 144 + 16 + 32 * p + 8 * tig);
+        w.q1[p] = *reinterpret_cast<const uint2*>(w1 + (size_t)b * 144 + 16 + 32 * p + 8 * tig);
+    }
+}
+
+template <int NT, bool GROUPED>
+__global__ void __launch_bounds__(256, (NT <= 8 ? 2 : 1)) q4k_gemm_tile_kernel(
+    const uint8_t* __restrict__ W, const uint8_t* const* __restrict__ Wptrs, int N, int nSB, const int8_t* __restrict__ codes,
+    const float* __restrict__ scales, int T, const int32_t* __restrict__ offs, const int32_t* __restrict__ rows,
+    float* __restrict__ dst, int ldd) {
+    constexpr int BT = 8 * NT, CS = 288, SS = 80, STAGE = BT * CS + BT * SS;  // SS: 64 bytes of scales padded so 4 tokens' float4 loads miss each other's banks
+    extern __shared__ __align__(16) uint8_t tile_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tig = lane & 3;
+    const int n0 = (blockIdx.x * 8 + warp) * 16;
+    int t_base, t_end;
+    const uint8_t* Wm = W;
+    if (GROUPED) {
+        const int e = blockIdx.z;
+        t_base = offs[e] + blockIdx.y * BT;
+        t_end = offs[e + 1];
+        if (t_base >= t_end) return;
+        Wm = Wptrs[e];
+    } else {
+        t_base = blockIdx.y * BT;
+        t_end = T;
+    }
+    const int K = nSB * 256, nG = nSB * 8;
+    const bool active = n0 < N;
+    const int r0 = min(n0 + gid, N - 1), r1 = min(n0 + gid + 8, N - 1);
+    const uint8_t* w0 = Wm + (size_t)r0 * nSB * 144;
+    const uint8_t* w1 = Wm + (size_t)r1 * nSB * 144;
+
+    auto load_stage = [&](int b, int st) {
+        uint8_t* sc = tile_smem + st * STAGE;
+        uint8_t* ss = sc + BT * CS;
+        for (int i = threadIdx.x; i < BT * 16; i += 256) {
+            const int tok = i >> 4, c = i & 15;
+            int t = min(t_base + tok, t_end - 1);
+            if (GROUPED && rows) t = rows[t];
+            cp_async16(sc + tok * CS + c * 16, codes + (size_t)t * K + 256 * b + 16 * c);
+        }
+        for (int i = threadIdx.x; i < BT * 8; i += 256) {
+            const int tok = i >> 3, q = i & 7, p = q >> 1, half = q & 1;  // half 0: scales of groups 2p,2p+1; 1: their sums
+            int t = min(t_base + tok, t_end - 1);
+            if (GROUPED && rows) t = rows[t];
+            cp_async8(ss + tok * SS + p * 16 + half * 8, scales + (size_t)t * 2 * nG + (half ? nG : 0) + 8 * b + 2 * p);
+        }
+    };
+
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+    WRegs wc, wn;
+    load_stage(0, 0);
+    cp_async_commit();
+    if (active) load_wregs(wc, w0, w1, 0, tig);
+    for (int b = 0; b < nSB; b++) {
+        if (b + 1 < nSB) {
+            load_stage(b + 1, (b + 1) & 1);
+            cp_async_commit();
+            if (active) load_wregs(wn, w0, w1, b + 1, tig);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (active) {
+            const uint8_t* sc = tile_smem + (b & 1) * STAGE;
+            const uint8_t* ss = sc + BT * CS;
+            float my_ds[2][2], my_nm[2][2];
+            {
+                int s_, m_;
+                const float d0 = h2f_bits((unsigned short)(wc.h0.x & 0xffffu)), dm0 = h2f_bits((unsigned short)(wc.h0.x >> 16));
+                const float d1 = h2f_bits((unsigned short)(wc.h1.x & 0xffffu)), dm1 = h2f_bits((unsigned short)(wc.h1.x >> 16));
+                q4k_scale_min(2 * tig, wc.h0.y, wc.h0.z, wc.h0.w, &s_, &m_);
+                my_ds[0][0] = __fmul_rn(d0, (float)s_); my_nm[0][0] = -__fmul_rn(dm0, (float)m_);
+                q4k_scale_min(2 * tig + 1, wc.h0.y, wc.h0.z, wc.h0.w, &s_, &m_);
+                my_ds[0][1] = __fmul_rn(d0, (float)s_); my_nm[0][1] = -__fmul_rn(dm0, (float)m_);
+                q4k_scale_min(2 * tig, wc.h1.y, wc.h1.z, wc.h1.w, &s_, &m_);
+                my_ds[1][0] = __fmul_rn(d1, (float)s_); my_nm[1][0] = -__fmul_rn(dm1, (float)m_);
+                q4k_scale_min(2 * tig + 1, wc.h1.y, wc.h1.z, wc.h1.w, &s_, &m_);
+                my_ds[1][1] = __fmul_rn(d1, (float)s_); my_nm[1][1] = -__fmul_rn(dm1, (float)m_);
+            }
+#pragma unroll
+            for (int p = 0; p < 4; p++) {
+                const int src = (lane & ~3) | p;
+                const float ds0lo = __shfl_sync(0xffffffffu, my_ds[0][0], src), ds0hi = __shfl_sync(0xffffffffu, my_ds[0][1], src);
+                const float ds1lo = __shfl_sync(0xffffffffu, my_ds[1][0], src), ds1hi = __shfl_sync(0xffffffffu, my_ds[1][1], src);
+                const float nm0lo = __shfl_sync(0xffffffffu, my_nm[0][0], src), nm0hi = __shfl_sync(0xffffffffu, my_nm[0][1], src);
+                const float nm1lo = __shfl_sync(0xffffffffu, my_nm[1][0], src), nm1hi = __shfl_sync(0xffffffffu, my_nm[1][1], src);
+                const uint2 q0 = wc.q0[p], q1 = wc.q1[p];
+                const unsigned al0 = q0.x & 0x0F0F0F0Fu, al1 = q1.x & 0x0F0F0F0Fu, al2 = q0.y & 0x0F0F0F0Fu, al3 = q1.y & 0x0F0F0F0Fu;
+                const unsigned ah0 = (q0.x >> 4) & 0x0F0F0F0Fu, ah1 = (q1.x >> 4) & 0x0F0F0F0Fu, ah2 = (q0.y >> 4) & 0x0F0F0F0Fu,
+                               ah3 = (q1.y >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+                for (int j = 0; j < NT; j++) {
+                    const uint8_t* tb = sc + (8 * j + gid) * CS + 64 * p + 8 * tig;
+                    const int2 blo = *reinterpret_cast<const int2*>(tb);
+                    const int2 bhi = *reinterpret_cast<const int2*>(tb + 32);
+                    int cl[4], ch[4];
+                    mma_u8s8_c(cl, al0, al1, al2, al3, (unsigned)blo.x, (unsigned)blo.y, MAGIC_I);
+                    mma_u8s8_c(ch, ah0, ah1, ah2, ah3, (unsigned)bhi.x, (unsigned)bhi.y, MAGIC_I);
+                    // {aS[g], aS[g+1], asum[g], asum[g+1]} of tokens 2*tig and 2*tig+1 of this tile
+                    const float4 s0 = *reinterpret_cast<const float4*>(ss + (8 * j + 2 * tig) * SS + p * 16);
+                    const float4 s1 = *reinterpret_cast<const float4*>(ss + (8 * j + 2 * tig + 1) * SS + p * 16);
+                    float f;
+                    f = acc[j][0];
+                    f = __fmaf_rn(__fsub_rn(__int_as_float(cl[0]), MAGIC_F), __fmul_rn(ds0lo, s0.x), f);
+                    f = __fmaf_rn(__fsub_rn(__int_as_float(ch[0]), MAGIC_F), __fmul_rn(ds0hi, s0.y), f);
+                    f = __fmaf_rn(nm0lo, s0.z, f);
+                    acc[j][0] = __fmaf_rn(nm0hi, s0.w, f);
+                    f = acc[j][1];
+                    f = __fmaf_rn(__fsub_rn(__int_as_float(cl[1]), MAGIC_F), __fmul_rn(ds0lo, s1.x), f);
+                    f = __fmaf_rn(__fsub_rn(__int_as_float(ch[1]), MAGIC_F), __fmul_rn(ds0hi, s1.y), f);
+                    f = __fmaf_rn(nm0lo, s1.z, f);
+                    acc[j][1] = __fmaf_rn(nm0hi, s1.w, f);
+                    f = acc[j][2];
+                    f = __fmaf_rn(__fsub_rn(__int_as_float(cl[2]), MAGIC_F), __fmul_rn(ds1lo, s0.x), f);
+                    f = __fmaf_rn(__fsub_rn(__int_as_float(ch[2]), MAGIC_F), __fmul_rn(ds1hi, s0.y), f);
+                    f = __fmaf_rn(nm1lo, s0.z, f);
+                    acc[j][2] = __fmaf_rn(nm1hi, s0.w, f);
+                    f = acc[j][3];
+                    f = __fmaf_rn(__fsub_rn(__int_as_float(cl[3]), MAGIC_F), __fmul_rn(ds1lo, s1.x), f);
+                    f = __fmaf_rn(__fsub_rn(__int_as_float(ch[3]), MAGIC_F), __fmul_rn(ds1hi, s1.y), f);
+                    f = __fmaf_rn(nm1lo, s1.z, f);
+                    acc[j][3] = __fmaf_rn(nm1hi, s1.w, f);
+                }
+            }
+            wc = wn;
+        }
+        __syncthreads();
+    }
+    if (!active) return;
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        const int t0 = t_base + 8 * j + 2 * tig, t1 = t0 + 1;
+        const int na = n0 + gid, nb = n0 + gid + 8;
+        if (t0 < t_end) {
+            if (na < N) dst[(size_t)t0 * ldd + na] = acc[j][0];
+            if (nb < N) dst[(size_t)t0 * ldd + nb] = acc[j][2];
+        }
+        if (t1 < t_end) {
+            if (na < N) dst[(size_t)t1 * ldd + na] = acc[j][1];
+            if (nb < N) dst[(size_t)t1 * ldd + nb] = acc[j][3];
+        }
+    }
+}
+
+template <int NT>
+int run_q4k_tile(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, int T, float* dst, int ldd) {
+    constexpr int smem = 2 * (8 * NT) * (288 + 80);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(q4k_gemm_tile_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        attr_set = true;
+    }
+    dim3 grid(ceil_div(N, 128), ceil_div(T, 8 * NT));
+    ProfScope ps(ctx, PROF_Q4K_GEMM);
+    q4k_gemm_tile_kernel<NT, false><<<grid, 256, smem, ctx->stream>>>(W, nullptr, N, nSB, aq.codes, aq.scales, T, nullptr, nullptr,
+                                                                     dst, ldd);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
 }
 
 // ---- f16 weights ----
@@ -421,17 +623,18 @@ int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, in
     if (T <= 8) return klass == B200_CLASS_EXACT ? run_q4k<1, false>(ctx, W, N, nSB, aq, T, dst, ldd)
                                                   : run_q4k<1, true>(ctx, W, N, nSB, aq, T, dst, ldd);
     if (T <= 16) return run_q4k<2, false>(ctx, W, N, nSB, aq, T, dst, ldd);
-    if (T <= 32) return run_q4k<4, false>(ctx, W, N, nSB, aq, T, dst, ldd);
-    return run_q4k<8, false>(ctx, W, N, nSB, aq, T, dst, ldd);
+    if (T <= 32) return run_q4k_tile<4>(ctx, W, N, nSB, aq, T, dst, ldd);
+    return run_q4k_tile<8>(ctx, W, N, nSB, aq, T, dst, ldd);
 }
 
 int launch_q4k_matmul_grouped(b200_ctx* ctx, const uint8_t* const* Wptrs, int n_experts, int N, int K, ActQ aq,
                               const int32_t* offs, const int32_t* rows, int max_rows_per_expert, float* dst, int ldd) {
     if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
-    dim3 grid(ceil_div(N, 128), ceil_div(max_rows_per_expert, 16), n_experts);
+    constexpr int NT = 2, smem = 2 * (8 * NT) * (288 + 80);
+    dim3 grid(ceil_div(N, 128), ceil_div(max_rows_per_expert, 8 * NT), n_experts);
     ProfScope ps(ctx, PROF_Q4K_GEMM);
-    q4k_gemm_mma_kernel<2, false, true><<<grid, 256, 0, ctx->stream>>>(nullptr, Wptrs, N, K / 256, aq.codes, aq.scales, 0, offs,
-                                                                       rows, dst, ldd);
+    q4k_gemm_tile_kernel<NT, true><<<grid, 256, smem, ctx->stream>>>(nullptr, Wptrs, N, K / 256, aq.codes, aq.scales, 0, offs,
+                                                                     rows, dst, ldd);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }
