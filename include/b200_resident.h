@@ -253,6 +253,30 @@ int b200_bench_attention(b200_ctx* ctx, int rows, int ctx_lo, int ctx_hi, int n_
                          int head_dim, int block_rows, uint64_t seed, int warmup, int iters,
                          float* ms_out, double* kv_bytes_out);
 
+/* Paged decode attention that allocates nothing. No counterpart in the reference (its backends allocate their split
+ * buffers when a model is built); it exists for hosts that cannot allocate when they need attention: a serving process
+ * whose device memory was handed out once at start-up and is owned by its own pool, or a plug-in living under another
+ * program's "no device allocation after init" rule, where a cudaMalloc in the step would break the host's memory budget.
+ *
+ * All pointers are DEVICE pointers owned by the caller: q [rows][ldq] f32 (query heads of row r at q + r*ldq),
+ * row_slot/row_pos [rows] (the block-table row and the position, i.e. keys-1, of each query), k_pool/v_pool the fp16
+ * pools laid out [block][kv_head][row_in_block][head_dim], block_table [n_table_rows][max_blocks], out [rows][n_heads*head_dim]
+ * f32. scale 0 means 1/sqrt(head_dim). Work is queued on the context's stream; the caller synchronizes that stream
+ * before reading `out`.
+ *
+ * The split partials live in one fixed 16 MiB device array inside the library (every GPU that loads the library holds
+ * it until the process exits). Limits: head_dim 64 or 128, n_heads/n_kv_heads in {1,2,4,8}, block_rows a multiple of 16,
+ * and rows * n_heads * ceil(max_keys/512) * (head_dim+2) * 4 bytes <= 16 MiB (e.g. 32 heads of 128: 63 rows at 2048 keys,
+ * 15 rows at 8192 keys); anything larger returns B200_BAD_ARGUMENT with the sizes in b200_last_error.
+ * The first call on a device looks up the array's address (no allocation); make that first call before starting any
+ * stream capture. The array is shared by every call and keeps the previous call's bytes; nothing in it needs clearing,
+ * but two calls whose kernels overlap on the GPU (different streams or contexts of one device) race on it:
+ * serialize them. The entry point calls no cudaMalloc, cudaFree or other allocating routine. */
+int b200_attention_noalloc(b200_ctx* ctx, const float* q, int ldq, int rows, int n_heads, int n_kv_heads, int head_dim,
+                           float scale, float softcap, const int32_t* row_slot, const int32_t* row_pos, int max_keys,
+                           const void* k_pool, const void* v_pool, const int32_t* block_table, int max_blocks,
+                           int block_rows, float* out);
+
 #ifdef __cplusplus
 }
 #endif
