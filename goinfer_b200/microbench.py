@@ -1,0 +1,50 @@
+"""Device-resident micro-benchmarks of the two kernels that carry the step, on synthetic data.
+
+  python -m goinfer_b200.microbench attention --rows 256 [--ctx-lo 128 --ctx-hi 8192 --heads 32 --kv-heads 8 --head-dim 128]
+  python -m goinfer_b200.microbench q4k --rows 1 2 4 8 16 32 256 [--n 12288 --k 4096]
+
+Times are CUDA-event averages per launch after warm-up. Weight matrices are cycled through several copies and KV pools
+are far larger than the 126 MB L2, so no launch finds its inputs cached.
+"""
+import argparse
+import json
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="what", required=True)
+    a = sub.add_parser("attention")
+    a.add_argument("--rows", type=int, default=256)
+    a.add_argument("--ctx-lo", type=int, default=128)
+    a.add_argument("--ctx-hi", type=int, default=8192)
+    a.add_argument("--heads", type=int, default=32)
+    a.add_argument("--kv-heads", type=int, default=8)
+    a.add_argument("--head-dim", type=int, default=128)
+    a.add_argument("--block-rows", type=int, default=16)
+    a.add_argument("--iters", type=int, default=10)
+    a.add_argument("--warmup", type=int, default=3)
+    g = sub.add_parser("q4k")
+    g.add_argument("--rows", type=int, nargs="+", default=[1, 2, 4, 8, 16, 32, 256])
+    g.add_argument("--n", type=int, default=12288)
+    g.add_argument("--k", type=int, default=4096)
+    g.add_argument("--klass", type=int, default=0)
+    g.add_argument("--iters", type=int, default=20)
+    g.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    from .ops import Ops
+    ops = Ops(0)
+    if args.what == "attention":
+        ms, kvb = ops.bench_attention(args.rows, args.ctx_lo, args.ctx_hi, args.heads, args.kv_heads, args.head_dim,
+                                      args.block_rows, 2, args.warmup, args.iters)
+        print(json.dumps({"kernel": "paged attention (split + combine)", "rows": args.rows, "ms_per_launch": ms,
+                          "kv_bytes": kvb, "GBps": kvb / ms / 1e6}))
+    else:
+        for m in args.rows:
+            ms = ops.bench_q4k_matmul(m, args.k, args.n, args.klass, 8, args.warmup, args.iters)
+            wb = args.n * args.k * 144 / 256
+            print(json.dumps({"kernel": "q4k matmul", "rows": m, "n": args.n, "k": args.k, "ms_per_launch": ms,
+                              "weight_GBps": wb / ms / 1e6, "TMACps": m * args.n * args.k / ms / 1e9}))
+
+
+if __name__ == "__main__":
+    main()
