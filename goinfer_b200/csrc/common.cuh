@@ -25,6 +25,11 @@ struct b200_ctx {
     std::string err;
     int64_t launches = 0;  // kernels this library launched on the context
     int sm_count = 148;
+    // scratch of the tcgen05 matmul (fp16 activations + split-K partials) and the device flag a bounded wait raises;
+    // owned by whoever set them (a model at finalize, or an operator-level entry point for the length of its call)
+    void* umma_scratch = nullptr;
+    size_t umma_scratch_bytes = 0;
+    int* err_flag = nullptr;
     // per-launch CUDA-event timing of the tagged kernel classes (off unless b200_profile sets a mask)
     unsigned prof_mask = 0;
     std::vector<ProfRec> prof_recs;
@@ -127,6 +132,10 @@ int launch_q4k_matmul(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T,
 // rows[a] and writes dst row a. Wptrs[e] is expert e's matrix.
 int launch_q4k_matmul_grouped(b200_ctx*, const uint8_t* const* Wptrs, int n_experts, int N, int K, ActQ aq,
                               const int32_t* offs, const int32_t* rows, int max_rows_per_expert, float* dst, int ldd);
+// gemm_umma.cu: fast-class tcgen05 matmul; scratch from q4k_umma_scratch_bytes
+size_t q4k_umma_scratch_bytes(int max_rows, int max_k, int max_n);
+int launch_q4k_matmul_umma(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
+                           size_t scratch_bytes, int* err_flag);
 int launch_f16w_matmul(b200_ctx*, const __half* W, int N, int K, const float* x, int T, float* dst, int ldd,
                        __half* split_scratch /* 2*T*K halves */);
 int launch_f32w_matmul(b200_ctx*, const float* W, int N, int K, const float* x, int T, float* dst, int ldd);

@@ -183,6 +183,9 @@ struct b200_model {
     ActQ aq_h, aq_ctx, aq_mid;
     __half* split = nullptr;
     AttnScratch asc;
+    void* umma_scratch = nullptr;  // fast class: tcgen05 matmul scratch
+    size_t umma_bytes = 0;
+    int* err_flag = nullptr;       // raised by a bounded device-side wait that gave up
     float* exact_scores = nullptr;  // exact class: [MR*nH][ctx_cap]
     // MoE
     float *rl = nullptr, *rw = nullptr, *egu_out = nullptr, *eo = nullptr, *emid = nullptr;
@@ -318,6 +321,9 @@ int run_layers(b200_model* m, int T, int max_keys) {
     const int H = c.hidden, nH = c.n_heads, nKV = c.n_kv_heads, hd = c.head_dim, qd = nH * hd, ldq = (nH + 2 * nKV) * hd;
     const float scale = c.attn_scale != 0.f ? c.attn_scale : (float)(1.0 / std::sqrt((double)hd));
     const ActQ none{};
+    ctx->umma_scratch = m->umma_scratch;  // this model's tcgen05 scratch and error flag serve its launches
+    ctx->umma_scratch_bytes = m->umma_bytes;
+    ctx->err_flag = m->err_flag;
     const float* delta = nullptr;  // pending residual add, fused into the next norm
     for (int l = 0; l < c.n_layers; l++) {
         LayerW& L = m->layers[l];
@@ -586,11 +592,20 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
         m->asc.max_splits = ceil_div(c.ctx_cap, attn_split_keys());
         ST_TRY(m->dalloc((void**)&m->asc.partial, attn_scratch_floats(MR, nH, hd, m->asc.max_splits) * 4, sb));
     }
+    if (c.kernel_class != B200_CLASS_EXACT && MR >= 64) {
+        // fast class: scratch of the tcgen05 matmul (fp16 activations + split-K partials), sized for the widest projection
+        int max_k = std::max(H, qd), max_n = std::max(ldq, H);
+        if (F) { max_k = std::max(max_k, F); max_n = std::max(max_n, 2 * F); }
+        m->umma_bytes = q4k_umma_scratch_bytes(MR, max_k, max_n);
+        ST_TRY(m->dalloc(&m->umma_scratch, m->umma_bytes, sb));
+    }
+    ST_TRY(m->dalloc((void**)&m->err_flag, 4, nullptr));
+    CUDA_TRY(ctx, cudaMemsetAsync(m->err_flag, 0, 4, ctx->stream));
     ST_TRY(m->dalloc((void**)&m->hn, (size_t)MLR * H * 4, sb));
     ST_TRY(m->dalloc((void**)&m->logits, (size_t)MLR * c.vocab * 4, sb));
     ST_TRY(m->dalloc((void**)&m->split, (size_t)2 * MLR * H * 2, sb));
     CUDA_TRY(ctx, cudaMallocHost((void**)&m->p_desc, (size_t)(2 + 3 * MR) * 4 + (size_t)MR * (4 + 4 + 4 + sizeof(b200_draw))));
-    CUDA_TRY(ctx, cudaMallocHost((void**)&m->p_ids, (size_t)MR * 4));
+    CUDA_TRY(ctx, cudaMallocHost((void**)&m->p_ids, (size_t)(MR + 1) * 4));
     CUDA_TRY(ctx, cudaEventCreate(&m->ev0));
     CUDA_TRY(ctx, cudaEventCreate(&m->ev1));
     m->finalized = true;
@@ -873,8 +888,13 @@ int b200_step_ragged(b200_model* m, int n_seqs, const int32_t* slot, const int32
         if (j0 + rn > n_out) ST_TRY(launch_draw(ctx, m->logits, rn, V, m->d_draws + j0, m->d_ids + j0, nullptr));
     }
     if (R > n_out) CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids, m->d_ids, (size_t)R * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids + m->MR, m->err_flag, 4, cudaMemcpyDeviceToHost, ctx->stream));
     CUDA_TRY(ctx, cudaEventRecord(m->ev1, ctx->stream));
     CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (m->p_ids[m->MR]) {
+        cudaMemsetAsync(m->err_flag, 0, 4, ctx->stream);
+        B200_FAIL(ctx, B200_TIMEOUT, "a bounded device-side wait gave up during the step");
+    }
     if (n_out && logits_out) memcpy(logits_out, m->p_logits, (size_t)n_out * V * 4);
     if (ids_out) {
         for (int i = 0; i < n_seqs; i++) ids_out[i] = -1;
@@ -963,7 +983,12 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
         if (ids_out) CUDA_TRY(ctx, cudaMemcpyAsync(log.data() + (size_t)st * S, m->d_ids_log, (size_t)S * 4, cudaMemcpyDeviceToHost, ctx->stream));
     }
     CUDA_TRY(ctx, cudaEventRecord(m->ev1, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids + m->MR, m->err_flag, 4, cudaMemcpyDeviceToHost, ctx->stream));
     CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (m->p_ids[m->MR]) {
+        cudaMemsetAsync(m->err_flag, 0, 4, ctx->stream);
+        B200_FAIL(ctx, B200_TIMEOUT, "a bounded device-side wait gave up during the decode loop");
+    }
     float ms = 0;
     cudaEventElapsedTime(&ms, m->ev0, m->ev1);
     if (ms_out) *ms_out = ms;

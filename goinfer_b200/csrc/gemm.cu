@@ -737,6 +737,10 @@ int run_q4k(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, int T, flo
 int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, int klass) {
     if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
     const int nSB = K / 256;
+    // Fast class from 64 rows (or when asked for by klass 2): tcgen05 fp16 matmul, if its scratch is in place.
+    if (klass != B200_CLASS_EXACT && (T >= 64 || klass == 2) && ctx->umma_scratch && !getenv("B200_NO_UMMA") &&
+        q4k_umma_scratch_bytes(T, K, N) <= ctx->umma_scratch_bytes)
+        return launch_q4k_matmul_umma(ctx, W, N, K, aq, T, dst, ldd, ctx->umma_scratch, ctx->umma_scratch_bytes, ctx->err_flag);
     // Rows up to 8 are HBM-bound: split K over the CTA's warps (unless the exact class asks for the one ascending
     // chain per output that every larger batch uses, so a row's bits do not depend on its batch).
     if (T <= 8 && klass == B200_CLASS_EXACT) return run_q4k<1, false>(ctx, W, N, nSB, aq, T, dst, ldd);

@@ -1,0 +1,498 @@
+// gemm_umma.cu — fast-class Q4_K matmul for dense token counts: tcgen05 tensor cores with TMEM accumulators.
+//
+//   dst[t][n] = sum_k X[t][k] * W[n][k],   W Q4_K [N][K],  X = code * scale of the per-32 int8 activations
+//
+// Both operands are brought to fp16 in shared memory and multiplied by tcgen05.mma (kind::f16, fp32 accumulate in
+// tensor memory). This is the non-bit-exact class the reference also has for large row counts (its int4 mma.sync GEMM,
+// backend/cuda/gemm_w4a8_mma.cu:21-27, reported through Caps.HasFastPrefill): the integer group dots of the exact class
+// are replaced by fp16 products of the dequantized values, each within 2^-11 of the exact operand.
+//
+// One CTA owns a [256 tokens] x [128*NT weight rows] output tile: per token tile an accumulator of 128*NT fp32 columns x
+// 128 lanes (NT = 2: all of the SM's tensor memory). What bounds this GEMM is the L2 -> SM traffic of the activation operand
+// (every CTA streams the whole [T][K] matrix), so the tile is as wide in weight rows as TMEM allows. K is walked in
+// chunks of 64 (one sub-block pair of a super-block):
+//   A ring (4 stages): 2 x [128 tokens][64] fp16, cp.async from the fp16 activation matrix two chunks ahead, whole rows
+//            per warp (coalesced), 128-byte swizzled K-major
+//   B ring (2 stages): 2 x [128 weight rows][64] fp16, dequantized by the CTA's threads (one 32-weight sub-block each)
+//            from raw Q4_K bytes loaded into registers two chunks ahead
+// Eight producer warps fill the rings and arrive on a `full` mbarrier per chunk; a ninth warp's elected thread
+// waits for it, issues the chunk's 16 tcgen05.mma (K=16 each) and a tcgen05.commit that arrives on the `empty` mbarrier
+// the producers wait on before they reuse a stage (a single issuing thread is paced by the tensor core, ~100 cycles per
+// MMA, so it must not be a thread the producers wait for). Nothing in the loop is a block-wide barrier. The epilogue reads
+// the accumulators with tcgen05.ld (each warp its 32 TMEM lanes = 32 tokens) and writes fp32 rows. With split-K
+// (gridDim.z > 1) each split writes its own partial matrix and a second kernel adds the splits in order.
+//
+// Every mbarrier wait is bounded: on expiry the CTA raises an error flag, frees its TMEM and returns.
+#include <cuda.h>  // the CUtensorMap type and enums only: the encoder is looked up through the runtime, nothing links to the driver library
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int kStages = 3;   // A ring (and barriers); the B ring has 2 stages
+constexpr int kTileBytes = 128 * 128;  // 128 rows x 64 fp16
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+// Bounded wait; false when the barrier did not complete the phase in time (or the CTA is aborting). try_wait suspends
+// the thread for a hardware-bounded time instead of spinning: 17 warps share 4 schedulers, and warps that spin on a
+// barrier take issue slots from the warps they are waiting for.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag = nullptr) {
+    for (int i = 0; i < (1 << 20); i++) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (abort_flag && *abort_flag) return false;
+    }
+    return false;
+}
+
+// K-major, 128-byte swizzle, 8-row groups 1024 bytes apart (cute/arch/mma_sm100_desc.hpp SmemDescriptor: start>>4 [0,14),
+// LBO>>4 [16,30), SBO>>4 [32,46), version 1 at [46,48), layout type SWIZZLE_128B = 2 at [61,64)).
+__device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// fp32 accumulate, f16 x f16, both K-major, M=128, N = 128 or 256 (InstrDescriptor: c_format [4,6), n>>3 [17,23), m>>4 [24,29)).
+__host__ __device__ constexpr unsigned idesc_for(unsigned n) { return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
+
+__device__ __forceinline__ void umma_f16(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ unsigned q4k_byte_u(int k, unsigned s0, unsigned s1, unsigned s2) {
+    unsigned w = k < 4 ? s0 : (k < 8 ? s1 : s2);
+    return (w >> ((k & 3) << 3)) & 0xffu;
+}
+__device__ __forceinline__ void q4k_scale_min_u(int j, unsigned s0, unsigned s1, unsigned s2, int* sc, int* m) {
+    if (j < 4) {
+        *sc = (int)(q4k_byte_u(j, s0, s1, s2) & 63u);
+        *m = (int)(q4k_byte_u(j + 4, s0, s1, s2) & 63u);
+    } else {
+        unsigned hi = q4k_byte_u(j + 4, s0, s1, s2);
+        *sc = (int)((hi & 0x0Fu) | ((q4k_byte_u(j - 4, s0, s1, s2) >> 6) << 4));
+        *m = (int)((hi >> 4) | ((q4k_byte_u(j, s0, s1, s2) >> 6) << 4));
+    }
+}
+
+// 8 weights of one 16-byte chunk (nibbles of words w0, w1) -> fp16, two at a time in half2 arithmetic. A nibble q is
+// placed at mantissa bits [6,10) of the half 16.0 (0x4C00), which makes the half 16 + q with no int->float conversion, and
+// w = (16 + q) * ds + c with c = -(16 ds + mn) is one half2 fma (c carries an extra rounding of about ds/128).
+// Nibbles come out paired (0,2),(1,3) per word, so the tile's K order inside every group of four is 0,2,1,3; the activation
+// matrix is written in the same order (a dot product does not care).
+template <bool HIGH>
+__device__ __forceinline__ uint4 dequant8(unsigned w0, unsigned w1, __half2 ds, __half2 c) {
+    auto cv = [&](unsigned w, int byte1) -> unsigned {
+        // nibble of bytes (0,2) or (1,3), low or high, moved to bits [6,10) and [22,26)
+        const int from = (byte1 ? 8 : 0) + (HIGH ? 4 : 0);
+        const unsigned sh = from <= 6 ? (w << (6 - from)) : (w >> (from - 6));
+        unsigned t = (sh & 0x03C003C0u) | 0x4C004C00u;
+        __half2 h = __hfma2(*reinterpret_cast<__half2*>(&t), ds, c);
+        return *reinterpret_cast<unsigned*>(&h);
+    };
+    uint4 o;
+    o.x = cv(w0, 0);
+    o.y = cv(w0, 1);
+    o.z = cv(w1, 0);
+    o.w = cv(w1, 1);
+    return o;
+}
+
+constexpr int kProducerWarps = 8;
+constexpr int kProducers = kProducerWarps * 32;
+constexpr int kUmmaThreads = kProducers + 96;  // 8 producer warps + the MMA-issuing, activation-loading and weight-loading warps
+constexpr int kRawRow = 144;                   // one Q4_K super-block
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// global -> shared bulk copy by the copy engine (no multicast); completion is counted in bytes on the mbarrier.
+// Both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// 2-D tiled copy by the copy engine (no multicast): box of the tensor map at (x, y) -> shared memory. x * element size
+// must be a multiple of 16 bytes.
+__device__ __forceinline__ void tensor_g2s_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+
+template <int NT>  // weight tiles of 128 rows per CTA: 2 when the grid still covers the SMs, else 1
+__global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __grid_constant__ CUtensorMap wmap, int N, int nSB,
+                                                                        const __half* __restrict__ X16, int T,
+                                                                        float* __restrict__ dst, int ldd, size_t split_stride,
+                                                                        int* __restrict__ err_flag) {
+    extern __shared__ __align__(1024) uint8_t umma_smem[];
+    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], raw_full, raw_empty;
+    __shared__ unsigned tmem_base_s;
+    __shared__ int abort_s;
+    constexpr int STAGE = 2 * kTileBytes;       // an A stage = two token tiles
+    constexpr int BSTAGE = NT * kTileBytes;     // a B stage = NT weight tiles, contiguous: one K-major tile of 128*NT rows
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * 128 * NT, t0 = blockIdx.y * 256;
+    // split-K ranges are whole super-blocks (4 chunks of 64)
+    const int splits = gridDim.z, sb0 = (int)((long long)nSB * blockIdx.z / splits),
+              sb1 = (int)((long long)nSB * (blockIdx.z + 1) / splits);
+    const int n_sb = sb1 - sb0, n_it = 4 * n_sb, K = nSB * 256;
+    // the swizzle atoms want 1024-byte aligned tiles; the launch reserves 1024 spare bytes for this round-up
+    uint8_t* smem = umma_smem + ((1024u - (smem_u32(umma_smem) & 1023u)) & 1023u);
+    uint8_t* bring = smem + (size_t)kStages * STAGE;  // 2 B stages of BSTAGE bytes
+    uint8_t* raw = bring + 2 * BSTAGE;                // the raw super-block (144 bytes) of each of the tile's 128*NT weight rows
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; s++) {
+            // per chunk: the loader's arrival that announces the A bytes + 8 warp arrivals after the B stores
+            mbar_init(smem_u32(&full_bar[s]), kProducerWarps + 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);  // one tcgen05.commit
+        }
+        mbar_init(smem_u32(&raw_full), 1);                 // the weight loader's announcement (+ the box's bytes)
+        mbar_init(smem_u32(&raw_empty), kProducerWarps);   // every producer warp has taken its rows out
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 0) {  // TMEM: per token tile one accumulator of 128*NT fp32 columns x 128 lanes (NT = 2: all 512 columns)
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(256 * NT));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = tmem_base_s;
+    volatile int* abort_v = &abort_s;
+
+    if (warp < kProducerWarps) {
+        // ---- producers ----
+        // B: NT = 2: thread = weight row tid, both sub-blocks of the chunk's pair. NT = 1: row tid & 127, sub-block
+        // tid >> 7 of the pair. Each thread keeps its row's current super-block (144 raw bytes) in registers; the weight
+        // loader fetches the tile's next super-blocks into `raw` meanwhile.
+        const int wr = NT == 2 ? tid : tid & 127, hf1 = (tid >> 7) & 1;
+        const unsigned b_off = (unsigned)wr * 128u, sw = (unsigned)(wr & 7);
+        uint4 hdr, q[8];  // the current super-block: d, dmin, 12 scale bytes; 128 code bytes
+        bool ok = true;
+
+        auto step = [&](int it, int p) -> bool {  // p = it & 3, a literal at every call site
+            // B stage it%2 was last read by the MMAs of chunk it-2
+            if (it > 1) {  // the verdict is made warp-uniform: the lanes meet in __syncwarp below
+                const bool w_ok = mbar_wait(smem_u32(&empty_bar[(it - 2) % kStages]), (unsigned)(((it - 2) / kStages) & 1), abort_v);
+                if (!__all_sync(0xffffffffu, w_ok)) return false;
+            }
+            if (p == 0) {  // take the row's next super-block out of `raw`, then hand `raw` back to the weight loader
+                const int sb = it >> 2;
+                const bool w_ok = mbar_wait(smem_u32(&raw_full), (unsigned)(sb & 1), abort_v);
+                if (!__all_sync(0xffffffffu, w_ok)) return false;
+                const uint4* rp = reinterpret_cast<const uint4*>(raw + (size_t)wr * kRawRow);
+                hdr = rp[0];
+#pragma unroll
+                for (int i = 0; i < 8; i++) q[i] = rp[1 + i];
+                // these reads are ordered before the copy engine's writes of the refill
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&raw_empty));
+            }
+            {   // dequantize the chunk's sub-blocks 2p (low nibbles of code bytes 32p..32p+31) and 2p+1 (high nibbles)
+                const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
+                const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+                uint8_t* rowp = bring + (size_t)(it & 1) * BSTAGE + b_off;
+                const uint4 qa = q[2 * p], qb = q[2 * p + 1];
+                const unsigned wq[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+                for (int hf = 0; hf < 2; hf++) {
+                    if (NT == 1 && hf != hf1) continue;
+                    int sc, mn;
+                    q4k_scale_min_u(2 * p + hf, hdr.y, hdr.z, hdr.w, &sc, &mn);
+                    const __half dsh = __float2half_rn(d * (float)sc);
+                    // the offset uses the rounded scale, so that the 16 * scale part cancels exactly
+                    const __half2 ds = __half2half2(dsh), c = __float2half2_rn(-(16.f * __half2float(dsh) + dmin * (float)mn));
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++) {
+                        const uint4 v = hf ? dequant8<true>(wq[2 * ch], wq[2 * ch + 1], ds, c) : dequant8<false>(wq[2 * ch], wq[2 * ch + 1], ds, c);
+                        *reinterpret_cast<uint4*>(rowp + (((unsigned)(4 * hf + ch) ^ sw) << 4)) = v;
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+            __syncwarp();  // every lane's stores are fenced: one arrival stands for the warp
+            if (lane == 0) mbar_arrive(smem_u32(&full_bar[it % kStages]));
+            return true;
+        };
+        for (int it = 0; it < n_it && ok; it += 4) {  // n_it is a multiple of 4
+            ok = step(it, 0);
+            if (ok) ok = step(it + 1, 1);
+            if (ok) ok = step(it + 2, 2);
+            if (ok) ok = step(it + 3, 3);
+        }
+        if (!ok) abort_s = 1;
+    } else if (warp == kProducerWarps && lane == 0) {
+        // ---- the MMA issuer: one thread; waits for a full stage, issues its 8 MMAs, commits to empty[it % 4] ----
+        for (int it = 0; it < n_it; it++) {
+            if (!mbar_wait(smem_u32(&full_bar[it % kStages]), (unsigned)((it / kStages) & 1), abort_v)) {
+                abort_s = 1;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const unsigned a0 = smem_u32(smem + (size_t)(it % kStages) * STAGE), b0 = smem_u32(bring + (size_t)(it & 1) * BSTAGE);
+            // one instruction spans all 128*NT weight rows (N = 128*NT): the token tile is fetched once for them
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++)
+                    umma_f16(tmem_base + mt * 128 * NT, umma_desc(a0 + mt * kTileBytes + ks * 32), umma_desc(b0 + ks * 32),
+                             idesc_for(128 * NT), (it > 0 || ks > 0) ? 1u : 0u);
+            umma_commit(smem_u32(&empty_bar[it % kStages]));
+        }
+        // all MMAs done: the last commit covers every earlier one. Only this thread waits for it; everyone else
+        // parks in the block barrier below.
+        if (n_it > 0 && !*abort_v) {
+            const int last = n_it - 1;
+            if (!mbar_wait(smem_u32(&empty_bar[last % kStages]), (unsigned)((last / kStages) & 1), abort_v)) abort_s = 1;
+        }
+    } else if (warp == kProducerWarps + 1 && lane == 0) {
+        // ---- the activation loader: one thread, one 32 KB bulk copy per chunk. The fp16 activation matrix is stored
+        // tile by tile ([token tile][chunk of K][256 rows][64]) in the swizzled order of the MMA tiles. ----
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(X16) + ((size_t)blockIdx.y * (size_t)(4 * nSB) + (size_t)(4 * sb0)) * STAGE;
+        int issued = 0;
+        for (int it = 0; it < n_it; it++) {
+            if (it >= kStages && !mbar_wait(smem_u32(&empty_bar[(it - kStages) % kStages]), (unsigned)(((it - kStages) / kStages) & 1), abort_v)) {
+                abort_s = 1;
+                break;
+            }
+            const unsigned bar = smem_u32(&full_bar[it % kStages]);
+            mbar_arrive_expect_tx(bar, STAGE);
+            bulk_g2s(smem_u32(smem + (size_t)(it % kStages) * STAGE), src + (size_t)it * STAGE, STAGE, bar);
+            issued = it + 1;
+        }
+        if (abort_s) {  // copies still in flight must land before the CTA may leave: bounded waits on their barriers
+            for (int it = max(0, issued - kStages); it < issued; it++) mbar_wait(smem_u32(&full_bar[it % kStages]), (unsigned)((it / kStages) & 1));
+        }
+    } else if (warp == kProducerWarps + 2 && lane == 0) {
+        // ---- the weight loader: one thread, one tiled copy per super-block: 144 raw bytes of each of the tile's rows
+        // (rows past N read as zeros, which dequantize to zero weights) ----
+        int issued = 0;
+        for (int sb = 0; sb < n_sb; sb++) {
+            if (sb > 0 && !mbar_wait(smem_u32(&raw_empty), (unsigned)((sb - 1) & 1), abort_v)) {
+                abort_s = 1;
+                break;
+            }
+            mbar_arrive_expect_tx(smem_u32(&raw_full), (unsigned)(128 * NT * kRawRow));
+            tensor_g2s_2d(smem_u32(raw), &wmap, (sb0 + sb) * kRawRow, n0, smem_u32(&raw_full));
+            issued = sb + 1;
+        }
+        // a copy still in flight must land before the CTA may leave: a bounded wait on its barrier
+        if (abort_s && issued > 0) mbar_wait(smem_u32(&raw_full), (unsigned)((issued - 1) & 1));
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    if (abort_s) {
+        if (tid == 0 && err_flag) atomicExch(err_flag, 1);
+    } else if (n_it > 0 && warp < kProducerWarps) {
+        // warp w reads TMEM lanes 32*(w%4).. of token tile mt = w/4, all 128*NT columns:
+        // tokens t0 + 128*mt + 32*(w%4) + lane, output columns n0 + column
+        float* out = dst + (size_t)blockIdx.z * split_stride;
+        const int mt = warp >> 2, lq = warp & 3;
+        const int tbase = t0 + mt * 128 + lq * 32;
+        uint8_t* tp = smem + warp * (32 * 144);
+#pragma unroll 1
+        for (int cb = 0; cb < 4 * NT; cb++) {
+            unsigned r[32];
+            const unsigned taddr = tmem_base + ((unsigned)(lq * 32) << 16) + (unsigned)(mt * 128 * NT + cb * 32);
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                  "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                  "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                  "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                : "r"(taddr));
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            // lane = token, registers = columns: turn the 32 x 32 block around in shared memory (the rings are idle now;
+            // rows 144 bytes apart keep both directions conflict-free) so that a store instruction writes whole rows
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                *reinterpret_cast<uint4*>(tp + lane * 144 + i * 16) = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+            __syncwarp();
+            const int nc = n0 + cb * 32 + (lane & 7) * 4;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int row = j * 4 + (lane >> 3), tt = tbase + row;
+                const uint4 v = *reinterpret_cast<const uint4*>(tp + row * 144 + (lane & 7) * 16);
+                if (tt < T && nc < N) {
+                    float* o = out + (size_t)tt * ldd + nc;
+                    if (nc + 4 <= N && (ldd & 3) == 0) *reinterpret_cast<uint4*>(o) = v;
+                    else {
+                        const unsigned e[4] = {v.x, v.y, v.z, v.w};
+                        for (int i = 0; i < 4; i++)
+                            if (nc + i < N) o[i] = __uint_as_float(e[i]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(256 * NT));
+}
+
+// X16[t][k'] = fp16(code * scale of its group). Two reorderings of K that the weight tiles share: inside every group of
+// four, positions 1 and 2 are swapped (the order the nibble pairs come out of a code word); and the matrix is stored as
+// the MMA's shared-memory tiles, [token tile of 256][chunk of 64 along K][256 rows][64], the 16-byte chunk c of a row at
+// position c ^ (t & 7) (the 128-byte swizzle), so that one contiguous 32 KB copy brings a stage in ready for the tensor
+// core. Rows past T in the last token tile are never written: they feed accumulator rows that are never stored.
+__global__ void act_to_f16_kernel(const int8_t* __restrict__ codes, const float* __restrict__ scales, int K,
+                                  __half* __restrict__ out) {
+    const int t = blockIdx.y, nG = K >> 5;
+    const int k8 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (k8 >= K) return;
+    const int2 c = *reinterpret_cast<const int2*>(codes + (size_t)t * K + k8);
+    const float s = scales[(size_t)t * 2 * nG + (k8 >> 5)];
+    const int8_t* cb = reinterpret_cast<const int8_t*>(&c);
+    uint4 o;
+    __half2 h;
+    h = __floats2half2_rn(__fmul_rn((float)cb[0], s), __fmul_rn((float)cb[2], s)); o.x = *reinterpret_cast<unsigned*>(&h);
+    h = __floats2half2_rn(__fmul_rn((float)cb[1], s), __fmul_rn((float)cb[3], s)); o.y = *reinterpret_cast<unsigned*>(&h);
+    h = __floats2half2_rn(__fmul_rn((float)cb[4], s), __fmul_rn((float)cb[6], s)); o.z = *reinterpret_cast<unsigned*>(&h);
+    h = __floats2half2_rn(__fmul_rn((float)cb[5], s), __fmul_rn((float)cb[7], s)); o.w = *reinterpret_cast<unsigned*>(&h);
+    const int seg = k8 >> 6, chunk = (k8 >> 3) & 7;
+    const size_t tile = ((size_t)(t >> 8) * (size_t)(K >> 6) + seg) * (256 * 64);
+    *reinterpret_cast<uint4*>(out + tile + (size_t)(t & 255) * 64 + ((chunk ^ (t & 7)) << 3)) = o;
+}
+
+// dst[t][n] = sum over splits, in split order
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, size_t split_stride, int splits, int T, int N,
+                                     float* __restrict__ dst, int ldd) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)T * N) return;
+    const int t = (int)(i / N), n = (int)(i % N);
+    float s = 0.f;
+    for (int k = 0; k < splits; k++) s += part[(size_t)k * split_stride + (size_t)t * N + n];
+    dst[(size_t)t * ldd + n] = s;
+}
+
+// The tensor map of a weight matrix seen as bytes, [N rows][nSB * 144], with a box of one super-block x 128*NT rows. A map
+// depends only on its key, so the cache never goes stale. cuTensorMapEncodeTiled is reached through the runtime's
+// driver-entry-point lookup.
+const CUtensorMap* weight_map(b200_ctx* ctx, const uint8_t* W, int N, int nSB, int NT) {
+    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static std::mutex mu;
+    static encode_fn encode = nullptr;
+    static std::map<std::tuple<const void*, int, int, int>, CUtensorMap*> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
+            qres != cudaDriverEntryPointSuccess) {
+            ctx->err = "cuTensorMapEncodeTiled is not available from this driver";
+            return nullptr;
+        }
+        encode = reinterpret_cast<encode_fn>(fn);
+    }
+    const auto key = std::make_tuple((const void*)W, N, nSB, NT);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    CUtensorMap* m = new CUtensorMap;
+    const cuuint64_t dims[2] = {(cuuint64_t)nSB * kRawRow, (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)nSB * kRawRow};
+    const cuuint32_t box[2] = {(cuuint32_t)kRawRow, (cuuint32_t)(128 * NT)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(W), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        delete m;
+        ctx->err = "cuTensorMapEncodeTiled failed with " + std::to_string((int)r) + " (N=" + std::to_string(N) + ", super-blocks=" + std::to_string(nSB) + ")";
+        return nullptr;
+    }
+    cache[key] = m;
+    return m;
+}
+
+}  // namespace
+
+size_t q4k_umma_scratch_bytes(int max_rows, int max_k, int max_n) {
+    // fp16 activations + split-K partials (up to 4 splits)
+    return (size_t)ceil_div(max_rows, 256) * 256 * max_k * 2 + (size_t)4 * max_rows * max_n * 4 + 256;
+}
+
+int launch_q4k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
+                           size_t scratch_bytes, int* err_flag) {
+    if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
+    if (reinterpret_cast<uintptr_t>(W) & 15) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tcgen05 matmul wants 16-byte aligned weights");
+    const int nSB = K / 256, t_tiles = ceil_div(T, 256);
+    // two weight tiles per CTA halve the activation traffic; one per CTA when that is what it takes to cover the SMs
+    const int max_splits = std::max(1, std::min(4, nSB / 2));
+    const int NT = ceil_div(N, 256) * t_tiles * max_splits >= ctx->sm_count * 3 / 4 ? 2 : 1;
+    const int n_tiles = ceil_div(N, 128 * NT);
+    const int splits = std::max(1, std::min(max_splits, ctx->sm_count / std::max(1, n_tiles * t_tiles)));
+    const size_t x_bytes = (size_t)t_tiles * 256 * K * 2;
+    const size_t part_bytes = splits > 1 ? (size_t)splits * T * N * 4 : 0;
+    if (x_bytes + part_bytes + 256 > scratch_bytes) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tcgen05 matmul scratch too small");
+    __half* x16 = reinterpret_cast<__half*>(scratch);
+    float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + ((x_bytes + 255) & ~(size_t)255));
+    {
+        dim3 grid(ceil_div(K / 8, 256), T);
+        act_to_f16_kernel<<<grid, 256, 0, ctx->stream>>>(aq.codes, aq.scales, K, x16);
+        LAUNCH_CHECK(ctx);
+    }
+    // A ring + B ring (sized for NT = 2) + one raw super-block per producer thread + round-up room
+    constexpr int smem = kStages * 2 * kTileBytes + 2 * 2 * kTileBytes + kProducers * kRawRow + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_set = true;
+    }
+    const CUtensorMap* wmap = weight_map(ctx, W, N, nSB, NT);
+    if (!wmap) return B200_CUDA_ERROR;
+    dim3 grid(n_tiles, t_tiles, splits);
+    float* out = splits > 1 ? part : dst;
+    const int out_ld = splits > 1 ? N : ldd;
+    const size_t stride = splits > 1 ? (size_t)T * N : 0;
+    {
+        ProfScope ps(ctx, PROF_Q4K_GEMM);
+        if (NT == 2) q4k_umma_gemm_kernel<2><<<grid, kUmmaThreads, smem, ctx->stream>>>(*wmap, N, nSB, x16, T, out, out_ld, stride, err_flag);
+        else q4k_umma_gemm_kernel<1><<<grid, kUmmaThreads, smem, ctx->stream>>>(*wmap, N, nSB, x16, T, out, out_ld, stride, err_flag);
+    }
+    LAUNCH_CHECK(ctx);
+    if (splits > 1) {
+        splitk_reduce_kernel<<<(unsigned)(((size_t)T * N + 255) / 256), 256, 0, ctx->stream>>>(part, stride, splits, T, N, dst, ldd);
+        LAUNCH_CHECK(ctx);
+    }
+    return B200_OK;
+}

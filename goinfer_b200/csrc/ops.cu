@@ -22,6 +22,39 @@ struct Tmp {  // device allocations freed at scope exit
     }
 };
 
+// Lends the context a tcgen05-matmul scratch for the length of an operator call (a model owns its own).
+struct UmmaScratch {
+    b200_ctx* ctx;
+    void* saved_p;
+    size_t saved_n;
+    int* saved_f;
+    explicit UmmaScratch(b200_ctx* c) : ctx(c), saved_p(c->umma_scratch), saved_n(c->umma_scratch_bytes), saved_f(c->err_flag) {}
+    int ensure(Tmp& t, int M, int K, int N) {
+        const size_t need = q4k_umma_scratch_bytes(M, K, N);
+        if (ctx->umma_scratch && ctx->umma_scratch_bytes >= need && ctx->err_flag) return B200_OK;
+        uint8_t* p;
+        int* f;
+        CUDA_TRY(ctx, t.get(&p, need));
+        CUDA_TRY(ctx, t.get(&f, 1));
+        CUDA_TRY(ctx, cudaMemsetAsync(f, 0, 4, ctx->stream));
+        ctx->umma_scratch = p;
+        ctx->umma_scratch_bytes = need;
+        ctx->err_flag = f;
+        return B200_OK;
+    }
+    int check() {  // after a stream synchronize
+        int flag = 0;
+        if (ctx->err_flag) cudaMemcpy(&flag, ctx->err_flag, 4, cudaMemcpyDeviceToHost);
+        if (flag) B200_FAIL(ctx, B200_TIMEOUT, "a bounded device-side wait in the tcgen05 matmul gave up");
+        return B200_OK;
+    }
+    ~UmmaScratch() {
+        ctx->umma_scratch = saved_p;
+        ctx->umma_scratch_bytes = saved_n;
+        ctx->err_flag = saved_f;
+    }
+};
+
 #define TMP_GET(ctx, tmp, ptr, n) CUDA_TRY(ctx, (tmp).get(&(ptr), (n)))
 #define H2D(ctx, dst, src, bytes) CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (ctx)->stream))
 #define D2H(ctx, dst, src, bytes) CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (ctx)->stream))
@@ -95,10 +128,12 @@ int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, i
     TMP_GET(ctx, t, aq.codes, (size_t)M * K); TMP_GET(ctx, t, aq.scales, (size_t)M * 2 * (K / 32));
     H2D(ctx, dw, w, wb); H2D(ctx, da, a, (size_t)M * K * 4);
     ST_TRY(launch_quant_g32(ctx, da, M, K, aq));
+    UmmaScratch us(ctx);
+    ST_TRY(us.ensure(t, M, K, N));
     ST_TRY(launch_q4k_matmul(ctx, dw, N, K, aq, M, dd, N, klass));
     D2H(ctx, dst, dd, (size_t)M * N * 4);
     SYNC(ctx);
-    return B200_OK;
+    return us.check();
 }
 
 int b200_op_q4k_quantize(b200_ctx* ctx, const float* w, int rows, int cols, uint8_t* out) {
@@ -209,6 +244,8 @@ int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_w
     for (int c = 0; c < n_weight_copies; c++) ST_TRY(launch_synth_q4k(ctx, dw + (size_t)c * wb, wb / 144, 0.02f, 17 + c));
     ST_TRY(launch_synth_normal_f32(ctx, da, (size_t)M * K, 1.f, 5));
     ST_TRY(launch_quant_g32(ctx, da, M, K, aq));
+    UmmaScratch us(ctx);
+    ST_TRY(us.ensure(t, M, K, N));
     cudaEvent_t e0, e1;
     CUDA_TRY(ctx, cudaEventCreate(&e0)); CUDA_TRY(ctx, cudaEventCreate(&e1));
     for (int i = 0; i < warmup; i++) ST_TRY(launch_q4k_matmul(ctx, dw + (size_t)(i % n_weight_copies) * wb, N, K, aq, M, dd, N, klass));
@@ -220,7 +257,7 @@ int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_w
     cudaEventElapsedTime(&ms, e0, e1);
     cudaEventDestroy(e0); cudaEventDestroy(e1);
     *ms_out = ms / iters;
-    return B200_OK;
+    return us.check();
 }
 
 int b200_bench_attention(b200_ctx* ctx, int rows, int ctx_lo, int ctx_hi, int n_heads, int n_kv_heads, int head_dim,

@@ -69,11 +69,34 @@ def test_q4k_matmul_exact_class(ops, oracle_lib, M):
     ref = oracle_lib.op_q4k_matmul_f64(raw, a, N)
     scale = np.abs(ref).max()
     assert np.abs(got - ref).max() <= 1e-5 * scale          # the reference's own GEMV bar
-    fast = ops.q4k_matmul(raw, a, N, klass=0)               # fast class: split-K up to 8 rows
-    assert np.abs(fast - ref).max() <= 1e-5 * scale
-    assert np.abs(fast - want).max() <= 2e-6 * scale
-    if M > 8:
+    fast = ops.q4k_matmul(raw, a, N, klass=0)               # fast class: other kernels up to 8 and from 64 rows
+    if M < 64:
+        assert np.abs(fast - ref).max() <= 1e-5 * scale
+        assert np.abs(fast - want).max() <= 2e-6 * scale
+    else:
+        assert np.abs(fast - ref).max() <= 4e-3 * scale     # tcgen05 fp16 operands
+    if 8 < M < 64:
         assert np.array_equal(fast, got)
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 256, 1024), (128, 384, 512), (200, 200, 1024), (256, 512, 2048), (300, 128, 256), (256, 640, 4096)])
+def test_q4k_matmul_fast_class_tcgen05(ops, oracle_lib, M, N, K):
+    """The tcgen05/TMEM matmul of the fast class: both operands dequantized to fp16 (sub-block scale, minimum and
+    activation each rounded to fp16; the weight's sub-block offset is rounded to fp16 as well, which is the larger
+    term: about 2^-8 of a quantization step per weight), fp32 accumulate. Held to 4e-3 of the output scale and 2.5e-3 in
+    relative L2 against the f64 value of the exact formula (the int8 activation codes the formula itself is built on are
+    several times coarser than that)."""
+    rng = np.random.default_rng(M + N + K)
+    raw = q4k.quantize(rng.normal(0, 0.02, (N, K)).astype(np.float32))
+    a = rng.normal(0, 1, (M, K)).astype(np.float32)
+    a[1, :64] = 0
+    a[2, 5] = 40.0                                   # an activation outlier
+    ref = oracle_lib.op_q4k_matmul_f64(raw, a, N)
+    got = ops.q4k_matmul(raw, a, N, klass=2)
+    scale = np.abs(ref).max()
+    assert np.abs(got - ref).max() <= 4e-3 * scale, np.abs(got - ref).max() / scale
+    rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+    assert rel <= 2.5e-3, rel
 
 
 def test_q4k_matmul_saturated_and_random_bytes(ops, oracle_lib):
