@@ -159,6 +159,11 @@ int launch_paged_attention(b200_ctx*, const float* q, int ldq, int T, int nH, in
                            const int32_t* row_slot, const int32_t* row_pos, int max_keys, KVView kv, AttnScratch sc,
                            float* out, ActQ aq);
 
+// attention_prefill.cu: causal attention for a run of rows of one slot at consecutive positions pos0.. (fast class)
+bool prefill_attention_supported(int nH, int nKV, int hd, int block_rows);
+int launch_prefill_attention(b200_ctx*, const float* q, int ldq, int nrows, int nH, int nKV, int hd, float scale, float softcap,
+                             int slot, int pos0, KVView kv, float* out, int ldo);
+
 // exact class: f64 arithmetic in the CPU path's own order; scores is [T*nH][ld] f32 scratch, ld >= max_keys
 int launch_paged_attention_exact(b200_ctx*, const float* q, int ldq, int T, int nH, int nKV, int hd, double scale,
                                  double softcap, const int32_t* row_slot, const int32_t* row_pos, int max_keys, KVView kv,

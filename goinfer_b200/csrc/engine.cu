@@ -187,6 +187,9 @@ struct b200_model {
     size_t umma_bytes = 0;
     int* err_flag = nullptr;       // raised by a bounded device-side wait that gave up
     float* exact_scores = nullptr;  // exact class: [MR*nH][ctx_cap]
+    // the step's leading prefill run (rows of one slot at consecutive positions), 0 rows when there is none;
+    // pf_tail_keys = the longest key range among the rows after it
+    int pf_rows = 0, pf_slot = 0, pf_pos0 = 0, pf_tail_keys = 1;
     // MoE
     float *rl = nullptr, *rw = nullptr, *egu_out = nullptr, *eo = nullptr, *emid = nullptr;
     int32_t *ridx = nullptr, *eoffs = nullptr, *erows = nullptr;
@@ -315,6 +318,8 @@ int matmul(b200_model* m, const DevMat& W, const float* xf, ActQ xq, int T, floa
     return launch_f32w_matmul(ctx, (const float*)W.p, W.rows, W.cols, xf, T, dst, ldd);
 }
 
+constexpr int kPrefillRunMin = 16;  // shorter runs stay with the flash-decode kernel, a row each
+
 int run_layers(b200_model* m, int T, int max_keys) {
     b200_ctx* ctx = m->ctx;
     const b200_model_cfg& c = m->c;
@@ -342,8 +347,21 @@ int run_layers(b200_model* m, int T, int max_keys) {
                                                 m->d_row_pos, max_keys, kv, m->exact_scores, c.ctx_cap, m->ctxb,
                                                 o_q ? m->aq_ctx : none));
         } else {
-            ST_TRY(launch_paged_attention(ctx, m->qkv, ldq, T, nH, nKV, hd, scale, c.attn_softcap, m->d_row_slot, m->d_row_pos,
-                                          max_keys, kv, m->asc, m->ctxb, o_q ? m->aq_ctx : none));
+            // a leading run of rows of one sequence (a prefill chunk) goes through the tiled causal kernel, the rest through
+            // flash-decode; both write f32 context rows and their per-32 codes
+            const int pf = m->pf_rows;
+            if (pf > 0) {
+                ST_TRY(launch_prefill_attention(ctx, m->qkv, ldq, pf, nH, nKV, hd, scale, c.attn_softcap, m->pf_slot, m->pf_pos0, kv,
+                                                m->ctxb, qd));
+                if (o_q) ST_TRY(launch_quant_g32(ctx, m->ctxb, pf, qd, m->aq_ctx));
+            }
+            if (T > pf) {
+                ActQ aq_tail = none;
+                if (o_q) aq_tail = ActQ{m->aq_ctx.codes + (size_t)pf * qd, m->aq_ctx.scales + (size_t)pf * 2 * (qd / 32)};
+                ST_TRY(launch_paged_attention(ctx, m->qkv + (size_t)pf * ldq, ldq, T - pf, nH, nKV, hd, scale, c.attn_softcap,
+                                              m->d_row_slot + pf, m->d_row_pos + pf, pf > 0 ? m->pf_tail_keys : max_keys, kv, m->asc,
+                                              m->ctxb + (size_t)pf * qd, aq_tail));
+            }
         }
         ST_TRY(matmul(m, L.wo, m->ctxb, m->aq_ctx, T, m->att, H));
         if (c.n_experts == 0) {
@@ -867,7 +885,19 @@ int b200_step_ragged(b200_model* m, int n_seqs, const int32_t* slot, const int32
         m->h_slot_len[slot[i]] = std::max(m->h_slot_len[slot[i]], pos[i] + n_rows[i]);
     }
     if (token_ids) ST_TRY(launch_embed_gather(ctx, m->embed.p, m->embed.kind, m->d_tokens, T, H, c.embed_scale, m->h));
-    ST_TRY(run_layers(m, T, max_keys));
+    // the first sequence's rows, when they are many, form the tiled prefill run (fast class only)
+    m->pf_rows = 0;
+    if (!m->exact_scores && n_rows[0] >= kPrefillRunMin && prefill_attention_supported(c.n_heads, c.n_kv_heads, c.head_dim, c.kv_block_rows) &&
+        !getenv("B200_NO_PREFILL_ATTN")) {
+        m->pf_rows = n_rows[0];
+        m->pf_slot = slot[0];
+        m->pf_pos0 = pos[0];
+        m->pf_tail_keys = 1;
+        for (int i = 1; i < n_seqs; i++) m->pf_tail_keys = std::max(m->pf_tail_keys, pos[i] + n_rows[i]);
+    }
+    const int st_layers = run_layers(m, T, max_keys);
+    m->pf_rows = 0;
+    if (st_layers != B200_OK) return st_layers;
     // ---- head, in chunks of MLR rows ----
     if ((size_t)std::max(n_out, 1) * V * 4 > m->p_logits_cap) {
         if (m->p_logits) cudaFreeHost(m->p_logits);

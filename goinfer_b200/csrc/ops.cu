@@ -233,6 +233,80 @@ int b200_op_attention(b200_ctx* ctx, const float* q, const float* k, const float
     return B200_OK;
 }
 
+namespace {
+// one slot holding `keys` rows of K/V in a fresh pool; fills kv and returns through the Tmp
+int build_one_slot_kv(b200_ctx* ctx, Tmp& t, const float* dk, const float* dv, int keys, int n_kv_heads, int head_dim, int block_rows,
+                      KVView* kv_out) {
+    const int max_blocks = ceil_div(keys, block_rows);
+    const size_t pool_elems = (size_t)(1 + max_blocks) * n_kv_heads * block_rows * head_dim;
+    __half *kp, *vp; int32_t *tbl, *nk;
+    TMP_GET(ctx, t, kp, pool_elems); TMP_GET(ctx, t, vp, pool_elems); TMP_GET(ctx, t, tbl, (size_t)max_blocks); TMP_GET(ctx, t, nk, 1);
+    CUDA_TRY(ctx, cudaMemsetAsync(kp, 0, pool_elems * 2, ctx->stream));
+    CUDA_TRY(ctx, cudaMemsetAsync(vp, 0, pool_elems * 2, ctx->stream));
+    H2D(ctx, nk, &keys, 4);
+    iota_blocks_kernel<<<ceil_div(max_blocks, 256), 256, 0, ctx->stream>>>(tbl, 1, max_blocks, nk, block_rows);
+    LAUNCH_CHECK(ctx);
+    const size_t kvn = (size_t)keys * n_kv_heads * head_dim;
+    scatter_kv_kernel<<<(unsigned)((kvn + 255) / 256), 256, 0, ctx->stream>>>(dk, dv, kp, vp, tbl, 1, keys, max_blocks, n_kv_heads,
+                                                                              head_dim, block_rows, nk);
+    LAUNCH_CHECK(ctx);
+    *kv_out = KVView{kp, vp, tbl, max_blocks, block_rows, n_kv_heads, head_dim};
+    return B200_OK;
+}
+}  // namespace
+
+int b200_op_prefill_attention(b200_ctx* ctx, const float* q, const float* k, const float* v, int rows, int pos0, int n_heads,
+                              int n_kv_heads, int head_dim, float scale, float softcap, int block_rows, float* out) {
+    if (rows <= 0 || pos0 < 0 || block_rows <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad attention shape");
+    if (!prefill_attention_supported(n_heads, n_kv_heads, head_dim, block_rows))
+        B200_FAIL(ctx, B200_DECLINED, "prefill attention: head_dim %d, group %d, %d-row blocks is not built", head_dim, n_heads / n_kv_heads, block_rows);
+    Tmp t;
+    const int keys = pos0 + rows;
+    const size_t kvn = (size_t)keys * n_kv_heads * head_dim, qn = (size_t)rows * n_heads * head_dim;
+    float *dq, *dk, *dv, *dout;
+    TMP_GET(ctx, t, dq, qn); TMP_GET(ctx, t, dk, kvn); TMP_GET(ctx, t, dv, kvn); TMP_GET(ctx, t, dout, qn);
+    H2D(ctx, dq, q, qn * 4); H2D(ctx, dk, k, kvn * 4); H2D(ctx, dv, v, kvn * 4);
+    KVView kv;
+    ST_TRY(build_one_slot_kv(ctx, t, dk, dv, keys, n_kv_heads, head_dim, block_rows, &kv));
+    const float sc_ = scale != 0.f ? scale : (float)(1.0 / std::sqrt((double)head_dim));
+    ST_TRY(launch_prefill_attention(ctx, dq, n_heads * head_dim, rows, n_heads, n_kv_heads, head_dim, sc_, softcap, 0, pos0, kv, dout,
+                                    n_heads * head_dim));
+    D2H(ctx, out, dout, qn * 4);
+    SYNC(ctx);
+    return B200_OK;
+}
+
+int b200_bench_prefill_attention(b200_ctx* ctx, int rows, int pos0, int n_heads, int n_kv_heads, int head_dim, int block_rows,
+                                 int warmup, int iters, float* ms_out) {
+    if (rows <= 0 || pos0 < 0 || iters <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad bench shape");
+    if (!prefill_attention_supported(n_heads, n_kv_heads, head_dim, block_rows)) B200_FAIL(ctx, B200_DECLINED, "prefill attention shape is not built");
+    Tmp t;
+    const int keys = pos0 + rows;
+    const size_t kvn = (size_t)keys * n_kv_heads * head_dim, qn = (size_t)rows * n_heads * head_dim;
+    float *dq, *dk, *dv, *dout;
+    TMP_GET(ctx, t, dq, qn); TMP_GET(ctx, t, dk, kvn); TMP_GET(ctx, t, dv, kvn); TMP_GET(ctx, t, dout, qn);
+    ST_TRY(launch_synth_normal_f32(ctx, dq, qn, 1.f, 11));
+    ST_TRY(launch_synth_normal_f32(ctx, dk, kvn, 0.5f, 12));
+    ST_TRY(launch_synth_normal_f32(ctx, dv, kvn, 0.5f, 13));
+    KVView kv;
+    ST_TRY(build_one_slot_kv(ctx, t, dk, dv, keys, n_kv_heads, head_dim, block_rows, &kv));
+    const float sc_ = (float)(1.0 / std::sqrt((double)head_dim));
+    cudaEvent_t e0, e1;
+    CUDA_TRY(ctx, cudaEventCreate(&e0)); CUDA_TRY(ctx, cudaEventCreate(&e1));
+    for (int i = 0; i < warmup; i++)
+        ST_TRY(launch_prefill_attention(ctx, dq, n_heads * head_dim, rows, n_heads, n_kv_heads, head_dim, sc_, 0.f, 0, pos0, kv, dout, n_heads * head_dim));
+    CUDA_TRY(ctx, cudaEventRecord(e0, ctx->stream));
+    for (int i = 0; i < iters; i++)
+        ST_TRY(launch_prefill_attention(ctx, dq, n_heads * head_dim, rows, n_heads, n_kv_heads, head_dim, sc_, 0.f, 0, pos0, kv, dout, n_heads * head_dim));
+    CUDA_TRY(ctx, cudaEventRecord(e1, ctx->stream));
+    SYNC(ctx);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    *ms_out = ms / iters;
+    return B200_OK;
+}
+
 int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_weight_copies, int warmup, int iters, float* ms_out) {
     if (K % 256 || M <= 0 || N <= 0 || n_weight_copies <= 0 || iters <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad bench shape");
     Tmp t;

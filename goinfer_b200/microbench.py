@@ -1,7 +1,8 @@
-"""Device-resident micro-benchmarks of the two kernels that carry the step, on synthetic data.
+"""Device-resident micro-benchmarks of the kernels that carry the step, on synthetic data.
 
   python -m goinfer_b200.microbench attention --rows 256 [--ctx-lo 128 --ctx-hi 8192 --heads 32 --kv-heads 8 --head-dim 128]
   python -m goinfer_b200.microbench q4k --rows 1 2 4 8 16 32 256 [--n 12288 --k 4096]
+  python -m goinfer_b200.microbench prefill --rows 2048 [--pos0 0 --heads 32 --kv-heads 8 --head-dim 128]
 
 Times are CUDA-event averages per launch after warm-up. Weight matrices are cycled through several copies and KV pools
 are far larger than the 126 MB L2, so no launch finds its inputs cached.
@@ -23,6 +24,15 @@ def main():
     a.add_argument("--block-rows", type=int, default=16)
     a.add_argument("--iters", type=int, default=10)
     a.add_argument("--warmup", type=int, default=3)
+    p = sub.add_parser("prefill")
+    p.add_argument("--rows", type=int, default=2048)
+    p.add_argument("--pos0", type=int, default=0)
+    p.add_argument("--heads", type=int, default=32)
+    p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--head-dim", type=int, default=128)
+    p.add_argument("--block-rows", type=int, default=16)
+    p.add_argument("--iters", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
     g = sub.add_parser("q4k")
     g.add_argument("--rows", type=int, nargs="+", default=[1, 2, 4, 8, 16, 32, 256])
     g.add_argument("--n", type=int, default=12288)
@@ -38,6 +48,14 @@ def main():
                                       args.block_rows, 2, args.warmup, args.iters)
         print(json.dumps({"kernel": "paged attention (split + combine)", "rows": args.rows, "ms_per_launch": ms,
                           "kv_bytes": kvb, "GBps": kvb / ms / 1e6}))
+    elif args.what == "prefill":
+        ms = ops.bench_prefill_attention(args.rows, args.pos0, args.heads, args.kv_heads, args.head_dim, args.block_rows,
+                                         args.warmup, args.iters)
+        # causal: row j sees pos0 + j + 1 keys; 4 flop per (row, key, head, dim): QK^T and PV, a multiply-add each
+        pairs = args.rows * args.pos0 + args.rows * (args.rows + 1) / 2
+        flop = 4.0 * pairs * args.heads * args.head_dim
+        print(json.dumps({"kernel": "prefill attention (causal run)", "rows": args.rows, "pos0": args.pos0, "ms_per_launch": ms,
+                          "TFLOPps": flop / ms / 1e9}))
     else:
         for m in args.rows:
             ms = ops.bench_q4k_matmul(m, args.k, args.n, args.klass, 8, args.warmup, args.iters)

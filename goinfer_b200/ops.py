@@ -94,6 +94,25 @@ class Ops:
                                                block_rows, klass, _p(out, C.c_float)))
         return out
 
+    def prefill_attention(self, q, k, v, pos0, n_heads, n_kv_heads, head_dim, scale=0.0, softcap=0.0, block_rows=16):
+        """q [rows][n_heads*head_dim], k/v [pos0+rows][n_kv_heads*head_dim]; row j sees keys 0..pos0+j."""
+        q = np.ascontiguousarray(q, np.float32)
+        k = np.ascontiguousarray(k, np.float32)
+        v = np.ascontiguousarray(v, np.float32)
+        rows = q.shape[0]
+        assert k.shape[0] == pos0 + rows and v.shape == k.shape
+        out = np.empty_like(q)
+        self._check(self.lib.b200_op_prefill_attention(self.ctx, _p(q, C.c_float), _p(k, C.c_float), _p(v, C.c_float), rows, pos0,
+                                                       n_heads, n_kv_heads, head_dim, C.c_float(scale), C.c_float(softcap),
+                                                       block_rows, _p(out, C.c_float)))
+        return out
+
+    def bench_prefill_attention(self, rows, pos0, n_heads, n_kv_heads, head_dim, block_rows=16, warmup=3, iters=10) -> float:
+        ms = C.c_float(0)
+        self._check(self.lib.b200_bench_prefill_attention(self.ctx, rows, pos0, n_heads, n_kv_heads, head_dim, block_rows,
+                                                          warmup, iters, C.byref(ms)))
+        return ms.value
+
     def bench_q4k_matmul(self, M, K, N, klass=0, n_weight_copies=8, warmup=3, iters=20) -> float:
         ms = C.c_float(0)
         self._check(self.lib.b200_bench_q4k_matmul(self.ctx, M, K, N, klass, n_weight_copies, warmup, iters, C.byref(ms)))

@@ -245,6 +245,13 @@ int b200_op_attention(b200_ctx* ctx, const float* q, const float* k, const float
                       int rows, int max_keys, int n_heads, int n_kv_heads, int head_dim, float scale,
                       float softcap, int block_rows, int klass /* 0 fast fp32, 1 exact f64 */, float* out);
 
+/* Causal attention of a prefill run: `rows` query rows of one sequence at positions pos0 .. pos0+rows-1 over its
+ * K/V [pos0+rows][n_kv_heads*head_dim] (f32 rounded to fp16 on upload, paged); row j attends keys 0 .. pos0+j
+ * (the per-row loop of decoder/program_cpu_n.go:497-515 over decoder/forwardn.go:295-501). Fast class. */
+int b200_op_prefill_attention(b200_ctx* ctx, const float* q, const float* k, const float* v, int rows, int pos0,
+                              int n_heads, int n_kv_heads, int head_dim, float scale, float softcap,
+                              int block_rows, float* out);
+
 /* Device-resident micro-benchmarks: average device milliseconds per launch over `iters` launches after
  * `warmup`, of the kernel the step would pick (or `klass`), on synthetic resident data. */
 int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_weight_copies,
@@ -252,6 +259,8 @@ int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_w
 int b200_bench_attention(b200_ctx* ctx, int rows, int ctx_lo, int ctx_hi, int n_heads, int n_kv_heads,
                          int head_dim, int block_rows, uint64_t seed, int warmup, int iters,
                          float* ms_out, double* kv_bytes_out);
+int b200_bench_prefill_attention(b200_ctx* ctx, int rows, int pos0, int n_heads, int n_kv_heads, int head_dim,
+                                 int block_rows, int warmup, int iters, float* ms_out);
 
 /* Paged decode attention that allocates nothing. No counterpart in the reference (its backends allocate their split
  * buffers when a model is built); it exists for hosts that cannot allocate when they need attention: a serving process

@@ -164,6 +164,36 @@ def test_fast_class_meets_the_reference_gpu_vs_cpu_bars(oracle_lib):
         lo = o.Forward(None, 40 + step, 0, token=t).astype(np.float64)
 
 
+def test_fast_class_prefill_run_kernel_in_a_ragged_step(oracle_lib, monkeypatch):
+    """The fast class sends a step's leading prefill chunk through the tiled causal kernel and the rows behind it through
+    flash-decode. A chunked prompt with decode rows riding along must land within the logit tolerance of the oracle, and
+    so must the same steps run with the tiled kernel switched off (every row a flash-decode row)."""
+    import os
+    outs = {}
+    for mode in ("tiled", "rows"):
+        if mode == "rows":
+            monkeypatch.setenv("B200_NO_PREFILL_ATTN", "1")
+        g, o, s = build_pair(oracle_lib, "tiny-qknorm", n_slots=4, ctx_cap=160, seed=13, max_rows=96, klass=abi.CLASS_AUTO)
+        rng = np.random.default_rng(4)
+        p0 = rng.integers(0, s.vocab, 90).tolist()
+        p1 = rng.integers(0, s.vocab, 21).tolist()
+        res = []
+        for r in (g, o) if mode == "tiled" else (g,):
+            r.PrefillLast(None, 0, 1, p1)
+            a = r.StepRagged([RaggedSeq(0, 0, None, p0[:53], None, RaggedPrefill(90, False)), RaggedSeq(1, 21, None, [5])])
+            b = r.StepRagged([RaggedSeq(0, 53, None, p0[53:], None, RaggedPrefill(90, True)), RaggedSeq(1, 22, None, [9])])
+            c = r.Forward(None, 90, 0, token=3)
+            res.append((a[1].Logits[0], b[0].Logits[-1], b[1].Logits[0], c))
+        outs[mode] = res
+        g.Close()
+    for x, y in zip(outs["tiled"][0], outs["tiled"][1]):
+        ok, err = close_logits(x, y)
+        assert ok, err
+    for x, y in zip(outs["tiled"][0], outs["rows"][0]):
+        ok, err = close_logits(x, y)     # an int8 activation code may flip on the last-bit differences of the two kernels
+        assert ok, err
+
+
 def test_kv_pool_full_writes_nothing_and_bad_steps_are_refused(oracle_lib):
     g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=3, ctx_cap=64, seed=9, kv_pool_blocks=1 + 3)
     for r in (g, o):

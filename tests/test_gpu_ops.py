@@ -213,6 +213,57 @@ def test_paged_attention_matches_the_f64_oracle(ops, oracle_lib, nH, nKV, hd):
     np.testing.assert_allclose(ops.attention(q, k, v, n_keys, nH, nKV, hd, scale, 0.0, block_rows=64, klass=1), want0, atol=0, rtol=3e-7)
 
 
+@pytest.mark.parametrize("nH,nKV,hd", [(32, 8, 128), (32, 4, 64), (4, 2, 64), (8, 8, 128), (16, 2, 128)])
+@pytest.mark.parametrize("rows,pos0,block_rows", [(16, 0, 16), (37, 0, 16), (45, 83, 16), (33, 500, 64), (130, 7, 16)])
+def test_prefill_attention_matches_the_f64_oracle(ops, oracle_lib, nH, nKV, hd, rows, pos0, block_rows):
+    """A run of rows at consecutive positions of one sequence (a prefill chunk): row j sees keys 0..pos0+j. The oracle is the
+    CPU path's per-row attention given each row its own key count; tile edges (16 rows, 32 keys), block edges and a chunk
+    that starts deep in the context are covered."""
+    rng = np.random.default_rng(hd + nH + rows + pos0)
+    keys = pos0 + rows
+    q = rng.normal(0, 1, (rows, nH * hd)).astype(np.float32)
+    k = rng.normal(0, 1, (keys, nKV * hd)).astype(np.float32)
+    v = rng.normal(0, 1, (keys, nKV * hd)).astype(np.float32)
+    scale = 1.0 / np.sqrt(hd)
+    n_keys = (pos0 + 1 + np.arange(rows)).astype(np.int32)
+    kk = np.broadcast_to(k, (rows,) + k.shape)
+    vv = np.broadcast_to(v, (rows,) + v.shape)
+    for cap in (0.0, 30.0):
+        want = oracle_lib.op_attention(q, kk, vv, n_keys, nH, nKV, hd, scale, cap)
+        got = ops.prefill_attention(q, k, v, pos0, nH, nKV, hd, scale, cap, block_rows=block_rows)
+        np.testing.assert_allclose(got, want, atol=2e-5, rtol=1e-4)   # fast class: fp32 online softmax vs f64
+
+
+def test_prefill_attention_properties_at_chunk_size(ops):
+    """Size-independent properties at the benchmark's prefill chunk (2048 rows, 32 query / 8 kv heads of 128): a constant
+    V comes back; the output is linear in V; row j does not depend on keys after pos0+j (later rows' keys are poisoned
+    one row at a time by comparing against a shorter run)."""
+    rng = np.random.default_rng(21)
+    nH, nKV, hd, rows, pos0 = 32, 8, 128, 2048, 160
+    keys = pos0 + rows
+    q = rng.normal(0, 1, (rows, nH * hd)).astype(np.float32)
+    k = rng.normal(0, 1, (keys, nKV * hd)).astype(np.float32)
+    v1 = rng.normal(0, 1, (keys, nKV * hd)).astype(np.float16).astype(np.float32)
+    const = np.broadcast_to(rng.normal(0, 1, (1, nKV * hd)).astype(np.float16).astype(np.float32), v1.shape)
+    o_const = ops.prefill_attention(q, k, const, pos0, nH, nKV, hd)
+    want = np.repeat(const[0].reshape(nKV, 1, hd), nH // nKV, axis=1).reshape(-1)
+    np.testing.assert_allclose(o_const, np.broadcast_to(want, o_const.shape), atol=2e-3, rtol=0)
+    o1 = ops.prefill_attention(q, k, v1, pos0, nH, nKV, hd)
+    o2 = ops.prefill_attention(q, k, 2 * v1, pos0, nH, nKV, hd)
+    np.testing.assert_allclose(o2, 2 * o1, atol=1e-5, rtol=1e-5)
+    # the first 1000 rows of the run, computed without the later keys present at all, are the same rows
+    short = ops.prefill_attention(q[:1000], k[:pos0 + 1000], v1[:pos0 + 1000], pos0, nH, nKV, hd)
+    assert np.array_equal(short[:992], o1[:992])        # whole 16-row tiles see identical key tiles
+    np.testing.assert_allclose(short[992:], o1[992:1000], atol=1e-6, rtol=1e-5)
+    # and a prefill row agrees with the flash-decode kernel's row for the same query
+    pick = np.array([0, 511, 2047])
+    n_keys = (pos0 + 1 + pick).astype(np.int32)
+    kk = np.broadcast_to(k, (3,) + k.shape)
+    vv = np.broadcast_to(v1, (3,) + v1.shape)
+    dec = ops.attention(q[pick], kk, vv, n_keys, nH, nKV, hd)
+    np.testing.assert_allclose(o1[pick], dec, atol=2e-5, rtol=1e-4)
+
+
 def test_attention_properties_at_full_context(ops):
     """Size-independent properties at the benchmark's largest context (8192 keys, 8 kv heads of 128):
     constant V gives that constant back; the output is linear in V; keys past n_keys do not matter."""
