@@ -29,6 +29,7 @@ sys.path.insert(0, ROOT)
 METRIC = "ragged-batch decode tok/s (Q4_K, 8B shape, B=256)"
 B, CTX_LO, CTX_HI, SEED = 256, 128, 8192, 2
 SAMPLE_SEQS, SAMPLE_LAYERS = 32, 2
+PF_ROWS, PF_DEEP = 2048, 4096      # the workload's prefill chunk: rows, and how deep into a context its second run starts
 
 
 def contexts():
@@ -172,8 +173,9 @@ def run_gpu(args):
     ctx = contexts()
     growth = 2 * (K + W) + 12                      # positions each sequence may advance over the timed loops
     cap = int(ctx.max()) + growth
-    blocks = 1 + int(np.ceil((ctx + growth) / 16).sum())
-    cfg = synth.make_cfg(s, B, cap, 16, blocks, B, abi.CLASS_AUTO)
+    # one more slot takes the 2048-row prefill chunk (at position 0, and again 4096 rows deep into a context)
+    blocks = 1 + int(np.ceil((ctx + growth) / 16).sum()) + (PF_DEEP + PF_ROWS) // 16 + 2
+    cfg = synth.make_cfg(s, B + 1, cap, 16, blocks, max(B, PF_ROWS), abi.CLASS_AUTO)
     with torch.cuda.stream(stream):
         r = Resident(cfg, device=local, stream=stream.cuda_stream)
         synth.load_device_weights(r, s, seed=SEED)
@@ -255,6 +257,43 @@ def run_gpu(args):
         breakdown = {n: {"ms_per_step": tag_ms[i] / 2, "launches_per_step": int(tag_n[i] // 2)} for i, n in enumerate(names) if tag_n[i]}
         breakdown["step_ms_with_events"] = float(ms.value) / 2
 
+        # ---- the workload's prefill chunk: PF_ROWS prompt rows of one sequence in one ragged step (device embedding gather,
+        # last row's logits read back), at position 0 and PF_DEEP rows into a context; device time by events on the stream ----
+        prefill = []
+        pf_tok = np.random.default_rng(SEED + 2).integers(0, s.vocab, PF_ROWS).astype(np.int32)
+        pf_logits = np.zeros(s.vocab, np.float32)
+        one = lambda v: np.array([v], np.int32)
+        for pos0 in (0, PF_DEEP):
+            best = None
+            for rep in range(3):
+                check(lib.b200_reset_slot(m, B))
+                if pos0:
+                    r.SynthKV(B, pos0, 0.5, 77)
+                if rep == 2:
+                    lib.b200_profile(bctx, 0xFF)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                e0.record(stream)
+                check(lib.b200_step_ragged(m, 1, p32(one(B)), p32(one(pos0)), p32(one(PF_ROWS)), p32(one(pos0 + PF_ROWS)),
+                                           np.array([1], np.uint8).ctypes.data_as(C.POINTER(C.c_uint8)), None, p32(pf_tok), None,
+                                           None, None, 0, pf_logits.ctypes.data_as(C.POINTER(C.c_float)), None, None))
+                e1.record(stream)
+                torch.cuda.synchronize()
+                wall_ms = (time.perf_counter() - t0) * 1e3
+                if rep == 2:
+                    lib.b200_profile_read(bctx, tag_ms, tag_n, 8)
+                    lib.b200_profile(bctx, 0)
+                    pf_break = {n: {"ms": tag_ms[i], "launches": int(tag_n[i])} for i, n in enumerate(names) if tag_n[i]}
+                else:
+                    dms = e0.elapsed_time(e1)
+                    best = (dms, wall_ms) if best is None or dms < best[0] else best
+            lin_flop = 2.0 * PF_ROWS * 36 * (4096 * 6144 + 4096 * 4096 + 3 * 4096 * 12288)
+            att_flop = 4.0 * (PF_ROWS * pos0 + PF_ROWS * (PF_ROWS + 1) / 2) * s.n_heads * s.head_dim * 36
+            prefill.append({"rows": PF_ROWS, "pos0": pos0, "ms": best[0], "tok_s": PF_ROWS / best[0] * 1e3, "e2e_ms": best[1],
+                            "linear_tflops": lin_flop / best[0] / 1e9, "attention_tflops": att_flop / best[0] / 1e9,
+                            "finite_logits": bool(np.isfinite(pf_logits).all()), "breakdown_with_events": pf_break})
+
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([dev_ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
@@ -289,6 +328,7 @@ def run_gpu(args):
                      "algorithmic_bytes_per_launch": attn_bytes_per_launch, "ms_per_launch": attn_ms_per_launch,
                      "launches_timed": attn_launches, "share_of_step": attn_ms_total / dev_ms if dev_ms else None},
         "breakdown": breakdown,
+        "prefill_chunk": prefill,
         "memory": {"weights_gb": caps.weight_bytes / 1e9, "kv_gb": caps.kv_bytes / 1e9, "scratch_gb": caps.scratch_bytes / 1e9},
     }
     if world == 1 and not args.no_cpu:

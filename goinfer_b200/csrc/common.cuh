@@ -137,7 +137,12 @@ size_t q4k_umma_scratch_bytes(int max_rows, int max_k, int max_n);
 int launch_q4k_matmul_umma(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
                            size_t scratch_bytes, int* err_flag);
 int launch_f16w_matmul(b200_ctx*, const __half* W, int N, int K, const float* x, int T, float* dst, int ldd,
-                       __half* split_scratch /* 2*T*K halves */);
+                       __half* split_scratch, int klass);
+// gemm_f16_umma.cu: the tcgen05 kernel behind it (fast class, dense row counts)
+size_t f16w_umma_scratch_bytes(int T, int K);
+bool f16w_umma_supported(const __half* W, int N, int K);
+int launch_f16w_matmul_umma(b200_ctx*, const __half* W, int N, int K, const float* x, int T, float* dst, int ldd, void* scratch,
+                            size_t scratch_bytes, int* err_flag);
 int launch_f32w_matmul(b200_ctx*, const float* W, int N, int K, const float* x, int T, float* dst, int ldd);
 // grouped f32 form (f32 test models with routed experts): same indirection as the Q4_K grouped matmul
 int launch_f32w_matmul_grouped(b200_ctx*, const float* const* Wptrs, int n_experts, int N, int K, const float* x,

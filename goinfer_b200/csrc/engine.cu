@@ -314,7 +314,7 @@ int fuse_rows(b200_model* m, std::vector<DevMat*> parts, DevMat* out) {
 int matmul(b200_model* m, const DevMat& W, const float* xf, ActQ xq, int T, float* dst, int ldd) {
     b200_ctx* ctx = m->ctx;
     if (W.kind == B200_K_Q4K) return launch_q4k_matmul(ctx, (const uint8_t*)W.p, W.rows, W.cols, xq, T, dst, ldd, m->c.kernel_class);
-    if (W.kind == B200_K_F16) return launch_f16w_matmul(ctx, (const __half*)W.p, W.rows, W.cols, xf, T, dst, ldd, m->split);
+    if (W.kind == B200_K_F16) return launch_f16w_matmul(ctx, (const __half*)W.p, W.rows, W.cols, xf, T, dst, ldd, m->split, m->c.kernel_class);
     return launch_f32w_matmul(ctx, (const float*)W.p, W.rows, W.cols, xf, T, dst, ldd);
 }
 

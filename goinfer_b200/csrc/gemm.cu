@@ -767,7 +767,12 @@ int launch_q4k_matmul_grouped(b200_ctx* ctx, const uint8_t* const* Wptrs, int n_
 
 // split_scratch: 2*T*K halves (the activation's f16 hi and lo parts), owned by the caller.
 int launch_f16w_matmul(b200_ctx* ctx, const __half* W, int N, int K, const float* x, int T, float* dst, int ldd,
-                       __half* split_scratch) {
+                       __half* split_scratch, int klass) {
+    // fast class, dense row counts (or forced with klass 2): the tcgen05 kernel
+    static const bool no_umma = getenv("B200_NO_UMMA") != nullptr;
+    if (klass != B200_CLASS_EXACT && (T >= 32 || klass == 2) && !no_umma && ctx->umma_scratch && f16w_umma_supported(W, N, K) &&
+        f16w_umma_scratch_bytes(T, K) <= ctx->umma_scratch_bytes)
+        return launch_f16w_matmul_umma(ctx, W, N, K, x, T, dst, ldd, ctx->umma_scratch, ctx->umma_scratch_bytes, ctx->err_flag);
     if (K % 32) {
         dim3 grid(ceil_div(N, 8), T);
         dense_matmul_f64_kernel<__half><<<grid, 256, 0, ctx->stream>>>(W, N, K, x, dst, ldd);

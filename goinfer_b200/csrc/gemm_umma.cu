@@ -23,8 +23,6 @@
 // (gridDim.z > 1) each split writes its own partial matrix and a second kernel adds the splits in order.
 //
 // Every mbarrier wait is bounded: on expiry the CTA raises an error flag, frees its TMEM and returns.
-#include <cuda.h>  // the CUtensorMap type and enums only: the encoder is looked up through the runtime, nothing links to the driver library
-
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
@@ -33,59 +31,11 @@
 #include <tuple>
 
 #include "common.cuh"
+#include "umma.cuh"
 
 namespace {
 
 constexpr int kStages = 3;   // A ring (and barriers); the B ring has 2 stages
-constexpr int kTileBytes = 128 * 128;  // 128 rows x 64 fp16
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-// Bounded wait; false when the barrier did not complete the phase in time (or the CTA is aborting). try_wait suspends
-// the thread for a hardware-bounded time instead of spinning: 17 warps share 4 schedulers, and warps that spin on a
-// barrier take issue slots from the warps they are waiting for.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag = nullptr) {
-    for (int i = 0; i < (1 << 20); i++) {
-        unsigned ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}\n"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        if (abort_flag && *abort_flag) return false;
-    }
-    return false;
-}
-
-// K-major, 128-byte swizzle, 8-row groups 1024 bytes apart (cute/arch/mma_sm100_desc.hpp SmemDescriptor: start>>4 [0,14),
-// LBO>>4 [16,30), SBO>>4 [32,46), version 1 at [46,48), layout type SWIZZLE_128B = 2 at [61,64)).
-__device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) {
-    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-
-// fp32 accumulate, f16 x f16, both K-major, M=128, N = 128 or 256 (InstrDescriptor: c_format [4,6), n>>3 [17,23), m>>4 [24,29)).
-__host__ __device__ constexpr unsigned idesc_for(unsigned n) { return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
-
-__device__ __forceinline__ void umma_f16(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
 
 __device__ __forceinline__ unsigned q4k_byte_u(int k, unsigned s0, unsigned s1, unsigned s2) {
     unsigned w = k < 4 ? s0 : (k < 8 ? s1 : s2);
@@ -129,25 +79,6 @@ constexpr int kProducerWarps = 8;
 constexpr int kProducers = kProducerWarps * 32;
 constexpr int kUmmaThreads = kProducers + 96;  // 8 producer warps + the MMA-issuing, activation-loading and weight-loading warps
 constexpr int kRawRow = 144;                   // one Q4_K super-block
-
-__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-// global -> shared bulk copy by the copy engine (no multicast); completion is counted in bytes on the mbarrier.
-// Both addresses 16-byte aligned, size a multiple of 16.
-__device__ __forceinline__ void bulk_g2s(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src),
-                 "r"(bytes), "r"(bar)
-                 : "memory");
-}
-
-// 2-D tiled copy by the copy engine (no multicast): box of the tensor map at (x, y) -> shared memory. x * element size
-// must be a multiple of 16 bytes.
-__device__ __forceinline__ void tensor_g2s_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
-                 "l"(map), "r"(x), "r"(y), "r"(bar)
-                 : "memory");
-}
 
 template <int NT>  // weight tiles of 128 rows per CTA: 2 when the grid still covers the SMs, else 1
 __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __grid_constant__ CUtensorMap wmap, int N, int nSB,
@@ -406,22 +337,13 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, size_t spli
 // depends only on its key, so the cache never goes stale. cuTensorMapEncodeTiled is reached through the runtime's
 // driver-entry-point lookup.
 const CUtensorMap* weight_map(b200_ctx* ctx, const uint8_t* W, int N, int nSB, int NT) {
-    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
     static std::mutex mu;
-    static encode_fn encode = nullptr;
     static std::map<std::tuple<const void*, int, int, int>, CUtensorMap*> cache;
     std::lock_guard<std::mutex> lock(mu);
+    const tensor_map_encode_fn encode = tensor_map_encoder();
     if (!encode) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
-            qres != cudaDriverEntryPointSuccess) {
-            ctx->err = "cuTensorMapEncodeTiled is not available from this driver";
-            return nullptr;
-        }
-        encode = reinterpret_cast<encode_fn>(fn);
+        ctx->err = "cuTensorMapEncodeTiled is not available from this driver";
+        return nullptr;
     }
     const auto key = std::make_tuple((const void*)W, N, nSB, NT);
     auto it = cache.find(key);

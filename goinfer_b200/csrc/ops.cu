@@ -29,8 +29,8 @@ struct UmmaScratch {
     size_t saved_n;
     int* saved_f;
     explicit UmmaScratch(b200_ctx* c) : ctx(c), saved_p(c->umma_scratch), saved_n(c->umma_scratch_bytes), saved_f(c->err_flag) {}
-    int ensure(Tmp& t, int M, int K, int N) {
-        const size_t need = q4k_umma_scratch_bytes(M, K, N);
+    int ensure(Tmp& t, int M, int K, int N) { return ensure_bytes(t, std::max(q4k_umma_scratch_bytes(M, K, N), f16w_umma_scratch_bytes(M, K))); }
+    int ensure_bytes(Tmp& t, size_t need) {
         if (ctx->umma_scratch && ctx->umma_scratch_bytes >= need && ctx->err_flag) return B200_OK;
         uint8_t* p;
         int* f;
@@ -133,6 +133,46 @@ int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, i
     ST_TRY(launch_q4k_matmul(ctx, dw, N, K, aq, M, dd, N, klass));
     D2H(ctx, dst, dd, (size_t)M * N * 4);
     SYNC(ctx);
+    return us.check();
+}
+
+int b200_op_f16_matmul(b200_ctx* ctx, const uint16_t* w, const float* a, int M, int K, int N, int klass, float* dst) {
+    if (M <= 0 || K <= 0 || N <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad matmul shape");
+    Tmp t;
+    __half *dw, *split; float *da, *dd;
+    TMP_GET(ctx, t, dw, (size_t)N * K); TMP_GET(ctx, t, da, (size_t)M * K); TMP_GET(ctx, t, dd, (size_t)M * N);
+    TMP_GET(ctx, t, split, (size_t)2 * M * K);
+    H2D(ctx, dw, w, (size_t)N * K * 2); H2D(ctx, da, a, (size_t)M * K * 4);
+    UmmaScratch us(ctx);
+    ST_TRY(us.ensure_bytes(t, f16w_umma_scratch_bytes(M, K)));
+    if (klass == 2 && !f16w_umma_supported(dw, N, K)) B200_FAIL(ctx, B200_DECLINED, "f16 tcgen05 matmul needs K %% 64 == 0 and N >= 256");
+    ST_TRY(launch_f16w_matmul(ctx, dw, N, K, da, M, dd, N, split, klass));
+    D2H(ctx, dst, dd, (size_t)M * N * 4);
+    SYNC(ctx);
+    return us.check();
+}
+
+int b200_bench_f16_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int warmup, int iters, float* ms_out) {
+    if (M <= 0 || K <= 0 || N <= 0 || iters <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad bench shape");
+    Tmp t;
+    __half *dw, *split; float *da, *dd;
+    TMP_GET(ctx, t, dw, (size_t)N * K); TMP_GET(ctx, t, da, (size_t)M * K); TMP_GET(ctx, t, dd, (size_t)M * N);
+    TMP_GET(ctx, t, split, (size_t)2 * M * K);
+    ST_TRY(launch_synth_f16(ctx, dw, (size_t)N * K, 0.02f, 23));
+    ST_TRY(launch_synth_normal_f32(ctx, da, (size_t)M * K, 1.f, 5));
+    UmmaScratch us(ctx);
+    ST_TRY(us.ensure_bytes(t, f16w_umma_scratch_bytes(M, K)));
+    cudaEvent_t e0, e1;
+    CUDA_TRY(ctx, cudaEventCreate(&e0)); CUDA_TRY(ctx, cudaEventCreate(&e1));
+    for (int i = 0; i < warmup; i++) ST_TRY(launch_f16w_matmul(ctx, dw, N, K, da, M, dd, N, split, klass));
+    CUDA_TRY(ctx, cudaEventRecord(e0, ctx->stream));
+    for (int i = 0; i < iters; i++) ST_TRY(launch_f16w_matmul(ctx, dw, N, K, da, M, dd, N, split, klass));
+    CUDA_TRY(ctx, cudaEventRecord(e1, ctx->stream));
+    SYNC(ctx);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    *ms_out = ms / iters;
     return us.check();
 }
 

@@ -2,6 +2,7 @@
 
   python -m goinfer_b200.microbench attention --rows 256 [--ctx-lo 128 --ctx-hi 8192 --heads 32 --kv-heads 8 --head-dim 128]
   python -m goinfer_b200.microbench q4k --rows 1 2 4 8 16 32 256 [--n 12288 --k 4096]
+  python -m goinfer_b200.microbench f16 --rows 256 [--n 151936 --k 4096]
   python -m goinfer_b200.microbench prefill --rows 2048 [--pos0 0 --heads 32 --kv-heads 8 --head-dim 128]
 
 Times are CUDA-event averages per launch after warm-up. Weight matrices are cycled through several copies and KV pools
@@ -33,6 +34,13 @@ def main():
     p.add_argument("--block-rows", type=int, default=16)
     p.add_argument("--iters", type=int, default=10)
     p.add_argument("--warmup", type=int, default=3)
+    h = sub.add_parser("f16")
+    h.add_argument("--rows", type=int, nargs="+", default=[256])
+    h.add_argument("--n", type=int, default=151936)
+    h.add_argument("--k", type=int, default=4096)
+    h.add_argument("--klass", type=int, default=0)
+    h.add_argument("--iters", type=int, default=10)
+    h.add_argument("--warmup", type=int, default=3)
     g = sub.add_parser("q4k")
     g.add_argument("--rows", type=int, nargs="+", default=[1, 2, 4, 8, 16, 32, 256])
     g.add_argument("--n", type=int, default=12288)
@@ -48,6 +56,12 @@ def main():
                                       args.block_rows, 2, args.warmup, args.iters)
         print(json.dumps({"kernel": "paged attention (split + combine)", "rows": args.rows, "ms_per_launch": ms,
                           "kv_bytes": kvb, "GBps": kvb / ms / 1e6}))
+    elif args.what == "f16":
+        for m in args.rows:
+            ms = ops.bench_f16_matmul(m, args.k, args.n, args.klass, args.warmup, args.iters)
+            wb = args.n * args.k * 2
+            print(json.dumps({"kernel": "f16-weight matmul", "rows": m, "n": args.n, "k": args.k, "ms_per_launch": ms,
+                              "weight_GBps": wb / ms / 1e6, "TMACps": m * args.n * args.k / ms / 1e9}))
     elif args.what == "prefill":
         ms = ops.bench_prefill_attention(args.rows, args.pos0, args.heads, args.kv_heads, args.head_dim, args.block_rows,
                                          args.warmup, args.iters)

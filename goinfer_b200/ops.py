@@ -94,6 +94,21 @@ class Ops:
                                                block_rows, klass, _p(out, C.c_float)))
         return out
 
+    def f16_matmul(self, w, a, klass=0):
+        """w f16 [N][K], a f32 [M][K] -> f32 [M][N]."""
+        w = np.ascontiguousarray(w, np.float16)
+        a = np.ascontiguousarray(a, np.float32)
+        (N, K), M = w.shape, a.shape[0]
+        out = np.empty((M, N), np.float32)
+        self._check(self.lib.b200_op_f16_matmul(self.ctx, w.view(np.uint16).ctypes.data_as(C.POINTER(C.c_uint16)), _p(a, C.c_float),
+                                                M, K, N, klass, _p(out, C.c_float)))
+        return out
+
+    def bench_f16_matmul(self, M, K, N, klass=0, warmup=3, iters=10) -> float:
+        ms = C.c_float(0)
+        self._check(self.lib.b200_bench_f16_matmul(self.ctx, M, K, N, klass, warmup, iters, C.byref(ms)))
+        return ms.value
+
     def prefill_attention(self, q, k, v, pos0, n_heads, n_kv_heads, head_dim, scale=0.0, softcap=0.0, block_rows=16):
         """q [rows][n_heads*head_dim], k/v [pos0+rows][n_kv_heads*head_dim]; row j sees keys 0..pos0+j."""
         q = np.ascontiguousarray(q, np.float32)

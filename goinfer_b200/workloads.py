@@ -1,0 +1,113 @@
+"""The benchmark configurations other than the headline one, as runnable workloads on one GPU.
+
+  python -m goinfer_b200.workloads decode --shape c4-moe --batch 128 --ctx-lo 256 --ctx-hi 4096 --seed 3
+  python -m goinfer_b200.workloads decode --shape c1-1.1b --batch 64 --ctx-lo 32 --ctx-hi 1280 --seed 1
+  python -m goinfer_b200.workloads serve  --shape c1-1.1b --sessions 512 --rate 40 --max-active 64 --seed 1
+
+`decode` pre-fills every slot's paged KV with synthetic rows at the drawn context lengths and times resident greedy
+decode steps (device loop, CUDA events); `serve` runs the continuous-batching driver of goinfer_b200.serve over a Poisson
+arrival trace. Weights are synthesized on the device (N(0, 0.02) quantized to Q4_K). Each prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import time
+
+import numpy as np
+
+
+def decode(shape: str, batch: int, ctx_lo: int, ctx_hi: int, seed: int, steps: int, warmup: int, device: int = 0,
+           n_layers: int = 0, breakdown: bool = True) -> dict:
+    from . import abi, synth
+    from .resident import Resident
+
+    s = synth.SHAPES[shape]
+    ctx = np.random.default_rng(seed).integers(ctx_lo, ctx_hi + 1, batch).astype(np.int32)
+    growth = steps + warmup + 8
+    cap = int(ctx.max()) + growth
+    blocks = 1 + int(np.ceil((ctx + growth) / 16).sum())
+    cfg = synth.make_cfg(s, batch, cap, 16, blocks, batch, abi.CLASS_AUTO, n_layers)
+    r = Resident(cfg, device=device)
+    synth.load_device_weights(r, s, seed=seed, n_layers=n_layers)
+    caps = r.finalize()
+    for i in range(batch):
+        r.SynthKV(i, int(ctx[i]), 0.5, 1000 + i)
+    lib, m, bctx = r.drv.lib, r.m, r.drv.ctx
+    p32 = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))
+    slot = np.arange(batch, dtype=np.int32)
+    pos = ctx.copy()
+    first = np.random.default_rng(seed + 1).integers(0, s.vocab, batch).astype(np.int32)
+    ms = C.c_float(0)
+
+    def check(st):
+        if st != abi.OK:
+            raise RuntimeError(f"b200 status {st}: {r.drv.last_error()}")
+
+    if warmup:
+        check(lib.b200_decode_loop_device(m, batch, p32(slot), p32(pos), p32(first), warmup, 1, None, C.byref(ms)))
+        pos += warmup
+    l0 = lib.b200_launch_count(bctx)
+    check(lib.b200_decode_loop_device(m, batch, p32(slot), p32(pos), p32(first), steps, 1, None, C.byref(ms)))
+    launches = int(lib.b200_launch_count(bctx) - l0)
+    dev_ms = float(ms.value)
+    keys = float(np.mean([(pos + 1 + i).sum() for i in range(steps)]))
+    pos += steps
+    L = n_layers or s.n_layers
+    out = {"workload": f"{shape}: B={batch} ragged decode, contexts U[{ctx_lo},{ctx_hi}] seed {seed}, paged fp16 KV 16-token blocks",
+           "layers": L, "steps": steps, "warmup": warmup, "ms_per_step": dev_ms / steps, "tok_s": batch * steps / (dev_ms * 1e-3),
+           "gpu_launches": launches, "kv_bytes_per_step": keys * 2 * s.n_kv_heads * s.head_dim * 2 * L,
+           "memory": {"weights_gb": caps.weight_bytes / 1e9, "kv_gb": caps.kv_bytes / 1e9, "scratch_gb": caps.scratch_bytes / 1e9}}
+    out["hbm_floor_ms"] = (out["kv_bytes_per_step"] + caps.weight_bytes) / 6540.5e9 * 1e3
+    if breakdown:
+        tag_ms = (C.c_double * 8)()
+        tag_n = (C.c_int64 * 8)()
+        lib.b200_profile(bctx, 0xFF)
+        check(lib.b200_decode_loop_device(m, batch, p32(slot), p32(pos), p32(first), 2, 1, None, C.byref(ms)))
+        lib.b200_profile_read(bctx, tag_ms, tag_n, 8)
+        lib.b200_profile(bctx, 0)
+        names = ("attn_split", "attn_combine", "q4k_matmul", "head_matmul", "norm_quant", "rope_kvstore", "swiglu_quant", "other")
+        out["breakdown_ms_per_step"] = {n: round(tag_ms[i] / 2, 4) for i, n in enumerate(names) if tag_n[i]}
+    r.Close()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="what", required=True)
+    d = sub.add_parser("decode")
+    d.add_argument("--shape", default="c4-moe")
+    d.add_argument("--batch", type=int, default=128)
+    d.add_argument("--ctx-lo", type=int, default=256)
+    d.add_argument("--ctx-hi", type=int, default=4096)
+    d.add_argument("--seed", type=int, default=3)
+    d.add_argument("--steps", type=int, default=8)
+    d.add_argument("--warmup", type=int, default=3)
+    d.add_argument("--layers", type=int, default=0)
+    v = sub.add_parser("serve")
+    v.add_argument("--shape", default="c1-1.1b")
+    v.add_argument("--sessions", type=int, default=512)
+    v.add_argument("--rate", type=float, default=40.0)
+    v.add_argument("--max-active", type=int, default=64)
+    v.add_argument("--seed", type=int, default=1)
+    v.add_argument("--prompt-lo", type=int, default=32)
+    v.add_argument("--prompt-hi", type=int, default=1024)
+    v.add_argument("--out-lo", type=int, default=16)
+    v.add_argument("--out-hi", type=int, default=256)
+    v.add_argument("--chunk", type=int, default=512)
+    v.add_argument("--layers", type=int, default=0)
+    v.add_argument("--time-scale", type=float, default=1.0, help="arrival times are divided by this (1 = real time)")
+    args = ap.parse_args()
+    if args.what == "decode":
+        print(json.dumps(decode(args.shape, args.batch, args.ctx_lo, args.ctx_hi, args.seed, args.steps, args.warmup,
+                                n_layers=args.layers)))
+    else:
+        from .serve import run_poisson
+        print(json.dumps(run_poisson(args.shape, args.sessions, args.rate, args.max_active, args.seed, args.prompt_lo,
+                                     args.prompt_hi, args.out_lo, args.out_hi, args.chunk, n_layers=args.layers,
+                                     time_scale=args.time_scale)))
+
+
+if __name__ == "__main__":
+    main()

@@ -229,6 +229,9 @@ int b200_op_q4k_dequant(b200_ctx* ctx, const uint8_t* w, int rows, int cols, flo
 int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, int K, int N, int klass,
                        float* dst);
 /* fp32 -> Q4_K with the library's quantizer; out is rows*cols/256*144 bytes. */
+/* dst[M][N] = a[M][K] . w[N][K]^T over f16 weights (the LM head's kind, decoder/forwardn.go:800-831): klass 0 picks by
+ * row count as a fast-class step does, 1 the accurate small-batch kernel, 2 forces the tcgen05 kernel. */
+int b200_op_f16_matmul(b200_ctx* ctx, const uint16_t* w, const float* a, int M, int K, int N, int klass, float* dst);
 int b200_op_q4k_quantize(b200_ctx* ctx, const float* w, int rows, int cols, uint8_t* out);
 /* RMSNorm rows (decoder/rmsnorm.go:29-92). */
 int b200_op_rmsnorm(b200_ctx* ctx, const float* x, const float* w, int rows, int dim, float eps, float* out);
@@ -256,6 +259,7 @@ int b200_op_prefill_attention(b200_ctx* ctx, const float* q, const float* k, con
  * `warmup`, of the kernel the step would pick (or `klass`), on synthetic resident data. */
 int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_weight_copies,
                           int warmup, int iters, float* ms_out);
+int b200_bench_f16_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int warmup, int iters, float* ms_out);
 int b200_bench_attention(b200_ctx* ctx, int rows, int ctx_lo, int ctx_hi, int n_heads, int n_kv_heads,
                          int head_dim, int block_rows, uint64_t seed, int warmup, int iters,
                          float* ms_out, double* kv_bytes_out);

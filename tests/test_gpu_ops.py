@@ -143,6 +143,23 @@ def test_rmsnorm(ops, oracle_lib):
     np.testing.assert_allclose(b, a, rtol=3e-7, atol=0)   # 1 ulp: the f64 sum is folded in another order
 
 
+@pytest.mark.parametrize("M,N,K", [(32, 256, 64), (33, 300, 128), (128, 512, 256), (130, 1000, 512), (256, 777, 2048), (5, 256, 64)])
+def test_f16_weight_matmul_tcgen05(ops, M, N, K):
+    """The fast class's LM-head kernel: f16 weights, f32 activations split into f16 hi + lo parts, fp32 accumulate on the
+    tensor cores. Against the f64 product of the same f16 weights: fp32-accumulation accuracy (a K-term fp32 sum)."""
+    rng = np.random.default_rng(M + N + K)
+    w = rng.normal(0, 0.02, (N, K)).astype(np.float16)
+    a = rng.normal(0, 1, (M, K)).astype(np.float32)
+    a[0, :] = 0
+    a[1, 3] = 300.0
+    ref = a.astype(np.float64) @ w.astype(np.float64).T
+    got = ops.f16_matmul(w, a, klass=2)
+    scale = np.abs(ref).max()
+    assert np.abs(got - ref).max() <= 2e-6 * scale * np.sqrt(K), np.abs(got - ref).max() / scale
+    small = ops.f16_matmul(w, a, klass=1)                      # the accurate small-batch kernel agrees to the same level
+    assert np.abs(small - ref).max() <= 2e-6 * scale * np.sqrt(K)
+
+
 def test_route_indices_bit_exact(ops, oracle_lib):
     rng = np.random.default_rng(6)
     for nE, k, norm in ((8, 2, True), (128, 8, True), (128, 8, False), (64, 6, True)):
