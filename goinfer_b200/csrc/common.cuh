@@ -30,6 +30,9 @@ struct b200_ctx {
     void* umma_scratch = nullptr;
     size_t umma_scratch_bytes = 0;
     int* err_flag = nullptr;
+    // tensor parallel: the NCCL communicator b200_tp_init made for this context (null on a single GPU)
+    void* tp_comm = nullptr;
+    int tp_rank = 0, tp_size = 1;
     // per-launch CUDA-event timing of the tagged kernel classes (off unless b200_profile sets a mask)
     unsigned prof_mask = 0;
     std::vector<ProfRec> prof_recs;
@@ -163,6 +166,10 @@ int attn_split_keys();
 int launch_paged_attention(b200_ctx*, const float* q, int ldq, int T, int nH, int nKV, int hd, float scale, float softcap,
                            const int32_t* row_slot, const int32_t* row_pos, int max_keys, KVView kv, AttnScratch sc,
                            float* out, ActQ aq);
+
+// tp.cu: collectives over the context's communicator, on its stream
+int tp_all_reduce_sum(b200_ctx*, float* buf, size_t n);
+int tp_all_gather_columns(b200_ctx*, const float* local, int rows, int w, float* gathered, float* full);
 
 // attention_prefill.cu: causal attention for a run of rows of one slot at consecutive positions pos0.. (fast class)
 bool prefill_attention_supported(int nH, int nKV, int hd, int block_rows);

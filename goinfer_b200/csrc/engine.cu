@@ -187,6 +187,7 @@ struct b200_model {
     size_t umma_bytes = 0;
     int* err_flag = nullptr;       // raised by a bounded device-side wait that gave up
     float* exact_scores = nullptr;  // exact class: [MR*nH][ctx_cap]
+    float *logits_local = nullptr, *logits_gather = nullptr;  // tensor parallel: [MLR][V/t] and the gathered [t][MLR][V/t]
     // the step's leading prefill run (rows of one slot at consecutive positions), 0 rows when there is none;
     // pf_tail_keys = the longest key range among the rows after it
     int pf_rows = 0, pf_slot = 0, pf_pos0 = 0, pf_tail_keys = 1;
@@ -253,7 +254,8 @@ DevMat* tensor_slot(b200_model* m, int which, int layer, int expert, float*** ve
 bool expected_shape(const b200_model_cfg& c, int which, int* rows, int* cols) {
     const int qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim;
     switch (which) {
-        case B200_T_EMBED: case B200_T_LM_HEAD: *rows = c.vocab; *cols = c.hidden; return true;
+        case B200_T_EMBED: *rows = c.vocab; *cols = c.hidden; return true;
+        case B200_T_LM_HEAD: *rows = c.tp_size > 1 ? c.vocab / c.tp_size : c.vocab; *cols = c.hidden; return true;  // a rank holds its vocabulary slice
         case B200_T_WQ: *rows = qd; *cols = c.hidden; return true;
         case B200_T_WK: case B200_T_WV: *rows = kvd; *cols = c.hidden; return true;
         case B200_T_WO: *rows = c.hidden; *cols = qd; return true;
@@ -318,6 +320,17 @@ int matmul(b200_model* m, const DevMat& W, const float* xf, ActQ xq, int T, floa
     return launch_f32w_matmul(ctx, (const float*)W.p, W.rows, W.cols, xf, T, dst, ldd);
 }
 
+// logits[rn][V] of `rn` already-normed rows: the LM head, whose vocabulary slices a tensor-parallel group gathers
+int head_logits(b200_model* m, int rn) {
+    b200_ctx* ctx = m->ctx;
+    const b200_model_cfg& c = m->c;
+    const int V = c.vocab;
+    if (c.tp_size <= 1) return matmul(m, m->head, m->hn, m->aq_h, rn, m->logits, V);
+    const int Vl = V / c.tp_size;
+    ST_TRY(matmul(m, m->head, m->hn, m->aq_h, rn, m->logits_local, Vl));
+    return tp_all_gather_columns(ctx, m->logits_local, rn, Vl, m->logits_gather, m->logits);
+}
+
 constexpr int kPrefillRunMin = 16;  // shorter runs stay with the flash-decode kernel, a row each
 
 int run_layers(b200_model* m, int T, int max_keys) {
@@ -364,6 +377,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
             }
         }
         ST_TRY(matmul(m, L.wo, m->ctxb, m->aq_ctx, T, m->att, H));
+        if (c.tp_size > 1) ST_TRY(tp_all_reduce_sum(ctx, m->att, (size_t)T * H));  // o is split by input columns: partial sums
         if (c.n_experts == 0) {
             const bool g_q = L.gu.kind == B200_K_Q4K, d_q = L.down.kind == B200_K_Q4K;
             ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, m->att, L.ffn_norm, T, H, c.rms_eps, g_q ? nullptr : m->normed,
@@ -371,6 +385,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
             ST_TRY(matmul(m, L.gu, m->normed, m->aq_h, T, m->gu, 2 * c.ffn));
             ST_TRY(launch_swiglu_quant(ctx, m->gu, T, c.ffn, 2 * c.ffn, d_q ? nullptr : m->mid, d_q ? m->aq_mid : none));
             ST_TRY(matmul(m, L.down, m->mid, m->aq_mid, T, m->att, H));
+            if (c.tp_size > 1) ST_TRY(tp_all_reduce_sum(ctx, m->att, (size_t)T * H));
         } else {
             // routed experts (decoder/mlp.go:36-120): f32 router on the f32 normed row, top-k, grouped expert GEMMs,
             // fold in routing-rank order
@@ -425,6 +440,7 @@ int b200_open(int device_ordinal, void* stream, b200_ctx** out) {
 
 void b200_close(b200_ctx* ctx) {
     if (!ctx) return;
+    b200_tp_destroy(ctx);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -438,7 +454,14 @@ int b200_model_create(b200_ctx* ctx, const b200_model_cfg* cfg, b200_model** out
         c.n_heads % c.n_kv_heads || c.n_slots <= 0 || c.ctx_cap <= 0 || c.kv_block_rows <= 0 || c.kv_pool_blocks < 2)
         B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad model configuration");
     if (c.kv_dtype != 0) B200_FAIL(ctx, B200_DECLINED, "only the fp16 paged KV cache is built");
-    if (c.tp_size > 1) B200_FAIL(ctx, B200_DECLINED, "tensor parallel shards are built by the multi-GPU driver, not this entry point");
+    if (c.tp_size > 1) {
+        // a tensor-parallel shard: the configuration carries this rank's share of heads, kv heads and FFN columns and the
+        // whole vocabulary; the context must hold the communicator of that size (b200_tp_init)
+        if (!ctx->tp_comm || ctx->tp_size != c.tp_size || ctx->tp_rank != c.tp_rank)
+            B200_FAIL(ctx, B200_BAD_ARGUMENT, "tensor-parallel rank %d of %d needs b200_tp_init with the same rank and size first", c.tp_rank, c.tp_size);
+        if (c.n_experts > 0) B200_FAIL(ctx, B200_DECLINED, "tensor parallel is built for dense models");
+        if (c.vocab % c.tp_size) B200_FAIL(ctx, B200_DECLINED, "the vocabulary does not divide over %d ranks", c.tp_size);
+    }
     if (c.head_dim > 256) B200_FAIL(ctx, B200_DECLINED, "head_dim above 256");
     if (c.n_experts > 512) B200_FAIL(ctx, B200_DECLINED, "more than 512 experts");
     auto* m = new b200_model();
@@ -621,6 +644,10 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
     CUDA_TRY(ctx, cudaMemsetAsync(m->err_flag, 0, 4, ctx->stream));
     ST_TRY(m->dalloc((void**)&m->hn, (size_t)MLR * H * 4, sb));
     ST_TRY(m->dalloc((void**)&m->logits, (size_t)MLR * c.vocab * 4, sb));
+    if (c.tp_size > 1) {
+        ST_TRY(m->dalloc((void**)&m->logits_local, (size_t)MLR * (c.vocab / c.tp_size) * 4, sb));
+        ST_TRY(m->dalloc((void**)&m->logits_gather, (size_t)MLR * c.vocab * 4, sb));
+    }
     ST_TRY(m->dalloc((void**)&m->split, (size_t)2 * MLR * H * 2, sb));
     CUDA_TRY(ctx, cudaMallocHost((void**)&m->p_desc, (size_t)(2 + 3 * MR) * 4 + (size_t)MR * (4 + 4 + 4 + sizeof(b200_draw))));
     CUDA_TRY(ctx, cudaMallocHost((void**)&m->p_ids, (size_t)(MR + 1) * 4));
@@ -909,7 +936,7 @@ int b200_step_ragged(b200_model* m, int n_seqs, const int32_t* slot, const int32
         const bool hq = m->head.kind == B200_K_Q4K;
         ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, nullptr, m->final_norm, rn, H, c.rms_eps, hq ? nullptr : m->hn,
                                         hq ? m->aq_h : ActQ{}, m->d_head_rows + j0));
-        ST_TRY(matmul(m, m->head, m->hn, m->aq_h, rn, m->logits, V));
+        ST_TRY(head_logits(m, rn));
         if (c.final_softcap > 0.f) ST_TRY(launch_softcap(ctx, m->logits, (size_t)rn * V, c.final_softcap));
         if (any_mask) ST_TRY(launch_mask_logits(ctx, m->logits, rn, V, m->d_row_mask + j0, m->d_masks));
         const int out_here = std::max(0, std::min(n_out, j0 + rn) - j0);
@@ -1005,7 +1032,7 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
         const bool hq = m->head.kind == B200_K_Q4K;
         ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, nullptr, m->final_norm, S, H, c.rms_eps, hq ? nullptr : m->hn,
                                         hq ? m->aq_h : ActQ{}, m->d_head_rows));
-        ST_TRY(matmul(m, m->head, m->hn, m->aq_h, S, m->logits, V));
+        ST_TRY(head_logits(m, S));
         if (c.final_softcap > 0.f) ST_TRY(launch_softcap(ctx, m->logits, (size_t)S * V, c.final_softcap));
         ST_TRY(launch_draw(ctx, m->logits, S, V, m->d_draws, m->d_ids, nullptr));
         advance_kernel<<<ceil_div(S, 256), 256, 0, ctx->stream>>>(m->d_tokens, m->d_ids, m->d_pos, S, advance_pos, ids_out ? m->d_ids_log : nullptr);

@@ -36,6 +36,7 @@ SHAPES: Dict[str, Shape] = {
     "c5-70b": Shape("c5-70b", 8192, 80, 64, 8, 128, 28672, 128256, 1e-5, 5e5),
     "tiny-dense": Shape("tiny-dense", 256, 2, 4, 2, 64, 512, 512, 1e-5, 1e4),
     "tiny-qknorm": Shape("tiny-qknorm", 512, 2, 4, 2, 128, 768, 640, 1e-6, 1e6, qk_norm=True),
+    "tiny-tp": Shape("tiny-tp", 512, 2, 8, 2, 64, 1024, 512, 1e-5, 1e4),   # splits over 2 ranks in whole super-blocks
     "tiny-moe": Shape("tiny-moe", 256, 2, 4, 2, 128, 0, 512, 1e-6, 1e6, qk_norm=True, n_experts=8, top_k=2, moe_ffn=256),
 }
 
@@ -123,13 +124,14 @@ def tensor_plan(s: Shape, n_layers: int = 0):
             yield abi.T_DOWN, l, -1, abi.K_Q4K, H, s.ffn
 
 
-def load_device_weights(r, s: Shape, seed: int, n_layers: int = 0, sigma: float = 0.02):
+def load_device_weights(r, s: Shape, seed: int, n_layers: int = 0, sigma: float = 0.02, head_rows: int = 0):
     """Synthesizes every tensor on the device (no host copies): seeded N(0, sigma), matrices quantized to
     Q4_K by the device quantizer, f16 embedding and head, unit norms with small seeded jitter."""
     H = s.hidden
     k = 0
     r.synth(abi.T_EMBED, abi.K_F16, s.vocab, H, sigma, seed * 1000003 + k); k += 1
-    r.synth(abi.T_LM_HEAD, abi.K_F16, s.vocab, H, sigma, seed * 1000003 + k); k += 1
+    # head_rows: a tensor-parallel rank holds a vocabulary slice of the head
+    r.synth(abi.T_LM_HEAD, abi.K_F16, head_rows or s.vocab, H, sigma, seed * 1000003 + k); k += 1
     rng = np.random.default_rng(seed)
     r.upload(abi.T_FINAL_NORM, (1 + rng.normal(0, 0.05, H)).astype(np.float32))
     for l in range(n_layers or s.n_layers):

@@ -132,6 +132,18 @@ const char* b200_last_error(b200_ctx* ctx);
 /* Counts kernels launched by this library on the context since open (bench accounting). */
 int64_t b200_launch_count(b200_ctx* ctx);
 
+/* Tensor parallel (the 70B-class configuration: q/k/v/gate/up split by output rows, o/down by input columns, the KV
+ * cache by kv head, an all-reduce of the partial [rows][hidden] products after the o and down projections, the LM head
+ * split by vocabulary slice and gathered). No counterpart in the reference's single-GPU CUDA backend. One process per GPU:
+ * rank 0 makes the id (b200_tp_unique_id, 128 bytes), the host carries it to the other ranks, every rank calls
+ * b200_tp_init on its context, then creates its model with tp_rank / tp_size set and its own share of n_heads,
+ * n_kv_heads and ffn in the configuration (vocab stays whole; the LM head tensor is this rank's [vocab/tp_size][hidden]
+ * slice). NCCL is opened with dlopen at the first of these calls. Every rank must make the same step calls in the same
+ * order. */
+int b200_tp_unique_id(b200_ctx* ctx, void* id_out, size_t bytes);
+int b200_tp_init(b200_ctx* ctx, const void* id, size_t bytes, int rank, int size);
+int b200_tp_destroy(b200_ctx* ctx);
+
 /* ---- model build: ResidencyBackend.BuildResident (decoder/residency.go:208-210) -------------------- */
 int b200_model_create(b200_ctx* ctx, const b200_model_cfg* cfg, b200_model** out);
 /* Copies one tensor to the device. `layer` is -1 for model-level tensors; `expert` is -1 unless `which`

@@ -1,0 +1,70 @@
+"""One rank of the tensor-parallel GPU check (launched by test_gpu_tp.py through torch.distributed.run, one process per
+GPU): a small dense model split over the ranks must give, on every rank, the same logits bit for bit, within the logit
+tolerance of the same model on one GPU and of the CPU oracle, and the same greedy ids."""
+import os
+import sys
+
+import numpy as np
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def main():
+    import torch.distributed as dist
+    from goinfer_b200 import abi, synth, tp
+    from goinfer_b200.resident import BatchDraw, BatchSeq, Resident
+    from helpers import close_logits
+
+    dist.init_process_group("gloo")
+    rank, world, dev = dist.get_rank(), dist.get_world_size(), int(os.environ.get("LOCAL_RANK", "0"))
+    s = synth.SHAPES["tiny-tp"]
+    sl = tp.local_shape(s, world)
+    tensors = list(synth.host_weights(s, seed=3))
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, s.vocab, n).tolist() for n in (37, 9)]
+    for klass in (abi.CLASS_AUTO, abi.CLASS_EXACT):
+        r = tp.build_rank(dist, s, synth.make_cfg(sl, 4, 128, 16, 0, 96, klass), dev, tensors)
+        outs = [r.PrefillLast(None, 0, i, tokens=p) for i, p in enumerate(prompts)]
+        ids = []
+        toks = [int(np.argmax(o)) for o in outs]
+        first = list(toks)
+        for step in range(6):
+            b = r.StepBatch([BatchSeq(i, len(prompts[i]) + step, None, toks[i], BatchDraw(Greedy=True)) for i in range(2)])
+            toks = [o.ID for o in b]
+            ids.append(toks)
+        last = r.StepBatch([BatchSeq(i, len(prompts[i]) + 6, None, toks[i]) for i in range(2)])
+        outs += [o.Logits for o in last]
+        # every rank holds the same bits
+        import torch
+        mine = torch.from_numpy(np.concatenate(outs).view(np.int32).copy())
+        ref = mine.clone()
+        dist.broadcast(ref, src=0)
+        assert bool((mine == ref).all()), "ranks disagree on the logits bits"
+        if rank == 0:
+            from oracle.binding import OracleResident
+            full = Resident(synth.make_cfg(s, 4, 128, 16, 0, 96, klass), device=dev)
+            orc = OracleResident(synth.make_cfg(s, 4, 128, 16, 0, 96, klass))
+            synth.load_host_weights([full, orc], s, seed=3)
+            full.finalize(); orc.finalize()
+            for res in (full, orc):
+                want = [res.PrefillLast(None, 0, i, tokens=p) for i, p in enumerate(prompts)]
+                wid = []
+                for step in range(6):
+                    b = res.StepBatch([BatchSeq(i, len(prompts[i]) + step, None, ids[step - 1][i] if step else first[i], BatchDraw(Greedy=True)) for i in range(2)])
+                    wid.append([o.ID for o in b])
+                for x, y in zip(outs[:2], want):
+                    ok, err = close_logits(x, y)
+                    assert ok, (klass, err)
+                agree = sum(a == b for sa, sb in zip(ids, wid) for a, b in zip(sa, sb))
+                assert agree >= 11, (klass, ids, wid)     # fed the same tokens, the greedy ids agree (a near-tie may flip one)
+            full.Close()
+        r.Close()
+        dist.barrier()
+    if rank == 0:
+        print("TP_OK", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
