@@ -67,10 +67,33 @@ __global__ void __launch_bounds__(256) add_rmsnorm_quant_kernel(float* __restric
     const int r = gather_rows ? gather_rows[j] : j;
     float* hr = h + (size_t)r * H;
     double ss = 0;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    // eight elements a pass: their loads are all in flight before the first dependent add (the sum keeps its order)
+    const float* dr = delta ? delta + (size_t)r * H : nullptr;
+    int i = threadIdx.x;
+    for (; i + 7 * (int)blockDim.x < H; i += 8 * blockDim.x) {
+        float x[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) x[u] = hr[i + u * blockDim.x];
+        if (dr) {
+            float d[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) d[u] = dr[i + u * blockDim.x];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                x[u] = __fadd_rn(x[u], d[u]);
+                hr[i + u * blockDim.x] = x[u];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            row[i + u * blockDim.x] = x[u];
+            ss += (double)x[u] * (double)x[u];
+        }
+    }
+    for (; i < H; i += blockDim.x) {
         float x = hr[i];
-        if (delta) {
-            x = __fadd_rn(x, delta[(size_t)r * H + i]);
+        if (dr) {
+            x = __fadd_rn(x, dr[i]);
             hr[i] = x;
         }
         row[i] = x;
@@ -84,7 +107,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_quant_kernel(float* __restric
     for (int k = 0; k < 8; k++) tot += red[k];
     const float inv = (float)(1.0 / sqrt(tot / (double)H + (double)eps));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nG = H >> 5;
-    for (int g = warp; g < nG; g += 8) {
+#pragma unroll 4
+    for (int g = warp; g < nG; g += 8) {  // unrolled: the groups' shuffle and divide chains interleave
         int i = g * 32 + lane;
         float y = __fmul_rn(__fmul_rn(row[i], inv), w[i]);
         if (normed) normed[(size_t)j * H + i] = y;
