@@ -167,6 +167,12 @@ int launch_paged_attention(b200_ctx*, const float* q, int ldq, int T, int nH, in
                            const int32_t* row_slot, const int32_t* row_pos, int max_keys, KVView kv, AttnScratch sc,
                            float* out, ActQ aq);
 
+// gemm_umma.cu: the cached tensor map (a CUtensorMap, opaque here) of a Q4_K matrix seen as bytes [N][nSB*144], box of one
+// super-block x box_rows rows; null (and ctx->err) when the driver cannot encode it
+const struct CUtensorMap_st* q4k_weight_map(b200_ctx*, const uint8_t* W, int N, int nSB, int box_rows);
+// gemm_stream.cu: Q4_K x int8 for 4..32 rows, weights streamed through a TMA ring (exact arithmetic; split-K when splits > 1)
+int launch_q4k_matmul_stream(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, bool allow_split);
+
 // tp.cu: collectives over the context's communicator, on its stream
 int tp_all_reduce_sum(b200_ctx*, float* buf, size_t n);
 int tp_all_gather_columns(b200_ctx*, const float* local, int rows, int w, float* gathered, float* full);

@@ -333,10 +333,12 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, size_t spli
     dst[(size_t)t * ldd + n] = s;
 }
 
-// The tensor map of a weight matrix seen as bytes, [N rows][nSB * 144], with a box of one super-block x 128*NT rows. A map
+}  // namespace
+
+// The tensor map of a weight matrix seen as bytes, [N rows][nSB * 144], with a box of one super-block x box_rows rows. A map
 // depends only on its key, so the cache never goes stale. cuTensorMapEncodeTiled is reached through the runtime's
 // driver-entry-point lookup.
-const CUtensorMap* weight_map(b200_ctx* ctx, const uint8_t* W, int N, int nSB, int NT) {
+const CUtensorMap* q4k_weight_map(b200_ctx* ctx, const uint8_t* W, int N, int nSB, int box_rows) {
     static std::mutex mu;
     static std::map<std::tuple<const void*, int, int, int>, CUtensorMap*> cache;
     std::lock_guard<std::mutex> lock(mu);
@@ -345,13 +347,13 @@ const CUtensorMap* weight_map(b200_ctx* ctx, const uint8_t* W, int N, int nSB, i
         ctx->err = "cuTensorMapEncodeTiled is not available from this driver";
         return nullptr;
     }
-    const auto key = std::make_tuple((const void*)W, N, nSB, NT);
+    const auto key = std::make_tuple((const void*)W, N, nSB, box_rows);
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
     CUtensorMap* m = new CUtensorMap;
-    const cuuint64_t dims[2] = {(cuuint64_t)nSB * kRawRow, (cuuint64_t)N};
-    const cuuint64_t strides[1] = {(cuuint64_t)nSB * kRawRow};
-    const cuuint32_t box[2] = {(cuuint32_t)kRawRow, (cuuint32_t)(128 * NT)};
+    const cuuint64_t dims[2] = {(cuuint64_t)nSB * 144, (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)nSB * 144};
+    const cuuint32_t box[2] = {(cuuint32_t)144, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(W), dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -364,8 +366,6 @@ const CUtensorMap* weight_map(b200_ctx* ctx, const uint8_t* W, int N, int nSB, i
     cache[key] = m;
     return m;
 }
-
-}  // namespace
 
 size_t q4k_umma_scratch_bytes(int max_rows, int max_k, int max_n) {
     // fp16 activations + split-K partials (up to 4 splits)
@@ -400,7 +400,7 @@ int launch_q4k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ a
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_set = true;
     }
-    const CUtensorMap* wmap = weight_map(ctx, W, N, nSB, NT);
+    const CUtensorMap* wmap = q4k_weight_map(ctx, W, N, nSB, 128 * NT);
     if (!wmap) return B200_CUDA_ERROR;
     dim3 grid(n_tiles, t_tiles, splits);
     float* out = splits > 1 ? part : dst;

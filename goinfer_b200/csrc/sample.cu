@@ -6,6 +6,8 @@
 //             (prob desc, id asc), cut p < minP*p0, drop zeros, renormalise), :442-458 drawFiltered (first
 //             prefix whose cumulative probability exceeds the caller's uniform u)
 //   route     decoder/mlp.go:130-184 routeExperts (softmax path), :370-411 softmaxF32, :415-440 topK
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace {
@@ -214,12 +216,16 @@ __global__ void __launch_bounds__(32) route_kernel(const float* __restrict__ log
 // One block; thread e owns expert e. offs[nE+1]; rows_tok[s] = token row of sorted slot s; slot_of[a] = sorted
 // slot of assignment a = row*k + rank (-1 when the rank is empty).
 __global__ void group_experts_kernel(const int32_t* __restrict__ idx, int n_assign, int k, int nE, int32_t* __restrict__ offs,
-                                     int32_t* __restrict__ rows_tok, int32_t* __restrict__ slot_of) {
-    extern __shared__ int s_cnt[];
+                                     int32_t* __restrict__ rows_tok, int32_t* __restrict__ slot_of, int n_staged) {
+    extern __shared__ int s_cnt[];     // nE counts, then the first n_staged assignments (all of them when they fit)
+    int* s_idx = s_cnt + nE;
     const int e = threadIdx.x;
+    for (int a = e; a < n_staged; a += blockDim.x) s_idx[a] = idx[a];
+    __syncthreads();
+    auto at = [&](int a) { return a < n_staged ? s_idx[a] : idx[a]; };
     int c = 0;
     if (e < nE)
-        for (int a = 0; a < n_assign; a++) c += idx[a] == e;
+        for (int a = 0; a < n_assign; a++) c += at(a) == e;
     if (e < nE) s_cnt[e] = c;
     __syncthreads();
     if (e == 0) {
@@ -231,10 +237,10 @@ __global__ void group_experts_kernel(const int32_t* __restrict__ idx, int n_assi
     if (e < nE) {
         int s = offs[e];
         for (int a = 0; a < n_assign; a++)
-            if (idx[a] == e) { rows_tok[s] = a / k; slot_of[a] = s; s++; }
+            if (at(a) == e) { rows_tok[s] = a / k; slot_of[a] = s; s++; }
     }
     for (int a = e; a < n_assign; a += blockDim.x)
-        if (idx[a] < 0) slot_of[a] = -1;
+        if (at(a) < 0) slot_of[a] = -1;
 }
 
 }  // namespace
@@ -260,8 +266,10 @@ int launch_route(b200_ctx* ctx, const float* logits, int T, int nE, int k, int n
 
 int launch_group_experts(b200_ctx* ctx, const int32_t* idx, int T, int k, int nE, int32_t* offs, int32_t* rows) {
     // rows holds rows_tok[T*k] followed by slot_of[T*k]
-    group_experts_kernel<<<1, max(32, ((nE + 31) / 32) * 32), nE * sizeof(int), ctx->stream>>>(idx, T * k, k, nE, offs, rows,
-                                                                                            rows + (size_t)T * k);
+    // the assignments are scanned once per expert: from shared memory as far as they fit (40 KB), the rest from global
+    const int n_staged = std::min(T * k, 10240);
+    group_experts_kernel<<<1, max(32, ((nE + 31) / 32) * 32), (nE + n_staged) * sizeof(int), ctx->stream>>>(
+        idx, T * k, k, nE, offs, rows, rows + (size_t)T * k, n_staged);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }
