@@ -99,6 +99,24 @@ def test_q4k_matmul_fast_class_tcgen05(ops, oracle_lib, M, N, K):
     assert rel <= 2.5e-3, rel
 
 
+@pytest.mark.parametrize("M", [4, 7, 8, 9, 16, 17, 31, 32])
+def test_q4k_matmul_streaming_kernel(ops, oracle_lib, M):
+    """The fast class's kernel for 4..32 rows streams weights and activation rows through a TMA ring and keeps the exact
+    class's arithmetic: without a K split (wide matrices) its bits are the oracle's; with one (narrow matrix, long K) the
+    partial chains are added in split order and the result stays within f32 rounding of it."""
+    rng = np.random.default_rng(40 + M)
+    for N, K, split in ((448 * 64 + 20, 512, False), (100, 4096, True)):
+        raw = q4k.quantize(rng.normal(0, 0.02, (N, K)).astype(np.float32))
+        a = rng.normal(0, 1, (M, K)).astype(np.float32)
+        a[M - 1, 32:64] = 0
+        want = oracle_lib.op_q4k_matmul(raw, a, N)
+        got = ops.q4k_matmul(raw, a, N, klass=0)
+        if not split:
+            assert np.array_equal(want.view(np.uint32), got.view(np.uint32))
+        else:
+            assert np.abs(got - want).max() <= 2e-6 * np.abs(want).max()
+
+
 def test_q4k_matmul_saturated_and_random_bytes(ops, oracle_lib):
     rng = np.random.default_rng(3)
     N, K = 32, 512
