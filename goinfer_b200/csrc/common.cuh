@@ -172,6 +172,11 @@ int launch_paged_attention(b200_ctx*, const float* q, int ldq, int T, int nH, in
 const struct CUtensorMap_st* q4k_weight_map(b200_ctx*, const uint8_t* W, int N, int nSB, int box_rows);
 // gemm_stream.cu: Q4_K x int8 for 4..32 rows, weights streamed through a TMA ring (exact arithmetic; split-K when splits > 1)
 int launch_q4k_matmul_stream(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, bool allow_split);
+// the same kernel over experts stacked in one buffer ([n_experts*N][K]) and expert-sorted activation rows
+bool q4k_stream_grouped_supported(const uint8_t* W_all, int N, int K);
+int launch_q4k_matmul_stream_grouped(b200_ctx*, const uint8_t* W_all, int n_experts, int N, int K, ActQ aq, const int32_t* offs,
+                                     int n_rows, int max_rows_per_expert, float* dst, int ldd);
+int launch_gather_act_rows(b200_ctx*, ActQ src, const int32_t* rows_tok, int n_rows, int K, ActQ dst);
 
 // tp.cu: collectives over the context's communicator, on its stream
 int tp_all_reduce_sum(b200_ctx*, float* buf, size_t n);

@@ -40,6 +40,7 @@ struct LayerW {
     DevMat qkv, gu;                         // fused at finalize
     std::vector<DevMat> egu;                // per expert gate|up
     const uint8_t** d_egu_ptrs = nullptr;   // device arrays of expert matrix pointers
+    uint8_t *egu_all = nullptr, *ed_all = nullptr;  // Q4_K experts stacked: [n_experts][2F][.] and [n_experts][H][.]
     const uint8_t** d_ed_ptrs = nullptr;
     double* inv_freq = nullptr;             // device, [rot_half]
     std::vector<double> h_inv_freq;
@@ -195,6 +196,7 @@ struct b200_model {
     float *rl = nullptr, *rw = nullptr, *egu_out = nullptr, *eo = nullptr, *emid = nullptr;
     int32_t *ridx = nullptr, *eoffs = nullptr, *erows = nullptr;
     ActQ aq_emid;
+    ActQ aq_sorted;  // routed experts: the layer's activation rows in expert-sorted order ([max_rows*top_k][hidden])
     // pinned host staging
     int32_t* p_desc = nullptr;
     float* p_logits = nullptr;
@@ -398,9 +400,20 @@ int run_layers(b200_model* m, int T, int max_keys) {
             const int32_t* rows_tok = m->erows;
             const int32_t* slot_of = m->erows + (size_t)T * kk;
             if (L.egu[0].kind == B200_K_Q4K) {
-                ST_TRY(launch_q4k_matmul_grouped(ctx, L.d_egu_ptrs, nE, 2 * F, H, m->aq_h, m->eoffs, rows_tok, T, m->egu_out, 2 * F));
-                ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, nullptr, m->aq_emid));
-                ST_TRY(launch_q4k_matmul_grouped(ctx, L.d_ed_ptrs, nE, H, F, m->aq_emid, m->eoffs, nullptr, T, m->eo, H));
+                static const bool no_stream = getenv("B200_NO_STREAM") != nullptr;
+                if (L.egu_all && m->aq_sorted.codes && !no_stream && q4k_stream_grouped_supported(L.egu_all, 2 * F, H) &&
+                    q4k_stream_grouped_supported(L.ed_all, H, F)) {
+                    // weights stream through the TMA ring: the activation rows go into expert-sorted order first, so that an
+                    // expert's rows are one tile of the buffer (same arithmetic and chain order as the kernel below)
+                    ST_TRY(launch_gather_act_rows(ctx, m->aq_h, rows_tok, T * kk, H, m->aq_sorted));
+                    ST_TRY(launch_q4k_matmul_stream_grouped(ctx, L.egu_all, nE, 2 * F, H, m->aq_sorted, m->eoffs, T * kk, T, m->egu_out, 2 * F));
+                    ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, nullptr, m->aq_emid));
+                    ST_TRY(launch_q4k_matmul_stream_grouped(ctx, L.ed_all, nE, H, F, m->aq_emid, m->eoffs, T * kk, T, m->eo, H));
+                } else {
+                    ST_TRY(launch_q4k_matmul_grouped(ctx, L.d_egu_ptrs, nE, 2 * F, H, m->aq_h, m->eoffs, rows_tok, T, m->egu_out, 2 * F));
+                    ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, nullptr, m->aq_emid));
+                    ST_TRY(launch_q4k_matmul_grouped(ctx, L.d_ed_ptrs, nE, H, F, m->aq_emid, m->eoffs, nullptr, T, m->eo, H));
+                }
             } else if (L.egu[0].kind == B200_K_F32) {
                 ST_TRY(launch_f32w_matmul_grouped(ctx, (const float* const*)L.d_egu_ptrs, nE, 2 * F, H, m->normed, m->eoffs, rows_tok, T, m->egu_out, 2 * F));
                 ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, m->emid, ActQ{}));
@@ -548,6 +561,27 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
                 pg[e] = (const uint8_t*)L.egu[e].p;
                 pd[e] = (const uint8_t*)L.ed[e].p;
             }
+            if (L.egu[0].kind == B200_K_Q4K && L.ed[0].kind == B200_K_Q4K) {
+                // stack the experts' matrices in one buffer each, so that one tensor map addresses every expert's rows
+                const size_t gb = L.egu[0].bytes, db = L.ed[0].bytes;
+                bool same = true;
+                for (int e = 0; e < c.n_experts; e++) same = same && L.egu[e].bytes == gb && L.ed[e].bytes == db && L.ed[e].kind == B200_K_Q4K;
+                if (same) {
+                    ST_TRY(m->dalloc((void**)&L.egu_all, gb * c.n_experts, &m->weight_bytes));
+                    ST_TRY(m->dalloc((void**)&L.ed_all, db * c.n_experts, &m->weight_bytes));
+                    for (int e = 0; e < c.n_experts; e++) {
+                        CUDA_TRY(ctx, cudaMemcpyAsync(L.egu_all + gb * e, L.egu[e].p, gb, cudaMemcpyDeviceToDevice, ctx->stream));
+                        CUDA_TRY(ctx, cudaMemcpyAsync(L.ed_all + db * e, L.ed[e].p, db, cudaMemcpyDeviceToDevice, ctx->stream));
+                    }
+                    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+                    for (int e = 0; e < c.n_experts; e++) {
+                        m->dfree(L.egu[e].p); m->weight_bytes -= gb; L.egu[e].p = L.egu_all + gb * e;
+                        m->dfree(L.ed[e].p); m->weight_bytes -= db; L.ed[e].p = L.ed_all + db * e;
+                        pg[e] = (const uint8_t*)L.egu[e].p;
+                        pd[e] = (const uint8_t*)L.ed[e].p;
+                    }
+                }
+            }
             ST_TRY(m->dalloc((void**)&L.d_egu_ptrs, c.n_experts * sizeof(void*), &m->weight_bytes));
             ST_TRY(m->dalloc((void**)&L.d_ed_ptrs, c.n_experts * sizeof(void*), &m->weight_bytes));
             CUDA_TRY(ctx, cudaMemcpy(L.d_egu_ptrs, pg.data(), c.n_experts * sizeof(void*), cudaMemcpyHostToDevice));
@@ -623,6 +657,10 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
         ST_TRY(m->dalloc((void**)&m->egu_out, (size_t)MR * kk * 2 * EF * 4, sb));
         ST_TRY(m->dalloc((void**)&m->eo, (size_t)MR * kk * H * 4, sb));
         if (m->layers[0].egu[0].kind != B200_K_Q4K) ST_TRY(m->dalloc((void**)&m->emid, (size_t)MR * kk * EF * 4, sb));
+        if (H % 256 == 0) {
+            ST_TRY(m->dalloc((void**)&m->aq_sorted.codes, (size_t)MR * kk * H, sb));
+            ST_TRY(m->dalloc((void**)&m->aq_sorted.scales, (size_t)MR * kk * 2 * (H / 32) * 4, sb));
+        }
         ST_TRY(m->dalloc((void**)&m->aq_emid.codes, (size_t)MR * kk * EF, sb));
         ST_TRY(m->dalloc((void**)&m->aq_emid.scales, (size_t)MR * kk * 2 * ceil_div(EF, 32) * 4, sb));
     }

@@ -62,7 +62,7 @@ template <int NT>  // token tiles of 8
 __global__ void __launch_bounds__(kSThreads) q4k_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap cmap,
                                                                const __grid_constant__ CUtensorMap smap, int N, int nSB,
                                                                int T, float* __restrict__ dst, int ldd, size_t split_stride,
-                                                               int* __restrict__ err_flag) {
+                                                               int* __restrict__ err_flag, const int32_t* __restrict__ offs) {
     extern __shared__ __align__(1024) uint8_t s_ring_raw[];
     uint8_t* s_ring = s_ring_raw + ((1024u - (smem_u32(s_ring_raw) & 1023u)) & 1023u);  // the launch reserves 1 KB for this round-up
     constexpr int kSStages = stream_stages(NT), kSStageBytes = stream_stage_bytes(NT);
@@ -70,8 +70,21 @@ __global__ void __launch_bounds__(kSThreads) q4k_stream_kernel(const __grid_cons
     __shared__ int abort_s;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
     const int n0 = blockIdx.x * kSRows;
-    const int splits = gridDim.y, sb0 = (int)((long long)nSB * blockIdx.y / splits), sb1 = (int)((long long)nSB * (blockIdx.y + 1) / splits);
-    const int n_sb = sb1 - sb0, K = nSB * 256, nG = nSB * 8;
+    // plain: grid.y splits K. Grouped (offs given): grid.y is the expert, whose weights are rows e*N .. of the map and whose
+    // activation rows are offs[e] .. offs[e+1] of the (expert-sorted) activation buffers.
+    int w_row0 = n0, t_base = 0, splits = gridDim.y, split = blockIdx.y, n_pass = 1;
+    if (offs) {
+        const int e = blockIdx.y;
+        t_base = offs[e];
+        T = offs[e + 1] - t_base;   // this expert's rows: walked 8*NT at a time, the weights streamed again for every pass
+        if (T <= 0) return;
+        n_pass = (T + 8 * NT - 1) / (8 * NT);
+        w_row0 = e * N + n0;
+        splits = 1;
+        split = 0;
+    }
+    const int sb0 = (int)((long long)nSB * split / splits), sb1 = (int)((long long)nSB * (split + 1) / splits);
+    const int n_sb = sb1 - sb0, nG = nSB * 8;
     if (tid == 0) {
         for (int s = 0; s < kSStages; s++) {
             mbar_init(smem_u32(&full[s]), 1);             // the producer's announcement (+ the box's bytes)
@@ -90,19 +103,19 @@ __global__ void __launch_bounds__(kSThreads) q4k_stream_kernel(const __grid_cons
         if (lane == 0) {
             constexpr unsigned tx = (unsigned)(kSWBytes + 8 * NT * (256 + 64));
             int issued = 0;
-            for (int i = 0; i < n_sb; i++) {
-                const int st = i % kSStages, b = sb0 + i;
+            for (int i = 0; i < n_pass * n_sb; i++) {
+                const int st = i % kSStages, b = sb0 + i % n_sb, t_row = t_base + (i / n_sb) * 8 * NT;
                 if (i >= kSStages && !mbar_wait(smem_u32(&empty[st]), (unsigned)(((i - kSStages) / kSStages) & 1), abort_v)) {
                     abort_s = 1;
                     break;
                 }
                 const unsigned bar = smem_u32(&full[st]), base = smem_u32(s_ring) + (unsigned)st * kSStageBytes;
                 mbar_arrive_expect_tx(bar, tx);
-                tensor_g2s_2d(base, &wmap, b * 144, n0, bar);
-                tensor_g2s_2d(base + kSWBytes, &cmap, 256 * b, 0, bar);
-                tensor_g2s_2d(base + kSWBytes + 8 * NT * 128, &cmap, 256 * b + 128, 0, bar);
-                tensor_g2s_2d(base + kSWBytes + 8 * NT * 256, &smap, 8 * b, 0, bar);
-                tensor_g2s_2d(base + kSWBytes + 8 * NT * 288, &smap, nG + 8 * b, 0, bar);
+                tensor_g2s_2d(base, &wmap, b * 144, w_row0, bar);
+                tensor_g2s_2d(base + kSWBytes, &cmap, 256 * b, t_row, bar);
+                tensor_g2s_2d(base + kSWBytes + 8 * NT * 128, &cmap, 256 * b + 128, t_row, bar);
+                tensor_g2s_2d(base + kSWBytes + 8 * NT * 256, &smap, 8 * b, t_row, bar);
+                tensor_g2s_2d(base + kSWBytes + 8 * NT * 288, &smap, nG + 8 * b, t_row, bar);
                 issued = i + 1;
             }
             // copies still in flight must land before the CTA may leave: bounded waits on their barriers
@@ -114,11 +127,14 @@ __global__ void __launch_bounds__(kSThreads) q4k_stream_kernel(const __grid_cons
 
     // ---- consumers: warp w owns rows n0 + 16w .. +15; lane rows gid and gid + 8 ----
     float acc[NT][4];
-#pragma unroll
-    for (int j = 0; j < NT; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     const unsigned row_off = (unsigned)(16 * warp + gid) * 144u;
     bool ok = true;
-    for (int i = 0; i < n_sb; i++) {
+    const int na = n0 + 16 * warp + gid, nb = na + 8;
+    for (int pass = 0; pass < n_pass && ok; pass++) {
+    const int Tp = T - pass * 8 * NT;  // rows from this pass on (the pass itself takes 8*NT of them)
+#pragma unroll
+    for (int j = 0; j < NT; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int i = pass * n_sb; i < (pass + 1) * n_sb; i++) {
         const int st = i % kSStages;
         const bool there = mbar_wait(smem_u32(&full[st]), (unsigned)((i / kSStages) & 1), abort_v);
         if (!__all_sync(0xffffffffu, there)) {
@@ -165,6 +181,7 @@ __global__ void __launch_bounds__(kSThreads) q4k_stream_kernel(const __grid_cons
                            ah3 = (q1[p].y >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
             for (int j = 0; j < NT; j++) {
+                if (8 * j >= Tp) continue;  // a token tile with no rows (uniform over the CTA)
                 // bytes 64p + 8tig .. (+32 for the pair's second sub-block) of row 8j + gid: half p >> 1, 16-byte chunk
                 // ((64p + 8tig) & 127) >> 4 stored at chunk ^ (row & 7)
                 const uint8_t* hb = act + (p >> 1) * (8 * NT * 128) + (8 * j + gid) * 128 + ((8 * tig) & 15);
@@ -205,24 +222,24 @@ __global__ void __launch_bounds__(kSThreads) q4k_stream_kernel(const __grid_cons
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&empty[st]));
     }
-    if (!ok) {
-        abort_s = 1;
-        if (lane == 0 && err_flag) atomicExch(err_flag, 1);
-        return;
-    }
-    float* out = dst + (size_t)blockIdx.y * split_stride;
-    const int na = n0 + 16 * warp + gid, nb = na + 8;
+    if (!ok) break;
+    float* out = dst + (size_t)split * split_stride + (size_t)(t_base + pass * 8 * NT) * ldd;
 #pragma unroll
     for (int j = 0; j < NT; j++) {
         const int t0 = 8 * j + 2 * tig, t1 = t0 + 1;
-        if (t0 < T) {
+        if (t0 < Tp) {
             if (na < N) out[(size_t)t0 * ldd + na] = acc[j][0];
             if (nb < N) out[(size_t)t0 * ldd + nb] = acc[j][2];
         }
-        if (t1 < T) {
+        if (t1 < Tp) {
             if (na < N) out[(size_t)t1 * ldd + na] = acc[j][1];
             if (nb < N) out[(size_t)t1 * ldd + nb] = acc[j][3];
         }
+    }
+    }
+    if (!ok) {
+        abort_s = 1;
+        if (lane == 0 && err_flag) atomicExch(err_flag, 1);
     }
 }
 
@@ -284,7 +301,7 @@ int run_stream(b200_ctx* ctx, const CUtensorMap* wmap, int N, int nSB, ActQ aq, 
     {
         ProfScope ps(ctx, PROF_Q4K_GEMM);
         q4k_stream_kernel<NT><<<grid, kSThreads, smem, ctx->stream>>>(*wmap, *cmap, *smap, N, nSB, T, out, splits > 1 ? N : ldd,
-                                                                     splits > 1 ? (size_t)T * N : 0, ctx->err_flag);
+                                                                     splits > 1 ? (size_t)T * N : 0, ctx->err_flag, nullptr);
     }
     LAUNCH_CHECK(ctx);
     if (splits > 1) {
@@ -294,7 +311,54 @@ int run_stream(b200_ctx* ctx, const CUtensorMap* wmap, int N, int nSB, ActQ aq, 
     return B200_OK;
 }
 
+// sorted[s] = row rows_tok[s] of the activation buffers: codes [.][K] and scales [.][2*nG]
+__global__ void gather_act_rows_kernel(const int8_t* __restrict__ codes, const float* __restrict__ scales, const int32_t* __restrict__ rows_tok,
+                                       int K, int8_t* __restrict__ codes_out, float* __restrict__ scales_out) {
+    const int s = blockIdx.x, r = rows_tok[s], nS = K / 16;  // K/32 scales + K/32 sums
+    const uint4* src = reinterpret_cast<const uint4*>(codes + (size_t)r * K);
+    uint4* dstc = reinterpret_cast<uint4*>(codes_out + (size_t)s * K);
+    for (int i = threadIdx.x; i < K / 16; i += blockDim.x) dstc[i] = src[i];
+    for (int i = threadIdx.x; i < nS; i += blockDim.x) scales_out[(size_t)s * nS + i] = scales[(size_t)r * nS + i];
+}
+
 }  // namespace
+
+int launch_gather_act_rows(b200_ctx* ctx, ActQ src, const int32_t* rows_tok, int n_rows, int K, ActQ dst) {
+    if (n_rows <= 0) return B200_OK;
+    gather_act_rows_kernel<<<n_rows, 128, 0, ctx->stream>>>(src.codes, src.scales, rows_tok, K, dst.codes, dst.scales);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+bool q4k_stream_grouped_supported(const uint8_t* W_all, int N, int K) { return N % kSRows == 0 && K % 256 == 0 && (reinterpret_cast<uintptr_t>(W_all) & 15) == 0; }
+
+// Experts' matrices stacked in one buffer ([n_experts * N][K] Q4_K); aq holds the activation rows in expert-sorted order
+// (rows offs[e] .. offs[e+1] belong to expert e, n_rows in all); dst rows are the sorted slots.
+int launch_q4k_matmul_stream_grouped(b200_ctx* ctx, const uint8_t* W_all, int n_experts, int N, int K, ActQ aq, const int32_t* offs,
+                                     int n_rows, int max_rows_per_expert, float* dst, int ldd) {
+    if (!q4k_stream_grouped_supported(W_all, N, K)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "grouped streaming matmul: N %% 64, K %% 256 or alignment");
+    if (n_rows <= 0) return B200_OK;
+    constexpr int NT = 2;
+    const int nSB = K / 256;
+    const CUtensorMap* wmap = q4k_weight_map(ctx, W_all, n_experts * N, nSB, kSRows);
+    const CUtensorMap* cmap = act_map(ctx, aq.codes, K, n_rows, 8 * NT, true);
+    const CUtensorMap* smap = act_map(ctx, aq.scales, nSB * 16, n_rows, 8 * NT, false);
+    if (!wmap || !cmap || !smap) return B200_CUDA_ERROR;
+    constexpr int smem = stream_stages(NT) * stream_stage_bytes(NT) + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_set = true;
+    }
+    (void)max_rows_per_expert;
+    dim3 grid(N / kSRows, n_experts);
+    {
+        ProfScope ps(ctx, PROF_Q4K_GEMM);
+        q4k_stream_kernel<NT><<<grid, kSThreads, smem, ctx->stream>>>(*wmap, *cmap, *smap, N, nSB, 0, dst, ldd, 0, ctx->err_flag, offs);
+    }
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
 
 int launch_q4k_matmul_stream(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, bool allow_split) {
     if (K % 256 || T < 1 || T > 32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the streaming Q4_K matmul takes 1..32 rows and K %% 256 == 0");
