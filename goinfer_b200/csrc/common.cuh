@@ -18,6 +18,16 @@ struct ProfRec {
     cudaEvent_t e0, e1;
 };
 
+// The K-split partial matrices a matmul left unsummed for its consumer: n matrices [rows][width of dst] `stride` floats
+// apart, to be added in order in place of reading `dst`.
+struct Parts {
+    const float* p = nullptr;
+    size_t stride = 0;
+    int n = 0;
+    const float* dst = nullptr;
+    int rows = 0, cols = 0;  // of dst (row stride = cols)
+};
+
 struct b200_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -30,6 +40,10 @@ struct b200_ctx {
     void* umma_scratch = nullptr;
     size_t umma_scratch_bytes = 0;
     int* err_flag = nullptr;
+    // set around a matmul whose consumer (residual add + norm, RoPE/KV store, residual add) can add the K-split partials
+    // itself: the matmul then skips its reduce kernel and leaves `pending`; the consumer that is handed pending.dst takes it
+    bool defer_reduce = false;
+    Parts pending;
     // tensor parallel: the NCCL communicator b200_tp_init made for this context (null on a single GPU)
     void* tp_comm = nullptr;
     int tp_rank = 0, tp_size = 1;
@@ -177,6 +191,9 @@ bool q4k_stream_grouped_supported(const uint8_t* W_all, int N, int K);
 int launch_q4k_matmul_stream_grouped(b200_ctx*, const uint8_t* W_all, int n_experts, int N, int K, ActQ aq, const int32_t* offs,
                                      int n_rows, int max_rows_per_expert, float* dst, int ldd);
 int launch_gather_act_rows(b200_ctx*, ActQ src, const int32_t* rows_tok, int n_rows, int K, ActQ dst);
+
+// gemm_umma.cu: sums partials nobody took into their dst (a safety net: every deferred matmul has a taker)
+int flush_pending_parts(b200_ctx*);
 
 // tp.cu: collectives over the context's communicator, on its stream
 int tp_all_reduce_sum(b200_ctx*, float* buf, size_t n);

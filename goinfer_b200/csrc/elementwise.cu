@@ -54,12 +54,20 @@ __global__ void embed_gather_kernel(const void* __restrict__ table, int kind, co
     }
 }
 
+// value i of a matrix kept as n K-split partials `stride` floats apart: added in order, starting from the first
+__device__ __forceinline__ float parts_at(const float* __restrict__ p, size_t stride, int n, size_t i) {
+    float s = p[i];
+    for (int k = 1; k < n; k++) s = __fadd_rn(s, p[(size_t)k * stride + i]);
+    return s;
+}
+
 // One block per output row. Dynamic shared memory: H floats (the normed row) + 8 doubles.
 __global__ void __launch_bounds__(256) add_rmsnorm_quant_kernel(float* __restrict__ h, const float* __restrict__ delta,
                                                                 const float* __restrict__ w, int H, float eps,
                                                                 float* __restrict__ normed, int8_t* __restrict__ codes,
                                                                 float* __restrict__ scales,
-                                                                const int32_t* __restrict__ gather_rows) {
+                                                                const int32_t* __restrict__ gather_rows, int n_parts,
+                                                                size_t part_stride) {
     extern __shared__ double smem_d[];
     double* red = smem_d;                 // 8 doubles
     float* row = (float*)(smem_d + 8);    // H floats
@@ -77,7 +85,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_quant_kernel(float* __restric
         if (dr) {
             float d[8];
 #pragma unroll
-            for (int u = 0; u < 8; u++) d[u] = dr[i + u * blockDim.x];
+            for (int u = 0; u < 8; u++) d[u] = n_parts ? parts_at(dr, part_stride, n_parts, i + u * blockDim.x) : dr[i + u * blockDim.x];
 #pragma unroll
             for (int u = 0; u < 8; u++) {
                 x[u] = __fadd_rn(x[u], d[u]);
@@ -93,7 +101,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_quant_kernel(float* __restric
     for (; i < H; i += blockDim.x) {
         float x = hr[i];
         if (dr) {
-            x = __fadd_rn(x, dr[i]);
+            x = __fadd_rn(x, n_parts ? parts_at(dr, part_stride, n_parts, i) : dr[i]);
             hr[i] = x;
         }
         row[i] = x;
@@ -155,9 +163,9 @@ __global__ void swiglu_plain_kernel(const float* __restrict__ gate_up, int F, in
     if (f < F) mid[(size_t)r * F + f] = __fmul_rn(silu_f64(gate_up[(size_t)r * ld + f]), gate_up[(size_t)r * ld + F + f]);
 }
 
-__global__ void add_kernel(float* __restrict__ h, const float* __restrict__ d, size_t n) {
+__global__ void add_kernel(float* __restrict__ h, const float* __restrict__ d, size_t n, int n_parts, size_t part_stride) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) h[i] = __fadd_rn(h[i], d[i]);
+    if (i < n) h[i] = __fadd_rn(h[i], n_parts ? parts_at(d, part_stride, n_parts, i) : d[i]);
 }
 
 __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
@@ -170,7 +178,8 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvstore_kernel(
     float* __restrict__ qkv, int ld, int nH, int nKV, int hd, int half, const double* __restrict__ inv_freq,
     const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, const int32_t* __restrict__ row_slot,
     const int32_t* __restrict__ row_pos, __half* __restrict__ kpool, __half* __restrict__ vpool,
-    const int32_t* __restrict__ table, int max_blocks, int block_rows) {
+    const int32_t* __restrict__ table, int max_blocks, int block_rows, const float* __restrict__ parts, int n_parts,
+    size_t part_stride) {
     extern __shared__ double smem_d[];
     double* cs = smem_d;                         // [half] cos, [half] sin
     float* hb = (float*)(smem_d + 2 * half);     // [8][hd]
@@ -193,7 +202,7 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvstore_kernel(
         float* src = rowp + (size_t)hh * hd;
         double ss = 0;
         for (int e = lane; e < hd; e += 32) {
-            float x = src[e];
+            float x = n_parts ? parts_at(parts, part_stride, n_parts, (size_t)r * ld + (size_t)hh * hd + e) : src[e];
             buf[e] = x;
             ss += (double)x * (double)x;
         }
@@ -252,7 +261,13 @@ int launch_add_rmsnorm_quant(b200_ctx* ctx, float* h, const float* delta, const 
     if (aq.codes && (H % 32)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "quantized rows need a width that is a multiple of 32");
     size_t smem = 8 * sizeof(double) + (size_t)H * sizeof(float);
     ProfScope ps(ctx, PROF_NORM_QUANT);
-    add_rmsnorm_quant_kernel<<<T, 256, smem, ctx->stream>>>(h, delta, w, H, eps, normed, aq.codes, aq.scales, gather_rows);
+    Parts pt{};
+    if (delta && ctx->pending.n > 0 && ctx->pending.dst == delta && !gather_rows) {  // the matmul left its K-split partials for us
+        pt = ctx->pending;
+        ctx->pending = Parts{};
+    }
+    add_rmsnorm_quant_kernel<<<T, 256, smem, ctx->stream>>>(h, pt.n ? pt.p : delta, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n,
+                                                            pt.stride);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }
@@ -280,7 +295,12 @@ int launch_swiglu_quant(b200_ctx* ctx, const float* gate_up, int T, int F, int l
 }
 
 int launch_add(b200_ctx* ctx, float* h, const float* delta, size_t n) {
-    add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(h, delta, n);
+    Parts pt{};
+    if (ctx->pending.n > 0 && ctx->pending.dst == delta) {
+        pt = ctx->pending;
+        ctx->pending = Parts{};
+    }
+    add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(h, pt.n ? pt.p : delta, n, pt.n, pt.stride);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }
@@ -297,9 +317,14 @@ int launch_qknorm_rope_kvstore(b200_ctx* ctx, float* qkv, int ld, int T, int nH,
     if (hd > 256 || 2 * rot_half > hd) B200_FAIL(ctx, B200_BAD_ARGUMENT, "head_dim up to 256, rotary_dim <= head_dim");
     size_t smem = 2 * (size_t)rot_half * sizeof(double) + 8 * (size_t)hd * sizeof(float);
     ProfScope ps(ctx, PROF_ROPE_KV);
+    Parts pt{};
+    if (ctx->pending.n > 0 && ctx->pending.dst == qkv) {  // the q|k|v matmul left its K-split partials for us
+        pt = ctx->pending;
+        ctx->pending = Parts{};
+    }
     qknorm_rope_kvstore_kernel<<<T, 256, smem, ctx->stream>>>(qkv, ld, nH, nKV, hd, rot_half, inv_freq, q_norm, k_norm, eps,
                                                               row_slot, row_pos, kv.k, kv.v, kv.table, kv.max_blocks,
-                                                              kv.block_rows);
+                                                              kv.block_rows, pt.p, pt.n, pt.stride);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }

@@ -350,7 +350,12 @@ int run_layers(b200_model* m, int T, int max_keys) {
         const bool q_in = L.qkv.kind == B200_K_Q4K;
         ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, delta, L.attn_norm, T, H, c.rms_eps, q_in ? nullptr : m->normed,
                                         q_in ? m->aq_h : none, nullptr));
+        // the consumers of the q|k|v, o and down products can add their K-split partials themselves (no reduce kernel)
+        static const bool tap_env = getenv("B200_DEBUG_TAP") != nullptr || getenv("B200_NO_DEFER") != nullptr;
+        const bool defer = c.tp_size <= 1 && !m->exact_scores && !tap_env;
+        ctx->defer_reduce = defer;
         ST_TRY(matmul(m, L.qkv, m->normed, m->aq_h, T, m->qkv, ldq));
+        ctx->defer_reduce = false;
         KVView kv{m->kpool[l], m->vpool[l], m->table, m->max_blocks, c.kv_block_rows, nKV, hd};
         ST_TRY(launch_qknorm_rope_kvstore(ctx, m->qkv, ldq, T, nH, nKV, hd, m->rot_half, L.inv_freq,
                                           c.qk_norm ? L.q_norm : nullptr, c.qk_norm ? L.k_norm : nullptr, c.rms_eps,
@@ -378,7 +383,9 @@ int run_layers(b200_model* m, int T, int max_keys) {
                                               m->ctxb + (size_t)pf * qd, aq_tail));
             }
         }
+        ctx->defer_reduce = defer;
         ST_TRY(matmul(m, L.wo, m->ctxb, m->aq_ctx, T, m->att, H));
+        ctx->defer_reduce = false;
         if (c.tp_size > 1) ST_TRY(tp_all_reduce_sum(ctx, m->att, (size_t)T * H));  // o is split by input columns: partial sums
         if (c.n_experts == 0) {
             const bool g_q = L.gu.kind == B200_K_Q4K, d_q = L.down.kind == B200_K_Q4K;
@@ -386,7 +393,9 @@ int run_layers(b200_model* m, int T, int max_keys) {
                                             g_q ? m->aq_h : none, nullptr));
             ST_TRY(matmul(m, L.gu, m->normed, m->aq_h, T, m->gu, 2 * c.ffn));
             ST_TRY(launch_swiglu_quant(ctx, m->gu, T, c.ffn, 2 * c.ffn, d_q ? nullptr : m->mid, d_q ? m->aq_mid : none));
+            ctx->defer_reduce = defer;
             ST_TRY(matmul(m, L.down, m->mid, m->aq_mid, T, m->att, H));
+            ctx->defer_reduce = false;
             if (c.tp_size > 1) ST_TRY(tp_all_reduce_sum(ctx, m->att, (size_t)T * H));
         } else {
             // routed experts (decoder/mlp.go:36-120): f32 router on the f32 normed row, top-k, grouped expert GEMMs,
@@ -426,6 +435,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
         delta = m->att;
     }
     if (delta) ST_TRY(launch_add(ctx, m->h, delta, (size_t)T * H));
+    ST_TRY(flush_pending_parts(ctx));
     return B200_OK;
 }
 

@@ -372,8 +372,19 @@ size_t q4k_umma_scratch_bytes(int max_rows, int max_k, int max_n) {
     return (size_t)ceil_div(max_rows, 256) * 256 * max_k * 2 + (size_t)4 * max_rows * max_n * 4 + 256;
 }
 
+int flush_pending_parts(b200_ctx* ctx) {
+    if (ctx->pending.n <= 0) return B200_OK;
+    const Parts pt = ctx->pending;
+    ctx->pending = Parts{};
+    splitk_reduce_kernel<<<(unsigned)(((size_t)pt.rows * pt.cols + 255) / 256), 256, 0, ctx->stream>>>(pt.p, pt.stride, pt.n, pt.rows, pt.cols,
+                                                                                                      const_cast<float*>(pt.dst), pt.cols);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
 int launch_q4k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
                            size_t scratch_bytes, int* err_flag) {
+    ST_TRY(flush_pending_parts(ctx));  // the scratch is about to be reused
     if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
     if (reinterpret_cast<uintptr_t>(W) & 15) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tcgen05 matmul wants 16-byte aligned weights");
     const int nSB = K / 256, t_tiles = ceil_div(T, 256);
@@ -413,8 +424,12 @@ int launch_q4k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ a
     }
     LAUNCH_CHECK(ctx);
     if (splits > 1) {
-        splitk_reduce_kernel<<<(unsigned)(((size_t)T * N + 255) / 256), 256, 0, ctx->stream>>>(part, stride, splits, T, N, dst, ldd);
-        LAUNCH_CHECK(ctx);
+        if (ctx->defer_reduce && ldd == N) {  // the consumer adds the partials (same order, same bits)
+            ctx->pending = Parts{part, stride, splits, dst, T, N};
+        } else {
+            splitk_reduce_kernel<<<(unsigned)(((size_t)T * N + 255) / 256), 256, 0, ctx->stream>>>(part, stride, splits, T, N, dst, ldd);
+            LAUNCH_CHECK(ctx);
+        }
     }
     return B200_OK;
 }
