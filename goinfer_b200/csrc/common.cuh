@@ -133,7 +133,8 @@ int launch_embed_gather(b200_ctx*, const void* table, int kind, const int32_t* i
 int launch_add_rmsnorm_quant(b200_ctx*, float* h, const float* delta, const float* w, int T, int H, float eps,
                              float* normed, ActQ aq, const int32_t* gather_rows);
 int launch_quant_g32(b200_ctx*, const float* x, int T, int K, ActQ aq);
-int launch_swiglu_quant(b200_ctx*, const float* gate_up, int T, int F, int ld, float* mid_f32, ActQ aq);
+// f64_silu: the reference's f64 silu (decoder/rmsnorm.go:204-207); false in the fast class (f32 expf, about 2e-7 relative)
+int launch_swiglu_quant(b200_ctx*, const float* gate_up, int T, int F, int ld, float* mid_f32, ActQ aq, bool f64_silu = true);
 int launch_add(b200_ctx*, float* h, const float* delta, size_t n);
 // q (in place, f32), k,v -> paged fp16 store; optional per-head RMSNorm, NeoX RoPE with f64 cos/sin.
 int launch_qknorm_rope_kvstore(b200_ctx*, float* qkv, int ld, int T, int nH, int nKV, int hd, int rot_half,

@@ -392,7 +392,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
             ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, m->att, L.ffn_norm, T, H, c.rms_eps, g_q ? nullptr : m->normed,
                                             g_q ? m->aq_h : none, nullptr));
             ST_TRY(matmul(m, L.gu, m->normed, m->aq_h, T, m->gu, 2 * c.ffn));
-            ST_TRY(launch_swiglu_quant(ctx, m->gu, T, c.ffn, 2 * c.ffn, d_q ? nullptr : m->mid, d_q ? m->aq_mid : none));
+            ST_TRY(launch_swiglu_quant(ctx, m->gu, T, c.ffn, 2 * c.ffn, d_q ? nullptr : m->mid, d_q ? m->aq_mid : none, c.kernel_class == B200_CLASS_EXACT));
             ctx->defer_reduce = defer;
             ST_TRY(matmul(m, L.down, m->mid, m->aq_mid, T, m->att, H));
             ctx->defer_reduce = false;
@@ -416,11 +416,11 @@ int run_layers(b200_model* m, int T, int max_keys) {
                     // expert's rows are one tile of the buffer (same arithmetic and chain order as the kernel below)
                     ST_TRY(launch_gather_act_rows(ctx, m->aq_h, rows_tok, T * kk, H, m->aq_sorted));
                     ST_TRY(launch_q4k_matmul_stream_grouped(ctx, L.egu_all, nE, 2 * F, H, m->aq_sorted, m->eoffs, T * kk, T, m->egu_out, 2 * F));
-                    ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, nullptr, m->aq_emid));
+                    ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, nullptr, m->aq_emid, c.kernel_class == B200_CLASS_EXACT));
                     ST_TRY(launch_q4k_matmul_stream_grouped(ctx, L.ed_all, nE, H, F, m->aq_emid, m->eoffs, T * kk, T, m->eo, H));
                 } else {
                     ST_TRY(launch_q4k_matmul_grouped(ctx, L.d_egu_ptrs, nE, 2 * F, H, m->aq_h, m->eoffs, rows_tok, T, m->egu_out, 2 * F));
-                    ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, nullptr, m->aq_emid));
+                    ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, nullptr, m->aq_emid, c.kernel_class == B200_CLASS_EXACT));
                     ST_TRY(launch_q4k_matmul_grouped(ctx, L.d_ed_ptrs, nE, H, F, m->aq_emid, m->eoffs, nullptr, T, m->eo, H));
                 }
             } else if (L.egu[0].kind == B200_K_F32) {

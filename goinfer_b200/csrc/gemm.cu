@@ -744,13 +744,14 @@ int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, in
     // Rows up to 8 are HBM-bound: split K over the CTA's warps (unless the exact class asks for the one ascending
     // chain per output that every larger batch uses, so a row's bits do not depend on its batch).
     if (T <= 8 && klass == B200_CLASS_EXACT) return run_q4k<1, false>(ctx, W, N, nSB, aq, T, dst, ldd);
+    if (klass == 4 && T <= 32 && (reinterpret_cast<uintptr_t>(W) & 15) == 0) return launch_q4k_matmul_stream(ctx, W, N, K, aq, T, dst, ldd, false);
     if (T == 1) return run_q4k_gemv<1>(ctx, W, N, nSB, aq, dst, ldd);
     if (T == 2) return run_q4k_gemv<2>(ctx, W, N, nSB, aq, dst, ldd);
     if (T == 3) return run_q4k_gemv<3>(ctx, W, N, nSB, aq, dst, ldd);
     // 4..32 rows, fast class: the weights stream through a TMA ring (klass 3 forces the older kernels for comparison)
     static const bool no_stream = getenv("B200_NO_STREAM") != nullptr;
     if (T <= 32 && klass != B200_CLASS_EXACT && klass != 3 && !no_stream && (reinterpret_cast<uintptr_t>(W) & 15) == 0)
-        return launch_q4k_matmul_stream(ctx, W, N, K, aq, T, dst, ldd, true);
+        return launch_q4k_matmul_stream(ctx, W, N, K, aq, T, dst, ldd, klass != 4);  // klass 4: the one-chain form (the exact class's bits)
     if (T <= 8) return run_q4k<1, true>(ctx, W, N, nSB, aq, T, dst, ldd);
     if (T <= 16) return run_q4k<2, false>(ctx, W, N, nSB, aq, T, dst, ldd);
     if (T <= 32) return run_q4k_tile<4>(ctx, W, N, nSB, aq, T, dst, ldd);
