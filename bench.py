@@ -308,8 +308,8 @@ def run_gpu(args):
         pass
     peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = attn_bytes_per_launch / (attn_ms_per_launch * 1e-3) / 1e9 if attn_ms_per_launch > 0 else 0.0
-    # DRAM bytes per launch from the ncu capture of the same kernel on a smaller case (profiles/attn_mma_kernel_hd128_g4_rows32.md:
-    # dram read+write = 1.015 x the algorithmic bytes), scaled by the keys a full launch processes (traffic is proportional to keys).
+    # DRAM bytes per launch from an ncu capture of the same kernel on a smaller case (32 rows: dram read + write = 1.015 x the
+    # algorithmic bytes), scaled by the keys a full launch processes (traffic is proportional to keys).
     traffic = 1.015 * attn_bytes_per_launch
     h2d = B * s.hidden * 4 + (2 + 3 * B) * 4 + B * 4 + B * 24
     line = {

@@ -8,19 +8,21 @@
 // are replaced by fp16 products of the dequantized values, each within 2^-11 of the exact operand.
 //
 // One CTA owns a [256 tokens] x [128*NT weight rows] output tile: per token tile an accumulator of 128*NT fp32 columns x
-// 128 lanes (NT = 2: all of the SM's tensor memory). What bounds this GEMM is the L2 -> SM traffic of the activation operand
-// (every CTA streams the whole [T][K] matrix), so the tile is as wide in weight rows as TMEM allows. K is walked in
+// 128 lanes (NT = 2: all of the SM's tensor memory; NT = 1 when that is what it takes to cover the SMs). K is walked in
 // chunks of 64 (one sub-block pair of a super-block):
-//   A ring (4 stages): 2 x [128 tokens][64] fp16, cp.async from the fp16 activation matrix two chunks ahead, whole rows
-//            per warp (coalesced), 128-byte swizzled K-major
-//   B ring (2 stages): 2 x [128 weight rows][64] fp16, dequantized by the CTA's threads (one 32-weight sub-block each)
-//            from raw Q4_K bytes loaded into registers two chunks ahead
-// Eight producer warps fill the rings and arrive on a `full` mbarrier per chunk; a ninth warp's elected thread
-// waits for it, issues the chunk's 16 tcgen05.mma (K=16 each) and a tcgen05.commit that arrives on the `empty` mbarrier
-// the producers wait on before they reuse a stage (a single issuing thread is paced by the tensor core, ~100 cycles per
-// MMA, so it must not be a thread the producers wait for). Nothing in the loop is a block-wide barrier. The epilogue reads
-// the accumulators with tcgen05.ld (each warp its 32 TMEM lanes = 32 tokens) and writes fp32 rows. With split-K
-// (gridDim.z > 1) each split writes its own partial matrix and a second kernel adds the splits in order.
+//   A ring (3 stages): 2 x [128 tokens][64] fp16. The fp16 activation matrix is written tile by tile in the MMA's
+//            swizzled order by act_to_f16_kernel, so a stage is ONE contiguous 32 KB bulk copy, issued by one thread.
+//   raw weights: the 144-byte super-blocks of the tile's rows, one tiled TMA copy (box 144 B x 128*NT rows) per
+//            super-block, issued by one thread; each producer thread keeps its row's super-block in registers.
+//   B ring (2 stages): [128*NT weight rows][64] fp16, dequantized by eight producer warps (a thread = a weight row;
+//            nibbles become fp16 by a mantissa trick, three instructions per pair of weights).
+// The producers arrive on a `full` mbarrier per chunk (the activation copy's bytes are counted on the same barrier); the
+// MMA warp's elected thread waits for it, issues the chunk's 8 tcgen05.mma (M128, N = 128*NT, K = 16 each) and a
+// tcgen05.commit that arrives on the `empty` mbarrier producers and loaders wait on before they reuse a stage. Nothing
+// in the loop is a block-wide barrier. The epilogue reads the accumulators with tcgen05.ld (each warp its 32 TMEM lanes =
+// 32 tokens), turns the 32x32 blocks around in shared memory and writes whole fp32 rows. With split-K (gridDim.z > 1)
+// each split writes its own partial matrix; a second kernel adds the splits in order, unless the caller's next kernel
+// does that itself (b200_ctx::defer_reduce).
 //
 // Every mbarrier wait is bounded: on expiry the CTA raises an error flag, frees its TMEM and returns.
 #include <algorithm>
@@ -136,7 +138,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
 
         auto step = [&](int it, int p) -> bool {  // p = it & 3, a literal at every call site
             // B stage it%2 was last read by the MMAs of chunk it-2
-            if (it > 1) {  // the verdict is made warp-uniform: the lanes meet in __syncwarp below
+            if (it > 1) {  // the answer is made warp-uniform: the lanes meet in __syncwarp below
                 const bool w_ok = mbar_wait(smem_u32(&empty_bar[(it - 2) % kStages]), (unsigned)(((it - 2) / kStages) & 1), abort_v);
                 if (!__all_sync(0xffffffffu, w_ok)) return false;
             }

@@ -1,7 +1,7 @@
 """Regenerates tests/golden/*.npz from the reference checkout's own test data.
 
-Run in a container that has the reference tree (default /root/reference); the GPU box does not, which is
-why the outputs are committed. Each .npz holds the tiny model's f32 weights (from the reference's
+Usage: python make_fixtures.py <path of the reference checkout>. Machines that run the tests need not have the
+reference tree, which is why the outputs are committed. Each .npz holds the tiny model's f32 weights (from the reference's
 committed safetensors) and the golden vectors the reference's tests compare against:
   llama_tiny   <- testdata/llama-tiny/ + testdata/llama_tiny_text_golden.json   (decoder/llama_tiny_test.go:22-80)
   qwen3moe_tiny<- testdata/qwen3moe-tiny/ + testdata/qwen3moe_forward_golden.json (decoder/qwen3moe_test.go)
@@ -14,7 +14,9 @@ import sys
 import numpy as np
 from safetensors.numpy import load_file
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_fixtures.py <path of the reference checkout>")
+REF = sys.argv[1]
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 
