@@ -192,6 +192,10 @@ struct b200_model {
     // the step's leading prefill run (rows of one slot at consecutive positions), 0 rows when there is none;
     // pf_tail_keys = the longest key range among the rows after it
     int pf_rows = 0, pf_slot = 0, pf_pos0 = 0, pf_tail_keys = 1;
+    // the decode loop's captured step (b200_decode_loop_device) and what it was captured for
+    cudaGraphExec_t loop_graph = nullptr;
+    int loop_graph_S = 0, loop_graph_splits = 0, loop_graph_adv = 0;
+    int64_t loop_graph_launches = 0;
     // MoE
     float *rl = nullptr, *rw = nullptr, *egu_out = nullptr, *eo = nullptr, *emid = nullptr;
     int32_t *ridx = nullptr, *eoffs = nullptr, *erows = nullptr;
@@ -724,6 +728,7 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
 void b200_model_free(b200_model* m) {
     if (!m) return;
     cudaStreamSynchronize(m->ctx->stream);
+    if (m->loop_graph) cudaGraphExecDestroy(m->loop_graph);
     for (void* p : m->allocs) cudaFree(p);
     if (m->p_desc) cudaFreeHost(m->p_desc);
     if (m->p_ids) cudaFreeHost(m->p_ids);
@@ -1070,7 +1075,7 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
     if (ids_out) log.resize((size_t)steps * S);
     CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     CUDA_TRY(ctx, cudaEventRecord(m->ev0, ctx->stream));
-    for (int st = 0; st < steps; st++) {
+    auto one_step = [&](int st) -> int {
         prepare_step_kernel<<<1, 256, 0, ctx->stream>>>(m->d_desc, m->d_pos, 1, m->table, m->max_blocks, c.kv_block_rows,
                                                         m->slot_mapped, m->free_stack, m->free_count, m->d_seq_row0,
                                                         m->d_row_slot, m->d_row_pos, m->status);
@@ -1086,7 +1091,49 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
         advance_kernel<<<ceil_div(S, 256), 256, 0, ctx->stream>>>(m->d_tokens, m->d_ids, m->d_pos, S, advance_pos, ids_out ? m->d_ids_log : nullptr);
         LAUNCH_CHECK(ctx);
         if (ids_out) CUDA_TRY(ctx, cudaMemcpyAsync(log.data() + (size_t)st * S, m->d_ids_log, (size_t)S * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        return B200_OK;
+    };
+    // A step's launches do not depend on the step (positions and tokens advance on the device), so from the second step on
+    // the loop replays one captured CUDA graph: several hundred launches become one. Kept off when ids are logged to the
+    // host every step, when kernels are being event-profiled, and under tensor parallel (the collectives stay eager).
+    static const bool no_graph = getenv("B200_NO_GRAPH") != nullptr;
+    const bool use_graph = steps >= 3 && !ids_out && ctx->prof_mask == 0 && c.tp_size <= 1 && !no_graph;
+    int done = 0;
+    if (use_graph) {
+        ST_TRY(one_step(0));  // eager: first-use set-up (function attributes, tensor maps) happens outside the capture
+        done = 1;
+        // grids depend on the key count only through the attention kernels' split count (the exact class: through the count itself)
+        const int key_splits = m->exact_scores ? max_keys : ceil_div(max_keys, 512);
+        if (!m->loop_graph || m->loop_graph_S != S || m->loop_graph_splits != key_splits || m->loop_graph_adv != advance_pos) {
+            if (m->loop_graph) { cudaGraphExecDestroy(m->loop_graph); m->loop_graph = nullptr; }
+            const int64_t l0 = ctx->launches;
+            CUDA_TRY(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+            const int st_cap = one_step(1);
+            cudaGraph_t g = nullptr;
+            const cudaError_t ce = cudaStreamEndCapture(ctx->stream, &g);
+            if (st_cap != B200_OK) {
+                if (g) cudaGraphDestroy(g);
+                return st_cap;
+            }
+            if (ce != cudaSuccess || !g) B200_FAIL(ctx, B200_CUDA_ERROR, "capturing the decode step failed: %s", cudaGetErrorString(ce));
+            m->loop_graph_launches = ctx->launches - l0;
+            ctx->launches = l0;  // capturing launched nothing
+            const cudaError_t ie = cudaGraphInstantiate(&m->loop_graph, g, 0);
+            cudaGraphDestroy(g);
+            if (ie != cudaSuccess) {
+                m->loop_graph = nullptr;
+                B200_FAIL(ctx, B200_CUDA_ERROR, "instantiating the decode step's graph failed: %s", cudaGetErrorString(ie));
+            }
+            m->loop_graph_S = S;
+            m->loop_graph_splits = key_splits;
+            m->loop_graph_adv = advance_pos;
+        }
+        for (; done < steps; done++) {
+            CUDA_TRY(ctx, cudaGraphLaunch(m->loop_graph, ctx->stream));
+            ctx->launches += m->loop_graph_launches;
+        }
     }
+    for (int st = done; st < steps; st++) ST_TRY(one_step(st));
     CUDA_TRY(ctx, cudaEventRecord(m->ev1, ctx->stream));
     CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids + m->MR, m->err_flag, 4, cudaMemcpyDeviceToHost, ctx->stream));
     CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));

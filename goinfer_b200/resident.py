@@ -304,6 +304,21 @@ class Resident:
         o = self.StepRagged([RaggedSeq(slot, start_pos, embs, tokens, None, RaggedPrefill(start_pos + n, True))])
         return o[0].Logits[-1]
 
+    def DecodeLoop(self, slots: Sequence[int], pos: Sequence[int], first_ids: Sequence[int], steps: int, log_ids: bool = True,
+                   advance: bool = True):
+        """`steps` greedy decode steps with the drawn ids fed back on the device (no host round trip between steps):
+        sequence i starts by feeding first_ids[i] at position pos[i]. Returns (ids [steps][n] or None, device ms).
+        Without log_ids the loop replays one captured CUDA graph from its second step on."""
+        n = len(slots)
+        sl = np.asarray(slots, np.int32)
+        ps = np.asarray(pos, np.int32)
+        fi = np.asarray(first_ids, np.int32)
+        ids = np.zeros((steps, n), np.int32) if log_ids else None
+        ms = C.c_float(0)
+        self._check(self.drv.fn("decode_loop_device")(self.m, n, _ptr(sl, C.c_int32), _ptr(ps, C.c_int32), _ptr(fi, C.c_int32), steps,
+                                                     1 if advance else 0, _ptr(ids, C.c_int32), C.byref(ms)))
+        return ids, ms.value
+
     def Stats(self) -> abi.Stats:
         s = abi.Stats()
         self._check(self.drv.fn("stats")(self.m, C.byref(s)))

@@ -194,6 +194,46 @@ def test_fast_class_prefill_run_kernel_in_a_ragged_step(oracle_lib, monkeypatch)
         assert ok, err
 
 
+@pytest.mark.parametrize("klass", [abi.CLASS_EXACT, abi.CLASS_AUTO])
+def test_device_decode_loop_equals_host_driven_steps(oracle_lib, klass):
+    """The resident decode loop (ids fed back on the device; what the benchmark's `value` times) draws the ids that
+    host-driven StepBatch calls draw, and, in the exact class, the oracle's. Run without the id log it replays a captured
+    CUDA graph from the second step on: the KV rows those replays wrote must carry a later logged continuation to the
+    same ids."""
+    g, o, s = build_pair(oracle_lib, "tiny-qknorm", n_slots=6, ctx_cap=96, seed=31, klass=klass)
+    rng = np.random.default_rng(12)
+    prompts = [rng.integers(0, s.vocab, n).tolist() for n in (9, 23, 40)]
+    first = []
+    for i, p in enumerate(prompts):
+        lg = g.PrefillLast(None, 0, i, p)
+        g.PrefillLast(None, 0, i + 3, p)
+        o.PrefillLast(None, 0, i, p)
+        first.append(int(np.argmax(lg)))
+    pos = [len(p) for p in prompts]
+    ids, ms = g.DecodeLoop([0, 1, 2], pos, first, steps=8)
+    assert ms > 0 and ids.shape == (8, 3)
+    # host-driven twin on the same GPU model (slots 3..5) and on the oracle
+    tok_g, tok_o = list(first), list(first)
+    for step in range(8):
+        bg = g.StepBatch([BatchSeq(i + 3, pos[i] + step, None, tok_g[i], BatchDraw(Greedy=True)) for i in range(3)])
+        tok_g = [b.ID for b in bg]
+        assert tok_g == ids[step].tolist(), step
+        if klass == abi.CLASS_EXACT:
+            bo = o.StepBatch([BatchSeq(i, pos[i] + step, None, tok_o[i], BatchDraw(Greedy=True)) for i in range(3)])
+            tok_o = [b.ID for b in bo]
+            assert tok_o == ids[step].tolist(), step
+    g.Close()
+    # the graph path: six unlogged steps (replays), then two logged ones fed the ids the logged run drew
+    g2, _, _ = build_pair(oracle_lib, "tiny-qknorm", n_slots=6, ctx_cap=96, seed=31, klass=klass)
+    for i, p in enumerate(prompts):
+        g2.PrefillLast(None, 0, i, p)
+    none, _ = g2.DecodeLoop([0, 1, 2], pos, first, steps=6, log_ids=False)
+    assert none is None
+    tail, _ = g2.DecodeLoop([0, 1, 2], [q + 6 for q in pos], ids[5].tolist(), steps=2)
+    assert tail.tolist() == ids[6:8].tolist()
+    g2.Close()
+
+
 def test_kv_pool_full_writes_nothing_and_bad_steps_are_refused(oracle_lib):
     g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=3, ctx_cap=64, seed=9, kv_pool_blocks=1 + 3)
     for r in (g, o):
