@@ -185,7 +185,7 @@ int launch_paged_attention(b200_ctx*, const float* q, int ldq, int T, int nH, in
 // gemm_umma.cu: the cached tensor map (a CUtensorMap, opaque here) of a Q4_K matrix seen as bytes [N][nSB*144], box of one
 // super-block x box_rows rows; null (and ctx->err) when the driver cannot encode it
 const struct CUtensorMap_st* q4k_weight_map(b200_ctx*, const uint8_t* W, int N, int nSB, int box_rows);
-// gemm_stream.cu: Q4_K x int8 for 4..32 rows, weights streamed through a TMA ring (exact arithmetic; split-K when splits > 1)
+// gemm_stream.cu: Q4_K x int8 for 4..64 rows, weights streamed through a TMA ring (exact arithmetic; split-K when splits > 1)
 int launch_q4k_matmul_stream(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, bool allow_split);
 // the same kernel over experts stacked in one buffer ([n_experts*N][K]) and expert-sorted activation rows
 bool q4k_stream_grouped_supported(const uint8_t* W_all, int N, int K);

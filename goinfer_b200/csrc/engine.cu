@@ -685,7 +685,7 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
         m->asc.max_splits = ceil_div(c.ctx_cap, attn_split_keys());
         ST_TRY(m->dalloc((void**)&m->asc.partial, attn_scratch_floats(MR, nH, hd, m->asc.max_splits) * 4, sb));
     }
-    if (c.kernel_class != B200_CLASS_EXACT && MR >= 64) {
+    if (c.kernel_class != B200_CLASS_EXACT && MR >= 4) {
         // fast class: scratch of the tcgen05 matmul (fp16 activations + split-K partials), sized for the widest projection
         int max_k = std::max(H, qd), max_n = std::max(ldq, H);
         if (F) { max_k = std::max(max_k, F); max_n = std::max(max_n, 2 * F); }

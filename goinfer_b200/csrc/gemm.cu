@@ -737,20 +737,22 @@ int run_q4k(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, int T, flo
 int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, int klass) {
     if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
     const int nSB = K / 256;
-    // Fast class from 64 rows (or when asked for by klass 2): tcgen05 fp16 matmul, if its scratch is in place.
-    if (klass != B200_CLASS_EXACT && (T >= 64 || klass == 2) && ctx->umma_scratch && !getenv("B200_NO_UMMA") &&
+    // Fast class from 33 rows (or when asked for by klass 2): tcgen05 fp16 matmul, if its scratch is in place. (Measured:
+    // at 45 rows it takes 111 us on a 28672x8192 matrix against 214 us for the integer kernels; below 33 rows the
+    // streaming integer kernel is the faster one.)
+    if (klass != B200_CLASS_EXACT && klass != 3 && klass != 4 && (T >= 33 || klass == 2) && ctx->umma_scratch && !getenv("B200_NO_UMMA") &&
         q4k_umma_scratch_bytes(T, K, N) <= ctx->umma_scratch_bytes)
         return launch_q4k_matmul_umma(ctx, W, N, K, aq, T, dst, ldd, ctx->umma_scratch, ctx->umma_scratch_bytes, ctx->err_flag);
     // Rows up to 8 are HBM-bound: split K over the CTA's warps (unless the exact class asks for the one ascending
     // chain per output that every larger batch uses, so a row's bits do not depend on its batch).
     if (T <= 8 && klass == B200_CLASS_EXACT) return run_q4k<1, false>(ctx, W, N, nSB, aq, T, dst, ldd);
-    if (klass == 4 && T <= 32 && (reinterpret_cast<uintptr_t>(W) & 15) == 0) return launch_q4k_matmul_stream(ctx, W, N, K, aq, T, dst, ldd, false);
+    if (klass == 4 && T <= 64 && (reinterpret_cast<uintptr_t>(W) & 15) == 0) return launch_q4k_matmul_stream(ctx, W, N, K, aq, T, dst, ldd, false);
     if (T == 1) return run_q4k_gemv<1>(ctx, W, N, nSB, aq, dst, ldd);
     if (T == 2) return run_q4k_gemv<2>(ctx, W, N, nSB, aq, dst, ldd);
     if (T == 3) return run_q4k_gemv<3>(ctx, W, N, nSB, aq, dst, ldd);
-    // 4..32 rows, fast class: the weights stream through a TMA ring (klass 3 forces the older kernels for comparison)
+    // 4..63 rows, fast class: the weights stream through a TMA ring (klass 3 forces the older kernels for comparison)
     static const bool no_stream = getenv("B200_NO_STREAM") != nullptr;
-    if (T <= 32 && klass != B200_CLASS_EXACT && klass != 3 && !no_stream && (reinterpret_cast<uintptr_t>(W) & 15) == 0)
+    if (T <= 63 && klass != B200_CLASS_EXACT && klass != 3 && !no_stream && (reinterpret_cast<uintptr_t>(W) & 15) == 0)
         return launch_q4k_matmul_stream(ctx, W, N, K, aq, T, dst, ldd, klass != 4);  // klass 4: the one-chain form (the exact class's bits)
     if (T <= 8) return run_q4k<1, true>(ctx, W, N, nSB, aq, T, dst, ldd);
     if (T <= 16) return run_q4k<2, false>(ctx, W, N, nSB, aq, T, dst, ldd);

@@ -1,4 +1,4 @@
-// gemm_stream.cu — Q4_K x per-32 int8 matmul for small row counts (4..32 rows), built to keep HBM busy.
+// gemm_stream.cu — Q4_K x per-32 int8 matmul for small row counts (4..63 rows), built to keep HBM busy.
 //
 //   dst[t][n] = sum over groups g of 32:  fma(idot(n,t,g), (d*sc_g)*aS[t][g], .) then fma(-(dmin*m_g), asum[t][g], .)
 //
@@ -28,7 +28,7 @@ constexpr int kSRows = 64, kSConsumers = 4, kSThreads = (kSConsumers + 1) * 32, 
 // copy engine's 128-byte swizzle (fragment loads of 8 rows then miss each other's banks), their 8 scales and their 8
 // group sums ([8*nt][32 B] each); rounded up to 1 KB so that every stage's swizzled halves sit on 1 KB boundaries
 __host__ __device__ constexpr int stream_stage_bytes(int nt) { return (kSWBytes + 8 * nt * (256 + 64) + 1023) / 1024 * 1024; }
-__host__ __device__ constexpr int stream_stages(int nt) { return nt <= 2 ? 4 : 3; }  // 48-58 KB per CTA: three or four CTAs per SM
+__host__ __device__ constexpr int stream_stages(int nt) { return nt <= 2 ? 4 : 3; }  // 48-87 KB per CTA: two to four CTAs per SM
 
 __device__ __forceinline__ unsigned s_byte(int k, unsigned s0, unsigned s1, unsigned s2) {
     unsigned w = k < 4 ? s0 : (k < 8 ? s1 : s2);
@@ -361,7 +361,7 @@ int launch_q4k_matmul_stream_grouped(b200_ctx* ctx, const uint8_t* W_all, int n_
 }
 
 int launch_q4k_matmul_stream(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, bool allow_split) {
-    if (K % 256 || T < 1 || T > 32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the streaming Q4_K matmul takes 1..32 rows and K %% 256 == 0");
+    if (K % 256 || T < 1 || T > 64) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the streaming Q4_K matmul takes 1..64 rows and K %% 256 == 0");
     if ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(aq.codes) | reinterpret_cast<uintptr_t>(aq.scales)) & 15)
         B200_FAIL(ctx, B200_BAD_ARGUMENT, "the streaming Q4_K matmul wants 16-byte aligned weights and activation buffers");
     const int nSB = K / 256, tiles = ceil_div(N, kSRows);
@@ -376,5 +376,6 @@ int launch_q4k_matmul_stream(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ
     float* part = reinterpret_cast<float*>(ctx->umma_scratch);
     if (T <= 8) return run_stream<1>(ctx, wmap, N, nSB, aq, T, dst, ldd, splits, part);
     if (T <= 16) return run_stream<2>(ctx, wmap, N, nSB, aq, T, dst, ldd, splits, part);
-    return run_stream<4>(ctx, wmap, N, nSB, aq, T, dst, ldd, splits, part);
+    if (T <= 32) return run_stream<4>(ctx, wmap, N, nSB, aq, T, dst, ldd, splits, part);
+    return run_stream<8>(ctx, wmap, N, nSB, aq, T, dst, ldd, splits, part);
 }

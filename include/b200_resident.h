@@ -238,7 +238,7 @@ int b200_op_quant_g32(b200_ctx* ctx, const float* x, int rows, int k, int8_t* co
 int b200_op_q4k_dequant(b200_ctx* ctx, const uint8_t* w, int rows, int cols, float* out);
 /* dst[M][N] = a[M][K] . W^T, W Q4_K [N][K]; activations quantized per 32 (actgroup.cu:311-355).
  * klass: 0 = library choice by M, 1 = exact kernels, 2 = fast (tcgen05 fp16) kernel; for kernel comparisons:
- * 3 = the register-direct kernels in place of the streaming one (4..32 rows), 4 = the streaming kernel in its
+ * 3 = the register-direct kernels in place of the streaming one (4..63 rows), 4 = the streaming kernel in its
  * one-chain form (the exact class's bits). */
 int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, int K, int N, int klass,
                        float* dst);

@@ -69,17 +69,15 @@ def test_q4k_matmul_exact_class(ops, oracle_lib, M):
     ref = oracle_lib.op_q4k_matmul_f64(raw, a, N)
     scale = np.abs(ref).max()
     assert np.abs(got - ref).max() <= 1e-5 * scale          # the reference's own GEMV bar
-    fast = ops.q4k_matmul(raw, a, N, klass=0)               # fast class: other kernels up to 8 and from 64 rows
-    if M < 64:
+    fast = ops.q4k_matmul(raw, a, N, klass=0)               # fast class: integer kernels up to 32 rows, tcgen05 fp16 from 33
+    if M <= 32:
         assert np.abs(fast - ref).max() <= 1e-5 * scale
         assert np.abs(fast - want).max() <= 2e-6 * scale
     else:
         assert np.abs(fast - ref).max() <= 4e-3 * scale     # tcgen05 fp16 operands
-    if 32 < M < 64:
-        assert np.array_equal(fast, got)
 
 
-@pytest.mark.parametrize("M,N,K", [(64, 256, 1024), (128, 384, 512), (200, 200, 1024), (256, 512, 2048), (300, 128, 256), (256, 640, 4096)])
+@pytest.mark.parametrize("M,N,K", [(33, 192, 512), (64, 256, 1024), (128, 384, 512), (200, 200, 1024), (256, 512, 2048), (300, 128, 256), (256, 640, 4096)])
 def test_q4k_matmul_fast_class_tcgen05(ops, oracle_lib, M, N, K):
     """The tcgen05/TMEM matmul of the fast class: both operands dequantized to fp16 (sub-block scale, minimum and
     activation each rounded to fp16; the weight's sub-block offset is rounded to fp16 as well, which is the larger
@@ -99,9 +97,9 @@ def test_q4k_matmul_fast_class_tcgen05(ops, oracle_lib, M, N, K):
     assert rel <= 2.5e-3, rel
 
 
-@pytest.mark.parametrize("M", [4, 7, 8, 9, 16, 17, 31, 32])
+@pytest.mark.parametrize("M", [4, 7, 8, 9, 16, 17, 31, 32, 33, 45, 63])
 def test_q4k_matmul_streaming_kernel(ops, oracle_lib, M):
-    """The kernel for 4..32 rows streams weights and activation rows through a TMA ring and keeps the exact class's
+    """The kernel for 4..63 rows streams weights and activation rows through a TMA ring and keeps the exact class's
     arithmetic. In its one-chain form (klass 4; also what the routed experts run) its bits are the oracle's. The fast
     class splits K between two groups of warps (and between CTAs for narrow matrices) and adds the chains in a fixed
     order: within f32 rounding of the oracle."""
@@ -114,7 +112,8 @@ def test_q4k_matmul_streaming_kernel(ops, oracle_lib, M):
         one_chain = ops.q4k_matmul(raw, a, N, klass=4)
         assert np.array_equal(want.view(np.uint32), one_chain.view(np.uint32))
         fast = ops.q4k_matmul(raw, a, N, klass=0)
-        assert np.abs(fast - want).max() <= 2e-6 * np.abs(want).max()
+        # up to 32 rows the fast class runs this kernel (K split between CTAs for narrow matrices); from 33 the tcgen05 one
+        assert np.abs(fast - want).max() <= (2e-6 if M <= 32 else 4e-3) * np.abs(want).max()
         assert np.array_equal(fast, ops.q4k_matmul(raw, a, N, klass=0))     # a fixed order: the same bits every time
 
 

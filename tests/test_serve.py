@@ -171,3 +171,22 @@ def test_drive_serves_a_trace_with_chunks_riding_runs():
     assert [s.last_id for s in trace3] == [s.last_id for s in trace]
     first_steps = [seqs[0][0] for kind, seqs in r3.steps if kind == "ragged"][:4]
     assert first_steps[0] == trace3[0].slot
+
+
+def test_admission_gate_is_a_pure_function_of_the_facts():
+    """decoder/admit.go:35-76: the order of the refusals, the name the Q4_K gate accepts, the activation-group gate."""
+    from goinfer_b200 import admit
+    ok = admit.admit(admit.AdmitFacts())
+    assert ok.Why == "" and ok.Shape == "" and ok.Gates == []
+    assert "does not implement residency" in admit.admit(admit.AdmitFacts(Residency=False, Backend="b200")).Why
+    # q4k is admitted by backend name: a shim registered under another name is refused before anything else is read
+    why = admit.admit(admit.AdmitFacts(Backend="b200", Shape="recurrent block")).Why
+    assert why == "--quant q4k (native Q4_K) has no resident kernel on b200 yet"
+    assert admit.admit(admit.AdmitFacts(Shape="recurrent block")).Why == "arch is not eligible for the resident decode runner: recurrent block"
+    assert admit.admit(admit.AdmitFacts(Gates=["router wider than 512 experts", "x"])).Why == "router wider than 512 experts"
+    assert admit.admit(admit.AdmitFacts(ActGroup=64)).Why == ""                    # CUDA residency honours any group
+    assert "ActQuantGroup 64" in admit.admit(admit.AdmitFacts(Backend="webgpu", QuantLabel="int8", ActGroup=64)).Why
+    assert admit.admit(admit.AdmitFacts(Backend="webgpu", QuantLabel="int8", ActGroup=0)).Why == ""
+    assert admit.admit_act_safe(admit.AdmitFacts()) and not admit.admit_act_safe(admit.AdmitFacts(ProjsInt4=True))
+    assert not admit.admit_act_safe(admit.AdmitFacts(ActGroup=0))
+    assert admit.admit_act_safe(admit.AdmitFacts(Backend="metal")) and not admit.admit_act_safe(admit.AdmitFacts(Backend="metal", QuantLabel="int8"))
