@@ -136,6 +136,18 @@ int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, i
     return us.check();
 }
 
+int b200_op_philox(b200_ctx* ctx, const uint32_t* ctr, const uint32_t* key, int n, uint32_t* out) {
+    if (n <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad count");
+    Tmp t;
+    uint32_t *dc, *dk, *dout;
+    TMP_GET(ctx, t, dc, (size_t)4 * n); TMP_GET(ctx, t, dk, (size_t)2 * n); TMP_GET(ctx, t, dout, (size_t)4 * n);
+    H2D(ctx, dc, ctr, (size_t)16 * n); H2D(ctx, dk, key, (size_t)8 * n);
+    ST_TRY(launch_philox(ctx, dc, dk, n, dout));
+    D2H(ctx, out, dout, (size_t)16 * n);
+    SYNC(ctx);
+    return B200_OK;
+}
+
 int b200_op_f16_matmul(b200_ctx* ctx, const uint16_t* w, const float* a, int M, int K, int N, int klass, float* dst) {
     if (M <= 0 || K <= 0 || N <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad matmul shape");
     Tmp t;

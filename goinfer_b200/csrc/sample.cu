@@ -47,6 +47,42 @@ __device__ __forceinline__ long long block_sum_i64(long long v, long long* red) 
     return t;
 }
 
+// Philox4x32-10 (Salmon et al., SC'11; internal/runtime/sampling/philox.go:21-36): integer only, so every backend draws the
+// same words. The key is bumped between rounds, not before the first.
+__device__ __forceinline__ void philox4x32(unsigned c0, unsigned c1, unsigned c2, unsigned c3, unsigned k0, unsigned k1, unsigned* out) {
+#pragma unroll
+    for (int r = 0; r < 10; r++) {
+        if (r > 0) { k0 += 0x9E3779B9u; k1 += 0xBB67AE85u; }
+        const unsigned hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        const unsigned hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        const unsigned n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+        c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+// 32 random bits -> a standard Gumbel variate, in f32 without cancellation (backend/cuda/gumbel.cu:50-60): with
+// w = (h + 0.5) / 2^32, E = -ln(1 - w) comes from log1p for h < 2^31 and from 1 - w = (~h + 0.5) / 2^32 (exact) above.
+__device__ __forceinline__ float gumbel_noise(unsigned h) {
+    float e;
+    if (h < 0x80000000u) {
+        const float w = __fmul_rn(__fadd_rn((float)h, 0.5f), 2.3283064365386963e-10f);
+        e = -log1pf(-w);
+    } else {
+        const float v = __fmul_rn(__fadd_rn((float)(~h), 0.5f), 2.3283064365386963e-10f);
+        e = -logf(v);
+    }
+    return -logf(e);
+}
+
+__global__ void philox_kernel(const uint32_t* __restrict__ ctr, const uint32_t* __restrict__ key, int n, uint32_t* __restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    unsigned r[4];
+    philox4x32(ctr[4 * i], ctr[4 * i + 1], ctr[4 * i + 2], ctr[4 * i + 3], key[2 * i], key[2 * i + 1], r);
+    for (int k = 0; k < 4; k++) out[4 * i + k] = r[k];
+}
+
 // One block per row.
 __global__ void __launch_bounds__(kDrawThreads) draw_kernel(const float* __restrict__ logits, int V,
                                                             const b200_draw* __restrict__ draws, int32_t* __restrict__ ids) {
@@ -90,6 +126,46 @@ __global__ void __launch_bounds__(kDrawThreads) draw_kernel(const float* __restr
     __syncthreads();
     if (dr.kind == B200_DRAW_GREEDY) {
         if (threadIdx.x == 0) ids[r] = s_arg;
+        return;
+    }
+    if (dr.kind == B200_DRAW_GUMBEL) {
+        // argmax_i(l_i * invT + G_i): a thread walks groups of four tokens (one Philox call each) in ascending order with a
+        // strict >, and ties between threads go to the lower index: the lowest index among the maxima, as on the host
+        // (sampler_gumbel.go:52-64). The seed and the draw index ride in the struct's bytes 8..23.
+        const unsigned* raw = reinterpret_cast<const unsigned*>(&draws[r]);
+        const unsigned k0 = raw[2], k1 = raw[3], d0 = raw[4], d1 = raw[5];
+        const float invT = dr.temperature;
+        float gb = -INFINITY;
+        int gi = -1;
+        for (int b = threadIdx.x; b * 4 < V; b += kDrawThreads) {
+            unsigned h[4];
+            philox4x32((unsigned)b, d0, d1, 0u, k0, k1, h);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int i = b * 4 + q;
+                if (i < V) {
+                    const float k = __fadd_rn(__fmul_rn(l[i], invT), gumbel_noise(h[q]));
+                    if (k > gb) { gb = k; gi = i; }
+                }
+            }
+        }
+        auto better = [](float ak, int ai, float bk, int bi2) { return ai >= 0 && (bi2 < 0 || ak > bk || (ak == bk && ai < bi2)); };
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ok_ = __shfl_xor_sync(0xffffffffu, gb, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, gi, o);
+            if (better(ok_, oi, gb, gi)) { gb = ok_; gi = oi; }
+        }
+        __syncthreads();  // s_val / s_idx were read by thread 0 above
+        if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = gb; s_idx[threadIdx.x >> 5] = gi; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float b = s_val[0];
+            int k = s_idx[0];
+            for (int w = 1; w < kDrawThreads / 32; w++)
+                if (better(s_val[w], s_idx[w], b, k)) { b = s_val[w]; k = s_idx[w]; }
+            ids[r] = k >= 0 ? k : s_arg;  // nothing comparable (an all -inf row): the plain argmax
+        }
         return;
     }
     // min-p
@@ -253,6 +329,12 @@ int launch_mask_logits(b200_ctx* ctx, float* logits, int R, int V, const int32_t
 
 int launch_draw(b200_ctx* ctx, const float* logits, int R, int V, const b200_draw* draws, int32_t* ids, float*) {
     draw_kernel<<<R, kDrawThreads, 0, ctx->stream>>>(logits, V, draws, ids);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_philox(b200_ctx* ctx, const uint32_t* ctr, const uint32_t* key, int n, uint32_t* out) {
+    philox_kernel<<<ceil_div(n, 128), 128, 0, ctx->stream>>>(ctr, key, n, out);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }

@@ -94,6 +94,13 @@ class Ops:
                                                block_rows, klass, _p(out, C.c_float)))
         return out
 
+    def philox(self, ctr, key):
+        c = np.ascontiguousarray(ctr, np.uint32).reshape(-1, 4)
+        k = np.ascontiguousarray(key, np.uint32).reshape(-1, 2)
+        out = np.empty_like(c)
+        self._check(self.lib.b200_op_philox(self.ctx, _p(c, C.c_uint32), _p(k, C.c_uint32), c.shape[0], _p(out, C.c_uint32)))
+        return out
+
     def f16_matmul(self, w, a, klass=0):
         """w f16 [N][K], a f32 [M][K] -> f32 [M][N]."""
         w = np.ascontiguousarray(w, np.float16)

@@ -60,13 +60,19 @@ def load_library() -> C.CDLL:
 
 @dataclass
 class BatchDraw:
-    """resident.BatchDraw plus the min-p fields this backend draws on-device."""
+    """resident.BatchDraw plus the draws this backend makes on the device: min-p with the host sampler's uniform, and
+    temperature-only Gumbel-max over the Philox stream (Seed, DrawIndex = Sampler.NextDraw)."""
     Greedy: bool = True
     Temperature: float = 1.0
     MinP: float = 0.0
     U: float = 0.0  # the uniform the host sampler drew for this token (min-p only)
+    Gumbel: bool = False
+    Seed: int = 0
+    DrawIndex: int = 0
 
     def to_c(self) -> abi.Draw:
+        if self.Gumbel:
+            return abi.gumbel_draw(self.Temperature, self.Seed, self.DrawIndex)
         if self.Greedy:
             return abi.Draw(abi.DRAW_GREEDY, 1.0, 0.0, 0.0, 0.0)
         return abi.Draw(abi.DRAW_MINP, self.Temperature, self.MinP, 0.0, self.U)

@@ -63,6 +63,12 @@ extern "C" {
 #define B200_DRAW_GREEDY 1 /* BatchDraw.Greedy: first maximal index (internal/runtime/sampling/sampler.go:485-518) */
 #define B200_DRAW_MINP   2 /* min-p retained set + CDF walk with the caller's uniform `u`
                               (sampler.go:586-724, drawFiltered :442-458)                            */
+#define B200_DRAW_GUMBEL 3 /* temperature-only sampling by Gumbel-max over Philox4x32-10 noise: argmax_i(l_i*invT + G_i)
+                              (internal/runtime/sampling/sampler_gumbel.go:37-64,104-110; philox.go:21-36;
+                              device twin backend/cuda/gumbel.cu). For this kind `temperature` carries invT =
+                              float32(1/T) as the host sampler computed it, the 8 bytes of {min_p, _pad} carry the
+                              64-bit seed and the 8 bytes of `u` the 64-bit draw index (Sampler.NextDraw); copy them
+                              in with memcpy. */
 
 /* ---- kernel classes (b200_model_cfg.kernel_class) -------------------------------------------------
  * The reference separates exact kernels from fast, non-bit-identical ones by a row floor
@@ -255,6 +261,8 @@ int b200_op_route(b200_ctx* ctx, const float* logits, int rows, int n_experts, i
 /* Draw over logits rows with optional masks (sampler.go:485-518, 586-724). */
 int b200_op_draw(b200_ctx* ctx, const float* logits, int rows, int vocab, const b200_draw* draws,
                  const int32_t* mask_index, const uint32_t* logit_mask, int n_masks, int32_t* ids);
+/* Philox4x32-10 (internal/runtime/sampling/philox.go:21-36) on the device: n (counter[4], key[2]) pairs -> out[4] each. */
+int b200_op_philox(b200_ctx* ctx, const uint32_t* ctr, const uint32_t* key, int n, uint32_t* out);
 /* Paged decode attention over caller-supplied contiguous K/V (f32 rounded to fp16 on upload):
  * q [rows][n_heads*head_dim]; row r attends keys [0, n_keys[r]) of its own K/V
  * (decoder/forwardn.go:295-501, acc64 branch). */

@@ -167,6 +167,22 @@ def op_draw(logits: np.ndarray, draws, mask_index=None, masks=None) -> np.ndarra
     return ids
 
 
+def op_philox(ctr: np.ndarray, key: np.ndarray) -> np.ndarray:
+    c = np.ascontiguousarray(ctr, np.uint32).reshape(-1, 4)
+    k = np.ascontiguousarray(key, np.uint32).reshape(-1, 2)
+    out = np.empty_like(c)
+    lib().oracle_op_philox(_p(c, C.c_uint32), _p(k, C.c_uint32), c.shape[0], _p(out, C.c_uint32))
+    return out
+
+
+def op_gumbel_keys(logits_row: np.ndarray, inv_t: float, seed: int, draw: int):
+    """-> (index the host draw picks or -1, every entry's key)."""
+    l = np.ascontiguousarray(logits_row, np.float32)
+    keys = np.empty_like(l)
+    idx = lib().oracle_op_gumbel_keys(_p(l, C.c_float), l.shape[0], C.c_float(inv_t), C.c_uint64(seed), C.c_uint64(draw), _p(keys, C.c_float))
+    return idx, keys
+
+
 def op_minp_set(logits_row: np.ndarray, temperature: float, min_p: float):
     l = np.ascontiguousarray(logits_row, np.float32)
     V = l.shape[0]

@@ -947,6 +947,59 @@ int oracle_op_route(const float* logits, int rows, int nE, int k, int norm, int3
     return B200_OK;
 }
 
+// Philox4x32-10 (internal/runtime/sampling/philox.go:21-36)
+static void philox4x32(const uint32_t ctr_in[4], const uint32_t key_in[2], uint32_t out[4]) {
+    uint32_t c[4] = {ctr_in[0], ctr_in[1], ctr_in[2], ctr_in[3]}, k0 = key_in[0], k1 = key_in[1];
+    for (int r = 0; r < 10; r++) {
+        if (r > 0) { k0 += 0x9E3779B9u; k1 += 0xBB67AE85u; }  // bumped between rounds, not before the first
+        const uint64_t p0 = (uint64_t)0xD2511F53u * c[0], p1 = (uint64_t)0xCD9E8D57u * c[2];
+        const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0, n1 = (uint32_t)p1, n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1, n3 = (uint32_t)p0;
+        c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+    }
+    memcpy(out, c, 16);
+}
+
+int oracle_op_philox(const uint32_t* ctr, const uint32_t* key, int n, uint32_t* out) {
+    for (int i = 0; i < n; i++) philox4x32(ctr + 4 * i, key + 2 * i, out + 4 * i);
+    return B200_OK;
+}
+
+// sampler_gumbel.go:37-48: 32 random bits -> a standard Gumbel variate (f64 transform), and one entry's key
+static float gumbel_noise(uint32_t h) {
+    const double w = ((double)h + 0.5) * (1.0 / 4294967296.0);
+    const double e = -log1p(-w);
+    return (float)(-log(e));
+}
+static float gumbel_key(float logit, float invT, uint32_t h) {
+    volatile float prod = logit * invT;  // the product is rounded to f32 before the add (no fused multiply-add)
+    return prod + gumbel_noise(h);
+}
+
+// sampler_gumbel.go:52-64,104-110: the draw over the whole row; ties to the lowest index; -1 (then the plain argmax)
+// when no entry is comparable. keys_out, if given, receives every entry's key.
+static int gumbel_draw(const float* logits, int V, float invT, uint64_t seed, uint64_t draw, float* keys_out) {
+    const uint32_t key[2] = {(uint32_t)seed, (uint32_t)(seed >> 32)};
+    float best = -INFINITY;
+    int idx = -1;
+    for (int b = 0; (b << 2) < V; b++) {
+        const uint32_t ctr[4] = {(uint32_t)b, (uint32_t)draw, (uint32_t)(draw >> 32), 0};
+        uint32_t r[4];
+        philox4x32(ctr, key, r);
+        for (int lane = 0; lane < 4; lane++) {
+            const int i = (b << 2) + lane;
+            if (i >= V) continue;
+            const float k = gumbel_key(logits[i], invT, r[lane]);
+            if (keys_out) keys_out[i] = k;
+            if (k > best) { best = k; idx = i; }
+        }
+    }
+    return idx;
+}
+
+int oracle_op_gumbel_keys(const float* logits, int vocab, float invT, uint64_t seed, uint64_t draw, float* keys) {
+    return gumbel_draw(logits, vocab, invT, seed, draw, keys);
+}
+
 int oracle_op_draw(const float* logits, int rows, int vocab, const b200_draw* draws, const int32_t* mask_index,
                    const uint32_t* logit_mask, int n_masks, int32_t* ids) {
     const int words = (vocab + 31) / 32;
@@ -959,7 +1012,13 @@ int oracle_op_draw(const float* logits, int rows, int vocab, const b200_draw* dr
                 if (!((mk[t >> 5] >> (t & 31)) & 1u)) row[t] = -INFINITY;
         }
         if (draws[r].kind == B200_DRAW_MINP) ids[r] = draw_minp(row.data(), vocab, draws[r].temperature, draws[r].min_p, draws[r].u, nullptr);
-        else ids[r] = argmax(row.data(), vocab);
+        else if (draws[r].kind == B200_DRAW_GUMBEL) {
+            uint64_t seed, draw;
+            memcpy(&seed, (const char*)&draws[r] + 8, 8);
+            memcpy(&draw, (const char*)&draws[r] + 16, 8);
+            const int id = gumbel_draw(row.data(), vocab, draws[r].temperature, seed, draw, nullptr);
+            ids[r] = id >= 0 ? id : argmax(row.data(), vocab);
+        } else ids[r] = argmax(row.data(), vocab);
     }
     return B200_OK;
 }

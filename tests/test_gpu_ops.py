@@ -319,3 +319,42 @@ def test_attention_properties_at_full_context(ops):
     for r in range(rows):
         k2[r, n_keys[r]:] = 1e4          # poison the keys outside the causal range
     assert np.array_equal(ops.attention(q, k2, v1, n_keys, nH, nKV, hd), o1)
+
+
+def test_philox_and_gumbel_draw_on_the_device(ops, oracle_lib):
+    """Philox4x32-10 is integer-only: the device's words are the oracle's, bit for bit (and the oracle's are the
+    Random123 known answers). The Gumbel-max draw then differs from the host's only in the float transform (f32 here,
+    f64 there), which can change the argmax only when the two best keys are within a few ulps: the reference measures
+    that rate rather than assuming it (backend/cuda/gumbel.cu:3-8), and so does this test."""
+    rng = np.random.default_rng(17)
+    ctr = rng.integers(0, 2**32, (500, 4), dtype=np.uint64).astype(np.uint32)
+    key = rng.integers(0, 2**32, (500, 2), dtype=np.uint64).astype(np.uint32)
+    ctr[0], key[0] = 0, 0
+    ctr[1], key[1] = 0xffffffff, 0xffffffff
+    got = ops.philox(ctr, key)
+    assert np.array_equal(got, oracle_lib.op_philox(ctr, key))
+    assert got[0].tolist() == [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]
+    assert got[1].tolist() == [0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd]
+    V, rows = 32003, 400                                     # a vocabulary that is not a multiple of 4
+    lg = rng.normal(0, 2.0, (rows, V)).astype(np.float32)
+    lg[3] = -np.inf                                          # nothing comparable: the plain argmax
+    lg[4, 100:200] = lg[4].max() + 50                        # a hundred-way tie far above the noise range: not all keys equal, one winner
+    draws = [abi.gumbel_draw(0.5 + (r % 7) * 0.25, 1000 + r // 50, r) for r in range(rows)]
+    want = oracle_lib.op_draw(lg, draws)
+    got = ops.draw(lg, draws)
+    assert got[3] == want[3] == 0
+    diff = np.nonzero(want != got)[0]
+    assert len(diff) <= 2, len(diff)                         # measured: f32 vs f64 noise flips well under 1% of rows
+    for r in diff:                                           # and only between keys that are f32 neighbours
+        inv_t = np.float32(1.0 / (0.5 + (r % 7) * 0.25))
+        _, keys = oracle_lib.op_gumbel_keys(lg[r], float(inv_t), 1000 + r // 50, int(r))
+        assert abs(keys[want[r]] - keys[got[r]]) <= 4e-6 * abs(keys[want[r]])
+    # masks apply before the draw: a masked-out winner cannot be drawn
+    words = (V + 31) // 32
+    mask = np.full((1, words), 0xFFFFFFFF, np.uint32)
+    w0 = int(want[0])
+    mask[0, w0 >> 5] &= ~np.uint32(1 << (w0 & 31))
+    mi = np.full(rows, -1, np.int32)
+    mi[0] = 0
+    gm = ops.draw(lg, draws, mi, mask)
+    assert gm[0] != w0 and gm[0] == oracle_lib.op_draw(lg, draws, mi, mask)[0]

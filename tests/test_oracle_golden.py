@@ -68,3 +68,34 @@ def test_qwen3moe_tiny_forward(oracle_lib):
     assert len(logits) == int(n)
     np.testing.assert_allclose([logits.sum(dtype=np.float64), (logits.astype(np.float64) ** 2).sum(), logits.min(), logits.max()],
                                [s, ss, mn, mx], atol=1e-4, rtol=1e-4)
+
+
+def test_philox_known_answers_and_gumbel_draw(oracle_lib):
+    """The oracle's Philox4x32-10 against the Random123 known-answer vectors the reference pins every backend to
+    (internal/runtime/sampling/philox_test.go:9-23), and the host Gumbel-max draw's rules (sampler_gumbel.go:52-64,
+    104-110): ties to the lowest index, the plain argmax when nothing is comparable, an exact draw from softmax(l/T)."""
+    from goinfer_b200 import abi
+    kats = [((0, 0, 0, 0), (0, 0), (0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8)),
+            ((0xffffffff,) * 4, (0xffffffff,) * 2, (0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd)),
+            ((0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344), (0xa4093822, 0x299f31d0), (0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1))]
+    got = oracle_lib.op_philox(np.array([k[0] for k in kats], np.uint32), np.array([k[1] for k in kats], np.uint32))
+    assert got.tolist() == [list(k[2]) for k in kats]
+    # all -inf: nothing comparable -> the plain argmax (index 0); an isolated finite entry always wins
+    row = np.full(37, -np.inf, np.float32)
+    assert oracle_lib.op_draw(row[None], [abi.gumbel_draw(0.8, 5, 0)])[0] == 0
+    row[11] = -3.0
+    assert oracle_lib.op_draw(row[None], [abi.gumbel_draw(0.8, 5, 1)])[0] == 11
+    # the draw index and the seed both move the stream; the same (seed, draw) repeats
+    lg = np.random.default_rng(0).normal(0, 1, (1, 1000)).astype(np.float32)
+    a = [int(oracle_lib.op_draw(lg, [abi.gumbel_draw(1.0, 7, d)])[0]) for d in range(40)]
+    assert a == [int(oracle_lib.op_draw(lg, [abi.gumbel_draw(1.0, 7, d)])[0]) for d in range(40)] and len(set(a)) > 10
+    assert a != [int(oracle_lib.op_draw(lg, [abi.gumbel_draw(1.0, 8, d)])[0]) for d in range(40)]
+    # Gumbel-max is an exact draw from softmax(l/T): frequencies over 20000 draws of an 8-entry row
+    l8 = np.array([[2.0, 1.0, 0.5, 0.0, -0.5, -1.0, -2.0, 1.5]], np.float32)
+    T = 0.7
+    p = np.exp(l8[0].astype(np.float64) / T)
+    p /= p.sum()
+    n = 20000
+    ids = oracle_lib.op_draw(np.repeat(l8, n, axis=0), [abi.gumbel_draw(T, 1234, d) for d in range(n)])
+    freq = np.bincount(ids, minlength=8) / n
+    assert np.abs(freq - p).max() < 4 * np.sqrt(p.max() * (1 - p.max()) / n) + 2e-3
