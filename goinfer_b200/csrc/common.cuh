@@ -213,6 +213,7 @@ int launch_paged_attention_exact(b200_ctx*, const float* q, int ldq, int T, int 
 // sample.cu
 int launch_mask_logits(b200_ctx*, float* logits, int R, int V, const int32_t* row_mask, const uint32_t* masks);
 int launch_draw(b200_ctx*, const float* logits, int R, int V, const b200_draw* draws, int32_t* ids, float* scratch);
+int launch_topk(b200_ctx*, const float* logits, int R, int V, int k, float invT, bool want_z, int32_t* ids, float* vals, double* z);
 int launch_philox(b200_ctx*, const uint32_t* ctr, const uint32_t* key, int n, uint32_t* out);
 int launch_route(b200_ctx*, const float* logits, int T, int nE, int k, int norm, int32_t* idx, float* wts);
 int launch_group_experts(b200_ctx*, const int32_t* idx, int T, int k, int nE, int32_t* offs, int32_t* rows);

@@ -188,6 +188,7 @@ struct b200_model {
     size_t umma_bytes = 0;
     int* err_flag = nullptr;       // raised by a bounded device-side wait that gave up
     float* exact_scores = nullptr;  // exact class: [MR*nH][ctx_cap]
+    void* d_topk = nullptr;  // ForwardTopK's outputs: 1024 ids, 1024 logits, Z
     float *logits_local = nullptr, *logits_gather = nullptr;  // tensor parallel: [MLR][V/t] and the gathered [t][MLR][V/t]
     // the step's leading prefill run (rows of one slot at consecutive positions), 0 rows when there is none;
     // pf_tail_keys = the longest key range among the rows after it
@@ -1029,6 +1030,29 @@ int b200_forward(b200_model* m, int slot, const float* emb, int token_id, int po
                               out_kind == 0 ? logits_out : nullptr, &id, nullptr);
     if (id_out) *id_out = id;
     return st;
+}
+
+int b200_forward_topk(b200_model* m, int slot, const float* emb, int token_id, int pos, int k, float inv_temperature,
+                      int32_t* ids_out, float* logits_out, double* z_out) {
+    b200_ctx* ctx = m->ctx;
+    if (!ids_out || !logits_out) B200_FAIL(ctx, B200_BAD_ARGUMENT, "top-K needs its output buffers");
+    // the row's logits stay on the device (a greedy-draw step reads nothing back but an id); the selection runs over them
+    const int32_t one = 1, s = slot, p = pos, tok = token_id;
+    b200_draw dr{B200_DRAW_GREEDY, 0, 0, 0, 0};
+    int32_t id = -1;
+    ST_TRY(b200_step_ragged(m, 1, &s, &p, &one, nullptr, nullptr, emb, emb ? nullptr : &tok, &dr, nullptr, nullptr, 0, nullptr, &id, nullptr));
+    if (!m->d_topk) {
+        ST_TRY(m->dalloc((void**)&m->d_topk, (size_t)1024 * 8 + 8, &m->scratch_bytes));
+    }
+    int32_t* di = reinterpret_cast<int32_t*>(m->d_topk);
+    float* dv = reinterpret_cast<float*>(di + 1024);
+    double* dz = reinterpret_cast<double*>(dv + 1024);
+    ST_TRY(launch_topk(ctx, m->logits, 1, m->c.vocab, k, inv_temperature, z_out != nullptr, di, dv, dz));
+    CUDA_TRY(ctx, cudaMemcpyAsync(ids_out, di, (size_t)k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(logits_out, dv, (size_t)k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (z_out) CUDA_TRY(ctx, cudaMemcpyAsync(z_out, dz, 8, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return B200_OK;
 }
 
 int b200_prefill_last(b200_model* m, int slot, int n, const float* embs, const int32_t* token_ids, int start_pos, float* logits_out) {

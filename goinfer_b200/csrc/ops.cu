@@ -136,6 +136,22 @@ int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, i
     return us.check();
 }
 
+int b200_op_topk(b200_ctx* ctx, const float* logits, int rows, int vocab, int k, float inv_temperature, int32_t* ids_out,
+                 float* logits_out, double* z_out) {
+    if (rows <= 0 || vocab <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad top-K shape");
+    Tmp t;
+    float *dl, *dv; int32_t* di; double* dz;
+    TMP_GET(ctx, t, dl, (size_t)rows * vocab); TMP_GET(ctx, t, dv, (size_t)rows * k); TMP_GET(ctx, t, di, (size_t)rows * k);
+    TMP_GET(ctx, t, dz, (size_t)rows);
+    H2D(ctx, dl, logits, (size_t)rows * vocab * 4);
+    ST_TRY(launch_topk(ctx, dl, rows, vocab, k, inv_temperature, z_out != nullptr, di, dv, dz));
+    D2H(ctx, ids_out, di, (size_t)rows * k * 4);
+    D2H(ctx, logits_out, dv, (size_t)rows * k * 4);
+    if (z_out) D2H(ctx, z_out, dz, (size_t)rows * 8);
+    SYNC(ctx);
+    return B200_OK;
+}
+
 int b200_op_philox(b200_ctx* ctx, const uint32_t* ctr, const uint32_t* key, int n, uint32_t* out) {
     if (n <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad count");
     Tmp t;

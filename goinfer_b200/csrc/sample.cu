@@ -75,6 +75,125 @@ __device__ __forceinline__ float gumbel_noise(unsigned h) {
     return -logf(e);
 }
 
+// ---- top-K rows (decoder/resident/subsystems.go:40-48, forward.go:91-96; device twin backend/cuda/topk.cu) ----
+// The K highest logits of a row ordered (logit descending, token id ascending), and Z = sum exp((l - max) * invT) over
+// the whole row. -0 and +0 tie, as on the host. One block per row: an exact 3-pass radix select (11 + 11 + 10 bits of an
+// order-preserving key) finds the K-th largest key; every entry above it and the first `need` entries equal to it by
+// ascending id are gathered and a bitonic sort orders the K survivors.
+constexpr int kTopKThreads = 1024, kTopKMax = 1024;
+
+__device__ __forceinline__ unsigned topk_key(float x) {
+    if (x == 0.0f) x = 0.0f;  // -0 -> +0
+    const unsigned u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(kTopKThreads) topk_kernel(const float* __restrict__ logits, int V, int K, float invT, int want_z,
+                                                            int32_t* __restrict__ ids, float* __restrict__ vals, double* __restrict__ z) {
+    __shared__ unsigned hist[2048];
+    __shared__ unsigned long long cand[kTopKMax];  // (key << 32) | ~id : sorts by key desc, id asc when sorted descending
+    __shared__ unsigned s_prefix, s_need, s_cnt_gt, s_cnt_eq;
+    __shared__ double s_red[kTopKThreads / 32];
+    __shared__ float s_maxv;
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float* l = logits + (size_t)r * V;
+    // radix select: after the passes, s_prefix is the K-th largest key and s_need how many entries equal to it are kept
+    unsigned prefix = 0, need = (unsigned)K;
+    const int shifts[3] = {21, 10, 0}, bits[3] = {11, 11, 10};
+    unsigned mask_hi = 0;  // the bits already fixed
+    for (int pass = 0; pass < 3; pass++) {
+        const int nb = 1 << bits[pass];
+        for (int i = tid; i < nb; i += kTopKThreads) hist[i] = 0;
+        __syncthreads();
+        for (int i = tid; i < V; i += kTopKThreads) {
+            const unsigned k = topk_key(l[i]);
+            if ((k & mask_hi) == prefix) atomicAdd(&hist[(k >> shifts[pass]) & (nb - 1)], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {  // walk the bins from the top: the bin where the running count reaches `need`
+            unsigned run = 0;
+            int b = nb - 1;
+            for (; b > 0; b--) {
+                if (run + hist[b] >= need) break;
+                run += hist[b];
+            }
+            s_prefix = prefix | ((unsigned)b << shifts[pass]);
+            s_need = need - run;
+        }
+        __syncthreads();
+        prefix = s_prefix;
+        need = s_need;
+        mask_hi |= (unsigned)(nb - 1) << shifts[pass];
+        __syncthreads();
+    }
+    // gather: every key above the K-th, in any order; then the `need` lowest ids among the equal ones
+    if (tid == 0) { s_cnt_gt = 0; s_cnt_eq = 0; }
+    __syncthreads();
+    const unsigned n_gt = (unsigned)K - need;
+    for (int i = tid; i < V; i += kTopKThreads) {
+        const unsigned k = topk_key(l[i]);
+        if (k > prefix) cand[atomicAdd(&s_cnt_gt, 1u)] = ((unsigned long long)k << 32) | (unsigned)(~i);
+    }
+    __syncthreads();
+    // equal keys by ascending id: a block-wide ordered scan in chunks of the block size
+    for (int base = 0; base < V && s_cnt_eq < need; base += kTopKThreads) {
+        const int i = base + tid;
+        const bool eq = i < V && topk_key(l[i]) == prefix;
+        // rank among this chunk's equal entries (ids ascend with tid)
+        const unsigned bal = __ballot_sync(0xffffffffu, eq);
+        const int lane = tid & 31, warp = tid >> 5;
+        if (lane == 0) hist[warp] = __popc(bal);
+        __syncthreads();
+        unsigned before = 0;
+        for (int w = 0; w < warp; w++) before += hist[w];
+        const unsigned rank = s_cnt_eq + before + __popc(bal & ((1u << lane) - 1));
+        unsigned chunk_total = 0;
+        for (int w = 0; w < kTopKThreads / 32; w++) chunk_total += hist[w];
+        if (eq && rank < need) cand[n_gt + rank] = ((unsigned long long)prefix << 32) | (unsigned)(~i);
+        __syncthreads();
+        if (tid == 0) s_cnt_eq += chunk_total;
+        __syncthreads();
+    }
+    // pad to a power of two and bitonic sort descending
+    int n2 = 1;
+    while (n2 < K) n2 <<= 1;
+    for (int i = K + tid; i < n2; i += kTopKThreads) cand[i] = 0ull;
+    __syncthreads();
+    for (int size = 2; size <= n2; size <<= 1)
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = tid; i < n2; i += kTopKThreads) {
+                const int j = i ^ stride;
+                if (j > i) {
+                    const bool desc = (i & size) == 0;
+                    const unsigned long long a = cand[i], b = cand[j];
+                    if (desc ? a < b : a > b) { cand[i] = b; cand[j] = a; }
+                }
+            }
+            __syncthreads();
+        }
+    for (int i = tid; i < K; i += kTopKThreads) {
+        const int id = (int)(~(unsigned)(cand[i] & 0xffffffffull));
+        ids[(size_t)r * K + i] = id;
+        vals[(size_t)r * K + i] = l[id];
+    }
+    if (want_z) {
+        if (tid == 0) s_maxv = l[(int)(~(unsigned)(cand[0] & 0xffffffffull))];
+        __syncthreads();
+        const double mx = (double)s_maxv, it = (double)invT;
+        double acc = 0;
+        for (int i = tid; i < V; i += kTopKThreads) acc += exp(((double)l[i] - mx) * it);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if ((tid & 31) == 0) s_red[tid >> 5] = acc;
+        __syncthreads();
+        if (tid == 0) {
+            double t = 0;
+            for (int w = 0; w < kTopKThreads / 32; w++) t += s_red[w];
+            z[r] = t;
+        }
+    }
+}
+
 __global__ void philox_kernel(const uint32_t* __restrict__ ctr, const uint32_t* __restrict__ key, int n, uint32_t* __restrict__ out) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
@@ -329,6 +448,13 @@ int launch_mask_logits(b200_ctx* ctx, float* logits, int R, int V, const int32_t
 
 int launch_draw(b200_ctx* ctx, const float* logits, int R, int V, const b200_draw* draws, int32_t* ids, float*) {
     draw_kernel<<<R, kDrawThreads, 0, ctx->stream>>>(logits, V, draws, ids);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_topk(b200_ctx* ctx, const float* logits, int R, int V, int k, float invT, bool want_z, int32_t* ids, float* vals, double* z) {
+    if (k < 1 || k > kTopKMax || k > V) B200_FAIL(ctx, B200_BAD_ARGUMENT, "top-K takes 1 <= k <= min(%d, vocab)", kTopKMax);
+    topk_kernel<<<R, kTopKThreads, 0, ctx->stream>>>(logits, V, k, invT, want_z ? 1 : 0, ids, vals, z);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }

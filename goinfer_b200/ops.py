@@ -94,6 +94,16 @@ class Ops:
                                                block_rows, klass, _p(out, C.c_float)))
         return out
 
+    def topk(self, logits, k, inv_t=1.0):
+        l = np.ascontiguousarray(logits, np.float32)
+        rows, V = l.shape
+        ids = np.empty((rows, k), np.int32)
+        vals = np.empty((rows, k), np.float32)
+        z = np.empty(rows, np.float64)
+        self._check(self.lib.b200_op_topk(self.ctx, _p(l, C.c_float), rows, V, k, C.c_float(inv_t), _p(ids, C.c_int32), _p(vals, C.c_float),
+                                          _p(z, C.c_double)))
+        return ids, vals, z
+
     def philox(self, ctr, key):
         c = np.ascontiguousarray(ctr, np.uint32).reshape(-1, 4)
         k = np.ascontiguousarray(key, np.uint32).reshape(-1, 2)

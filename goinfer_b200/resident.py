@@ -304,6 +304,19 @@ class Resident:
     def ForwardArgmax(self, emb: Optional[np.ndarray], pos: int, slot: int = 0, token: Optional[int] = None) -> int:
         return self.StepBatch([BatchSeq(slot, pos, emb, token, BatchDraw(Greedy=True))])[0].ID
 
+    def ForwardTopK(self, emb: Optional[np.ndarray], pos: int, k: int, temperature: float = 1.0, want_z: bool = True, slot: int = 0,
+                    token: Optional[int] = None):
+        """DecodeSubsystem.ForwardTopK: the k best (ids, logits) of the row, ordered (logit desc, id asc), and Z."""
+        ids = np.empty(k, np.int32)
+        vals = np.empty(k, np.float32)
+        z = C.c_double(0)
+        e = None if emb is None else np.ascontiguousarray(emb, np.float32)
+        inv_t = float(np.float32(1.0 / (temperature if temperature > 0 else 1.0)))
+        self._check(self.drv.fn("forward_topk")(self.m, slot, _ptr(e, C.c_float), -1 if token is None else int(token), pos, k,
+                                               C.c_float(inv_t), _ptr(ids, C.c_int32), _ptr(vals, C.c_float),
+                                               C.byref(z) if want_z else None))
+        return ids, vals, (z.value if want_z else None)
+
     def PrefillLast(self, embs: Optional[np.ndarray], start_pos: int, slot: int = 0,
                     tokens: Optional[Sequence[int]] = None) -> np.ndarray:
         n = len(embs) if embs is not None else len(tokens)

@@ -210,6 +210,10 @@ int b200_step_ragged(b200_model* m, int n_seqs, const int32_t* slot, const int32
 int b200_forward(b200_model* m, int slot, const float* emb, int token_id, int pos, int out_kind,
                  float* logits_out, int32_t* id_out);
 /* PrefillSubsystem.PrefillLast: n rows from start_pos on one slot, logits of the last row. */
+/* DecodeSubsystem.ForwardTopK (decoder/resident/subsystems.go:40-48): one row at `pos`, only its k best logits (and Z when
+ * z_out is not NULL) come back instead of the vocabulary-wide row. inv_temperature = float32(1/T). */
+int b200_forward_topk(b200_model* m, int slot, const float* emb, int token_id, int pos, int k, float inv_temperature,
+                      int32_t* ids_out, float* logits_out, double* z_out);
 int b200_prefill_last(b200_model* m, int slot, int n, const float* embs, const int32_t* token_ids,
                       int start_pos, float* logits_out);
 
@@ -261,6 +265,11 @@ int b200_op_route(b200_ctx* ctx, const float* logits, int rows, int n_experts, i
 /* Draw over logits rows with optional masks (sampler.go:485-518, 586-724). */
 int b200_op_draw(b200_ctx* ctx, const float* logits, int rows, int vocab, const b200_draw* draws,
                  const int32_t* mask_index, const uint32_t* logit_mask, int n_masks, int32_t* ids);
+/* The k best logits of each row ordered (logit descending, token id ascending; -0 and +0 tie) and, when z_out is not
+ * NULL, Z = sum exp((l - max) * inv_temperature) over the whole row (decoder/resident/forward.go:91-96; device twin
+ * backend/cuda/topk.cu). 1 <= k <= min(1024, vocab). */
+int b200_op_topk(b200_ctx* ctx, const float* logits, int rows, int vocab, int k, float inv_temperature,
+                 int32_t* ids_out, float* logits_out, double* z_out);
 /* Philox4x32-10 (internal/runtime/sampling/philox.go:21-36) on the device: n (counter[4], key[2]) pairs -> out[4] each. */
 int b200_op_philox(b200_ctx* ctx, const uint32_t* ctr, const uint32_t* key, int n, uint32_t* out);
 /* Paged decode attention over caller-supplied contiguous K/V (f32 rounded to fp16 on upload):

@@ -167,6 +167,16 @@ def op_draw(logits: np.ndarray, draws, mask_index=None, masks=None) -> np.ndarra
     return ids
 
 
+def op_topk(logits: np.ndarray, k: int, inv_t: float = 1.0):
+    l = np.ascontiguousarray(logits, np.float32)
+    rows, V = l.shape
+    ids = np.empty((rows, k), np.int32)
+    vals = np.empty((rows, k), np.float32)
+    z = np.empty(rows, np.float64)
+    lib().oracle_op_topk(_p(l, C.c_float), rows, V, k, C.c_float(inv_t), _p(ids, C.c_int32), _p(vals, C.c_float), _p(z, C.c_double))
+    return ids, vals, z
+
+
 def op_philox(ctr: np.ndarray, key: np.ndarray) -> np.ndarray:
     c = np.ascontiguousarray(ctr, np.uint32).reshape(-1, 4)
     k = np.ascontiguousarray(key, np.uint32).reshape(-1, 2)

@@ -959,6 +959,27 @@ static void philox4x32(const uint32_t ctr_in[4], const uint32_t key_in[2], uint3
     memcpy(out, c, 16);
 }
 
+// decoder topKByLogit's order: (logit descending, id ascending), -0 == +0; Z = sum exp((l - max) * invT) in f64
+int oracle_op_topk(const float* logits, int rows, int vocab, int k, float invT, int32_t* ids, float* vals, double* z) {
+    std::vector<int> order(vocab);
+    for (int r = 0; r < rows; r++) {
+        const float* l = logits + (size_t)r * vocab;
+        for (int i = 0; i < vocab; i++) order[i] = i;
+        std::partial_sort(order.begin(), order.begin() + k, order.end(), [&](int a, int b) {
+            if (l[a] != l[b]) return l[a] > l[b];
+            return a < b;
+        });
+        for (int i = 0; i < k; i++) { ids[(size_t)r * k + i] = order[i]; vals[(size_t)r * k + i] = l[order[i]]; }
+        if (z) {
+            const double mx = l[order[0]];
+            double acc = 0;
+            for (int i = 0; i < vocab; i++) acc += exp(((double)l[i] - mx) * (double)invT);
+            z[r] = acc;
+        }
+    }
+    return B200_OK;
+}
+
 int oracle_op_philox(const uint32_t* ctr, const uint32_t* key, int n, uint32_t* out) {
     for (int i = 0; i < n; i++) philox4x32(ctr + 4 * i, key + 2 * i, out + 4 * i);
     return B200_OK;

@@ -234,6 +234,23 @@ def test_device_decode_loop_equals_host_driven_steps(oracle_lib, klass):
     g2.Close()
 
 
+def test_forward_topk_and_gumbel_sample_in_a_step(oracle_lib):
+    """ForwardTopK returns the k best of the row Forward returns (same order as the host's); a Gumbel draw in a batched
+    step draws the id the host draw picks from that row's logits (DecodeSubsystem.ForwardTopK / ForwardSample,
+    decoder/resident/subsystems.go:40-60)."""
+    g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=4, ctx_cap=64, seed=17)
+    p = np.random.default_rng(5).integers(0, s.vocab, 21).tolist()
+    for i in range(3):
+        g.PrefillLast(None, 0, i, p)
+    full = g.Forward(None, 21, 0, token=7)
+    ids, vals, z = g.ForwardTopK(None, 21, 16, temperature=0.8, slot=1, token=7)
+    wi, wv, wz = oracle_lib.op_topk(full[None], 16, float(np.float32(1 / 0.8)))
+    assert np.array_equal(ids, wi[0]) and np.array_equal(vals, wv[0]) and abs(z - wz[0]) <= 1e-12 * wz[0]
+    out = g.StepBatch([BatchSeq(2, 21, None, 7, BatchDraw(Gumbel=True, Temperature=0.8, Seed=99, DrawIndex=4))])
+    want = oracle_lib.op_draw(full[None], [abi.gumbel_draw(0.8, 99, 4)])[0]
+    assert out[0].ID == want and out[0].Logits is None
+
+
 def test_kv_pool_full_writes_nothing_and_bad_steps_are_refused(oracle_lib):
     g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=3, ctx_cap=64, seed=9, kv_pool_blocks=1 + 3)
     for r in (g, o):

@@ -358,3 +358,22 @@ def test_philox_and_gumbel_draw_on_the_device(ops, oracle_lib):
     mi[0] = 0
     gm = ops.draw(lg, draws, mi, mask)
     assert gm[0] != w0 and gm[0] == oracle_lib.op_draw(lg, draws, mi, mask)[0]
+
+
+@pytest.mark.parametrize("V,k", [(32003, 40), (151936, 256), (1000, 1000), (5000, 1), (70000, 1024)])
+def test_topk_rows_match_the_host_order(ops, oracle_lib, V, k):
+    """The K best logits ordered (logit descending, token id ascending) with -0 and +0 tied, and the whole-row Z
+    (decoder/resident/forward.go:91-96; the tie order is a contract: it feeds the host's cumulative draw)."""
+    rng = np.random.default_rng(V + k)
+    lg = rng.normal(0, 3.0, (4, V)).astype(np.float32)
+    lg[1] = np.round(lg[1])                       # heavy ties, many of them across the K boundary
+    lg[1, ::7] = -0.0
+    lg[1, 3::7] = 0.0
+    lg[2, : V // 2] = -np.inf
+    lg[3] = 1.25                                  # everything ties: the K lowest ids
+    want_i, want_v, want_z = oracle_lib.op_topk(lg, k, 1.0 / 0.7)
+    got_i, got_v, got_z = ops.topk(lg, k, 1.0 / 0.7)
+    assert np.array_equal(got_i, want_i)
+    assert np.array_equal(got_v.view(np.uint32), want_v.view(np.uint32))
+    np.testing.assert_allclose(got_z, want_z, rtol=1e-12)
+    assert got_i[3].tolist() == list(range(k))
