@@ -47,8 +47,9 @@ struct LayerW {
 };
 
 __global__ void init_pool_kernel(int32_t* free_stack, int32_t* free_count, int blocks, int32_t* table, size_t table_n,
-                                 int32_t* slot_mapped, int n_slots) {
+                                 int32_t* slot_mapped, int n_slots, int32_t* refs) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < (size_t)blocks) refs[i] = 0;
     // take pops the last entry: ascending ids 1..blocks-1 (backend/cuda/kvpool.go:50-64)
     if (i < (size_t)blocks - 1) free_stack[i] = (int32_t)(blocks - 1 - i);
     if (i < table_n) table[i] = 0;
@@ -57,16 +58,67 @@ __global__ void init_pool_kernel(int32_t* free_stack, int32_t* free_count, int b
 }
 
 __global__ void reset_slot_kernel(int32_t* free_stack, int32_t* free_count, int32_t* table, int max_blocks,
-                                  int32_t* slot_mapped, int slot) {
-    // single thread: unref in table order, each freed block appended (kvpool.go:58-64)
+                                  int32_t* slot_mapped, int slot, int32_t* refs) {
+    // single thread: unref in table order, a block whose last reference goes is appended (kvpool.go:58-64,78-84)
     int n = slot_mapped[slot], fc = *free_count;
     int32_t* t = table + (size_t)slot * max_blocks;
     for (int b = 0; b < n; b++) {
-        if (t[b]) free_stack[fc++] = t[b];
+        if (t[b] && --refs[t[b]] <= 0) {
+            refs[t[b]] = 0;
+            free_stack[fc++] = t[b];
+        }
         t[b] = 0;
     }
     *free_count = fc;
     slot_mapped[slot] = 0;
+}
+
+// dst (empty) takes the first n_full blocks of src by reference and, when tail is set, a block of its own for the rows
+// of src's next block that it keeps (the caller copies them): backend/cuda/kvpool.go:511-536 (kvShare).
+__global__ void share_prefix_kernel(int32_t* table, int max_blocks, int32_t* slot_mapped, int32_t* refs, int32_t* free_stack,
+                                    int32_t* free_count, int src, int dst, int n_full, int tail) {
+    const int32_t* st = table + (size_t)src * max_blocks;
+    int32_t* dt = table + (size_t)dst * max_blocks;
+    for (int b = 0; b < n_full; b++) {
+        dt[b] = st[b];
+        refs[st[b]]++;
+    }
+    int fc = *free_count;
+    if (tail) {
+        const int32_t id = free_stack[--fc];
+        refs[id] = 1;
+        dt[n_full] = id;
+    }
+    *free_count = fc;
+    slot_mapped[dst] = n_full + (tail ? 1 : 0);
+}
+
+// A slot about to write into blocks [b_lo, b_hi) that other tables also name takes blocks of its own first
+// (kvpool.go:436-477, kvMap): the caller copies the rows it keeps.
+__global__ void cow_kernel(int32_t* table, int max_blocks, int32_t* refs, int32_t* free_stack, int32_t* free_count, int slot, int b_lo,
+                           int b_hi) {
+    int32_t* t = table + (size_t)slot * max_blocks;
+    int fc = *free_count;
+    for (int b = b_lo; b < b_hi; b++) {
+        const int32_t old = t[b];
+        if (old && refs[old] > 1) {
+            const int32_t id = free_stack[--fc];
+            refs[id] = 1;
+            refs[old]--;
+            t[b] = id;
+        }
+    }
+    *free_count = fc;
+}
+
+// rows [0, rows) of block `from` -> block `to`, every kv head, K and V of one layer (exact copies)
+__global__ void copy_block_rows_kernel(__half* kpool, __half* vpool, int from, int to, int rows, int nKV, int block_rows, int hd) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, n = (size_t)nKV * rows * hd;
+    if (i >= n) return;
+    const int e = (int)(i % hd), r = (int)((i / hd) % rows), kvh = (int)(i / ((size_t)hd * rows));
+    const size_t so = (((size_t)from * nKV + kvh) * block_rows + r) * hd + e, dn = (((size_t)to * nKV + kvh) * block_rows + r) * hd + e;
+    kpool[dn] = kpool[so];
+    vpool[dn] = vpool[so];
 }
 
 // Descriptor layout (int32 words): [0] n_seqs, [1] T, then slot[S], pos[S], nrows[S] with S = n_seqs.
@@ -76,7 +128,8 @@ __global__ void __launch_bounds__(256) prepare_step_kernel(const int32_t* __rest
                                                            int block_rows, int32_t* __restrict__ slot_mapped,
                                                            int32_t* __restrict__ free_stack, int32_t* __restrict__ free_count,
                                                            int32_t* __restrict__ seq_row0, int32_t* __restrict__ row_slot,
-                                                           int32_t* __restrict__ row_pos, int32_t* __restrict__ status) {
+                                                           int32_t* __restrict__ row_pos, int32_t* __restrict__ status,
+                                                           int32_t* __restrict__ refs) {
     const int S = desc[0], T = desc[1];
     const int32_t* slot = desc + 2;
     const int32_t* pos = use_pos_dev ? pos_dev : desc + 2 + S;
@@ -92,6 +145,7 @@ __global__ void __launch_bounds__(256) prepare_step_kernel(const int32_t* __rest
             for (int b = mapped; b < need; b++) {
                 if (fc <= 0 || b >= max_blocks) { bad = 1; break; }  // the host counters rule this out
                 t[b] = free_stack[--fc];
+                refs[t[b]] = 1;
             }
             if (need > mapped) slot_mapped[slot[i]] = need;
         }
@@ -171,6 +225,49 @@ struct b200_model {
     int max_blocks = 0;
     std::vector<int> h_slot_len, h_slot_mapped;
     int h_free = 0;
+    // The host's mirror of the device allocator (same order of pops and pushes, so the same ids): what lets the host count a
+    // step's block needs before anything is launched, shared and copy-on-write blocks included, and name blocks to copy.
+    int32_t* refs = nullptr;                 // device: tables naming each block
+    std::vector<int32_t> h_table, h_refs, h_stack;
+    int32_t h_pop() {
+        const int32_t id = h_stack.back();
+        h_stack.pop_back();
+        h_refs[id] = 1;
+        h_free--;
+        return id;
+    }
+    void h_unref(int32_t id) {
+        if (id && --h_refs[id] <= 0) {
+            h_refs[id] = 0;
+            h_stack.push_back(id);
+            h_free++;
+        }
+    }
+    int32_t* h_tab(int slot) { return h_table.data() + (size_t)slot * max_blocks; }
+    void h_pool_init() {
+        h_table.assign((size_t)c.n_slots * max_blocks, 0);
+        h_refs.assign(c.kv_pool_blocks, 0);
+        h_stack.clear();
+        for (int b = c.kv_pool_blocks - 1; b >= 1; b--) h_stack.push_back(b);
+        h_free = c.kv_pool_blocks - 1;
+    }
+    // the mirror of what prepare_step_kernel does for rows up to `end` of a slot
+    void h_append(int slot, int end) {
+        const int need = (end + c.kv_block_rows - 1) / c.kv_block_rows;
+        for (int b = h_slot_mapped[slot]; b < need; b++) h_tab(slot)[b] = h_pop();
+        if (need > h_slot_mapped[slot]) h_slot_mapped[slot] = need;
+        h_slot_len[slot] = std::max(h_slot_len[slot], end);
+    }
+    // blocks of [pos, end) that other tables also name: each costs a block of the slot's own before it is written
+    int h_cow_need(int slot, int pos, int end) const {
+        const int B = c.kv_block_rows, b_hi = std::min(h_slot_mapped[slot], (end + B - 1) / B);
+        int n = 0;
+        for (int b = pos / B; b < b_hi; b++) {
+            const int32_t id = h_table[(size_t)slot * max_blocks + b];
+            if (id && h_refs[id] > 1) n++;
+        }
+        return n;
+    }
 
     // step buffers (device)
     int MR = 0, MLR = 0;  // max rows, max logit rows per head chunk
@@ -628,10 +725,12 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
     ST_TRY(m->dalloc((void**)&m->free_stack, (size_t)c.kv_pool_blocks * 4, &m->kv_bytes));
     ST_TRY(m->dalloc((void**)&m->free_count, 4, nullptr));
     ST_TRY(m->dalloc((void**)&m->slot_mapped, (size_t)c.n_slots * 4, nullptr));
+    ST_TRY(m->dalloc((void**)&m->refs, (size_t)c.kv_pool_blocks * 4, &m->kv_bytes));
     ST_TRY(m->dalloc((void**)&m->status, 4, nullptr));
     CUDA_TRY(ctx, cudaMemsetAsync(m->status, 0, 4, ctx->stream));
     m->h_slot_len.assign(c.n_slots, 0);
     m->h_slot_mapped.assign(c.n_slots, 0);
+    m->h_pool_init();
     // step buffers
     const int MR = m->MR = std::max(1, c.max_rows);
     const int MLR = m->MLR = std::min(MR, std::max(c.n_slots, 64));
@@ -744,9 +843,12 @@ int b200_kv_slots(b200_model* m) { return m->c.n_slots; }
 int b200_reset_slot(b200_model* m, int slot) {
     b200_ctx* ctx = m->ctx;
     if (!m->finalized || slot < 0 || slot >= m->c.n_slots) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad slot %d", slot);
-    reset_slot_kernel<<<1, 1, 0, ctx->stream>>>(m->free_stack, m->free_count, m->table, m->max_blocks, m->slot_mapped, slot);
+    reset_slot_kernel<<<1, 1, 0, ctx->stream>>>(m->free_stack, m->free_count, m->table, m->max_blocks, m->slot_mapped, slot, m->refs);
     LAUNCH_CHECK(ctx);
-    m->h_free += m->h_slot_mapped[slot];
+    for (int b = 0; b < m->h_slot_mapped[slot]; b++) {
+        m->h_unref(m->h_tab(slot)[b]);
+        m->h_tab(slot)[b] = 0;
+    }
     m->h_slot_mapped[slot] = 0;
     m->h_slot_len[slot] = 0;
     return B200_OK;
@@ -758,11 +860,11 @@ int b200_reset(b200_model* m) {
     const size_t tn = (size_t)m->c.n_slots * m->max_blocks;
     const size_t n = std::max<size_t>(std::max<size_t>(tn, m->c.kv_pool_blocks), m->c.n_slots);
     init_pool_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(m->free_stack, m->free_count, m->c.kv_pool_blocks,
-                                                                           m->table, tn, m->slot_mapped, m->c.n_slots);
+                                                                           m->table, tn, m->slot_mapped, m->c.n_slots, m->refs);
     LAUNCH_CHECK(ctx);
     std::fill(m->h_slot_len.begin(), m->h_slot_len.end(), 0);
     std::fill(m->h_slot_mapped.begin(), m->h_slot_mapped.end(), 0);
-    m->h_free = m->c.kv_pool_blocks - 1;
+    m->h_pool_init();
     return B200_OK;
 }
 
@@ -785,22 +887,61 @@ int blocks_needed(const b200_model* m, int slot, int end) {
     return std::max(0, ceil_div(end, m->c.kv_block_rows) - m->h_slot_mapped[slot]);
 }
 
-// Maps the blocks of rows [0, end) of one slot on the device (used by the KV upload/synthesis entry points).
-int map_slot_rows(b200_model* m, int slot, int end) {
+// rows [0, rows) of block `from` -> block `to` in every layer
+int copy_block_rows(b200_model* m, int from, int to, int rows) {
     b200_ctx* ctx = m->ctx;
-    const int need = blocks_needed(m, slot, end);
+    const b200_model_cfg& c = m->c;
+    if (rows <= 0) return B200_OK;
+    const size_t n = (size_t)c.n_kv_heads * rows * c.head_dim;
+    for (int l = 0; l < c.n_layers; l++) {
+        copy_block_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(m->kpool[l], m->vpool[l], from, to, rows, c.n_kv_heads,
+                                                                                    c.kv_block_rows, c.head_dim);
+        LAUNCH_CHECK(ctx);
+    }
+    return B200_OK;
+}
+
+// Before a slot writes rows [pos, end): blocks of that range other tables also name are replaced by blocks of its own, the
+// rows before pos kept (backend/cuda/kvpool.go:436-477). The caller has counted the blocks this takes (h_cow_need).
+int make_private(b200_model* m, int slot, int pos, int end) {
+    b200_ctx* ctx = m->ctx;
+    if (m->h_cow_need(slot, pos, end) == 0) return B200_OK;
+    const int B = m->c.kv_block_rows, b_lo = pos / B, b_hi = std::min(m->h_slot_mapped[slot], ceil_div(end, B));
+    cow_kernel<<<1, 1, 0, ctx->stream>>>(m->table, m->max_blocks, m->refs, m->free_stack, m->free_count, slot, b_lo, b_hi);
+    LAUNCH_CHECK(ctx);
+    for (int b = b_lo; b < b_hi; b++) {
+        const int32_t old = m->h_tab(slot)[b];
+        if (old && m->h_refs[old] > 1) {
+            const int32_t id = m->h_pop();
+            m->h_refs[old]--;
+            m->h_tab(slot)[b] = id;
+            if (b == b_lo) ST_TRY(copy_block_rows(m, old, id, pos - b * B));
+        }
+    }
+    return B200_OK;
+}
+
+// Maps the blocks of rows [0, end) of one slot on the device and makes the blocks of [base, end) its own (used by the KV
+// upload/synthesis entry points, which write those rows).
+int map_slot_rows(b200_model* m, int slot, int base, int end) {
+    b200_ctx* ctx = m->ctx;
+    const int fresh = blocks_needed(m, slot, end), need = fresh + m->h_cow_need(slot, base, end);
     if (need > m->h_free) { m->stats.kv_pool_full++; B200_FAIL(ctx, B200_KV_POOL_FULL, "kv pool full: %d blocks needed, %d free", need, m->h_free); }
-    if (need == 0) return B200_OK;
+    ST_TRY(make_private(m, slot, base, end));
+    if (fresh == 0) return B200_OK;
     int32_t* d = m->p_desc;
     d[0] = 1; d[1] = 1; d[2] = slot; d[3] = end - 1; d[4] = 1;
     CUDA_TRY(ctx, cudaMemcpyAsync(m->d_desc, d, 5 * 4, cudaMemcpyHostToDevice, ctx->stream));
     prepare_step_kernel<<<1, 256, 0, ctx->stream>>>(m->d_desc, m->d_pos, 0, m->table, m->max_blocks, m->c.kv_block_rows,
                                                     m->slot_mapped, m->free_stack, m->free_count, m->d_seq_row0, m->d_row_slot,
-                                                    m->d_row_pos, m->status);
+                                                    m->d_row_pos, m->status, m->refs);
     LAUNCH_CHECK(ctx);
     CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));  // p_desc is reused by the next call
-    m->h_free -= need;
-    m->h_slot_mapped[slot] += need;
+    {
+        const int keep_len = m->h_slot_len[slot];
+        m->h_append(slot, end);
+        m->h_slot_len[slot] = keep_len;  // the callers set the stored length themselves
+    }
     return B200_OK;
 }
 
@@ -813,7 +954,7 @@ int b200_synth_kv(b200_model* m, int slot, int n_pos, float sigma, uint64_t seed
     const b200_model_cfg& c = m->c;
     if (!m->finalized || slot < 0 || slot >= c.n_slots || n_pos < 0 || n_pos > c.ctx_cap) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad slot or length");
     if (n_pos == 0) return B200_OK;
-    ST_TRY(map_slot_rows(m, slot, n_pos));
+    ST_TRY(map_slot_rows(m, slot, 0, n_pos));
     const size_t n = (size_t)n_pos * c.n_kv_heads * c.head_dim;
     for (int l = 0; l < c.n_layers; l++) {
         synth_kv_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(m->kpool[l], m->vpool[l],
@@ -831,7 +972,7 @@ int b200_upload_kv(b200_model* m, int slot, int layer, int base, int n, const fl
     const b200_model_cfg& c = m->c;
     if (!m->finalized || slot < 0 || slot >= c.n_slots || layer < 0 || layer >= c.n_layers || base < 0 || n <= 0 || base + n > c.ctx_cap)
         B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad slot, layer or range");
-    ST_TRY(map_slot_rows(m, slot, base + n));
+    ST_TRY(map_slot_rows(m, slot, base, base + n));
     const size_t cnt = (size_t)n * c.n_kv_heads * c.head_dim;
     float *dk = nullptr, *dv = nullptr;
     CUDA_TRY(ctx, cudaMalloc(&dk, cnt * 4));
@@ -846,6 +987,47 @@ int b200_upload_kv(b200_model* m, int slot, int layer, int base, int n, const fl
     cudaFree(dk);
     cudaFree(dv);
     m->h_slot_len[slot] = std::max(m->h_slot_len[slot], base + n);
+    return B200_OK;
+}
+
+int b200_copy_kv(b200_model* m, int dst_slot, int src_slot, int n_rows) {
+    b200_ctx* ctx = m->ctx;
+    const b200_model_cfg& c = m->c;
+    if (!m->finalized || dst_slot < 0 || dst_slot >= c.n_slots || src_slot < 0 || src_slot >= c.n_slots || dst_slot == src_slot)
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad slots %d <- %d", dst_slot, src_slot);
+    if (n_rows < 0 || n_rows > m->h_slot_len[src_slot]) B200_FAIL(ctx, B200_BAD_ARGUMENT, "slot %d stores %d rows, %d asked", src_slot, m->h_slot_len[src_slot], n_rows);
+    const int B = c.kv_block_rows, n_full = n_rows / B, tail = n_rows % B;
+    // what dst holds now goes back to the pool first (in the mirror too), then the budget is checked: nothing is written on refusal
+    const int freed_after_reset = [&] {
+        int n = 0;
+        for (int b = 0; b < m->h_slot_mapped[dst_slot]; b++) {
+            const int32_t id = m->h_tab(dst_slot)[b];
+            if (id && m->h_refs[id] == 1) n++;
+        }
+        return n;
+    }();
+    if ((tail ? 1 : 0) > m->h_free + freed_after_reset) {
+        m->stats.kv_pool_full++;
+        B200_FAIL(ctx, B200_KV_POOL_FULL, "kv pool full: 1 block needed, %d free", m->h_free + freed_after_reset);
+    }
+    ST_TRY(b200_reset_slot(m, dst_slot));
+    if (n_rows == 0) return B200_OK;
+    share_prefix_kernel<<<1, 1, 0, ctx->stream>>>(m->table, m->max_blocks, m->slot_mapped, m->refs, m->free_stack, m->free_count, src_slot,
+                                                  dst_slot, n_full, tail ? 1 : 0);
+    LAUNCH_CHECK(ctx);
+    for (int b = 0; b < n_full; b++) {
+        const int32_t id = m->h_tab(src_slot)[b];
+        m->h_tab(dst_slot)[b] = id;
+        m->h_refs[id]++;
+    }
+    m->h_slot_mapped[dst_slot] = n_full;
+    if (tail) {
+        const int32_t id = m->h_pop();
+        m->h_tab(dst_slot)[n_full] = id;
+        m->h_slot_mapped[dst_slot] = n_full + 1;
+        ST_TRY(copy_block_rows(m, m->h_tab(src_slot)[n_full], id, tail));
+    }
+    m->h_slot_len[dst_slot] = n_rows;
     return B200_OK;
 }
 
@@ -878,7 +1060,7 @@ int b200_step_ragged(b200_model* m, int n_seqs, const int32_t* slot, const int32
                 if (last != (pos[i] + n_rows[i] == pl)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the chunk ends at %d of a %d-row prompt with Last %d", pos[i] + n_rows[i], pl, (int)last);
             }
             T += n_rows[i];
-            need += blocks_needed(m, slot[i], pos[i] + n_rows[i]);
+            need += blocks_needed(m, slot[i], pos[i] + n_rows[i]) + m->h_cow_need(slot[i], pos[i], pos[i] + n_rows[i]);
             max_keys = std::max(max_keys, pos[i] + n_rows[i]);
         }
     }
@@ -954,17 +1136,13 @@ int b200_step_ragged(b200_model* m, int n_seqs, const int32_t* slot, const int32
         CUDA_TRY(ctx, cudaMemcpyAsync(m->h, embs, (size_t)T * H * 4, cudaMemcpyHostToDevice, ctx->stream));
     }
     // ---- device: map blocks, build row arrays, run the layers ----
+    for (int i = 0; i < n_seqs; i++) ST_TRY(make_private(m, slot[i], pos[i], pos[i] + n_rows[i]));  // blocks shared with other slots
     prepare_step_kernel<<<1, 256, 0, ctx->stream>>>(m->d_desc, m->d_pos, 0, m->table, m->max_blocks, c.kv_block_rows,
                                                     m->slot_mapped, m->free_stack, m->free_count, m->d_seq_row0, m->d_row_slot,
-                                                    m->d_row_pos, m->status);
+                                                    m->d_row_pos, m->status, m->refs);
     LAUNCH_CHECK(ctx);
     // the host counters follow what the kernel does
-    for (int i = 0; i < n_seqs; i++) {
-        const int nb = blocks_needed(m, slot[i], pos[i] + n_rows[i]);
-        m->h_free -= nb;
-        m->h_slot_mapped[slot[i]] += nb;
-        m->h_slot_len[slot[i]] = std::max(m->h_slot_len[slot[i]], pos[i] + n_rows[i]);
-    }
+    for (int i = 0; i < n_seqs; i++) m->h_append(slot[i], pos[i] + n_rows[i]);
     if (token_ids) ST_TRY(launch_embed_gather(ctx, m->embed.p, m->embed.kind, m->d_tokens, T, H, c.embed_scale, m->h));
     // the first sequence's rows, when they are many, form the tiled prefill run (fast class only)
     m->pf_rows = 0;
@@ -1076,11 +1254,12 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
             const int end = pos0[i] + (advance_pos ? steps : 1);
             if (pos0[i] < 0 || end > c.ctx_cap || pos0[i] > m->h_slot_len[slot[i]]) B200_FAIL(ctx, B200_BAD_ARGUMENT, "sequence %d outside its slot", i);
             if (first_ids[i] < 0 || first_ids[i] >= V) B200_FAIL(ctx, B200_BAD_ARGUMENT, "token id out of range");
-            need += blocks_needed(m, slot[i], end);
+            need += blocks_needed(m, slot[i], end) + m->h_cow_need(slot[i], pos0[i], end);
             max_keys = std::max(max_keys, end);
         }
     }
     if (need > m->h_free) { m->stats.kv_pool_full++; B200_FAIL(ctx, B200_KV_POOL_FULL, "kv pool full: %d blocks needed, %d free", need, m->h_free); }
+    for (int i = 0; i < S; i++) ST_TRY(make_private(m, slot[i], pos0[i], pos0[i] + (advance_pos ? steps : 1)));
     if (ids_out && !m->d_ids_log) ST_TRY(m->dalloc((void**)&m->d_ids_log, (size_t)m->MR * 4, &m->scratch_bytes));
     int32_t* d = m->p_desc;
     d[0] = S; d[1] = S;
@@ -1102,7 +1281,7 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
     auto one_step = [&](int st) -> int {
         prepare_step_kernel<<<1, 256, 0, ctx->stream>>>(m->d_desc, m->d_pos, 1, m->table, m->max_blocks, c.kv_block_rows,
                                                         m->slot_mapped, m->free_stack, m->free_count, m->d_seq_row0,
-                                                        m->d_row_slot, m->d_row_pos, m->status);
+                                                        m->d_row_slot, m->d_row_pos, m->status, m->refs);
         LAUNCH_CHECK(ctx);
         ST_TRY(launch_embed_gather(ctx, m->embed.p, m->embed.kind, m->d_tokens, S, H, c.embed_scale, m->h));
         ST_TRY(run_layers(m, S, max_keys));
@@ -1169,13 +1348,7 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
     cudaEventElapsedTime(&ms, m->ev0, m->ev1);
     if (ms_out) *ms_out = ms;
     if (ids_out) memcpy(ids_out, log.data(), log.size() * 4);
-    for (int i = 0; i < S; i++) {
-        const int end = pos0[i] + (advance_pos ? steps : 1);
-        const int nb = blocks_needed(m, slot[i], end);
-        m->h_free -= nb;
-        m->h_slot_mapped[slot[i]] += nb;
-        m->h_slot_len[slot[i]] = std::max(m->h_slot_len[slot[i]], end);
-    }
+    for (int i = 0; i < S; i++) m->h_append(slot[i], pos0[i] + (advance_pos ? steps : 1));
     m->stats.steps += steps;
     m->stats.rows += (int64_t)steps * S;
     m->stats.last_step_device_ms = ms / steps;

@@ -227,6 +227,10 @@ class Resident:
         self._check(self.drv.fn("upload_kv")(self.m, slot, layer, base, k.shape[0], _ptr(k, C.c_float),
                                              _ptr(v, C.c_float)))
 
+    def CopyKV(self, dst: int, src: int, n_rows: int):
+        """KVSubsystem.CopyKV: dst is reset and then holds src's first n_rows rows (whole blocks shared, copy on write)."""
+        self._check(self.drv.fn("copy_kv")(self.m, dst, src, n_rows))
+
     def SynthKV(self, slot: int, n_pos: int, sigma: float, seed: int):
         self._check(self.drv.fn("synth_kv")(self.m, slot, n_pos, C.c_float(sigma), C.c_uint64(seed)))
 

@@ -214,6 +214,13 @@ int b200_forward(b200_model* m, int slot, const float* emb, int token_id, int po
  * z_out is not NULL) come back instead of the vocabulary-wide row. inv_temperature = float32(1/T). */
 int b200_forward_topk(b200_model* m, int slot, const float* emb, int token_id, int pos, int k, float inv_temperature,
                       int32_t* ids_out, float* logits_out, double* z_out);
+/* Prefix reuse over paged blocks (KVSubsystem.CopyKV; backend/cuda/kvpool.go:16-27,436-536): dst_slot is reset and then
+ * holds the first n_rows rows of src_slot. Whole blocks are shared by reference (a block counts the tables that name it
+ * and goes back to the pool when the last one lets go); the rows of a partial last block are copied into a block of
+ * dst's own. A slot that later writes into a block another table also names first takes a block of its own and keeps
+ * the rows before the write (copy on write), so no slot ever writes a block another slot reads.
+ * B200_KV_POOL_FULL (nothing changed) when the one block this may take is not there. */
+int b200_copy_kv(b200_model* m, int dst_slot, int src_slot, int n_rows);
 int b200_prefill_last(b200_model* m, int slot, int n, const float* embs, const int32_t* token_ids,
                       int start_pos, float* logits_out);
 

@@ -439,6 +439,20 @@ struct oracle_model {
     std::vector<Layer> layers;
     std::vector<Slot> slots;
     std::vector<int32_t> free_blocks;  // take pops the last: ascending ids (kvpool.go:50-64)
+    std::vector<int32_t> refs;         // the tables that name each block (kvpool.go:42-44,78-84)
+    int32_t take() { const int32_t b = free_blocks.back(); free_blocks.pop_back(); refs[b] = 1; return b; }
+    void unref(int32_t b) { if (b && --refs[b] <= 0) { refs[b] = 0; free_blocks.push_back(b); } }
+    // blocks of rows [pos, end) of a slot's table that other tables also name
+    int cow_need(const std::vector<int32_t>& t, int pos, int end) const {
+        int n = 0;
+        for (int b = pos / c.kv_block_rows; b < (end + c.kv_block_rows - 1) / c.kv_block_rows && b < (int)t.size(); b++) n += t[b] && refs[t[b]] > 1;
+        return n;
+    }
+    // a slot about to write rows [pos, end) takes blocks of its own for the shared ones first (kvpool.go:436-477)
+    void make_private(std::vector<int32_t>& t, int pos, int end) {
+        for (int b = pos / c.kv_block_rows; b < (end + c.kv_block_rows - 1) / c.kv_block_rows && b < (int)t.size(); b++)
+            if (t[b] && refs[t[b]] > 1) { const int32_t id = take(); refs[t[b]]--; t[b] = id; }
+    }
     std::string err;
     float kv_round(float x) const { return c.kv_dtype == 1 ? x : f16_to_f32(f32_to_f16(x)); }
     double scale() const { return c.attn_scale != 0.f ? (double)c.attn_scale : 1.0 / std::sqrt((double)c.head_dim); }
@@ -547,6 +561,7 @@ int oracle_model_create(const b200_model_cfg* cfg, oracle_model** out) {
         s.table.assign(maxBlocks, 0);
     }
     for (int b = cfg->kv_pool_blocks - 1; b >= 1; b--) m->free_blocks.push_back(b);
+    m->refs.assign(cfg->kv_pool_blocks, 0);
     *out = m;
     return B200_OK;
 }
@@ -584,8 +599,8 @@ int oracle_set_rope_inv_freq(oracle_model* m, int layer, const double* f, int n)
 int oracle_reset_slot(oracle_model* m, int slot) {
     if (slot < 0 || slot >= m->c.n_slots) return B200_BAD_ARGUMENT;
     Slot& s = m->slots[slot];
-    for (auto& b : s.table) {  // unref in table order; each freed block is appended (kvpool.go:58-64)
-        if (b) m->free_blocks.push_back(b);
+    for (auto& b : s.table) {  // unref in table order; a block whose last reference goes is appended (kvpool.go:58-64,78-84)
+        m->unref(b);
         b = 0;
     }
     for (auto& k : s.k) k.clear();
@@ -598,6 +613,7 @@ int oracle_reset(oracle_model* m) {
     // A full reset rebuilds the pool, so block ids are handed out ascending again.
     m->free_blocks.clear();
     for (int b = m->c.kv_pool_blocks - 1; b >= 1; b--) m->free_blocks.push_back(b);
+    m->refs.assign(m->c.kv_pool_blocks, 0);
     return B200_OK;
 }
 
@@ -610,15 +626,37 @@ int oracle_block_table(oracle_model* m, int slot, int32_t* out, int n) {
 
 int oracle_free_blocks(oracle_model* m) { return (int)m->free_blocks.size(); }
 
+// KVSubsystem.CopyKV over the block tables of backend/cuda/kvpool.go:511-536: dst is reset, shares src's whole blocks of
+// rows [0, n) by reference and takes one block of its own for a partial last block; the rows themselves are copied.
+int oracle_copy_kv(oracle_model* m, int dst, int src, int n) {
+    if (dst < 0 || dst >= m->c.n_slots || src < 0 || src >= m->c.n_slots || dst == src || n < 0) return B200_BAD_ARGUMENT;
+    const int kvDim = m->c.n_kv_heads * m->c.head_dim, B = m->c.kv_block_rows;
+    Slot& d = m->slots[dst];
+    const Slot& s = m->slots[src];
+    if ((size_t)n * kvDim > s.k[0].size()) { m->err = "more rows asked than the source stores"; return B200_BAD_ARGUMENT; }
+    int freed = 0;
+    for (int32_t b : d.table) freed += b && m->refs[b] == 1;
+    if ((n % B ? 1 : 0) > (int)m->free_blocks.size() + freed) return B200_KV_POOL_FULL;
+    oracle_reset_slot(m, dst);
+    for (int b = 0; b < n / B; b++) { d.table[b] = s.table[b]; m->refs[s.table[b]]++; }
+    if (n % B) d.table[n / B] = m->take();
+    for (int l = 0; l < m->c.n_layers; l++) {
+        d.k[l].assign(s.k[l].begin(), s.k[l].begin() + (size_t)n * kvDim);
+        d.v[l].assign(s.v[l].begin(), s.v[l].begin() + (size_t)n * kvDim);
+    }
+    return B200_OK;
+}
+
 int oracle_upload_kv(oracle_model* m, int slot, int layer, int base, int n, const float* keys, const float* vals) {
     if (slot < 0 || slot >= m->c.n_slots || layer < 0 || layer >= m->c.n_layers) return B200_BAD_ARGUMENT;
     Slot& s = m->slots[slot];
     const int kvDim = m->c.n_kv_heads * m->c.head_dim;
     int need = blocks_for(m, base + n), have = 0;
     for (int i = 0; i < need; i++) have += s.table[i] != 0;
-    if (need - have > (int)m->free_blocks.size()) return B200_KV_POOL_FULL;
+    if (need - have + m->cow_need(s.table, base, base + n) > (int)m->free_blocks.size()) return B200_KV_POOL_FULL;
+    m->make_private(s.table, base, base + n);
     for (int i = 0; i < need; i++)
-        if (!s.table[i]) { s.table[i] = m->free_blocks.back(); m->free_blocks.pop_back(); }
+        if (!s.table[i]) s.table[i] = m->take();
     if (s.k[layer].size() < (size_t)(base + n) * kvDim) {
         const size_t room = std::min((size_t)m->c.ctx_cap, (size_t)(base + n) + 64) * kvDim;  // headroom for the appends that follow
         s.k[layer].reserve(room);
@@ -697,12 +735,14 @@ int oracle_step_ragged(oracle_model* m, int n_seqs, const int32_t* slot, const i
     for (int i = 0; i < n_seqs; i++) {
         const auto& t = m->slots[slot[i]].table;
         for (int b = 0; b < blocks_for(m, pos[i] + n_rows[i]); b++) need += t[b] == 0;
+        need += m->cow_need(t, pos[i], pos[i] + n_rows[i]);
     }
     if (need > (int)m->free_blocks.size()) return B200_KV_POOL_FULL;
+    for (int i = 0; i < n_seqs; i++) m->make_private(m->slots[slot[i]].table, pos[i], pos[i] + n_rows[i]);  // shared blocks first
     for (int i = 0; i < n_seqs; i++) {
         auto& t = m->slots[slot[i]].table;
         for (int b = 0; b < blocks_for(m, pos[i] + n_rows[i]); b++)
-            if (!t[b]) { t[b] = m->free_blocks.back(); m->free_blocks.pop_back(); }
+            if (!t[b]) t[b] = m->take();
     }
     std::vector<int> rseq(T), rpos(T);
     {

@@ -234,6 +234,33 @@ def test_device_decode_loop_equals_host_driven_steps(oracle_lib, klass):
     g2.Close()
 
 
+def test_device_decode_loop_over_a_shared_prefix(oracle_lib):
+    """The decode loop, graph replays included, on slots whose first blocks are shared: one taker starts at the end of the
+    prefix, one rolls back into a shared block and so takes its own copy before the loop's first step; the source and
+    the oracle's host-driven twin see the same ids and tables afterwards."""
+    g, o, s = build_pair(oracle_lib, "tiny-qknorm", n_slots=4, ctx_cap=96, seed=31)
+    p = np.random.default_rng(3).integers(0, s.vocab, 32).tolist()
+    for r in (g, o):
+        r.PrefillLast(None, 0, 0, p)
+        r.CopyKV(1, 0, 32)
+        r.CopyKV(2, 0, 32)
+    pos, first = [32, 32, 21], [5, 5, 6]
+    ids, _ = g.DecodeLoop([0, 1, 2], pos, first, steps=4)
+    none, _ = g.DecodeLoop([0, 1, 2], [q + 4 for q in pos], ids[3].tolist(), steps=3, log_ids=False)
+    tok = list(first)
+    for step in range(7):
+        bo = o.StepBatch([BatchSeq(i, pos[i] + step, None, tok[i], BatchDraw(Greedy=True)) for i in range(3)])
+        tok = [b.ID for b in bo]
+        if step < 4:
+            assert tok == ids[step].tolist(), step
+    assert ids[:, 0].tolist() == ids[:, 1].tolist()
+    for sl in range(3):
+        assert np.array_equal(g.BlockTable(sl), o.BlockTable(sl)), sl
+    assert g.BlockTable(2)[1] != g.BlockTable(0)[1] and g.BlockTable(2)[0] == g.BlockTable(0)[0]
+    ok, err = close_logits(g.Forward(None, 28, 2, token=3), o.Forward(None, 28, 2, token=3))
+    assert ok, err
+
+
 def test_forward_topk_and_gumbel_sample_in_a_step(oracle_lib):
     """ForwardTopK returns the k best of the row Forward returns (same order as the host's); a Gumbel draw in a batched
     step draws the id the host draw picks from that row's logits (DecodeSubsystem.ForwardTopK / ForwardSample,
@@ -249,6 +276,81 @@ def test_forward_topk_and_gumbel_sample_in_a_step(oracle_lib):
     out = g.StepBatch([BatchSeq(2, 21, None, 7, BatchDraw(Gumbel=True, Temperature=0.8, Seed=99, DrawIndex=4))])
     want = oracle_lib.op_draw(full[None], [abi.gumbel_draw(0.8, 99, 4)])[0]
     assert out[0].ID == want and out[0].Logits is None
+
+
+def test_prefix_reuse_shares_blocks_and_copies_on_write(oracle_lib):
+    """CopyKV over the paged pool (backend/cuda/kvpool.go:16-27,436-536): whole blocks are shared by reference, a partial
+    last block is copied, a slot that writes into a shared block takes its own first, and a block returns to the pool with
+    its last reference. Continuations from a shared prefix are bit-identical to a slot that prefilled the prefix itself
+    (exact class), the block tables and free counts follow the oracle's allocator through every step."""
+    g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=6, ctx_cap=96, seed=23, kv_pool_blocks=1 + 14)
+    p = np.random.default_rng(9).integers(0, s.vocab, 40).tolist()
+
+    def same_tables():
+        for sl in range(6):
+            assert np.array_equal(g.BlockTable(sl), o.BlockTable(sl)), sl
+        assert g.Stats().kv_blocks_in_use == 14 - o.FreeBlocks()
+
+    for r in (g, o):
+        r.PrefillLast(None, 0, 0, p)                 # 40 rows: blocks 1, 2 and 8 rows of block 3
+        r.CopyKV(1, 0, 40)                           # shares 1, 2; copies the tail into a block of its own
+        r.CopyKV(2, 0, 20)                           # shares 1; copies 4 rows
+        r.CopyKV(3, 0, 32)                           # shares 1, 2; no tail
+    same_tables()
+    t0, t1 = g.BlockTable(0), g.BlockTable(1)
+    assert t1[:2].tolist() == t0[:2].tolist() and t1[2] not in (0, t0[2])
+    assert g.BlockTable(3)[:3].tolist() == [t0[0], t0[1], 0]
+    # the continuation of a shared prefix == the source's own continuation, bit for bit
+    a = g.Forward(None, 40, 0, token=7)
+    b = g.Forward(None, 40, 1, token=7)
+    assert np.array_equal(a, b)
+    ok, err = close_logits(b, o.Forward(None, 40, 1, token=7))
+    assert ok, err
+    o.Forward(None, 40, 0, token=7)
+    # a partial prefix, continued differently, == a slot that prefilled that prefix itself
+    g.PrefillLast(None, 0, 4, p[:20])
+    o.PrefillLast(None, 0, 4, p[:20])
+    for r in (g, o):
+        r.Forward(None, 20, 4, token=11)
+    c2 = g.Forward(None, 20, 2, token=11)
+    o.Forward(None, 20, 2, token=11)
+    g.ResetSlot(4); o.ResetSlot(4)
+    g.PrefillLast(None, 0, 4, p[:20]); o.PrefillLast(None, 0, 4, p[:20])
+    assert np.array_equal(c2, g.Forward(None, 20, 4, token=11))
+    o.Forward(None, 20, 4, token=11)
+    same_tables()
+    # copy on write: slot 3 rewrites row 20, inside shared block 2; it takes its own block and keeps rows 16..19
+    before = g.BlockTable(3).copy()
+    w = g.Forward(None, 20, 3, token=11)
+    o.Forward(None, 20, 3, token=11)
+    after = g.BlockTable(3)
+    assert after[0] == before[0] and after[1] != before[1] and after[1] != 0
+    assert np.array_equal(w, c2)                     # the same prefix rows and the same token as slot 2's step above
+    assert np.array_equal(g.Forward(None, 41, 0, token=9), g.Forward(None, 41, 1, token=9))   # the source and its other sharers are untouched
+    o.Forward(None, 41, 0, token=9); o.Forward(None, 41, 1, token=9)
+    same_tables()
+    # the source lets go: its shared blocks stay until the last table naming them does
+    used = g.Stats().kv_blocks_in_use
+    g.ResetSlot(0); o.ResetSlot(0)
+    assert g.Stats().kv_blocks_in_use == used - 1    # only its private tail block came back
+    same_tables()
+    assert np.array_equal(g.Forward(None, 42, 1, token=5)[:8], g.Forward(None, 42, 1, token=5)[:8])
+    o.Forward(None, 42, 1, token=5); o.Forward(None, 42, 1, token=5)
+    for sl in (1, 2, 3, 4):
+        g.ResetSlot(sl); o.ResetSlot(sl)
+    assert g.Stats().kv_blocks_in_use == 0 and o.FreeBlocks() == 14
+    # freed blocks are handed out again in the oracle's order
+    g.PrefillLast(None, 0, 5, p[:33]); o.PrefillLast(None, 0, 5, p[:33])
+    same_tables()
+    # a refusal changes nothing: the one block a partial copy needs is not there
+    g2, o2, _ = build_pair(oracle_lib, "tiny-dense", n_slots=3, ctx_cap=64, seed=23, kv_pool_blocks=1 + 2)
+    for r in (g2, o2):
+        r.PrefillLast(None, 0, 0, p[:24])            # both blocks taken
+        with pytest.raises(ErrKVPoolFull):
+            r.CopyKV(1, 0, 20)
+        assert r.BlockTable(1).sum() == 0
+        r.CopyKV(1, 0, 16)                           # a whole block needs none
+    assert np.array_equal(g2.BlockTable(1), o2.BlockTable(1))
 
 
 def test_kv_pool_full_writes_nothing_and_bad_steps_are_refused(oracle_lib):

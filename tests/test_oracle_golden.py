@@ -99,3 +99,49 @@ def test_philox_known_answers_and_gumbel_draw(oracle_lib):
     ids = oracle_lib.op_draw(np.repeat(l8, n, axis=0), [abi.gumbel_draw(T, 1234, d) for d in range(n)])
     freq = np.bincount(ids, minlength=8) / n
     assert np.abs(freq - p).max() < 4 * np.sqrt(p.max() * (1 - p.max()) / n) + 2e-3
+
+
+def test_prefix_reuse_on_the_golden_model(oracle_lib):
+    """A slot that takes another's prefix by CopyKV continues exactly like the slot that prefilled it, whole blocks are
+    shared and come back only with their last reference, and a write into a shared block goes to a private copy
+    (backend/cuda/kvpool.go:16-27 refcounts and copy-on-write, :436-536 the table append and copy paths)."""
+    r, g = _oracle(oracle_lib, "llama_tiny", n_slots=4, kv_block_rows=4)
+    ids = g["prompt_ids"].tolist()
+    n = len(ids)
+    solo = r.PrefillLast(None, 0, slot=0, tokens=ids)
+    assert int(np.argmax(solo)) == int(g["argmax"])
+    free0 = r.FreeBlocks()
+    keep = n - 1                                            # all but the last row: the taker feeds that row itself
+    r.CopyKV(1, 0, keep)
+    whole, tail = keep // 4, keep % 4
+    assert free0 - r.FreeBlocks() == (1 if tail else 0)     # shared blocks cost nothing, the copied tail one block
+    t0, t1 = r.BlockTable(0), r.BlockTable(1)
+    assert t1[:whole].tolist() == t0[:whole].tolist()
+    if tail:
+        assert t1[whole] not in (0, t0[whole])
+    again = r.Forward(None, keep, slot=1, token=ids[keep])
+    assert np.array_equal(again, solo)
+    # the golden continuation from the shared prefix
+    tok, pos, out = int(g["argmax"]), n, [int(g["argmax"])]
+    for _ in range(len(g["continuation_ids"]) - 1):
+        tok = r.ForwardArgmax(None, pos, slot=1, token=tok)
+        out.append(tok)
+        pos += 1
+    assert out == g["continuation_ids"].tolist()
+    # slot 2 shares a whole first block, then rewrites inside it: the source must not see the write
+    r.CopyKV(2, 0, 4)
+    assert r.BlockTable(2)[0] == t0[0]
+    f = r.FreeBlocks()
+    r.Forward(None, 2, slot=2, token=ids[0])
+    assert r.BlockTable(2)[0] != t0[0] and r.FreeBlocks() == f - 1
+    assert np.array_equal(r.Forward(None, n - 1, slot=0, token=ids[n - 1]), solo)
+    # the source lets go first: only blocks nobody else names come back
+    shared_with_1 = whole
+    own0 = int((r.BlockTable(0) != 0).sum())
+    f = r.FreeBlocks()
+    r.ResetSlot(0)
+    assert r.FreeBlocks() == f + own0 - shared_with_1
+    assert np.array_equal(r.Forward(None, keep, slot=1, token=ids[keep]), solo)   # rewriting its own private row: same result
+    r.ResetSlot(1)
+    r.ResetSlot(2)
+    assert r.FreeBlocks() == free0 + own0
