@@ -267,24 +267,45 @@ class _Session:
     t_last: float = 0.0
     t_end: float = 0.0
     gaps: List[float] = field(default_factory=list)
+    out_ids: List[int] = field(default_factory=list)
+    reused: int = 0
 
 
-def poisson_trace(n: int, rate: float, seed: int, prompt_lo: int, prompt_hi: int, out_lo: int, out_hi: int, vocab: int):
+def poisson_trace(n: int, rate: float, seed: int, prompt_lo: int, prompt_hi: int, out_lo: int, out_hi: int, vocab: int,
+                  preamble: int = 0, n_preambles: int = 1):
+    """preamble > 0: every prompt starts with one of n_preambles shared token runs of that length (a system prompt),
+    drawn after everything else so that the lengths and arrivals equal the preamble-free trace of the same seed."""
     rng = np.random.default_rng(seed)
     arrivals = np.cumsum(rng.exponential(1.0 / rate, n))
     p_len = rng.integers(prompt_lo, prompt_hi + 1, n)
     o_len = rng.integers(out_lo, out_hi + 1, n)
     prompts = [rng.integers(0, vocab, int(k)).astype(np.int32) for k in p_len]
+    if preamble > 0:
+        heads = [rng.integers(0, vocab, preamble).astype(np.int32) for _ in range(max(n_preambles, 1))]
+        which = rng.integers(0, len(heads), n)
+        for i in range(n):
+            k = min(preamble, len(prompts[i]) - 1)
+            prompts[i][:k] = heads[int(which[i])][:k]
     return [_Session(i, float(arrivals[i]), prompts[i], int(o_len[i])) for i in range(n)]
 
 
 def drive(r, sessions: List[_Session], max_active: int, chunk: int, time_scale: float = 1.0, clock=time.perf_counter,
-          sleep=time.sleep) -> dict:
-    """Runs the trace to completion on resident `r` (greedy decoding); returns the measurements."""
+          sleep=time.sleep, index=None, root=None, class_map=None) -> dict:
+    """Runs the trace to completion on resident `r` (greedy decoding); returns the measurements.
+
+    With `index` (a kvindex.SlotIndex over the same max_active slots) a finished session's rows stay in its slot, published
+    block by block, until the slot is given away; a new prompt takes the longest published prefix another slot holds by
+    `CopyKV` (whole device blocks shared by reference), or continues in place in the slot that already holds most of it,
+    and prefills only the rest (decoder admission: Score / PickSlot, Hits / CapHit / DeclineShortLead, Copied, Prefilled,
+    Commit; internal/runtime/kvmgr/slots.go, share.go)."""
+    from . import kvindex
     from .resident import BatchDraw, BatchSeq, RaggedPrefill, RaggedSeq
     adm = Admission(max_active)
     bat = Batcher(r, max_active)
     free_slots = list(range(max_active - 1, -1, -1))
+    busy = [False] * max_active
+    cm = class_map or kvindex.ClassMap()
+    reuse_stats = {"copies": 0, "in_place": 0, "rows_reused": 0, "rows_prefilled": 0}
     waiting = deque(sessions)              # by arrival time
     prefilling: Deque[_Session] = deque()  # admitted, prompt not yet in: the oldest one's next chunk rides each run
     decoding: List[_Session] = []
@@ -294,16 +315,65 @@ def drive(r, sessions: List[_Session], max_active: int, chunk: int, time_scale: 
     t0 = clock()
     now = lambda: (clock() - t0) * time_scale if time_scale > 0 else float("inf")
 
+    def place(s: _Session) -> int:
+        """The slot for s and how many of its prompt's leading rows are already there when this returns."""
+        prompt = [int(t) for t in s.prompt]
+        req = kvindex.Request(root, prompt)
+        n = len(prompt)
+        scores = [index.Score(i, req) for i in range(max_active)]
+        lens = [index.Len(i) for i in range(max_active)]
+        uses = [index.Use(i) for i in range(max_active)]
+        pick = kvindex.pick_slot_within(scores, lens, uses, busy)
+        donor, rows = kvindex.plan_reuse(index, req, cm)
+        reuse = 0
+        if scores[pick] > 0 and lens[pick] > 0 and scores[pick] >= rows:
+            # its own rows, kept in place at token granularity
+            reuse = cm.DeclineShortLead(n, cm.CapInPlace(index.Seq(pick).classes, (), n, scores[pick]))
+        if reuse > 0:
+            index.Acquired(pick, reuse, prompt)
+            index.Forget(pick)
+            reuse_stats["in_place"] += 1
+        elif donor >= 0 and donor != pick and rows > 0:
+            r.CopyKV(pick, donor, rows)
+            index.Copied(donor, pick, 0, rows)
+            index.Acquired(pick, rows, prompt)
+            index.Forget(pick)
+            reuse = rows
+            reuse_stats["copies"] += 1
+        else:
+            r.ResetSlot(pick)
+            index.Acquired(pick, 0, prompt)
+            index.Forget(pick)
+        index.Touch(pick)
+        s.slot, s.reused = pick, reuse
+        return reuse
+
     def start(s: _Session):
-        s.slot = free_slots.pop()
-        s.passes = chunk_plan(len(s.prompt), chunk)
+        if index is None:
+            s.slot = free_slots.pop()
+        else:
+            s.done_rows = place(s)
+            busy[s.slot] = True
+            reuse_stats["rows_reused"] += s.done_rows
+            reuse_stats["rows_prefilled"] += len(s.prompt) - s.done_rows
+        s.passes = chunk_plan(len(s.prompt) - s.done_rows, chunk)
         prefilling.append(s)
 
-    def finish(s: _Session, t: float):
+    def finish(s: _Session, t: float, failed: bool = False):
         s.t_end = t
         finished.append(s)
-        r.ResetSlot(s.slot)
-        free_slots.append(s.slot)
+        if index is None:
+            r.ResetSlot(s.slot)
+            free_slots.append(s.slot)
+        else:
+            busy[s.slot] = False
+            if failed:
+                index.Forget(s.slot)
+                r.ResetSlot(s.slot)
+            else:
+                # the last drawn id was never fed, so its row does not exist: the slot holds the prompt and all but that id
+                index.Commit(s.slot, root, [int(x) for x in s.prompt] + s.out_ids[:-1], None, len(s.prompt), cm)
+                index.Touch(s.slot)
         nxt = adm.Release()
         if nxt is not None:
             start(nxt.payload)
@@ -342,9 +412,10 @@ def drive(r, sessions: List[_Session], max_active: int, chunk: int, time_scale: 
         for s, (o, err) in zip(run_sessions, outs):
             if err is not None:
                 decoding.remove(s)
-                finish(s, t)
+                finish(s, t, failed=True)
                 continue
             s.last_id = int(o.ID)
+            s.out_ids.append(s.last_id)
             s.generated += 1
             s.gaps.append(t - s.t_last)
             s.t_last = t
@@ -356,7 +427,10 @@ def drive(r, sessions: List[_Session], max_active: int, chunk: int, time_scale: 
             if not c_sess.passes:
                 prefilling.popleft()
                 c_sess.last_id = int(np.argmax(c_out.Logits[-1]))   # greedy: first maximal index
+                c_sess.out_ids.append(c_sess.last_id)
                 c_sess.generated = 1
+                if index is not None:
+                    index.Prefilled(c_sess.slot, root, [int(x) for x in c_sess.prompt], None, cm)
                 c_sess.t_first = c_sess.t_last = t
                 if c_sess.generated >= c_sess.out_len:
                     finish(c_sess, t)
@@ -370,7 +444,7 @@ def drive(r, sessions: List[_Session], max_active: int, chunk: int, time_scale: 
     gaps = np.concatenate([np.asarray(s.gaps) for s in finished if s.gaps]) / scale if any(s.gaps for s in finished) else np.zeros(1)
     pct = lambda a, q: float(np.percentile(a, q))
     st = bat.stats
-    return {"sessions": len(finished), "makespan_s": makespan, "output_tokens": out_tok, "prompt_tokens": in_tok,
+    return {"sessions": len(finished), **({"prefix_reuse": reuse_stats} if index is not None else {}), "makespan_s": makespan, "output_tokens": out_tok, "prompt_tokens": in_tok,
             "output_tok_s": out_tok / makespan, "total_tok_s": (out_tok + in_tok) / makespan,
             "ttft_ms": {"p50": pct(ttft, 50) * 1e3, "p95": pct(ttft, 95) * 1e3, "p99": pct(ttft, 99) * 1e3},
             "inter_token_ms": {"p50": pct(gaps, 50) * 1e3, "p99": pct(gaps, 99) * 1e3},
@@ -381,10 +455,12 @@ def drive(r, sessions: List[_Session], max_active: int, chunk: int, time_scale: 
 
 
 def run_poisson(shape: str, n_sessions: int, rate: float, max_active: int, seed: int, prompt_lo: int, prompt_hi: int, out_lo: int,
-                out_hi: int, chunk: int = 512, device: int = 0, n_layers: int = 0, time_scale: float = 1.0) -> dict:
+                out_hi: int, chunk: int = 512, device: int = 0, n_layers: int = 0, time_scale: float = 1.0, preamble: int = 0,
+                n_preambles: int = 1, prefix_reuse: bool = False) -> dict:
     """Builds the synthetic model, runs the trace, returns one result dict. time_scale > 1 compresses the arrival clock;
-    0 makes every session arrive at once (the closed-loop capacity of the engine at `max_active`)."""
-    from . import abi, synth
+    0 makes every session arrive at once (the closed-loop capacity of the engine at `max_active`). preamble > 0 gives the
+    prompts shared leading runs; prefix_reuse serves them from the slots that already hold them."""
+    from . import abi, kvindex, synth
     from .resident import Resident
     s = synth.SHAPES[shape]
     cap = prompt_hi + out_hi + 1
@@ -393,14 +469,20 @@ def run_poisson(shape: str, n_sessions: int, rate: float, max_active: int, seed:
     r = Resident(cfg, device=device)
     synth.load_device_weights(r, s, seed=seed, n_layers=n_layers)
     r.finalize()
-    trace = poisson_trace(n_sessions, rate, seed, prompt_lo, prompt_hi, out_lo, out_hi, s.vocab)
+    trace = poisson_trace(n_sessions, rate, seed, prompt_lo, prompt_hi, out_lo, out_hi, s.vocab, preamble, n_preambles)
     # warm the kernels' first-launch costs outside the measurement
     r.PrefillLast(None, 0, 0, tokens=list(range(1, 65)))
     r.ResetSlot(0)
-    res = drive(r, trace, max_active, chunk, time_scale)
+    kw = {}
+    if prefix_reuse:
+        caps = r.ResidentCaps()
+        kw = dict(index=kvindex.SlotIndex(max_active), root=kvindex.Root(Model=f"{shape}/q4k/b200", Precision="f16"),
+                  class_map=kvindex.ClassMap(Floor=caps.fast_prefill_floor, MinRows=16) if caps.has_fast_prefill else kvindex.ClassMap())
+    res = drive(r, trace, max_active, chunk, time_scale, **kw)
     res["workload"] = (f"{shape}: {n_sessions} sessions, Poisson {rate}/s seed {seed}"
                        f"{'' if time_scale == 1.0 else f' (arrival clock x{time_scale})' if time_scale > 0 else ' (all at t=0)'}, "
-                       f"prompts U[{prompt_lo},{prompt_hi}], outputs U[{out_lo},{out_hi}], <= {max_active} admitted, greedy, "
+                       f"prompts U[{prompt_lo},{prompt_hi}]{f' sharing {n_preambles} preamble(s) of {preamble}' if preamble else ''}"
+                       f"{', prefix reuse on' if prefix_reuse else ''}, outputs U[{out_lo},{out_hi}], <= {max_active} admitted, greedy, "
                        f"paged fp16 KV 16-token blocks, prefill chunks of {chunk} riding the decode runs")
     r.Close()
     return res

@@ -196,6 +196,9 @@ def main():
     v.add_argument("--chunk", type=int, default=512)
     v.add_argument("--layers", type=int, default=0)
     v.add_argument("--time-scale", type=float, default=1.0, help="arrival times are divided by this (1 = real time)")
+    v.add_argument("--preamble", type=int, default=0, help="leading tokens every prompt shares with one of --n-preambles runs")
+    v.add_argument("--n-preambles", type=int, default=1)
+    v.add_argument("--prefix-reuse", action="store_true", help="serve shared prefixes from the slots that hold them (CopyKV)")
     args = ap.parse_args()
     if args.what == "decode":
         print(json.dumps(decode(args.shape, args.batch, args.ctx_lo, args.ctx_hi, args.seed, args.steps, args.warmup,
@@ -209,7 +212,8 @@ def main():
         from .serve import run_poisson
         print(json.dumps(run_poisson(args.shape, args.sessions, args.rate, args.max_active, args.seed, args.prompt_lo,
                                      args.prompt_hi, args.out_lo, args.out_hi, args.chunk, n_layers=args.layers,
-                                     time_scale=args.time_scale)))
+                                     time_scale=args.time_scale, preamble=args.preamble, n_preambles=args.n_preambles,
+                                     prefix_reuse=args.prefix_reuse)))
 
 
 if __name__ == "__main__":

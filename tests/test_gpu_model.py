@@ -353,6 +353,33 @@ def test_prefix_reuse_shares_blocks_and_copies_on_write(oracle_lib):
     assert np.array_equal(g2.BlockTable(1), o2.BlockTable(1))
 
 
+def test_serve_driver_with_prefix_reuse_draws_the_same_ids():
+    """The continuous-batching driver over prompts that share a preamble, with the prefix index on and off: in the exact
+    class a row is the same bits whichever slot or pass wrote it, so every session draws the same ids, while most preamble
+    rows are taken by CopyKV or kept in place instead of prefilled."""
+    from goinfer_b200 import kvindex, serve
+    s = synth.SHAPES["tiny-dense"]
+
+    def run(reuse):
+        cfg = synth.make_cfg(s, 4, 400, 16, 1 + 4 * 25, 64 + 4, abi.CLASS_EXACT, 0)
+        r = Resident(cfg)
+        synth.load_host_weights([r], s, 5, 0)
+        r.finalize()
+        trace = serve.poisson_trace(10, 40.0, 3, 150, 330, 3, 12, s.vocab, preamble=140, n_preambles=2)
+        kw = dict(index=kvindex.SlotIndex(4), root=kvindex.Root("tiny", Precision="f16"), class_map=kvindex.ClassMap()) if reuse else {}
+        res = serve.drive(r, trace, max_active=4, chunk=64, time_scale=4.0, **kw)
+        st = r.Stats()
+        r.Close()
+        return res, [x.out_ids for x in sorted(trace, key=lambda x: x.idx)], st
+
+    base, ids0, st0 = run(False)
+    res, ids1, st1 = run(True)
+    assert ids0 == ids1
+    pr = res["prefix_reuse"]
+    assert pr["copies"] >= 1 and pr["rows_reused"] >= 5 * 128
+    assert st1.prefill_rows == st0.prefill_rows - pr["rows_reused"]
+
+
 def test_kv_pool_full_writes_nothing_and_bad_steps_are_refused(oracle_lib):
     g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=3, ctx_cap=64, seed=9, kv_pool_blocks=1 + 3)
     for r in (g, o):

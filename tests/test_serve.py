@@ -173,6 +173,48 @@ def test_drive_serves_a_trace_with_chunks_riding_runs():
     assert first_steps[0] == trace3[0].slot
 
 
+def test_drive_with_the_prefix_index_takes_shared_preambles_by_copy():
+    """Prompts sharing a 200-token preamble: after the first one finishes its prefill the others take its three whole
+    64-row blocks by CopyKV (or keep them in place when they inherit the slot) and prefill only the rest; the ids are the
+    ones the same trace draws without reuse."""
+    from goinfer_b200 import kvindex
+    vocab = 97
+    mk = lambda: serve.poisson_trace(10, 40.0, 3, 230, 300, 2, 6, vocab, preamble=200)
+    base = mk()
+    r0 = FakeResident(slots=3, lo=2)
+    serve.drive(r0, base, max_active=3, chunk=64, time_scale=0.0)
+    trace = mk()
+    assert all(np.array_equal(a.prompt[:200], trace[0].prompt[:200]) for a in trace)
+    r = FakeResident(slots=3, lo=2)
+    r.copies = []
+    r.CopyKV = lambda dst, src, n: r.copies.append((dst, src, n))
+    # arrivals 25 ms apart on a clock where a step costs 1 ms: the second and third prompts find empty slots and a donor
+    t = [0.0]
+    def sleep(d):
+        t[0] += d
+    ob, orr = r.StepBatch, r.StepRagged
+    def sb(seqs):
+        t[0] += 1e-3
+        return ob(seqs)
+    def sr(seqs):
+        t[0] += 1e-3
+        return orr(seqs)
+    r.StepBatch, r.StepRagged = sb, sr
+    res = serve.drive(r, trace, max_active=3, chunk=64, clock=lambda: t[0], sleep=sleep, index=kvindex.SlotIndex(3),
+                      root=kvindex.Root("m", Precision="f16"), class_map=kvindex.ClassMap())
+    assert res["sessions"] == 10 and [s.last_id for s in trace] == [s.last_id for s in base]
+    pr = res["prefix_reuse"]
+    assert pr["copies"] + pr["in_place"] >= 7 and pr["copies"] == len(r.copies) >= 1
+    assert all(n == 192 and dst != src for dst, src, n in r.copies)
+    assert pr["rows_reused"] + pr["rows_prefilled"] == res["prompt_tokens"]
+    assert pr["rows_reused"] >= 7 * 192
+    # a session that took rows starts its prefill where they end
+    for s in trace:
+        if s.reused:
+            first = next(q for k, seqs in r.steps if k == "ragged" for q in seqs[:1] if q[0] == s.slot and q[1] >= s.reused)
+            assert first[1] == s.reused or first[1] > s.reused
+
+
 def test_admission_gate_is_a_pure_function_of_the_facts():
     """decoder/admit.go:35-76: the order of the refusals, the name the Q4_K gate accepts, the activation-group gate."""
     from goinfer_b200 import admit
