@@ -37,6 +37,37 @@ __device__ __forceinline__ void quant_group_warp(float y, int8_t* codes_g, float
     }
 }
 
+// The same quantizer for a group held 8 values per lane by four consecutive lanes (q4 = lane & 3 is the lane's place in
+// its group). The maximum and the integer sum do not depend on the order they are taken in, so the codes, scale and sum
+// are those of quant_group_warp. Every lane of the warp must call it (lanes past the row pass zeros and `live` false).
+__device__ __forceinline__ void quant_group_quad(const float (&y)[8], int8_t* codes_g, float* sc_out, float* asum_out, int q4, bool live) {
+    float ma = 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; u++) ma = fmaxf(ma, fabsf(y[u]));
+    ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, 1));
+    ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, 2));
+    const float sc = __fdiv_rn(ma, 127.f);
+    const float inv = sc > 0.f ? __fdiv_rn(1.f, sc) : 0.f;
+    int sum = 0;
+    unsigned w[2] = {0u, 0u};
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        int q = __float2int_rn(__fmul_rn(y[u], inv));
+        q = max(-127, min(127, q));
+        sum += q;
+        w[u >> 2] |= (unsigned)(q & 0xff) << (8 * (u & 3));
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (live) {
+        *reinterpret_cast<uint2*>(codes_g + 8 * q4) = make_uint2(w[0], w[1]);
+        if (q4 == 0) {
+            *sc_out = sc;
+            *asum_out = __fmul_rn(sc, (float)sum);
+        }
+    }
+}
+
 __global__ void embed_gather_kernel(const void* __restrict__ table, int kind, const int32_t* __restrict__ ids, int H,
                                     float scale, float* __restrict__ h) {
     int r = blockIdx.x;
@@ -128,6 +159,104 @@ __global__ void __launch_bounds__(256) add_rmsnorm_quant_kernel(float* __restric
         if (normed) normed[(size_t)j * H + i] = __fmul_rn(__fmul_rn(row[i], inv), w[i]);
 }
 
+// The same row pass for widths that are a multiple of 32 and at most 8 * 256 * P: a thread keeps its P chunks of eight
+// consecutive values in registers from the loads to the stores (no shared row buffer, every load of the row in flight at
+// once), and a group of 32 is four lanes, so its maximum and sum take two shuffles each. The sum of squares is added in
+// another order than the kernel above adds it, in f64, which the rounded f32 factor does not see.
+template <int P>
+__global__ void __launch_bounds__(256) add_rmsnorm_quant_vec_kernel(float* __restrict__ h, const float* __restrict__ delta,
+                                                                    const float* __restrict__ w, int H, float eps,
+                                                                    float* __restrict__ normed, int8_t* __restrict__ codes,
+                                                                    float* __restrict__ scales, const int32_t* __restrict__ gather_rows,
+                                                                    int n_parts, size_t part_stride) {
+    __shared__ double red[8];
+    const int j = blockIdx.x, r = gather_rows ? gather_rows[j] : j, nC = H >> 3, nG = H >> 5;
+    float* hr = h + (size_t)r * H;
+    const float* dr = delta ? delta + (size_t)r * H : nullptr;
+    float x[P][8];
+#pragma unroll
+    for (int p = 0; p < P; p++) {
+        const int c = p * 256 + threadIdx.x;
+        if (c < nC) {
+            const float4 a = *reinterpret_cast<const float4*>(hr + 8 * c), b = *reinterpret_cast<const float4*>(hr + 8 * c + 4);
+            x[p][0] = a.x; x[p][1] = a.y; x[p][2] = a.z; x[p][3] = a.w; x[p][4] = b.x; x[p][5] = b.y; x[p][6] = b.z; x[p][7] = b.w;
+        } else {
+#pragma unroll
+            for (int u = 0; u < 8; u++) x[p][u] = 0.f;
+        }
+    }
+    if (dr) {
+        float d[P][8];
+        const int np = n_parts ? n_parts : 1;
+#pragma unroll
+        for (int p = 0; p < P; p++) {
+            const int c = p * 256 + threadIdx.x;
+#pragma unroll
+            for (int u = 0; u < 8; u++) d[p][u] = 0.f;
+            if (c < nC) {
+                for (int k = 0; k < np; k++) {  // the partials are added in split order, starting from the first
+                    const float* src = dr + (size_t)k * part_stride + 8 * c;
+                    const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+                    if (k == 0) {
+                        d[p][0] = a.x; d[p][1] = a.y; d[p][2] = a.z; d[p][3] = a.w; d[p][4] = b.x; d[p][5] = b.y; d[p][6] = b.z; d[p][7] = b.w;
+                    } else {
+                        d[p][0] = __fadd_rn(d[p][0], a.x); d[p][1] = __fadd_rn(d[p][1], a.y); d[p][2] = __fadd_rn(d[p][2], a.z);
+                        d[p][3] = __fadd_rn(d[p][3], a.w); d[p][4] = __fadd_rn(d[p][4], b.x); d[p][5] = __fadd_rn(d[p][5], b.y);
+                        d[p][6] = __fadd_rn(d[p][6], b.z); d[p][7] = __fadd_rn(d[p][7], b.w);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < P; p++) {
+            const int c = p * 256 + threadIdx.x;
+            if (c < nC) {
+#pragma unroll
+                for (int u = 0; u < 8; u++) x[p][u] = __fadd_rn(x[p][u], d[p][u]);
+                *reinterpret_cast<float4*>(hr + 8 * c) = make_float4(x[p][0], x[p][1], x[p][2], x[p][3]);
+                *reinterpret_cast<float4*>(hr + 8 * c + 4) = make_float4(x[p][4], x[p][5], x[p][6], x[p][7]);
+            }
+        }
+    }
+    double ss = 0;
+#pragma unroll
+    for (int p = 0; p < P; p++)
+#pragma unroll
+        for (int u = 0; u < 8; u++) ss += (double)x[p][u] * (double)x[p][u];
+    ss = warp_sum_f64(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    double tot = 0;
+#pragma unroll
+    for (int k = 0; k < 8; k++) tot += red[k];
+    const float inv = (float)(1.0 / sqrt(tot / (double)H + (double)eps));
+    const int q4 = threadIdx.x & 3;
+#pragma unroll
+    for (int p = 0; p < P; p++) {
+        const int c = p * 256 + threadIdx.x;
+        if (p * 256 + (int)(threadIdx.x & ~31u) >= nC) break;  // a whole warp past the row (uniform)
+        const bool live = c < nC;
+        float y[8];
+        if (live) {
+            const float4 a = *reinterpret_cast<const float4*>(w + 8 * c), b = *reinterpret_cast<const float4*>(w + 8 * c + 4);
+            const float wv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int u = 0; u < 8; u++) y[u] = __fmul_rn(__fmul_rn(x[p][u], inv), wv[u]);
+            if (normed) {
+                *reinterpret_cast<float4*>(normed + (size_t)j * H + 8 * c) = make_float4(y[0], y[1], y[2], y[3]);
+                *reinterpret_cast<float4*>(normed + (size_t)j * H + 8 * c + 4) = make_float4(y[4], y[5], y[6], y[7]);
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < 8; u++) y[u] = 0.f;
+        }
+        if (codes) {
+            const int g = c >> 2;
+            quant_group_quad(y, codes + (size_t)j * H + (size_t)g * 32, scales + (size_t)j * 2 * nG + g, scales + (size_t)j * 2 * nG + nG + g, q4, live);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) quant_g32_kernel(const float* __restrict__ x, int K, int8_t* __restrict__ codes,
                                                         float* __restrict__ scales) {
     const int r = blockIdx.y, lane = threadIdx.x & 31, nG = K >> 5;
@@ -158,6 +287,35 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float* __restri
     float y = __fmul_rn(F64 ? silu_f64(gt) : silu_f32(gt), up);
     if (mid) mid[(size_t)r * F + f] = y;
     if (codes) quant_group_warp(y, codes + (size_t)r * F + g * 32, scales + (size_t)r * 2 * nG + g, scales + (size_t)r * 2 * nG + nG + g, lane);
+}
+
+// The same with eight consecutive values per thread (vector loads, a group is four lanes). F a multiple of 32.
+template <bool F64>
+__global__ void __launch_bounds__(256) swiglu_quant_vec_kernel(const float* __restrict__ gate_up, int F, int ld, float* __restrict__ mid,
+                                                               int8_t* __restrict__ codes, float* __restrict__ scales) {
+    const int r = blockIdx.y, nG = F >> 5, nC = F >> 3;
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (blockIdx.x * 256 + (int)(threadIdx.x & ~31u) >= nC) return;  // a whole warp past the row
+    const bool live = c < nC;
+    float y[8];
+    if (live) {
+        const float* gp = gate_up + (size_t)r * ld + 8 * c;
+        const float4 g0 = *reinterpret_cast<const float4*>(gp), g1 = *reinterpret_cast<const float4*>(gp + 4);
+        const float4 u0 = *reinterpret_cast<const float4*>(gp + F), u1 = *reinterpret_cast<const float4*>(gp + F + 4);
+        const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+        for (int u = 0; u < 8; u++) y[u] = __fmul_rn(F64 ? silu_f64(gv[u]) : silu_f32(gv[u]), uv[u]);
+        if (mid) {
+            *reinterpret_cast<float4*>(mid + (size_t)r * F + 8 * c) = make_float4(y[0], y[1], y[2], y[3]);
+            *reinterpret_cast<float4*>(mid + (size_t)r * F + 8 * c + 4) = make_float4(y[4], y[5], y[6], y[7]);
+        }
+    } else {
+#pragma unroll
+        for (int u = 0; u < 8; u++) y[u] = 0.f;
+    }
+    const int g = c >> 2;
+    quant_group_quad(y, codes + (size_t)r * F + (size_t)g * 32, scales + (size_t)r * 2 * nG + g, scales + (size_t)r * 2 * nG + nG + g,
+                     threadIdx.x & 3, live);
 }
 
 // plain SwiGLU for widths that are not a multiple of 32 (f32-weight models)
@@ -270,8 +428,18 @@ int launch_add_rmsnorm_quant(b200_ctx* ctx, float* h, const float* delta, const 
         pt = ctx->pending;
         ctx->pending = Parts{};
     }
-    add_rmsnorm_quant_kernel<<<T, 256, smem, ctx->stream>>>(h, pt.n ? pt.p : delta, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n,
-                                                            pt.stride);
+    const float* dl = pt.n ? pt.p : delta;
+    const bool vec = H % 32 == 0 && H <= 8192 && !((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(dl) | reinterpret_cast<uintptr_t>(w) |
+                                                    reinterpret_cast<uintptr_t>(normed) | (uintptr_t)(pt.stride * 4)) & 15) &&
+                     !(reinterpret_cast<uintptr_t>(aq.codes) & 7);
+    if (vec && H <= 2048)
+        add_rmsnorm_quant_vec_kernel<1><<<T, 256, 0, ctx->stream>>>(h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
+    else if (vec && H <= 4096)
+        add_rmsnorm_quant_vec_kernel<2><<<T, 256, 0, ctx->stream>>>(h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
+    else if (vec)
+        add_rmsnorm_quant_vec_kernel<4><<<T, 256, 0, ctx->stream>>>(h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
+    else
+        add_rmsnorm_quant_kernel<<<T, 256, smem, ctx->stream>>>(h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }
@@ -288,9 +456,17 @@ int launch_swiglu_quant(b200_ctx* ctx, const float* gate_up, int T, int F, int l
     ProfScope ps(ctx, PROF_SWIGLU);
     if (aq.codes) {
         if (F % 32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "F must be a multiple of 32");
-        dim3 grid(ceil_div(F / 32, 8), T);
-        if (f64_silu) swiglu_quant_kernel<true><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales);
-        else swiglu_quant_kernel<false><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales);
+        const bool vec = !((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(mid) | (uintptr_t)((size_t)ld * 4)) & 15) &&
+                         !(reinterpret_cast<uintptr_t>(aq.codes) & 7);
+        if (vec) {
+            dim3 grid(ceil_div(F / 8, 256), T);
+            if (f64_silu) swiglu_quant_vec_kernel<true><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales);
+            else swiglu_quant_vec_kernel<false><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales);
+        } else {
+            dim3 grid(ceil_div(F / 32, 8), T);
+            if (f64_silu) swiglu_quant_kernel<true><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales);
+            else swiglu_quant_kernel<false><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales);
+        }
     } else {
         dim3 grid(ceil_div(F, 256), T);
         swiglu_plain_kernel<<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid);
