@@ -367,13 +367,34 @@ __global__ void attn_combine_kernel(const float* __restrict__ partial, int nH, i
     const int h = blockIdx.x, r = blockIdx.y, e = threadIdx.x;
     const int nsp = (row_pos[r] + 1 + split_keys - 1) / split_keys;
     const float* p = partial + ((size_t)r * nH + h) * max_splits * (HD + 2);
+    // eight splits' loads are in flight at a time; the sums keep the split order
     float M = -INFINITY;
-    for (int s = 0; s < nsp; s++) M = fmaxf(M, p[(size_t)s * (HD + 2) + HD]);
+    for (int s0 = 0; s0 < nsp; s0 += 8) {
+        float mv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) mv[u] = s0 + u < nsp ? p[(size_t)(s0 + u) * (HD + 2) + HD] : -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 8; u++) M = fmaxf(M, mv[u]);
+    }
     float tot = 0.f, l = 0.f;
-    for (int s = 0; s < nsp; s++) {
-        const float f = __expf(p[(size_t)s * (HD + 2) + HD] - M);
-        tot += p[(size_t)s * (HD + 2) + e] * f;
-        l += p[(size_t)s * (HD + 2) + HD + 1] * f;
+    for (int s0 = 0; s0 < nsp; s0 += 8) {
+        float mv[8], av[8], lv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const bool in = s0 + u < nsp;
+            const float* ps = p + (size_t)(s0 + u) * (HD + 2);
+            mv[u] = in ? ps[HD] : 0.f;
+            av[u] = in ? ps[e] : 0.f;
+            lv[u] = in ? ps[HD + 1] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            if (s0 + u < nsp) {
+                const float f = __expf(mv[u] - M);
+                tot += av[u] * f;
+                l += lv[u] * f;
+            }
+        }
     }
     const float y = tot / l;
     const int D = nH * HD;
@@ -395,6 +416,81 @@ __global__ void attn_combine_kernel(const float* __restrict__ partial, int nH, i
             scales[(size_t)r * 2 * nG + nG + g] = __fmul_rn(sc, (float)sum);
         }
     }
+}
+
+// The same merge with two values per thread and four heads per block (grid (nH/4, T), 2*HD threads): with up to eight
+// splits every load of the row is issued at once, before the maximum is known. Same sums in the same order, same codes.
+template <int HD>
+__global__ void __launch_bounds__(2 * HD) attn_combine2_kernel(const float* __restrict__ partial, int nH, int max_splits, int split_keys,
+                                                               const int32_t* __restrict__ row_pos, float* __restrict__ out,
+                                                               int8_t* __restrict__ codes, float* __restrict__ scales) {
+    constexpr int TPH = HD / 2;  // threads per head
+    const int h = blockIdx.x * 4 + threadIdx.x / TPH, r = blockIdx.y, e = 2 * (threadIdx.x % TPH);
+    const int nsp = (row_pos[r] + 1 + split_keys - 1) / split_keys;
+    const float* p = partial + ((size_t)r * nH + h) * max_splits * (HD + 2);
+    float M = -INFINITY, tot0 = 0.f, tot1 = 0.f, l = 0.f;
+    if (nsp <= 8) {
+        float mv[8], lv[8];
+        float2 av[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const bool in = u < nsp;
+            const float* ps = p + (size_t)u * (HD + 2);
+            const float2 ml = in ? *reinterpret_cast<const float2*>(ps + HD) : make_float2(-INFINITY, 0.f);
+            mv[u] = ml.x;
+            lv[u] = ml.y;
+            av[u] = in ? *reinterpret_cast<const float2*>(ps + e) : make_float2(0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) M = fmaxf(M, mv[u]);
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            if (u < nsp) {
+                const float f = __expf(mv[u] - M);
+                tot0 += av[u].x * f;
+                tot1 += av[u].y * f;
+                l += lv[u] * f;
+            }
+        }
+    } else {
+        for (int s = 0; s < nsp; s++) M = fmaxf(M, p[(size_t)s * (HD + 2) + HD]);
+        for (int s = 0; s < nsp; s++) {
+            const float* ps = p + (size_t)s * (HD + 2);
+            const float f = __expf(ps[HD] - M);
+            const float2 a = *reinterpret_cast<const float2*>(ps + e);
+            tot0 += a.x * f;
+            tot1 += a.y * f;
+            l += ps[HD + 1] * f;
+        }
+    }
+    const float y0 = tot0 / l, y1 = tot1 / l;
+    const int D = nH * HD;
+    *reinterpret_cast<float2*>(out + (size_t)r * D + h * HD + e) = make_float2(y0, y1);
+    if (codes) {
+        const int g = (h * HD + e) >> 5, nG = D >> 5;
+        float ma = fmaxf(fabsf(y0), fabsf(y1));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, o));
+        const float sc = __fdiv_rn(ma, 127.f);
+        const float inv = sc > 0.f ? __fdiv_rn(1.f, sc) : 0.f;
+        const int q0 = max(-127, min(127, __float2int_rn(__fmul_rn(y0, inv)))), q1 = max(-127, min(127, __float2int_rn(__fmul_rn(y1, inv))));
+        int sum = q0 + q1;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        *reinterpret_cast<uint16_t*>(codes + (size_t)r * D + h * HD + e) = (uint16_t)((q0 & 0xff) | ((q1 & 0xff) << 8));
+        if ((threadIdx.x & 15) == 0) {
+            scales[(size_t)r * 2 * nG + g] = sc;
+            scales[(size_t)r * 2 * nG + nG + g] = __fmul_rn(sc, (float)sum);
+        }
+    }
+}
+
+template <int HD>
+void launch_combine(b200_ctx* ctx, const float* partial, int nH, int T, int max_splits, int split_keys, const int32_t* row_pos, float* out, ActQ aq) {
+    if (nH % 4 == 0 && !((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(out)) & 7) && !(reinterpret_cast<uintptr_t>(aq.codes) & 1))
+        attn_combine2_kernel<HD><<<dim3(nH / 4, T), 2 * HD, 0, ctx->stream>>>(partial, nH, max_splits, split_keys, row_pos, out, aq.codes, aq.scales);
+    else
+        attn_combine_kernel<HD><<<dim3(nH, T), HD, 0, ctx->stream>>>(partial, nH, max_splits, split_keys, row_pos, out, aq.codes, aq.scales);
 }
 
 // One warp per (row, head); lanes stride the keys. head_dim <= 64.
@@ -527,7 +623,7 @@ int run_split(b200_ctx* ctx, const float* q, int ldq, int T, int nH, int nKV, fl
     LAUNCH_CHECK(ctx);
     {
         ProfScope ps(ctx, PROF_ATTN_COMBINE);
-        attn_combine_kernel<HD><<<dim3(nH, T), HD, 0, ctx->stream>>>(sc.partial, nH, sc.max_splits, kSplitKeys, row_pos, out, aq.codes, aq.scales);
+        launch_combine<HD>(ctx, sc.partial, nH, T, sc.max_splits, kSplitKeys, row_pos, out, aq);
     }
     LAUNCH_CHECK(ctx);
     return B200_OK;
@@ -555,7 +651,7 @@ int run_mma(b200_ctx* ctx, const float* q, int ldq, int T, int nH, int nKV, floa
     LAUNCH_CHECK(ctx);
     {
         ProfScope ps(ctx, PROF_ATTN_COMBINE);
-        attn_combine_kernel<HD><<<dim3(nH, T), HD, 0, ctx->stream>>>(sc.partial, nH, sc.max_splits, kMmaSplitKeys, row_pos, out, aq.codes, aq.scales);
+        launch_combine<HD>(ctx, sc.partial, nH, T, sc.max_splits, kMmaSplitKeys, row_pos, out, aq);
     }
     LAUNCH_CHECK(ctx);
     return B200_OK;

@@ -396,6 +396,93 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvstore_kernel(
     }
 }
 
+// The same for head_dim 128 with two heads per warp and sixteen per block (grid.y walks the heads): a lane keeps four
+// consecutive values of a head, the loads of both heads (and of every K-split partial) are in flight while the block's
+// cos/sin table is computed, and the rotation partner comes by shuffle. Same arithmetic, expression by expression.
+__global__ void __launch_bounds__(256) qknorm_rope_kvstore_vec_kernel(
+    float* __restrict__ qkv, int ld, int nH, int nKV, int half, const double* __restrict__ inv_freq,
+    const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, const int32_t* __restrict__ row_slot,
+    const int32_t* __restrict__ row_pos, __half* __restrict__ kpool, __half* __restrict__ vpool,
+    const int32_t* __restrict__ table, int max_blocks, int block_rows, const float* __restrict__ parts, int n_parts,
+    size_t part_stride) {
+    constexpr int hd = 128;
+    __shared__ double cs[2 * 64];  // [half] cos, [half] sin
+    const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_heads = nH + 2 * nKV;
+    const int pos = row_pos[r], slot = row_slot[r];
+    float x[2][4];
+    const float* base = n_parts ? parts : qkv;
+    const int np = n_parts ? n_parts : 1;
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+        const int hh = blockIdx.y * 16 + 2 * warp + u;
+        x[u][0] = x[u][1] = x[u][2] = x[u][3] = 0.f;
+        if (hh < n_heads) {
+            const size_t off = (size_t)r * ld + (size_t)hh * hd + 4 * lane;
+            for (int k = 0; k < np; k++) {
+                const float4 a = *reinterpret_cast<const float4*>(base + (size_t)k * part_stride + off);
+                if (k == 0) {
+                    x[u][0] = a.x; x[u][1] = a.y; x[u][2] = a.z; x[u][3] = a.w;
+                } else {
+                    x[u][0] = __fadd_rn(x[u][0], a.x); x[u][1] = __fadd_rn(x[u][1], a.y);
+                    x[u][2] = __fadd_rn(x[u][2], a.z); x[u][3] = __fadd_rn(x[u][3], a.w);
+                }
+            }
+        }
+    }
+    for (int d = threadIdx.x; d < half; d += blockDim.x) {
+        double th = (double)pos * inv_freq[d];
+        double sn, c;
+        sincos(th, &sn, &c);
+        cs[d] = c;
+        cs[half + d] = sn;
+    }
+    __syncthreads();
+    const int blk = table[(size_t)slot * max_blocks + pos / block_rows];
+    const int rib = pos % block_rows;
+    const int e0 = 4 * lane;                       // this lane's first element
+    const bool first = e0 < half, second = !first && e0 < 2 * half;
+    const int partner = first ? lane + half / 4 : lane - half / 4;
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+        const int hh = blockIdx.y * 16 + 2 * warp + u;
+        if (hh >= n_heads) break;  // uniform over the warp
+        const bool is_q = hh < nH, is_k = !is_q && hh < nH + nKV;
+        const float* nw = is_q ? q_norm : (is_k ? k_norm : nullptr);
+        float v[4] = {x[u][0], x[u][1], x[u][2], x[u][3]};
+        if (nw) {
+            double ss = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) ss += (double)v[i] * (double)v[i];
+            ss = warp_sum_f64(ss);
+            const float inv = (float)(1.0 / sqrt(ss / (double)hd + (double)eps));
+            const float4 wv = *reinterpret_cast<const float4*>(nw + e0);
+            v[0] = __fmul_rn(__fmul_rn(v[0], inv), wv.x); v[1] = __fmul_rn(__fmul_rn(v[1], inv), wv.y);
+            v[2] = __fmul_rn(__fmul_rn(v[2], inv), wv.z); v[3] = __fmul_rn(__fmul_rn(v[3], inv), wv.w);
+        }
+        if (is_q || is_k) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float other = __shfl_sync(0xffffffffu, v[i], partner & 31);
+                if (first) {
+                    const double x1 = v[i], x2 = other, c = cs[e0 + i], sn = cs[half + e0 + i];
+                    v[i] = (float)(x1 * c - x2 * sn);
+                } else if (second) {
+                    const double x1 = other, x2 = v[i], c = cs[e0 + i - half], sn = cs[e0 + i];
+                    v[i] = (float)(x2 * c + x1 * sn);
+                }
+            }
+        }
+        if (is_q) {
+            *reinterpret_cast<float4*>(qkv + (size_t)r * ld + (size_t)hh * hd + e0) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+            const int kvh = is_k ? hh - nH : hh - nH - nKV;
+            __half* dst = (is_k ? kpool : vpool) + (((size_t)blk * nKV + kvh) * block_rows + rib) * hd + e0;
+            const __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+            *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const unsigned*>(&h0), *reinterpret_cast<const unsigned*>(&h1));
+        }
+    }
+}
+
 // eo rows are in expert-sorted slot order; slot_of[row*k + rank] names the slot (-1: empty rank).
 __global__ void fold_experts_kernel(const float* __restrict__ eo, const float* __restrict__ wts,
                                     const int32_t* __restrict__ slot_of, int k, int H, float* __restrict__ out) {
@@ -503,6 +590,15 @@ int launch_qknorm_rope_kvstore(b200_ctx* ctx, float* qkv, int ld, int T, int nH,
         pt = ctx->pending;
         ctx->pending = Parts{};
     }
+    const bool vec = hd == 128 && rot_half % 4 == 0 && rot_half <= 64 && ld % 4 == 0 &&
+                     !((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(pt.p) | (uintptr_t)(pt.stride * 4) |
+                        reinterpret_cast<uintptr_t>(q_norm) | reinterpret_cast<uintptr_t>(k_norm)) & 15) &&
+                     !((reinterpret_cast<uintptr_t>(kv.k) | reinterpret_cast<uintptr_t>(kv.v)) & 7);
+    if (vec) {
+        dim3 grid(T, ceil_div(nH + 2 * nKV, 16));
+        qknorm_rope_kvstore_vec_kernel<<<grid, 256, 0, ctx->stream>>>(qkv, ld, nH, nKV, rot_half, inv_freq, q_norm, k_norm, eps, row_slot, row_pos,
+                                                                      kv.k, kv.v, kv.table, kv.max_blocks, kv.block_rows, pt.p, pt.n, pt.stride);
+    } else
     qknorm_rope_kvstore_kernel<<<T, 256, smem, ctx->stream>>>(qkv, ld, nH, nKV, hd, rot_half, inv_freq, q_norm, k_norm, eps,
                                                               row_slot, row_pos, kv.k, kv.v, kv.table, kv.max_blocks,
                                                               kv.block_rows, pt.p, pt.n, pt.stride);
