@@ -336,12 +336,20 @@ def run_gpu(args):
     if world == 1 and not args.no_gemv:
         from goinfer_b200.ops import Ops
         ops = Ops(local)
-        rows = []
-        for M in (1, 2, 4, 8, 16, 32):
-            t = ops.bench_q4k_matmul(M, 4096, 12288, 0, 8, 3, 20)
-            gb = 12288 * 4096 * 144 / 256 / 1e9
-            rows.append({"rows": M, "ms": t, "weight_GBps": gb / (t * 1e-3), "frac_of_measured_peak": gb / (t * 1e-3) / peak})
-        line["q4k_gemv_12288x4096"] = rows
+        # the matrices a decode step of this shape streams: up/down (28 MB), gate|up as the step fuses them (57 MB), and the
+        # vocabulary projection were it Q4_K (350 MB). `read_floor_ms` is a kernel that only reads the same bytes, launched
+        # the same way: what this size allows at all (launch and drain are a fixed part of a launch this short).
+        for name, N, K, copies in (("q4k_gemv_12288x4096", 12288, 4096, 8), ("q4k_gemv_24576x4096", 24576, 4096, 8),
+                                   ("q4k_gemv_151936x4096", 151936, 4096, 3)):
+            gb = N * K * 144 / 256 / 1e9
+            floor_ms = ops.bench_read(N * K * 144 // 256, copies, 3, 20)
+            rows = []
+            for M in (1, 2, 4, 8, 16, 32):
+                t = ops.bench_q4k_matmul(M, K, N, 0, copies, 3, 20)
+                rows.append({"rows": M, "ms": t, "weight_GBps": gb / (t * 1e-3), "frac_of_measured_peak": gb / (t * 1e-3) / peak,
+                             "frac_of_read_floor": floor_ms / t})
+            line[name] = {"weight_mb": gb * 1e3, "read_floor_ms": floor_ms, "read_floor_frac_of_measured_peak": gb / (floor_ms * 1e-3) / peak,
+                          "rows": rows}
     print(json.dumps(line), flush=True)
 
 

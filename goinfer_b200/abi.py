@@ -7,7 +7,7 @@ OK, DECLINED, KV_POOL_FULL, BAD_ARGUMENT, CUDA_ERROR, TIMEOUT, NCCL_ERROR = rang
 
 T_EMBED, T_FINAL_NORM, T_LM_HEAD, T_ATTN_NORM, T_WQ, T_WK, T_WV, T_WO, T_Q_NORM, T_K_NORM, T_FFN_NORM, \
     T_GATE, T_UP, T_DOWN, T_ROUTER, T_EXP_GATE, T_EXP_UP, T_EXP_DOWN = range(18)
-K_F32, K_F16, K_Q4K = 0, 1, 2
+K_F32, K_F16, K_Q4K, K_Q5K, K_Q6K = 0, 1, 2, 3, 4
 DRAW_LOGITS, DRAW_GREEDY, DRAW_MINP, DRAW_GUMBEL = 0, 1, 2, 3
 CLASS_AUTO, CLASS_EXACT = 0, 1
 
@@ -63,6 +63,6 @@ EXPORTS = (
     "b200_decode_loop_device", "b200_stats", "b200_profile", "b200_profile_read", "b200_debug_read_hidden", "b200_op_quant_g32", "b200_op_q4k_dequant",
     "b200_op_q4k_matmul", "b200_op_q4k_quantize", "b200_op_rmsnorm", "b200_op_route", "b200_op_draw",
     "b200_tp_unique_id", "b200_tp_init", "b200_tp_destroy",
-    "b200_copy_kv", "b200_op_philox", "b200_op_topk", "b200_forward_topk", "b200_op_attention", "b200_op_prefill_attention", "b200_op_f16_matmul", "b200_bench_f16_matmul", "b200_bench_q4k_matmul", "b200_bench_attention",
+    "b200_copy_kv", "b200_op_philox", "b200_op_topk", "b200_forward_topk", "b200_op_attention", "b200_op_prefill_attention", "b200_op_f16_matmul", "b200_bench_f16_matmul", "b200_bench_q4k_matmul", "b200_bench_read", "b200_op_kq_matmul", "b200_bench_attention",
     "b200_bench_prefill_attention", "b200_attention_noalloc",
 )

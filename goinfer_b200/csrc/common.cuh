@@ -146,6 +146,8 @@ int launch_softcap(b200_ctx*, float* x, size_t n, float cap);
 // gemm.cu
 // dst[T][N] (ld = ldd) = act . W^T for a Q4_K matrix; klass 0 auto, 1 exact, 2 fast.
 int launch_q4k_matmul(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, int klass);
+int launch_kq_matmul(b200_ctx*, int kind, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd);  // Q5_K (file blocks) / Q6_K (planes)
+int launch_q6k_to_planes(b200_ctx*, const uint8_t* raw, size_t n_blocks, uint8_t* planes);
 // grouped form: expert e owns assignment rows [offs[e], offs[e+1]); assignment a reads activation row
 // rows[a] and writes dst row a. Wptrs[e] is expert e's matrix.
 int launch_q4k_matmul_grouped(b200_ctx*, const uint8_t* const* Wptrs, int n_experts, int N, int K, ActQ aq,

@@ -20,16 +20,25 @@
 
 namespace {
 
+constexpr int kKindMixed = 100;  // a projection group whose parts are K-quants of different kinds, multiplied part by part
+
 struct DevMat {
     int kind = -1, rows = 0, cols = 0;
     void* p = nullptr;
     size_t bytes = 0;
-    bool present() const { return kind >= 0 && p; }
+    DevMat* seg[3] = {nullptr, nullptr, nullptr};  // kKindMixed: the parts, in row order
+    int n_seg = 0;
+    bool present() const { return kind >= 0 && (p || n_seg > 0); }
 };
+
+// the kinds that multiply the per-32 int8 activations
+bool is_kquant(int kind) { return kind == B200_K_Q4K || kind == B200_K_Q5K || kind == B200_K_Q6K || kind == kKindMixed; }
 
 size_t mat_bytes(int kind, size_t rows, size_t cols) {
     if (kind == B200_K_F32) return rows * cols * 4;
     if (kind == B200_K_F16) return rows * cols * 2;
+    if (kind == B200_K_Q5K) return rows * cols / 256 * 176;
+    if (kind == B200_K_Q6K) return rows * cols / 256 * 210;
     return rows * cols / 256 * 144;
 }
 
@@ -382,9 +391,12 @@ int prep_mat(b200_model* m, int which, int layer, int expert, int kind, int rows
     int er, ec;
     if (!expected_shape(m->c, which, &er, &ec) || er != rows || ec != cols)
         B200_FAIL(ctx, B200_BAD_ARGUMENT, "tensor %d: shape [%d,%d], expected [%d,%d]", which, rows, cols, er, ec);
-    if (kind == B200_K_Q4K && cols % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs cols %% 256 == 0");
+    if (kind < B200_K_F32 || kind > B200_K_Q6K) B200_FAIL(ctx, B200_BAD_ARGUMENT, "unknown tensor kind %d", kind);
+    if (is_kquant(kind) && cols % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K-quants need cols %% 256 == 0");
     if (which == B200_T_ROUTER && kind != B200_K_F32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the router stays f32");
-    if (which == B200_T_EMBED && kind == B200_K_Q4K) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the embedding table is f32 or f16");
+    if (which == B200_T_EMBED && is_kquant(kind)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the embedding table is f32 or f16");
+    if ((kind == B200_K_Q5K || kind == B200_K_Q6K) && (expert >= 0 || m->c.tp_size > 1))
+        B200_FAIL(ctx, B200_DECLINED, "Q5_K / Q6_K tensors are taken for dense, single-GPU models");
     if (mat->p) { m->dfree(mat->p); m->weight_bytes -= mat->bytes; }
     mat->kind = kind; mat->rows = rows; mat->cols = cols;
     mat->bytes = mat_bytes(kind, rows, cols);
@@ -398,11 +410,22 @@ int fuse_rows(b200_model* m, std::vector<DevMat*> parts, DevMat* out) {
     b200_ctx* ctx = m->ctx;
     size_t bytes = 0;
     int rows = 0;
+    bool same = true, all_kq = true;
     for (auto* p : parts) {
-        if (!p->present() || p->kind != parts[0]->kind || p->cols != parts[0]->cols)
-            B200_FAIL(ctx, B200_DECLINED, "projection group with mixed kinds or a missing tensor");
+        if (!p->present() || p->cols != parts[0]->cols) B200_FAIL(ctx, B200_DECLINED, "projection group with a missing tensor or unequal widths");
+        same = same && p->kind == parts[0]->kind;
+        all_kq = all_kq && is_kquant(p->kind);
         bytes += p->bytes;
         rows += p->rows;
+    }
+    if (!same || parts[0]->kind == B200_K_Q6K) {
+        // K-quants of different kinds (a Q4_K_M file's q|k|v or gate|up), or Q6_K parts (whose planes do not concatenate):
+        // the parts stay where they are and are multiplied one after the other into their columns of the output
+        if (!all_kq || parts.size() > 3) B200_FAIL(ctx, B200_DECLINED, "projection group mixing quantized and float tensors");
+        out->kind = kKindMixed; out->cols = parts[0]->cols; out->rows = rows; out->bytes = 0; out->p = nullptr;
+        out->n_seg = (int)parts.size();
+        for (size_t i = 0; i < parts.size(); i++) out->seg[i] = parts[i];
+        return B200_OK;
     }
     out->kind = parts[0]->kind; out->cols = parts[0]->cols; out->rows = rows; out->bytes = bytes;
     ST_TRY(m->dalloc(&out->p, bytes, &m->weight_bytes));
@@ -420,6 +443,18 @@ int fuse_rows(b200_model* m, std::vector<DevMat*> parts, DevMat* out) {
 int matmul(b200_model* m, const DevMat& W, const float* xf, ActQ xq, int T, float* dst, int ldd) {
     b200_ctx* ctx = m->ctx;
     if (W.kind == B200_K_Q4K) return launch_q4k_matmul(ctx, (const uint8_t*)W.p, W.rows, W.cols, xq, T, dst, ldd, m->c.kernel_class);
+    if (W.kind == B200_K_Q5K || W.kind == B200_K_Q6K) return launch_kq_matmul(ctx, W.kind, (const uint8_t*)W.p, W.rows, W.cols, xq, T, dst, ldd);
+    if (W.kind == kKindMixed) {
+        const bool defer = ctx->defer_reduce;
+        ctx->defer_reduce = false;  // a part's K-split partials cannot stand for the whole output
+        int off = 0;
+        for (int i = 0; i < W.n_seg; i++) {
+            ST_TRY(matmul(m, *W.seg[i], xf, xq, T, dst + off, ldd));
+            off += W.seg[i]->rows;
+        }
+        ctx->defer_reduce = defer;
+        return B200_OK;
+    }
     if (W.kind == B200_K_F16) return launch_f16w_matmul(ctx, (const __half*)W.p, W.rows, W.cols, xf, T, dst, ldd, m->split, m->c.kernel_class);
     return launch_f32w_matmul(ctx, (const float*)W.p, W.rows, W.cols, xf, T, dst, ldd);
 }
@@ -449,7 +484,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
     const float* delta = nullptr;  // pending residual add, fused into the next norm
     for (int l = 0; l < c.n_layers; l++) {
         LayerW& L = m->layers[l];
-        const bool q_in = L.qkv.kind == B200_K_Q4K;
+        const bool q_in = is_kquant(L.qkv.kind);
         ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, delta, L.attn_norm, T, H, c.rms_eps, q_in ? nullptr : m->normed,
                                         q_in ? m->aq_h : none, nullptr));
         // the consumers of the q|k|v, o and down products can add their K-split partials themselves (no reduce kernel)
@@ -462,7 +497,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
         ST_TRY(launch_qknorm_rope_kvstore(ctx, m->qkv, ldq, T, nH, nKV, hd, m->rot_half, L.inv_freq,
                                           c.qk_norm ? L.q_norm : nullptr, c.qk_norm ? L.k_norm : nullptr, c.rms_eps,
                                           m->d_row_slot, m->d_row_pos, kv));
-        const bool o_q = L.wo.kind == B200_K_Q4K;
+        const bool o_q = is_kquant(L.wo.kind);
         if (m->exact_scores) {
             const double scale_d = c.attn_scale != 0.f ? (double)c.attn_scale : 1.0 / std::sqrt((double)hd);
             ST_TRY(launch_paged_attention_exact(ctx, m->qkv, ldq, T, nH, nKV, hd, scale_d, (double)c.attn_softcap, m->d_row_slot,
@@ -490,7 +525,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
         ctx->defer_reduce = false;
         if (c.tp_size > 1) ST_TRY(tp_all_reduce_sum(ctx, m->att, (size_t)T * H));  // o is split by input columns: partial sums
         if (c.n_experts == 0) {
-            const bool g_q = L.gu.kind == B200_K_Q4K, d_q = L.down.kind == B200_K_Q4K;
+            const bool g_q = is_kquant(L.gu.kind), d_q = is_kquant(L.down.kind);
             ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, m->att, L.ffn_norm, T, H, c.rms_eps, g_q ? nullptr : m->normed,
                                             g_q ? m->aq_h : none, nullptr));
             ST_TRY(matmul(m, L.gu, m->normed, m->aq_h, T, m->gu, 2 * c.ffn));
@@ -623,6 +658,19 @@ int b200_upload_tensor(b200_model* m, int which, int layer, int expert, int kind
     DevMat* mat;
     ST_TRY(prep_mat(m, which, layer, expert, kind, rows, cols, &mat));
     if (bytes != mat->bytes) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tensor %d: %zu bytes, expected %zu", which, bytes, mat->bytes);
+    if (kind == B200_K_Q6K) {
+        // the file's 210-byte blocks are laid out as four planes on the device (16-byte aligned loads): through a staging copy
+        void* stage = nullptr;
+        CUDA_TRY(ctx, cudaMalloc(&stage, bytes));
+        // on the model's own stream, so that the re-layout kernel is ordered after the copy (a plain cudaMemcpy from pageable
+        // memory may return while its DMA is still in flight, and this stream does not wait for the default stream)
+        cudaError_t e = cudaMemcpyAsync(stage, host, bytes, cudaMemcpyHostToDevice, ctx->stream);
+        int st = e == cudaSuccess ? launch_q6k_to_planes(ctx, (const uint8_t*)stage, bytes / 210, (uint8_t*)mat->p) : B200_CUDA_ERROR;
+        if (st == B200_OK) e = cudaStreamSynchronize(ctx->stream);
+        cudaFree(stage);
+        if (e != cudaSuccess) B200_FAIL(ctx, B200_CUDA_ERROR, "Q6_K upload: %s", cudaGetErrorString(e));
+        return st;
+    }
     CUDA_TRY(ctx, cudaMemcpy(mat->p, host, bytes, cudaMemcpyHostToDevice));
     return B200_OK;
 }
@@ -633,6 +681,7 @@ int b200_synth_tensor(b200_model* m, int which, int layer, int expert, int kind,
     DevMat* mat;
     ST_TRY(prep_mat(m, which, layer, expert, kind, rows, cols, &mat));
     const size_t n = (size_t)rows * cols;
+    if (kind == B200_K_Q5K || kind == B200_K_Q6K) B200_FAIL(ctx, B200_BAD_ARGUMENT, "no device synthesis for Q5_K / Q6_K tensors: upload them");
     if (kind == B200_K_Q4K) return launch_synth_q4k(ctx, (uint8_t*)mat->p, n / 256, sigma, seed);
     if (kind == B200_K_F16) return launch_synth_f16(ctx, (__half*)mat->p, n, sigma, seed);
     return launch_synth_normal_f32(ctx, (float*)mat->p, n, sigma, seed);
@@ -654,6 +703,7 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
     const b200_model_cfg& c = m->c;
     if (m->finalized) B200_FAIL(ctx, B200_BAD_ARGUMENT, "model already finalized");
     const int H = c.hidden, nH = c.n_heads, nKV = c.n_kv_heads, hd = c.head_dim;
+    CUDA_TRY(ctx, cudaDeviceSynchronize());  // every upload's copy has landed before this stream touches the tensors
     if (!m->embed.present() || !m->head.present() || !m->final_norm) B200_FAIL(ctx, B200_DECLINED, "embedding, head or final norm missing");
     for (int l = 0; l < c.n_layers; l++) {
         LayerW& L = m->layers[l];
@@ -1165,7 +1215,7 @@ int b200_step_ragged(b200_model* m, int n_seqs, const int32_t* slot, const int32
     }
     for (int j0 = 0; j0 < R; j0 += m->MLR) {
         const int rn = std::min(m->MLR, R - j0);
-        const bool hq = m->head.kind == B200_K_Q4K;
+        const bool hq = is_kquant(m->head.kind);
         ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, nullptr, m->final_norm, rn, H, c.rms_eps, hq ? nullptr : m->hn,
                                         hq ? m->aq_h : ActQ{}, m->d_head_rows + j0));
         ST_TRY(head_logits(m, rn));
@@ -1285,7 +1335,7 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
         LAUNCH_CHECK(ctx);
         ST_TRY(launch_embed_gather(ctx, m->embed.p, m->embed.kind, m->d_tokens, S, H, c.embed_scale, m->h));
         ST_TRY(run_layers(m, S, max_keys));
-        const bool hq = m->head.kind == B200_K_Q4K;
+        const bool hq = is_kquant(m->head.kind);
         ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, nullptr, m->final_norm, S, H, c.rms_eps, hq ? nullptr : m->hn,
                                         hq ? m->aq_h : ActQ{}, m->d_head_rows));
         ST_TRY(head_logits(m, S));

@@ -1,0 +1,213 @@
+// kquant.cu — the GGUF Q5_K and Q6_K lanes: weight rows in the file's 5- and 6-bit super-blocks times the per-32 int8
+// activations of the step. A Q4_K_M checkpoint keeps some projections (attn_v, ffn_down in half the layers, the head)
+// in these formats; they are multiplied as they are, not through an int8 or fp16 copy.
+//
+//   Q5_K  (176 B / 256 weights: d, dmin, 12 bytes of 6-bit scales and minimums, qh[32], qs[128]):
+//         y += (d*sc_g*aS_g) * idot_g - (dmin*m_g) * asum_g   per group g of 32, codes 0..31   (backend/cuda/actgroup.cu:77-143)
+//   Q6_K  (210 B / 256 weights: ql[128], qh[64], 16 int8 sub-scales, d) kept as four planes over the whole matrix
+//         (ql | qh | sub-scales | d, every plane 16-byte aligned: backend/cuda/pack_stream.go q6kPlanes):
+//         y += (sc_h * idot_h) * (d*aS_g)   per half-group h of 16, codes -32..31              (backend/cuda/actgroup.cu:145-205)
+//
+// One warp owns one weight row and up to four activation rows; integer dots by dp4a, f32 terms, a shuffle tree at the
+// end. A token's sum does not depend on the other tokens of the launch, so a row's bits do not depend on its batch.
+// The bar is the reference's own for these kernels: |y - f64 product| <= 1e-5 * sum |w*a|
+// (backend/cuda/kernels/kso1c_kernels_test.go:146-151).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ int kq_dp4a_us(unsigned a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int kq_dp4a_ss(int a, int b, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ float kq_h2f(unsigned short b) { return __half2float(__ushort_as_half(b)); }
+__device__ __forceinline__ unsigned kq_byte(int k, unsigned s0, unsigned s1, unsigned s2) {
+    const unsigned w = k < 4 ? s0 : (k < 8 ? s1 : s2);
+    return (w >> ((k & 3) << 3)) & 0xffu;
+}
+// 6-bit scale and minimum of sub-block j (ggml get_scale_min_k4)
+__device__ __forceinline__ void kq_scale_min(int j, unsigned s0, unsigned s1, unsigned s2, int* sc, int* m) {
+    if (j < 4) {
+        *sc = (int)(kq_byte(j, s0, s1, s2) & 63u);
+        *m = (int)(kq_byte(j + 4, s0, s1, s2) & 63u);
+    } else {
+        const unsigned hi = kq_byte(j + 4, s0, s1, s2);
+        *sc = (int)((hi & 0x0Fu) | ((kq_byte(j - 4, s0, s1, s2) >> 6) << 4));
+        *m = (int)((hi >> 4) | ((kq_byte(j, s0, s1, s2) >> 6) << 4));
+    }
+}
+
+// Q5_K. Lane: super-block b0 + (lane >> 2) of the row (eight in flight), pair j = lane & 3 (sub-blocks 2j and 2j+1: the low and
+// high nibbles of code bytes 32j .. 32j+31, whose fifth bits are bits 2j and 2j+1 of the 32 qh bytes).
+template <int TT>
+__global__ void __launch_bounds__(256) q5k_gemv_kernel(const uint8_t* __restrict__ W, int N, int nSB, const int8_t* __restrict__ codes,
+                                                       const float* __restrict__ scales, int T, float* __restrict__ dst, int ldd) {
+    const int lane = threadIdx.x & 31, n = blockIdx.x * 8 + (threadIdx.x >> 5), t0 = blockIdx.y * TT;
+    if (n >= N) return;
+    const int j = lane & 3, sub = lane >> 2, K = nSB * 256, nG = nSB * 8;
+    const uint8_t* row = W + (size_t)n * nSB * 176;
+    float acc[TT];
+#pragma unroll
+    for (int t = 0; t < TT; t++) acc[t] = 0.f;
+    for (int b = sub; b < nSB; b += 8) {
+        const uint8_t* blk = row + (size_t)b * 176;
+        const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+        const uint4 qh0 = *reinterpret_cast<const uint4*>(blk + 16), qh1 = *reinterpret_cast<const uint4*>(blk + 32);
+        const uint4 q0 = *reinterpret_cast<const uint4*>(blk + 48 + 32 * j), q1 = *reinterpret_cast<const uint4*>(blk + 64 + 32 * j);
+        const float d = kq_h2f((unsigned short)(hdr.x & 0xffffu)), dmin = kq_h2f((unsigned short)(hdr.x >> 16));
+        int scLo, mLo, scHi, mHi;
+        kq_scale_min(2 * j, hdr.y, hdr.z, hdr.w, &scLo, &mLo);
+        kq_scale_min(2 * j + 1, hdr.y, hdr.z, hdr.w, &scHi, &mHi);
+        const float dsLo = __fmul_rn(d, (float)scLo), dsHi = __fmul_rn(d, (float)scHi);
+        const float nmLo = -__fmul_rn(dmin, (float)mLo), nmHi = -__fmul_rn(dmin, (float)mHi);
+        const unsigned qs[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const unsigned qh[8] = {qh0.x, qh0.y, qh0.z, qh0.w, qh1.x, qh1.y, qh1.z, qh1.w};
+        unsigned wl[8], wh[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            wl[i] = (qs[i] & 0x0F0F0F0Fu) | (((qh[i] >> (2 * j)) & 0x01010101u) << 4);
+            wh[i] = ((qs[i] >> 4) & 0x0F0F0F0Fu) | (((qh[i] >> (2 * j + 1)) & 0x01010101u) << 4);
+        }
+        const int g = 8 * b + 2 * j;
+#pragma unroll
+        for (int t = 0; t < TT; t++) {
+            if (t0 + t >= T) break;
+            const int4* av = reinterpret_cast<const int4*>(codes + (size_t)(t0 + t) * K + 256 * b + 64 * j);
+            const int4 l0 = av[0], l1 = av[1], h0 = av[2], h1 = av[3];
+            const float* sp = scales + (size_t)(t0 + t) * 2 * nG;
+            const float2 aS = *reinterpret_cast<const float2*>(sp + g), as = *reinterpret_cast<const float2*>(sp + nG + g);
+            int pl = 0, ph = 0;
+            pl = kq_dp4a_us(wl[0], l0.x, pl); pl = kq_dp4a_us(wl[1], l0.y, pl); pl = kq_dp4a_us(wl[2], l0.z, pl); pl = kq_dp4a_us(wl[3], l0.w, pl);
+            pl = kq_dp4a_us(wl[4], l1.x, pl); pl = kq_dp4a_us(wl[5], l1.y, pl); pl = kq_dp4a_us(wl[6], l1.z, pl); pl = kq_dp4a_us(wl[7], l1.w, pl);
+            ph = kq_dp4a_us(wh[0], h0.x, ph); ph = kq_dp4a_us(wh[1], h0.y, ph); ph = kq_dp4a_us(wh[2], h0.z, ph); ph = kq_dp4a_us(wh[3], h0.w, ph);
+            ph = kq_dp4a_us(wh[4], h1.x, ph); ph = kq_dp4a_us(wh[5], h1.y, ph); ph = kq_dp4a_us(wh[6], h1.z, ph); ph = kq_dp4a_us(wh[7], h1.w, ph);
+            float f = acc[t];
+            f = __fmaf_rn((float)pl, __fmul_rn(dsLo, aS.x), f);
+            f = __fmaf_rn((float)ph, __fmul_rn(dsHi, aS.y), f);
+            f = __fmaf_rn(nmLo, as.x, f);
+            acc[t] = __fmaf_rn(nmHi, as.y, f);
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < TT; t++) {
+        float f = acc[t];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) f += __shfl_down_sync(0xffffffffu, f, off);
+        if (lane == 0 && t0 + t < T) dst[(size_t)(t0 + t) * ldd + n] = f;
+    }
+}
+
+// Q6_K in planes. Lane: super-block b0 + (lane >> 3) (four in flight), half hh = (lane >> 2) & 1 of the block (128 weights),
+// quarter q = lane & 3: elements 8q .. 8q+7 of each of the half's four groups of 32 (one 8-byte load of the low codes for
+// groups 0 and 2, one for 1 and 3, one of the two-bit planes, one of the half's eight sub-scales). is = q >> 1 picks the
+// sub-scale of the element's half-group.
+template <int TT>
+__global__ void __launch_bounds__(256) q6k_gemv_kernel(const uint8_t* __restrict__ W, int N, int nSB, const int8_t* __restrict__ codes,
+                                                       const float* __restrict__ scales, int T, float* __restrict__ dst, int ldd) {
+    const int lane = threadIdx.x & 31, n = blockIdx.x * 8 + (threadIdx.x >> 5), t0 = blockIdx.y * TT;
+    if (n >= N) return;
+    const size_t TB = (size_t)N * nSB;  // blocks in the matrix
+    const uint8_t* qlp = W;
+    const uint8_t* qhp = W + 128 * TB;
+    const uint8_t* scp = W + 192 * TB;
+    const unsigned short* dp = reinterpret_cast<const unsigned short*>(W + 208 * TB);
+    const int sub = lane >> 3, hh = (lane >> 2) & 1, q = lane & 3, is = q >> 1, K = nSB * 256, nG = nSB * 8;
+    float acc[TT];
+#pragma unroll
+    for (int t = 0; t < TT; t++) acc[t] = 0.f;
+    for (int b = sub; b < nSB; b += 4) {
+        const size_t nb = (size_t)n * nSB + b;
+        const uint2 qa = *reinterpret_cast<const uint2*>(qlp + nb * 128 + 64 * hh + 8 * q);        // low codes of groups 0 (low nibble) and 2 (high)
+        const uint2 qb = *reinterpret_cast<const uint2*>(qlp + nb * 128 + 64 * hh + 32 + 8 * q);   // of groups 1 and 3
+        const uint2 qh = *reinterpret_cast<const uint2*>(qhp + nb * 64 + 32 * hh + 8 * q);         // two more bits a group
+        const uint2 sw = *reinterpret_cast<const uint2*>(scp + nb * 16 + 8 * hh);                  // the half's 8 sub-scales
+        const float d = kq_h2f(dp[nb]);
+        int c[4];
+        c[0] = (int)(signed char)((sw.x >> (8 * is)) & 0xffu);
+        c[1] = (int)(signed char)((sw.x >> (8 * (is + 2))) & 0xffu);
+        c[2] = (int)(signed char)((sw.y >> (8 * is)) & 0xffu);
+        c[3] = (int)(signed char)((sw.y >> (8 * (is + 2))) & 0xffu);
+        int v[4][2];
+        v[0][0] = (int)__vsub4((qa.x & 0x0F0F0F0Fu) | ((qh.x & 0x03030303u) << 4), 0x20202020u);
+        v[0][1] = (int)__vsub4((qa.y & 0x0F0F0F0Fu) | ((qh.y & 0x03030303u) << 4), 0x20202020u);
+        v[1][0] = (int)__vsub4((qb.x & 0x0F0F0F0Fu) | (((qh.x >> 2) & 0x03030303u) << 4), 0x20202020u);
+        v[1][1] = (int)__vsub4((qb.y & 0x0F0F0F0Fu) | (((qh.y >> 2) & 0x03030303u) << 4), 0x20202020u);
+        v[2][0] = (int)__vsub4(((qa.x >> 4) & 0x0F0F0F0Fu) | (((qh.x >> 4) & 0x03030303u) << 4), 0x20202020u);
+        v[2][1] = (int)__vsub4(((qa.y >> 4) & 0x0F0F0F0Fu) | (((qh.y >> 4) & 0x03030303u) << 4), 0x20202020u);
+        v[3][0] = (int)__vsub4(((qb.x >> 4) & 0x0F0F0F0Fu) | (((qh.x >> 6) & 0x03030303u) << 4), 0x20202020u);
+        v[3][1] = (int)__vsub4(((qb.y >> 4) & 0x0F0F0F0Fu) | (((qh.y >> 6) & 0x03030303u) << 4), 0x20202020u);
+        const int g0 = 8 * b + 4 * hh;
+#pragma unroll
+        for (int t = 0; t < TT; t++) {
+            if (t0 + t >= T) break;
+            const int8_t* ab = codes + (size_t)(t0 + t) * K + 256 * b + 128 * hh + 8 * q;
+            const float* sp = scales + (size_t)(t0 + t) * 2 * nG + g0;
+            float f = acc[t];
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                const int2 a = *reinterpret_cast<const int2*>(ab + 32 * g);
+                const int p = kq_dp4a_ss(v[g][1], a.y, kq_dp4a_ss(v[g][0], a.x, 0));
+                f = __fmaf_rn((float)(c[g] * p), __fmul_rn(d, sp[g]), f);
+            }
+            acc[t] = f;
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < TT; t++) {
+        float f = acc[t];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) f += __shfl_down_sync(0xffffffffu, f, off);
+        if (lane == 0 && t0 + t < T) dst[(size_t)(t0 + t) * ldd + n] = f;
+    }
+}
+
+// the file's 210-byte blocks -> the four planes
+__global__ void q6k_to_planes_kernel(const uint8_t* __restrict__ raw, size_t TB, uint8_t* __restrict__ out) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (block, byte)
+    if (i >= TB * 210) return;
+    const size_t g = i / 210;
+    const int o = (int)(i % 210);
+    const uint8_t v = raw[i];
+    if (o < 128) out[g * 128 + o] = v;
+    else if (o < 192) out[128 * TB + g * 64 + (o - 128)] = v;
+    else if (o < 208) out[192 * TB + g * 16 + (o - 192)] = v;
+    else out[208 * TB + g * 2 + (o - 208)] = v;
+}
+
+}  // namespace
+
+// W: Q5_K as in the file; Q6_K in planes (launch_q6k_to_planes). Any T: the rows go four at a time.
+int launch_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd) {
+    if (K % 256 || T < 1) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K-quant matmul needs K %% 256 == 0 and at least one row");
+    if ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(aq.codes)) & 15) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K-quant matmul wants 16-byte aligned buffers");
+    const int nSB = K / 256;
+    ProfScope ps(ctx, PROF_Q4K_GEMM);
+    const int tt = T == 1 ? 1 : (T == 2 ? 2 : 4);
+    dim3 grid(ceil_div(N, 8), ceil_div(T, tt));
+    if (kind == B200_K_Q5K) {
+        if (tt == 1) q5k_gemv_kernel<1><<<grid, 256, 0, ctx->stream>>>(W, N, nSB, aq.codes, aq.scales, T, dst, ldd);
+        else if (tt == 2) q5k_gemv_kernel<2><<<grid, 256, 0, ctx->stream>>>(W, N, nSB, aq.codes, aq.scales, T, dst, ldd);
+        else q5k_gemv_kernel<4><<<grid, 256, 0, ctx->stream>>>(W, N, nSB, aq.codes, aq.scales, T, dst, ldd);
+    } else if (kind == B200_K_Q6K) {
+        if (tt == 1) q6k_gemv_kernel<1><<<grid, 256, 0, ctx->stream>>>(W, N, nSB, aq.codes, aq.scales, T, dst, ldd);
+        else if (tt == 2) q6k_gemv_kernel<2><<<grid, 256, 0, ctx->stream>>>(W, N, nSB, aq.codes, aq.scales, T, dst, ldd);
+        else q6k_gemv_kernel<4><<<grid, 256, 0, ctx->stream>>>(W, N, nSB, aq.codes, aq.scales, T, dst, ldd);
+    } else {
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "not a Q5_K / Q6_K matrix");
+    }
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_q6k_to_planes(b200_ctx* ctx, const uint8_t* raw, size_t n_blocks, uint8_t* planes) {
+    const size_t n = n_blocks * 210;
+    q6k_to_planes_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(raw, n_blocks, planes);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}

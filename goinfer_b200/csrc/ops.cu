@@ -136,6 +136,25 @@ int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, i
     return us.check();
 }
 
+int b200_op_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* w, const float* a, int M, int K, int N, float* dst) {
+    if (K % 256 || (kind != B200_K_Q5K && kind != B200_K_Q6K)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "a Q5_K or Q6_K matrix with K %% 256 == 0");
+    Tmp t;
+    const size_t nb = (size_t)N * K / 256, wb = nb * (kind == B200_K_Q5K ? 176 : 210);
+    uint8_t *dw, *dp = nullptr; float *da, *dd; ActQ aq;
+    TMP_GET(ctx, t, dw, wb); TMP_GET(ctx, t, da, (size_t)M * K); TMP_GET(ctx, t, dd, (size_t)M * N);
+    TMP_GET(ctx, t, aq.codes, (size_t)M * K); TMP_GET(ctx, t, aq.scales, (size_t)M * 2 * (K / 32));
+    H2D(ctx, dw, w, wb); H2D(ctx, da, a, (size_t)M * K * 4);
+    if (kind == B200_K_Q6K) {
+        TMP_GET(ctx, t, dp, wb);
+        ST_TRY(launch_q6k_to_planes(ctx, dw, nb, dp));
+    }
+    ST_TRY(launch_quant_g32(ctx, da, M, K, aq));
+    ST_TRY(launch_kq_matmul(ctx, kind, kind == B200_K_Q6K ? dp : dw, N, K, aq, M, dd, N));
+    D2H(ctx, dst, dd, (size_t)M * N * 4);
+    SYNC(ctx);
+    return B200_OK;
+}
+
 int b200_op_topk(b200_ctx* ctx, const float* logits, int rows, int vocab, int k, float inv_temperature, int32_t* ids_out,
                  float* logits_out, double* z_out) {
     if (rows <= 0 || vocab <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad top-K shape");
@@ -368,6 +387,46 @@ int b200_bench_prefill_attention(b200_ctx* ctx, int rows, int pos0, int n_heads,
         ST_TRY(launch_prefill_attention(ctx, dq, n_heads * head_dim, rows, n_heads, n_kv_heads, head_dim, sc_, 0.f, 0, pos0, kv, dout, n_heads * head_dim));
     CUDA_TRY(ctx, cudaEventRecord(e1, ctx->stream));
     SYNC(ctx);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    *ms_out = ms / iters;
+    return B200_OK;
+}
+
+namespace {
+__global__ void __launch_bounds__(512) read_sum_kernel(const uint4* __restrict__ p, size_t n, unsigned* __restrict__ sink) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t st = (size_t)gridDim.x * blockDim.x;
+    unsigned s = 0;
+    for (; i + 3 * st < n; i += 4 * st) {
+        const uint4 a = p[i], b = p[i + st], c = p[i + 2 * st], d = p[i + 3 * st];
+        s += a.x ^ a.y ^ a.z ^ a.w ^ b.x ^ b.y ^ b.z ^ b.w ^ c.x ^ c.y ^ c.z ^ c.w ^ d.x ^ d.y ^ d.z ^ d.w;
+    }
+    for (; i < n; i += st) {
+        const uint4 a = p[i];
+        s += a.x ^ a.y ^ a.z ^ a.w;
+    }
+    if (s == 0x12345678u) sink[0] = s;  // keeps the loads alive; practically never taken
+}
+}  // namespace
+
+int b200_bench_read(b200_ctx* ctx, size_t bytes, int n_copies, int warmup, int iters, float* ms_out) {
+    if (bytes < 16 || n_copies <= 0 || iters <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad bench shape");
+    Tmp t;
+    const size_t n = bytes / 16;
+    uint8_t* buf; unsigned* sink;
+    TMP_GET(ctx, t, buf, n * 16 * n_copies); TMP_GET(ctx, t, sink, 1);
+    CUDA_TRY(ctx, cudaMemsetAsync(buf, 0x11, n * 16 * n_copies, ctx->stream));
+    const int grid = ctx->sm_count * 4;
+    cudaEvent_t e0, e1;
+    CUDA_TRY(ctx, cudaEventCreate(&e0)); CUDA_TRY(ctx, cudaEventCreate(&e1));
+    for (int i = 0; i < warmup; i++) read_sum_kernel<<<grid, 512, 0, ctx->stream>>>(reinterpret_cast<const uint4*>(buf) + (size_t)(i % n_copies) * n, n, sink);
+    CUDA_TRY(ctx, cudaEventRecord(e0, ctx->stream));
+    for (int i = 0; i < iters; i++) read_sum_kernel<<<grid, 512, 0, ctx->stream>>>(reinterpret_cast<const uint4*>(buf) + (size_t)(i % n_copies) * n, n, sink);
+    CUDA_TRY(ctx, cudaEventRecord(e1, ctx->stream));
+    SYNC(ctx);
+    LAUNCH_CHECK(ctx);
     float ms = 0;
     cudaEventElapsedTime(&ms, e0, e1);
     cudaEventDestroy(e0); cudaEventDestroy(e1);

@@ -150,6 +150,21 @@ class Ops:
         self._check(self.lib.b200_bench_q4k_matmul(self.ctx, M, K, N, klass, n_weight_copies, warmup, iters, C.byref(ms)))
         return ms.value
 
+    def kq_matmul(self, kind: int, raw: np.ndarray, a: np.ndarray, N: int) -> np.ndarray:
+        """Q5_K / Q6_K weights (the file's blocks) x f32 rows, quantized per 32 on the device."""
+        raw = np.ascontiguousarray(raw, np.uint8)
+        a = np.ascontiguousarray(a, np.float32)
+        M, K = a.shape
+        out = np.empty((M, N), np.float32)
+        self._check(self.lib.b200_op_kq_matmul(self.ctx, kind, raw.ctypes.data_as(C.POINTER(C.c_uint8)), a.ctypes.data_as(C.POINTER(C.c_float)),
+                                               M, K, N, out.ctypes.data_as(C.POINTER(C.c_float))))
+        return out
+
+    def bench_read(self, nbytes, n_copies=8, warmup=3, iters=20) -> float:
+        ms = C.c_float(0)
+        self._check(self.lib.b200_bench_read(self.ctx, C.c_size_t(nbytes), n_copies, warmup, iters, C.byref(ms)))
+        return ms.value
+
     def bench_attention(self, rows, ctx_lo, ctx_hi, n_heads, n_kv_heads, head_dim, block_rows=16, seed=2, warmup=3, iters=10):
         ms = C.c_float(0)
         kvb = C.c_double(0)

@@ -60,28 +60,46 @@ def make_cfg(s: Shape, n_slots: int, ctx_cap: int, kv_block_rows: int = 16, kv_p
     return c
 
 
-def host_weights(s: Shape, seed: int, n_layers: int = 0, sigma: float = 0.02):
+Q4_K_M_KINDS = {abi.T_WV: abi.K_Q6K, abi.T_DOWN: abi.K_Q6K, abi.T_LM_HEAD: abi.K_Q6K, abi.T_WK: abi.K_Q5K, abi.T_UP: abi.K_Q5K}
+"""A mix like a Q4_K_M file's (its 6-bit v, down and head; Q5_K stands in for the files that use it for q|k|v): q|k|v and
+gate|up become groups of unlike kinds."""
+
+
+def host_weights(s: Shape, seed: int, n_layers: int = 0, sigma: float = 0.02, kinds=None):
     """Yields (which, layer, expert, kind, rows, cols, array) for every tensor, built on the host.
-    Matrices are N(0, sigma) f32 quantized to Q4_K; norms are 1 + N(0, 0.05); embed/head are f16."""
+    Matrices are N(0, sigma) f32 quantized to Q4_K (or the K-quant `kinds` names for that tensor: {which: kind}, dense
+    models only); norms are 1 + N(0, 0.05); embed/head are f16 unless `kinds` names the head."""
     rng = np.random.default_rng(seed)
     H, qd, kvd = s.hidden, s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
+    kinds = kinds or {}
 
     def q(rows, cols):
         return q4k.quantize(rng.normal(0, sigma, (rows, cols)).astype(np.float32))
+
+    def mat(which, layer, rows, cols):
+        kind = kinds.get(which, abi.K_Q4K)
+        w = rng.normal(0, sigma, (rows, cols)).astype(np.float32)
+        if kind == abi.K_Q4K:
+            return which, layer, -1, kind, rows, cols, q4k.quantize(w)
+        from . import kquants
+        return which, layer, -1, kind, rows, cols, (kquants.q5k_quantize(w) if kind == abi.K_Q5K else kquants.q6k_quantize(w))
 
     def norm(n):
         return (1 + rng.normal(0, 0.05, n)).astype(np.float32)
 
     yield abi.T_EMBED, -1, -1, abi.K_F16, s.vocab, H, rng.normal(0, sigma, (s.vocab, H)).astype(np.float16)
-    yield abi.T_LM_HEAD, -1, -1, abi.K_F16, s.vocab, H, rng.normal(0, sigma, (s.vocab, H)).astype(np.float16)
+    if abi.T_LM_HEAD in kinds:
+        yield mat(abi.T_LM_HEAD, -1, s.vocab, H)
+    else:
+        yield abi.T_LM_HEAD, -1, -1, abi.K_F16, s.vocab, H, rng.normal(0, sigma, (s.vocab, H)).astype(np.float16)
     yield abi.T_FINAL_NORM, -1, -1, abi.K_F32, 1, H, norm(H)
     for l in range(n_layers or s.n_layers):
         yield abi.T_ATTN_NORM, l, -1, abi.K_F32, 1, H, norm(H)
         yield abi.T_FFN_NORM, l, -1, abi.K_F32, 1, H, norm(H)
-        yield abi.T_WQ, l, -1, abi.K_Q4K, qd, H, q(qd, H)
-        yield abi.T_WK, l, -1, abi.K_Q4K, kvd, H, q(kvd, H)
-        yield abi.T_WV, l, -1, abi.K_Q4K, kvd, H, q(kvd, H)
-        yield abi.T_WO, l, -1, abi.K_Q4K, H, qd, q(H, qd)
+        yield mat(abi.T_WQ, l, qd, H)
+        yield mat(abi.T_WK, l, kvd, H)
+        yield mat(abi.T_WV, l, kvd, H)
+        yield mat(abi.T_WO, l, H, qd)
         if s.qk_norm:
             yield abi.T_Q_NORM, l, -1, abi.K_F32, 1, s.head_dim, norm(s.head_dim)
             yield abi.T_K_NORM, l, -1, abi.K_F32, 1, s.head_dim, norm(s.head_dim)
@@ -92,14 +110,14 @@ def host_weights(s: Shape, seed: int, n_layers: int = 0, sigma: float = 0.02):
                 yield abi.T_EXP_UP, l, e, abi.K_Q4K, s.moe_ffn, H, q(s.moe_ffn, H)
                 yield abi.T_EXP_DOWN, l, e, abi.K_Q4K, H, s.moe_ffn, q(H, s.moe_ffn)
         else:
-            yield abi.T_GATE, l, -1, abi.K_Q4K, s.ffn, H, q(s.ffn, H)
-            yield abi.T_UP, l, -1, abi.K_Q4K, s.ffn, H, q(s.ffn, H)
-            yield abi.T_DOWN, l, -1, abi.K_Q4K, H, s.ffn, q(H, s.ffn)
+            yield mat(abi.T_GATE, l, s.ffn, H)
+            yield mat(abi.T_UP, l, s.ffn, H)
+            yield mat(abi.T_DOWN, l, H, s.ffn)
 
 
-def load_host_weights(residents, s: Shape, seed: int, n_layers: int = 0, sigma: float = 0.02):
+def load_host_weights(residents, s: Shape, seed: int, n_layers: int = 0, sigma: float = 0.02, kinds=None):
     """Uploads the same host-built tensors into every resident in `residents` (e.g. GPU and oracle)."""
-    for which, layer, expert, kind, rows, cols, arr in host_weights(s, seed, n_layers, sigma):
+    for which, layer, expert, kind, rows, cols, arr in host_weights(s, seed, n_layers, sigma, kinds):
         for r in residents:
             r.upload(which, arr, layer, expert, kind, rows, cols)
 

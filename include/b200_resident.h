@@ -57,6 +57,14 @@ extern "C" {
 #define B200_K_Q4K 2 /* GGUF Q4_K super-blocks, 144 bytes per 256 weights, row-major [rows][cols/256][144]
                         (decoder/gguf.go:1508-1537; device twin backend/cuda/actgroup.cu:311-355). A Q4K
                         matrix multiplies per-32-group int8 activations (backend/cuda/actgroup.cu:32-54). */
+#define B200_K_Q5K 3 /* GGUF Q5_K super-blocks, 176 bytes per 256 weights (d, dmin, 12 scale bytes, qh[32], qs[128]), as in
+                        the file; x per-32 int8 activations (backend/cuda/actgroup.cu:77-143). */
+#define B200_K_Q6K 4 /* GGUF Q6_K super-blocks, 210 bytes per 256 weights (ql[128], qh[64], 16 int8 sub-scales, d), uploaded as in
+                        the file and kept on the device as four planes (ql, qh, sub-scales, d: the layout of
+                        backend/cuda/pack_stream.go q6kPlanes); x per-32 int8 activations (backend/cuda/actgroup.cu:145-205).
+                        The Q5_K / Q6_K matmuls are held to the reference's own bar for them: within 1e-5 of sum |w*a| of the
+                        f64 product of the dequantized row (backend/cuda/kernels/kso1c_kernels_test.go:146-151). q|k|v and
+                        gate|up may mix Q4_K, Q5_K and Q6_K parts, as Q4_K_M files do. */
 
 /* ---- draw kinds ----------------------------------------------------------------------------------- */
 #define B200_DRAW_LOGITS 0 /* no draw: the row's logits are returned (BatchSeq.Draw == nil)          */
@@ -293,8 +301,15 @@ int b200_op_prefill_attention(b200_ctx* ctx, const float* q, const float* k, con
                               int n_heads, int n_kv_heads, int head_dim, float scale, float softcap,
                               int block_rows, float* out);
 
+/* dst[M][N] = x . W^T for W of kind B200_K_Q5K / B200_K_Q6K given as the file's blocks ([N][K/256][176 or 210] bytes) and f32
+ * x [M][K], quantized per 32 on the device like the step does. */
+int b200_op_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* w_host, const float* x_host, int M, int K, int N, float* dst_host);
+
 /* Device-resident micro-benchmarks: average device milliseconds per launch over `iters` launches after
  * `warmup`, of the kernel the step would pick (or `klass`), on synthetic resident data. */
+/* The read-only floor of a streaming kernel over `bytes` bytes: a grid-stride 16-byte-load kernel that only sums what it
+ * reads, launched back to back over `n_copies` copies of the buffer like the matmul benchmark launches its weights. */
+int b200_bench_read(b200_ctx* ctx, size_t bytes, int n_copies, int warmup, int iters, float* ms_out);
 int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_weight_copies,
                           int warmup, int iters, float* ms_out);
 int b200_bench_f16_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int warmup, int iters, float* ms_out);

@@ -130,6 +130,26 @@ def op_q4k_matmul_f64(raw: np.ndarray, a: np.ndarray, N: int) -> np.ndarray:
     return out
 
 
+def op_kq_dequant(kind: int, raw: np.ndarray, rows: int, cols: int, plant: int = 0) -> np.ndarray:
+    raw = np.ascontiguousarray(raw, np.uint8)
+    out = np.empty((rows, cols), np.float64)
+    st = lib().oracle_op_kq_dequant(kind, _p(raw, C.c_uint8), rows, cols, plant, _p(out, C.c_double))
+    assert st == 0
+    return out
+
+
+def op_kq_matmul_f64(kind: int, raw: np.ndarray, a: np.ndarray, N: int, plant: int = 0):
+    """-> (dst [M][N], bar [M][N] = sum |w*a|) in f64."""
+    raw = np.ascontiguousarray(raw, np.uint8)
+    a = np.ascontiguousarray(a, np.float32)
+    M, K = a.shape
+    out = np.empty((M, N), np.float64)
+    bar = np.empty((M, N), np.float64)
+    st = lib().oracle_op_kq_matmul_f64(kind, _p(raw, C.c_uint8), _p(a, C.c_float), M, K, N, plant, _p(out, C.c_double), _p(bar, C.c_double))
+    assert st == 0
+    return out, bar
+
+
 def op_q4k_quantize(w: np.ndarray) -> np.ndarray:
     w = np.ascontiguousarray(w, np.float32)
     rows, cols = w.shape

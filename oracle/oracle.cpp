@@ -112,6 +112,58 @@ inline void q4k_unpack(const uint8_t* blk, Q4KBlock* o) {
         }
 }
 
+// ---- GGUF Q5_K (176 bytes: d, dmin, 12 bytes of 6-bit scales and minimums, qh[32], qs[128]) and Q6_K (210 bytes: ql[128],
+//      qh[64], 16 int8 sub-scales, d) rows in f64, the formulas of ggml's dequantize_row_q5_K / dequantize_row_q6_K as the
+//      reference's own tests restate them (backend/cuda/kernels/ks_a1_test.go:69-114). `plant` > 0 makes one of the wrong
+//      readings that the reference's kernel test shows to be red (backend/cuda/kernels/kso1c_kernels_test.go:40-104):
+//      1 the fifth bit of Q5_K dropped, 2 the -32 of Q6_K dropped, 3 a Q6_K group read with its neighbour's sub-scale. ----
+inline void q5k_row(const uint8_t* raw, int nSB, double* out, int plant = 0) {
+    for (int sb = 0; sb < nSB; sb++) {
+        const uint8_t* b = raw + (size_t)sb * 176;
+        uint16_t hd, hm;
+        memcpy(&hd, b, 2);
+        memcpy(&hm, b + 2, 2);
+        const double d = f16_to_f32(hd), dmin = f16_to_f32(hm);
+        const uint8_t *sc = b + 4, *qh = b + 16, *qs = b + 48;
+        for (int j = 0; j < 4; j++) {
+            int s1, m1, s2, m2;
+            q4k_scale_min(2 * j, sc, &s1, &m1);
+            q4k_scale_min(2 * j + 1, sc, &s2, &m2);
+            for (int l = 0; l < 32; l++) {
+                double lo = qs[32 * j + l] & 15, hi = qs[32 * j + l] >> 4;
+                if (plant != 1 && (qh[l] & (1 << (2 * j)))) lo += 16;
+                if (plant != 1 && (qh[l] & (2 << (2 * j)))) hi += 16;
+                out[256 * sb + 64 * j + l] = d * s1 * lo - dmin * m1;
+                out[256 * sb + 64 * j + 32 + l] = d * s2 * hi - dmin * m2;
+            }
+        }
+    }
+}
+
+inline void q6k_row(const uint8_t* raw, int nSB, double* out, int plant = 0) {
+    const int off = plant == 2 ? 0 : 32;
+    for (int sb = 0; sb < nSB; sb++) {
+        const uint8_t* b = raw + (size_t)sb * 210;
+        uint16_t hd;
+        memcpy(&hd, b + 208, 2);
+        const double d = f16_to_f32(hd);
+        for (int n = 0; n < 2; n++) {
+            const uint8_t *ql = b + 64 * n, *qh = b + 128 + 32 * n;
+            const int8_t* sc = (const int8_t*)(b + 192 + 8 * n);
+            double* y = out + 256 * sb + 128 * n;
+            for (int l = 0; l < 32; l++) {
+                int is = l / 16;
+                if (plant == 3) is ^= 1;
+                const int q[4] = {(int)((ql[l] & 15) | (((qh[l] >> 0) & 3) << 4)) - off, (int)((ql[l + 32] & 15) | (((qh[l] >> 2) & 3) << 4)) - off,
+                                  (int)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - off, (int)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - off};
+                for (int g = 0; g < 4; g++) y[l + 32 * g] = d * (double)sc[is + 2 * g] * (double)q[g];
+            }
+        }
+    }
+}
+
+inline size_t kq_block_bytes(int kind) { return kind == B200_K_Q5K ? 176 : kind == B200_K_Q6K ? 210 : 144; }
+
 // ---- per-32 activation quantizer: backend/cuda/actgroup.cu:32-54, host twin
 //      backend/cuda/kernels/actgroup_kernel_test.go:69-91 ----
 void quant_g32(const float* x, int k, int8_t* codes, float* scales /*2*k/32*/) {
@@ -213,6 +265,7 @@ struct Mat {
     std::vector<float> f32;
     std::vector<uint16_t> f16;
     std::vector<uint8_t> q4k;
+    std::vector<double> deq;  // Q5_K / Q6_K rows, dequantized in f64 at upload
     bool present() const { return kind >= 0; }
 };
 
@@ -257,6 +310,27 @@ void matmul(const Mat& W, const float* a, int T, float* dst) {
                     }
                 }
                 for (int t = 0; t < T; t++) dst[(size_t)t * N + n] = acc[t];
+            }
+        }
+        return;
+    }
+    if (W.kind == B200_K_Q5K || W.kind == B200_K_Q6K) {
+        // the f64 sum of w[k] * (code[k] * scale[k/32]) over the dequantized row: the reference the native Q5_K / Q6_K
+        // kernels are held to, within 1e-5 of sum |w*a| (backend/cuda/kernels/kso1c_kernels_test.go:43-72,146-151)
+        const int nG = K / 32;
+        std::vector<int8_t> codes((size_t)T * K);
+        std::vector<float> scales((size_t)T * 2 * nG);
+#pragma omp parallel for schedule(static)
+        for (int t = 0; t < T; t++) quant_g32(a + (size_t)t * K, K, &codes[(size_t)t * K], &scales[(size_t)t * 2 * nG]);
+#pragma omp parallel for schedule(static)
+        for (int n = 0; n < N; n++) {
+            const double* w = &W.deq[(size_t)n * K];
+            for (int t = 0; t < T; t++) {
+                const int8_t* ca = &codes[(size_t)t * K];
+                const float* aS = &scales[(size_t)t * 2 * nG];
+                double s = 0;
+                for (int k = 0; k < K; k++) s += w[k] * (double)ca[k] * (double)aS[k >> 5];
+                dst[(size_t)t * N + n] = (float)s;
             }
         }
         return;
@@ -586,6 +660,14 @@ int oracle_upload_tensor(oracle_model* m, int which, int layer, int expert, int 
     if (kind == B200_K_F32 && bytes == n * 4) mat->f32.assign((const float*)host, (const float*)host + n);
     else if (kind == B200_K_F16 && bytes == n * 2) mat->f16.assign((const uint16_t*)host, (const uint16_t*)host + n);
     else if (kind == B200_K_Q4K && cols % 256 == 0 && bytes == n / 256 * 144) mat->q4k.assign((const uint8_t*)host, (const uint8_t*)host + bytes);
+    else if ((kind == B200_K_Q5K || kind == B200_K_Q6K) && cols % 256 == 0 && bytes == n / 256 * kq_block_bytes(kind)) {
+        mat->deq.resize(n);
+        const size_t rb = (size_t)cols / 256 * kq_block_bytes(kind);
+        for (int r = 0; r < rows; r++) {
+            if (kind == B200_K_Q5K) q5k_row((const uint8_t*)host + (size_t)r * rb, cols / 256, &mat->deq[(size_t)r * cols]);
+            else q6k_row((const uint8_t*)host + (size_t)r * rb, cols / 256, &mat->deq[(size_t)r * cols]);
+        }
+    }
     else { m->err = "tensor kind/size mismatch"; mat->kind = -1; return B200_BAD_ARGUMENT; }
     return B200_OK;
 }
@@ -965,6 +1047,47 @@ int oracle_op_q4k_matmul_f64(const uint8_t* w, const float* a, int M, int K, int
                 }
             }
             dst[(size_t)t * N + n] = acc;
+        }
+    }
+    return B200_OK;
+}
+
+// Q5_K / Q6_K rows in f64 (kind B200_K_Q5K / B200_K_Q6K), with an optional planted misreading.
+int oracle_op_kq_dequant(int kind, const uint8_t* w, int rows, int cols, int plant, double* out) {
+    if ((kind != B200_K_Q5K && kind != B200_K_Q6K) || cols % 256) return B200_BAD_ARGUMENT;
+    const size_t rb = (size_t)cols / 256 * kq_block_bytes(kind);
+    for (int r = 0; r < rows; r++) {
+        if (kind == B200_K_Q5K) q5k_row(w + (size_t)r * rb, cols / 256, out + (size_t)r * cols, plant);
+        else q6k_row(w + (size_t)r * rb, cols / 256, out + (size_t)r * cols, plant);
+    }
+    return B200_OK;
+}
+
+// dst[t][n] = sum_k w[n][k] * code[t][k] * scale[t][k/32] in f64 and bar[t][n] = sum |.|: the reference of the native
+// Q5_K / Q6_K matmul (kso1cRef). plant 4 reads every row one super-block late.
+int oracle_op_kq_matmul_f64(int kind, const uint8_t* w, const float* a, int M, int K, int N, int plant, double* dst, double* bar) {
+    if ((kind != B200_K_Q5K && kind != B200_K_Q6K) || K % 256) return B200_BAD_ARGUMENT;
+    const int nSB = K / 256, nG = K / 32;
+    const size_t bs = kq_block_bytes(kind), rb = (size_t)nSB * bs;
+    std::vector<int8_t> codes((size_t)M * K);
+    std::vector<float> scales((size_t)M * 2 * nG);
+    for (int t = 0; t < M; t++) quant_g32(a + (size_t)t * K, K, &codes[(size_t)t * K], &scales[(size_t)t * 2 * nG]);
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; n++) {
+        std::vector<double> row(K);
+        std::vector<uint8_t> r(w + (size_t)n * rb, w + (size_t)(n + 1) * rb);
+        if (plant == 4 && nSB > 1) std::rotate(r.begin(), r.begin() + bs, r.end());
+        if (kind == B200_K_Q5K) q5k_row(r.data(), nSB, row.data(), plant);
+        else q6k_row(r.data(), nSB, row.data(), plant);
+        for (int t = 0; t < M; t++) {
+            double s = 0, b = 0;
+            for (int k = 0; k < K; k++) {
+                const double x = row[k] * (double)codes[(size_t)t * K + k] * (double)scales[(size_t)t * 2 * nG + (k >> 5)];
+                s += x;
+                b += std::fabs(x);
+            }
+            dst[(size_t)t * N + n] = s;
+            if (bar) bar[(size_t)t * N + n] = b;
         }
     }
     return B200_OK;

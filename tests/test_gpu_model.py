@@ -380,6 +380,46 @@ def test_serve_driver_with_prefix_reuse_draws_the_same_ids():
     assert st1.prefill_rows == st0.prefill_rows - pr["rows_reused"]
 
 
+@pytest.mark.parametrize("klass", [abi.CLASS_EXACT, abi.CLASS_AUTO])
+def test_q4_k_m_like_model_with_q5k_and_q6k_parts(oracle_lib, klass, tmp_path):
+    """A model whose projections mix kinds the way a Q4_K_M file does (Q6_K v, down and head, Q5_K k and up: q|k|v and
+    gate|up become groups of unlike parts): a ragged prefill and greedy decode steps against the oracle, then the same
+    model read back from a GGUF file gives the same bits as the direct upload."""
+    from goinfer_b200 import gguf
+    from test_kquants import _tiny_gguf
+    path, s, ts = _tiny_gguf(tmp_path, "qwen3", synth.Q4_K_M_KINDS, seed=8)
+    mk = lambda: synth.make_cfg(s, 3, 96, 16, 0, 0, klass, 0)
+    g, o = Resident(mk()), oracle_lib.OracleResident(mk())
+    for which, layer, expert, kind, rows, cols, arr in ts:
+        for r in (g, o):
+            r.upload(which, arr, layer, expert, kind, rows, cols)
+    g.finalize()
+    o.finalize()
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, s.vocab, n).tolist() for n in (21, 5)]
+    first = []
+    for i, p in enumerate(prompts):
+        lg, lo = g.PrefillLast(None, 0, i, p), o.PrefillLast(None, 0, i, p)
+        ok, err = close_logits(lg, lo)
+        assert ok, (i, err)
+        first.append(int(np.argmax(lo)))
+    tok = list(first)
+    for step in range(6):
+        bg = g.StepBatch([BatchSeq(i, len(prompts[i]) + step, None, tok[i]) for i in range(2)])
+        bo = o.StepBatch([BatchSeq(i, len(prompts[i]) + step, None, tok[i]) for i in range(2)])
+        for i in range(2):
+            ok, err = close_logits(bg[i].Logits, bo[i].Logits)
+            assert ok, (step, i, err)
+            gid, oid = int(np.argmax(bg[i].Logits)), int(np.argmax(bo[i].Logits))
+            assert greedy_margin_ok(bo[i].Logits, gid, oid)
+        tok = [int(np.argmax(b.Logits)) for b in bo]
+    # through a file
+    f, d = gguf.load(path, lambda cfg: Resident(cfg), n_slots=3, ctx_cap=96, kernel_class=klass)
+    assert np.array_equal(f.PrefillLast(None, 0, 2, prompts[0]), g.PrefillLast(None, 0, 2, prompts[0]))
+    f.Close()
+    g.Close()
+
+
 def test_kv_pool_full_writes_nothing_and_bad_steps_are_refused(oracle_lib):
     g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=3, ctx_cap=64, seed=9, kv_pool_blocks=1 + 3)
     for r in (g, o):

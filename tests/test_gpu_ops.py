@@ -152,6 +152,38 @@ def test_q4k_batch_rows_equal_single_rows_within_class(ops):
     assert np.array_equal(big[:3], ops.q4k_matmul(raw, b[:3], N, klass=1))   # exact class: across the 8-row boundary too
 
 
+@pytest.mark.parametrize("kind", [abi.K_Q5K, abi.K_Q6K])
+def test_q5k_q6k_matmul_within_the_reference_bar(ops, oracle_lib, kind):
+    """The native Q5_K / Q6_K matmuls against the f64 product of the dequantized rows, |err| / sum|w*a| <= 1e-5, at the
+    super-block counts and the ragged row count of the reference's kernel test, for 1..9 activation rows; and every planted
+    misreading of the format (a dropped fifth bit, a dropped -32, a neighbour's sub-scale, a row read one super-block
+    late) is red against the kernel's output (backend/cuda/kernels/kso1c_kernels_test.go:108-177)."""
+    from test_kquants import random_blocks
+    rng = np.random.default_rng(1024)
+    N = 8 * 3 + 5
+    worst = 0.0
+    for nSB in (1, 2, 6, 12, 19, 32, 35):
+        K = 256 * nSB
+        raw = random_blocks(rng, kind, N, K)
+        for M in (1, 2, 3, 4, 5, 9):
+            a = rng.normal(0, 1, (M, K)).astype(np.float32)
+            a[:, rng.integers(0, K, 3)] *= 30.0    # outliers
+            got = ops.kq_matmul(kind, raw, a, N).astype(np.float64)
+            want, bar = oracle_lib.op_kq_matmul_f64(kind, raw, a, N)
+            e = np.abs(got - want) / (bar + 1e-30)
+            assert np.all(np.isfinite(got)) and e.max() <= 1e-5, (nSB, M, e.max())
+            worst = max(worst, e.max())
+            if M == 3:
+                for plant in ((1, 4) if kind == abi.K_Q5K else (2, 3, 4)):
+                    if plant == 4 and nSB == 1:
+                        continue
+                    bad, pb = oracle_lib.op_kq_matmul_f64(kind, raw, a, N, plant)
+                    assert (np.abs(got - bad) / (pb + 1e-30)).max() > 1e-5, (nSB, plant)
+                # a row's bits do not depend on the rows it is batched with
+                assert np.array_equal(ops.kq_matmul(kind, raw, a[1:2], N)[0], ops.kq_matmul(kind, raw, a, N)[1])
+    assert worst < 1e-5
+
+
 def test_rmsnorm(ops, oracle_lib):
     rng = np.random.default_rng(5)
     x = rng.normal(0, 3, (5, 2048)).astype(np.float32)
