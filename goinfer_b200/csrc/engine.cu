@@ -28,6 +28,7 @@ struct DevMat {
     size_t bytes = 0;
     DevMat* seg[3] = {nullptr, nullptr, nullptr};  // kKindMixed: the parts, in row order
     int n_seg = 0;
+    __half* f16 = nullptr;  // Q5_K / Q6_K, fast class: a dequantized copy for the tensor-core matmul at dense row counts
     bool present() const { return kind >= 0 && (p || n_seg > 0); }
 };
 
@@ -290,6 +291,7 @@ struct b200_model {
     ActQ aq_h, aq_ctx, aq_mid;
     __half* split = nullptr;
     AttnScratch asc;
+    float* kq_act = nullptr;       // fast class with Q5_K / Q6_K tensors: code * scale activations for their fp16 matmul
     void* umma_scratch = nullptr;  // fast class: tcgen05 matmul scratch
     size_t umma_bytes = 0;
     int* err_flag = nullptr;       // raised by a bounded device-side wait that gave up
@@ -443,7 +445,17 @@ int fuse_rows(b200_model* m, std::vector<DevMat*> parts, DevMat* out) {
 int matmul(b200_model* m, const DevMat& W, const float* xf, ActQ xq, int T, float* dst, int ldd) {
     b200_ctx* ctx = m->ctx;
     if (W.kind == B200_K_Q4K) return launch_q4k_matmul(ctx, (const uint8_t*)W.p, W.rows, W.cols, xq, T, dst, ldd, m->c.kernel_class);
-    if (W.kind == B200_K_Q5K || W.kind == B200_K_Q6K) return launch_kq_matmul(ctx, W.kind, (const uint8_t*)W.p, W.rows, W.cols, xq, T, dst, ldd);
+    if (W.kind == B200_K_Q5K || W.kind == B200_K_Q6K) {
+        // from 32 rows in the fast class: fp16 copy of the weights x (code * scale) activations on the tensor cores (the
+        // dp4a lane re-reads the matrix for every four rows); the weights are then within 2^-11 of their values
+        static const bool no_umma = getenv("B200_NO_UMMA") != nullptr;
+        if (W.f16 && m->kq_act && T >= 32 && m->c.kernel_class != B200_CLASS_EXACT && !no_umma && ctx->umma_scratch &&
+            f16w_umma_supported(W.f16, W.rows, W.cols) && f16w_umma_scratch_bytes(T, W.cols) <= ctx->umma_scratch_bytes) {
+            ST_TRY(launch_act_dequant(ctx, xq, T, W.cols, m->kq_act));
+            return launch_f16w_matmul_umma(ctx, W.f16, W.rows, W.cols, m->kq_act, T, dst, ldd, ctx->umma_scratch, ctx->umma_scratch_bytes, ctx->err_flag);
+        }
+        return launch_kq_matmul(ctx, W.kind, (const uint8_t*)W.p, W.rows, W.cols, xq, T, dst, ldd);
+    }
     if (W.kind == kKindMixed) {
         const bool defer = ctx->defer_reduce;
         ctx->defer_reduce = false;  // a part's K-split partials cannot stand for the whole output
@@ -840,6 +852,22 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
         int max_k = std::max(H, qd), max_n = std::max(ldq, H);
         if (F) { max_k = std::max(max_k, F); max_n = std::max(max_n, 2 * F); }
         m->umma_bytes = q4k_umma_scratch_bytes(MR, max_k, max_n);
+        // Q5_K / Q6_K tensors: fp16 copies for the tensor-core matmul from 32 rows on
+        std::vector<DevMat*> kq;
+        for (int l = 0; l < c.n_layers; l++) {
+            LayerW& L = m->layers[l];
+            for (DevMat* d : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down, &L.qkv, &L.gu})
+                if (d->p && (d->kind == B200_K_Q5K || d->kind == B200_K_Q6K)) kq.push_back(d);
+        }
+        if (m->head.p && (m->head.kind == B200_K_Q5K || m->head.kind == B200_K_Q6K)) kq.push_back(&m->head);
+        if (!kq.empty() && MR >= 32) {
+            for (DevMat* d : kq) {
+                ST_TRY(m->dalloc((void**)&d->f16, (size_t)d->rows * d->cols * 2, &m->weight_bytes));
+                ST_TRY(launch_kq_to_f16(ctx, d->kind, (const uint8_t*)d->p, d->rows, d->cols, d->f16));
+            }
+            ST_TRY(m->dalloc((void**)&m->kq_act, (size_t)MR * max_k * 4, sb));
+            m->umma_bytes = std::max(m->umma_bytes, f16w_umma_scratch_bytes(MR, max_k));
+        }
         ST_TRY(m->dalloc(&m->umma_scratch, m->umma_bytes, sb));
     }
     ST_TRY(m->dalloc((void**)&m->err_flag, 4, nullptr));

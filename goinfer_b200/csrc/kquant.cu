@@ -167,6 +167,50 @@ __global__ void __launch_bounds__(256) q6k_gemv_kernel(const uint8_t* __restrict
     }
 }
 
+// ---- fp16 copies for the tensor-core path at dense row counts (fast class): one thread per 32 weights ----
+__global__ void __launch_bounds__(256) q5k_to_f16_kernel(const uint8_t* __restrict__ W, size_t n_blocks, __half* __restrict__ out) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (block, sub-block)
+    if (i >= n_blocks * 8) return;
+    const size_t g = i >> 3;
+    const int j = (int)(i & 7);
+    const uint8_t* blk = W + g * 176;
+    const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+    const float d = kq_h2f((unsigned short)(hdr.x & 0xffffu)), dmin = kq_h2f((unsigned short)(hdr.x >> 16));
+    int sc, mn;
+    kq_scale_min(j, hdr.y, hdr.z, hdr.w, &sc, &mn);
+    const float ds = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)mn);
+    const uint8_t *qh = blk + 16, *qs = blk + 48 + 32 * (j >> 1);
+    __half* o = out + g * 256 + 32 * j;
+    for (int l = 0; l < 32; l++) {
+        const int code = ((j & 1) ? (qs[l] >> 4) : (qs[l] & 15)) | (((qh[l] >> j) & 1) << 4);
+        o[l] = __float2half_rn(__fmaf_rn(ds, (float)code, -dm));
+    }
+}
+
+__global__ void __launch_bounds__(256) q6k_to_f16_kernel(const uint8_t* __restrict__ W, size_t n_blocks, __half* __restrict__ out) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (block, group of 32)
+    if (i >= n_blocks * 8) return;
+    const size_t g = i >> 3;
+    const int grp = (int)(i & 7), hh = grp >> 2, gg = grp & 3;
+    const uint8_t* ql = W + g * 128 + 64 * hh + 32 * (gg & 1);
+    const uint8_t* qh = W + 128 * n_blocks + g * 64 + 32 * hh;
+    const int8_t* sc = reinterpret_cast<const int8_t*>(W + 192 * n_blocks + g * 16 + 8 * hh + 2 * gg);
+    const float d = kq_h2f(reinterpret_cast<const unsigned short*>(W + 208 * n_blocks)[g]);
+    __half* o = out + g * 256 + 32 * grp;
+    for (int l = 0; l < 32; l++) {
+        const int lo = (gg & 2) ? (ql[l] >> 4) : (ql[l] & 15);
+        const int code = (lo | (((qh[l] >> (2 * gg)) & 3) << 4)) - 32;
+        o[l] = __float2half_rn(__fmul_rn(__fmul_rn(d, (float)sc[l >> 4]), (float)code));
+    }
+}
+
+// x[t][k] = code * scale of its group: the activations as the K-quant lanes see them, for the fp16 tensor-core path
+__global__ void act_dequant_kernel(const int8_t* __restrict__ codes, const float* __restrict__ scales, int K, float* __restrict__ out) {
+    const int t = blockIdx.y, k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= K) return;
+    out[(size_t)t * K + k] = __fmul_rn((float)codes[(size_t)t * K + k], scales[(size_t)t * 2 * (K >> 5) + (k >> 5)]);
+}
+
 // the file's 210-byte blocks -> the four planes
 __global__ void q6k_to_planes_kernel(const uint8_t* __restrict__ raw, size_t TB, uint8_t* __restrict__ out) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (block, byte)
@@ -201,6 +245,23 @@ int launch_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* W, int N, int K, Ac
     } else {
         B200_FAIL(ctx, B200_BAD_ARGUMENT, "not a Q5_K / Q6_K matrix");
     }
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_kq_to_f16(b200_ctx* ctx, int kind, const uint8_t* W, int N, int K, __half* out) {
+    const size_t nb = (size_t)N * K / 256;
+    const unsigned grid = (unsigned)((nb * 8 + 255) / 256);
+    if (kind == B200_K_Q5K) q5k_to_f16_kernel<<<grid, 256, 0, ctx->stream>>>(W, nb, out);
+    else if (kind == B200_K_Q6K) q6k_to_f16_kernel<<<grid, 256, 0, ctx->stream>>>(W, nb, out);
+    else B200_FAIL(ctx, B200_BAD_ARGUMENT, "not a Q5_K / Q6_K matrix");
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_act_dequant(b200_ctx* ctx, ActQ aq, int T, int K, float* out) {
+    dim3 grid(ceil_div(K, 256), T);
+    act_dequant_kernel<<<grid, 256, 0, ctx->stream>>>(aq.codes, aq.scales, K, out);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }

@@ -434,6 +434,52 @@ int b200_bench_read(b200_ctx* ctx, size_t bytes, int n_copies, int warmup, int i
     return B200_OK;
 }
 
+namespace {
+// random code bytes with scales of a sane size at the f16 fields (Q5_K: d and dmin at 0 and 2; Q6_K planes: the d plane)
+__global__ void kq_fill_kernel(uint8_t* __restrict__ w, size_t n_bytes, size_t n_blocks, int kind, uint64_t seed) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_bytes) return;
+    uint64_t z = (i + 1) * 0x9E3779B97F4A7C15ull + seed;
+    z ^= z >> 31; z *= 0xBF58476D1CE4E5B9ull; z ^= z >> 29;
+    uint8_t v = (uint8_t)(z >> 24);
+    if (kind == B200_K_Q5K) {
+        const size_t o = i % 176;
+        if (o < 4) v = (o & 1) ? 0x20 : (uint8_t)(z >> 40);   // f16 with exponent byte 0x20: about 0.008 .. 0.016
+    } else {
+        if (i >= 208 * n_blocks) v = ((i - 208 * n_blocks) & 1) ? 0x20 : (uint8_t)(z >> 40);
+    }
+    w[i] = v;
+}
+}  // namespace
+
+int b200_bench_kq_matmul(b200_ctx* ctx, int kind, int M, int K, int N, int n_weight_copies, int warmup, int iters, float* ms_out) {
+    if (K % 256 || M <= 0 || N <= 0 || n_weight_copies <= 0 || iters <= 0 || (kind != B200_K_Q5K && kind != B200_K_Q6K))
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad bench shape");
+    Tmp t;
+    const size_t nb = (size_t)N * K / 256, wb = nb * (kind == B200_K_Q5K ? 176 : 210), wbp = (wb + 255) & ~(size_t)255;
+    uint8_t* dw; float *da, *dd; ActQ aq;
+    TMP_GET(ctx, t, dw, wbp * n_weight_copies); TMP_GET(ctx, t, da, (size_t)M * K); TMP_GET(ctx, t, dd, (size_t)M * N);
+    TMP_GET(ctx, t, aq.codes, (size_t)M * K); TMP_GET(ctx, t, aq.scales, (size_t)M * 2 * (K / 32));
+    for (int c = 0; c < n_weight_copies; c++) {
+        kq_fill_kernel<<<(unsigned)((wb + 255) / 256), 256, 0, ctx->stream>>>(dw + (size_t)c * wbp, wb, nb, kind, 17 + c);
+        LAUNCH_CHECK(ctx);
+    }
+    ST_TRY(launch_synth_normal_f32(ctx, da, (size_t)M * K, 1.f, 5));
+    ST_TRY(launch_quant_g32(ctx, da, M, K, aq));
+    cudaEvent_t e0, e1;
+    CUDA_TRY(ctx, cudaEventCreate(&e0)); CUDA_TRY(ctx, cudaEventCreate(&e1));
+    for (int i = 0; i < warmup; i++) ST_TRY(launch_kq_matmul(ctx, kind, dw + (size_t)(i % n_weight_copies) * wbp, N, K, aq, M, dd, N));
+    CUDA_TRY(ctx, cudaEventRecord(e0, ctx->stream));
+    for (int i = 0; i < iters; i++) ST_TRY(launch_kq_matmul(ctx, kind, dw + (size_t)(i % n_weight_copies) * wbp, N, K, aq, M, dd, N));
+    CUDA_TRY(ctx, cudaEventRecord(e1, ctx->stream));
+    SYNC(ctx);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    *ms_out = ms / iters;
+    return B200_OK;
+}
+
 int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_weight_copies, int warmup, int iters, float* ms_out) {
     if (K % 256 || M <= 0 || N <= 0 || n_weight_copies <= 0 || iters <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad bench shape");
     Tmp t;

@@ -48,6 +48,7 @@ def main():
     g.add_argument("--klass", type=int, default=0)
     g.add_argument("--iters", type=int, default=20)
     g.add_argument("--warmup", type=int, default=3)
+    g.add_argument("--kind", choices=["q4k", "q5k", "q6k"], default="q4k", help="q5k / q6k: the native K-quant lanes")
     args = ap.parse_args()
     from .ops import Ops
     ops = Ops(0)
@@ -71,10 +72,16 @@ def main():
         print(json.dumps({"kernel": "prefill attention (causal run)", "rows": args.rows, "pos0": args.pos0, "ms_per_launch": ms,
                           "TFLOPps": flop / ms / 1e9}))
     else:
+        from . import abi
         for m in args.rows:
-            ms = ops.bench_q4k_matmul(m, args.k, args.n, args.klass, 8, args.warmup, args.iters)
-            wb = args.n * args.k * 144 / 256
-            print(json.dumps({"kernel": "q4k matmul", "rows": m, "n": args.n, "k": args.k, "ms_per_launch": ms,
+            if args.kind == "q4k":
+                ms = ops.bench_q4k_matmul(m, args.k, args.n, args.klass, 8, args.warmup, args.iters)
+                wb = args.n * args.k * 144 / 256
+            else:
+                kind = abi.K_Q5K if args.kind == "q5k" else abi.K_Q6K
+                ms = ops.bench_kq_matmul(kind, m, args.k, args.n, 8, args.warmup, args.iters)
+                wb = args.n * args.k * (176 if args.kind == "q5k" else 210) / 256
+            print(json.dumps({"kernel": args.kind + " matmul", "rows": m, "n": args.n, "k": args.k, "ms_per_launch": ms,
                               "weight_GBps": wb / ms / 1e6, "TMACps": m * args.n * args.k / ms / 1e9}))
 
 

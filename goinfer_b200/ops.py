@@ -160,6 +160,11 @@ class Ops:
                                                M, K, N, out.ctypes.data_as(C.POINTER(C.c_float))))
         return out
 
+    def bench_kq_matmul(self, kind, M, K, N, n_weight_copies=8, warmup=3, iters=20) -> float:
+        ms = C.c_float(0)
+        self._check(self.lib.b200_bench_kq_matmul(self.ctx, kind, M, K, N, n_weight_copies, warmup, iters, C.byref(ms)))
+        return ms.value
+
     def bench_read(self, nbytes, n_copies=8, warmup=3, iters=20) -> float:
         ms = C.c_float(0)
         self._check(self.lib.b200_bench_read(self.ctx, C.c_size_t(nbytes), n_copies, warmup, iters, C.byref(ms)))

@@ -310,6 +310,8 @@ int b200_op_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* w_host, const floa
 /* The read-only floor of a streaming kernel over `bytes` bytes: a grid-stride 16-byte-load kernel that only sums what it
  * reads, launched back to back over `n_copies` copies of the buffer like the matmul benchmark launches its weights. */
 int b200_bench_read(b200_ctx* ctx, size_t bytes, int n_copies, int warmup, int iters, float* ms_out);
+/* The Q5_K / Q6_K matmul (kind B200_K_Q5K / B200_K_Q6K) on random blocks with sane scales, cycled over copies. */
+int b200_bench_kq_matmul(b200_ctx* ctx, int kind, int M, int K, int N, int n_weight_copies, int warmup, int iters, float* ms_out);
 int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_weight_copies,
                           int warmup, int iters, float* ms_out);
 int b200_bench_f16_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int warmup, int iters, float* ms_out);

@@ -388,7 +388,7 @@ def test_q4_k_m_like_model_with_q5k_and_q6k_parts(oracle_lib, klass, tmp_path):
     from goinfer_b200 import gguf
     from test_kquants import _tiny_gguf
     path, s, ts = _tiny_gguf(tmp_path, "qwen3", synth.Q4_K_M_KINDS, seed=8)
-    mk = lambda: synth.make_cfg(s, 3, 96, 16, 0, 0, klass, 0)
+    mk = lambda: synth.make_cfg(s, 4, 96, 16, 0, 0, klass, 0)
     g, o = Resident(mk()), oracle_lib.OracleResident(mk())
     for which, layer, expert, kind, rows, cols, arr in ts:
         for r in (g, o):
@@ -413,8 +413,17 @@ def test_q4_k_m_like_model_with_q5k_and_q6k_parts(oracle_lib, klass, tmp_path):
             gid, oid = int(np.argmax(bg[i].Logits)), int(np.argmax(bo[i].Logits))
             assert greedy_margin_ok(bo[i].Logits, gid, oid)
         tok = [int(np.argmax(b.Logits)) for b in bo]
+    # a 40-row pass: in the fast class the Q5_K / Q6_K parts go through their fp16 copies on the tensor cores
+    # (weights within 2^-11 of their values: held to the bars the reference holds its GPU backends to against its CPU path,
+    # decoder/selftest_gpu.go:30-35, and to a max-abs error of a few hundredths on logits of order one)
+    p40 = rng.integers(0, s.vocab, 40).tolist()
+    lg, lo = g.PrefillLast(None, 0, 3, p40).astype(np.float64), o.PrefillLast(None, 0, 3, p40).astype(np.float64)
+    cos = float(lg @ lo / (np.linalg.norm(lg) * np.linalg.norm(lo)))
+    rel = float(np.linalg.norm(lg - lo) / np.linalg.norm(lo))
+    assert cos >= 0.9995 and rel <= 0.03 and np.abs(lg - lo).max() <= 0.05, (cos, rel, np.abs(lg - lo).max())
+    assert greedy_margin_ok(lo, int(np.argmax(lg)), int(np.argmax(lo)))
     # through a file
-    f, d = gguf.load(path, lambda cfg: Resident(cfg), n_slots=3, ctx_cap=96, kernel_class=klass)
+    f, d = gguf.load(path, lambda cfg: Resident(cfg), n_slots=4, ctx_cap=96, kernel_class=klass)
     assert np.array_equal(f.PrefillLast(None, 0, 2, prompts[0]), g.PrefillLast(None, 0, 2, prompts[0]))
     f.Close()
     g.Close()
