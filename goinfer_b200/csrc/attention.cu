@@ -211,6 +211,8 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const float* __restrict__
                                                        const __half* __restrict__ kpool, const __half* __restrict__ vpool,
                                                        const int32_t* __restrict__ table, int max_blocks, int block_rows,
                                                        float* __restrict__ partial, int max_splits, int split_keys) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int KS = HD / 16, CPR = HD / 8, ROWB = HD * 2, TILE = 16 * ROWB, CPL = 16 * CPR / 32;
     extern __shared__ __align__(128) uint8_t attn_smem[];
     const int r = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
@@ -424,6 +426,8 @@ template <int HD>
 __global__ void __launch_bounds__(2 * HD) attn_combine2_kernel(const float* __restrict__ partial, int nH, int max_splits, int split_keys,
                                                                const int32_t* __restrict__ row_pos, float* __restrict__ out,
                                                                int8_t* __restrict__ codes, float* __restrict__ scales) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int TPH = HD / 2;  // threads per head
     const int h = blockIdx.x * 4 + threadIdx.x / TPH, r = blockIdx.y, e = 2 * (threadIdx.x % TPH);
     const int nsp = (row_pos[r] + 1 + split_keys - 1) / split_keys;
@@ -488,7 +492,7 @@ __global__ void __launch_bounds__(2 * HD) attn_combine2_kernel(const float* __re
 template <int HD>
 void launch_combine(b200_ctx* ctx, const float* partial, int nH, int T, int max_splits, int split_keys, const int32_t* row_pos, float* out, ActQ aq) {
     if (nH % 4 == 0 && !((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(out)) & 7) && !(reinterpret_cast<uintptr_t>(aq.codes) & 1))
-        attn_combine2_kernel<HD><<<dim3(nH / 4, T), 2 * HD, 0, ctx->stream>>>(partial, nH, max_splits, split_keys, row_pos, out, aq.codes, aq.scales);
+        launch_pdl(attn_combine2_kernel<HD>, dim3(nH / 4, T), dim3(2 * HD), 0, ctx->stream, partial, nH, max_splits, split_keys, row_pos, out, aq.codes, aq.scales);
     else
         attn_combine_kernel<HD><<<dim3(nH, T), HD, 0, ctx->stream>>>(partial, nH, max_splits, split_keys, row_pos, out, aq.codes, aq.scales);
 }
@@ -645,8 +649,8 @@ int run_mma(b200_ctx* ctx, const float* q, int ldq, int T, int nH, int nKV, floa
     dim3 grid(nsp, nKV, T);
     {
         ProfScope ps(ctx, PROF_ATTN_SPLIT);
-        attn_mma_kernel<HD, G><<<grid, 128, smem, ctx->stream>>>(q, ldq, nH, nKV, scale, cap, row_slot, row_pos, kv.k, kv.v, kv.table,
-                                                                kv.max_blocks, kv.block_rows, sc.partial, sc.max_splits, kMmaSplitKeys);
+        launch_pdl(attn_mma_kernel<HD, G>, grid, dim3(128), smem, ctx->stream, q, ldq, nH, nKV, scale, cap, row_slot, row_pos, kv.k, kv.v, kv.table,
+                   kv.max_blocks, kv.block_rows, sc.partial, sc.max_splits, kMmaSplitKeys);
     }
     LAUNCH_CHECK(ctx);
     {

@@ -110,6 +110,39 @@ struct ProfScope {
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// ---- programmatic dependent launch -------------------------------------------------------------------------------
+// A kernel launched with launch_pdl may start while the kernel before it on the stream is still running: its blocks are
+// placed as soon as every block of the earlier kernel has called pdl_trigger() (or left), and they must call pdl_wait()
+// before they read or write anything an earlier kernel may touch; pdl_wait() returns when the earlier kernels have
+// completed and their writes are visible. What runs before the wait (index arithmetic, barrier set-up, loads of weights,
+// which no kernel writes) overlaps the earlier kernel's tail, and the launch latency disappears from the chain.
+// RULE: only kernels whose every thread reaches pdl_wait() before its first dependent access go through launch_pdl.
+// Without the launch attribute both calls do nothing.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static const bool on = getenv("B200_NO_PDL") == nullptr;
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // an error surfaces in LAUNCH_CHECK's cudaGetLastError
+}
+#endif
+
 // ---- device buffers a Q4_K matmul reads: int8 codes [T][K] and scales [T][2*K/32] ----
 struct ActQ {
     int8_t* codes = nullptr;

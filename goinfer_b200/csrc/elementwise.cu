@@ -70,6 +70,8 @@ __device__ __forceinline__ void quant_group_quad(const float (&y)[8], int8_t* co
 
 __global__ void embed_gather_kernel(const void* __restrict__ table, int kind, const int32_t* __restrict__ ids, int H,
                                     float scale, float* __restrict__ h) {
+    pdl_trigger();
+    pdl_wait();
     int r = blockIdx.x;
     size_t id = (size_t)ids[r];
     float* out = h + (size_t)r * H;
@@ -169,6 +171,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_quant_vec_kernel(float* __res
                                                                     float* __restrict__ normed, int8_t* __restrict__ codes,
                                                                     float* __restrict__ scales, const int32_t* __restrict__ gather_rows,
                                                                     int n_parts, size_t part_stride) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ double red[8];
     const int j = blockIdx.x, r = gather_rows ? gather_rows[j] : j, nC = H >> 3, nG = H >> 5;
     float* hr = h + (size_t)r * H;
@@ -293,6 +297,8 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float* __restri
 template <bool F64>
 __global__ void __launch_bounds__(256) swiglu_quant_vec_kernel(const float* __restrict__ gate_up, int F, int ld, float* __restrict__ mid,
                                                                int8_t* __restrict__ codes, float* __restrict__ scales) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.y, nG = F >> 5, nC = F >> 3;
     const int c = blockIdx.x * 256 + threadIdx.x;
     if (blockIdx.x * 256 + (int)(threadIdx.x & ~31u) >= nC) return;  // a whole warp past the row
@@ -326,6 +332,8 @@ __global__ void swiglu_plain_kernel(const float* __restrict__ gate_up, int F, in
 }
 
 __global__ void add_kernel(float* __restrict__ h, const float* __restrict__ d, size_t n, int n_parts, size_t part_stride) {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) h[i] = __fadd_rn(h[i], n_parts ? parts_at(d, part_stride, n_parts, i) : d[i]);
 }
@@ -405,6 +413,8 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvstore_vec_kernel(
     const int32_t* __restrict__ row_pos, __half* __restrict__ kpool, __half* __restrict__ vpool,
     const int32_t* __restrict__ table, int max_blocks, int block_rows, const float* __restrict__ parts, int n_parts,
     size_t part_stride) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int hd = 128;
     __shared__ double cs[2 * 64];  // [half] cos, [half] sin
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_heads = nH + 2 * nKV;
@@ -500,7 +510,7 @@ __global__ void fold_experts_kernel(const float* __restrict__ eo, const float* _
 }  // namespace
 
 int launch_embed_gather(b200_ctx* ctx, const void* table, int kind, const int32_t* ids, int T, int H, float scale, float* h) {
-    embed_gather_kernel<<<T, 256, 0, ctx->stream>>>(table, kind, ids, H, (scale == 0.f ? 1.f : scale), h);
+    launch_pdl(embed_gather_kernel, dim3(T), dim3(256), 0, ctx->stream, table, kind, ids, H, (scale == 0.f ? 1.f : scale), h);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }
@@ -520,11 +530,11 @@ int launch_add_rmsnorm_quant(b200_ctx* ctx, float* h, const float* delta, const 
                                                     reinterpret_cast<uintptr_t>(normed) | (uintptr_t)(pt.stride * 4)) & 15) &&
                      !(reinterpret_cast<uintptr_t>(aq.codes) & 7);
     if (vec && H <= 2048)
-        add_rmsnorm_quant_vec_kernel<1><<<T, 256, 0, ctx->stream>>>(h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
+        launch_pdl(add_rmsnorm_quant_vec_kernel<1>, dim3(T), dim3(256), 0, ctx->stream, h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
     else if (vec && H <= 4096)
-        add_rmsnorm_quant_vec_kernel<2><<<T, 256, 0, ctx->stream>>>(h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
+        launch_pdl(add_rmsnorm_quant_vec_kernel<2>, dim3(T), dim3(256), 0, ctx->stream, h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
     else if (vec)
-        add_rmsnorm_quant_vec_kernel<4><<<T, 256, 0, ctx->stream>>>(h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
+        launch_pdl(add_rmsnorm_quant_vec_kernel<4>, dim3(T), dim3(256), 0, ctx->stream, h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
     else
         add_rmsnorm_quant_kernel<<<T, 256, smem, ctx->stream>>>(h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
     LAUNCH_CHECK(ctx);
@@ -547,8 +557,8 @@ int launch_swiglu_quant(b200_ctx* ctx, const float* gate_up, int T, int F, int l
                          !(reinterpret_cast<uintptr_t>(aq.codes) & 7);
         if (vec) {
             dim3 grid(ceil_div(F / 8, 256), T);
-            if (f64_silu) swiglu_quant_vec_kernel<true><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales);
-            else swiglu_quant_vec_kernel<false><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales);
+            if (f64_silu) launch_pdl(swiglu_quant_vec_kernel<true>, grid, dim3(256), 0, ctx->stream, gate_up, F, ld, mid, aq.codes, aq.scales);
+            else launch_pdl(swiglu_quant_vec_kernel<false>, grid, dim3(256), 0, ctx->stream, gate_up, F, ld, mid, aq.codes, aq.scales);
         } else {
             dim3 grid(ceil_div(F / 32, 8), T);
             if (f64_silu) swiglu_quant_kernel<true><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales);
@@ -568,7 +578,7 @@ int launch_add(b200_ctx* ctx, float* h, const float* delta, size_t n) {
         pt = ctx->pending;
         ctx->pending = Parts{};
     }
-    add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(h, pt.n ? pt.p : delta, n, pt.n, pt.stride);
+    launch_pdl(add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, ctx->stream, h, pt.n ? pt.p : delta, n, pt.n, pt.stride);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }
@@ -596,8 +606,8 @@ int launch_qknorm_rope_kvstore(b200_ctx* ctx, float* qkv, int ld, int T, int nH,
                      !((reinterpret_cast<uintptr_t>(kv.k) | reinterpret_cast<uintptr_t>(kv.v)) & 7);
     if (vec) {
         dim3 grid(T, ceil_div(nH + 2 * nKV, 16));
-        qknorm_rope_kvstore_vec_kernel<<<grid, 256, 0, ctx->stream>>>(qkv, ld, nH, nKV, rot_half, inv_freq, q_norm, k_norm, eps, row_slot, row_pos,
-                                                                      kv.k, kv.v, kv.table, kv.max_blocks, kv.block_rows, pt.p, pt.n, pt.stride);
+        launch_pdl(qknorm_rope_kvstore_vec_kernel, grid, dim3(256), 0, ctx->stream, qkv, ld, nH, nKV, rot_half, inv_freq, q_norm, k_norm, eps, row_slot,
+                   row_pos, kv.k, kv.v, kv.table, kv.max_blocks, kv.block_rows, pt.p, pt.n, pt.stride);
     } else
     qknorm_rope_kvstore_kernel<<<T, 256, smem, ctx->stream>>>(qkv, ld, nH, nKV, hd, rot_half, inv_freq, q_norm, k_norm, eps,
                                                               row_slot, row_pos, kv.k, kv.v, kv.table, kv.max_blocks,

@@ -418,6 +418,8 @@ template <int TT, int R, int U>
 __global__ void __launch_bounds__(256) q4k_gemv_dp4a_kernel(const uint8_t* __restrict__ W, int N, int nSB,
                                                             const int8_t* __restrict__ codes, const float* __restrict__ scales,
                                                             float* __restrict__ dst, int ldd) {
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int n0 = (blockIdx.x * 8 + warp) * R;
     if (n0 >= N) return;
@@ -511,8 +513,8 @@ template <int TT>
 int run_q4k_gemv(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, float* dst, int ldd) {
     ProfScope ps(ctx, PROF_Q4K_GEMM);
     // 2 rows per warp at one token, 4 at two or three (the activation loads are shared by a warp's rows)
-    if (TT == 1) q4k_gemv_dp4a_kernel<TT, 2, 1><<<ceil_div(N, 16), 256, 0, ctx->stream>>>(W, N, nSB, aq.codes, aq.scales, dst, ldd);
-    else q4k_gemv_dp4a_kernel<TT, 4, 1><<<ceil_div(N, 32), 256, 0, ctx->stream>>>(W, N, nSB, aq.codes, aq.scales, dst, ldd);
+    if (TT == 1) launch_pdl(q4k_gemv_dp4a_kernel<TT, 2, 1>, dim3(ceil_div(N, 16)), dim3(256), 0, ctx->stream, W, N, nSB, aq.codes, aq.scales, dst, ldd);
+    else launch_pdl(q4k_gemv_dp4a_kernel<TT, 4, 1>, dim3(ceil_div(N, 32)), dim3(256), 0, ctx->stream, W, N, nSB, aq.codes, aq.scales, dst, ldd);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }

@@ -29,6 +29,7 @@ __global__ void __launch_bounds__(kHThreads, 1) f16w_umma_gemm_kernel(const __gr
                                                                       const __half* __restrict__ xhi, const __half* __restrict__ xlo,
                                                                       int T, float* __restrict__ dst, int ldd,
                                                                       int* __restrict__ err_flag) {
+    pdl_trigger();
     extern __shared__ __align__(1024) uint8_t h_smem[];
     __shared__ __align__(8) uint64_t full_bar[kHStages], empty_bar[kHStages];
     __shared__ unsigned tmem_base_s;
@@ -56,6 +57,7 @@ __global__ void __launch_bounds__(kHThreads, 1) f16w_umma_gemm_kernel(const __gr
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = tmem_base_s;
     volatile int* abort_v = &abort_s;
+    pdl_wait();  // set up while the kernel before this one drained; its outputs are complete from here
 
     if (warp == 8 && lane == 0) {
         // ---- loader ----
@@ -152,6 +154,8 @@ __global__ void __launch_bounds__(kHThreads, 1) f16w_umma_gemm_kernel(const __gr
 // x f32 [T][K] -> hi and lo f16 parts, each stored as the MMA's shared-memory tiles: [token tile of 128][chunk of 64
 // along K][128 rows][64], the 16-byte chunk c of a row at position c ^ (t & 7). Rows past T are written as zeros.
 __global__ void split_to_tiles_kernel(const float* __restrict__ x, int T, int K, __half* __restrict__ hi, __half* __restrict__ lo) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.y;
     const int k8 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (k8 >= K) return;
@@ -223,7 +227,7 @@ int launch_f16w_matmul_umma(b200_ctx* ctx, const __half* W, int N, int K, const 
     __half* lo = hi + (size_t)t_tiles * 128 * K;
     {
         dim3 grid(ceil_div(K / 8, 256), t_tiles * 128);
-        split_to_tiles_kernel<<<grid, 256, 0, ctx->stream>>>(x, T, K, hi, lo);
+        launch_pdl(split_to_tiles_kernel, grid, dim3(256), 0, ctx->stream, x, T, K, hi, lo);
         LAUNCH_CHECK(ctx);
     }
     constexpr int smem = kHStages * kHStageBytes + 1024;
@@ -237,7 +241,7 @@ int launch_f16w_matmul_umma(b200_ctx* ctx, const __half* W, int N, int K, const 
     dim3 grid(t_tiles, ceil_div(N, 256));
     {
         ProfScope ps(ctx, PROF_HEAD_GEMM);
-        f16w_umma_gemm_kernel<<<grid, kHThreads, smem, ctx->stream>>>(*wmap, N, K, hi, lo, T, dst, ldd, err_flag);
+        launch_pdl(f16w_umma_gemm_kernel, grid, dim3(kHThreads), smem, ctx->stream, *wmap, N, K, hi, lo, T, dst, ldd, err_flag);
     }
     LAUNCH_CHECK(ctx);
     return B200_OK;

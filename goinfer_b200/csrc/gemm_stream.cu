@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(kSThreads) q4k_stream_kernel(const __grid_cons
                                                                const __grid_constant__ CUtensorMap smap, int N, int nSB,
                                                                int T, float* __restrict__ dst, int ldd, size_t split_stride,
                                                                int* __restrict__ err_flag, const int32_t* __restrict__ offs) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(1024) uint8_t s_ring_raw[];
     uint8_t* s_ring = s_ring_raw + ((1024u - (smem_u32(s_ring_raw) & 1023u)) & 1023u);  // the launch reserves 1 KB for this round-up
     constexpr int kSStages = stream_stages(NT), kSStageBytes = stream_stage_bytes(NT);
@@ -246,6 +248,8 @@ __global__ void __launch_bounds__(kSThreads) q4k_stream_kernel(const __grid_cons
 // dst[t][n] = sum over splits, in split order
 __global__ void stream_reduce_kernel(const float* __restrict__ part, size_t split_stride, int splits, int T, int N,
                                      float* __restrict__ dst, int ldd) {
+    pdl_trigger();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)T * N) return;
     const int t = (int)(i / N), n = (int)(i % N);
@@ -300,12 +304,12 @@ int run_stream(b200_ctx* ctx, const CUtensorMap* wmap, int N, int nSB, ActQ aq, 
     float* out = splits > 1 ? part : dst;
     {
         ProfScope ps(ctx, PROF_Q4K_GEMM);
-        q4k_stream_kernel<NT><<<grid, kSThreads, smem, ctx->stream>>>(*wmap, *cmap, *smap, N, nSB, T, out, splits > 1 ? N : ldd,
-                                                                     splits > 1 ? (size_t)T * N : 0, ctx->err_flag, nullptr);
+        launch_pdl(q4k_stream_kernel<NT>, grid, dim3(kSThreads), smem, ctx->stream, *wmap, *cmap, *smap, N, nSB, T, out, splits > 1 ? N : ldd,
+                   splits > 1 ? (size_t)T * N : (size_t)0, ctx->err_flag, (const int32_t*)nullptr);
     }
     LAUNCH_CHECK(ctx);
     if (splits > 1) {
-        stream_reduce_kernel<<<(unsigned)(((size_t)T * N + 255) / 256), 256, 0, ctx->stream>>>(part, (size_t)T * N, splits, T, N, dst, ldd);
+        launch_pdl(stream_reduce_kernel, dim3((unsigned)(((size_t)T * N + 255) / 256)), dim3(256), 0, ctx->stream, part, (size_t)T * N, splits, T, N, dst, ldd);
         LAUNCH_CHECK(ctx);
     }
     return B200_OK;
@@ -354,7 +358,7 @@ int launch_q4k_matmul_stream_grouped(b200_ctx* ctx, const uint8_t* W_all, int n_
     dim3 grid(N / kSRows, n_experts);
     {
         ProfScope ps(ctx, PROF_Q4K_GEMM);
-        q4k_stream_kernel<NT><<<grid, kSThreads, smem, ctx->stream>>>(*wmap, *cmap, *smap, N, nSB, 0, dst, ldd, 0, ctx->err_flag, offs);
+        launch_pdl(q4k_stream_kernel<NT>, grid, dim3(kSThreads), smem, ctx->stream, *wmap, *cmap, *smap, N, nSB, 0, dst, ldd, (size_t)0, ctx->err_flag, offs);
     }
     LAUNCH_CHECK(ctx);
     return B200_OK;

@@ -87,6 +87,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                                                                         const __half* __restrict__ X16, int T,
                                                                         float* __restrict__ dst, int ldd, size_t split_stride,
                                                                         int* __restrict__ err_flag) {
+    pdl_trigger();  // the next kernel's blocks may be placed as ours retire; they wait for our completion before they touch data
     extern __shared__ __align__(1024) uint8_t umma_smem[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], raw_full, raw_empty;
     __shared__ unsigned tmem_base_s;
@@ -125,6 +126,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = tmem_base_s;
     volatile int* abort_v = &abort_s;
+    pdl_wait();  // barriers and tensor memory were set up while the kernel before this one drained; its outputs are complete from here
 
     if (warp < kProducerWarps) {
         // ---- producers ----
@@ -307,6 +309,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
 // core. Rows past T in the last token tile are never written: they feed accumulator rows that are never stored.
 __global__ void act_to_f16_kernel(const int8_t* __restrict__ codes, const float* __restrict__ scales, int K,
                                   __half* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.y, nG = K >> 5;
     const int k8 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (k8 >= K) return;
@@ -327,6 +331,8 @@ __global__ void act_to_f16_kernel(const int8_t* __restrict__ codes, const float*
 // dst[t][n] = sum over splits, in split order
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, size_t split_stride, int splits, int T, int N,
                                      float* __restrict__ dst, int ldd) {
+    pdl_trigger();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)T * N) return;
     const int t = (int)(i / N), n = (int)(i % N);
@@ -402,7 +408,7 @@ int launch_q4k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ a
     float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + ((x_bytes + 255) & ~(size_t)255));
     {
         dim3 grid(ceil_div(K / 8, 256), T);
-        act_to_f16_kernel<<<grid, 256, 0, ctx->stream>>>(aq.codes, aq.scales, K, x16);
+        launch_pdl(act_to_f16_kernel, grid, dim3(256), 0, ctx->stream, aq.codes, aq.scales, K, x16);
         LAUNCH_CHECK(ctx);
     }
     // A ring + B ring (sized for NT = 2) + one raw super-block per producer thread + round-up room
@@ -421,15 +427,15 @@ int launch_q4k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ a
     const size_t stride = splits > 1 ? (size_t)T * N : 0;
     {
         ProfScope ps(ctx, PROF_Q4K_GEMM);
-        if (NT == 2) q4k_umma_gemm_kernel<2><<<grid, kUmmaThreads, smem, ctx->stream>>>(*wmap, N, nSB, x16, T, out, out_ld, stride, err_flag);
-        else q4k_umma_gemm_kernel<1><<<grid, kUmmaThreads, smem, ctx->stream>>>(*wmap, N, nSB, x16, T, out, out_ld, stride, err_flag);
+        if (NT == 2) launch_pdl(q4k_umma_gemm_kernel<2>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag);
+        else launch_pdl(q4k_umma_gemm_kernel<1>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag);
     }
     LAUNCH_CHECK(ctx);
     if (splits > 1) {
         if (ctx->defer_reduce && ldd == N) {  // the consumer adds the partials (same order, same bits)
             ctx->pending = Parts{part, stride, splits, dst, T, N};
         } else {
-            splitk_reduce_kernel<<<(unsigned)(((size_t)T * N + 255) / 256), 256, 0, ctx->stream>>>(part, stride, splits, T, N, dst, ldd);
+            launch_pdl(splitk_reduce_kernel, dim3((unsigned)(((size_t)T * N + 255) / 256)), dim3(256), 0, ctx->stream, part, stride, splits, T, N, dst, ldd);
             LAUNCH_CHECK(ctx);
         }
     }

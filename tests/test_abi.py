@@ -43,3 +43,25 @@ def test_open_without_a_gpu_fails_loudly(lib):
     from goinfer_b200.resident import Resident, ResidentError
     with pytest.raises(ResidentError):
         Resident(abi.ModelCfg())
+
+
+def test_every_programmatically_launched_kernel_waits():
+    """A kernel that goes through launch_pdl may start before the kernel ahead of it has finished, so its body must
+    call pdl_wait() (before its first dependent access; this checks that the call is there at all) and pdl_trigger()."""
+    import glob
+    import os
+    import re
+    src = {}
+    for path in glob.glob(os.path.join(os.path.dirname(__file__), "..", "goinfer_b200", "csrc", "*.cu")):
+        src[path] = open(path).read()
+    names = set()
+    for text in src.values():
+        names |= set(re.findall(r"launch_pdl\(\s*([A-Za-z_0-9]+)", text))
+    assert len(names) >= 10
+    all_text = "\n".join(src.values())
+    for name in sorted(names):
+        m = re.search(r"__global__[^;{]*?\b" + name + r"\s*\(", all_text)
+        assert m, name
+        end = all_text.find("__global__", m.end())
+        body = all_text[m.end():end if end > 0 else len(all_text)]
+        assert "pdl_wait()" in body and "pdl_trigger()" in body, name
