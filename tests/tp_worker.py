@@ -54,8 +54,17 @@ def main():
                     b = res.StepBatch([BatchSeq(i, len(prompts[i]) + step, None, ids[step - 1][i] if step else first[i], BatchDraw(Greedy=True)) for i in range(2)])
                     wid.append([o.ID for o in b])
                 for x, y in zip(outs[:2], want):
-                    ok, err = close_logits(x, y)
-                    assert ok, (klass, err)
+                    if klass == abi.CLASS_EXACT:
+                        ok, err = close_logits(x, y)
+                        assert ok, (klass, err)
+                    else:
+                        # fast class: fp16 tensor-core products summed in another split of K on every rank count; held to the
+                        # bars the reference holds its GPU backends to against its CPU path (decoder/selftest_gpu.go:30-35)
+                        # and to a few hundredths on logits of order one
+                        a, b = np.asarray(x, np.float64), np.asarray(y, np.float64)
+                        cos = float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
+                        rel = float(np.linalg.norm(a - b) / np.linalg.norm(b))
+                        assert cos >= 0.9995 and rel <= 0.03 and np.abs(a - b).max() <= 0.05, (klass, cos, rel, np.abs(a - b).max())
                 agree = sum(a == b for sa, sb in zip(ids, wid) for a, b in zip(sa, sb))
                 assert agree >= 11, (klass, ids, wid)     # fed the same tokens, the greedy ids agree (a near-tie may flip one)
             full.Close()
