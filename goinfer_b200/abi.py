@@ -63,6 +63,6 @@ EXPORTS = (
     "b200_decode_loop_device", "b200_stats", "b200_profile", "b200_profile_read", "b200_debug_read_hidden", "b200_op_quant_g32", "b200_op_q4k_dequant",
     "b200_op_q4k_matmul", "b200_op_q4k_quantize", "b200_op_rmsnorm", "b200_op_route", "b200_op_draw",
     "b200_tp_unique_id", "b200_tp_init", "b200_tp_destroy",
-    "b200_copy_kv", "b200_op_philox", "b200_op_topk", "b200_forward_topk", "b200_op_attention", "b200_op_prefill_attention", "b200_op_f16_matmul", "b200_bench_f16_matmul", "b200_bench_q4k_matmul", "b200_bench_read", "b200_bench_kq_matmul", "b200_op_kq_matmul", "b200_bench_attention",
+    "b200_copy_kv", "b200_op_philox", "b200_op_topk", "b200_forward_topk", "b200_op_attention", "b200_op_prefill_attention", "b200_op_f16_matmul", "b200_bench_f16_matmul", "b200_bench_q4k_matmul", "b200_bench_read", "b200_bench_kq_matmul", "b200_op_kq_matmul", "b200_op_gate_up_swiglu", "b200_bench_attention",
     "b200_bench_prefill_attention", "b200_attention_noalloc",
 )

@@ -167,7 +167,8 @@ int launch_add_rmsnorm_quant(b200_ctx*, float* h, const float* delta, const floa
                              float* normed, ActQ aq, const int32_t* gather_rows);
 int launch_quant_g32(b200_ctx*, const float* x, int T, int K, ActQ aq);
 // f64_silu: the reference's f64 silu (decoder/rmsnorm.go:204-207); false in the fast class (f32 expf, about 2e-7 relative)
-int launch_swiglu_quant(b200_ctx*, const float* gate_up, int T, int F, int ld, float* mid_f32, ActQ aq, bool f64_silu = true);
+int launch_swiglu_quant(b200_ctx*, const float* gate_up, int T, int F, int ld, float* mid_f32, ActQ aq, bool f64_silu = true,
+                        bool interleaved128 = false);  // interleaved128: gate f at (f/128)*256 + f%128, up 128 further
 int launch_add(b200_ctx*, float* h, const float* delta, size_t n);
 // q (in place, f32), k,v -> paged fp16 store; optional per-head RMSNorm, NeoX RoPE with f64 cos/sin.
 int launch_qknorm_rope_kvstore(b200_ctx*, float* qkv, int ld, int T, int nH, int nKV, int hd, int rot_half,
@@ -191,6 +192,9 @@ int launch_q4k_matmul_grouped(b200_ctx*, const uint8_t* const* Wptrs, int n_expe
 size_t q4k_umma_scratch_bytes(int max_rows, int max_k, int max_n);
 int launch_q4k_matmul_umma(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
                            size_t scratch_bytes, int* err_flag);
+int launch_q4k_matmul_umma_swiglu(b200_ctx*, const uint8_t* W_interleaved, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
+                                  size_t scratch_bytes, int* err_flag, ActQ swiglu_out, bool force, bool* fused);
+int launch_interleave_rows128(b200_ctx*, const uint8_t* gate, const uint8_t* up, int F, size_t row_bytes, uint8_t* out);  // tile t: gate rows 128t.., up rows 128t..
 int launch_f16w_matmul(b200_ctx*, const __half* W, int N, int K, const float* x, int T, float* dst, int ldd,
                        __half* split_scratch, int klass);
 // gemm_f16_umma.cu: the tcgen05 kernel behind it (fast class, dense row counts)

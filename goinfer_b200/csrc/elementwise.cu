@@ -282,12 +282,13 @@ __device__ __forceinline__ float silu_f32(float x) { return __fdiv_rn(x, __fadd_
 template <bool F64>
 __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float* __restrict__ gate_up, int F, int ld,
                                                            float* __restrict__ mid, int8_t* __restrict__ codes,
-                                                           float* __restrict__ scales) {
+                                                           float* __restrict__ scales, int il) {
     const int r = blockIdx.y, lane = threadIdx.x & 31, nG = F >> 5;
     const int g = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (g >= nG) return;
     const int f = g * 32 + lane;
-    const float gt = gate_up[(size_t)r * ld + f], up = gate_up[(size_t)r * ld + F + f];
+    const size_t gi = il ? (size_t)(f >> 7) * 256 + (f & 127) : (size_t)f;  // il: gate|up interleaved by 128 columns
+    const float gt = gate_up[(size_t)r * ld + gi], up = gate_up[(size_t)r * ld + gi + (il ? 128 : F)];
     float y = __fmul_rn(F64 ? silu_f64(gt) : silu_f32(gt), up);
     if (mid) mid[(size_t)r * F + f] = y;
     if (codes) quant_group_warp(y, codes + (size_t)r * F + g * 32, scales + (size_t)r * 2 * nG + g, scales + (size_t)r * 2 * nG + nG + g, lane);
@@ -296,7 +297,7 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float* __restri
 // The same with eight consecutive values per thread (vector loads, a group is four lanes). F a multiple of 32.
 template <bool F64>
 __global__ void __launch_bounds__(256) swiglu_quant_vec_kernel(const float* __restrict__ gate_up, int F, int ld, float* __restrict__ mid,
-                                                               int8_t* __restrict__ codes, float* __restrict__ scales) {
+                                                               int8_t* __restrict__ codes, float* __restrict__ scales, int il) {
     pdl_trigger();
     pdl_wait();
     const int r = blockIdx.y, nG = F >> 5, nC = F >> 3;
@@ -305,9 +306,10 @@ __global__ void __launch_bounds__(256) swiglu_quant_vec_kernel(const float* __re
     const bool live = c < nC;
     float y[8];
     if (live) {
-        const float* gp = gate_up + (size_t)r * ld + 8 * c;
+        const int f = 8 * c, up_off = il ? 128 : F;
+        const float* gp = gate_up + (size_t)r * ld + (il ? (size_t)(f >> 7) * 256 + (f & 127) : (size_t)f);
         const float4 g0 = *reinterpret_cast<const float4*>(gp), g1 = *reinterpret_cast<const float4*>(gp + 4);
-        const float4 u0 = *reinterpret_cast<const float4*>(gp + F), u1 = *reinterpret_cast<const float4*>(gp + F + 4);
+        const float4 u0 = *reinterpret_cast<const float4*>(gp + up_off), u1 = *reinterpret_cast<const float4*>(gp + up_off + 4);
         const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
         for (int u = 0; u < 8; u++) y[u] = __fmul_rn(F64 ? silu_f64(gv[u]) : silu_f32(gv[u]), uv[u]);
@@ -493,6 +495,16 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvstore_vec_kernel(
     }
 }
 
+// out row 256t + j = gate row 128t + j, out row 256t + 128 + j = up row 128t + j (rows of row_bytes bytes, a multiple of 16)
+__global__ void interleave_rows128_kernel(const uint8_t* __restrict__ gate, const uint8_t* __restrict__ up, size_t row_bytes,
+                                          uint8_t* __restrict__ out) {
+    const int o = blockIdx.x, t = o >> 8, j = o & 255;
+    const uint8_t* src = (j < 128 ? gate : up) + (size_t)(128 * t + (j & 127)) * row_bytes;
+    uint4* d = reinterpret_cast<uint4*>(out + (size_t)o * row_bytes);
+    const uint4* s = reinterpret_cast<const uint4*>(src);
+    for (size_t i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) d[i] = s[i];
+}
+
 // eo rows are in expert-sorted slot order; slot_of[row*k + rank] names the slot (-1: empty rank).
 __global__ void fold_experts_kernel(const float* __restrict__ eo, const float* __restrict__ wts,
                                     const int32_t* __restrict__ slot_of, int k, int H, float* __restrict__ out) {
@@ -549,25 +561,34 @@ int launch_quant_g32(b200_ctx* ctx, const float* x, int T, int K, ActQ aq) {
     return B200_OK;
 }
 
-int launch_swiglu_quant(b200_ctx* ctx, const float* gate_up, int T, int F, int ld, float* mid, ActQ aq, bool f64_silu) {
+int launch_swiglu_quant(b200_ctx* ctx, const float* gate_up, int T, int F, int ld, float* mid, ActQ aq, bool f64_silu, bool interleaved128) {
     ProfScope ps(ctx, PROF_SWIGLU);
+    const int il = interleaved128 ? 1 : 0;
+    if (il && (!aq.codes || F % 128)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "interleaved gate|up needs a quantized output and F %% 128 == 0");
     if (aq.codes) {
         if (F % 32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "F must be a multiple of 32");
         const bool vec = !((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(mid) | (uintptr_t)((size_t)ld * 4)) & 15) &&
                          !(reinterpret_cast<uintptr_t>(aq.codes) & 7);
         if (vec) {
             dim3 grid(ceil_div(F / 8, 256), T);
-            if (f64_silu) launch_pdl(swiglu_quant_vec_kernel<true>, grid, dim3(256), 0, ctx->stream, gate_up, F, ld, mid, aq.codes, aq.scales);
-            else launch_pdl(swiglu_quant_vec_kernel<false>, grid, dim3(256), 0, ctx->stream, gate_up, F, ld, mid, aq.codes, aq.scales);
+            if (f64_silu) launch_pdl(swiglu_quant_vec_kernel<true>, grid, dim3(256), 0, ctx->stream, gate_up, F, ld, mid, aq.codes, aq.scales, il);
+            else launch_pdl(swiglu_quant_vec_kernel<false>, grid, dim3(256), 0, ctx->stream, gate_up, F, ld, mid, aq.codes, aq.scales, il);
         } else {
             dim3 grid(ceil_div(F / 32, 8), T);
-            if (f64_silu) swiglu_quant_kernel<true><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales);
-            else swiglu_quant_kernel<false><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales);
+            if (f64_silu) swiglu_quant_kernel<true><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales, il);
+            else swiglu_quant_kernel<false><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales, il);
         }
     } else {
         dim3 grid(ceil_div(F, 256), T);
         swiglu_plain_kernel<<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid);
     }
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+int launch_interleave_rows128(b200_ctx* ctx, const uint8_t* gate, const uint8_t* up, int F, size_t row_bytes, uint8_t* out) {
+    if (F % 128 || row_bytes % 16) B200_FAIL(ctx, B200_BAD_ARGUMENT, "row interleave needs F %% 128 == 0 and 16-byte rows");
+    interleave_rows128_kernel<<<2 * F, 128, 0, ctx->stream>>>(gate, up, row_bytes, out);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }

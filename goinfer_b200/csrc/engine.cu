@@ -48,6 +48,7 @@ struct LayerW {
     DevMat wq, wk, wv, wo, gate, up, down, router;
     std::vector<DevMat> eg, eu, ed;
     DevMat qkv, gu;                         // fused at finalize
+    bool gu_il = false;                     // gu's rows are gate|up interleaved by 128 (fast class, Q4_K): tile t = gate rows 128t.. then up rows 128t..
     std::vector<DevMat> egu;                // per expert gate|up
     const uint8_t** d_egu_ptrs = nullptr;   // device arrays of expert matrix pointers
     uint8_t *egu_all = nullptr, *ed_all = nullptr;  // Q4_K experts stacked: [n_experts][2F][.] and [n_experts][H][.]
@@ -540,8 +541,20 @@ int run_layers(b200_model* m, int T, int max_keys) {
             const bool g_q = is_kquant(L.gu.kind), d_q = is_kquant(L.down.kind);
             ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, m->att, L.ffn_norm, T, H, c.rms_eps, g_q ? nullptr : m->normed,
                                             g_q ? m->aq_h : none, nullptr));
-            ST_TRY(matmul(m, L.gu, m->normed, m->aq_h, T, m->gu, 2 * c.ffn));
-            ST_TRY(launch_swiglu_quant(ctx, m->gu, T, c.ffn, 2 * c.ffn, d_q ? nullptr : m->mid, d_q ? m->aq_mid : none, c.kernel_class == B200_CLASS_EXACT));
+            bool fused = false;
+            static const bool no_umma_env = getenv("B200_NO_UMMA") != nullptr, no_fuse_env = getenv("B200_NO_FUSED_SWIGLU") != nullptr;
+            if (L.gu_il && d_q && T >= 33 && !tap_env && !no_umma_env && ctx->umma_scratch &&
+                q4k_umma_scratch_bytes(T, H, 2 * c.ffn) <= ctx->umma_scratch_bytes) {
+                // the tcgen05 GEMM; where it runs two weight tiles per CTA without a K split its epilogue is the SwiGLU and the
+                // quantizer (the f32 gate|up matrix is never written), else the product lands in m->gu, interleaved
+                ST_TRY(launch_q4k_matmul_umma_swiglu(ctx, (const uint8_t*)L.gu.p, 2 * c.ffn, H, m->aq_h, T, m->gu, 2 * c.ffn, ctx->umma_scratch,
+                                                     ctx->umma_scratch_bytes, ctx->err_flag, no_fuse_env ? ActQ{} : m->aq_mid, false, &fused));
+            } else {
+                ST_TRY(matmul(m, L.gu, m->normed, m->aq_h, T, m->gu, 2 * c.ffn));
+            }
+            if (!fused)
+                ST_TRY(launch_swiglu_quant(ctx, m->gu, T, c.ffn, 2 * c.ffn, d_q ? nullptr : m->mid, d_q ? m->aq_mid : none,
+                                           c.kernel_class == B200_CLASS_EXACT, L.gu_il));
             ctx->defer_reduce = defer;
             ST_TRY(matmul(m, L.down, m->mid, m->aq_mid, T, m->att, H));
             ctx->defer_reduce = false;
@@ -724,7 +737,19 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
         ST_TRY(fuse_rows(m, {&L.wq, &L.wk, &L.wv}, &L.qkv));
         if (c.n_experts == 0) {
             if (!L.down.present()) B200_FAIL(ctx, B200_DECLINED, "layer %d: down projection missing", l);
-            ST_TRY(fuse_rows(m, {&L.gate, &L.up}, &L.gu));
+            if (c.kernel_class != B200_CLASS_EXACT && L.gate.present() && L.up.present() && L.gate.kind == B200_K_Q4K && L.up.kind == B200_K_Q4K &&
+                L.down.kind == B200_K_Q4K && c.ffn % 128 == 0 && L.gate.cols == L.up.cols && !getenv("B200_NO_INTERLEAVE")) {
+                // fast class: gate and up rows interleaved by 128, so that one 256-row tile of the tcgen05 GEMM holds gate and
+                // up of the same 128 columns and its epilogue can apply the SwiGLU; every other consumer reads the same order
+                L.gu.kind = B200_K_Q4K; L.gu.cols = L.gate.cols; L.gu.rows = 2 * c.ffn; L.gu.bytes = L.gate.bytes + L.up.bytes;
+                ST_TRY(m->dalloc(&L.gu.p, L.gu.bytes, &m->weight_bytes));
+                ST_TRY(launch_interleave_rows128(ctx, (const uint8_t*)L.gate.p, (const uint8_t*)L.up.p, c.ffn, (size_t)L.gate.cols / 256 * 144, (uint8_t*)L.gu.p));
+                CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+                for (DevMat* p : {&L.gate, &L.up}) { m->dfree(p->p); m->weight_bytes -= p->bytes; p->p = nullptr; }
+                L.gu_il = true;
+            } else {
+                ST_TRY(fuse_rows(m, {&L.gate, &L.up}, &L.gu));
+            }
         } else {
             if (!L.router.present()) B200_FAIL(ctx, B200_DECLINED, "layer %d: router missing", l);
             L.egu.resize(c.n_experts);

@@ -82,11 +82,19 @@ constexpr int kProducers = kProducerWarps * 32;
 constexpr int kUmmaThreads = kProducers + 96;  // 8 producer warps + the MMA-issuing, activation-loading and weight-loading warps
 constexpr int kRawRow = 144;                   // one Q4_K super-block
 
-template <int NT>  // weight tiles of 128 rows per CTA: 2 when the grid still covers the SMs, else 1
+// fast class: silu in f32, the same expression as the stand-alone SwiGLU kernel's
+__device__ __forceinline__ float umma_silu(float x) { return __fdiv_rn(x, __fadd_rn(1.f, expf(-x))); }
+
+// NT: weight tiles of 128 rows per CTA: 2 when the grid still covers the SMs, else 1.
+// SWIGLU (NT = 2, no K split): the weight rows are gate|up interleaved by 128 (tile t = gate rows 128t.. then up rows 128t..),
+// so a thread of the epilogue holds, for its token, gate and up of the same 32 columns: it writes silu(gate) * up quantized
+// per 32 (codes [T][F], scales and group sums [T][2*F/32]) and the f32 gate|up matrix never exists.
+template <int NT, bool SWIGLU>
 __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __grid_constant__ CUtensorMap wmap, int N, int nSB,
                                                                         const __half* __restrict__ X16, int T,
                                                                         float* __restrict__ dst, int ldd, size_t split_stride,
-                                                                        int* __restrict__ err_flag) {
+                                                                        int* __restrict__ err_flag, int8_t* __restrict__ sw_codes,
+                                                                        float* __restrict__ sw_scales) {
     pdl_trigger();  // the next kernel's blocks may be placed as ours retire; they wait for our completion before they touch data
     extern __shared__ __align__(1024) uint8_t umma_smem[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], raw_full, raw_empty;
@@ -260,6 +268,55 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
         const int mt = warp >> 2, lq = warp & 3;
         const int tbase = t0 + mt * 128 + lq * 32;
         uint8_t* tp = smem + warp * (32 * 144);
+        if constexpr (SWIGLU) {
+            const int F = N >> 1, nG = F >> 5, tt = tbase + lane;
+#pragma unroll 1
+            for (int cb = 0; cb < 4; cb++) {
+                unsigned rg[32], ru[32];
+                const unsigned ta = tmem_base + ((unsigned)(lq * 32) << 16) + (unsigned)(mt * 256 + cb * 32);
+#define UMMA_LD32(R, ADDR)                                                                                                          \
+    asm volatile(                                                                                                                    \
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                                    \
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n" \
+        : "=r"(R[0]), "=r"(R[1]), "=r"(R[2]), "=r"(R[3]), "=r"(R[4]), "=r"(R[5]), "=r"(R[6]), "=r"(R[7]), "=r"(R[8]), "=r"(R[9]),      \
+          "=r"(R[10]), "=r"(R[11]), "=r"(R[12]), "=r"(R[13]), "=r"(R[14]), "=r"(R[15]), "=r"(R[16]), "=r"(R[17]), "=r"(R[18]),       \
+          "=r"(R[19]), "=r"(R[20]), "=r"(R[21]), "=r"(R[22]), "=r"(R[23]), "=r"(R[24]), "=r"(R[25]), "=r"(R[26]), "=r"(R[27]),       \
+          "=r"(R[28]), "=r"(R[29]), "=r"(R[30]), "=r"(R[31])                                                                         \
+        : "r"(ADDR))
+                UMMA_LD32(rg, ta);
+                UMMA_LD32(ru, ta + 128u);
+#undef UMMA_LD32
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                const int f0 = blockIdx.x * 128 + cb * 32;  // the group's first column of the [T][F] product
+                float y[32], ma = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    y[i] = __fmul_rn(umma_silu(__uint_as_float(rg[i])), __uint_as_float(ru[i]));
+                    ma = fmaxf(ma, fabsf(y[i]));
+                }
+                // the per-32 quantizer of the step (sc = max/127, round to nearest even, clamp, group sum)
+                const float sc = __fdiv_rn(ma, 127.f);
+                const float inv = sc > 0.f ? __fdiv_rn(1.f, sc) : 0.f;
+                int sum = 0;
+                unsigned w[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) w[i] = 0u;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    int q = __float2int_rn(__fmul_rn(y[i], inv));
+                    q = max(-127, min(127, q));
+                    sum += q;
+                    w[i >> 2] |= (unsigned)(q & 0xff) << (8 * (i & 3));
+                }
+                if (tt < T && f0 < F) {
+                    uint4* o = reinterpret_cast<uint4*>(sw_codes + (size_t)tt * F + f0);
+                    o[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                    o[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    sw_scales[(size_t)tt * 2 * nG + (f0 >> 5)] = sc;
+                    sw_scales[(size_t)tt * 2 * nG + nG + (f0 >> 5)] = __fmul_rn(sc, (float)sum);
+                }
+            }
+        } else {
 #pragma unroll 1
         for (int cb = 0; cb < 4 * NT; cb++) {
             unsigned r[32];
@@ -295,6 +352,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                     }
                 }
             }
+        }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -392,15 +450,28 @@ int flush_pending_parts(b200_ctx* ctx) {
 
 int launch_q4k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
                            size_t scratch_bytes, int* err_flag) {
+    return launch_q4k_matmul_umma_swiglu(ctx, W, N, K, aq, T, dst, ldd, scratch, scratch_bytes, err_flag, ActQ{}, false, nullptr);
+}
+
+// With `sw` set and W = gate|up interleaved by 128 rows ([2F][K]): when the launch has two weight tiles per CTA and no K
+// split (or `force`), the epilogue writes silu(gate) * up quantized per 32 into `sw` and *fused = true; otherwise the
+// f32 product goes to dst as usual (its columns in the interleaved order) and *fused = false.
+int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
+                                  size_t scratch_bytes, int* err_flag, ActQ sw, bool force, bool* fused) {
+    if (fused) *fused = false;
     ST_TRY(flush_pending_parts(ctx));  // the scratch is about to be reused
     if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
     if (reinterpret_cast<uintptr_t>(W) & 15) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tcgen05 matmul wants 16-byte aligned weights");
     const int nSB = K / 256, t_tiles = ceil_div(T, 256);
     // two weight tiles per CTA halve the activation traffic; one per CTA when that is what it takes to cover the SMs
     const int max_splits = std::max(1, std::min(4, nSB / 2));
-    const int NT = ceil_div(N, 256) * t_tiles * max_splits >= ctx->sm_count * 3 / 4 ? 2 : 1;
+    int NT = ceil_div(N, 256) * t_tiles * max_splits >= ctx->sm_count * 3 / 4 ? 2 : 1;
+    if (sw.codes && force) NT = 2;
     const int n_tiles = ceil_div(N, 128 * NT);
-    const int splits = std::max(1, std::min(max_splits, ctx->sm_count / std::max(1, n_tiles * t_tiles)));
+    int splits = std::max(1, std::min(max_splits, ctx->sm_count / std::max(1, n_tiles * t_tiles)));
+    if (sw.codes && force) splits = 1;
+    const bool fuse = sw.codes && NT == 2 && splits == 1 && N % 256 == 0 && (N / 2) % 32 == 0 && !(reinterpret_cast<uintptr_t>(sw.codes) & 15);
+    if (sw.codes && !fuse && !dst) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the fused SwiGLU epilogue does not apply to this shape and no f32 output was given");
     const size_t x_bytes = (size_t)t_tiles * 256 * K * 2;
     const size_t part_bytes = splits > 1 ? (size_t)splits * T * N * 4 : 0;
     if (x_bytes + part_bytes + 256 > scratch_bytes) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tcgen05 matmul scratch too small");
@@ -415,8 +486,9 @@ int launch_q4k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ a
     constexpr int smem = kStages * 2 * kTileBytes + 2 * 2 * kTileBytes + kProducers * kRawRow + 1024;
     static bool attr_set = false;
     if (!attr_set) {
-        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_set = true;
     }
     const CUtensorMap* wmap = q4k_weight_map(ctx, W, N, nSB, 128 * NT);
@@ -427,10 +499,14 @@ int launch_q4k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ a
     const size_t stride = splits > 1 ? (size_t)T * N : 0;
     {
         ProfScope ps(ctx, PROF_Q4K_GEMM);
-        if (NT == 2) launch_pdl(q4k_umma_gemm_kernel<2>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag);
-        else launch_pdl(q4k_umma_gemm_kernel<1>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag);
+        int8_t* const no_codes = nullptr;
+        float* const no_scales = nullptr;
+        if (fuse) launch_pdl(q4k_umma_gemm_kernel<2, true>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, sw.codes, sw.scales);
+        else if (NT == 2) launch_pdl(q4k_umma_gemm_kernel<2, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales);
+        else launch_pdl(q4k_umma_gemm_kernel<1, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales);
     }
     LAUNCH_CHECK(ctx);
+    if (fuse && fused) *fused = true;
     if (splits > 1) {
         if (ctx->defer_reduce && ldd == N) {  // the consumer adds the partials (same order, same bits)
             ctx->pending = Parts{part, stride, splits, dst, T, N};

@@ -136,6 +136,37 @@ int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, i
     return us.check();
 }
 
+int b200_op_gate_up_swiglu(b200_ctx* ctx, const uint8_t* w, const float* a, int M, int K, int F, int mode, int8_t* codes_out,
+                           float* scales_out) {
+    if (K % 256 || F % 128 || M <= 0 || mode < 0 || mode > 2) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K %% 256, F %% 128, mode 0..2");
+    Tmp t;
+    const size_t rb = (size_t)K / 256 * 144, wb = (size_t)2 * F * rb;
+    uint8_t *dw, *dil; float *da, *dgu; ActQ aq, mid;
+    TMP_GET(ctx, t, dw, wb); TMP_GET(ctx, t, dil, wb); TMP_GET(ctx, t, da, (size_t)M * K); TMP_GET(ctx, t, dgu, (size_t)M * 2 * F);
+    TMP_GET(ctx, t, aq.codes, (size_t)M * K); TMP_GET(ctx, t, aq.scales, (size_t)M * 2 * (K / 32));
+    TMP_GET(ctx, t, mid.codes, (size_t)M * F); TMP_GET(ctx, t, mid.scales, (size_t)M * 2 * (F / 32));
+    H2D(ctx, dw, w, wb); H2D(ctx, da, a, (size_t)M * K * 4);
+    ST_TRY(launch_quant_g32(ctx, da, M, K, aq));
+    UmmaScratch us(ctx);
+    ST_TRY(us.ensure(t, M, K, 2 * F));
+    bool fused = false;
+    if (mode == 0) {
+        // gate rows then up rows, the tcgen05 matmul, then the stand-alone SwiGLU + quantizer
+        ST_TRY(launch_q4k_matmul(ctx, dw, 2 * F, K, aq, M, dgu, 2 * F, 2));
+        ST_TRY(launch_swiglu_quant(ctx, dgu, M, F, 2 * F, nullptr, mid, false, false));
+    } else {
+        ST_TRY(launch_interleave_rows128(ctx, dw, dw + (size_t)F * rb, F, rb, dil));
+        ST_TRY(launch_q4k_matmul_umma_swiglu(ctx, dil, 2 * F, K, aq, M, dgu, 2 * F, ctx->umma_scratch, ctx->umma_scratch_bytes, ctx->err_flag,
+                                             mode == 1 ? mid : ActQ{}, mode == 1, &fused));
+        if (mode == 1 && !fused) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the fused epilogue did not apply");
+        if (!fused) ST_TRY(launch_swiglu_quant(ctx, dgu, M, F, 2 * F, nullptr, mid, false, true));
+    }
+    D2H(ctx, codes_out, mid.codes, (size_t)M * F);
+    D2H(ctx, scales_out, mid.scales, (size_t)M * 2 * (F / 32) * 4);
+    SYNC(ctx);
+    return us.check();
+}
+
 int b200_op_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* w, const float* a, int M, int K, int N, float* dst) {
     if (K % 256 || (kind != B200_K_Q5K && kind != B200_K_Q6K)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "a Q5_K or Q6_K matrix with K %% 256 == 0");
     Tmp t;

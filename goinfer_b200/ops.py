@@ -160,6 +160,17 @@ class Ops:
                                                M, K, N, out.ctypes.data_as(C.POINTER(C.c_float))))
         return out
 
+    def gate_up_swiglu(self, raw: np.ndarray, a: np.ndarray, F: int, mode: int):
+        """-> (codes int8 [M][F], scales f32 [M][2*F/32]) of silu(gate) * up; mode 0 separate kernels, 1 fused epilogue, 2 interleaved + separate."""
+        raw = np.ascontiguousarray(raw, np.uint8)
+        a = np.ascontiguousarray(a, np.float32)
+        M, K = a.shape
+        codes = np.empty((M, F), np.int8)
+        scales = np.empty((M, 2 * (F // 32)), np.float32)
+        self._check(self.lib.b200_op_gate_up_swiglu(self.ctx, raw.ctypes.data_as(C.POINTER(C.c_uint8)), a.ctypes.data_as(C.POINTER(C.c_float)),
+                                                    M, K, F, mode, codes.ctypes.data_as(C.POINTER(C.c_int8)), scales.ctypes.data_as(C.POINTER(C.c_float))))
+        return codes, scales
+
     def bench_kq_matmul(self, kind, M, K, N, n_weight_copies=8, warmup=3, iters=20) -> float:
         ms = C.c_float(0)
         self._check(self.lib.b200_bench_kq_matmul(self.ctx, kind, M, K, N, n_weight_copies, warmup, iters, C.byref(ms)))

@@ -301,6 +301,12 @@ int b200_op_prefill_attention(b200_ctx* ctx, const float* q, const float* k, con
                               int n_heads, int n_kv_heads, int head_dim, float scale, float softcap,
                               int block_rows, float* out);
 
+/* silu(x . Wgate^T) * (x . Wup^T), quantized per 32: codes [M][F], scales then group sums [M][2*F/32]. w = Q4_K gate rows then up
+ * rows ([2F][K]). Fast class. mode 0: tcgen05 matmul, then the SwiGLU + quantizer kernel; mode 1: gate|up rows interleaved by 128 and
+ * the SwiGLU + quantizer in the matmul's epilogue; mode 2: interleaved rows, separate kernels. The three give the same bytes. */
+int b200_op_gate_up_swiglu(b200_ctx* ctx, const uint8_t* w_host, const float* x_host, int M, int K, int F, int mode,
+                           int8_t* codes_out, float* scales_out);
+
 /* dst[M][N] = x . W^T for W of kind B200_K_Q5K / B200_K_Q6K given as the file's blocks ([N][K/256][176 or 210] bytes) and f32
  * x [M][K], quantized per 32 on the device like the step does. */
 int b200_op_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* w_host, const float* x_host, int M, int K, int N, float* dst_host);

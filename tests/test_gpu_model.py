@@ -429,6 +429,32 @@ def test_q4_k_m_like_model_with_q5k_and_q6k_parts(oracle_lib, klass, tmp_path):
     g.Close()
 
 
+def test_fast_class_ffn_with_the_swiglu_in_the_gemm_epilogue(oracle_lib):
+    """A 1024-row pass over a model whose gate|up product is wide enough (28 weight tiles x 4 token tiles) for the tcgen05
+    GEMM to run two weight tiles per CTA without a K split: its epilogue then applies the SwiGLU and the quantizer, and the
+    f32 gate|up matrix is never written. The last row's logits against the oracle, within the bars the reference holds its
+    GPU backends to (decoder/selftest_gpu.go:30-35); shorter passes of the same model take the interleaved weights through
+    the other kernels."""
+    import dataclasses
+    s = dataclasses.replace(synth.SHAPES["tiny-dense"], ffn=3584)
+    mk = lambda: synth.make_cfg(s, 2, 1100, 16, 0, 1024, abi.CLASS_AUTO, 1)
+    g, o = Resident(mk()), oracle_lib.OracleResident(mk())
+    synth.load_host_weights([g, o], s, 12, 1)
+    g.finalize()
+    o.finalize()
+    rng = np.random.default_rng(4)
+    for slot, n in ((0, 1024), (1, 20)):
+        p = rng.integers(0, s.vocab, n).tolist()
+        lg, lo = g.PrefillLast(None, 0, slot, p).astype(np.float64), o.PrefillLast(None, 0, slot, p).astype(np.float64)
+        cos = float(lg @ lo / (np.linalg.norm(lg) * np.linalg.norm(lo)))
+        rel = float(np.linalg.norm(lg - lo) / np.linalg.norm(lo))
+        assert cos >= 0.9995 and rel <= 0.03, (n, cos, rel)
+        assert greedy_margin_ok(lo, int(np.argmax(lg)), int(np.argmax(lo)))
+    ok, err = close_logits(g.Forward(None, 20, 1, token=3), o.Forward(None, 20, 1, token=3))
+    assert ok, err
+    g.Close()
+
+
 def test_kv_pool_full_writes_nothing_and_bad_steps_are_refused(oracle_lib):
     g, o, s = build_pair(oracle_lib, "tiny-dense", n_slots=3, ctx_cap=64, seed=9, kv_pool_blocks=1 + 3)
     for r in (g, o):

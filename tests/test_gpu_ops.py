@@ -184,6 +184,36 @@ def test_q5k_q6k_matmul_within_the_reference_bar(ops, oracle_lib, kind):
     assert worst < 1e-5
 
 
+@pytest.mark.parametrize("M,F,K", [(40, 14208, 512), (300, 7168, 512)])
+def test_gate_up_swiglu_in_the_matmul_epilogue(ops, oracle_lib, M, F, K):
+    """silu(gate) * up quantized per 32 by the tcgen05 GEMM's own epilogue (gate|up rows interleaved by 128) gives the bytes
+    of the matmul followed by the SwiGLU + quantizer kernel, interleaved or not (shapes at which all three run two weight
+    tiles per CTA without a K split, so that every product is summed in the same order); and the values are the oracle's
+    within the fast class's bar."""
+    rng = np.random.default_rng(M)
+    raw = q4k.quantize(rng.normal(0, 0.05, (2 * F, K)).astype(np.float32))
+    a = rng.normal(0, 1, (M, K)).astype(np.float32)
+    c0, s0 = ops.gate_up_swiglu(raw, a, F, 0)
+    c1, s1 = ops.gate_up_swiglu(raw, a, F, 1)
+    c2, s2 = ops.gate_up_swiglu(raw, a, F, 2)
+    assert np.array_equal(c1, c0) and np.array_equal(s1.view(np.uint32), s0.view(np.uint32))
+    assert np.array_equal(c2, c0) and np.array_equal(s2.view(np.uint32), s0.view(np.uint32))
+    gu = oracle_lib.op_q4k_matmul_f64(raw, a, 2 * F)
+    g, u = gu[:, :F], gu[:, F:]
+    want = g / (1 + np.exp(-g)) * u
+    nG = F // 32
+    got = c1.astype(np.float64).reshape(M, nG, 32) * s1[:, :nG].astype(np.float64)[..., None]
+    err = np.linalg.norm(got.reshape(M, F) - want, axis=1) / np.linalg.norm(want, axis=1)
+    assert err.max() < 1.5e-2, err.max()    # the int8 per-32 quantizer itself is about 0.9e-2 of a row's norm here; the GEMM adds 2.5e-3
+    oc, osc = oracle_lib.op_quant_g32(want.astype(np.float32))
+    dc = np.abs(c1.astype(np.int32) - oc.astype(np.int32))
+    assert dc.max() <= 4 and (dc > 0).mean() < 0.2 and dc.mean() < 0.2, (dc.max(), (dc > 0).mean(), dc.mean())
+    np.testing.assert_allclose(s1[:, :nG], osc[:, :nG], rtol=4e-2, atol=1e-7)   # a group's largest product, fp16 operands
+    assert np.median(np.abs(s1[:, :nG] / osc[:, :nG] - 1)) < 2e-3
+    # the group sums are the scale times the integer sum of the codes
+    np.testing.assert_array_equal(s1[:, nG:], (s1[:, :nG] * c1.reshape(M, nG, 32).astype(np.int32).sum(-1).astype(np.float32)).astype(np.float32))
+
+
 def test_rmsnorm(ops, oracle_lib):
     rng = np.random.default_rng(5)
     x = rng.normal(0, 3, (5, 2048)).astype(np.float32)
