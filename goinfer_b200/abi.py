@@ -7,7 +7,7 @@ OK, DECLINED, KV_POOL_FULL, BAD_ARGUMENT, CUDA_ERROR, TIMEOUT, NCCL_ERROR = rang
 
 T_EMBED, T_FINAL_NORM, T_LM_HEAD, T_ATTN_NORM, T_WQ, T_WK, T_WV, T_WO, T_Q_NORM, T_K_NORM, T_FFN_NORM, \
     T_GATE, T_UP, T_DOWN, T_ROUTER, T_EXP_GATE, T_EXP_UP, T_EXP_DOWN = range(18)
-K_F32, K_F16, K_Q4K, K_Q5K, K_Q6K = 0, 1, 2, 3, 4
+K_F32, K_F16, K_Q4K, K_Q5K, K_Q6K, K_I8 = 0, 1, 2, 3, 4, 5
 DRAW_LOGITS, DRAW_GREEDY, DRAW_MINP, DRAW_GUMBEL = 0, 1, 2, 3
 CLASS_AUTO, CLASS_EXACT = 0, 1
 

@@ -161,7 +161,7 @@ struct KVView {
 
 // ---- launchers (each returns a B200_* status) ----
 // elementwise.cu
-int launch_embed_gather(b200_ctx*, const void* table, int kind, const int32_t* ids, int T, int H, float scale, float* h);
+int launch_embed_gather(b200_ctx*, const void* table, int kind, int n_rows, const int32_t* ids, int T, int H, float scale, float* h);
 // h += delta (delta may be null), then RMSNorm(h)*w -> normed f32 (may be null) and/or per-32 int8 (aq.codes may be null).
 int launch_add_rmsnorm_quant(b200_ctx*, float* h, const float* delta, const float* w, int T, int H, float eps,
                              float* normed, ActQ aq, const int32_t* gather_rows);

@@ -68,14 +68,21 @@ __device__ __forceinline__ void quant_group_quad(const float (&y)[8], int8_t* co
     }
 }
 
-__global__ void embed_gather_kernel(const void* __restrict__ table, int kind, const int32_t* __restrict__ ids, int H,
+__global__ void embed_gather_kernel(const void* __restrict__ table, int kind, int n_rows, const int32_t* __restrict__ ids, int H,
                                     float scale, float* __restrict__ h) {
     pdl_trigger();
     pdl_wait();
     int r = blockIdx.x;
     size_t id = (size_t)ids[r];
     float* out = h + (size_t)r * H;
-    if (kind == B200_K_F32) {
+    if (kind == B200_K_I8) {  // int8 rows, then one f32 scale per row
+        const int8_t* row = (const int8_t*)table + id * H;
+        const float ws = reinterpret_cast<const float*>((const int8_t*)table + (size_t)n_rows * H)[id];
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = __fmul_rn((float)row[i], ws);
+            out[i] = scale != 1.f ? __fmul_rn(v, scale) : v;
+        }
+    } else if (kind == B200_K_F32) {
         const float* row = (const float*)table + id * H;
         for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = scale != 1.f ? __fmul_rn(row[i], scale) : row[i];
     } else {
@@ -521,8 +528,8 @@ __global__ void fold_experts_kernel(const float* __restrict__ eo, const float* _
 
 }  // namespace
 
-int launch_embed_gather(b200_ctx* ctx, const void* table, int kind, const int32_t* ids, int T, int H, float scale, float* h) {
-    launch_pdl(embed_gather_kernel, dim3(T), dim3(256), 0, ctx->stream, table, kind, ids, H, (scale == 0.f ? 1.f : scale), h);
+int launch_embed_gather(b200_ctx* ctx, const void* table, int kind, int n_rows, const int32_t* ids, int T, int H, float scale, float* h) {
+    launch_pdl(embed_gather_kernel, dim3(T), dim3(256), 0, ctx->stream, table, kind, n_rows, ids, H, (scale == 0.f ? 1.f : scale), h);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }

@@ -33,13 +33,16 @@ struct DevMat {
 };
 
 // the kinds that multiply the per-32 int8 activations
-bool is_kquant(int kind) { return kind == B200_K_Q4K || kind == B200_K_Q5K || kind == B200_K_Q6K || kind == kKindMixed; }
+bool is_kquant(int kind) { return kind == B200_K_Q4K || kind == B200_K_Q5K || kind == B200_K_Q6K || kind == B200_K_I8 || kind == kKindMixed; }
+// the kinds multiplied by the dp4a lanes of kquant.cu (and, from 32 rows in the fast class, through an fp16 copy)
+bool is_lane_kind(int kind) { return kind == B200_K_Q5K || kind == B200_K_Q6K || kind == B200_K_I8; }
 
 size_t mat_bytes(int kind, size_t rows, size_t cols) {
     if (kind == B200_K_F32) return rows * cols * 4;
     if (kind == B200_K_F16) return rows * cols * 2;
     if (kind == B200_K_Q5K) return rows * cols / 256 * 176;
     if (kind == B200_K_Q6K) return rows * cols / 256 * 210;
+    if (kind == B200_K_I8) return rows * cols + rows * 4;
     return rows * cols / 256 * 144;
 }
 
@@ -394,12 +397,13 @@ int prep_mat(b200_model* m, int which, int layer, int expert, int kind, int rows
     int er, ec;
     if (!expected_shape(m->c, which, &er, &ec) || er != rows || ec != cols)
         B200_FAIL(ctx, B200_BAD_ARGUMENT, "tensor %d: shape [%d,%d], expected [%d,%d]", which, rows, cols, er, ec);
-    if (kind < B200_K_F32 || kind > B200_K_Q6K) B200_FAIL(ctx, B200_BAD_ARGUMENT, "unknown tensor kind %d", kind);
-    if (is_kquant(kind) && cols % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K-quants need cols %% 256 == 0");
+    if (kind < B200_K_F32 || kind > B200_K_I8) B200_FAIL(ctx, B200_BAD_ARGUMENT, "unknown tensor kind %d", kind);
+    if (is_kquant(kind) && kind != B200_K_I8 && cols % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K-quants need cols %% 256 == 0");
+    if (kind == B200_K_I8 && cols % 32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "int8 rows need cols %% 32 == 0");
     if (which == B200_T_ROUTER && kind != B200_K_F32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the router stays f32");
-    if (which == B200_T_EMBED && is_kquant(kind)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the embedding table is f32 or f16");
-    if ((kind == B200_K_Q5K || kind == B200_K_Q6K) && (expert >= 0 || m->c.tp_size > 1))
-        B200_FAIL(ctx, B200_DECLINED, "Q5_K / Q6_K tensors are taken for dense, single-GPU models");
+    if (which == B200_T_EMBED && is_kquant(kind) && kind != B200_K_I8) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the embedding table is f32, f16 or int8");
+    if (is_lane_kind(kind) && (expert >= 0 || m->c.tp_size > 1))
+        B200_FAIL(ctx, B200_DECLINED, "Q5_K / Q6_K / int8 tensors are taken for dense, single-GPU models");
     if (mat->p) { m->dfree(mat->p); m->weight_bytes -= mat->bytes; }
     mat->kind = kind; mat->rows = rows; mat->cols = cols;
     mat->bytes = mat_bytes(kind, rows, cols);
@@ -421,7 +425,7 @@ int fuse_rows(b200_model* m, std::vector<DevMat*> parts, DevMat* out) {
         bytes += p->bytes;
         rows += p->rows;
     }
-    if (!same || parts[0]->kind == B200_K_Q6K) {
+    if (!same || parts[0]->kind == B200_K_Q6K || parts[0]->kind == B200_K_I8) {
         // K-quants of different kinds (a Q4_K_M file's q|k|v or gate|up), or Q6_K parts (whose planes do not concatenate):
         // the parts stay where they are and are multiplied one after the other into their columns of the output
         if (!all_kq || parts.size() > 3) B200_FAIL(ctx, B200_DECLINED, "projection group mixing quantized and float tensors");
@@ -446,7 +450,7 @@ int fuse_rows(b200_model* m, std::vector<DevMat*> parts, DevMat* out) {
 int matmul(b200_model* m, const DevMat& W, const float* xf, ActQ xq, int T, float* dst, int ldd) {
     b200_ctx* ctx = m->ctx;
     if (W.kind == B200_K_Q4K) return launch_q4k_matmul(ctx, (const uint8_t*)W.p, W.rows, W.cols, xq, T, dst, ldd, m->c.kernel_class);
-    if (W.kind == B200_K_Q5K || W.kind == B200_K_Q6K) {
+    if (is_lane_kind(W.kind)) {
         // from 32 rows in the fast class: fp16 copy of the weights x (code * scale) activations on the tensor cores (the
         // dp4a lane re-reads the matrix for every four rows); the weights are then within 2^-11 of their values
         static const bool no_umma = getenv("B200_NO_UMMA") != nullptr;
@@ -706,7 +710,7 @@ int b200_synth_tensor(b200_model* m, int which, int layer, int expert, int kind,
     DevMat* mat;
     ST_TRY(prep_mat(m, which, layer, expert, kind, rows, cols, &mat));
     const size_t n = (size_t)rows * cols;
-    if (kind == B200_K_Q5K || kind == B200_K_Q6K) B200_FAIL(ctx, B200_BAD_ARGUMENT, "no device synthesis for Q5_K / Q6_K tensors: upload them");
+    if (is_lane_kind(kind)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "no device synthesis for Q5_K / Q6_K / int8 tensors: upload them");
     if (kind == B200_K_Q4K) return launch_synth_q4k(ctx, (uint8_t*)mat->p, n / 256, sigma, seed);
     if (kind == B200_K_F16) return launch_synth_f16(ctx, (__half*)mat->p, n, sigma, seed);
     return launch_synth_normal_f32(ctx, (float*)mat->p, n, sigma, seed);
@@ -882,9 +886,9 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
         for (int l = 0; l < c.n_layers; l++) {
             LayerW& L = m->layers[l];
             for (DevMat* d : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down, &L.qkv, &L.gu})
-                if (d->p && (d->kind == B200_K_Q5K || d->kind == B200_K_Q6K)) kq.push_back(d);
+                if (d->p && is_lane_kind(d->kind)) kq.push_back(d);
         }
-        if (m->head.p && (m->head.kind == B200_K_Q5K || m->head.kind == B200_K_Q6K)) kq.push_back(&m->head);
+        if (m->head.p && is_lane_kind(m->head.kind)) kq.push_back(&m->head);
         if (!kq.empty() && MR >= 32) {
             for (DevMat* d : kq) {
                 ST_TRY(m->dalloc((void**)&d->f16, (size_t)d->rows * d->cols * 2, &m->weight_bytes));
@@ -1246,7 +1250,7 @@ int b200_step_ragged(b200_model* m, int n_seqs, const int32_t* slot, const int32
     LAUNCH_CHECK(ctx);
     // the host counters follow what the kernel does
     for (int i = 0; i < n_seqs; i++) m->h_append(slot[i], pos[i] + n_rows[i]);
-    if (token_ids) ST_TRY(launch_embed_gather(ctx, m->embed.p, m->embed.kind, m->d_tokens, T, H, c.embed_scale, m->h));
+    if (token_ids) ST_TRY(launch_embed_gather(ctx, m->embed.p, m->embed.kind, m->embed.rows, m->d_tokens, T, H, c.embed_scale, m->h));
     // the first sequence's rows, when they are many, form the tiled prefill run (fast class only)
     m->pf_rows = 0;
     if (!m->exact_scores && n_rows[0] >= kPrefillRunMin && prefill_attention_supported(c.n_heads, c.n_kv_heads, c.head_dim, c.kv_block_rows) &&
@@ -1386,7 +1390,7 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
                                                         m->slot_mapped, m->free_stack, m->free_count, m->d_seq_row0,
                                                         m->d_row_slot, m->d_row_pos, m->status, m->refs);
         LAUNCH_CHECK(ctx);
-        ST_TRY(launch_embed_gather(ctx, m->embed.p, m->embed.kind, m->d_tokens, S, H, c.embed_scale, m->h));
+        ST_TRY(launch_embed_gather(ctx, m->embed.p, m->embed.kind, m->embed.rows, m->d_tokens, S, H, c.embed_scale, m->h));
         ST_TRY(run_layers(m, S, max_keys));
         const bool hq = is_kquant(m->head.kind);
         ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, nullptr, m->final_norm, S, H, c.rms_eps, hq ? nullptr : m->hn,

@@ -167,6 +167,48 @@ __global__ void __launch_bounds__(256) q6k_gemv_kernel(const uint8_t* __restrict
     }
 }
 
+// int8 rows with a scale per row (W8A8). Lane: 16 consecutive codes (half a group of 32) of every 32nd half-group of the row:
+// four dp4a, one f32 term with the group's activation scale; the row scale multiplies the warp's total.
+template <int TT>
+__global__ void __launch_bounds__(256) i8_gemv_kernel(const uint8_t* __restrict__ W, int N, int K, const int8_t* __restrict__ codes,
+                                                      const float* __restrict__ scales, int T, float* __restrict__ dst, int ldd) {
+    const int lane = threadIdx.x & 31, n = blockIdx.x * 8 + (threadIdx.x >> 5), t0 = blockIdx.y * TT;
+    if (n >= N) return;
+    const int nG = K >> 5, nH = K >> 4;
+    const uint4* row = reinterpret_cast<const uint4*>(W + (size_t)n * K);
+    const float ws = reinterpret_cast<const float*>(W + (size_t)N * K)[n];
+    float acc[TT];
+#pragma unroll
+    for (int t = 0; t < TT; t++) acc[t] = 0.f;
+    for (int c = lane; c < nH; c += 32) {
+        const uint4 w = row[c];
+#pragma unroll
+        for (int t = 0; t < TT; t++) {
+            if (t0 + t >= T) break;
+            const int4 a = reinterpret_cast<const int4*>(codes + (size_t)(t0 + t) * K)[c];
+            int p = kq_dp4a_ss((int)w.x, a.x, 0);
+            p = kq_dp4a_ss((int)w.y, a.y, p);
+            p = kq_dp4a_ss((int)w.z, a.z, p);
+            p = kq_dp4a_ss((int)w.w, a.w, p);
+            acc[t] = __fmaf_rn((float)p, scales[(size_t)(t0 + t) * 2 * nG + (c >> 1)], acc[t]);
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < TT; t++) {
+        float f = acc[t];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) f += __shfl_down_sync(0xffffffffu, f, off);
+        if (lane == 0 && t0 + t < T) dst[(size_t)(t0 + t) * ldd + n] = __fmul_rn(f, ws);
+    }
+}
+
+__global__ void __launch_bounds__(256) i8_to_f16_kernel(const uint8_t* __restrict__ W, int N, int K, __half* __restrict__ out) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)N * K) return;
+    const float ws = reinterpret_cast<const float*>(W + (size_t)N * K)[i / K];
+    out[i] = __float2half_rn(__fmul_rn((float)reinterpret_cast<const int8_t*>(W)[i], ws));
+}
+
 // ---- fp16 copies for the tensor-core path at dense row counts (fast class): one thread per 32 weights ----
 __global__ void __launch_bounds__(256) q5k_to_f16_kernel(const uint8_t* __restrict__ W, size_t n_blocks, __half* __restrict__ out) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (block, sub-block)
@@ -228,6 +270,18 @@ __global__ void q6k_to_planes_kernel(const uint8_t* __restrict__ raw, size_t TB,
 
 // W: Q5_K as in the file; Q6_K in planes (launch_q6k_to_planes). Any T: the rows go four at a time.
 int launch_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd) {
+    if (kind == B200_K_I8) {
+        if (K % 32 || T < 1) B200_FAIL(ctx, B200_BAD_ARGUMENT, "int8 matmul needs K %% 32 == 0 and at least one row");
+        if ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(aq.codes)) & 15) B200_FAIL(ctx, B200_BAD_ARGUMENT, "int8 matmul wants 16-byte aligned buffers");
+        ProfScope ps(ctx, PROF_HEAD_GEMM);
+        const int tt = T == 1 ? 1 : (T == 2 ? 2 : 4);
+        dim3 grid(ceil_div(N, 8), ceil_div(T, tt));
+        if (tt == 1) i8_gemv_kernel<1><<<grid, 256, 0, ctx->stream>>>(W, N, K, aq.codes, aq.scales, T, dst, ldd);
+        else if (tt == 2) i8_gemv_kernel<2><<<grid, 256, 0, ctx->stream>>>(W, N, K, aq.codes, aq.scales, T, dst, ldd);
+        else i8_gemv_kernel<4><<<grid, 256, 0, ctx->stream>>>(W, N, K, aq.codes, aq.scales, T, dst, ldd);
+        LAUNCH_CHECK(ctx);
+        return B200_OK;
+    }
     if (K % 256 || T < 1) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K-quant matmul needs K %% 256 == 0 and at least one row");
     if ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(aq.codes)) & 15) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K-quant matmul wants 16-byte aligned buffers");
     const int nSB = K / 256;
@@ -250,6 +304,11 @@ int launch_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* W, int N, int K, Ac
 }
 
 int launch_kq_to_f16(b200_ctx* ctx, int kind, const uint8_t* W, int N, int K, __half* out) {
+    if (kind == B200_K_I8) {
+        i8_to_f16_kernel<<<(unsigned)(((size_t)N * K + 255) / 256), 256, 0, ctx->stream>>>(W, N, K, out);
+        LAUNCH_CHECK(ctx);
+        return B200_OK;
+    }
     const size_t nb = (size_t)N * K / 256;
     const unsigned grid = (unsigned)((nb * 8 + 255) / 256);
     if (kind == B200_K_Q5K) q5k_to_f16_kernel<<<grid, 256, 0, ctx->stream>>>(W, nb, out);

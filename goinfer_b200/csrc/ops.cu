@@ -168,9 +168,10 @@ int b200_op_gate_up_swiglu(b200_ctx* ctx, const uint8_t* w, const float* a, int 
 }
 
 int b200_op_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* w, const float* a, int M, int K, int N, float* dst) {
-    if (K % 256 || (kind != B200_K_Q5K && kind != B200_K_Q6K)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "a Q5_K or Q6_K matrix with K %% 256 == 0");
+    if (kind == B200_K_I8 ? K % 32 != 0 : (K % 256 || (kind != B200_K_Q5K && kind != B200_K_Q6K)))
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "a Q5_K or Q6_K matrix with K %% 256 == 0, or int8 rows with K %% 32 == 0");
     Tmp t;
-    const size_t nb = (size_t)N * K / 256, wb = nb * (kind == B200_K_Q5K ? 176 : 210);
+    const size_t nb = (size_t)N * K / 256, wb = kind == B200_K_I8 ? (size_t)N * K + (size_t)N * 4 : nb * (kind == B200_K_Q5K ? 176 : 210);
     uint8_t *dw, *dp = nullptr; float *da, *dd; ActQ aq;
     TMP_GET(ctx, t, dw, wb); TMP_GET(ctx, t, da, (size_t)M * K); TMP_GET(ctx, t, dd, (size_t)M * N);
     TMP_GET(ctx, t, aq.codes, (size_t)M * K); TMP_GET(ctx, t, aq.scales, (size_t)M * 2 * (K / 32));

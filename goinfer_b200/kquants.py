@@ -117,6 +117,25 @@ def q6k_quantize(w: np.ndarray) -> np.ndarray:
     return out.reshape(-1)
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# int8 rows with one f32 scale per row (W8A8: backend/cuda/actgroup.cu:287-297,417-432); bytes: [rows][cols] int8, then rows f32
+# ---------------------------------------------------------------------------------------------------------------------
+def i8_quantize(w: np.ndarray) -> np.ndarray:
+    w = np.asarray(w, np.float32)
+    amax = np.abs(w).max(axis=1)
+    scale = (amax / 127.0).astype(np.float32)
+    inv = np.where(scale > 0, 1.0 / np.where(scale > 0, scale, 1), 0).astype(np.float32)
+    codes = np.clip(np.rint(w * inv[:, None]), -127, 127).astype(np.int8)
+    return np.concatenate([codes.reshape(-1).view(np.uint8), scale.view(np.uint8)])
+
+
+def i8_dequantize(raw: np.ndarray, rows: int, cols: int) -> np.ndarray:
+    b = np.frombuffer(raw, np.uint8)
+    codes = b[:rows * cols].view(np.int8).reshape(rows, cols).astype(np.float64)
+    scale = b[rows * cols:rows * cols + rows * 4].view(np.float32).astype(np.float64)
+    return codes * scale[:, None]
+
+
 def dequantize(kind: int, raw: np.ndarray, rows: int, cols: int) -> np.ndarray:
     """Any K-quant kind -> f64/f32 [rows, cols]."""
     from . import abi
@@ -126,4 +145,6 @@ def dequantize(kind: int, raw: np.ndarray, rows: int, cols: int) -> np.ndarray:
         return q5k_dequantize(raw, rows, cols)
     if kind == abi.K_Q6K:
         return q6k_dequantize(raw, rows, cols)
+    if kind == abi.K_I8:
+        return i8_dequantize(raw, rows, cols)
     raise ValueError(f"kind {kind} is not a K-quant")

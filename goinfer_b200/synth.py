@@ -65,6 +65,11 @@ Q4_K_M_KINDS = {abi.T_WV: abi.K_Q6K, abi.T_DOWN: abi.K_Q6K, abi.T_LM_HEAD: abi.K
 gate|up become groups of unlike kinds."""
 
 
+W8A8_KINDS = {abi.T_EMBED: abi.K_I8, abi.T_LM_HEAD: abi.K_I8, abi.T_WO: abi.K_I8}
+"""What a q4k load of the reference looks like where a tensor has no raw K-quant bytes: int8 rows with a scale per row for the
+embedding table, the head and (here) one projection."""
+
+
 def host_weights(s: Shape, seed: int, n_layers: int = 0, sigma: float = 0.02, kinds=None):
     """Yields (which, layer, expert, kind, rows, cols, array) for every tensor, built on the host.
     Matrices are N(0, sigma) f32 quantized to Q4_K (or the K-quant `kinds` names for that tensor: {which: kind}, dense
@@ -82,12 +87,16 @@ def host_weights(s: Shape, seed: int, n_layers: int = 0, sigma: float = 0.02, ki
         if kind == abi.K_Q4K:
             return which, layer, -1, kind, rows, cols, q4k.quantize(w)
         from . import kquants
-        return which, layer, -1, kind, rows, cols, (kquants.q5k_quantize(w) if kind == abi.K_Q5K else kquants.q6k_quantize(w))
+        quant = {abi.K_Q5K: kquants.q5k_quantize, abi.K_Q6K: kquants.q6k_quantize, abi.K_I8: kquants.i8_quantize}[kind]
+        return which, layer, -1, kind, rows, cols, quant(w)
 
     def norm(n):
         return (1 + rng.normal(0, 0.05, n)).astype(np.float32)
 
-    yield abi.T_EMBED, -1, -1, abi.K_F16, s.vocab, H, rng.normal(0, sigma, (s.vocab, H)).astype(np.float16)
+    if abi.T_EMBED in kinds:
+        yield mat(abi.T_EMBED, -1, s.vocab, H)
+    else:
+        yield abi.T_EMBED, -1, -1, abi.K_F16, s.vocab, H, rng.normal(0, sigma, (s.vocab, H)).astype(np.float16)
     if abi.T_LM_HEAD in kinds:
         yield mat(abi.T_LM_HEAD, -1, s.vocab, H)
     else:

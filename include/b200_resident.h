@@ -65,6 +65,11 @@ extern "C" {
                         The Q5_K / Q6_K matmuls are held to the reference's own bar for them: within 1e-5 of sum |w*a| of the
                         f64 product of the dequantized row (backend/cuda/kernels/kso1c_kernels_test.go:146-151). q|k|v and
                         gate|up may mix Q4_K, Q5_K and Q6_K parts, as Q4_K_M files do. */
+#define B200_K_I8 5  /* int8 rows with one f32 scale per row (W8A8: what the reference keeps the embedding table, the LM head
+                        and every projection without raw K-quant bytes as under q4k, decoder/weightmat.go:74-83): the upload is
+                        [rows][cols] int8 followed by rows f32 scales. dst[n] = (sum over groups of 32: aS_g * idot_g) * wScale[n]
+                        (backend/cuda/actgroup.cu:287-297,417-432); an embedding row is code * wScale[row]. Held to the reference's
+                        GEMV bar: 1e-5 of sum |w*a| against the f64 product (backend/cuda/kernels/actgroup_kernel_test.go:305-364). */
 
 /* ---- draw kinds ----------------------------------------------------------------------------------- */
 #define B200_DRAW_LOGITS 0 /* no draw: the row's logits are returned (BatchSeq.Draw == nil)          */

@@ -265,7 +265,7 @@ struct Mat {
     std::vector<float> f32;
     std::vector<uint16_t> f16;
     std::vector<uint8_t> q4k;
-    std::vector<double> deq;  // Q5_K / Q6_K rows, dequantized in f64 at upload
+    std::vector<double> deq;  // Q5_K / Q6_K rows, dequantized in f64 at upload; int8 rows: code * row scale
     bool present() const { return kind >= 0; }
 };
 
@@ -314,7 +314,7 @@ void matmul(const Mat& W, const float* a, int T, float* dst) {
         }
         return;
     }
-    if (W.kind == B200_K_Q5K || W.kind == B200_K_Q6K) {
+    if (W.kind == B200_K_Q5K || W.kind == B200_K_Q6K || W.kind == B200_K_I8) {
         // the f64 sum of w[k] * (code[k] * scale[k/32]) over the dequantized row: the reference the native Q5_K / Q6_K
         // kernels are held to, within 1e-5 of sum |w*a| (backend/cuda/kernels/kso1c_kernels_test.go:43-72,146-151)
         const int nG = K / 32;
@@ -668,6 +668,15 @@ int oracle_upload_tensor(oracle_model* m, int which, int layer, int expert, int 
             else q6k_row((const uint8_t*)host + (size_t)r * rb, cols / 256, &mat->deq[(size_t)r * cols]);
         }
     }
+    else if (kind == B200_K_I8 && bytes == n + (size_t)rows * 4) {
+        // int8 rows then one f32 scale per row (W8A8, backend/cuda/actgroup.cu:287-297,417-432): w = code * scale[row]
+        const int8_t* q = (const int8_t*)host;
+        std::vector<float> sc(rows);
+        memcpy(sc.data(), (const uint8_t*)host + n, (size_t)rows * 4);
+        mat->deq.resize(n);
+        for (int r = 0; r < rows; r++)
+            for (int k = 0; k < cols; k++) mat->deq[(size_t)r * cols + k] = (double)q[(size_t)r * cols + k] * (double)sc[r];
+    }
     else { m->err = "tensor kind/size mismatch"; mat->kind = -1; return B200_BAD_ARGUMENT; }
     return B200_OK;
 }
@@ -842,7 +851,8 @@ int oracle_step_ragged(oracle_model* m, int n_seqs, const int32_t* slot, const i
         } else {
             int id = token_ids[r];
             if (id < 0 || id >= V) { m->err = "token id out of range"; return B200_BAD_ARGUMENT; }
-            if (m->embed.kind == B200_K_F32) memcpy(hr, &m->embed.f32[(size_t)id * H], (size_t)H * 4);
+            if (m->embed.kind == B200_K_I8) for (int j = 0; j < H; j++) hr[j] = (float)m->embed.deq[(size_t)id * H + j];  // code * scale: one f32 product
+            else if (m->embed.kind == B200_K_F32) memcpy(hr, &m->embed.f32[(size_t)id * H], (size_t)H * 4);
             else for (int j = 0; j < H; j++) hr[j] = f16_to_f32(m->embed.f16[(size_t)id * H + j]);
             if (c.embed_scale != 0.f && c.embed_scale != 1.f) for (int j = 0; j < H; j++) hr[j] *= c.embed_scale;
         }
@@ -1066,6 +1076,29 @@ int oracle_op_kq_dequant(int kind, const uint8_t* w, int rows, int cols, int pla
 // dst[t][n] = sum_k w[n][k] * code[t][k] * scale[t][k/32] in f64 and bar[t][n] = sum |.|: the reference of the native
 // Q5_K / Q6_K matmul (kso1cRef). plant 4 reads every row one super-block late.
 int oracle_op_kq_matmul_f64(int kind, const uint8_t* w, const float* a, int M, int K, int N, int plant, double* dst, double* bar) {
+    if (kind == B200_K_I8) {
+        if (K % 32) return B200_BAD_ARGUMENT;
+        const int nG = K / 32;
+        const int8_t* q = (const int8_t*)w;
+        std::vector<float> ws(N);
+        memcpy(ws.data(), w + (size_t)N * K, (size_t)N * 4);
+        std::vector<int8_t> codes((size_t)M * K);
+        std::vector<float> scales((size_t)M * 2 * nG);
+        for (int t = 0; t < M; t++) quant_g32(a + (size_t)t * K, K, &codes[(size_t)t * K], &scales[(size_t)t * 2 * nG]);
+#pragma omp parallel for schedule(static)
+        for (int n = 0; n < N; n++)
+            for (int t = 0; t < M; t++) {
+                double s = 0, b = 0;
+                for (int k = 0; k < K; k++) {
+                    const double x = (double)q[(size_t)n * K + k] * (double)ws[n] * (double)codes[(size_t)t * K + k] * (double)scales[(size_t)t * 2 * nG + (k >> 5)];
+                    s += x;
+                    b += std::fabs(x);
+                }
+                dst[(size_t)t * N + n] = s;
+                if (bar) bar[(size_t)t * N + n] = b;
+            }
+        return B200_OK;
+    }
     if ((kind != B200_K_Q5K && kind != B200_K_Q6K) || K % 256) return B200_BAD_ARGUMENT;
     const int nSB = K / 256, nG = K / 32;
     const size_t bs = kq_block_bytes(kind), rb = (size_t)nSB * bs;

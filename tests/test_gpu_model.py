@@ -429,6 +429,34 @@ def test_q4_k_m_like_model_with_q5k_and_q6k_parts(oracle_lib, klass, tmp_path):
     g.Close()
 
 
+@pytest.mark.parametrize("klass", [abi.CLASS_EXACT, abi.CLASS_AUTO])
+def test_w8a8_embedding_head_and_projection(oracle_lib, klass):
+    """int8 rows with a scale per row for the embedding table, the LM head and the o projection (what a q4k load of the
+    reference keeps where a tensor has no raw K-quant bytes): prefill, decode steps and a 40-row pass against the oracle."""
+    s = synth.SHAPES["tiny-qknorm"]
+    mk = lambda: synth.make_cfg(s, 3, 96, 16, 0, 0, klass, 0)
+    g, o = Resident(mk()), oracle_lib.OracleResident(mk())
+    synth.load_host_weights([g, o], s, 15, kinds=synth.W8A8_KINDS)
+    g.finalize()
+    o.finalize()
+    rng = np.random.default_rng(5)
+    p = rng.integers(0, s.vocab, 13).tolist()
+    ok, err = close_logits(g.PrefillLast(None, 0, 0, p), o.PrefillLast(None, 0, 0, p))
+    assert ok, err
+    tok = 7
+    for step in range(4):
+        lg, lo = g.Forward(None, 13 + step, 0, token=tok), o.Forward(None, 13 + step, 0, token=tok)
+        ok, err = close_logits(lg, lo)
+        assert ok, (step, err)
+        tok = int(np.argmax(lo))
+    p40 = rng.integers(0, s.vocab, 40).tolist()
+    lg, lo = g.PrefillLast(None, 0, 1, p40).astype(np.float64), o.PrefillLast(None, 0, 1, p40).astype(np.float64)
+    cos = float(lg @ lo / (np.linalg.norm(lg) * np.linalg.norm(lo)))
+    rel = float(np.linalg.norm(lg - lo) / np.linalg.norm(lo))
+    assert cos >= 0.9995 and rel <= 0.03, (cos, rel)
+    g.Close()
+
+
 def test_fast_class_ffn_with_the_swiglu_in_the_gemm_epilogue(oracle_lib):
     """A 1024-row pass over a model whose gate|up product is wide enough (28 weight tiles x 4 token tiles) for the tcgen05
     GEMM to run two weight tiles per CTA without a K split: its epilogue then applies the SwiGLU and the quantizer, and the

@@ -184,6 +184,24 @@ def test_q5k_q6k_matmul_within_the_reference_bar(ops, oracle_lib, kind):
     assert worst < 1e-5
 
 
+def test_int8_rows_matmul_within_the_reference_bar(ops, oracle_lib):
+    """W8A8 rows (int8 codes, a scale per row) x per-32 int8 activations against the f64 product, |err| / sum|w*a| <= 1e-5
+    (the bar of the reference's GEMV tests, backend/cuda/kernels/actgroup_kernel_test.go:305-364), ragged N, 1..9 rows."""
+    from goinfer_b200 import kquants
+    rng = np.random.default_rng(77)
+    N = 8 * 3 + 5
+    for K in (32, 96, 512, 4096 + 32):
+        raw = kquants.i8_quantize(rng.normal(0, 0.05, (N, K)).astype(np.float32))
+        for M in (1, 2, 3, 4, 5, 9):
+            a = rng.normal(0, 1, (M, K)).astype(np.float32)
+            a[:, rng.integers(0, K, 2)] *= 30.0
+            got = ops.kq_matmul(abi.K_I8, raw, a, N).astype(np.float64)
+            want, bar = oracle_lib.op_kq_matmul_f64(abi.K_I8, raw, a, N)
+            e = np.abs(got - want) / (bar + 1e-30)
+            assert e.max() <= 1e-5, (K, M, e.max())
+        assert np.array_equal(ops.kq_matmul(abi.K_I8, raw, a[1:2], N)[0], ops.kq_matmul(abi.K_I8, raw, a, N)[1])
+
+
 @pytest.mark.parametrize("M,F,K", [(40, 14208, 512), (300, 7168, 512)])
 def test_gate_up_swiglu_in_the_matmul_epilogue(ops, oracle_lib, M, F, K):
     """silu(gate) * up quantized per 32 by the tcgen05 GEMM's own epilogue (gate|up rows interleaved by 128) gives the bytes

@@ -110,6 +110,29 @@ def test_oracle_model_with_mixed_kinds_runs_and_differs_from_q4k_only(oracle_lib
     assert np.corrcoef(la, lb)[0, 1] > 0.9
 
 
+def test_int8_rows_oracle_and_model(oracle_lib):
+    """W8A8: the oracle's product is the f64 sum of code_w * scale_row * code_a * scale_group; a model with an int8 embedding
+    table, head and o projection runs and gathers code * scale rows."""
+    rng = np.random.default_rng(8)
+    N, K, M = 11, 96, 3
+    w = rng.normal(0, 0.05, (N, K)).astype(np.float32)
+    raw = kquants.i8_quantize(w)
+    assert raw.size == N * K + N * 4
+    back = kquants.i8_dequantize(raw, N, K)
+    assert np.abs(back - w).max() <= np.abs(w).max(axis=1).max() / 127 * 0.5001
+    a = rng.normal(0, 1, (M, K)).astype(np.float32)
+    got, bar = oracle_lib.op_kq_matmul_f64(abi.K_I8, raw, a, N)
+    codes, scales = oracle_lib.op_quant_g32(a)
+    act = codes.astype(np.float64) * np.repeat(scales[:, :K // 32].astype(np.float64), 32, axis=1)
+    np.testing.assert_allclose(got, act @ back.T, rtol=1e-12, atol=1e-14)
+    s = synth.SHAPES["tiny-dense"]
+    r = oracle_lib.OracleResident(synth.make_cfg(s, 2, 64, 16, 0, 0, abi.CLASS_EXACT, 0))
+    synth.load_host_weights([r], s, 4, kinds=synth.W8A8_KINDS)
+    r.finalize()
+    lg = r.PrefillLast(None, 0, 0, list(range(3, 12)))
+    assert np.all(np.isfinite(lg)) and lg.std() > 0
+
+
 def _tiny_gguf(tmp_path, arch, kinds, seed=6, permute=False):
     """A GGUF file of the tiny-dense shape's host weights; -> (path, the tensors it was written from)."""
     s = synth.SHAPES["tiny-qknorm" if arch == "qwen3" else "tiny-dense"]
