@@ -82,8 +82,9 @@ constexpr int kProducers = kProducerWarps * 32;
 constexpr int kUmmaThreads = kProducers + 96;  // 8 producer warps + the MMA-issuing, activation-loading and weight-loading warps
 constexpr int kRawRow = 144;                   // one Q4_K super-block
 
-// fast class: silu in f32, the same expression as the stand-alone SwiGLU kernel's
-__device__ __forceinline__ float umma_silu(float x) { return __fdiv_rn(x, __fadd_rn(1.f, expf(-x))); }
+// fast class: silu in f32 with the hardware exponential and reciprocal (about 1e-6 relative of the f64 value), the same
+// expression as the stand-alone SwiGLU kernel's, so that the two give the same bits
+__device__ __forceinline__ float umma_silu(float x) { return __fdividef(x, __fadd_rn(1.f, __expf(-x))); }
 
 // NT: weight tiles of 128 rows per CTA: 2 when the grid still covers the SMs, else 1.
 // SWIGLU (NT = 2, no K split): the weight rows are gate|up interleaved by 128 (tile t = gate rows 128t.. then up rows 128t..),

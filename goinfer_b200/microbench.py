@@ -4,6 +4,7 @@
   python -m goinfer_b200.microbench q4k --rows 1 2 4 8 16 32 256 [--n 12288 --k 4096]
   python -m goinfer_b200.microbench f16 --rows 256 [--n 151936 --k 4096]
   python -m goinfer_b200.microbench prefill --rows 2048 [--pos0 0 --heads 32 --kv-heads 8 --head-dim 128]
+  python -m goinfer_b200.microbench gateup --rows 256 [--f 12288 --k 4096 --mode 1]   (one call through host buffers: for profilers)
 
 Times are CUDA-event averages per launch after warm-up. Weight matrices are cycled through several copies and KV pools
 are far larger than the 126 MB L2, so no launch finds its inputs cached.
@@ -49,6 +50,11 @@ def main():
     g.add_argument("--iters", type=int, default=20)
     g.add_argument("--warmup", type=int, default=3)
     g.add_argument("--kind", choices=["q4k", "q5k", "q6k"], default="q4k", help="q5k / q6k: the native K-quant lanes")
+    u = sub.add_parser("gateup")
+    u.add_argument("--rows", type=int, default=256)
+    u.add_argument("--f", type=int, default=12288)
+    u.add_argument("--k", type=int, default=4096)
+    u.add_argument("--mode", type=int, default=1, help="0 matmul + SwiGLU kernel, 1 SwiGLU in the matmul's epilogue, 2 interleaved rows + SwiGLU kernel")
     args = ap.parse_args()
     from .ops import Ops
     ops = Ops(0)
@@ -63,6 +69,19 @@ def main():
             wb = args.n * args.k * 2
             print(json.dumps({"kernel": "f16-weight matmul", "rows": m, "n": args.n, "k": args.k, "ms_per_launch": ms,
                               "weight_GBps": wb / ms / 1e6, "TMACps": m * args.n * args.k / ms / 1e9}))
+    elif args.what == "gateup":
+        import time
+        import numpy as np
+        rng = np.random.default_rng(0)
+        nb = 2 * args.f * args.k // 256
+        raw = rng.integers(0, 256, (nb, 144), dtype=np.uint8)
+        raw[:, 0:2] = rng.uniform(0.001, 0.01, nb).astype(np.float16).view(np.uint8).reshape(nb, 2)   # d
+        raw[:, 2:4] = rng.uniform(0.001, 0.01, nb).astype(np.float16).view(np.uint8).reshape(nb, 2)   # dmin
+        a = rng.normal(0, 1, (args.rows, args.k)).astype(np.float32)
+        t = time.perf_counter()
+        codes, scales = ops.gate_up_swiglu(raw.reshape(-1), a, args.f, args.mode)
+        print(json.dumps({"kernel": "gate|up matmul + SwiGLU + quantizer", "mode": args.mode, "rows": args.rows, "f": args.f, "k": args.k,
+                          "wall_ms_with_copies": (time.perf_counter() - t) * 1e3, "codes_checksum": int(codes.astype(np.int64).sum())}))
     elif args.what == "prefill":
         ms = ops.bench_prefill_attention(args.rows, args.pos0, args.heads, args.kv_heads, args.head_dim, args.block_rows,
                                          args.warmup, args.iters)
