@@ -44,6 +44,13 @@ struct b200_ctx {
     // itself: the matmul then skips its reduce kernel and leaves `pending`; the consumer that is handed pending.dst takes it
     bool defer_reduce = false;
     Parts pending;
+    // fp16 activation tiles made by the kernel that quantized the activations (instead of a conversion kernel ahead of the
+    // tcgen05 matmul): when x16_slot_bytes is set the scratch starts with two slots of that size (a matmul reads one while
+    // its epilogue or the next producer fills the other) and the K-split partials follow them. x16_ready is set by the
+    // caller around the one matmul whose activations a producer has just laid out, and is null otherwise.
+    size_t x16_slot_bytes = 0;
+    int x16_toggle = 0;
+    const __half* x16_ready = nullptr;
     // tensor parallel: the NCCL communicator b200_tp_init made for this context (null on a single GPU)
     void* tp_comm = nullptr;
     int tp_rank = 0, tp_size = 1;
@@ -127,6 +134,22 @@ inline bool pdl_enabled() {
     return on;
 }
 
+// Eight consecutive activations (k8 a multiple of 8) of row t as the tcgen05 matmul's fp16 tiles hold them: the matrix is
+// stored [token tile of 256][chunk of 64 along K][256 rows][64], the 16-byte chunk c of a row at position c ^ (t & 7) (the
+// 128-byte swizzle), positions 1 and 2 of every group of four swapped (the order nibble pairs leave a code word in).
+// v[i] = code * scale, rounded to fp16 here.
+__device__ __forceinline__ void x16_store8(__half* __restrict__ out, int K, int t, int k8, const float (&v)[8]) {
+    uint4 o;
+    __half2 h;
+    h = __floats2half2_rn(v[0], v[2]); o.x = *reinterpret_cast<unsigned*>(&h);
+    h = __floats2half2_rn(v[1], v[3]); o.y = *reinterpret_cast<unsigned*>(&h);
+    h = __floats2half2_rn(v[4], v[6]); o.z = *reinterpret_cast<unsigned*>(&h);
+    h = __floats2half2_rn(v[5], v[7]); o.w = *reinterpret_cast<unsigned*>(&h);
+    const int seg = k8 >> 6, chunk = (k8 >> 3) & 7;
+    const size_t tile = ((size_t)(t >> 8) * (size_t)(K >> 6) + seg) * (256 * 64);
+    *reinterpret_cast<uint4*>(out + tile + (size_t)(t & 255) * 64 + ((chunk ^ (t & 7)) << 3)) = o;
+}
+
 template <typename... KArgs, typename... Args>
 inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
@@ -164,11 +187,11 @@ struct KVView {
 int launch_embed_gather(b200_ctx*, const void* table, int kind, int n_rows, const int32_t* ids, int T, int H, float scale, float* h);
 // h += delta (delta may be null), then RMSNorm(h)*w -> normed f32 (may be null) and/or per-32 int8 (aq.codes may be null).
 int launch_add_rmsnorm_quant(b200_ctx*, float* h, const float* delta, const float* w, int T, int H, float eps,
-                             float* normed, ActQ aq, const int32_t* gather_rows);
+                             float* normed, ActQ aq, const int32_t* gather_rows, __half* x16 = nullptr);
 int launch_quant_g32(b200_ctx*, const float* x, int T, int K, ActQ aq);
 // f64_silu: the reference's f64 silu (decoder/rmsnorm.go:204-207); false in the fast class (f32 expf, about 2e-7 relative)
 int launch_swiglu_quant(b200_ctx*, const float* gate_up, int T, int F, int ld, float* mid_f32, ActQ aq, bool f64_silu = true,
-                        bool interleaved128 = false);  // interleaved128: gate f at (f/128)*256 + f%128, up 128 further
+                        bool interleaved128 = false, __half* x16 = nullptr);  // x16: also lay the fp16 tiles out (x16_store8)  // interleaved128: gate f at (f/128)*256 + f%128, up 128 further
 int launch_add(b200_ctx*, float* h, const float* delta, size_t n);
 // q (in place, f32), k,v -> paged fp16 store; optional per-head RMSNorm, NeoX RoPE with f64 cos/sin.
 int launch_qknorm_rope_kvstore(b200_ctx*, float* qkv, int ld, int T, int nH, int nKV, int hd, int rot_half,
@@ -193,7 +216,8 @@ size_t q4k_umma_scratch_bytes(int max_rows, int max_k, int max_n);
 int launch_q4k_matmul_umma(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
                            size_t scratch_bytes, int* err_flag);
 int launch_q4k_matmul_umma_swiglu(b200_ctx*, const uint8_t* W_interleaved, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
-                                  size_t scratch_bytes, int* err_flag, ActQ swiglu_out, bool force, bool* fused);
+                                  size_t scratch_bytes, int* err_flag, ActQ swiglu_out, bool force, bool* fused, __half* swiglu_x16 = nullptr);
+__half* x16_next_slot(b200_ctx*);  // the scratch's other fp16 activation slot (null when the scratch has none)
 int launch_interleave_rows128(b200_ctx*, const uint8_t* gate, const uint8_t* up, int F, size_t row_bytes, uint8_t* out);  // tile t: gate rows 128t.., up rows 128t..
 int launch_f16w_matmul(b200_ctx*, const __half* W, int N, int K, const float* x, int T, float* dst, int ldd,
                        __half* split_scratch, int klass);

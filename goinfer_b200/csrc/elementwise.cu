@@ -40,7 +40,8 @@ __device__ __forceinline__ void quant_group_warp(float y, int8_t* codes_g, float
 // The same quantizer for a group held 8 values per lane by four consecutive lanes (q4 = lane & 3 is the lane's place in
 // its group). The maximum and the integer sum do not depend on the order they are taken in, so the codes, scale and sum
 // are those of quant_group_warp. Every lane of the warp must call it (lanes past the row pass zeros and `live` false).
-__device__ __forceinline__ void quant_group_quad(const float (&y)[8], int8_t* codes_g, float* sc_out, float* asum_out, int q4, bool live) {
+__device__ __forceinline__ void quant_group_quad(const float (&y)[8], int8_t* codes_g, float* sc_out, float* asum_out, int q4, bool live,
+                                                 float* deq = nullptr /* [8]: code * scale */) {
     float ma = 0.f;
 #pragma unroll
     for (int u = 0; u < 8; u++) ma = fmaxf(ma, fabsf(y[u]));
@@ -56,6 +57,7 @@ __device__ __forceinline__ void quant_group_quad(const float (&y)[8], int8_t* co
         q = max(-127, min(127, q));
         sum += q;
         w[u >> 2] |= (unsigned)(q & 0xff) << (8 * (u & 3));
+        if (deq) deq[u] = __fmul_rn((float)q, sc);
     }
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
@@ -177,7 +179,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_quant_vec_kernel(float* __res
                                                                     const float* __restrict__ w, int H, float eps,
                                                                     float* __restrict__ normed, int8_t* __restrict__ codes,
                                                                     float* __restrict__ scales, const int32_t* __restrict__ gather_rows,
-                                                                    int n_parts, size_t part_stride) {
+                                                                    int n_parts, size_t part_stride, __half* __restrict__ x16) {
     pdl_trigger();
     pdl_wait();
     __shared__ double red[8];
@@ -263,7 +265,10 @@ __global__ void __launch_bounds__(256) add_rmsnorm_quant_vec_kernel(float* __res
         }
         if (codes) {
             const int g = c >> 2;
-            quant_group_quad(y, codes + (size_t)j * H + (size_t)g * 32, scales + (size_t)j * 2 * nG + g, scales + (size_t)j * 2 * nG + nG + g, q4, live);
+            float dq[8];
+            quant_group_quad(y, codes + (size_t)j * H + (size_t)g * 32, scales + (size_t)j * 2 * nG + g, scales + (size_t)j * 2 * nG + nG + g, q4, live,
+                             x16 ? dq : nullptr);
+            if (x16 && live) x16_store8(x16, H, j, 8 * c, dq);
         }
     }
 }
@@ -305,7 +310,8 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float* __restri
 // The same with eight consecutive values per thread (vector loads, a group is four lanes). F a multiple of 32.
 template <bool F64>
 __global__ void __launch_bounds__(256) swiglu_quant_vec_kernel(const float* __restrict__ gate_up, int F, int ld, float* __restrict__ mid,
-                                                               int8_t* __restrict__ codes, float* __restrict__ scales, int il) {
+                                                               int8_t* __restrict__ codes, float* __restrict__ scales, int il,
+                                                               __half* __restrict__ x16) {
     pdl_trigger();
     pdl_wait();
     const int r = blockIdx.y, nG = F >> 5, nC = F >> 3;
@@ -330,8 +336,10 @@ __global__ void __launch_bounds__(256) swiglu_quant_vec_kernel(const float* __re
         for (int u = 0; u < 8; u++) y[u] = 0.f;
     }
     const int g = c >> 2;
+    float dq[8];
     quant_group_quad(y, codes + (size_t)r * F + (size_t)g * 32, scales + (size_t)r * 2 * nG + g, scales + (size_t)r * 2 * nG + nG + g,
-                     threadIdx.x & 3, live);
+                     threadIdx.x & 3, live, x16 ? dq : nullptr);
+    if (x16 && live) x16_store8(x16, F, r, 8 * c, dq);
 }
 
 // plain SwiGLU for widths that are not a multiple of 32 (f32-weight models)
@@ -536,7 +544,7 @@ int launch_embed_gather(b200_ctx* ctx, const void* table, int kind, int n_rows, 
 }
 
 int launch_add_rmsnorm_quant(b200_ctx* ctx, float* h, const float* delta, const float* w, int T, int H, float eps,
-                             float* normed, ActQ aq, const int32_t* gather_rows) {
+                             float* normed, ActQ aq, const int32_t* gather_rows, __half* x16) {
     if (aq.codes && (H % 32)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "quantized rows need a width that is a multiple of 32");
     size_t smem = 8 * sizeof(double) + (size_t)H * sizeof(float);
     ProfScope ps(ctx, PROF_NORM_QUANT);
@@ -550,13 +558,15 @@ int launch_add_rmsnorm_quant(b200_ctx* ctx, float* h, const float* delta, const 
                                                     reinterpret_cast<uintptr_t>(normed) | (uintptr_t)(pt.stride * 4)) & 15) &&
                      !(reinterpret_cast<uintptr_t>(aq.codes) & 7);
     if (vec && H <= 2048)
-        launch_pdl(add_rmsnorm_quant_vec_kernel<1>, dim3(T), dim3(256), 0, ctx->stream, h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
+        launch_pdl(add_rmsnorm_quant_vec_kernel<1>, dim3(T), dim3(256), 0, ctx->stream, h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride, x16);
     else if (vec && H <= 4096)
-        launch_pdl(add_rmsnorm_quant_vec_kernel<2>, dim3(T), dim3(256), 0, ctx->stream, h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
+        launch_pdl(add_rmsnorm_quant_vec_kernel<2>, dim3(T), dim3(256), 0, ctx->stream, h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride, x16);
     else if (vec)
-        launch_pdl(add_rmsnorm_quant_vec_kernel<4>, dim3(T), dim3(256), 0, ctx->stream, h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
-    else
+        launch_pdl(add_rmsnorm_quant_vec_kernel<4>, dim3(T), dim3(256), 0, ctx->stream, h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride, x16);
+    else {
+        if (x16) B200_FAIL(ctx, B200_BAD_ARGUMENT, "fp16 activation tiles are laid out by the vector kernel only (width %% 32, aligned buffers)");
         add_rmsnorm_quant_kernel<<<T, 256, smem, ctx->stream>>>(h, dl, w, H, eps, normed, aq.codes, aq.scales, gather_rows, pt.n, pt.stride);
+    }
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }
@@ -569,7 +579,8 @@ int launch_quant_g32(b200_ctx* ctx, const float* x, int T, int K, ActQ aq) {
     return B200_OK;
 }
 
-int launch_swiglu_quant(b200_ctx* ctx, const float* gate_up, int T, int F, int ld, float* mid, ActQ aq, bool f64_silu, bool interleaved128) {
+int launch_swiglu_quant(b200_ctx* ctx, const float* gate_up, int T, int F, int ld, float* mid, ActQ aq, bool f64_silu, bool interleaved128,
+                        __half* x16) {
     ProfScope ps(ctx, PROF_SWIGLU);
     const int il = interleaved128 ? 1 : 0;
     if (il && (!aq.codes || F % 128)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "interleaved gate|up needs a quantized output and F %% 128 == 0");
@@ -579,9 +590,10 @@ int launch_swiglu_quant(b200_ctx* ctx, const float* gate_up, int T, int F, int l
                          !(reinterpret_cast<uintptr_t>(aq.codes) & 7);
         if (vec) {
             dim3 grid(ceil_div(F / 8, 256), T);
-            if (f64_silu) launch_pdl(swiglu_quant_vec_kernel<true>, grid, dim3(256), 0, ctx->stream, gate_up, F, ld, mid, aq.codes, aq.scales, il);
-            else launch_pdl(swiglu_quant_vec_kernel<false>, grid, dim3(256), 0, ctx->stream, gate_up, F, ld, mid, aq.codes, aq.scales, il);
+            if (f64_silu) launch_pdl(swiglu_quant_vec_kernel<true>, grid, dim3(256), 0, ctx->stream, gate_up, F, ld, mid, aq.codes, aq.scales, il, x16);
+            else launch_pdl(swiglu_quant_vec_kernel<false>, grid, dim3(256), 0, ctx->stream, gate_up, F, ld, mid, aq.codes, aq.scales, il, x16);
         } else {
+            if (x16) B200_FAIL(ctx, B200_BAD_ARGUMENT, "fp16 activation tiles are laid out by the vector kernel only (aligned buffers)");
             dim3 grid(ceil_div(F / 32, 8), T);
             if (f64_silu) swiglu_quant_kernel<true><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales, il);
             else swiglu_quant_kernel<false><<<grid, 256, 0, ctx->stream>>>(gate_up, F, ld, mid, aq.codes, aq.scales, il);

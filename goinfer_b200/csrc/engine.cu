@@ -297,6 +297,7 @@ struct b200_model {
     AttnScratch asc;
     float* kq_act = nullptr;       // fast class with Q5_K / Q6_K tensors: code * scale activations for their fp16 matmul
     void* umma_scratch = nullptr;  // fast class: tcgen05 matmul scratch
+    size_t x16_slot_bytes = 0;     // its two fp16 activation slots (0: the scratch has none)
     size_t umma_bytes = 0;
     int* err_flag = nullptr;       // raised by a bounded device-side wait that gave up
     float* exact_scores = nullptr;  // exact class: [MR*nH][ctx_cap]
@@ -498,17 +499,31 @@ int run_layers(b200_model* m, int T, int max_keys) {
     ctx->umma_scratch = m->umma_scratch;  // this model's tcgen05 scratch and error flag serve its launches
     ctx->umma_scratch_bytes = m->umma_bytes;
     ctx->err_flag = m->err_flag;
+    ctx->x16_slot_bytes = m->x16_slot_bytes;
+    ctx->x16_ready = nullptr;
+    // A producer lays out the fp16 activation tiles of the tcgen05 matmul that follows it (no conversion kernel) when that
+    // matmul is a plain Q4_K one at a dense row count in the fast class.
+    static const bool no_x16_env = getenv("B200_NO_X16_FUSE") != nullptr || getenv("B200_NO_UMMA") != nullptr;
+    auto x16_for = [&](const DevMat& W) -> __half* {
+        if (no_x16_env || !m->x16_slot_bytes || W.kind != B200_K_Q4K || T < 33 || c.kernel_class == B200_CLASS_EXACT || (W.cols % 256) ||
+            (size_t)ceil_div(T, 256) * 256 * W.cols * 2 > m->x16_slot_bytes)
+            return nullptr;
+        return x16_next_slot(ctx);
+    };
     const float* delta = nullptr;  // pending residual add, fused into the next norm
     for (int l = 0; l < c.n_layers; l++) {
         LayerW& L = m->layers[l];
         const bool q_in = is_kquant(L.qkv.kind);
+        __half* x16 = q_in ? x16_for(L.qkv) : nullptr;
         ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, delta, L.attn_norm, T, H, c.rms_eps, q_in ? nullptr : m->normed,
-                                        q_in ? m->aq_h : none, nullptr));
+                                        q_in ? m->aq_h : none, nullptr, x16));
         // the consumers of the q|k|v, o and down products can add their K-split partials themselves (no reduce kernel)
         static const bool tap_env = getenv("B200_DEBUG_TAP") != nullptr || getenv("B200_NO_DEFER") != nullptr;
         const bool defer = c.tp_size <= 1 && !m->exact_scores && !tap_env;
         ctx->defer_reduce = defer;
+        ctx->x16_ready = x16;
         ST_TRY(matmul(m, L.qkv, m->normed, m->aq_h, T, m->qkv, ldq));
+        ctx->x16_ready = nullptr;
         ctx->defer_reduce = false;
         KVView kv{m->kpool[l], m->vpool[l], m->table, m->max_blocks, c.kv_block_rows, nKV, hd};
         ST_TRY(launch_qknorm_rope_kvstore(ctx, m->qkv, ldq, T, nH, nKV, hd, m->rot_half, L.inv_freq,
@@ -543,24 +558,30 @@ int run_layers(b200_model* m, int T, int max_keys) {
         if (c.tp_size > 1) ST_TRY(tp_all_reduce_sum(ctx, m->att, (size_t)T * H));  // o is split by input columns: partial sums
         if (c.n_experts == 0) {
             const bool g_q = is_kquant(L.gu.kind), d_q = is_kquant(L.down.kind);
+            __half* x16g = g_q ? x16_for(L.gu) : nullptr;
             ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, m->att, L.ffn_norm, T, H, c.rms_eps, g_q ? nullptr : m->normed,
-                                            g_q ? m->aq_h : none, nullptr));
+                                            g_q ? m->aq_h : none, nullptr, x16g));
+            __half* x16d = d_q ? x16_for(L.down) : nullptr;   // the other slot: laid out by whoever quantizes silu(gate) * up
             bool fused = false;
+            ctx->x16_ready = x16g;
             static const bool no_umma_env = getenv("B200_NO_UMMA") != nullptr, no_fuse_env = getenv("B200_NO_FUSED_SWIGLU") != nullptr;
             if (L.gu_il && d_q && T >= 33 && !tap_env && !no_umma_env && ctx->umma_scratch &&
                 q4k_umma_scratch_bytes(T, H, 2 * c.ffn) <= ctx->umma_scratch_bytes) {
                 // the tcgen05 GEMM; where it runs two weight tiles per CTA without a K split its epilogue is the SwiGLU and the
                 // quantizer (the f32 gate|up matrix is never written), else the product lands in m->gu, interleaved
                 ST_TRY(launch_q4k_matmul_umma_swiglu(ctx, (const uint8_t*)L.gu.p, 2 * c.ffn, H, m->aq_h, T, m->gu, 2 * c.ffn, ctx->umma_scratch,
-                                                     ctx->umma_scratch_bytes, ctx->err_flag, no_fuse_env ? ActQ{} : m->aq_mid, false, &fused));
+                                                     ctx->umma_scratch_bytes, ctx->err_flag, no_fuse_env ? ActQ{} : m->aq_mid, false, &fused, x16d));
             } else {
                 ST_TRY(matmul(m, L.gu, m->normed, m->aq_h, T, m->gu, 2 * c.ffn));
             }
+            ctx->x16_ready = nullptr;
             if (!fused)
                 ST_TRY(launch_swiglu_quant(ctx, m->gu, T, c.ffn, 2 * c.ffn, d_q ? nullptr : m->mid, d_q ? m->aq_mid : none,
-                                           c.kernel_class == B200_CLASS_EXACT, L.gu_il));
+                                           c.kernel_class == B200_CLASS_EXACT, L.gu_il, x16d));
             ctx->defer_reduce = defer;
+            ctx->x16_ready = x16d;
             ST_TRY(matmul(m, L.down, m->mid, m->aq_mid, T, m->att, H));
+            ctx->x16_ready = nullptr;
             ctx->defer_reduce = false;
             if (c.tp_size > 1) ST_TRY(tp_all_reduce_sum(ctx, m->att, (size_t)T * H));
         } else {
@@ -881,6 +902,9 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
         int max_k = std::max(H, qd), max_n = std::max(ldq, H);
         if (F) { max_k = std::max(max_k, F); max_n = std::max(max_n, 2 * F); }
         m->umma_bytes = q4k_umma_scratch_bytes(MR, max_k, max_n);
+        // two fp16 activation slots ahead of the partials: producers lay the tiles out for the matmul that follows them
+        m->x16_slot_bytes = ((size_t)ceil_div(MR, 256) * 256 * max_k * 2 + 255) & ~(size_t)255;
+        m->umma_bytes += m->x16_slot_bytes;
         // Q5_K / Q6_K tensors: fp16 copies for the tensor-core matmul from 32 rows on
         std::vector<DevMat*> kq;
         for (int l = 0; l < c.n_layers; l++) {

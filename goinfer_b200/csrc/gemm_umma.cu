@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                                                                         const __half* __restrict__ X16, int T,
                                                                         float* __restrict__ dst, int ldd, size_t split_stride,
                                                                         int* __restrict__ err_flag, int8_t* __restrict__ sw_codes,
-                                                                        float* __restrict__ sw_scales) {
+                                                                        float* __restrict__ sw_scales, __half* __restrict__ sw_x16) {
     pdl_trigger();  // the next kernel's blocks may be placed as ours retire; they wait for our completion before they touch data
     extern __shared__ __align__(1024) uint8_t umma_smem[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], raw_full, raw_empty;
@@ -315,6 +315,18 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                     o[1] = make_uint4(w[4], w[5], w[6], w[7]);
                     sw_scales[(size_t)tt * 2 * nG + (f0 >> 5)] = sc;
                     sw_scales[(size_t)tt * 2 * nG + nG + (f0 >> 5)] = __fmul_rn(sc, (float)sum);
+                    if (sw_x16) {  // the next matmul's fp16 activation tiles, laid out here instead of by a conversion kernel
+#pragma unroll
+                        for (int c8 = 0; c8 < 4; c8++) {
+                            float dq[8];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const int q = (int)(signed char)((w[(8 * c8 + i) >> 2] >> (8 * (i & 3))) & 0xffu);
+                                dq[i] = __fmul_rn((float)q, sc);
+                            }
+                            x16_store8(sw_x16, F, tt, f0 + 8 * c8, dq);
+                        }
+                    }
                 }
             }
         } else {
@@ -457,8 +469,14 @@ int launch_q4k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ a
 // With `sw` set and W = gate|up interleaved by 128 rows ([2F][K]): when the launch has two weight tiles per CTA and no K
 // split (or `force`), the epilogue writes silu(gate) * up quantized per 32 into `sw` and *fused = true; otherwise the
 // f32 product goes to dst as usual (its columns in the interleaved order) and *fused = false.
+__half* x16_next_slot(b200_ctx* ctx) {
+    if (!ctx->x16_slot_bytes || !ctx->umma_scratch) return nullptr;
+    ctx->x16_toggle ^= 1;
+    return reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(ctx->umma_scratch) + (size_t)ctx->x16_toggle * ctx->x16_slot_bytes);
+}
+
 int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
-                                  size_t scratch_bytes, int* err_flag, ActQ sw, bool force, bool* fused) {
+                                  size_t scratch_bytes, int* err_flag, ActQ sw, bool force, bool* fused, __half* sw_x16) {
     if (fused) *fused = false;
     ST_TRY(flush_pending_parts(ctx));  // the scratch is about to be reused
     if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
@@ -475,14 +493,21 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
     if (sw.codes && !fuse && !dst) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the fused SwiGLU epilogue does not apply to this shape and no f32 output was given");
     const size_t x_bytes = (size_t)t_tiles * 256 * K * 2;
     const size_t part_bytes = splits > 1 ? (size_t)splits * T * N * 4 : 0;
-    if (x_bytes + part_bytes + 256 > scratch_bytes) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tcgen05 matmul scratch too small");
-    __half* x16 = reinterpret_cast<__half*>(scratch);
-    float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + ((x_bytes + 255) & ~(size_t)255));
-    {
+    // the scratch: with activation slots, two of them and then the partials; else the activations and then the partials
+    const bool slots = ctx->x16_slot_bytes > 0 && scratch == ctx->umma_scratch;
+    const size_t part_off = slots ? 2 * ctx->x16_slot_bytes : ((x_bytes + 255) & ~(size_t)255);
+    if ((slots && x_bytes > ctx->x16_slot_bytes) || part_off + part_bytes + 256 > scratch_bytes)
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "tcgen05 matmul scratch too small");
+    float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + part_off);
+    const __half* x16 = slots ? ctx->x16_ready : nullptr;  // laid out by the kernel that quantized these activations
+    if (!x16) {
+        __half* mine = slots ? x16_next_slot(ctx) : reinterpret_cast<__half*>(scratch);
         dim3 grid(ceil_div(K / 8, 256), T);
-        launch_pdl(act_to_f16_kernel, grid, dim3(256), 0, ctx->stream, aq.codes, aq.scales, K, x16);
+        launch_pdl(act_to_f16_kernel, grid, dim3(256), 0, ctx->stream, aq.codes, aq.scales, K, mine);
         LAUNCH_CHECK(ctx);
+        x16 = mine;
     }
+    if (sw_x16 && sw_x16 == x16) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the epilogue's activation slot is the one this matmul reads");
     // A ring + B ring (sized for NT = 2) + one raw super-block per producer thread + round-up room
     constexpr int smem = kStages * 2 * kTileBytes + 2 * 2 * kTileBytes + kProducers * kRawRow + 1024;
     static bool attr_set = false;
@@ -502,9 +527,10 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
         ProfScope ps(ctx, PROF_Q4K_GEMM);
         int8_t* const no_codes = nullptr;
         float* const no_scales = nullptr;
-        if (fuse) launch_pdl(q4k_umma_gemm_kernel<2, true>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, sw.codes, sw.scales);
-        else if (NT == 2) launch_pdl(q4k_umma_gemm_kernel<2, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales);
-        else launch_pdl(q4k_umma_gemm_kernel<1, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales);
+        __half* const no_x16 = nullptr;
+        if (fuse) launch_pdl(q4k_umma_gemm_kernel<2, true>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, sw.codes, sw.scales, sw_x16);
+        else if (NT == 2) launch_pdl(q4k_umma_gemm_kernel<2, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16);
+        else launch_pdl(q4k_umma_gemm_kernel<1, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16);
     }
     LAUNCH_CHECK(ctx);
     if (fuse && fused) *fused = true;

@@ -28,7 +28,11 @@ struct UmmaScratch {
     void* saved_p;
     size_t saved_n;
     int* saved_f;
-    explicit UmmaScratch(b200_ctx* c) : ctx(c), saved_p(c->umma_scratch), saved_n(c->umma_scratch_bytes), saved_f(c->err_flag) {}
+    size_t saved_slot;
+    explicit UmmaScratch(b200_ctx* c) : ctx(c), saved_p(c->umma_scratch), saved_n(c->umma_scratch_bytes), saved_f(c->err_flag), saved_slot(c->x16_slot_bytes) {
+        c->x16_slot_bytes = 0;  // operator entry points use the plain layout: activations, then partials
+        c->x16_ready = nullptr;
+    }
     int ensure(Tmp& t, int M, int K, int N) { return ensure_bytes(t, std::max(q4k_umma_scratch_bytes(M, K, N), f16w_umma_scratch_bytes(M, K))); }
     int ensure_bytes(Tmp& t, size_t need) {
         if (ctx->umma_scratch && ctx->umma_scratch_bytes >= need && ctx->err_flag) return B200_OK;
@@ -52,6 +56,7 @@ struct UmmaScratch {
         ctx->umma_scratch = saved_p;
         ctx->umma_scratch_bytes = saved_n;
         ctx->err_flag = saved_f;
+        ctx->x16_slot_bytes = saved_slot;
     }
 };
 
