@@ -425,7 +425,8 @@ __global__ void attn_combine_kernel(const float* __restrict__ partial, int nH, i
 template <int HD>
 __global__ void __launch_bounds__(2 * HD) attn_combine2_kernel(const float* __restrict__ partial, int nH, int max_splits, int split_keys,
                                                                const int32_t* __restrict__ row_pos, float* __restrict__ out,
-                                                               int8_t* __restrict__ codes, float* __restrict__ scales) {
+                                                               int8_t* __restrict__ codes, float* __restrict__ scales,
+                                                               __half* __restrict__ x16, int x16_row0) {
     pdl_trigger();
     pdl_wait();
     constexpr int TPH = HD / 2;  // threads per head
@@ -482,6 +483,10 @@ __global__ void __launch_bounds__(2 * HD) attn_combine2_kernel(const float* __re
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         *reinterpret_cast<uint16_t*>(codes + (size_t)r * D + h * HD + e) = (uint16_t)((q0 & 0xff) | ((q1 & 0xff) << 8));
+        if (x16) {  // the o projection's fp16 activation tiles
+            x16_store1(x16, D, x16_row0 + r, h * HD + e, __fmul_rn((float)q0, sc));
+            x16_store1(x16, D, x16_row0 + r, h * HD + e + 1, __fmul_rn((float)q1, sc));
+        }
         if ((threadIdx.x & 15) == 0) {
             scales[(size_t)r * 2 * nG + g] = sc;
             scales[(size_t)r * 2 * nG + nG + g] = __fmul_rn(sc, (float)sum);
@@ -491,9 +496,12 @@ __global__ void __launch_bounds__(2 * HD) attn_combine2_kernel(const float* __re
 
 template <int HD>
 void launch_combine(b200_ctx* ctx, const float* partial, int nH, int T, int max_splits, int split_keys, const int32_t* row_pos, float* out, ActQ aq) {
-    if (nH % 4 == 0 && !((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(out)) & 7) && !(reinterpret_cast<uintptr_t>(aq.codes) & 1))
-        launch_pdl(attn_combine2_kernel<HD>, dim3(nH / 4, T), dim3(2 * HD), 0, ctx->stream, partial, nH, max_splits, split_keys, row_pos, out, aq.codes, aq.scales);
-    else
+    if (nH % 4 == 0 && !((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(out)) & 7) && !(reinterpret_cast<uintptr_t>(aq.codes) & 1)) {
+        __half* x16 = aq.codes ? ctx->x16_want : nullptr;
+        launch_pdl(attn_combine2_kernel<HD>, dim3(nH / 4, T), dim3(2 * HD), 0, ctx->stream, partial, nH, max_splits, split_keys, row_pos, out, aq.codes, aq.scales,
+                   x16, ctx->x16_row0);
+        if (x16) ctx->x16_done += T;
+    } else
         attn_combine_kernel<HD><<<dim3(nH, T), HD, 0, ctx->stream>>>(partial, nH, max_splits, split_keys, row_pos, out, aq.codes, aq.scales);
 }
 

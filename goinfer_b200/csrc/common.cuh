@@ -51,6 +51,10 @@ struct b200_ctx {
     size_t x16_slot_bytes = 0;
     int x16_toggle = 0;
     const __half* x16_ready = nullptr;
+    // a request to the attention output's quantizers (the split merge, the per-32 quantizer of a prefill run) to lay rows
+    // x16_row0.. of the slot out as they quantize them; each adds the rows it covered to x16_done
+    __half* x16_want = nullptr;
+    int x16_row0 = 0, x16_done = 0;
     // tensor parallel: the NCCL communicator b200_tp_init made for this context (null on a single GPU)
     void* tp_comm = nullptr;
     int tp_rank = 0, tp_size = 1;
@@ -148,6 +152,14 @@ __device__ __forceinline__ void x16_store8(__half* __restrict__ out, int K, int 
     const int seg = k8 >> 6, chunk = (k8 >> 3) & 7;
     const size_t tile = ((size_t)(t >> 8) * (size_t)(K >> 6) + seg) * (256 * 64);
     *reinterpret_cast<uint4*>(out + tile + (size_t)(t & 255) * 64 + ((chunk ^ (t & 7)) << 3)) = o;
+}
+
+// one activation of row t at column k into the same tiles
+__device__ __forceinline__ void x16_store1(__half* __restrict__ out, int K, int t, int k, float v) {
+    const int i = k & 7, pos = (i == 1 || i == 2) ? 3 - i : ((i == 5 || i == 6) ? 11 - i : i);
+    const int seg = k >> 6, chunk = (k >> 3) & 7;
+    const size_t tile = ((size_t)(t >> 8) * (size_t)(K >> 6) + seg) * (256 * 64);
+    out[tile + (size_t)(t & 255) * 64 + ((chunk ^ (t & 7)) << 3) + pos] = __float2half_rn(v);
 }
 
 template <typename... KArgs, typename... Args>

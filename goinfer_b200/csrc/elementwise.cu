@@ -282,6 +282,31 @@ __global__ void __launch_bounds__(256) quant_g32_kernel(const float* __restrict_
     quant_group_warp(y, codes + (size_t)r * K + g * 32, scales + (size_t)r * 2 * nG + g, scales + (size_t)r * 2 * nG + nG + g, lane);
 }
 
+// The same quantizer with eight values per thread (K a multiple of 32, aligned rows); optionally lays the rows out as the
+// tcgen05 matmul's fp16 tiles, rows x16_row0.. of the slot.
+__global__ void __launch_bounds__(256) quant_g32_vec_kernel(const float* __restrict__ x, int K, int8_t* __restrict__ codes,
+                                                            float* __restrict__ scales, __half* __restrict__ x16, int x16_row0) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.y, nG = K >> 5, nC = K >> 3;
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (blockIdx.x * 256 + (int)(threadIdx.x & ~31u) >= nC) return;  // a whole warp past the row
+    const bool live = c < nC;
+    float y[8];
+    if (live) {
+        const float4 a = *reinterpret_cast<const float4*>(x + (size_t)r * K + 8 * c), b = *reinterpret_cast<const float4*>(x + (size_t)r * K + 8 * c + 4);
+        y[0] = a.x; y[1] = a.y; y[2] = a.z; y[3] = a.w; y[4] = b.x; y[5] = b.y; y[6] = b.z; y[7] = b.w;
+    } else {
+#pragma unroll
+        for (int u = 0; u < 8; u++) y[u] = 0.f;
+    }
+    const int g = c >> 2;
+    float dq[8];
+    quant_group_quad(y, codes + (size_t)r * K + (size_t)g * 32, scales + (size_t)r * 2 * nG + g, scales + (size_t)r * 2 * nG + nG + g, threadIdx.x & 3,
+                     live, x16 ? dq : nullptr);
+    if (x16 && live) x16_store8(x16, K, x16_row0 + r, 8 * c, dq);
+}
+
 __device__ __forceinline__ float silu_f64(float x) {
     double x64 = (double)x;
     return (float)(x64 / (1.0 + exp(-x64)));
@@ -573,8 +598,14 @@ int launch_add_rmsnorm_quant(b200_ctx* ctx, float* h, const float* delta, const 
 
 int launch_quant_g32(b200_ctx* ctx, const float* x, int T, int K, ActQ aq) {
     if (K % 32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K must be a multiple of 32");
-    dim3 grid(ceil_div(K / 32, 8), T);
-    quant_g32_kernel<<<grid, 256, 0, ctx->stream>>>(x, K, aq.codes, aq.scales);
+    if (!((reinterpret_cast<uintptr_t>(x) | (uintptr_t)((size_t)K * 4)) & 15) && !(reinterpret_cast<uintptr_t>(aq.codes) & 7)) {
+        __half* x16 = ctx->x16_want;
+        launch_pdl(quant_g32_vec_kernel, dim3(ceil_div(K / 8, 256), T), dim3(256), 0, ctx->stream, x, K, aq.codes, aq.scales, x16, ctx->x16_row0);
+        if (x16) ctx->x16_done += T;
+    } else {
+        dim3 grid(ceil_div(K / 32, 8), T);
+        quant_g32_kernel<<<grid, 256, 0, ctx->stream>>>(x, K, aq.codes, aq.scales);
+    }
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }

@@ -501,6 +501,11 @@ int run_layers(b200_model* m, int T, int max_keys) {
     ctx->err_flag = m->err_flag;
     ctx->x16_slot_bytes = m->x16_slot_bytes;
     ctx->x16_ready = nullptr;
+    struct X16Guard {  // no request or hand-off outlives this call, whichever way it returns
+        b200_ctx* c;
+        ~X16Guard() { c->x16_want = nullptr; c->x16_ready = nullptr; }
+    } x16_guard{ctx};
+    ctx->x16_want = nullptr;
     // A producer lays out the fp16 activation tiles of the tcgen05 matmul that follows it (no conversion kernel) when that
     // matmul is a plain Q4_K one at a dense row count in the fast class.
     static const bool no_x16_env = getenv("B200_NO_X16_FUSE") != nullptr || getenv("B200_NO_UMMA") != nullptr;
@@ -530,6 +535,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
                                           c.qk_norm ? L.q_norm : nullptr, c.qk_norm ? L.k_norm : nullptr, c.rms_eps,
                                           m->d_row_slot, m->d_row_pos, kv));
         const bool o_q = is_kquant(L.wo.kind);
+        __half* x16o = nullptr;
         if (m->exact_scores) {
             const double scale_d = c.attn_scale != 0.f ? (double)c.attn_scale : 1.0 / std::sqrt((double)hd);
             ST_TRY(launch_paged_attention_exact(ctx, m->qkv, ldq, T, nH, nKV, hd, scale_d, (double)c.attn_softcap, m->d_row_slot,
@@ -539,11 +545,16 @@ int run_layers(b200_model* m, int T, int max_keys) {
             // a leading run of rows of one sequence (a prefill chunk) goes through the tiled causal kernel, the rest through
             // flash-decode; both write f32 context rows and their per-32 codes
             const int pf = m->pf_rows;
+            x16o = o_q ? x16_for(L.wo) : nullptr;   // the o projection's tiles: laid out by whoever quantizes the context rows
+            ctx->x16_want = x16o;
+            ctx->x16_done = 0;
+            ctx->x16_row0 = 0;
             if (pf > 0) {
                 ST_TRY(launch_prefill_attention(ctx, m->qkv, ldq, pf, nH, nKV, hd, scale, c.attn_softcap, m->pf_slot, m->pf_pos0, kv,
                                                 m->ctxb, qd));
                 if (o_q) ST_TRY(launch_quant_g32(ctx, m->ctxb, pf, qd, m->aq_ctx));
             }
+            ctx->x16_row0 = pf;
             if (T > pf) {
                 ActQ aq_tail = none;
                 if (o_q) aq_tail = ActQ{m->aq_ctx.codes + (size_t)pf * qd, m->aq_ctx.scales + (size_t)pf * 2 * (qd / 32)};
@@ -552,8 +563,11 @@ int run_layers(b200_model* m, int T, int max_keys) {
                                               m->ctxb + (size_t)pf * qd, aq_tail));
             }
         }
+        ctx->x16_want = nullptr;
         ctx->defer_reduce = defer;
+        ctx->x16_ready = (x16o && ctx->x16_done == T) ? x16o : nullptr;   // every context row was laid out
         ST_TRY(matmul(m, L.wo, m->ctxb, m->aq_ctx, T, m->att, H));
+        ctx->x16_ready = nullptr;
         ctx->defer_reduce = false;
         if (c.tp_size > 1) ST_TRY(tp_all_reduce_sum(ctx, m->att, (size_t)T * H));  // o is split by input columns: partial sums
         if (c.n_experts == 0) {
