@@ -32,6 +32,7 @@ GGML_TYPES = {
     12: ("Q4_K", 256, 144, abi.K_Q4K),
     13: ("Q5_K", 256, 176, abi.K_Q5K),
     14: ("Q6_K", 256, 210, abi.K_Q6K),
+    30: ("BF16", 1, 2, None),
 }
 TYPE_OF_KIND = {abi.K_F32: 0, abi.K_F16: 1, abi.K_Q4K: 12, abi.K_Q5K: 13, abi.K_Q6K: 14}
 
@@ -170,6 +171,10 @@ def describe(g: GGUFFile) -> GGUFModel:
     if emb is None:
         raise ValueError("token_embd.weight is missing")
     vocab = emb.dims[1]
+    biased = sorted(n for n in g.tensors if n.endswith(".bias"))
+    if biased:
+        # the resident step has no bias add (the path's model families, llama and qwen3, have none; qwen2's q/k/v do)
+        raise ValueError(f"tensors with a bias are not supported by this engine: {biased[0]} and {len(biased) - 1} more")
     return GGUFModel(arch, hidden, u("block_count"), heads, u("attention.head_count_kv") or heads, head_dim, u("feed_forward_length"), vocab,
                      u("context_length"), g.float(f"{arch}.attention.layer_norm_rms_epsilon", 1e-5 if arch == "llama" else 1e-6),
                      g.float(f"{arch}.rope.freq_base", ARCH_DEFAULT_ROPE_BASE[arch]), "blk.0.attn_q_norm.weight" in g.tensors,
@@ -218,6 +223,8 @@ def _widen(g: GGUFFile, t: TensorInfo, rows: int, cols: int) -> np.ndarray:
         return raw.view(np.float32).reshape(rows, cols).astype(np.float32)
     if name == "F16":
         return raw.view(np.float16).reshape(rows, cols).astype(np.float32)
+    if name == "BF16":
+        return (raw.view(np.uint16).astype(np.uint32) << 16).view(np.float32).reshape(rows, cols)
     if name == "Q8_0":
         b = raw.reshape(rows, cols // 32, 34)
         d = b[..., 0:2].copy().view(np.float16)[..., 0].astype(np.float32)
@@ -261,8 +268,9 @@ def tensors(g: GGUFFile, d: Optional[GGUFModel] = None) -> Iterator[tuple]:
     yield matrix("token_embd.weight", abi.T_EMBED, -1)
     yield vector("output_norm.weight", abi.T_FINAL_NORM, -1)
     if d.tied_head:
-        w = matrix("token_embd.weight", abi.T_EMBED, -1)
-        yield (abi.T_LM_HEAD,) + w[1:]
+        # the head multiplies the table's own rows: a K-quant table stays in its blocks for the head (its native lane) and is
+        # widened only for the gather
+        yield matrix("token_embd.weight", abi.T_LM_HEAD, -1)
     else:
         yield matrix("output.weight", abi.T_LM_HEAD, -1)
     for l in range(d.n_layers):

@@ -202,3 +202,44 @@ def test_gguf_loaded_oracle_equals_direct_upload(oracle_lib, tmp_path):
     direct.finalize()
     toks = [5, 9, 2, 30, 7, 7, 1]
     assert np.array_equal(r.PrefillLast(None, 0, 0, toks), direct.PrefillLast(None, 0, 0, toks))
+
+
+def test_gguf_tied_head_and_bf16(oracle_lib, tmp_path):
+    """A file without output.weight ties the head to the embedding table: a Q6_K table reaches the head in its own blocks and the
+    gather as f16; BF16 tensors are widened."""
+    s = synth.SHAPES["tiny-dense"]
+    ts = [t for t in synth.host_weights(s, 9, kinds={abi.T_EMBED: abi.K_Q6K}) if t[0] != abi.T_LM_HEAD]
+    names = {abi.T_EMBED: "token_embd.weight", abi.T_FINAL_NORM: "output_norm.weight"}
+    lname = {abi.T_WQ: "attn_q", abi.T_WK: "attn_k", abi.T_WV: "attn_v", abi.T_WO: "attn_output", abi.T_GATE: "ffn_gate", abi.T_UP: "ffn_up",
+             abi.T_DOWN: "ffn_down", abi.T_ATTN_NORM: "attn_norm", abi.T_FFN_NORM: "ffn_norm"}
+    out = []
+    for which, layer, _, kind, rows, cols, arr in ts:
+        name = names[which] if which in names else f"blk.{layer}.{lname[which]}.weight"
+        data, gt = np.ascontiguousarray(arr).view(np.uint8).reshape(-1), gguf.TYPE_OF_KIND[kind]
+        if which in (abi.T_ATTN_NORM, abi.T_FFN_NORM, abi.T_FINAL_NORM):   # norms as BF16 (their values survive: 1 + small, rounded here)
+            bf = (np.ascontiguousarray(arr, np.float32).view(np.uint32) >> 16).astype(np.uint16)
+            data, gt = bf.view(np.uint8).reshape(-1), 30
+        out.append((name, (cols, rows) if rows > 1 else (cols,), gt, data))
+    meta = {"general.architecture": "qwen2", "qwen2.embedding_length": s.hidden, "qwen2.block_count": s.n_layers,
+            "qwen2.attention.head_count": s.n_heads, "qwen2.attention.head_count_kv": s.n_kv_heads, "qwen2.feed_forward_length": s.ffn,
+            "qwen2.context_length": 64, "qwen2.attention.layer_norm_rms_epsilon": float(s.rms_eps)}
+    path = str(tmp_path / "tied.gguf")
+    gguf.write(path, meta, out)
+    g = gguf.GGUFFile(path)
+    d = gguf.describe(g)
+    assert d.tied_head and d.rope_base == 1000000.0 and d.head_dim == s.hidden // s.n_heads
+    got = {(w, l): (k, a) for w, l, _, k, _, _, a in gguf.tensors(g, d)}
+    emb = next(t for t in ts if t[0] == abi.T_EMBED)
+    assert got[(abi.T_LM_HEAD, -1)][0] == abi.K_Q6K and np.array_equal(got[(abi.T_LM_HEAD, -1)][1], emb[6])
+    k, a = got[(abi.T_EMBED, -1)]
+    assert k == abi.K_F16
+    np.testing.assert_allclose(a.astype(np.float64), kquants.q6k_dequantize(emb[6], s.vocab, s.hidden), rtol=1e-3, atol=1e-6)
+    nk, na = got[(abi.T_FINAL_NORM, -1)]
+    want = next(t for t in ts if t[0] == abi.T_FINAL_NORM)[6]
+    assert nk == abi.K_F32 and np.abs(na - want).max() <= 2.0 ** -7
+    r, _ = gguf.load(path, lambda cfg: oracle_lib.OracleResident(cfg), n_slots=2, ctx_cap=64, kernel_class=abi.CLASS_EXACT)
+    assert np.all(np.isfinite(r.PrefillLast(None, 0, 0, [1, 2, 3, 4, 5])))
+    # a file whose projections carry biases is refused, not loaded without them
+    gguf.write(str(tmp_path / "biased.gguf"), meta, out + [("blk.0.attn_q.bias", (s.n_heads * s.head_dim,), 0, np.zeros(s.n_heads * s.head_dim, np.float32))])
+    with pytest.raises(ValueError, match="bias"):
+        gguf.describe(gguf.GGUFFile(str(tmp_path / "biased.gguf")))
