@@ -12,6 +12,10 @@ step streams far more than the 126 MB L2); one step = one greedy decode token fo
 
 One JSON line on stdout (rank 0). `value` is tok/s with everything resident in HBM and the drawn ids fed back on the
 device; `e2e` is the same metric through the C ABI's step call with host buffers (embedding rows in, ids out, every step).
+Beside them, on one GPU: `parity` (the timed kernel class against the CPU oracle on a 256-sequence step of this shape),
+`exact_class` (the same workload in the exact kernel class), `c4` and `c1` (the routed-expert and the 1.1B-shape decode
+configurations), the Q4_K small-batch matmul sweep and the CPU baseline; on N >= 2 GPUs, after the replica legs, `tp_c5`:
+the 70B-class shape tensor-parallel over the N ranks.
 """
 import argparse
 import ctypes as C
@@ -50,6 +54,7 @@ def cpu_sample(steps, warmup):
     Layer time is scaled by 36/SAMPLE_LAYERS and the batch by B/SAMPLE_SEQS (CPU cost is linear in both)."""
     from goinfer_b200 import abi, q4k, synth
     from oracle import binding as ob
+    ob.use_all_cores()   # a launcher's OMP_NUM_THREADS=1 would otherwise leave the CPU arm on one core
     s = synth.SHAPES["c3-8b"]
     ctx = contexts()[:SAMPLE_SEQS]
     cap = int(ctx.max()) + warmup + steps + 2
@@ -155,6 +160,51 @@ class Clocks:
                 "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+
+def parity_leg(device):
+    """The kernel class the benchmark times against the CPU oracle: one StepBatch of 256 sequences of this shape (2 of the 36
+    layers, the head cut to 32768 rows, contexts U[96,320] uploaded to both sides, host-built N(0,0.02) weights quantized to
+    Q4_K given to both), i.e. the tcgen05 matmuls, the fused SwiGLU epilogue, the tensor-core flash-decode and the tcgen05
+    head exactly as the timed step runs them."""
+    from goinfer_b200 import abi, synth
+    from oracle import binding as ob, parity
+    ob.use_all_cores()
+    m = parity.decode_step_parity(synth.SHAPES["c3-8b"], 2, B, 96, 320, abi.CLASS_AUTO, seed=SEED, vocab=32768, device=device)
+    m["sample"] = ("one StepBatch of 256 sequences, 2 of 36 layers, head cut to 32768 rows, contexts U[96,320], fast class vs the "
+                   "CPU oracle; bar = 2e-2 + 1e-2*|oracle| per logit; near tie = the oracle's two logits within 4e-2")
+    return m
+
+
+def exact_class_leg(device, stream, steps=3, warmup=1):
+    """The headline workload in the exact kernel class (f64 attention in the CPU path's order, one ascending f32 chain per
+    matmul output): the class whose logits stay inside the build's bar at every depth."""
+    import torch
+    from goinfer_b200 import abi, synth
+    from goinfer_b200.resident import Resident
+    s = synth.SHAPES["c3-8b"]
+    ctx = contexts()
+    growth = steps + warmup + 4
+    cap = int(ctx.max()) + growth
+    blocks = 1 + int(np.ceil((ctx + growth) / 16).sum())
+    cfg = synth.make_cfg(s, B, cap, 16, blocks, B, abi.CLASS_EXACT)
+    with torch.cuda.stream(stream):
+        r = Resident(cfg, device=device, stream=stream.cuda_stream)
+        synth.load_device_weights(r, s, seed=SEED)
+        r.finalize()
+        for i in range(B):
+            r.SynthKV(i, int(ctx[i]), 0.5, 1000 + i)
+        first = np.random.default_rng(SEED + 1).integers(0, s.vocab, B).astype(np.int32)
+        pos = ctx.copy()
+        if warmup:
+            r.DecodeLoop(range(B), pos, first, warmup, log_ids=False)
+            pos += warmup
+        _, ms = r.DecodeLoop(range(B), pos, first, steps, log_ids=False)
+        r.Close()
+        r.drv.close()
+    return {"ms_per_step": ms / steps, "tok_s": B * steps / (ms * 1e-3), "steps": steps, "warmup": warmup,
+            "kernel_class": "exact (f64 attention, one-chain Q4_K matmuls)"}
+
+
 def run_gpu(args):
     import torch
     from goinfer_b200 import abi, synth
@@ -169,6 +219,9 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     stream = torch.cuda.Stream()
     K, W = args.steps, max(args.warmup, 0)
+    extra = {}
+    if world == 1 and not args.no_cpu:
+        extra["parity"] = parity_leg(local)   # small models of its own, freed before the workload's 160 GB of KV are laid out
     s = synth.SHAPES["c3-8b"]
     ctx = contexts()
     growth = 2 * (K + W) + 12                      # positions each sequence may advance over the timed loops
@@ -293,6 +346,21 @@ def run_gpu(args):
             prefill.append({"rows": PF_ROWS, "pos0": pos0, "ms": best[0], "tok_s": PF_ROWS / best[0] * 1e3, "e2e_ms": best[1],
                             "linear_tflops": lin_flop / best[0] / 1e9, "attention_tflops": att_flop / best[0] / 1e9,
                             "finite_logits": bool(np.isfinite(pf_logits).all()), "breakdown_with_events": pf_break})
+        r.Close()
+        r.drv.close()
+
+    if world == 1 and not args.no_extra:
+        from goinfer_b200 import workloads
+        extra["exact_class"] = exact_class_leg(local, stream)
+        extra["c4"] = workloads.decode("c4-moe", 128, 256, 4096, 3, steps=4, warmup=2, device=local)
+        extra["c1"] = workloads.decode("c1-1.1b", 64, 32, 1280, 1, steps=8, warmup=3, device=local)
+    if world > 1 and not args.no_extra:
+        # the 70B-class shape split over these same ranks (its own communicator; the largest batch whose KV fits)
+        from goinfer_b200 import workloads
+        barrier()
+        tp_c5 = workloads.decode_tp("c5-70b", 256, 1024, 32768, 4, steps=4, warmup=2)
+        if tp_c5 is not None:
+            extra["tp_c5"] = tp_c5
 
     if world > 1:
         import torch.distributed as dist
@@ -331,6 +399,7 @@ def run_gpu(args):
         "prefill_chunk": prefill,
         "memory": {"weights_gb": caps.weight_bytes / 1e9, "kv_gb": caps.kv_bytes / 1e9, "scratch_gb": caps.scratch_bytes / 1e9},
     }
+    line.update(extra)
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = {k: v for k, v in cpu_sample(2, 1).items() if k != "ms_per_step"}
     if world == 1 and not args.no_gemv:
@@ -361,6 +430,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-gemv", action="store_true", help="skip the Q4_K small-batch matmul sweep")
+    ap.add_argument("--no-extra", action="store_true", help="skip the legs beside the headline workload (exact class, c4, c1; tp_c5 on N >= 2)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -54,15 +54,20 @@ class Stats(C.Structure):
         ("last_step_device_ms", C.c_double)]
 
 
-# Every symbol include/b200_resident.h declares; the loader checks each one resolves.
+# Every symbol include/b200_resident.h declares (the resident backend's boundary); the loader checks each one resolves.
 EXPORTS = (
-    "b200_open", "b200_close", "b200_last_error", "b200_launch_count", "b200_model_create",
-    "b200_upload_tensor", "b200_synth_tensor", "b200_set_rope_inv_freq", "b200_model_finalize",
-    "b200_model_free", "b200_kv_slots", "b200_reset_slot", "b200_reset", "b200_block_table",
-    "b200_synth_kv", "b200_upload_kv", "b200_step_ragged", "b200_forward", "b200_prefill_last",
-    "b200_decode_loop_device", "b200_stats", "b200_profile", "b200_profile_read", "b200_debug_read_hidden", "b200_op_quant_g32", "b200_op_q4k_dequant",
-    "b200_op_q4k_matmul", "b200_op_q4k_quantize", "b200_op_rmsnorm", "b200_op_route", "b200_op_draw",
-    "b200_tp_unique_id", "b200_tp_init", "b200_tp_destroy",
-    "b200_copy_kv", "b200_op_philox", "b200_op_topk", "b200_forward_topk", "b200_op_attention", "b200_op_prefill_attention", "b200_op_f16_matmul", "b200_bench_f16_matmul", "b200_bench_q4k_matmul", "b200_bench_read", "b200_bench_kq_matmul", "b200_op_kq_matmul", "b200_op_gate_up_swiglu", "b200_bench_attention",
-    "b200_bench_prefill_attention", "b200_attention_noalloc",
+    "b200_open", "b200_close", "b200_last_error", "b200_model_create", "b200_upload_tensor", "b200_set_rope_inv_freq",
+    "b200_model_finalize", "b200_model_free", "b200_kv_slots", "b200_reset_slot", "b200_reset", "b200_block_table",
+    "b200_upload_kv", "b200_copy_kv", "b200_step_ragged", "b200_forward", "b200_forward_topk", "b200_prefill_last",
+    "b200_stats", "b200_tp_unique_id", "b200_tp_init", "b200_tp_destroy",
+    "b200_op_quant_g32", "b200_op_q4k_dequant", "b200_op_q4k_matmul", "b200_op_q4k_quantize", "b200_op_f16_matmul",
+    "b200_op_rmsnorm", "b200_op_route", "b200_op_draw", "b200_op_topk", "b200_op_philox", "b200_op_attention",
+    "b200_op_prefill_attention", "b200_op_gate_up_swiglu", "b200_op_kq_matmul", "b200_attention_noalloc",
+)
+
+# Every symbol include/b200_bench.h declares (measurement, synthetic workloads, test hooks).
+BENCH_EXPORTS = (
+    "b200_launch_count", "b200_synth_tensor", "b200_synth_kv", "b200_decode_loop_device", "b200_debug_read_hidden",
+    "b200_profile", "b200_profile_read", "b200_bench_read", "b200_bench_kq_matmul", "b200_bench_q4k_matmul",
+    "b200_bench_f16_matmul", "b200_bench_attention", "b200_bench_prefill_attention", "b200_debug_wait_fault",
 )

@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
                                                          int max_splits) {
     constexpr int DPL = HD / 32, KB = 32 / G;
     const int r = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
-    const int nkeys = row_pos[r] + 1;
+    const int nkeys = min(row_pos[r] + 1, max_blocks * block_rows);  // a position past the table reads no block outside it
     const int k0 = split * kSplitKeys;
     if (k0 >= nkeys) return;
     const int k1 = min(nkeys, k0 + kSplitKeys);
@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const float* __restrict__
     constexpr int KS = HD / 16, CPR = HD / 8, ROWB = HD * 2, TILE = 16 * ROWB, CPL = 16 * CPR / 32;
     extern __shared__ __align__(128) uint8_t attn_smem[];
     const int r = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
-    const int nkeys = row_pos[r] + 1;
+    const int nkeys = min(row_pos[r] + 1, max_blocks * block_rows);  // a position past the table reads no block outside it
     const int k0 = split * split_keys;
     if (k0 >= nkeys) return;
     const int k1 = min(nkeys, k0 + split_keys);
@@ -367,7 +367,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ partial, int nH, i
                                     const int32_t* __restrict__ row_pos, float* __restrict__ out, int8_t* __restrict__ codes,
                                     float* __restrict__ scales) {
     const int h = blockIdx.x, r = blockIdx.y, e = threadIdx.x;
-    const int nsp = (row_pos[r] + 1 + split_keys - 1) / split_keys;
+    const int nsp = min((row_pos[r] + 1 + split_keys - 1) / split_keys, max_splits);  // never past the row's slots of the array
     const float* p = partial + ((size_t)r * nH + h) * max_splits * (HD + 2);
     // eight splits' loads are in flight at a time; the sums keep the split order
     float M = -INFINITY;
@@ -431,7 +431,7 @@ __global__ void __launch_bounds__(2 * HD) attn_combine2_kernel(const float* __re
     pdl_wait();
     constexpr int TPH = HD / 2;  // threads per head
     const int h = blockIdx.x * 4 + threadIdx.x / TPH, r = blockIdx.y, e = 2 * (threadIdx.x % TPH);
-    const int nsp = (row_pos[r] + 1 + split_keys - 1) / split_keys;
+    const int nsp = min((row_pos[r] + 1 + split_keys - 1) / split_keys, max_splits);  // never past the row's slots of the array
     const float* p = partial + ((size_t)r * nH + h) * max_splits * (HD + 2);
     float M = -INFINITY, tot0 = 0.f, tot1 = 0.f, l = 0.f;
     if (nsp <= 8) {
@@ -649,10 +649,9 @@ int run_mma(b200_ctx* ctx, const float* q, int ldq, int T, int nH, int nKV, floa
     const int nsp = ceil_div(max_keys, kMmaSplitKeys);
     if (nsp > sc.max_splits) B200_FAIL(ctx, B200_BAD_ARGUMENT, "attention scratch too small for %d keys", max_keys);
     constexpr int smem = 4 * kMmaStages * 2 * 16 * HD * 2;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;  // the attribute belongs to the device
+    if (attr_once.first(ctx->device)) {
         CUDA_TRY(ctx, cudaFuncSetAttribute(attn_mma_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_set = true;
     }
     dim3 grid(nsp, nKV, T);
     {

@@ -208,10 +208,9 @@ template <int HD, int G>
 int run_prefill(b200_ctx* ctx, const float* q, int ldq, int nrows, int nH, int nKV, float scale, float cap, int pos0,
                 const int32_t* tbl, KVView kv, float* out, int ldo) {
     constexpr int smem = kPfStages * 2 * kPfKeys * HD * 2;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;  // the attribute belongs to the device
+    if (attr_once.first(ctx->device)) {
         CUDA_TRY(ctx, cudaFuncSetAttribute(attn_prefill_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_set = true;
     }
     dim3 grid(ceil_div(nrows, 16), nKV);
     {

@@ -7,7 +7,7 @@
 #include <string>
 #include <vector>
 
-#include "../../include/b200_resident.h"
+#include "../../include/b200_bench.h"  // brings in b200_resident.h
 
 // Kernel classes the per-launch profiler tells apart.
 enum ProfTag { PROF_ATTN_SPLIT = 0, PROF_ATTN_COMBINE, PROF_Q4K_GEMM, PROF_HEAD_GEMM, PROF_NORM_QUANT, PROF_ROPE_KV,
@@ -120,6 +120,18 @@ struct ProfScope {
     } while (0)
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// One-time set-up that belongs to a device rather than to the process (cudaFuncSetAttribute): a flag per device ordinal.
+// Calls into the library are serialized per context; two contexts of different devices touch different flags.
+struct PerDeviceOnce {
+    bool done[64] = {};
+    bool first(int device) {
+        bool& d = done[device & 63];
+        const bool was = d;
+        d = true;
+        return !was;
+    }
+};
 
 // ---- programmatic dependent launch -------------------------------------------------------------------------------
 // A kernel launched with launch_pdl may start while the kernel before it on the stream is still running: its blocks are

@@ -947,7 +947,7 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
     }
     ST_TRY(m->dalloc((void**)&m->split, (size_t)2 * MLR * H * 2, sb));
     CUDA_TRY(ctx, cudaMallocHost((void**)&m->p_desc, (size_t)(2 + 3 * MR) * 4 + (size_t)MR * (4 + 4 + 4 + sizeof(b200_draw))));
-    CUDA_TRY(ctx, cudaMallocHost((void**)&m->p_ids, (size_t)(MR + 1) * 4));
+    CUDA_TRY(ctx, cudaMallocHost((void**)&m->p_ids, (size_t)(MR + 2) * 4));  // ids, then the error flag and the allocator status
     CUDA_TRY(ctx, cudaEventCreate(&m->ev0));
     CUDA_TRY(ctx, cudaEventCreate(&m->ev1));
     m->finalized = true;
@@ -1066,6 +1066,19 @@ int make_private(b200_model* m, int slot, int pos, int end) {
     return B200_OK;
 }
 
+// After a synchronize that brought the device's error flag (p_ids[MR]) and allocator status (p_ids[MR+1]) back: a bounded
+// wait that gave up is B200_TIMEOUT; a prepare_step_kernel that found its free stack empty, a table full or a row count
+// unlike the descriptor's means the host's counters and the device allocator disagree, which no later step can repair.
+int check_device_flags(b200_model* m, const char* what) {
+    b200_ctx* ctx = m->ctx;
+    const int timed_out = m->p_ids[m->MR], alloc_bad = m->p_ids[m->MR + 1];
+    if (timed_out) cudaMemsetAsync(m->err_flag, 0, 4, ctx->stream);
+    if (alloc_bad) cudaMemsetAsync(m->status, 0, 4, ctx->stream);
+    if (alloc_bad) B200_FAIL(ctx, B200_CUDA_ERROR, "the device block allocator disagreed with the host's counters during %s; reset the model", what);
+    if (timed_out) B200_FAIL(ctx, B200_TIMEOUT, "a bounded device-side wait gave up during %s", what);
+    return B200_OK;
+}
+
 // Maps the blocks of rows [0, end) of one slot on the device and makes the blocks of [base, end) its own (used by the KV
 // upload/synthesis entry points, which write those rows).
 int map_slot_rows(b200_model* m, int slot, int base, int end) {
@@ -1081,7 +1094,10 @@ int map_slot_rows(b200_model* m, int slot, int base, int end) {
                                                     m->slot_mapped, m->free_stack, m->free_count, m->d_seq_row0, m->d_row_slot,
                                                     m->d_row_pos, m->status, m->refs);
     LAUNCH_CHECK(ctx);
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids + m->MR + 1, m->status, 4, cudaMemcpyDeviceToHost, ctx->stream));
     CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));  // p_desc is reused by the next call
+    m->p_ids[m->MR] = 0;
+    ST_TRY(check_device_flags(m, "a KV upload"));
     {
         const int keep_len = m->h_slot_len[slot];
         m->h_append(slot, end);
@@ -1119,18 +1135,19 @@ int b200_upload_kv(b200_model* m, int slot, int layer, int base, int n, const fl
         B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad slot, layer or range");
     ST_TRY(map_slot_rows(m, slot, base, base + n));
     const size_t cnt = (size_t)n * c.n_kv_heads * c.head_dim;
-    float *dk = nullptr, *dv = nullptr;
-    CUDA_TRY(ctx, cudaMalloc(&dk, cnt * 4));
-    CUDA_TRY(ctx, cudaMalloc(&dv, cnt * 4));
-    CUDA_TRY(ctx, cudaMemcpyAsync(dk, keys, cnt * 4, cudaMemcpyHostToDevice, ctx->stream));
-    CUDA_TRY(ctx, cudaMemcpyAsync(dv, vals, cnt * 4, cudaMemcpyHostToDevice, ctx->stream));
+    struct Staging {  // freed on every way out
+        float *k = nullptr, *v = nullptr;
+        ~Staging() { cudaFree(k); cudaFree(v); }
+    } stg;
+    CUDA_TRY(ctx, cudaMalloc(&stg.k, cnt * 4));
+    CUDA_TRY(ctx, cudaMalloc(&stg.v, cnt * 4));
+    CUDA_TRY(ctx, cudaMemcpyAsync(stg.k, keys, cnt * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(stg.v, vals, cnt * 4, cudaMemcpyHostToDevice, ctx->stream));
     upload_kv_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, ctx->stream>>>(m->kpool[layer], m->vpool[layer],
-                                                                             m->table + (size_t)slot * m->max_blocks, dk, dv, base, n,
+                                                                             m->table + (size_t)slot * m->max_blocks, stg.k, stg.v, base, n,
                                                                              c.n_kv_heads, c.head_dim, c.kv_block_rows);
     LAUNCH_CHECK(ctx);
     CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    cudaFree(dk);
-    cudaFree(dv);
     m->h_slot_len[slot] = std::max(m->h_slot_len[slot], base + n);
     return B200_OK;
 }
@@ -1323,12 +1340,10 @@ int b200_step_ragged(b200_model* m, int n_seqs, const int32_t* slot, const int32
     }
     if (R > n_out) CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids, m->d_ids, (size_t)R * 4, cudaMemcpyDeviceToHost, ctx->stream));
     CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids + m->MR, m->err_flag, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids + m->MR + 1, m->status, 4, cudaMemcpyDeviceToHost, ctx->stream));
     CUDA_TRY(ctx, cudaEventRecord(m->ev1, ctx->stream));
     CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    if (m->p_ids[m->MR]) {
-        cudaMemsetAsync(m->err_flag, 0, 4, ctx->stream);
-        B200_FAIL(ctx, B200_TIMEOUT, "a bounded device-side wait gave up during the step");
-    }
+    ST_TRY(check_device_flags(m, "the step"));
     if (n_out && logits_out) memcpy(logits_out, m->p_logits, (size_t)n_out * V * 4);
     if (ids_out) {
         for (int i = 0; i < n_seqs; i++) ids_out[i] = -1;
@@ -1484,16 +1499,17 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
     for (int st = done; st < steps; st++) ST_TRY(one_step(st));
     CUDA_TRY(ctx, cudaEventRecord(m->ev1, ctx->stream));
     CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids + m->MR, m->err_flag, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids + m->MR + 1, m->status, 4, cudaMemcpyDeviceToHost, ctx->stream));
     CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    if (m->p_ids[m->MR]) {
-        cudaMemsetAsync(m->err_flag, 0, 4, ctx->stream);
-        B200_FAIL(ctx, B200_TIMEOUT, "a bounded device-side wait gave up during the decode loop");
-    }
+    ST_TRY(check_device_flags(m, "the decode loop"));
     float ms = 0;
     cudaEventElapsedTime(&ms, m->ev0, m->ev1);
     if (ms_out) *ms_out = ms;
     if (ids_out) memcpy(ids_out, log.data(), log.size() * 4);
-    for (int i = 0; i < S; i++) m->h_append(slot[i], pos0[i] + (advance_pos ? steps : 1));
+    // The mirror pops blocks in the order the device did: step by step, and within a step sequence by sequence (a sequence
+    // by sequence replay would hand two sequences that cross block edges in different steps each other's ids).
+    for (int st = 0; st < (advance_pos ? steps : 1); st++)
+        for (int i = 0; i < S; i++) m->h_append(slot[i], pos0[i] + st + 1);
     m->stats.steps += steps;
     m->stats.rows += (int64_t)steps * S;
     m->stats.last_step_device_ms = ms / steps;

@@ -387,10 +387,9 @@ __global__ void __launch_bounds__(256, (NT <= 8 ? 2 : 1)) q4k_gemm_tile_kernel(
 template <int NT>
 int run_q4k_tile(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, int T, float* dst, int ldd) {
     constexpr int smem = 2 * (8 * NT) * (288 + 80);
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;  // the attribute belongs to the device
+    if (attr_once.first(ctx->device)) {
         cudaFuncSetAttribute(q4k_gemm_tile_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        attr_set = true;
     }
     dim3 grid(ceil_div(N, 128), ceil_div(T, 8 * NT));
     ProfScope ps(ctx, PROF_Q4K_GEMM);
@@ -742,7 +741,8 @@ int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, in
     // Fast class from 33 rows (or when asked for by klass 2): tcgen05 fp16 matmul, if its scratch is in place. (Measured:
     // at 45 rows it takes 111 us on a 28672x8192 matrix against 214 us for the integer kernels; below 33 rows the
     // streaming integer kernel is the faster one.)
-    if (klass != B200_CLASS_EXACT && klass != 3 && klass != 4 && (T >= 33 || klass == 2) && ctx->umma_scratch && !getenv("B200_NO_UMMA") &&
+    static const bool no_umma_env = getenv("B200_NO_UMMA") != nullptr;
+    if (klass != B200_CLASS_EXACT && klass != 3 && klass != 4 && (T >= 33 || klass == 2) && ctx->umma_scratch && !no_umma_env &&
         q4k_umma_scratch_bytes(T, K, N) <= ctx->umma_scratch_bytes)
         return launch_q4k_matmul_umma(ctx, W, N, K, aq, T, dst, ldd, ctx->umma_scratch, ctx->umma_scratch_bytes, ctx->err_flag);
     // Rows up to 8 are HBM-bound: split K over the CTA's warps (unless the exact class asks for the one ascending

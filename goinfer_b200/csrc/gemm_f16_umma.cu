@@ -25,6 +25,12 @@ constexpr int kHStages = 3;
 constexpr int kHStageBytes = 2 * kTileBytes + 2 * kTileBytes;  // A hi, A lo, B (256 rows = two tiles)
 constexpr int kHThreads = 10 * 32;
 
+// Test hook for the bounded waits (b200_debug_wait_fault): [0] = how many polls the MMA issuer gives a stage to fill
+// (0: the default), [1] = the K chunk from which the loader stops bringing stages in (-1: never). With a chunk withheld
+// the issuer's wait runs out, the CTA raises the error flag, waits for the copies it did start, frees its tensor memory
+// and returns; nothing spins without a limit.
+__device__ int g_wait_fault[2] = {0, -1};
+
 __global__ void __launch_bounds__(kHThreads, 1) f16w_umma_gemm_kernel(const __grid_constant__ CUtensorMap wmap, int N, int K,
                                                                       const __half* __restrict__ xhi, const __half* __restrict__ xlo,
                                                                       int T, float* __restrict__ dst, int ldd,
@@ -65,7 +71,9 @@ __global__ void __launch_bounds__(kHThreads, 1) f16w_umma_gemm_kernel(const __gr
         const uint8_t* ahi = reinterpret_cast<const uint8_t*>(xhi) + a_off;
         const uint8_t* alo = reinterpret_cast<const uint8_t*>(xlo) + a_off;
         int issued = 0;
+        const int withhold_from = g_wait_fault[1];
         for (int it = 0; it < n_it; it++) {
+            if (it == withhold_from) break;  // test hook: the stages from here on never fill
             if (it >= kHStages && !mbar_wait(smem_u32(&empty_bar[it % kHStages]), (unsigned)(((it - kHStages) / kHStages) & 1), abort_v)) {
                 abort_s = 1;
                 break;
@@ -81,8 +89,9 @@ __global__ void __launch_bounds__(kHThreads, 1) f16w_umma_gemm_kernel(const __gr
             for (int it = max(0, issued - kHStages); it < issued; it++) mbar_wait(smem_u32(&full_bar[it % kHStages]), (unsigned)((it / kHStages) & 1));
     } else if (warp == 9 && lane == 0) {
         // ---- MMA issuer ----
+        const int polls = g_wait_fault[0] > 0 ? g_wait_fault[0] : kWaitPolls;
         for (int it = 0; it < n_it; it++) {
-            if (!mbar_wait(smem_u32(&full_bar[it % kHStages]), (unsigned)((it / kHStages) & 1), abort_v)) {
+            if (!mbar_wait(smem_u32(&full_bar[it % kHStages]), (unsigned)((it / kHStages) & 1), abort_v, polls)) {
                 abort_s = 1;
                 break;
             }
@@ -231,10 +240,9 @@ int launch_f16w_matmul_umma(b200_ctx* ctx, const __half* W, int N, int K, const 
         LAUNCH_CHECK(ctx);
     }
     constexpr int smem = kHStages * kHStageBytes + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;  // the attribute belongs to the device
+    if (attr_once.first(ctx->device)) {
         CUDA_TRY(ctx, cudaFuncSetAttribute(f16w_umma_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_set = true;
     }
     const CUtensorMap* wmap = f16_weight_map(ctx, W, N, K);
     if (!wmap) return B200_CUDA_ERROR;
@@ -244,5 +252,17 @@ int launch_f16w_matmul_umma(b200_ctx* ctx, const __half* W, int N, int K, const 
         launch_pdl(f16w_umma_gemm_kernel, grid, dim3(kHThreads), smem, ctx->stream, *wmap, N, K, hi, lo, T, dst, ldd, err_flag);
     }
     LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+// Test hook: arms (or, with polls = 0 and withhold_chunk = -1, disarms) the wait fault of the f16 tcgen05 matmul on the
+// context's device. Armed, the loader of every CTA stops bringing stages in at K chunk `withhold_chunk` and the MMA
+// issuer gives a stage `polls` polls to fill, so the issuer's bounded wait runs out: the kernel raises the error flag and
+// returns, and the entry point that launched it reports B200_TIMEOUT. Nothing faults and nothing waits without a limit.
+extern "C" int b200_debug_wait_fault(b200_ctx* ctx, int polls, int withhold_chunk) {
+    if (!ctx || polls < 0) return B200_BAD_ARGUMENT;
+    const int v[2] = {polls, withhold_chunk};
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyToSymbol(g_wait_fault, v, sizeof v));
     return B200_OK;
 }

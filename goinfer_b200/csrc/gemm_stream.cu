@@ -295,10 +295,9 @@ int run_stream(b200_ctx* ctx, const CUtensorMap* wmap, int N, int nSB, ActQ aq, 
     const CUtensorMap* cmap = act_map(ctx, aq.codes, nSB * 256, T, 8 * NT, true);
     const CUtensorMap* smap = act_map(ctx, aq.scales, nSB * 16, T, 8 * NT, false);
     if (!cmap || !smap) return B200_CUDA_ERROR;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;  // the attribute belongs to the device
+    if (attr_once.first(ctx->device)) {
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_set = true;
     }
     dim3 grid(ceil_div(N, kSRows), splits);
     float* out = splits > 1 ? part : dst;
@@ -349,10 +348,9 @@ int launch_q4k_matmul_stream_grouped(b200_ctx* ctx, const uint8_t* W_all, int n_
     const CUtensorMap* smap = act_map(ctx, aq.scales, nSB * 16, n_rows, 8 * NT, false);
     if (!wmap || !cmap || !smap) return B200_CUDA_ERROR;
     constexpr int smem = stream_stages(NT) * stream_stage_bytes(NT) + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;  // the attribute belongs to the device
+    if (attr_once.first(ctx->device)) {
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_set = true;
     }
     (void)max_rows_per_expert;
     dim3 grid(N / kSRows, n_experts);

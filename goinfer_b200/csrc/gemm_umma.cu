@@ -510,12 +510,11 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
     if (sw_x16 && sw_x16 == x16) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the epilogue's activation slot is the one this matmul reads");
     // A ring + B ring (sized for NT = 2) + one raw super-block per producer thread + round-up room
     constexpr int smem = kStages * 2 * kTileBytes + 2 * 2 * kTileBytes + kProducers * kRawRow + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;  // the attribute belongs to the device
+    if (attr_once.first(ctx->device)) {
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_set = true;
     }
     const CUtensorMap* wmap = q4k_weight_map(ctx, W, N, nSB, 128 * NT);
     if (!wmap) return B200_CUDA_ERROR;

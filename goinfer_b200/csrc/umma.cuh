@@ -22,8 +22,9 @@ __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
 // Bounded wait; false when the barrier did not complete the phase in time (or the CTA is aborting). try_wait suspends
 // the thread for a hardware-bounded time instead of spinning: 17 warps share 4 schedulers, and warps that spin on a
 // barrier take issue slots from the warps they are waiting for.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag = nullptr) {
-    for (int i = 0; i < (1 << 20); i++) {
+constexpr int kWaitPolls = 1 << 20;
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag = nullptr, int polls = kWaitPolls) {
+    for (int i = 0; i < polls; i++) {
         unsigned ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"

@@ -49,7 +49,7 @@ def load_library() -> C.CDLL:
                 f"{_LIB_PATH} is not built; run `python -c 'import __graft_entry__ as g; g.build()'` "
                 "(there is no CPU fallback)")
         lib = C.CDLL(_LIB_PATH)
-        missing = [s for s in abi.EXPORTS if not hasattr(lib, s)]
+        missing = [s for s in abi.EXPORTS + abi.BENCH_EXPORTS if not hasattr(lib, s)]
         if missing:
             raise ImportError(f"libgoinfer_b200.so lacks symbols: {missing}")
         lib.b200_last_error.restype = C.c_char_p

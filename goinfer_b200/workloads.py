@@ -78,12 +78,17 @@ def decode_tp(shape: str, batch: int, ctx_lo: int, ctx_hi: int, seed: int, steps
               kv_budget_gb: float = 0.0) -> dict:
     """Tensor-parallel decode: run under torch.distributed.run, one process per GPU. The batch is cut to the first
     sequences whose paged KV fits the ranks' memory (the 70B-class configuration's full batch does not fit 8 GPUs);
-    the cut is reported. Rank 0 returns the result, the others None."""
+    the cut is reported. Rank 0 returns the result, the others None. A process group the caller already initialised
+    (gloo or nccl) is used as it is and left open; otherwise a gloo group is made for the length of the call."""
     import os
+    import torch
     import torch.distributed as dist
     from . import abi, synth, tp
 
-    dist.init_process_group("gloo")
+    own_group = not dist.is_initialized()
+    if own_group:
+        dist.init_process_group("gloo")
+    on_gpu = dist.get_backend() == "nccl"
     rank, world, dev = dist.get_rank(), dist.get_world_size(), int(os.environ.get("LOCAL_RANK", "0"))
     s = synth.SHAPES[shape]
     sl = tp.local_shape(s, world)
@@ -128,13 +133,14 @@ def decode_tp(shape: str, batch: int, ctx_lo: int, ctx_hi: int, seed: int, steps
     launches = int(lib.b200_launch_count(bctx) - l0)
     dev_ms = tp.max_over_ranks(dist, float(ms.value))
     # every rank drew the same ids (the logits were gathered, the draw is replicated)
-    import torch
     mine = torch.from_numpy(ids.copy())
+    if on_gpu:
+        mine = mine.cuda()
     ref = mine.clone()
     dist.broadcast(ref, src=0)
-    flag = torch.tensor([1 if bool((mine == ref).all()) else 0])
+    flag = torch.tensor([1 if bool((mine == ref).all()) else 0], device=mine.device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    same = bool(flag[0] == 1)
+    same = bool(flag.cpu()[0] == 1)
     keys = float(np.mean([(pos + 1 + i).sum() for i in range(steps)]))
     pos += steps
     tag_ms = (C.c_double * 8)()
@@ -154,10 +160,13 @@ def decode_tp(shape: str, batch: int, ctx_lo: int, ctx_hi: int, seed: int, steps
                "all_reduce_bytes_per_step": 2 * L * b_fit * s.hidden * 4,
                "memory_per_rank": {"weights_gb": caps.weight_bytes / 1e9, "kv_gb": caps.kv_bytes / 1e9, "scratch_gb": caps.scratch_bytes / 1e9},
                "hbm_floor_ms": (keys * per_pos + caps.weight_bytes) / 6540.5e9 * 1e3,
+               "nvls": os.environ.get("NCCL_NVLS_ENABLE", "library default"),
                "breakdown_ms_per_step_rank0": {n: round(tag_ms[i] / 2, 4) for i, n in enumerate(names) if tag_n[i]}}
     dist.barrier()
     r.Close()
-    dist.destroy_process_group()
+    r.drv.close()
+    if own_group:
+        dist.destroy_process_group()
     return out
 
 

@@ -86,8 +86,12 @@ extern "C" {
 /* ---- kernel classes (b200_model_cfg.kernel_class) -------------------------------------------------
  * The reference separates exact kernels from fast, non-bit-identical ones by a row floor
  * (resident.Caps.HasFastPrefill / FastPrefillFloor, decoder/resident/forward.go:119-146). */
-#define B200_CLASS_AUTO  0 /* fast class: fp32 flash-decode attention, split-K Q4_K matmul at up to 8 rows.
-                              Integer dots stay exact; f32 sums are folded in another order than the CPU path's. */
+#define B200_CLASS_AUTO  0 /* fast class: tensor-core flash-decode and tiled prefill attention with fp32 online softmax; Q4_K
+                              matmuls by row count: integer-dot kernels with the CPU path's per-group formula at small row
+                              counts (f32 sums folded in another order), and from 33 rows a tcgen05 matmul over the
+                              dequantized fp16 weights and fp16(code * scale) activations with fp32 accumulation.
+                              Held to the logit bar on shallow models and to cosine >= 0.995 / relative L2 <= 0.10
+                              (decoder/selftest_gpu.go:30-35) at depth. */
 #define B200_CLASS_EXACT 1 /* exact class: attention in f64 in the CPU path's own order (decoder/forwardn.go:379-499)
                               and one ascending f32 chain per matmul output at every row count, so a row's bits do
                               not depend on its batch (decoder/resident/subsystems.go:102-110)             */
@@ -148,9 +152,6 @@ int b200_open(int device_ordinal, void* stream, b200_ctx** out);
 void b200_close(b200_ctx* ctx);
 /* Text of the last non-OK status on this context (the Go shim turns it into an error value). */
 const char* b200_last_error(b200_ctx* ctx);
-/* Counts kernels launched by this library on the context since open (bench accounting). */
-int64_t b200_launch_count(b200_ctx* ctx);
-
 /* Tensor parallel (the 70B-class configuration: q/k/v/gate/up split by output rows, o/down by input columns, the KV
  * cache by kv head, an all-reduce of the partial [rows][hidden] products after the o and down projections, the LM head
  * split by vocabulary slice and gathered). No counterpart in the reference's single-GPU CUDA backend. One process per GPU:
@@ -169,11 +170,6 @@ int b200_model_create(b200_ctx* ctx, const b200_model_cfg* cfg, b200_model** out
  * is an expert tensor. The host buffer stays the caller's. */
 int b200_upload_tensor(b200_model* m, int which, int layer, int expert, int kind,
                        int rows, int cols, const void* host, size_t bytes);
-/* Fills one Q4_K tensor on the device with seeded N(0, sigma) weights quantized by the library's
- * deterministic quantizer (no host copy). The reference has no fp32->Q4_K quantizer (it only reads
- * GGUF, decoder/gguf.go:1508-1537); this exists for synthetic-weight workloads. */
-int b200_synth_tensor(b200_model* m, int which, int layer, int expert, int kind,
-                      int rows, int cols, float sigma, uint64_t seed);
 /* Per-layer RoPE inverse frequencies (BackendView.RopeInvFreq, decoder/residency.go:604-619). `layer`
  * -1 sets every layer. Without a call the table is theta^(-2d/rotary_dim) (decoder/ropescale.go:285-290). */
 int b200_set_rope_inv_freq(b200_model* m, int layer, const double* inv_freq, int n);
@@ -188,9 +184,6 @@ int b200_reset_slot(b200_model* m, int slot);
 int b200_reset(b200_model* m);
 /* Copies a slot's block table (ctx_cap / kv_block_rows entries, 0 = unmapped) to `out`. */
 int b200_block_table(b200_model* m, int slot, int32_t* out, int n);
-/* Fills the KV rows [0, n_pos) of a slot in every layer with seeded N(0, sigma) fp16 values (synthetic
- * prefix contexts for a decode benchmark) and maps their blocks. */
-int b200_synth_kv(b200_model* m, int slot, int n_pos, float sigma, uint64_t seed);
 /* ResidentForward.UploadKV (decoder/resident/forward.go:5-33): rows [base, base+n) of one layer, f32
  * [n][n_kv_heads*head_dim], rounded to the cache's fp16. */
 int b200_upload_kv(b200_model* m, int slot, int layer, int base, int n, const float* keys, const float* vals);
@@ -222,7 +215,6 @@ int b200_step_ragged(b200_model* m, int n_seqs, const int32_t* slot, const int32
  * (decoder/resident/forward.go:5-33): one row at `pos`. out_kind: 0 logits, 1 argmax id, 2 nothing. */
 int b200_forward(b200_model* m, int slot, const float* emb, int token_id, int pos, int out_kind,
                  float* logits_out, int32_t* id_out);
-/* PrefillSubsystem.PrefillLast: n rows from start_pos on one slot, logits of the last row. */
 /* DecodeSubsystem.ForwardTopK (decoder/resident/subsystems.go:40-48): one row at `pos`, only its k best logits (and Z when
  * z_out is not NULL) come back instead of the vocabulary-wide row. inv_temperature = float32(1/T). */
 int b200_forward_topk(b200_model* m, int slot, const float* emb, int token_id, int pos, int k, float inv_temperature,
@@ -234,29 +226,11 @@ int b200_forward_topk(b200_model* m, int slot, const float* emb, int token_id, i
  * the rows before the write (copy on write), so no slot ever writes a block another slot reads.
  * B200_KV_POOL_FULL (nothing changed) when the one block this may take is not there. */
 int b200_copy_kv(b200_model* m, int dst_slot, int src_slot, int n_rows);
+/* PrefillSubsystem.PrefillLast (decoder/resident/subsystems.go): n rows from start_pos on one slot, logits of the last row. */
 int b200_prefill_last(b200_model* m, int slot, int n, const float* embs, const int32_t* token_ids,
                       int start_pos, float* logits_out);
 
-/* Timed decode steps with everything already on the device (benchmark leg "value"): runs `steps`
- * greedy StepBatch iterations over the given sequences, feeding each drawn id back as the next token,
- * and returns the device time of the whole loop in milliseconds. */
-int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, const int32_t* pos0,
-                            const int32_t* first_ids, int steps, int advance_pos,
-                            int32_t* ids_out /*[steps][n_seqs] or NULL*/, float* ms_out);
-
 int b200_stats(b200_model* m, b200_stats_t* out);
-/* Debug tap for parity work: copies the first n floats of the residual stream ([rows][hidden]) as the latest
- * step left it after its last layer. */
-int b200_debug_read_hidden(b200_model* m, float* out, int n);
-
-/* Per-launch CUDA-event timing of kernel classes, on the stream the kernels are launched on (the role of
- * the reference's per-phase decodeTiming clocks, decoder/policy_decode.go:10-14). tag_mask bit i enables
- * class i: 0 attention split, 1 attention combine, 2 Q4_K matmul, 3 LM-head matmul, 4 norm+quant,
- * 5 RoPE+KV store, 6 SwiGLU+quant. b200_profile_read synchronizes, sums milliseconds and launches per class
- * since the last read, and clears the records. */
-int b200_profile(b200_ctx* ctx, unsigned tag_mask);
-int b200_profile_read(b200_ctx* ctx, double* ms_by_tag, int64_t* launches_by_tag, int n_tags);
-
 /* ---- operator-level entry points (host buffers in, host buffers out) -------------------------------
  * The reference exposes its matmul as Backend.MatmulBT(a, b, dst, M, K, N) (decoder/backend.go:23-32)
  * and tests kernels against host twins (backend/cuda/kernels/actgroup_kernel_test.go). These run the
@@ -272,10 +246,11 @@ int b200_op_q4k_dequant(b200_ctx* ctx, const uint8_t* w, int rows, int cols, flo
  * one-chain form (the exact class's bits). */
 int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, int K, int N, int klass,
                        float* dst);
-/* fp32 -> Q4_K with the library's quantizer; out is rows*cols/256*144 bytes. */
 /* dst[M][N] = a[M][K] . w[N][K]^T over f16 weights (the LM head's kind, decoder/forwardn.go:800-831): klass 0 picks by
  * row count as a fast-class step does, 1 the accurate small-batch kernel, 2 forces the tcgen05 kernel. */
 int b200_op_f16_matmul(b200_ctx* ctx, const uint16_t* w, const float* a, int M, int K, int N, int klass, float* dst);
+/* fp32 -> Q4_K with the library's deterministic quantizer (the reference only reads Q4_K, decoder/gguf.go:1508-1537); out is
+ * rows*cols/256*144 bytes. */
 int b200_op_q4k_quantize(b200_ctx* ctx, const float* w, int rows, int cols, uint8_t* out);
 /* RMSNorm rows (decoder/rmsnorm.go:29-92). */
 int b200_op_rmsnorm(b200_ctx* ctx, const float* x, const float* w, int rows, int dim, float eps, float* out);
@@ -316,37 +291,27 @@ int b200_op_gate_up_swiglu(b200_ctx* ctx, const uint8_t* w_host, const float* x_
  * x [M][K], quantized per 32 on the device like the step does. */
 int b200_op_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* w_host, const float* x_host, int M, int K, int N, float* dst_host);
 
-/* Device-resident micro-benchmarks: average device milliseconds per launch over `iters` launches after
- * `warmup`, of the kernel the step would pick (or `klass`), on synthetic resident data. */
-/* The read-only floor of a streaming kernel over `bytes` bytes: a grid-stride 16-byte-load kernel that only sums what it
- * reads, launched back to back over `n_copies` copies of the buffer like the matmul benchmark launches its weights. */
-int b200_bench_read(b200_ctx* ctx, size_t bytes, int n_copies, int warmup, int iters, float* ms_out);
-/* The Q5_K / Q6_K matmul (kind B200_K_Q5K / B200_K_Q6K) on random blocks with sane scales, cycled over copies. */
-int b200_bench_kq_matmul(b200_ctx* ctx, int kind, int M, int K, int N, int n_weight_copies, int warmup, int iters, float* ms_out);
-int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_weight_copies,
-                          int warmup, int iters, float* ms_out);
-int b200_bench_f16_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int warmup, int iters, float* ms_out);
-int b200_bench_attention(b200_ctx* ctx, int rows, int ctx_lo, int ctx_hi, int n_heads, int n_kv_heads,
-                         int head_dim, int block_rows, uint64_t seed, int warmup, int iters,
-                         float* ms_out, double* kv_bytes_out);
-int b200_bench_prefill_attention(b200_ctx* ctx, int rows, int pos0, int n_heads, int n_kv_heads, int head_dim,
-                                 int block_rows, int warmup, int iters, float* ms_out);
-
 /* Paged decode attention that allocates nothing. No counterpart in the reference (its backends allocate their split
  * buffers when a model is built); it exists for hosts that cannot allocate when they need attention: a serving process
  * whose device memory was handed out once at start-up and is owned by its own pool, or a plug-in living under another
  * program's "no device allocation after init" rule, where a cudaMalloc in the step would break the host's memory budget.
  *
- * All pointers are DEVICE pointers owned by the caller: q [rows][ldq] f32 (query heads of row r at q + r*ldq),
- * row_slot/row_pos [rows] (the block-table row and the position, i.e. keys-1, of each query), k_pool/v_pool the fp16
- * pools laid out [block][kv_head][row_in_block][head_dim], block_table [n_table_rows][max_blocks], out [rows][n_heads*head_dim]
- * f32. scale 0 means 1/sqrt(head_dim). Work is queued on the context's stream; the caller synchronizes that stream
- * before reading `out`.
+ * All pointers are DEVICE pointers owned by the caller: q [rows][ldq] f32 (query heads of row r at q + r*ldq; 8-byte
+ * aligned, ldq even), row_slot/row_pos [rows] (the block-table row and the position, i.e. keys-1, of each query),
+ * k_pool/v_pool the fp16 pools laid out [block][kv_head][row_in_block][head_dim] (16-byte aligned), block_table
+ * [n_table_rows][max_blocks], out [rows][n_heads*head_dim] f32 (8-byte aligned). scale 0 means 1/sqrt(head_dim). Work is
+ * queued on the context's stream; the caller synchronizes that stream before reading `out`. The context's device is made
+ * current for the length of the call and the caller's own device is current again when it returns.
+ *
+ * Preconditions the library cannot check (the arrays live on the device): 0 <= row_pos[r] < max_keys, row_slot[r] names a
+ * row of block_table, and every table entry of a row's keys names a block of the pools. A row_pos[r] >= max_keys reads
+ * nothing outside the table or the scratch, but that row's output is meaningless.
  *
  * The split partials live in one fixed 16 MiB device array inside the library (every GPU that loads the library holds
- * it until the process exits). Limits: head_dim 64 or 128, n_heads/n_kv_heads in {1,2,4,8}, block_rows a multiple of 16,
- * and rows * n_heads * ceil(max_keys/512) * (head_dim+2) * 4 bytes <= 16 MiB (e.g. 32 heads of 128: 63 rows at 2048 keys,
- * 15 rows at 8192 keys); anything larger returns B200_BAD_ARGUMENT with the sizes in b200_last_error.
+ * it until the process exits). Limits: head_dim 64 or 128, n_heads/n_kv_heads in {1,2,4,8}, block_rows a positive multiple
+ * of 16, max_blocks * block_rows >= max_keys, and rows * n_heads * ceil(max_keys/512) * (head_dim+2) * 4 bytes <= 16 MiB
+ * (e.g. 32 heads of 128: 252 rows at 2048 keys, 63 rows at 8192 keys); anything else returns B200_BAD_ARGUMENT with the
+ * sizes in b200_last_error.
  * The first call on a device looks up the array's address (no allocation); make that first call before starting any
  * stream capture. The array is shared by every call and keeps the previous call's bytes; nothing in it needs clearing,
  * but two calls whose kernels overlap on the GPU (different streams or contexts of one device) race on it:

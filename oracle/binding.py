@@ -237,3 +237,11 @@ def op_attention(q, k, v, n_keys, n_heads, n_kv_heads, head_dim, scale, softcap=
 
 def threads() -> int:
     return lib().oracle_threads()
+
+
+def use_all_cores() -> int:
+    """Gives the oracle's parallel loops every core this process may run on (torch.distributed.run exports
+    OMP_NUM_THREADS=1 to its workers) and returns the thread count in use."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_threads(n)
+    return threads()

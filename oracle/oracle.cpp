@@ -1278,4 +1278,13 @@ int oracle_threads(void) {
 #endif
 }
 
+// Sets the worker count of the parallel loops (a launcher may have exported OMP_NUM_THREADS=1 for its own reasons).
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 }  // extern "C"

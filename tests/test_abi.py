@@ -1,4 +1,4 @@
-"""The C-ABI library loads and exports every symbol include/b200_resident.h declares (no GPU calls)."""
+"""The C-ABI library loads and exports every symbol include/b200_resident.h and include/b200_bench.h declare (no GPU calls)."""
 import os
 import re
 
@@ -16,13 +16,22 @@ def lib():
     return resident.load_library()
 
 
-def test_every_declared_symbol_is_exported(lib):
-    hdr = open(os.path.join(ROOT, "include", "b200_resident.h")).read()
+@pytest.mark.parametrize("header,table", [("b200_resident.h", abi.EXPORTS), ("b200_bench.h", abi.BENCH_EXPORTS)])
+def test_every_declared_symbol_is_exported(lib, header, table):
+    hdr = open(os.path.join(ROOT, "include", header)).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)   # declarations only, not names mentioned in comments
     declared = set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", hdr))
     assert declared, "no declarations parsed"
-    assert declared == set(abi.EXPORTS), declared ^ set(abi.EXPORTS)
+    assert declared == set(table), declared ^ set(table)
     for name in declared:
         assert hasattr(lib, name), name
+
+
+def test_the_product_header_declares_only_reference_facing_entry_points():
+    """Every declaration of b200_resident.h cites the reference interface it stands in for (or says that it has none);
+    benchmark, synthesis and debug entry points live in b200_bench.h."""
+    hdr = open(os.path.join(ROOT, "include", "b200_resident.h")).read()
+    assert not re.search(r"\bb200_(bench|synth|debug|profile)_?[a-z0-9_]*\s*\(", re.sub(r"/\*.*?\*/", "", hdr, flags=re.S))
 
 
 def test_struct_layouts_match_the_header():

@@ -9,6 +9,7 @@ import numpy as np
 import pytest
 
 from goinfer_b200 import abi, q4k
+from goinfer_b200.resident import ResidentError
 
 pytestmark = pytest.mark.gpu
 
@@ -457,3 +458,26 @@ def test_topk_rows_match_the_host_order(ops, oracle_lib, V, k):
     assert np.array_equal(got_v.view(np.uint32), want_v.view(np.uint32))
     np.testing.assert_allclose(got_z, want_z, rtol=1e-12)
     assert got_i[3].tolist() == list(range(k))
+
+
+def test_a_bounded_device_wait_that_runs_out_reports_timeout_and_the_context_stays_usable(ops):
+    """Every spin in the tcgen05 kernels is bounded: when a stage never fills, the waiting thread gives up after its poll
+    limit, the CTA raises the model's error flag, waits for the copies it started, frees its tensor memory and returns, and
+    the entry point reports B200_TIMEOUT (status 5). The test hook makes the f16 matmul's loader stop bringing stages in
+    from K chunk 2 on and shortens the issuer's limit; the call must come back with status 5, and with the hook disarmed
+    the same context must multiply correctly again."""
+    import ctypes as C
+    rng = np.random.default_rng(5)
+    M, K, N = 128, 512, 512
+    w = rng.normal(0, 0.05, (N, K)).astype(np.float16)
+    a = rng.normal(0, 1, (M, K)).astype(np.float32)
+    want = a.astype(np.float64) @ w.astype(np.float64).T
+    np.testing.assert_allclose(ops.f16_matmul(w, a, klass=2), want, atol=2e-4, rtol=1e-4)
+    assert ops.lib.b200_debug_wait_fault(ops.ctx, 20000, 2) == abi.OK
+    try:
+        with pytest.raises(ResidentError) as e:
+            ops.f16_matmul(w, a, klass=2)
+        assert e.value.status == abi.TIMEOUT, str(e.value)
+    finally:
+        assert ops.lib.b200_debug_wait_fault(ops.ctx, 0, -1) == abi.OK
+    np.testing.assert_allclose(ops.f16_matmul(w, a, klass=2), want, atol=2e-4, rtol=1e-4)

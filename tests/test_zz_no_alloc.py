@@ -4,8 +4,9 @@ Its split partials live in a fixed 16 MiB array inside the library instead of a 
 
 The test drives it through the C ABI with device buffers made by torch, twice in a row with different inputs (the
 second call finds the first call's leftovers in the shared array), and compares each result with the allocating entry
-point b200_op_attention on the same data, to the tolerance the attention tests use. It also checks that a request too
-large for the array is refused with the sizes in the error text. The file sorts last so that a run that stops at the
+point b200_op_attention on the same data and with the CPU oracle's f64 attention, to the tolerance the attention tests
+use. It also checks that the caller's current device is the same after a call as before it, and that requests too
+large for the array, or whose table cannot hold the keys, are refused with the sizes in the error text. The file sorts last so that a run that stops at the
 first failure has already run every other test."""
 import ctypes as C
 
@@ -35,7 +36,7 @@ def _paged(k, v, n_keys, nKV, hd, block_rows):
     return kp, vp, table
 
 
-def test_no_alloc_attention_matches_the_allocating_entry_point_twice():
+def test_no_alloc_attention_matches_the_allocating_entry_point_twice(oracle_lib):
     import torch
     from goinfer_b200.ops import Ops
     stream = torch.cuda.Stream()
@@ -50,6 +51,7 @@ def test_no_alloc_attention_matches_the_allocating_entry_point_twice():
         k = rng.normal(0, 1, (rows, max_keys, nKV * hd)).astype(np.float32)
         v = rng.normal(0, 1, (rows, max_keys, nKV * hd)).astype(np.float32)
         want = ops.attention(q, k, v, n_keys, nH, nKV, hd, 0.0, 0.0, block_rows=br)
+        want64 = oracle_lib.op_attention(q, k, v, n_keys, nH, nKV, hd, 1.0 / np.sqrt(hd), 0.0)
         kp, vp, table = _paged(k, v, n_keys, nKV, hd, br)
         dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
         dq, dk, dv, dt = dev(q), dev(kp), dev(vp), dev(table)
@@ -61,11 +63,20 @@ def test_no_alloc_attention_matches_the_allocating_entry_point_twice():
                                         max_keys, p(dk), p(dv), p(dt), table.shape[1], br, p(dout))
         assert st == abi.OK, ops.drv.last_error()
         torch.cuda.synchronize()
+        assert torch.cuda.current_device() == 0
         got = dout.cpu().numpy()
         np.testing.assert_allclose(got, want, atol=2e-5, rtol=1e-4, err_msg=f"call {call}")
+        np.testing.assert_allclose(got, want64, atol=2e-5, rtol=1e-4, err_msg=f"call {call} against the f64 oracle")
     # a request whose partials do not fit the fixed array is refused, and says why
-    st = lib.b200_attention_noalloc(ctx, p(dq), nH * hd, 64, nH, nKV, hd, C.c_float(0.0), C.c_float(0.0), p(dslot), p(dpos),
-                                    8192, p(dk), p(dv), p(dt), table.shape[1], br, p(dout))
+    # (refusals come before any launch, so the sizes named here need no buffers behind them)
+    st = lib.b200_attention_noalloc(ctx, p(dq), nH * hd, 100, nH, nKV, hd, C.c_float(0.0), C.c_float(0.0), p(dslot), p(dpos),
+                                    8192, p(dk), p(dv), p(dt), 8192 // br, br, p(dout))
     assert st == abi.BAD_ARGUMENT
     msg = ops.drv.last_error()
     assert "scratch" in msg and "16777216" in msg, msg
+    # a table too short for the key range, a block size of zero and a misaligned q are refused too
+    for kwargs in (dict(max_blocks=table.shape[1] - 1), dict(block_rows=0), dict(q_off=4)):
+        st = lib.b200_attention_noalloc(ctx, C.c_void_p(dq.data_ptr() + kwargs.get("q_off", 0)), nH * hd, rows, nH, nKV, hd, C.c_float(0.0),
+                                        C.c_float(0.0), p(dslot), p(dpos), max_keys, p(dk), p(dv), p(dt),
+                                        kwargs.get("max_blocks", table.shape[1]), kwargs.get("block_rows", br), p(dout))
+        assert st == abi.BAD_ARGUMENT, kwargs
