@@ -199,10 +199,19 @@ def exact_class_leg(device, stream, steps=3, warmup=1):
             r.DecodeLoop(range(B), pos, first, warmup, log_ids=False)
             pos += warmup
         _, ms = r.DecodeLoop(range(B), pos, first, steps, log_ids=False)
+        pos += steps
+        lib, bctx = r.drv.lib, r.drv.ctx
+        tag_ms, tag_n = (C.c_double * 8)(), (C.c_int64 * 8)()
+        lib.b200_profile(bctx, 0xFF)
+        r.DecodeLoop(range(B), pos, first, 1, log_ids=False)
+        lib.b200_profile_read(bctx, tag_ms, tag_n, 8)
+        lib.b200_profile(bctx, 0)
+        names = ("attn_scores", "attn_softmax", "q4k_matmul", "head_matmul", "norm_quant", "rope_kvstore", "swiglu_quant", "attn_av")
         r.Close()
         r.drv.close()
     return {"ms_per_step": ms / steps, "tok_s": B * steps / (ms * 1e-3), "steps": steps, "warmup": warmup,
-            "kernel_class": "exact (f64 attention, one-chain Q4_K matmuls)"}
+            "kernel_class": "exact (f64 attention, one-chain Q4_K matmuls)",
+            "breakdown_ms_per_step": {n: round(tag_ms[i], 3) for i, n in enumerate(names) if tag_n[i]}}
 
 
 def run_gpu(args):

@@ -674,13 +674,22 @@ int launch_paged_attention_exact(b200_ctx* ctx, const float* q, int ldq, int T, 
                                  double softcap, const int32_t* row_slot, const int32_t* row_pos, int max_keys, KVView kv,
                                  float* scores, int ld, float* out, ActQ aq) {
     if (max_keys > ld) B200_FAIL(ctx, B200_BAD_ARGUMENT, "exact attention scratch holds %d keys, %d asked", ld, max_keys);
-    attn_exact_scores_kernel<<<dim3(ceil_div(max_keys, 128), nH, T), 128, 0, ctx->stream>>>(
-        q, ldq, nH, nKV, hd, scale, softcap, row_slot, row_pos, kv.k, kv.table, kv.max_blocks, kv.block_rows, scores, ld);
+    {
+        ProfScope ps(ctx, PROF_ATTN_SPLIT);
+        attn_exact_scores_kernel<<<dim3(ceil_div(max_keys, 128), nH, T), 128, 0, ctx->stream>>>(
+            q, ldq, nH, nKV, hd, scale, softcap, row_slot, row_pos, kv.k, kv.table, kv.max_blocks, kv.block_rows, scores, ld);
+    }
     LAUNCH_CHECK(ctx);
-    attn_exact_softmax_kernel<<<dim3(nH, T), 256, 0, ctx->stream>>>(row_pos, nH, scale, softcap, scores, ld);
+    {
+        ProfScope ps(ctx, PROF_ATTN_COMBINE);
+        attn_exact_softmax_kernel<<<dim3(nH, T), 256, 0, ctx->stream>>>(row_pos, nH, scale, softcap, scores, ld);
+    }
     LAUNCH_CHECK(ctx);
-    attn_exact_av_kernel<<<dim3(nH, T), ((hd + 31) / 32) * 32, 0, ctx->stream>>>(scores, ld, nH, nKV, hd, row_slot, row_pos, kv.v,
-                                                                                 kv.table, kv.max_blocks, kv.block_rows, out);
+    {
+        ProfScope ps(ctx, PROF_OTHER);
+        attn_exact_av_kernel<<<dim3(nH, T), ((hd + 31) / 32) * 32, 0, ctx->stream>>>(scores, ld, nH, nKV, hd, row_slot, row_pos, kv.v,
+                                                                                     kv.table, kv.max_blocks, kv.block_rows, out);
+    }
     LAUNCH_CHECK(ctx);
     if (aq.codes) return launch_quant_g32(ctx, out, T, nH * hd, aq);
     return B200_OK;

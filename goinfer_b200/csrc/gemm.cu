@@ -14,28 +14,9 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "kq_common.cuh"
 
 namespace {
-
-__device__ __forceinline__ unsigned q4k_byte(int k, unsigned s0, unsigned s1, unsigned s2) {
-    unsigned w = k < 4 ? s0 : (k < 8 ? s1 : s2);
-    return (w >> ((k & 3) << 3)) & 0xffu;
-}
-
-// 6-bit scale and minimum of sub-block j from the 12 packed bytes (ggml get_scale_min_k4;
-// backend/cuda/kernels/ks_a1_test.go:62-67).
-__device__ __forceinline__ void q4k_scale_min(int j, unsigned s0, unsigned s1, unsigned s2, int* sc, int* m) {
-    if (j < 4) {
-        *sc = (int)(q4k_byte(j, s0, s1, s2) & 63u);
-        *m = (int)(q4k_byte(j + 4, s0, s1, s2) & 63u);
-    } else {
-        unsigned hi = q4k_byte(j + 4, s0, s1, s2);
-        *sc = (int)((hi & 0x0Fu) | ((q4k_byte(j - 4, s0, s1, s2) >> 6) << 4));
-        *m = (int)((hi >> 4) | ((q4k_byte(j, s0, s1, s2) >> 6) << 4));
-    }
-}
-
-__device__ __forceinline__ float h2f_bits(unsigned short b) { return __half2float(__ushort_as_half(b)); }
 
 #define MAGIC_I 0x4B400000
 #define MAGIC_F 12582912.0f
@@ -107,15 +88,15 @@ __global__ void __launch_bounds__(256) q4k_gemm_mma_kernel(const uint8_t* __rest
         float my_ds[2][2], my_nm[2][2];
         {
             int s, m;
-            const float d0 = h2f_bits((unsigned short)(h0.x & 0xffffu)), dm0 = h2f_bits((unsigned short)(h0.x >> 16));
-            const float d1 = h2f_bits((unsigned short)(h1.x & 0xffffu)), dm1 = h2f_bits((unsigned short)(h1.x >> 16));
-            q4k_scale_min(2 * tig, h0.y, h0.z, h0.w, &s, &m);
+            const float d0 = kq_h2f((unsigned short)(h0.x & 0xffffu)), dm0 = kq_h2f((unsigned short)(h0.x >> 16));
+            const float d1 = kq_h2f((unsigned short)(h1.x & 0xffffu)), dm1 = kq_h2f((unsigned short)(h1.x >> 16));
+            kq_scale_min(2 * tig, h0.y, h0.z, h0.w, &s, &m);
             my_ds[0][0] = __fmul_rn(d0, (float)s); my_nm[0][0] = -__fmul_rn(dm0, (float)m);
-            q4k_scale_min(2 * tig + 1, h0.y, h0.z, h0.w, &s, &m);
+            kq_scale_min(2 * tig + 1, h0.y, h0.z, h0.w, &s, &m);
             my_ds[0][1] = __fmul_rn(d0, (float)s); my_nm[0][1] = -__fmul_rn(dm0, (float)m);
-            q4k_scale_min(2 * tig, h1.y, h1.z, h1.w, &s, &m);
+            kq_scale_min(2 * tig, h1.y, h1.z, h1.w, &s, &m);
             my_ds[1][0] = __fmul_rn(d1, (float)s); my_nm[1][0] = -__fmul_rn(dm1, (float)m);
-            q4k_scale_min(2 * tig + 1, h1.y, h1.z, h1.w, &s, &m);
+            kq_scale_min(2 * tig + 1, h1.y, h1.z, h1.w, &s, &m);
             my_ds[1][1] = __fmul_rn(d1, (float)s); my_nm[1][1] = -__fmul_rn(dm1, (float)m);
         }
 #pragma unroll
@@ -308,15 +289,15 @@ __global__ void __launch_bounds__(256, (NT <= 8 ? 2 : 1)) q4k_gemm_tile_kernel(
             float my_ds[2][2], my_nm[2][2];
             {
                 int s_, m_;
-                const float d0 = h2f_bits((unsigned short)(wc.h0.x & 0xffffu)), dm0 = h2f_bits((unsigned short)(wc.h0.x >> 16));
-                const float d1 = h2f_bits((unsigned short)(wc.h1.x & 0xffffu)), dm1 = h2f_bits((unsigned short)(wc.h1.x >> 16));
-                q4k_scale_min(2 * tig, wc.h0.y, wc.h0.z, wc.h0.w, &s_, &m_);
+                const float d0 = kq_h2f((unsigned short)(wc.h0.x & 0xffffu)), dm0 = kq_h2f((unsigned short)(wc.h0.x >> 16));
+                const float d1 = kq_h2f((unsigned short)(wc.h1.x & 0xffffu)), dm1 = kq_h2f((unsigned short)(wc.h1.x >> 16));
+                kq_scale_min(2 * tig, wc.h0.y, wc.h0.z, wc.h0.w, &s_, &m_);
                 my_ds[0][0] = __fmul_rn(d0, (float)s_); my_nm[0][0] = -__fmul_rn(dm0, (float)m_);
-                q4k_scale_min(2 * tig + 1, wc.h0.y, wc.h0.z, wc.h0.w, &s_, &m_);
+                kq_scale_min(2 * tig + 1, wc.h0.y, wc.h0.z, wc.h0.w, &s_, &m_);
                 my_ds[0][1] = __fmul_rn(d0, (float)s_); my_nm[0][1] = -__fmul_rn(dm0, (float)m_);
-                q4k_scale_min(2 * tig, wc.h1.y, wc.h1.z, wc.h1.w, &s_, &m_);
+                kq_scale_min(2 * tig, wc.h1.y, wc.h1.z, wc.h1.w, &s_, &m_);
                 my_ds[1][0] = __fmul_rn(d1, (float)s_); my_nm[1][0] = -__fmul_rn(dm1, (float)m_);
-                q4k_scale_min(2 * tig + 1, wc.h1.y, wc.h1.z, wc.h1.w, &s_, &m_);
+                kq_scale_min(2 * tig + 1, wc.h1.y, wc.h1.z, wc.h1.w, &s_, &m_);
                 my_ds[1][1] = __fmul_rn(d1, (float)s_); my_nm[1][1] = -__fmul_rn(dm1, (float)m_);
             }
 #pragma unroll
@@ -465,10 +446,10 @@ __global__ void __launch_bounds__(256) q4k_gemv_dp4a_kernel(const uint8_t* __res
 #pragma unroll
             for (int r = 0; r < R; r++) {
                 const uint4 h = hdr[u][r];
-                const float d = h2f_bits((unsigned short)(h.x & 0xffffu)), dmin = h2f_bits((unsigned short)(h.x >> 16));
+                const float d = kq_h2f((unsigned short)(h.x & 0xffffu)), dmin = kq_h2f((unsigned short)(h.x >> 16));
                 int scLo, mLo, scHi, mHi;
-                q4k_scale_min(2 * j, h.y, h.z, h.w, &scLo, &mLo);
-                q4k_scale_min(2 * j + 1, h.y, h.z, h.w, &scHi, &mHi);
+                kq_scale_min(2 * j, h.y, h.z, h.w, &scLo, &mLo);
+                kq_scale_min(2 * j + 1, h.y, h.z, h.w, &scHi, &mHi);
                 const float dsLo = __fmul_rn(d, (float)scLo), dsHi = __fmul_rn(d, (float)scHi);
                 const float nmLo = -__fmul_rn(dmin, (float)mLo), nmHi = -__fmul_rn(dmin, (float)mHi);
                 const uint4 a = q0[u][r], c = q1[u][r];
@@ -624,11 +605,11 @@ __global__ void q4k_dequant_kernel(const uint8_t* __restrict__ W, size_t n_block
     if (blk >= n_blocks) return;
     const uint8_t* b = W + blk * 144;
     const uint4 h = *reinterpret_cast<const uint4*>(b);
-    const float d = h2f_bits((unsigned short)(h.x & 0xffffu)), dmin = h2f_bits((unsigned short)(h.x >> 16));
+    const float d = kq_h2f((unsigned short)(h.x & 0xffffu)), dmin = kq_h2f((unsigned short)(h.x >> 16));
     const int e = threadIdx.x;  // 0..255
     const int j = e >> 5, p = e >> 6, l = e & 31;
     int sc, m;
-    q4k_scale_min(j, h.y, h.z, h.w, &sc, &m);
+    kq_scale_min(j, h.y, h.z, h.w, &sc, &m);
     const uint8_t q = b[16 + 32 * p + l];
     const int code = (j & 1) ? (q >> 4) : (q & 0x0F);
     out[blk * 256 + e] = __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)code), __fmul_rn(dmin, (float)m));

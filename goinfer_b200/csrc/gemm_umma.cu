@@ -34,25 +34,11 @@
 
 #include "common.cuh"
 #include "umma.cuh"
+#include "kq_common.cuh"
 
 namespace {
 
 constexpr int kStages = 3;   // A ring (and barriers); the B ring has 2 stages
-
-__device__ __forceinline__ unsigned q4k_byte_u(int k, unsigned s0, unsigned s1, unsigned s2) {
-    unsigned w = k < 4 ? s0 : (k < 8 ? s1 : s2);
-    return (w >> ((k & 3) << 3)) & 0xffu;
-}
-__device__ __forceinline__ void q4k_scale_min_u(int j, unsigned s0, unsigned s1, unsigned s2, int* sc, int* m) {
-    if (j < 4) {
-        *sc = (int)(q4k_byte_u(j, s0, s1, s2) & 63u);
-        *m = (int)(q4k_byte_u(j + 4, s0, s1, s2) & 63u);
-    } else {
-        unsigned hi = q4k_byte_u(j + 4, s0, s1, s2);
-        *sc = (int)((hi & 0x0Fu) | ((q4k_byte_u(j - 4, s0, s1, s2) >> 6) << 4));
-        *m = (int)((hi >> 4) | ((q4k_byte_u(j, s0, s1, s2) >> 6) << 4));
-    }
-}
 
 // 8 weights of one 16-byte chunk (nibbles of words w0, w1) -> fp16, two at a time in half2 arithmetic. A nibble q is
 // placed at mantissa bits [6,10) of the half 16.0 (0x4C00), which makes the half 16 + q with no int->float conversion, and
@@ -176,7 +162,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                 for (int hf = 0; hf < 2; hf++) {
                     if (NT == 1 && hf != hf1) continue;
                     int sc, mn;
-                    q4k_scale_min_u(2 * p + hf, hdr.y, hdr.z, hdr.w, &sc, &mn);
+                    kq_scale_min(2 * p + hf, hdr.y, hdr.z, hdr.w, &sc, &mn);
                     const __half dsh = __float2half_rn(d * (float)sc);
                     // the offset uses the rounded scale, so that the 16 * scale part cancels exactly
                     const __half2 ds = __half2half2(dsh), c = __float2half2_rn(-(16.f * __half2float(dsh) + dmin * (float)mn));

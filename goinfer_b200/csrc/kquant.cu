@@ -13,6 +13,7 @@
 // The bar is the reference's own for these kernels: |y - f64 product| <= 1e-5 * sum |w*a|
 // (backend/cuda/kernels/kso1c_kernels_test.go:146-151).
 #include "common.cuh"
+#include "kq_common.cuh"
 
 namespace {
 
@@ -26,23 +27,6 @@ __device__ __forceinline__ int kq_dp4a_ss(int a, int b, int c) {
     asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-__device__ __forceinline__ float kq_h2f(unsigned short b) { return __half2float(__ushort_as_half(b)); }
-__device__ __forceinline__ unsigned kq_byte(int k, unsigned s0, unsigned s1, unsigned s2) {
-    const unsigned w = k < 4 ? s0 : (k < 8 ? s1 : s2);
-    return (w >> ((k & 3) << 3)) & 0xffu;
-}
-// 6-bit scale and minimum of sub-block j (ggml get_scale_min_k4)
-__device__ __forceinline__ void kq_scale_min(int j, unsigned s0, unsigned s1, unsigned s2, int* sc, int* m) {
-    if (j < 4) {
-        *sc = (int)(kq_byte(j, s0, s1, s2) & 63u);
-        *m = (int)(kq_byte(j + 4, s0, s1, s2) & 63u);
-    } else {
-        const unsigned hi = kq_byte(j + 4, s0, s1, s2);
-        *sc = (int)((hi & 0x0Fu) | ((kq_byte(j - 4, s0, s1, s2) >> 6) << 4));
-        *m = (int)((hi >> 4) | ((kq_byte(j, s0, s1, s2) >> 6) << 4));
-    }
-}
-
 // Q5_K. Lane: super-block b0 + (lane >> 2) of the row (eight in flight), pair j = lane & 3 (sub-blocks 2j and 2j+1: the low and
 // high nibbles of code bytes 32j .. 32j+31, whose fifth bits are bits 2j and 2j+1 of the 32 qh bytes).
 template <int TT>
