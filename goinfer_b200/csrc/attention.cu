@@ -621,6 +621,152 @@ __global__ void attn_exact_av_kernel(const float* __restrict__ scores, int ld, i
     out[(size_t)r * nH * hd + (size_t)h * hd + d] = (float)acc;
 }
 
+// ---- exact class, tiled: the same arithmetic with the K and V rows read once for the G query heads of a kv head ----
+// Scores. Grid (key tiles of 256, kv heads, rows), 128 threads, two keys a thread (tid and tid + 128 of the tile). The G
+// heads' query rows sit in shared memory as f64; a thread reads its keys' rows 16 bytes at a time and runs G ascending f64
+// chains per key (fused multiply-adds: the f64 value may differ from a separate multiply and add in its last bit, which the
+// rounding to f32 hides except for values within 2^-29 of a rounding boundary).
+template <int HD, int G>
+__global__ void __launch_bounds__(128) attn_exact_scores_tile_kernel(const float* __restrict__ q, int ldq, int nH, int nKV,
+                                                                     const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
+                                                                     const __half* __restrict__ kpool, const int32_t* __restrict__ table,
+                                                                     int max_blocks, int block_rows, float* __restrict__ scores, int ld) {
+    __shared__ double2 qs[G][HD / 2];
+    const int r = blockIdx.z, kvh = blockIdx.y, key0 = blockIdx.x * 256;
+    const int nkeys = min(row_pos[r] + 1, max_blocks * block_rows);
+    if (key0 >= nkeys) return;
+    for (int i = threadIdx.x; i < G * HD / 2; i += 128) {
+        const int g = i / (HD / 2), d2 = i % (HD / 2);
+        const float2 v = *reinterpret_cast<const float2*>(q + (size_t)r * ldq + (size_t)(kvh * G + g) * HD + 2 * d2);
+        qs[g][d2] = make_double2((double)v.x, (double)v.y);
+    }
+    __syncthreads();
+    const int32_t* tbl = table + (size_t)row_slot[r] * max_blocks;
+    const int ka = key0 + threadIdx.x, kb = ka + 128;
+    const bool has_a = ka < nkeys, has_b = kb < nkeys;
+    if (!has_a) return;
+    const int kbc = has_b ? kb : ka;  // a thread without a second key reads its first one twice and drops the result
+    const uint4* ra = reinterpret_cast<const uint4*>(kpool + (((size_t)tbl[ka / block_rows] * nKV + kvh) * block_rows + ka % block_rows) * HD);
+    const uint4* rb = reinterpret_cast<const uint4*>(kpool + (((size_t)tbl[kbc / block_rows] * nKV + kvh) * block_rows + kbc % block_rows) * HD);
+    double acc_a[G], acc_b[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) acc_a[g] = acc_b[g] = 0.0;
+#pragma unroll 2
+    for (int c = 0; c < HD / 8; c++) {
+        const uint4 va = ra[c], vb = rb[c];
+        const __half2* ha = reinterpret_cast<const __half2*>(&va);
+        const __half2* hb = reinterpret_cast<const __half2*>(&vb);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 fa = __half22float2(ha[i]), fb = __half22float2(hb[i]);
+            const double a0 = fa.x, a1 = fa.y, b0 = fb.x, b1 = fb.y;
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const double2 qq = qs[g][4 * c + i];
+                acc_a[g] = fma(qq.x, a0, acc_a[g]);
+                acc_b[g] = fma(qq.x, b0, acc_b[g]);
+                acc_a[g] = fma(qq.y, a1, acc_a[g]);
+                acc_b[g] = fma(qq.y, b1, acc_b[g]);
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        float* s = scores + ((size_t)r * nH + kvh * G + g) * ld;
+        s[ka] = (float)acc_a[g];
+        if (has_b) s[kb] = (float)acc_b[g];
+    }
+}
+
+// Weighted sum of the V rows. Grid (kv heads, rows), 256 threads: thread (dg, kl) owns dims 8*dg .. 8*dg+7 of the G heads and
+// the keys kl, kl + KL, ... of every 256-key chunk, whose weights sit in shared memory as f64. Each thread folds its keys in
+// ascending order in f64; the KL partial sums (KL consecutive lanes of a warp) are then added in a fixed butterfly. (The CPU path folds all keys in one ascending
+// chain: the f64 sums differ in their last bits, the f32 results only where the f64 value lies within 2^-29 of a rounding
+// boundary.)
+template <int HD, int G>
+__global__ void __launch_bounds__(256) attn_exact_av_tile_kernel(const float* __restrict__ w, int ld, int nH, int nKV,
+                                                                 const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos,
+                                                                 const __half* __restrict__ vpool, const int32_t* __restrict__ table,
+                                                                 int max_blocks, int block_rows, float* __restrict__ out) {
+    constexpr int DG = HD / 8, KL = 256 / DG, CH = 256;
+    static_assert(KL <= 32, "the key lanes of a dim group are lanes of one warp");
+    __shared__ double ws[G][CH];
+    const int kvh = blockIdx.x, r = blockIdx.y;
+    const int nkeys = min(row_pos[r] + 1, max_blocks * block_rows);
+    const int kl = threadIdx.x % KL, dg = threadIdx.x / KL;
+    const int32_t* tbl = table + (size_t)row_slot[r] * max_blocks;
+    double acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; g++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[g][j] = 0.0;
+    for (int kc = 0; kc < nkeys; kc += CH) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < G * CH; i += 256) {
+            const int g = i / CH, kk = i % CH;
+            ws[g][kk] = kc + kk < nkeys ? (double)w[((size_t)r * nH + kvh * G + g) * ld + kc + kk] : 0.0;
+        }
+        __syncthreads();
+        const int n = min(CH, nkeys - kc);
+        for (int kk = kl; kk < n; kk += KL) {
+            const int key = kc + kk;
+            const uint4 v = *reinterpret_cast<const uint4*>(vpool + (((size_t)tbl[key / block_rows] * nKV + kvh) * block_rows + key % block_rows) * HD + 8 * dg);
+            const __half2* hv = reinterpret_cast<const __half2*>(&v);
+            double vd[8];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(hv[i]);
+                vd[2 * i] = f.x;
+                vd[2 * i + 1] = f.y;
+            }
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const double wg = ws[g][kk];
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[g][j] = fma(wg, vd[j], acc[g][j]);
+            }
+        }
+    }
+    // fold the KL key lanes
+#pragma unroll
+    for (int off = KL / 2; off >= 1; off >>= 1)
+#pragma unroll
+        for (int g = 0; g < G; g++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[g][j] += __shfl_xor_sync(0xffffffffu, acc[g][j], off);
+    if (kl == 0) {
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            float* o = out + (size_t)r * nH * HD + (size_t)(kvh * G + g) * HD + 8 * dg;
+            *reinterpret_cast<float4*>(o) = make_float4((float)acc[g][0], (float)acc[g][1], (float)acc[g][2], (float)acc[g][3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4((float)acc[g][4], (float)acc[g][5], (float)acc[g][6], (float)acc[g][7]);
+        }
+    }
+}
+
+template <int HD, int G>
+int run_exact_tiled(b200_ctx* ctx, const float* q, int ldq, int T, int nH, int nKV, const int32_t* row_slot, const int32_t* row_pos,
+                    int max_keys, KVView kv, float* scores, int ld, float* out, double scale, double softcap) {
+    {
+        ProfScope ps(ctx, PROF_ATTN_SPLIT);
+        attn_exact_scores_tile_kernel<HD, G><<<dim3(ceil_div(max_keys, 256), nKV, T), 128, 0, ctx->stream>>>(
+            q, ldq, nH, nKV, row_slot, row_pos, kv.k, kv.table, kv.max_blocks, kv.block_rows, scores, ld);
+    }
+    LAUNCH_CHECK(ctx);
+    {
+        ProfScope ps(ctx, PROF_ATTN_COMBINE);
+        attn_exact_softmax_kernel<<<dim3(nH, T), 256, 0, ctx->stream>>>(row_pos, nH, scale, softcap, scores, ld);
+    }
+    LAUNCH_CHECK(ctx);
+    {
+        ProfScope ps(ctx, PROF_OTHER);
+        attn_exact_av_tile_kernel<HD, G><<<dim3(nKV, T), 256, 0, ctx->stream>>>(scores, ld, nH, nKV, row_slot, row_pos, kv.v, kv.table,
+                                                                               kv.max_blocks, kv.block_rows, out);
+    }
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
 template <int HD, int G>
 int run_split(b200_ctx* ctx, const float* q, int ldq, int T, int nH, int nKV, float scale, float cap, const int32_t* row_slot,
               const int32_t* row_pos, int max_keys, KVView kv, AttnScratch sc, float* out, ActQ aq) {
@@ -674,6 +820,25 @@ int launch_paged_attention_exact(b200_ctx* ctx, const float* q, int ldq, int T, 
                                  double softcap, const int32_t* row_slot, const int32_t* row_pos, int max_keys, KVView kv,
                                  float* scores, int ld, float* out, ActQ aq) {
     if (max_keys > ld) B200_FAIL(ctx, B200_BAD_ARGUMENT, "exact attention scratch holds %d keys, %d asked", ld, max_keys);
+    // the usual head shapes: tiled kernels that read a K or V row once for the G heads of its kv head (16-byte row pieces:
+    // the pools and q must be 16- and 8-byte aligned, which the engine's buffers are)
+    const int G = nH / nKV;
+    const bool aligned = (reinterpret_cast<uintptr_t>(kv.k) & 15) == 0 && (reinterpret_cast<uintptr_t>(kv.v) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(q) & 7) == 0 && (ldq & 1) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    static const bool no_tiled = getenv("B200_EXACT_ATTN_PLAIN") != nullptr;
+    if (aligned && !no_tiled) {
+        int st = -1;
+#define EXACT_CASE(HD_, G_) \
+    if (hd == HD_ && G == G_) st = run_exact_tiled<HD_, G_>(ctx, q, ldq, T, nH, nKV, row_slot, row_pos, max_keys, kv, scores, ld, out, scale, softcap)
+        EXACT_CASE(128, 1); EXACT_CASE(128, 2); EXACT_CASE(128, 4); EXACT_CASE(128, 8);
+        EXACT_CASE(64, 1); EXACT_CASE(64, 2); EXACT_CASE(64, 4); EXACT_CASE(64, 8);
+#undef EXACT_CASE
+        if (st >= 0) {
+            if (st != B200_OK) return st;
+            if (aq.codes) return launch_quant_g32(ctx, out, T, nH * hd, aq);
+            return B200_OK;
+        }
+    }
     {
         ProfScope ps(ctx, PROF_ATTN_SPLIT);
         attn_exact_scores_kernel<<<dim3(ceil_div(max_keys, 128), nH, T), 128, 0, ctx->stream>>>(

@@ -225,8 +225,9 @@ int launch_fold_experts(b200_ctx*, const float* eo, const float* wts, const int3
 int launch_softcap(b200_ctx*, float* x, size_t n, float cap);
 
 // gemm.cu
-// dst[T][N] (ld = ldd) = act . W^T for a Q4_K matrix; klass 0 auto, 1 exact, 2 fast.
-int launch_q4k_matmul(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, int klass);
+// dst[T][N] (ld = ldd) = act . W^T for a Q4_K matrix; klass 0 auto, 1 exact, 2 fast. W_tiles: the same matrix tile by tile
+// (launch_q4k_to_tiles) or null; the kernels that stream tiles run only when it is given.
+int launch_q4k_matmul(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, int klass, const uint8_t* W_tiles = nullptr);
 int launch_kq_matmul(b200_ctx*, int kind, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd);  // Q5_K (file blocks) / Q6_K (planes)
 int launch_q6k_to_planes(b200_ctx*, const uint8_t* raw, size_t n_blocks, uint8_t* planes);
 int launch_kq_to_f16(b200_ctx*, int kind, const uint8_t* W, int N, int K, __half* out);  // dequantized fp16 copy [N][K]
@@ -241,6 +242,14 @@ int launch_q4k_matmul_umma(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, i
                            size_t scratch_bytes, int* err_flag);
 int launch_q4k_matmul_umma_swiglu(b200_ctx*, const uint8_t* W_interleaved, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
                                   size_t scratch_bytes, int* err_flag, ActQ swiglu_out, bool force, bool* fused, __half* swiglu_x16 = nullptr);
+int launch_act_to_f16(b200_ctx*, ActQ aq, int T, int K, __half* out);  // the fp16 activation tiles of quantized rows (what the producers otherwise lay out)
+// gemm_small.cu: the fast class's matmul for up to 32 rows (fp16 dequant in registers, mma.sync, weights streamed once);
+// uses the context's scratch like the tcgen05 matmul and takes the producers' activation tiles the same way
+// its weights are kept tile by tile ([row tile of 16][super-block][16 rows][144 B]: launch_q4k_to_tiles, q4k_tiles_bytes)
+int q4k_small_min_rows();
+size_t q4k_tiles_bytes(int N, int K);
+int launch_q4k_to_tiles(b200_ctx*, const uint8_t* row_major, int N, int K, uint8_t* tiles);
+int launch_q4k_matmul_small(b200_ctx*, const uint8_t* W_tiles, int N, int K, ActQ aq, int T, float* dst, int ldd);
 __half* x16_next_slot(b200_ctx*);  // the scratch's other fp16 activation slot (null when the scratch has none)
 int launch_interleave_rows128(b200_ctx*, const uint8_t* gate, const uint8_t* up, int F, size_t row_bytes, uint8_t* out);  // tile t: gate rows 128t.., up rows 128t..
 int launch_f16w_matmul(b200_ctx*, const __half* W, int N, int K, const float* x, int T, float* dst, int ldd,

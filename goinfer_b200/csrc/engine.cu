@@ -29,6 +29,7 @@ struct DevMat {
     DevMat* seg[3] = {nullptr, nullptr, nullptr};  // kKindMixed: the parts, in row order
     int n_seg = 0;
     __half* f16 = nullptr;  // Q5_K / Q6_K, fast class: a dequantized copy for the tensor-core matmul at dense row counts
+    uint8_t* tiles = nullptr;  // Q4_K, fast class: the matrix tile by tile, what the small-batch kernel streams (launch_q4k_to_tiles)
     bool present() const { return kind >= 0 && (p || n_seg > 0); }
 };
 
@@ -450,7 +451,7 @@ int fuse_rows(b200_model* m, std::vector<DevMat*> parts, DevMat* out) {
 // dst[T][N] = x . W^T, picking the kernel by the weight kind
 int matmul(b200_model* m, const DevMat& W, const float* xf, ActQ xq, int T, float* dst, int ldd) {
     b200_ctx* ctx = m->ctx;
-    if (W.kind == B200_K_Q4K) return launch_q4k_matmul(ctx, (const uint8_t*)W.p, W.rows, W.cols, xq, T, dst, ldd, m->c.kernel_class);
+    if (W.kind == B200_K_Q4K) return launch_q4k_matmul(ctx, (const uint8_t*)W.p, W.rows, W.cols, xq, T, dst, ldd, m->c.kernel_class, W.tiles);
     if (is_lane_kind(W.kind)) {
         // from 32 rows in the fast class: fp16 copy of the weights x (code * scale) activations on the tensor cores (the
         // dp4a lane re-reads the matrix for every four rows); the weights are then within 2^-11 of their values
@@ -510,7 +511,8 @@ int run_layers(b200_model* m, int T, int max_keys) {
     // matmul is a plain Q4_K one at a dense row count in the fast class.
     static const bool no_x16_env = getenv("B200_NO_X16_FUSE") != nullptr || getenv("B200_NO_UMMA") != nullptr;
     auto x16_for = [&](const DevMat& W) -> __half* {
-        if (no_x16_env || !m->x16_slot_bytes || W.kind != B200_K_Q4K || T < 33 || c.kernel_class == B200_CLASS_EXACT || (W.cols % 256) ||
+        const int x16_from = q4k_small_min_rows() > 0 ? std::min(33, q4k_small_min_rows()) : 33;  // the small-batch kernel reads the same tiles
+        if (no_x16_env || !m->x16_slot_bytes || W.kind != B200_K_Q4K || T < x16_from || c.kernel_class == B200_CLASS_EXACT || (W.cols % 256) ||
             (size_t)ceil_div(T, 256) * 256 * W.cols * 2 > m->x16_slot_bytes)
             return nullptr;
         return x16_next_slot(ctx);
@@ -919,6 +921,21 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
         // two fp16 activation slots ahead of the partials: producers lay the tiles out for the matmul that follows them
         m->x16_slot_bytes = ((size_t)ceil_div(MR, 256) * 256 * max_k * 2 + 255) & ~(size_t)255;
         m->umma_bytes += m->x16_slot_bytes;
+        // Q4_K projections: a tile-by-tile copy for the small-batch kernel (up to 32 rows)
+        if (q4k_small_min_rows() > 0) {
+            for (int l = 0; l < c.n_layers; l++) {
+                LayerW& L = m->layers[l];
+                for (DevMat* d : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down, &L.qkv, &L.gu})
+                    if (d->p && d->kind == B200_K_Q4K && d->cols % 256 == 0) {
+                        ST_TRY(m->dalloc((void**)&d->tiles, q4k_tiles_bytes(d->rows, d->cols), &m->weight_bytes));
+                        ST_TRY(launch_q4k_to_tiles(ctx, (const uint8_t*)d->p, d->rows, d->cols, d->tiles));
+                    }
+            }
+            if (m->head.p && m->head.kind == B200_K_Q4K && m->head.cols % 256 == 0) {
+                ST_TRY(m->dalloc((void**)&m->head.tiles, q4k_tiles_bytes(m->head.rows, m->head.cols), &m->weight_bytes));
+                ST_TRY(launch_q4k_to_tiles(ctx, (const uint8_t*)m->head.p, m->head.rows, m->head.cols, m->head.tiles));
+            }
+        }
         // Q5_K / Q6_K tensors: fp16 copies for the tensor-core matmul from 32 rows on
         std::vector<DevMat*> kq;
         for (int l = 0; l < c.n_layers; l++) {

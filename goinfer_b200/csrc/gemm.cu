@@ -716,16 +716,25 @@ int run_q4k(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, int T, flo
 
 }  // namespace
 
-int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, int klass) {
+int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, int klass, const uint8_t* W_tiles) {
     if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
     const int nSB = K / 256;
     // Fast class from 33 rows (or when asked for by klass 2): tcgen05 fp16 matmul, if its scratch is in place. (Measured:
     // at 45 rows it takes 111 us on a 28672x8192 matrix against 214 us for the integer kernels; below 33 rows the
     // streaming integer kernel is the faster one.)
     static const bool no_umma_env = getenv("B200_NO_UMMA") != nullptr;
-    if (klass != B200_CLASS_EXACT && klass != 3 && klass != 4 && (T >= 33 || klass == 2) && ctx->umma_scratch && !no_umma_env &&
+    if (klass != B200_CLASS_EXACT && klass != 3 && klass != 4 && klass != 5 && klass != 6 && (T >= 33 || klass == 2) && ctx->umma_scratch && !no_umma_env &&
         q4k_umma_scratch_bytes(T, K, N) <= ctx->umma_scratch_bytes)
         return launch_q4k_matmul_umma(ctx, W, N, K, aq, T, dst, ldd, ctx->umma_scratch, ctx->umma_scratch_bytes, ctx->err_flag);
+    // Fast class, up to 32 rows (klass 5 forces it): fp16 dequant in registers + mma.sync, the weights streamed once
+    {
+        const int small_min = q4k_small_min_rows();
+        const bool fast = klass == 0 || klass == 2;
+        if (W_tiles && (klass == 5 || (fast && small_min > 0 && T >= small_min)) && T <= 32 && ctx->umma_scratch && !no_umma_env &&
+            q4k_umma_scratch_bytes(T, K, N) <= ctx->umma_scratch_bytes)
+            return launch_q4k_matmul_small(ctx, W_tiles, N, K, aq, T, dst, ldd);
+        if (klass == 5) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the small-batch Q4_K matmul needs the tiled weights, 1..32 rows and the fast class's scratch");
+    }
     // Rows up to 8 are HBM-bound: split K over the CTA's warps (unless the exact class asks for the one ascending
     // chain per output that every larger batch uses, so a row's bits do not depend on its batch).
     if (T <= 8 && klass == B200_CLASS_EXACT) return run_q4k<1, false>(ctx, W, N, nSB, aq, T, dst, ldd);
@@ -736,7 +745,7 @@ int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, in
     // 4..63 rows, fast class: the weights stream through a TMA ring (klass 3 forces the older kernels for comparison)
     static const bool no_stream = getenv("B200_NO_STREAM") != nullptr;
     if (T <= 63 && klass != B200_CLASS_EXACT && klass != 3 && !no_stream && (reinterpret_cast<uintptr_t>(W) & 15) == 0)
-        return launch_q4k_matmul_stream(ctx, W, N, K, aq, T, dst, ldd, klass != 4);  // klass 4: the one-chain form (the exact class's bits)
+        return launch_q4k_matmul_stream(ctx, W, N, K, aq, T, dst, ldd, klass != 4);  // klass 4: the one-chain form (the exact class's bits); 6: split
     if (T <= 8) return run_q4k<1, true>(ctx, W, N, nSB, aq, T, dst, ldd);
     if (T <= 16) return run_q4k<2, false>(ctx, W, N, nSB, aq, T, dst, ldd);
     if (T <= 32) return run_q4k_tile<4>(ctx, W, N, nSB, aq, T, dst, ldd);

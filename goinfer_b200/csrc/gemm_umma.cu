@@ -432,6 +432,14 @@ const CUtensorMap* q4k_weight_map(b200_ctx* ctx, const uint8_t* W, int N, int nS
     return m;
 }
 
+// fp16(code * scale) of the quantized activation rows, in the tile layout the fast-class matmuls read
+int launch_act_to_f16(b200_ctx* ctx, ActQ aq, int T, int K, __half* out) {
+    dim3 grid(ceil_div(K / 8, 256), T);
+    launch_pdl(act_to_f16_kernel, grid, dim3(256), 0, ctx->stream, aq.codes, aq.scales, K, out);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
 size_t q4k_umma_scratch_bytes(int max_rows, int max_k, int max_n) {
     // fp16 activations + split-K partials (up to 4 splits)
     return (size_t)ceil_div(max_rows, 256) * 256 * max_k * 2 + (size_t)4 * max_rows * max_n * 4 + 256;
@@ -488,9 +496,7 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
     const __half* x16 = slots ? ctx->x16_ready : nullptr;  // laid out by the kernel that quantized these activations
     if (!x16) {
         __half* mine = slots ? x16_next_slot(ctx) : reinterpret_cast<__half*>(scratch);
-        dim3 grid(ceil_div(K / 8, 256), T);
-        launch_pdl(act_to_f16_kernel, grid, dim3(256), 0, ctx->stream, aq.codes, aq.scales, K, mine);
-        LAUNCH_CHECK(ctx);
+        ST_TRY(launch_act_to_f16(ctx, aq, T, K, mine));
         x16 = mine;
     }
     if (sw_x16 && sw_x16 == x16) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the epilogue's activation slot is the one this matmul reads");

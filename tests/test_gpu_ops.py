@@ -70,12 +70,12 @@ def test_q4k_matmul_exact_class(ops, oracle_lib, M):
     ref = oracle_lib.op_q4k_matmul_f64(raw, a, N)
     scale = np.abs(ref).max()
     assert np.abs(got - ref).max() <= 1e-5 * scale          # the reference's own GEMV bar
-    fast = ops.q4k_matmul(raw, a, N, klass=0)               # fast class: integer kernels up to 32 rows, tcgen05 fp16 from 33
-    if M <= 32:
+    fast = ops.q4k_matmul(raw, a, N, klass=0)               # fast class: the dp4a lanes up to three rows, fp16 tensor-core kernels from four
+    if M <= 3:
         assert np.abs(fast - ref).max() <= 1e-5 * scale
         assert np.abs(fast - want).max() <= 2e-6 * scale
     else:
-        assert np.abs(fast - ref).max() <= 4e-3 * scale     # tcgen05 fp16 operands
+        assert np.abs(fast - ref).max() <= 4e-3 * scale     # fp16 operands (mma.sync up to 32 rows, tcgen05 above)
 
 
 @pytest.mark.parametrize("M,N,K", [(33, 192, 512), (64, 256, 1024), (128, 384, 512), (200, 200, 1024), (256, 512, 2048), (300, 128, 256), (256, 640, 4096)])
@@ -101,8 +101,8 @@ def test_q4k_matmul_fast_class_tcgen05(ops, oracle_lib, M, N, K):
 @pytest.mark.parametrize("M", [4, 7, 8, 9, 16, 17, 31, 32, 33, 45, 63])
 def test_q4k_matmul_streaming_kernel(ops, oracle_lib, M):
     """The kernel for 4..63 rows streams weights and activation rows through a TMA ring and keeps the exact class's
-    arithmetic. In its one-chain form (klass 4; also what the routed experts run) its bits are the oracle's. The fast
-    class splits K between two groups of warps (and between CTAs for narrow matrices) and adds the chains in a fixed
+    arithmetic. In its one-chain form (klass 4; also what the routed experts run) its bits are the oracle's. Its split form
+    (klass 6) divides K between two groups of warps (and between CTAs for narrow matrices) and adds the chains in a fixed
     order: within f32 rounding of the oracle."""
     rng = np.random.default_rng(40 + M)
     for N, K in ((448 * 64 + 20, 512), (100, 4096), (192, 1024)):
@@ -112,10 +112,11 @@ def test_q4k_matmul_streaming_kernel(ops, oracle_lib, M):
         want = oracle_lib.op_q4k_matmul(raw, a, N)
         one_chain = ops.q4k_matmul(raw, a, N, klass=4)
         assert np.array_equal(want.view(np.uint32), one_chain.view(np.uint32))
-        fast = ops.q4k_matmul(raw, a, N, klass=0)
-        # up to 32 rows the fast class runs this kernel (K split between CTAs for narrow matrices); from 33 the tcgen05 one
-        assert np.abs(fast - want).max() <= (2e-6 if M <= 32 else 4e-3) * np.abs(want).max()
-        assert np.array_equal(fast, ops.q4k_matmul(raw, a, N, klass=0))     # a fixed order: the same bits every time
+        split = ops.q4k_matmul(raw, a, N, klass=6)
+        # klass 6: this kernel with K split between two groups of warps (and between CTAs for narrow matrices), the chains
+        # added in a fixed order: within f32 rounding of the oracle
+        assert np.abs(split - want).max() <= 2e-6 * np.abs(want).max()
+        assert np.array_equal(split, ops.q4k_matmul(raw, a, N, klass=6))     # a fixed order: the same bits every time
 
 
 def test_q4k_matmul_saturated_and_random_bytes(ops, oracle_lib):
@@ -143,10 +144,13 @@ def test_q4k_batch_rows_equal_single_rows_within_class(ops):
     full = ops.q4k_matmul(raw, a, N, klass=1)
     for r in range(8):
         assert np.array_equal(full[r], ops.q4k_matmul(raw, a[r:r + 1], N, klass=1)[0])
-    # the fast class runs other kernels at 1-3 rows than at 4-8: equal to rounding, not to the bit
+    # the fast class runs other kernels at 1-3 rows (integer dots) than at 4-32 (fp16 operands): equal to the fp16 tolerance
     fast = ops.q4k_matmul(raw, a, N, klass=0)
     for r in range(8):
-        np.testing.assert_allclose(fast[r], ops.q4k_matmul(raw, a[r:r + 1], N, klass=0)[0], atol=2e-6 * np.abs(full).max(), rtol=0)
+        np.testing.assert_allclose(fast[r], ops.q4k_matmul(raw, a[r:r + 1], N, klass=0)[0], atol=4e-3 * np.abs(full).max(), rtol=0)
+    # within the small-batch kernel a row's bits do not depend on the rows beside it (each token is its own MMA column)
+    for n in (4, 5, 8):
+        assert np.array_equal(fast[:n], ops.q4k_matmul(raw, a[:n], N, klass=5)), n
     b = rng.normal(0, 1, (40, K)).astype(np.float32)
     big = ops.q4k_matmul(raw, b, N, klass=1)
     assert np.array_equal(big[:12], ops.q4k_matmul(raw, b[:12], N, klass=1))
@@ -481,3 +485,29 @@ def test_a_bounded_device_wait_that_runs_out_reports_timeout_and_the_context_sta
     finally:
         assert ops.lib.b200_debug_wait_fault(ops.ctx, 0, -1) == abi.OK
     np.testing.assert_allclose(ops.f16_matmul(w, a, klass=2), want, atol=2e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 7, 8, 9, 16, 17, 25, 32])
+def test_q4k_matmul_small_batch_kernel(ops, oracle_lib, M):
+    """The fast class's kernel for up to 32 rows (klass 5 forces it; klass 0 picks it from 4 rows): the matrix re-laid tile by
+    tile, raw super-blocks through per-warp rings of bulk copies, nibbles to fp16 in registers, mma.sync m16n8k16 with fp32
+    accumulation, the minimum term as its own small product, the activation tiles in the layout the quantizing kernels write.
+    Against the f64 value of the exact formula: the tcgen05 matmul's tolerance (both round the sub-block scale and the
+    activations to fp16). Shapes: ragged row counts (rows past N are zero blocks), one super-block, an odd count of
+    super-blocks, a K long enough to be split into ranges, a tall matrix."""
+    rng = np.random.default_rng(70 + M)
+    for N, K in ((100, 256), (448 * 64 + 20, 512), (192, 4096), (1000, 768), (4096, 2048)):
+        raw = q4k.quantize(rng.normal(0, 0.02, (N, K)).astype(np.float32))
+        a = rng.normal(0, 1, (M, K)).astype(np.float32)
+        a[M - 1, 32:64] = 0
+        if M > 2:
+            a[1, 5] = 40.0                                 # an activation outlier
+        ref = oracle_lib.op_q4k_matmul_f64(raw, a, N)
+        got = ops.q4k_matmul(raw, a, N, klass=5)
+        scale = np.abs(ref).max()
+        assert np.abs(got - ref).max() <= 4e-3 * scale, (N, K, np.abs(got - ref).max() / scale)
+        rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+        assert rel <= 2.5e-3, (N, K, rel)
+        assert np.array_equal(got, ops.q4k_matmul(raw, a, N, klass=5))      # K ranges are added in a fixed order
+        if M >= 4:
+            assert np.array_equal(got, ops.q4k_matmul(raw, a, N, klass=0))  # what the fast class picks at these row counts
