@@ -75,10 +75,29 @@ __device__ __forceinline__ unsigned prmt(unsigned a, unsigned b, unsigned sel) {
     return r;
 }
 
+// (w & mask) | magic in one LOP3: both constants must sit in registers for that (as immediates the compiler spends two
+// instructions per nibble pair, and this is the kernel's hottest line), so they are handed over as opaque values
+__device__ __forceinline__ unsigned and_or(unsigned w, unsigned mask, unsigned magic) {
+    unsigned r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w), "r"(mask), "r"(magic));
+    return r;
+}
+__device__ __forceinline__ unsigned opaque(unsigned v) {
+    unsigned r;
+    asm volatile("mov.u32 %0, %1;" : "=r"(r) : "r"(v));
+    return r;
+}
+struct NibbleConsts {
+    unsigned mask_lo, magic_lo, mask_hi, magic_hi;   // 0x000F000F | 1024.0 halves; 0x00F000F0 | 64.0 halves
+};
 // low nibbles of bytes 0 and 2 of w -> {q0, q2} * ds (the half 1024 + q, times ds, minus 1024 ds: one rounding)
-__device__ __forceinline__ unsigned deq_lo(unsigned w, __half2 ds, __half2 c) { return as_u32(__hfma2(as_h2((w & 0x000F000Fu) | 0x64006400u), ds, c)); }
+__device__ __forceinline__ unsigned deq_lo(unsigned w, __half2 ds, __half2 c, const NibbleConsts& k) {
+    return as_u32(__hfma2(as_h2(and_or(w, k.mask_lo, k.magic_lo)), ds, c));
+}
 // high nibbles of bytes 0 and 2 (the half 64 + q)
-__device__ __forceinline__ unsigned deq_hi(unsigned w, __half2 ds, __half2 c) { return as_u32(__hfma2(as_h2((w & 0x00F000F0u) | 0x54005400u), ds, c)); }
+__device__ __forceinline__ unsigned deq_hi(unsigned w, __half2 ds, __half2 c, const NibbleConsts& k) {
+    return as_u32(__hfma2(as_h2(and_or(w, k.mask_hi, k.magic_hi)), ds, c));
+}
 
 struct RowScales {
     __half2 ds_lo, c_lo, ds_hi, c_hi;  // sub-block 2p: scale and -1024 * scale; sub-block 2p+1: scale and -64 * scale
@@ -216,6 +235,7 @@ __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t*
     unsigned asum[kSbw][NT], asum_next[kSbw][NT];
     load_asum(0, asum_next);
 
+    const NibbleConsts kc{opaque(0x000F000Fu), opaque(0x64006400u), opaque(0x00F000F0u), opaque(0x54005400u)};
     int done = 0, ws = 0, as = 0;
     unsigned wph = 0, aph = 0;   // ring positions and the phase parities of their barriers
 #pragma unroll 1
@@ -275,14 +295,14 @@ __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t*
                         const unsigned w0 = wq[mt][0][2 * jj + hw], w1 = wq[mt][1][2 * jj + hw];
                         const unsigned w0s = w0 >> 8, w1s = w1 >> 8;   // bytes 1 and 3 where bytes 0 and 2 were
                         {   // low nibbles: sub-block 2p
-                            const unsigned a0 = deq_lo(w0, rs[mt][0].ds_lo, rs[mt][0].c_lo), a1 = deq_lo(w1, rs[mt][1].ds_lo, rs[mt][1].c_lo);
-                            const unsigned a2 = deq_lo(w0s, rs[mt][0].ds_lo, rs[mt][0].c_lo), a3 = deq_lo(w1s, rs[mt][1].ds_lo, rs[mt][1].c_lo);
+                            const unsigned a0 = deq_lo(w0, rs[mt][0].ds_lo, rs[mt][0].c_lo, kc), a1 = deq_lo(w1, rs[mt][1].ds_lo, rs[mt][1].c_lo, kc);
+                            const unsigned a2 = deq_lo(w0s, rs[mt][0].ds_lo, rs[mt][0].c_lo, kc), a3 = deq_lo(w1s, rs[mt][1].ds_lo, rs[mt][1].c_lo, kc);
 #pragma unroll
                             for (int nt = 0; nt < NT; nt++) mma_f16(acc[mt][nt], a0, a1, a2, a3, hw ? bl[nt].z : bl[nt].x, hw ? bl[nt].w : bl[nt].y);
                         }
                         {   // high nibbles: sub-block 2p + 1
-                            const unsigned a0 = deq_hi(w0, rs[mt][0].ds_hi, rs[mt][0].c_hi), a1 = deq_hi(w1, rs[mt][1].ds_hi, rs[mt][1].c_hi);
-                            const unsigned a2 = deq_hi(w0s, rs[mt][0].ds_hi, rs[mt][0].c_hi), a3 = deq_hi(w1s, rs[mt][1].ds_hi, rs[mt][1].c_hi);
+                            const unsigned a0 = deq_hi(w0, rs[mt][0].ds_hi, rs[mt][0].c_hi, kc), a1 = deq_hi(w1, rs[mt][1].ds_hi, rs[mt][1].c_hi, kc);
+                            const unsigned a2 = deq_hi(w0s, rs[mt][0].ds_hi, rs[mt][0].c_hi, kc), a3 = deq_hi(w1s, rs[mt][1].ds_hi, rs[mt][1].c_hi, kc);
 #pragma unroll
                             for (int nt = 0; nt < NT; nt++)
                                 mma_f16(kTwoAcc ? acc2[kTwoAcc ? mt : 0][kTwoAcc ? nt : 0] : acc[mt][nt], a0, a1, a2, a3, hw ? bh[nt].z : bh[nt].x,
@@ -406,13 +426,12 @@ int run_small(b200_ctx* ctx, const uint8_t* W, int N, int nSB, const __half* x16
 }  // namespace
 
 // The row count from which the fast class takes this kernel. Below it the dp4a lanes are faster (their work grows with the
-// row count, this kernel's is that of eight rows at any count up to eight): measured on 24576 x 4096, 17.7 against 23.1 us
-// at two rows, 23.3 against 28.9 us (the integer streaming kernel) at four. B200_SMALL_MIN_ROWS overrides it for comparisons;
-// 0 turns the kernel off.
+// row count, this kernel's is that of eight rows at any count up to eight): measured on 151936 x 4096, 88 us (dp4a) against
+// 99 us at two rows, 164 us against 99 us at three. B200_SMALL_MIN_ROWS overrides it for comparisons; 0 turns the kernel off.
 int q4k_small_min_rows() {
     static const int v = [] {
         const char* e = getenv("B200_SMALL_MIN_ROWS");
-        return e ? atoi(e) : 4;
+        return e ? atoi(e) : 3;
     }();
     return v;
 }

@@ -30,7 +30,7 @@ def build_pair(oracle_lib, shape_name, n_slots=4, ctx_cap=256, seed=0, n_layers=
 
 
 def fast_class_close(a, b):
-    """The bars a shallow model in the fast class is held to where its matmuls run with fp16 operands (from two rows on): the
+    """The bars a shallow model in the fast class is held to where its matmuls run with fp16 operands (from three rows on): the
     reference's own GPU-vs-CPU bars, tightened (cosine >= 0.9995, relative L2 <= 0.03), and a max-abs error of a few
     hundredths on logits of order one. -> (ok, description)"""
     a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
@@ -178,7 +178,7 @@ def test_fast_class_meets_the_reference_gpu_vs_cpu_bars(oracle_lib):
 def test_fast_class_prefill_run_kernel_in_a_ragged_step(oracle_lib, monkeypatch):
     """The fast class sends a step's leading prefill chunk through the tiled causal kernel and the rows behind it through
     flash-decode. A chunked prompt with decode rows riding along must land within the fast class's bars of the oracle (its
-    matmuls run with fp16 operands from four rows on), and so must the same steps run with the tiled kernel switched off
+    matmuls run with fp16 operands from three rows on), and so must the same steps run with the tiled kernel switched off
     (every row a flash-decode row)."""
     import os
     outs = {}
@@ -407,7 +407,7 @@ def test_q4_k_m_like_model_with_q5k_and_q6k_parts(oracle_lib, klass, tmp_path):
             r.upload(which, arr, layer, expert, kind, rows, cols)
     g.finalize()
     o.finalize()
-    # exact class: the build's logit bar; fast class: fp16-operand matmuls from two rows on, held to the bars of fast_class_close
+    # exact class: the build's logit bar; fast class: fp16-operand matmuls from three rows on, held to the bars of fast_class_close
     close = close_logits if klass == abi.CLASS_EXACT else fast_class_close
     rng = np.random.default_rng(2)
     prompts = [rng.integers(0, s.vocab, n).tolist() for n in (21, 5)]

@@ -70,8 +70,8 @@ def test_q4k_matmul_exact_class(ops, oracle_lib, M):
     ref = oracle_lib.op_q4k_matmul_f64(raw, a, N)
     scale = np.abs(ref).max()
     assert np.abs(got - ref).max() <= 1e-5 * scale          # the reference's own GEMV bar
-    fast = ops.q4k_matmul(raw, a, N, klass=0)               # fast class: the dp4a lanes up to three rows, fp16 tensor-core kernels from four
-    if M <= 3:
+    fast = ops.q4k_matmul(raw, a, N, klass=0)               # fast class: the dp4a lanes up to two rows, fp16 tensor-core kernels from three
+    if M <= 2:
         assert np.abs(fast - ref).max() <= 1e-5 * scale
         assert np.abs(fast - want).max() <= 2e-6 * scale
     else:
@@ -144,7 +144,7 @@ def test_q4k_batch_rows_equal_single_rows_within_class(ops):
     full = ops.q4k_matmul(raw, a, N, klass=1)
     for r in range(8):
         assert np.array_equal(full[r], ops.q4k_matmul(raw, a[r:r + 1], N, klass=1)[0])
-    # the fast class runs other kernels at 1-3 rows (integer dots) than at 4-32 (fp16 operands): equal to the fp16 tolerance
+    # the fast class runs other kernels at 1-2 rows (integer dots) than at 3-32 (fp16 operands): equal to the fp16 tolerance
     fast = ops.q4k_matmul(raw, a, N, klass=0)
     for r in range(8):
         np.testing.assert_allclose(fast[r], ops.q4k_matmul(raw, a[r:r + 1], N, klass=0)[0], atol=4e-3 * np.abs(full).max(), rtol=0)
@@ -489,7 +489,7 @@ def test_a_bounded_device_wait_that_runs_out_reports_timeout_and_the_context_sta
 
 @pytest.mark.parametrize("M", [1, 2, 3, 7, 8, 9, 16, 17, 25, 32])
 def test_q4k_matmul_small_batch_kernel(ops, oracle_lib, M):
-    """The fast class's kernel for up to 32 rows (klass 5 forces it; klass 0 picks it from 4 rows): the matrix re-laid tile by
+    """The fast class's kernel for up to 32 rows (klass 5 forces it; klass 0 picks it from 3 rows): the matrix re-laid tile by
     tile, raw super-blocks through per-warp rings of bulk copies, nibbles to fp16 in registers, mma.sync m16n8k16 with fp32
     accumulation, the minimum term as its own small product, the activation tiles in the layout the quantizing kernels write.
     Against the f64 value of the exact formula: the tcgen05 matmul's tolerance (both round the sub-block scale and the
@@ -509,5 +509,5 @@ def test_q4k_matmul_small_batch_kernel(ops, oracle_lib, M):
         rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
         assert rel <= 2.5e-3, (N, K, rel)
         assert np.array_equal(got, ops.q4k_matmul(raw, a, N, klass=5))      # K ranges are added in a fixed order
-        if M >= 4:
+        if M >= 3:
             assert np.array_equal(got, ops.q4k_matmul(raw, a, N, klass=0))  # what the fast class picks at these row counts
