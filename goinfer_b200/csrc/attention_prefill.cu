@@ -11,6 +11,8 @@
 //   O[16][HD] += P V              P = the S accumulators re-used as the A fragment, split hi + lo as well
 // The walk is flash-attention style, one pass over the keys, nothing written but the final rows. The arithmetic is the
 // decode kernel's (same splits, same fp32 softmax); only the grouping of rows differs.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -235,6 +237,11 @@ int launch_prefill_attention(b200_ctx* ctx, const float* q, int ldq, int nrows, 
                              float softcap, int slot, int pos0, KVView kv, float* out, int ldo) {
     if (nrows <= 0) return B200_OK;
     const int G = nH / nKV;
+    // long runs: the tcgen05 kernel (128 rows of a head per CTA)
+    static const bool no_umma = getenv("B200_NO_UMMA") != nullptr || getenv("B200_NO_PREFILL_UMMA") != nullptr;
+    if (!no_umma && nrows >= prefill_umma_min_rows() &&
+        prefill_attention_umma_supported(nH, nKV, hd, kv.block_rows, q, ldq, kv.k, kv.v, out, ldo))
+        return launch_prefill_attention_umma(ctx, q, ldq, nrows, nH, nKV, hd, scale, softcap, slot, pos0, kv, out, ldo, prefill_umma_precision());
     const int32_t* tbl = kv.table + (size_t)slot * kv.max_blocks;
 #define PF_CASE(HD_, G_) \
     if (hd == HD_ && G == G_) return run_prefill<HD_, G_>(ctx, q, ldq, nrows, nH, nKV, scale, softcap, pos0, tbl, kv, out, ldo)

@@ -302,6 +302,14 @@ int tp_all_gather_columns(b200_ctx*, const float* local, int rows, int w, float*
 bool prefill_attention_supported(int nH, int nKV, int hd, int block_rows);
 int launch_prefill_attention(b200_ctx*, const float* q, int ldq, int nrows, int nH, int nKV, int hd, float scale, float softcap,
                              int slot, int pos0, KVView kv, float* out, int ldo);
+// attention_prefill_umma.cu: the same for long runs on tcgen05 (precision: 0 = Q and P in single fp16, 1 = Q as fp16 hi + lo,
+// 2 = Q and P as hi + lo)
+int prefill_umma_min_rows();
+int prefill_umma_precision();
+bool prefill_attention_umma_supported(int nH, int nKV, int hd, int block_rows, const void* q, int ldq, const void* kpool, const void* vpool,
+                                      const void* out, int ldo);
+int launch_prefill_attention_umma(b200_ctx*, const float* q, int ldq, int nrows, int nH, int nKV, int hd, float scale, float softcap, int slot,
+                                  int pos0, KVView kv, float* out, int ldo, int precision);
 
 // exact class: f64 arithmetic in the CPU path's own order; scores is [T*nH][ld] f32 scratch, ld >= max_keys
 int launch_paged_attention_exact(b200_ctx*, const float* q, int ldq, int T, int nH, int nKV, int hd, double scale,

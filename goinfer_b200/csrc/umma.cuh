@@ -39,6 +39,24 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
     return false;
 }
 
+// The same bounded wait, polling with test_wait (which never suspends the thread): for hand-offs on a kernel's critical path
+// between a few warps, where the time a suspended thread takes to come back shows in every tile.
+__device__ __forceinline__ bool mbar_wait_spin(unsigned bar, unsigned parity, volatile int* abort_flag = nullptr, int polls = kWaitPolls * 16) {
+    for (int i = 0; i < polls; i++) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((i & 63) == 63 && abort_flag && *abort_flag) return false;
+    }
+    return false;
+}
+
 // K-major, 128-byte swizzle, 8-row groups 1024 bytes apart (cute/arch/mma_sm100_desc.hpp SmemDescriptor: start>>4 [0,14),
 // LBO>>4 [16,30), SBO>>4 [32,46), version 1 at [46,48), layout type SWIZZLE_128B = 2 at [61,64)).
 __device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) {

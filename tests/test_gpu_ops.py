@@ -333,8 +333,19 @@ def test_paged_attention_matches_the_f64_oracle(ops, oracle_lib, nH, nKV, hd):
     np.testing.assert_allclose(ops.attention(q, k, v, n_keys, nH, nKV, hd, scale, 0.0, block_rows=64, klass=1), want0, atol=0, rtol=3e-7)
 
 
+def _tcgen05_prefill_bar(got, want):
+    """Runs of 128 rows and more go through the tcgen05 kernel, whose operands (Q, K, V and the softmax weights) are single
+    fp16 values with fp32 accumulation and fp32 softmax: relative L2 5e-4 and max |error| 1e-3 on unit-variance data
+    (measured: 2.6e-4 and 6.8e-4)."""
+    assert np.isfinite(got).all()
+    rel = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want)
+    assert rel <= 5e-4, rel
+    assert np.abs(got - want).max() <= 1e-3, np.abs(got - want).max()
+
+
 @pytest.mark.parametrize("nH,nKV,hd", [(32, 8, 128), (32, 4, 64), (4, 2, 64), (8, 8, 128), (16, 2, 128)])
-@pytest.mark.parametrize("rows,pos0,block_rows", [(16, 0, 16), (37, 0, 16), (45, 83, 16), (33, 500, 64), (130, 7, 16)])
+@pytest.mark.parametrize("rows,pos0,block_rows", [(16, 0, 16), (37, 0, 16), (45, 83, 16), (33, 500, 64), (130, 7, 16), (128, 0, 16), (300, 77, 16),
+                                                  (257, 500, 64)])
 def test_prefill_attention_matches_the_f64_oracle(ops, oracle_lib, nH, nKV, hd, rows, pos0, block_rows):
     """A run of rows at consecutive positions of one sequence (a prefill chunk): row j sees keys 0..pos0+j. The oracle is the
     CPU path's per-row attention given each row its own key count; tile edges (16 rows, 32 keys), block edges and a chunk
@@ -351,7 +362,10 @@ def test_prefill_attention_matches_the_f64_oracle(ops, oracle_lib, nH, nKV, hd, 
     for cap in (0.0, 30.0):
         want = oracle_lib.op_attention(q, kk, vv, n_keys, nH, nKV, hd, scale, cap)
         got = ops.prefill_attention(q, k, v, pos0, nH, nKV, hd, scale, cap, block_rows=block_rows)
-        np.testing.assert_allclose(got, want, atol=2e-5, rtol=1e-4)   # fast class: fp32 online softmax vs f64
+        if rows < 128:
+            np.testing.assert_allclose(got, want, atol=2e-5, rtol=1e-4)   # mma.sync kernel, hi + lo operands: fp32 online softmax vs f64
+        else:
+            _tcgen05_prefill_bar(got, want)
 
 
 def test_prefill_attention_properties_at_chunk_size(ops):
@@ -373,15 +387,15 @@ def test_prefill_attention_properties_at_chunk_size(ops):
     np.testing.assert_allclose(o2, 2 * o1, atol=1e-5, rtol=1e-5)
     # the first 1000 rows of the run, computed without the later keys present at all, are the same rows
     short = ops.prefill_attention(q[:1000], k[:pos0 + 1000], v1[:pos0 + 1000], pos0, nH, nKV, hd)
-    assert np.array_equal(short[:992], o1[:992])        # whole 16-row tiles see identical key tiles
-    np.testing.assert_allclose(short[992:], o1[992:1000], atol=1e-6, rtol=1e-5)
+    assert np.array_equal(short[:896], o1[:896])        # whole 128-row tiles see identical key tiles
+    np.testing.assert_allclose(short[896:], o1[896:1000], atol=1e-6, rtol=1e-5)
     # and a prefill row agrees with the flash-decode kernel's row for the same query
     pick = np.array([0, 511, 2047])
     n_keys = (pos0 + 1 + pick).astype(np.int32)
     kk = np.broadcast_to(k, (3,) + k.shape)
     vv = np.broadcast_to(v1, (3,) + v1.shape)
     dec = ops.attention(q[pick], kk, vv, n_keys, nH, nKV, hd)
-    np.testing.assert_allclose(o1[pick], dec, atol=2e-5, rtol=1e-4)
+    np.testing.assert_allclose(o1[pick], dec, atol=1e-3, rtol=0)    # the tcgen05 kernel's bar (the decode kernel is at fp32 level)
 
 
 def test_attention_properties_at_full_context(ops):
