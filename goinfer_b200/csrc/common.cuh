@@ -228,8 +228,8 @@ int launch_softcap(b200_ctx*, float* x, size_t n, float cap);
 // dst[T][N] (ld = ldd) = act . W^T for a Q4_K matrix; klass 0 auto, 1 exact, 2 fast. W_tiles: the same matrix tile by tile
 // (launch_q4k_to_tiles) or null; the kernels that stream tiles run only when it is given.
 int launch_q4k_matmul(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, int klass, const uint8_t* W_tiles = nullptr);
-int launch_kq_matmul(b200_ctx*, int kind, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd);  // Q5_K (file blocks) / Q6_K (planes)
-int launch_q6k_to_planes(b200_ctx*, const uint8_t* raw, size_t n_blocks, uint8_t* planes);
+int launch_kq_matmul(b200_ctx*, int kind, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd);  // Q5_K (file blocks) / Q6_K (bodies + d: launch_q6k_repack)
+int launch_q6k_repack(b200_ctx*, const uint8_t* raw, size_t n_blocks, uint8_t* planes);
 int launch_kq_to_f16(b200_ctx*, int kind, const uint8_t* W, int N, int K, __half* out);  // dequantized fp16 copy [N][K]
 int launch_act_dequant(b200_ctx*, ActQ aq, int T, int K, float* out);                    // code * scale, f32 [T][K]
 // grouped form: expert e owns assignment rows [offs[e], offs[e+1]); assignment a reads activation row

@@ -428,7 +428,7 @@ int fuse_rows(b200_model* m, std::vector<DevMat*> parts, DevMat* out) {
         rows += p->rows;
     }
     if (!same || parts[0]->kind == B200_K_Q6K || parts[0]->kind == B200_K_I8) {
-        // K-quants of different kinds (a Q4_K_M file's q|k|v or gate|up), or Q6_K parts (whose planes do not concatenate):
+        // K-quants of different kinds (a Q4_K_M file's q|k|v or gate|up), or Q6_K parts (whose d values sit behind the blocks, so two matrices do not concatenate):
         // the parts stay where they are and are multiplied one after the other into their columns of the output
         if (!all_kq || parts.size() > 3) B200_FAIL(ctx, B200_DECLINED, "projection group mixing quantized and float tensors");
         out->kind = kKindMixed; out->cols = parts[0]->cols; out->rows = rows; out->bytes = 0; out->p = nullptr;
@@ -725,13 +725,13 @@ int b200_upload_tensor(b200_model* m, int which, int layer, int expert, int kind
     ST_TRY(prep_mat(m, which, layer, expert, kind, rows, cols, &mat));
     if (bytes != mat->bytes) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tensor %d: %zu bytes, expected %zu", which, bytes, mat->bytes);
     if (kind == B200_K_Q6K) {
-        // the file's 210-byte blocks are laid out as four planes on the device (16-byte aligned loads): through a staging copy
+        // the file's 210-byte blocks become 208-byte bodies followed by their d values on the device (16-byte aligned loads): through a staging copy
         void* stage = nullptr;
         CUDA_TRY(ctx, cudaMalloc(&stage, bytes));
         // on the model's own stream, so that the re-layout kernel is ordered after the copy (a plain cudaMemcpy from pageable
         // memory may return while its DMA is still in flight, and this stream does not wait for the default stream)
         cudaError_t e = cudaMemcpyAsync(stage, host, bytes, cudaMemcpyHostToDevice, ctx->stream);
-        int st = e == cudaSuccess ? launch_q6k_to_planes(ctx, (const uint8_t*)stage, bytes / 210, (uint8_t*)mat->p) : B200_CUDA_ERROR;
+        int st = e == cudaSuccess ? launch_q6k_repack(ctx, (const uint8_t*)stage, bytes / 210, (uint8_t*)mat->p) : B200_CUDA_ERROR;
         if (st == B200_OK) e = cudaStreamSynchronize(ctx->stream);
         cudaFree(stage);
         if (e != cudaSuccess) B200_FAIL(ctx, B200_CUDA_ERROR, "Q6_K upload: %s", cudaGetErrorString(e));

@@ -4,9 +4,9 @@
 //
 //   Q5_K  (176 B / 256 weights: d, dmin, 12 bytes of 6-bit scales and minimums, qh[32], qs[128]):
 //         y += (d*sc_g*aS_g) * idot_g - (dmin*m_g) * asum_g   per group g of 32, codes 0..31   (backend/cuda/actgroup.cu:77-143)
-//   Q6_K  (210 B / 256 weights: ql[128], qh[64], 16 int8 sub-scales, d) kept as four planes over the whole matrix
-//         (ql | qh | sub-scales | d, every plane 16-byte aligned: backend/cuda/pack_stream.go q6kPlanes):
-//         y += (sc_h * idot_h) * (d*aS_g)   per half-group h of 16, codes -32..31              (backend/cuda/actgroup.cu:145-205)
+//   Q6_K  (210 B / 256 weights: ql[128], qh[64], 16 int8 sub-scales, d) kept as the blocks' first 208 bytes row by row
+//         (16-byte aligned, so a lane's loads are 16-byte ones) followed by the blocks' d values:
+//         y += (d*sc_h*aS_g) * idot_h   per half-group h of 16, codes -32..31   (the W6A8 product of backend/cuda/actgroup.cu:145-205)
 //
 // One warp owns one weight row and up to four activation rows; integer dots by dp4a, f32 terms, a shuffle tree at the
 // end. A token's sum does not depend on the other tokens of the launch, so a row's bits do not depend on its batch.
@@ -87,57 +87,65 @@ __global__ void __launch_bounds__(256) q5k_gemv_kernel(const uint8_t* __restrict
     }
 }
 
-// Q6_K in planes. Lane: super-block b0 + (lane >> 3) (four in flight), half hh = (lane >> 2) & 1 of the block (128 weights),
-// quarter q = lane & 3: elements 8q .. 8q+7 of each of the half's four groups of 32 (one 8-byte load of the low codes for
-// groups 0 and 2, one for 1 and 3, one of the two-bit planes, one of the half's eight sub-scales). is = q >> 1 picks the
-// sub-scale of the element's half-group.
+// Q6_K on the device: per weight row, the file's blocks with their trailing d taken out, [row][super-block][208 B] (ql[128],
+// qh[64], 16 int8 sub-scales: 16-byte aligned, so every load below is a 16-byte one), followed by one fp16 d per block
+// ([row][super-block]). A block's 256 weights: half n = e / 128, then four groups of 32 (gq), element l of a group:
+// low four bits in ql[64 n + 32 (gq & 1) + l] (low nibble for gq < 2, high for gq >= 2), two more bits in qh[32 n + l] at
+// shift 2 gq; value = d * sc[8 n + 2 gq + l / 16] * (q - 32).
+//
+// Lane map: lane = 4 * (super-block of the pass) + 2 * n + h owns l = 16 h .. 16 h + 15 of half n, i.e. 64 weights of one
+// super-block (16 of each group), eight super-blocks a pass; one sub-scale per group (index 8 n + 2 gq + h). The 6-bit codes
+// stay unsigned: sum (q - 32) a = dp4a(q, a) - 32 * dp4a(1, a).
+constexpr size_t kQ6Body = 208;
 template <int TT>
 __global__ void __launch_bounds__(256) q6k_gemv_kernel(const uint8_t* __restrict__ W, int N, int nSB, const int8_t* __restrict__ codes,
                                                        const float* __restrict__ scales, int T, float* __restrict__ dst, int ldd) {
     const int lane = threadIdx.x & 31, n = blockIdx.x * 8 + (threadIdx.x >> 5), t0 = blockIdx.y * TT;
     if (n >= N) return;
-    const size_t TB = (size_t)N * nSB;  // blocks in the matrix
-    const uint8_t* qlp = W;
-    const uint8_t* qhp = W + 128 * TB;
-    const uint8_t* scp = W + 192 * TB;
-    const unsigned short* dp = reinterpret_cast<const unsigned short*>(W + 208 * TB);
-    const int sub = lane >> 3, hh = (lane >> 2) & 1, q = lane & 3, is = q >> 1, K = nSB * 256, nG = nSB * 8;
+    const int half = (lane >> 1) & 1, h = lane & 1, K = nSB * 256, nG = nSB * 8;
+    const uint8_t* body = W + (size_t)n * nSB * kQ6Body;
+    const unsigned short* dp = reinterpret_cast<const unsigned short*>(W + (size_t)N * nSB * kQ6Body) + (size_t)n * nSB;
     float acc[TT];
 #pragma unroll
     for (int t = 0; t < TT; t++) acc[t] = 0.f;
-    for (int b = sub; b < nSB; b += 4) {
-        const size_t nb = (size_t)n * nSB + b;
-        const uint2 qa = *reinterpret_cast<const uint2*>(qlp + nb * 128 + 64 * hh + 8 * q);        // low codes of groups 0 (low nibble) and 2 (high)
-        const uint2 qb = *reinterpret_cast<const uint2*>(qlp + nb * 128 + 64 * hh + 32 + 8 * q);   // of groups 1 and 3
-        const uint2 qh = *reinterpret_cast<const uint2*>(qhp + nb * 64 + 32 * hh + 8 * q);         // two more bits a group
-        const uint2 sw = *reinterpret_cast<const uint2*>(scp + nb * 16 + 8 * hh);                  // the half's 8 sub-scales
-        const float d = kq_h2f(dp[nb]);
-        int c[4];
-        c[0] = (int)(signed char)((sw.x >> (8 * is)) & 0xffu);
-        c[1] = (int)(signed char)((sw.x >> (8 * (is + 2))) & 0xffu);
-        c[2] = (int)(signed char)((sw.y >> (8 * is)) & 0xffu);
-        c[3] = (int)(signed char)((sw.y >> (8 * (is + 2))) & 0xffu);
-        int v[4][2];
-        v[0][0] = (int)__vsub4((qa.x & 0x0F0F0F0Fu) | ((qh.x & 0x03030303u) << 4), 0x20202020u);
-        v[0][1] = (int)__vsub4((qa.y & 0x0F0F0F0Fu) | ((qh.y & 0x03030303u) << 4), 0x20202020u);
-        v[1][0] = (int)__vsub4((qb.x & 0x0F0F0F0Fu) | (((qh.x >> 2) & 0x03030303u) << 4), 0x20202020u);
-        v[1][1] = (int)__vsub4((qb.y & 0x0F0F0F0Fu) | (((qh.y >> 2) & 0x03030303u) << 4), 0x20202020u);
-        v[2][0] = (int)__vsub4(((qa.x >> 4) & 0x0F0F0F0Fu) | (((qh.x >> 4) & 0x03030303u) << 4), 0x20202020u);
-        v[2][1] = (int)__vsub4(((qa.y >> 4) & 0x0F0F0F0Fu) | (((qh.y >> 4) & 0x03030303u) << 4), 0x20202020u);
-        v[3][0] = (int)__vsub4(((qb.x >> 4) & 0x0F0F0F0Fu) | (((qh.x >> 6) & 0x03030303u) << 4), 0x20202020u);
-        v[3][1] = (int)__vsub4(((qb.y >> 4) & 0x0F0F0F0Fu) | (((qh.y >> 6) & 0x03030303u) << 4), 0x20202020u);
-        const int g0 = 8 * b + 4 * hh;
+    for (int b = lane >> 2; b < nSB; b += 8) {
+        const uint8_t* blk = body + (size_t)b * kQ6Body;
+        const uint4 la = *reinterpret_cast<const uint4*>(blk + 64 * half + 16 * h);         // groups 0 (low nibbles) and 2 (high)
+        const uint4 lb = *reinterpret_cast<const uint4*>(blk + 64 * half + 32 + 16 * h);    // groups 1 and 3
+        const uint4 hb = *reinterpret_cast<const uint4*>(blk + 128 + 32 * half + 16 * h);   // the two upper bits of all four groups
+        const uint2 sw = *reinterpret_cast<const uint2*>(blk + 192 + 8 * half);            // the half's eight sub-scales
+        const float d = kq_h2f(dp[b]);
+        const unsigned lo_a[4] = {la.x, la.y, la.z, la.w}, lo_b[4] = {lb.x, lb.y, lb.z, lb.w}, up[4] = {hb.x, hb.y, hb.z, hb.w};
+        // sub-scale of group gq: byte 2 gq + h of the eight
+        float dsc[4];
+#pragma unroll
+        for (int gq = 0; gq < 4; gq++) {
+            const unsigned w = gq < 2 ? sw.x : sw.y;
+            dsc[gq] = __fmul_rn(d, (float)(int)(signed char)((w >> (8 * (2 * (gq & 1) + h))) & 0xffu));
+        }
+        unsigned q6[4][4];   // [group][word of four codes], 0..63
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            q6[0][i] = (lo_a[i] & 0x0F0F0F0Fu) | ((up[i] << 4) & 0x30303030u);
+            q6[1][i] = (lo_b[i] & 0x0F0F0F0Fu) | ((up[i] << 2) & 0x30303030u);
+            q6[2][i] = ((lo_a[i] >> 4) & 0x0F0F0F0Fu) | (up[i] & 0x30303030u);
+            q6[3][i] = ((lo_b[i] >> 4) & 0x0F0F0F0Fu) | ((up[i] >> 2) & 0x30303030u);
+        }
+        const int g0 = 8 * b + 4 * half;
 #pragma unroll
         for (int t = 0; t < TT; t++) {
             if (t0 + t >= T) break;
-            const int8_t* ab = codes + (size_t)(t0 + t) * K + 256 * b + 128 * hh + 8 * q;
+            const int8_t* ab = codes + (size_t)(t0 + t) * K + 256 * b + 128 * half + 16 * h;
             const float* sp = scales + (size_t)(t0 + t) * 2 * nG + g0;
             float f = acc[t];
 #pragma unroll
-            for (int g = 0; g < 4; g++) {
-                const int2 a = *reinterpret_cast<const int2*>(ab + 32 * g);
-                const int p = kq_dp4a_ss(v[g][1], a.y, kq_dp4a_ss(v[g][0], a.x, 0));
-                f = __fmaf_rn((float)(c[g] * p), __fmul_rn(d, sp[g]), f);
+            for (int gq = 0; gq < 4; gq++) {
+                const int4 a = *reinterpret_cast<const int4*>(ab + 32 * gq);
+                int dot = kq_dp4a_us(q6[gq][0], a.x, 0), sum = kq_dp4a_ss(0x01010101, a.x, 0);
+                dot = kq_dp4a_us(q6[gq][1], a.y, dot); sum = kq_dp4a_ss(0x01010101, a.y, sum);
+                dot = kq_dp4a_us(q6[gq][2], a.z, dot); sum = kq_dp4a_ss(0x01010101, a.z, sum);
+                dot = kq_dp4a_us(q6[gq][3], a.w, dot); sum = kq_dp4a_ss(0x01010101, a.w, sum);
+                f = __fmaf_rn((float)(dot - 32 * sum), __fmul_rn(dsc[gq], sp[gq]), f);
             }
             acc[t] = f;
         }
@@ -146,7 +154,7 @@ __global__ void __launch_bounds__(256) q6k_gemv_kernel(const uint8_t* __restrict
     for (int t = 0; t < TT; t++) {
         float f = acc[t];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) f += __shfl_down_sync(0xffffffffu, f, off);
+        for (int off = 1; off < 32; off <<= 1) f += __shfl_xor_sync(0xffffffffu, f, off);
         if (lane == 0 && t0 + t < T) dst[(size_t)(t0 + t) * ldd + n] = f;
     }
 }
@@ -217,15 +225,16 @@ __global__ void __launch_bounds__(256) q6k_to_f16_kernel(const uint8_t* __restri
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (block, group of 32)
     if (i >= n_blocks * 8) return;
     const size_t g = i >> 3;
-    const int grp = (int)(i & 7), hh = grp >> 2, gg = grp & 3;
-    const uint8_t* ql = W + g * 128 + 64 * hh + 32 * (gg & 1);
-    const uint8_t* qh = W + 128 * n_blocks + g * 64 + 32 * hh;
-    const int8_t* sc = reinterpret_cast<const int8_t*>(W + 192 * n_blocks + g * 16 + 8 * hh + 2 * gg);
-    const float d = kq_h2f(reinterpret_cast<const unsigned short*>(W + 208 * n_blocks)[g]);
+    const int grp = (int)(i & 7), half = grp >> 2, gq = grp & 3;
+    const uint8_t* blk = W + g * kQ6Body;
+    const uint8_t* ql = blk + 64 * half + 32 * (gq & 1);
+    const uint8_t* qh = blk + 128 + 32 * half;
+    const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192 + 8 * half + 2 * gq);
+    const float d = kq_h2f(reinterpret_cast<const unsigned short*>(W + n_blocks * kQ6Body)[g]);
     __half* o = out + g * 256 + 32 * grp;
     for (int l = 0; l < 32; l++) {
-        const int lo = (gg & 2) ? (ql[l] >> 4) : (ql[l] & 15);
-        const int code = (lo | (((qh[l] >> (2 * gg)) & 3) << 4)) - 32;
+        const int lo = (gq & 2) ? (ql[l] >> 4) : (ql[l] & 15);
+        const int code = (lo | (((qh[l] >> (2 * gq)) & 3) << 4)) - 32;
         o[l] = __float2half_rn(__fmul_rn(__fmul_rn(d, (float)sc[l >> 4]), (float)code));
     }
 }
@@ -237,22 +246,19 @@ __global__ void act_dequant_kernel(const int8_t* __restrict__ codes, const float
     out[(size_t)t * K + k] = __fmul_rn((float)codes[(size_t)t * K + k], scales[(size_t)t * 2 * (K >> 5) + (k >> 5)]);
 }
 
-// the file's 210-byte blocks -> the four planes
-__global__ void q6k_to_planes_kernel(const uint8_t* __restrict__ raw, size_t TB, uint8_t* __restrict__ out) {
+// the file's 210-byte blocks -> 208-byte bodies, then the blocks' d values
+__global__ void q6k_repack_kernel(const uint8_t* __restrict__ raw, size_t TB, uint8_t* __restrict__ out) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (block, byte)
     if (i >= TB * 210) return;
     const size_t g = i / 210;
     const int o = (int)(i % 210);
-    const uint8_t v = raw[i];
-    if (o < 128) out[g * 128 + o] = v;
-    else if (o < 192) out[128 * TB + g * 64 + (o - 128)] = v;
-    else if (o < 208) out[192 * TB + g * 16 + (o - 192)] = v;
-    else out[208 * TB + g * 2 + (o - 208)] = v;
+    if (o < 208) out[g * kQ6Body + o] = raw[i];
+    else out[TB * kQ6Body + g * 2 + (o - 208)] = raw[i];
 }
 
 }  // namespace
 
-// W: Q5_K as in the file; Q6_K in planes (launch_q6k_to_planes). Any T: the rows go four at a time.
+// W: Q5_K as in the file; Q6_K as 208-byte bodies + d (launch_q6k_repack). Any T: the rows go four at a time.
 int launch_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd) {
     if (kind == B200_K_I8) {
         if (K % 32 || T < 1) B200_FAIL(ctx, B200_BAD_ARGUMENT, "int8 matmul needs K %% 32 == 0 and at least one row");
@@ -309,9 +315,9 @@ int launch_act_dequant(b200_ctx* ctx, ActQ aq, int T, int K, float* out) {
     return B200_OK;
 }
 
-int launch_q6k_to_planes(b200_ctx* ctx, const uint8_t* raw, size_t n_blocks, uint8_t* planes) {
+int launch_q6k_repack(b200_ctx* ctx, const uint8_t* raw, size_t n_blocks, uint8_t* planes) {  // planes: n_blocks * 210 bytes
     const size_t n = n_blocks * 210;
-    q6k_to_planes_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(raw, n_blocks, planes);
+    q6k_repack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(raw, n_blocks, planes);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }

@@ -188,7 +188,7 @@ int b200_op_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* w, const float* a,
     H2D(ctx, dw, w, wb); H2D(ctx, da, a, (size_t)M * K * 4);
     if (kind == B200_K_Q6K) {
         TMP_GET(ctx, t, dp, wb);
-        ST_TRY(launch_q6k_to_planes(ctx, dw, nb, dp));
+        ST_TRY(launch_q6k_repack(ctx, dw, nb, dp));
     }
     ST_TRY(launch_quant_g32(ctx, da, M, K, aq));
     ST_TRY(launch_kq_matmul(ctx, kind, kind == B200_K_Q6K ? dp : dw, N, K, aq, M, dd, N));
@@ -477,7 +477,7 @@ int b200_bench_read(b200_ctx* ctx, size_t bytes, int n_copies, int warmup, int i
 }
 
 namespace {
-// random code bytes with scales of a sane size at the f16 fields (Q5_K: d and dmin at 0 and 2; Q6_K planes: the d plane)
+// random code bytes with scales of a sane size at the f16 fields (Q5_K: d and dmin at 0 and 2; Q6_K: the d values behind the bodies)
 __global__ void kq_fill_kernel(uint8_t* __restrict__ w, size_t n_bytes, size_t n_blocks, int kind, uint64_t seed) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_bytes) return;

@@ -47,31 +47,39 @@ __device__ __forceinline__ long long block_sum_i64(long long v, long long* red) 
     return t;
 }
 
-// Philox4x32-10 (Salmon et al., SC'11; internal/runtime/sampling/philox.go:21-36): integer only, so every backend draws the
-// same words. The key is bumped between rounds, not before the first.
+// Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11; the host's statement is
+// internal/runtime/sampling/philox.go:21-36). Integer only, so every backend draws the same words. One round: the two
+// 32 x 32 -> 64 bit products M0 * c0 and M1 * c2; the new counter is (hi(M1 c2) ^ c1 ^ k0, lo(M1 c2), hi(M0 c0) ^ c3 ^ k1,
+// lo(M0 c0)). Round r runs under the key k + r * W (the Weyl sequence: the key is bumped between rounds, not before the first).
+struct PhiloxState {
+    unsigned c[4];
+};
+__device__ __forceinline__ PhiloxState philox_round(PhiloxState s, unsigned key0, unsigned key1) {
+    const unsigned long long prod_a = (unsigned long long)0xD2511F53u * s.c[0];
+    const unsigned long long prod_b = (unsigned long long)0xCD9E8D57u * s.c[2];
+    PhiloxState n;
+    n.c[0] = (unsigned)(prod_b >> 32) ^ s.c[1] ^ key0;
+    n.c[1] = (unsigned)prod_b;
+    n.c[2] = (unsigned)(prod_a >> 32) ^ s.c[3] ^ key1;
+    n.c[3] = (unsigned)prod_a;
+    return n;
+}
 __device__ __forceinline__ void philox4x32(unsigned c0, unsigned c1, unsigned c2, unsigned c3, unsigned k0, unsigned k1, unsigned* out) {
+    PhiloxState s{{c0, c1, c2, c3}};
 #pragma unroll
-    for (int r = 0; r < 10; r++) {
-        if (r > 0) { k0 += 0x9E3779B9u; k1 += 0xBB67AE85u; }
-        const unsigned hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
-        const unsigned hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
-        const unsigned n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
-        c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
-    }
-    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+    for (unsigned r = 0; r < 10u; r++) s = philox_round(s, k0 + r * 0x9E3779B9u, k1 + r * 0xBB67AE85u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) out[i] = s.c[i];
 }
 
-// 32 random bits -> a standard Gumbel variate, in f32 without cancellation (backend/cuda/gumbel.cu:50-60): with
-// w = (h + 0.5) / 2^32, E = -ln(1 - w) comes from log1p for h < 2^31 and from 1 - w = (~h + 0.5) / 2^32 (exact) above.
+// 32 random bits -> a standard Gumbel variate G = -ln(-ln(w)), w = (h + 0.5) / 2^32 in (0, 1), in f32 without cancellation.
+// The f32 operations and their order are the host sampler's (internal/runtime/sampling/sampler_gumbel.go:37-64; device twin
+// backend/cuda/gumbel.cu:50-60), because a draw must pick the same token on every backend: E = -ln(1 - w) is taken from log1p
+// on the lower half of the range, and on the upper half from 1 - w = (~h + 0.5) / 2^32, which is exact.
 __device__ __forceinline__ float gumbel_noise(unsigned h) {
-    float e;
-    if (h < 0x80000000u) {
-        const float w = __fmul_rn(__fadd_rn((float)h, 0.5f), 2.3283064365386963e-10f);
-        e = -log1pf(-w);
-    } else {
-        const float v = __fmul_rn(__fadd_rn((float)(~h), 0.5f), 2.3283064365386963e-10f);
-        e = -logf(v);
-    }
+    const bool lower = (h >> 31) == 0u;
+    const float unit = __fmul_rn(__fadd_rn((float)(lower ? h : ~h), 0.5f), 2.3283064365386963e-10f);   // w below, 1 - w above
+    const float e = lower ? -log1pf(-unit) : -logf(unit);
     return -logf(e);
 }
 

@@ -60,8 +60,8 @@ extern "C" {
 #define B200_K_Q5K 3 /* GGUF Q5_K super-blocks, 176 bytes per 256 weights (d, dmin, 12 scale bytes, qh[32], qs[128]), as in
                         the file; x per-32 int8 activations (backend/cuda/actgroup.cu:77-143). */
 #define B200_K_Q6K 4 /* GGUF Q6_K super-blocks, 210 bytes per 256 weights (ql[128], qh[64], 16 int8 sub-scales, d), uploaded as in
-                        the file and kept on the device as four planes (ql, qh, sub-scales, d: the layout of
-                        backend/cuda/pack_stream.go q6kPlanes); x per-32 int8 activations (backend/cuda/actgroup.cu:145-205).
+                        the file; the device keeps each block's first 208 bytes row by row (16-byte aligned) and the d values
+                        behind them; x per-32 int8 activations (the W6A8 product, backend/cuda/actgroup.cu:145-205).
                         The Q5_K / Q6_K matmuls are held to the reference's own bar for them: within 1e-5 of sum |w*a| of the
                         f64 product of the dequantized row (backend/cuda/kernels/kso1c_kernels_test.go:146-151). q|k|v and
                         gate|up may mix Q4_K, Q5_K and Q6_K parts, as Q4_K_M files do. */
