@@ -45,13 +45,24 @@ constexpr int kStages = 3;   // A ring (and barriers); the B ring has 2 stages
 // w = (16 + q) * ds + c with c = -(16 ds + mn) is one half2 fma (c carries an extra rounding of about ds/128).
 // Nibbles come out paired (0,2),(1,3) per word, so the tile's K order inside every group of four is 0,2,1,3; the activation
 // matrix is written in the same order (a dot product does not care).
+// (x & mask) | magic in one LOP3: with both constants in registers (as immediates the compiler spends two instructions a pair)
+__device__ __forceinline__ unsigned and_or_u(unsigned x, unsigned mask, unsigned magic) {
+    unsigned r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(x), "r"(mask), "r"(magic));
+    return r;
+}
+__device__ __forceinline__ unsigned opaque_u(unsigned v) {
+    unsigned r;
+    asm volatile("mov.u32 %0, %1;" : "=r"(r) : "r"(v));
+    return r;
+}
 template <bool HIGH>
-__device__ __forceinline__ uint4 dequant8(unsigned w0, unsigned w1, __half2 ds, __half2 c) {
+__device__ __forceinline__ uint4 dequant8(unsigned w0, unsigned w1, __half2 ds, __half2 c, unsigned mask, unsigned magic) {
     auto cv = [&](unsigned w, int byte1) -> unsigned {
         // nibble of bytes (0,2) or (1,3), low or high, moved to bits [6,10) and [22,26)
         const int from = (byte1 ? 8 : 0) + (HIGH ? 4 : 0);
         const unsigned sh = from <= 6 ? (w << (6 - from)) : (w >> (from - 6));
-        unsigned t = (sh & 0x03C003C0u) | 0x4C004C00u;
+        unsigned t = and_or_u(sh, mask, magic);
         __half2 h = __hfma2(*reinterpret_cast<__half2*>(&t), ds, c);
         return *reinterpret_cast<unsigned*>(&h);
     };
@@ -61,6 +72,20 @@ __device__ __forceinline__ uint4 dequant8(unsigned w0, unsigned w1, __half2 ds, 
     o.z = cv(w1, 0);
     o.w = cv(w1, 1);
     return o;
+}
+
+// scales and minima of sub-blocks 2p and 2p+1 from the header's 12 packed bytes, two at a time (the 6-bit fields of a pair sit
+// in neighbouring bytes): {sc(2p), sc(2p+1)} and {m(2p), m(2p+1)} in the two low bytes. p is a literal at every call site.
+__device__ __forceinline__ void pair_scale_min(const uint4 hdr, int p, unsigned* scs, unsigned* ms) {
+    if (p < 2) {
+        *scs = (hdr.y >> (16 * p)) & 0x3F3Fu;
+        *ms = (hdr.z >> (16 * p)) & 0x3F3Fu;
+    } else {
+        const int sh = 16 * (p - 2);
+        const unsigned lo = hdr.w >> sh;
+        *scs = (lo & 0x0F0Fu) | (((hdr.y >> sh) >> 2) & 0x3030u);
+        *ms = ((lo >> 4) & 0x0F0Fu) | (((hdr.z >> sh) >> 2) & 0x3030u);
+    }
 }
 
 constexpr int kProducerWarps = 8;
@@ -132,6 +157,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
         const unsigned b_off = (unsigned)wr * 128u, sw = (unsigned)(wr & 7);
         uint4 hdr, q[8];  // the current super-block: d, dmin, 12 scale bytes; 128 code bytes
         bool ok = true;
+        const unsigned k_mask = opaque_u(0x03C003C0u), k_magic = opaque_u(0x4C004C00u);   // registers, so that mask-and-or is one LOP3
 
         auto step = [&](int it, int p) -> bool {  // p = it & 3, a literal at every call site
             // B stage it%2 was last read by the MMAs of chunk it-2
@@ -158,17 +184,19 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                 uint8_t* rowp = bring + (size_t)(it & 1) * BSTAGE + b_off;
                 const uint4 qa = q[2 * p], qb = q[2 * p + 1];
                 const unsigned wq[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                unsigned scs, ms;
+                pair_scale_min(hdr, p, &scs, &ms);
 #pragma unroll
                 for (int hf = 0; hf < 2; hf++) {
                     if (NT == 1 && hf != hf1) continue;
-                    int sc, mn;
-                    kq_scale_min(2 * p + hf, hdr.y, hdr.z, hdr.w, &sc, &mn);
+                    const int sc = (int)((scs >> (8 * hf)) & 0xffu), mn = (int)((ms >> (8 * hf)) & 0xffu);
                     const __half dsh = __float2half_rn(d * (float)sc);
                     // the offset uses the rounded scale, so that the 16 * scale part cancels exactly
                     const __half2 ds = __half2half2(dsh), c = __float2half2_rn(-(16.f * __half2float(dsh) + dmin * (float)mn));
 #pragma unroll
                     for (int ch = 0; ch < 4; ch++) {
-                        const uint4 v = hf ? dequant8<true>(wq[2 * ch], wq[2 * ch + 1], ds, c) : dequant8<false>(wq[2 * ch], wq[2 * ch + 1], ds, c);
+                        const uint4 v = hf ? dequant8<true>(wq[2 * ch], wq[2 * ch + 1], ds, c, k_mask, k_magic)
+                                           : dequant8<false>(wq[2 * ch], wq[2 * ch + 1], ds, c, k_mask, k_magic);
                         *reinterpret_cast<uint4*>(rowp + (((unsigned)(4 * hf + ch) ^ sw) << 4)) = v;
                     }
                 }
