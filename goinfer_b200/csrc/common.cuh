@@ -238,10 +238,12 @@ int launch_q4k_matmul_grouped(b200_ctx*, const uint8_t* const* Wptrs, int n_expe
                               const int32_t* offs, const int32_t* rows, int max_rows_per_expert, float* dst, int ldd);
 // gemm_umma.cu: fast-class tcgen05 matmul; scratch from q4k_umma_scratch_bytes
 size_t q4k_umma_scratch_bytes(int max_rows, int max_k, int max_n);
+// W_tiles: the tile-major copy (launch_q4k_to_tiles); when given it is what the kernel fetches and W may be null
 int launch_q4k_matmul_umma(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
-                           size_t scratch_bytes, int* err_flag);
+                           size_t scratch_bytes, int* err_flag, const uint8_t* W_tiles = nullptr);
 int launch_q4k_matmul_umma_swiglu(b200_ctx*, const uint8_t* W_interleaved, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
-                                  size_t scratch_bytes, int* err_flag, ActQ swiglu_out, bool force, bool* fused, __half* swiglu_x16 = nullptr);
+                                  size_t scratch_bytes, int* err_flag, ActQ swiglu_out, bool force, bool* fused, __half* swiglu_x16 = nullptr,
+                                  const uint8_t* W_tiles = nullptr);
 int launch_act_to_f16(b200_ctx*, ActQ aq, int T, int K, __half* out);  // the fp16 activation tiles of quantized rows (what the producers otherwise lay out)
 // gemm_small.cu: the fast class's matmul for up to 32 rows (fp16 dequant in registers, mma.sync, weights streamed once);
 // uses the context's scratch like the tcgen05 matmul and takes the producers' activation tiles the same way

@@ -29,8 +29,10 @@ struct DevMat {
     DevMat* seg[3] = {nullptr, nullptr, nullptr};  // kKindMixed: the parts, in row order
     int n_seg = 0;
     __half* f16 = nullptr;  // Q5_K / Q6_K, fast class: a dequantized copy for the tensor-core matmul at dense row counts
-    uint8_t* tiles = nullptr;  // Q4_K, fast class: the matrix tile by tile, what the small-batch kernel streams (launch_q4k_to_tiles)
-    bool present() const { return kind >= 0 && (p || n_seg > 0); }
+    // Q4_K, fast class: the matrix tile by tile (launch_q4k_to_tiles). Every fast-class kernel reads this layout, so the
+    // row-major matrix is dropped once it exists (p == nullptr) unless a debugging switch asks for the older kernels.
+    uint8_t* tiles = nullptr;
+    bool present() const { return kind >= 0 && (p || n_seg > 0 || tiles); }
 };
 
 // the kinds that multiply the per-32 int8 activations
@@ -586,7 +588,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
                 // the tcgen05 GEMM; where it runs two weight tiles per CTA without a K split its epilogue is the SwiGLU and the
                 // quantizer (the f32 gate|up matrix is never written), else the product lands in m->gu, interleaved
                 ST_TRY(launch_q4k_matmul_umma_swiglu(ctx, (const uint8_t*)L.gu.p, 2 * c.ffn, H, m->aq_h, T, m->gu, 2 * c.ffn, ctx->umma_scratch,
-                                                     ctx->umma_scratch_bytes, ctx->err_flag, no_fuse_env ? ActQ{} : m->aq_mid, false, &fused, x16d));
+                                                     ctx->umma_scratch_bytes, ctx->err_flag, no_fuse_env ? ActQ{} : m->aq_mid, false, &fused, x16d, L.gu.tiles));
             } else {
                 ST_TRY(matmul(m, L.gu, m->normed, m->aq_h, T, m->gu, 2 * c.ffn));
             }
@@ -921,20 +923,30 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
         // two fp16 activation slots ahead of the partials: producers lay the tiles out for the matmul that follows them
         m->x16_slot_bytes = ((size_t)ceil_div(MR, 256) * 256 * max_k * 2 + 255) & ~(size_t)255;
         m->umma_bytes += m->x16_slot_bytes;
-        // Q4_K projections: a tile-by-tile copy for the small-batch kernel (up to 32 rows)
+        // Q4_K projections are re-laid tile by tile, the layout the fast class's kernels fetch with plain bulk copies (the
+        // one- and two-row dp4a kernel, the small-batch kernel up to 32 rows, the tcgen05 kernel above). The row-major
+        // matrix is then released, unless the kernel class or a debugging switch can route a step to the older kernels
+        // that read it, or the scratch cannot hold the matrix's worst case.
         if (q4k_small_min_rows() > 0) {
+            const bool may_drop = (c.kernel_class == B200_CLASS_AUTO || c.kernel_class == 2) && !getenv("B200_KEEP_ROW_MAJOR") && !getenv("B200_NO_UMMA") &&
+                                  !getenv("B200_UMMA_ROW_MAJOR") && !getenv("B200_DEBUG_TAP");
+            auto to_tiles = [&](DevMat* d, int max_rows) -> int {
+                if (!d->p || d->kind != B200_K_Q4K || d->cols % 256) return B200_OK;
+                ST_TRY(m->dalloc((void**)&d->tiles, q4k_tiles_bytes(d->rows, d->cols), &m->weight_bytes));
+                ST_TRY(launch_q4k_to_tiles(ctx, (const uint8_t*)d->p, d->rows, d->cols, d->tiles));
+                if (may_drop && q4k_umma_scratch_bytes(max_rows, d->cols, d->rows) <= m->umma_bytes) {
+                    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+                    m->dfree(d->p);
+                    d->p = nullptr;
+                    m->weight_bytes -= d->bytes;
+                }
+                return B200_OK;
+            };
             for (int l = 0; l < c.n_layers; l++) {
                 LayerW& L = m->layers[l];
-                for (DevMat* d : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down, &L.qkv, &L.gu})
-                    if (d->p && d->kind == B200_K_Q4K && d->cols % 256 == 0) {
-                        ST_TRY(m->dalloc((void**)&d->tiles, q4k_tiles_bytes(d->rows, d->cols), &m->weight_bytes));
-                        ST_TRY(launch_q4k_to_tiles(ctx, (const uint8_t*)d->p, d->rows, d->cols, d->tiles));
-                    }
+                for (DevMat* d : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down, &L.qkv, &L.gu}) ST_TRY(to_tiles(d, MR));
             }
-            if (m->head.p && m->head.kind == B200_K_Q4K && m->head.cols % 256 == 0) {
-                ST_TRY(m->dalloc((void**)&m->head.tiles, q4k_tiles_bytes(m->head.rows, m->head.cols), &m->weight_bytes));
-                ST_TRY(launch_q4k_to_tiles(ctx, (const uint8_t*)m->head.p, m->head.rows, m->head.cols, m->head.tiles));
-            }
+            ST_TRY(to_tiles(&m->head, MLR));
         }
         // Q5_K / Q6_K tensors: fp16 copies for the tensor-core matmul from 32 rows on
         std::vector<DevMat*> kq;

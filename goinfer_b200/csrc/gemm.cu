@@ -489,9 +489,118 @@ __global__ void __launch_bounds__(256) q4k_gemv_dp4a_kernel(const uint8_t* __res
 }
 
 
+// The same products from the tile-major copy ([16-row tile][super-block][16 rows][144 B], what a fast-class model keeps):
+// a CTA takes one 16-row tile, warp w the super-blocks w, w+8, ...; lane l owns rows (l >> 2) and (l >> 2) + 8 and the
+// sub-block pair (l & 3), so a warp's loads of one super-block are the tile's 2304 contiguous bytes and the CTA's eight
+// warps read 18 KB in one piece. The eight row-lanes of a pair read the same activations (one broadcast). Lane partials
+// fold over the four pairs by two xor shuffles, warp partials through shared memory in warp order.
 template <int TT>
-int run_q4k_gemv(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, float* dst, int ldd) {
+__global__ void __launch_bounds__(256) q4k_gemv_tiles_kernel(const uint8_t* __restrict__ W16, int N, int nSB,
+                                                             const int8_t* __restrict__ codes, const float* __restrict__ scales,
+                                                             float* __restrict__ dst, int ldd) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float part[8][16][TT];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = lane & 3, r0 = lane >> 2;
+    const int K = nSB * 256, nG = nSB * 8;
+    const uint8_t* tile = W16 + (size_t)blockIdx.x * nSB * (16 * 144);
+    float acc[2][TT];
+#pragma unroll
+    for (int r = 0; r < 2; r++)
+#pragma unroll
+        for (int t = 0; t < TT; t++) acc[r][t] = 0.f;
+    constexpr int U = 2;  // super-blocks in flight per warp
+    for (int b0 = warp; b0 < nSB; b0 += 8 * U) {
+        uint4 hdr[U][2], q0[U][2], q1[U][2];
+        bool ok[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int b = b0 + 8 * u;
+            ok[u] = b < nSB;
+            const uint8_t* blk0 = tile + (size_t)(ok[u] ? b : b0) * (16 * 144);
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const uint8_t* blk = blk0 + (r0 + 8 * r) * 144;
+                hdr[u][r] = *reinterpret_cast<const uint4*>(blk);
+                q0[u][r] = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j);
+                q1[u][r] = *reinterpret_cast<const uint4*>(blk + 32 + 32 * j);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            if (!ok[u]) continue;
+            const int b = b0 + 8 * u, g = 8 * b + 2 * j;
+            int4 al[TT][2], ah[TT][2];
+            float2 aS[TT], as[TT];
+#pragma unroll
+            for (int t = 0; t < TT; t++) {
+                const int4* av = reinterpret_cast<const int4*>(codes + (size_t)t * K + 256 * b + 64 * j);
+                al[t][0] = av[0]; al[t][1] = av[1]; ah[t][0] = av[2]; ah[t][1] = av[3];
+                aS[t] = *reinterpret_cast<const float2*>(scales + (size_t)t * 2 * nG + g);
+                as[t] = *reinterpret_cast<const float2*>(scales + (size_t)t * 2 * nG + nG + g);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const uint4 h = hdr[u][r];
+                const float d = kq_h2f((unsigned short)(h.x & 0xffffu)), dmin = kq_h2f((unsigned short)(h.x >> 16));
+                int scLo, mLo, scHi, mHi;
+                kq_scale_min(2 * j, h.y, h.z, h.w, &scLo, &mLo);
+                kq_scale_min(2 * j + 1, h.y, h.z, h.w, &scHi, &mHi);
+                const float dsLo = __fmul_rn(d, (float)scLo), dsHi = __fmul_rn(d, (float)scHi);
+                const float nmLo = -__fmul_rn(dmin, (float)mLo), nmHi = -__fmul_rn(dmin, (float)mHi);
+                const uint4 a = q0[u][r], c = q1[u][r];
+                const unsigned wl[8] = {a.x & 0x0F0F0F0Fu, a.y & 0x0F0F0F0Fu, a.z & 0x0F0F0F0Fu, a.w & 0x0F0F0F0Fu,
+                                        c.x & 0x0F0F0F0Fu, c.y & 0x0F0F0F0Fu, c.z & 0x0F0F0F0Fu, c.w & 0x0F0F0F0Fu};
+                const unsigned wh[8] = {a.x & 0xF0F0F0F0u, a.y & 0xF0F0F0F0u, a.z & 0xF0F0F0F0u, a.w & 0xF0F0F0F0u,
+                                        c.x & 0xF0F0F0F0u, c.y & 0xF0F0F0F0u, c.z & 0xF0F0F0F0u, c.w & 0xF0F0F0F0u};
+#pragma unroll
+                for (int t = 0; t < TT; t++) {
+                    int pl = 0, ph = 0;
+                    pl = dp4a_us(wl[0], al[t][0].x, pl); pl = dp4a_us(wl[1], al[t][0].y, pl);
+                    pl = dp4a_us(wl[2], al[t][0].z, pl); pl = dp4a_us(wl[3], al[t][0].w, pl);
+                    pl = dp4a_us(wl[4], al[t][1].x, pl); pl = dp4a_us(wl[5], al[t][1].y, pl);
+                    pl = dp4a_us(wl[6], al[t][1].z, pl); pl = dp4a_us(wl[7], al[t][1].w, pl);
+                    ph = dp4a_us(wh[0], ah[t][0].x, ph); ph = dp4a_us(wh[1], ah[t][0].y, ph);
+                    ph = dp4a_us(wh[2], ah[t][0].z, ph); ph = dp4a_us(wh[3], ah[t][0].w, ph);
+                    ph = dp4a_us(wh[4], ah[t][1].x, ph); ph = dp4a_us(wh[5], ah[t][1].y, ph);
+                    ph = dp4a_us(wh[6], ah[t][1].z, ph); ph = dp4a_us(wh[7], ah[t][1].w, ph);
+                    float f = acc[r][t];
+                    f = __fmaf_rn((float)pl, __fmul_rn(dsLo, aS[t].x), f);
+                    f = __fmaf_rn((float)ph, __fmul_rn(__fmul_rn(dsHi, aS[t].y), 0.0625f), f);  // ph = 16 * idot, 1/16 is exact
+                    f = __fmaf_rn(nmLo, as[t].x, f);
+                    acc[r][t] = __fmaf_rn(nmHi, as[t].y, f);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; r++)
+#pragma unroll
+        for (int t = 0; t < TT; t++) {
+            float f = acc[r][t];
+            f += __shfl_xor_sync(0xffffffffu, f, 1);
+            f += __shfl_xor_sync(0xffffffffu, f, 2);
+            if (j == 0) part[warp][r0 + 8 * r][t] = f;
+        }
+    __syncthreads();
+    if (threadIdx.x < 16 * TT) {
+        const int row = threadIdx.x / TT, t = threadIdx.x % TT, n = blockIdx.x * 16 + row;
+        float f = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) f += part[w][row][t];
+        if (n < N) dst[(size_t)t * ldd + n] = f;
+    }
+}
+
+template <int TT>
+int run_q4k_gemv(b200_ctx* ctx, const uint8_t* W, int N, int nSB, ActQ aq, float* dst, int ldd, int tiled = 0) {
     ProfScope ps(ctx, PROF_Q4K_GEMM);
+    if (tiled) {
+        launch_pdl(q4k_gemv_tiles_kernel<TT>, dim3(ceil_div(N, 16)), dim3(256), 0, ctx->stream, W, N, nSB, aq.codes, aq.scales, dst, ldd);
+        LAUNCH_CHECK(ctx);
+        return B200_OK;
+    }
     // 2 rows per warp at one token, 4 at two or three (the activation loads are shared by a warp's rows)
     if (TT == 1) launch_pdl(q4k_gemv_dp4a_kernel<TT, 2, 1>, dim3(ceil_div(N, 16)), dim3(256), 0, ctx->stream, W, N, nSB, aq.codes, aq.scales, dst, ldd);
     else launch_pdl(q4k_gemv_dp4a_kernel<TT, 4, 1>, dim3(ceil_div(N, 32)), dim3(256), 0, ctx->stream, W, N, nSB, aq.codes, aq.scales, dst, ldd);
@@ -725,7 +834,7 @@ int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, in
     static const bool no_umma_env = getenv("B200_NO_UMMA") != nullptr;
     if (klass != B200_CLASS_EXACT && klass != 3 && klass != 4 && klass != 5 && klass != 6 && (T >= 33 || klass == 2) && ctx->umma_scratch && !no_umma_env &&
         q4k_umma_scratch_bytes(T, K, N) <= ctx->umma_scratch_bytes)
-        return launch_q4k_matmul_umma(ctx, W, N, K, aq, T, dst, ldd, ctx->umma_scratch, ctx->umma_scratch_bytes, ctx->err_flag);
+        return launch_q4k_matmul_umma(ctx, W, N, K, aq, T, dst, ldd, ctx->umma_scratch, ctx->umma_scratch_bytes, ctx->err_flag, W_tiles);
     // Fast class, up to 32 rows (klass 5 forces it): fp16 dequant in registers + mma.sync, the weights streamed once
     {
         const int small_min = q4k_small_min_rows();
@@ -734,6 +843,15 @@ int launch_q4k_matmul(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, in
             q4k_umma_scratch_bytes(T, K, N) <= ctx->umma_scratch_bytes)
             return launch_q4k_matmul_small(ctx, W_tiles, N, K, aq, T, dst, ldd);
         if (klass == 5) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the small-batch Q4_K matmul needs the tiled weights, 1..32 rows and the fast class's scratch");
+    }
+    if (!W) {
+        // only the tile-major copy is resident (a fast-class model drops the row-major one): the kernels that read it
+        if (!W_tiles) B200_FAIL(ctx, B200_BAD_ARGUMENT, "no weights");
+        if (T == 1) return run_q4k_gemv<1>(ctx, W_tiles, N, nSB, aq, dst, ldd, 1);
+        if (T == 2) return run_q4k_gemv<2>(ctx, W_tiles, N, nSB, aq, dst, ldd, 1);
+        if (T == 3) return run_q4k_gemv<3>(ctx, W_tiles, N, nSB, aq, dst, ldd, 1);
+        if (T <= 32 && ctx->umma_scratch) return launch_q4k_matmul_small(ctx, W_tiles, N, K, aq, T, dst, ldd);
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "this row count or kernel class needs the row-major Q4_K matrix, which this model did not keep");
     }
     // Rows up to 8 are HBM-bound: split K over the CTA's warps (unless the exact class asks for the one ascending
     // chain per output that every larger batch uses, so a row's bits do not depend on its batch).

@@ -106,7 +106,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                                                                         const __half* __restrict__ X16, int T,
                                                                         float* __restrict__ dst, int ldd, size_t split_stride,
                                                                         int* __restrict__ err_flag, int8_t* __restrict__ sw_codes,
-                                                                        float* __restrict__ sw_scales, __half* __restrict__ sw_x16) {
+                                                                        float* __restrict__ sw_scales, __half* __restrict__ sw_x16,
+                                                                        const uint8_t* __restrict__ w16) {
     pdl_trigger();  // the next kernel's blocks may be placed as ours retire; they wait for our completion before they touch data
     extern __shared__ __align__(1024) uint8_t umma_smem[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], raw_full, raw_empty;
@@ -256,16 +257,26 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
             for (int it = max(0, issued - kStages); it < issued; it++) mbar_wait(smem_u32(&full_bar[it % kStages]), (unsigned)((it / kStages) & 1));
         }
     } else if (warp == kProducerWarps + 2 && lane == 0) {
-        // ---- the weight loader: one thread, one tiled copy per super-block: 144 raw bytes of each of the tile's rows
-        // (rows past N read as zeros, which dequantize to zero weights) ----
+        // ---- the weight loader: one thread. From the row-major matrix, one tiled copy per super-block: 144 raw bytes of
+        // each of the tile's rows (rows past N read as zeros, which dequantize to zero weights). From the tile-major copy
+        // (w16: [16-row tile][super-block][16][144], padded with zero blocks to whole tiles), 2304 contiguous bytes per
+        // 16 rows; 16-row tiles past the matrix are not fetched, and their columns of the product are never stored. ----
         int issued = 0;
+        const int tile0 = n0 / 16, live = min(8 * NT, (N + 15) / 16 - tile0);
         for (int sb = 0; sb < n_sb; sb++) {
             if (sb > 0 && !mbar_wait(smem_u32(&raw_empty), (unsigned)((sb - 1) & 1), abort_v)) {
                 abort_s = 1;
                 break;
             }
-            mbar_arrive_expect_tx(smem_u32(&raw_full), (unsigned)(128 * NT * kRawRow));
-            tensor_g2s_2d(smem_u32(raw), &wmap, (sb0 + sb) * kRawRow, n0, smem_u32(&raw_full));
+            if (w16) {
+                mbar_arrive_expect_tx(smem_u32(&raw_full), (unsigned)(live * 16 * kRawRow));
+                for (int i = 0; i < live; i++)
+                    bulk_g2s(smem_u32(raw + (size_t)i * 16 * kRawRow), w16 + ((size_t)(tile0 + i) * nSB + sb0 + sb) * (16 * kRawRow), 16 * kRawRow,
+                             smem_u32(&raw_full));
+            } else {
+                mbar_arrive_expect_tx(smem_u32(&raw_full), (unsigned)(128 * NT * kRawRow));
+                tensor_g2s_2d(smem_u32(raw), &wmap, (sb0 + sb) * kRawRow, n0, smem_u32(&raw_full));
+            }
             issued = sb + 1;
         }
         // a copy still in flight must land before the CTA may leave: a bounded wait on its barrier
@@ -484,8 +495,8 @@ int flush_pending_parts(b200_ctx* ctx) {
 }
 
 int launch_q4k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
-                           size_t scratch_bytes, int* err_flag) {
-    return launch_q4k_matmul_umma_swiglu(ctx, W, N, K, aq, T, dst, ldd, scratch, scratch_bytes, err_flag, ActQ{}, false, nullptr);
+                           size_t scratch_bytes, int* err_flag, const uint8_t* W_tiles) {
+    return launch_q4k_matmul_umma_swiglu(ctx, W, N, K, aq, T, dst, ldd, scratch, scratch_bytes, err_flag, ActQ{}, false, nullptr, nullptr, W_tiles);
 }
 
 // With `sw` set and W = gate|up interleaved by 128 rows ([2F][K]): when the launch has two weight tiles per CTA and no K
@@ -498,11 +509,14 @@ __half* x16_next_slot(b200_ctx* ctx) {
 }
 
 int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
-                                  size_t scratch_bytes, int* err_flag, ActQ sw, bool force, bool* fused, __half* sw_x16) {
+                                  size_t scratch_bytes, int* err_flag, ActQ sw, bool force, bool* fused, __half* sw_x16, const uint8_t* W_tiles) {
     if (fused) *fused = false;
+    static const bool no_tiles_env = getenv("B200_UMMA_ROW_MAJOR") != nullptr;  // measurement: keep the tiled copies of the row-major matrix
+    if (no_tiles_env && W) W_tiles = nullptr;
+    if (!W && !W_tiles) B200_FAIL(ctx, B200_BAD_ARGUMENT, "no weights");
     ST_TRY(flush_pending_parts(ctx));  // the scratch is about to be reused
     if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q4_K needs K %% 256 == 0");
-    if (reinterpret_cast<uintptr_t>(W) & 15) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tcgen05 matmul wants 16-byte aligned weights");
+    if ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(W_tiles)) & 15) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tcgen05 matmul wants 16-byte aligned weights");
     const int nSB = K / 256, t_tiles = ceil_div(T, 256);
     // two weight tiles per CTA halve the activation traffic; one per CTA when that is what it takes to cover the SMs
     const int max_splits = std::max(1, std::min(4, nSB / 2));
@@ -536,7 +550,8 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     }
-    const CUtensorMap* wmap = q4k_weight_map(ctx, W, N, nSB, 128 * NT);
+    static const CUtensorMap no_map{};  // the tile-major copy is fetched with plain bulk copies
+    const CUtensorMap* wmap = W_tiles ? &no_map : q4k_weight_map(ctx, W, N, nSB, 128 * NT);
     if (!wmap) return B200_CUDA_ERROR;
     dim3 grid(n_tiles, t_tiles, splits);
     float* out = splits > 1 ? part : dst;
@@ -547,9 +562,9 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
         int8_t* const no_codes = nullptr;
         float* const no_scales = nullptr;
         __half* const no_x16 = nullptr;
-        if (fuse) launch_pdl(q4k_umma_gemm_kernel<2, true>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, sw.codes, sw.scales, sw_x16);
-        else if (NT == 2) launch_pdl(q4k_umma_gemm_kernel<2, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16);
-        else launch_pdl(q4k_umma_gemm_kernel<1, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16);
+        if (fuse) launch_pdl(q4k_umma_gemm_kernel<2, true>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, sw.codes, sw.scales, sw_x16, W_tiles);
+        else if (NT == 2) launch_pdl(q4k_umma_gemm_kernel<2, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16, W_tiles);
+        else launch_pdl(q4k_umma_gemm_kernel<1, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16, W_tiles);
     }
     LAUNCH_CHECK(ctx);
     if (fuse && fused) *fused = true;

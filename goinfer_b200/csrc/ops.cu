@@ -126,6 +126,8 @@ int b200_op_q4k_dequant(b200_ctx* ctx, const uint8_t* w, int rows, int cols, flo
 
 int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, int K, int N, int klass, float* dst) {
     if (K % 256) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K %% 256");
+    const bool tiles_only = klass == 7;  // the fast class as a model runs it: only the tile-major copy is given to the kernels
+    if (tiles_only) klass = 0;
     Tmp t;
     const size_t wb = (size_t)N * K / 256 * 144;
     uint8_t* dw; float *da, *dd; ActQ aq;
@@ -136,11 +138,11 @@ int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, i
     UmmaScratch us(ctx);
     ST_TRY(us.ensure(t, M, K, N));
     uint8_t* dtiles = nullptr;   // the tile-by-tile copy a model keeps for the small-batch kernel
-    if ((klass == 0 || klass == 2 || klass == 5) && M <= 32) {
+    if (tiles_only || ((klass == 0 || klass == 2 || klass == 5) && M <= 32)) {
         TMP_GET(ctx, t, dtiles, q4k_tiles_bytes(N, K));
         ST_TRY(launch_q4k_to_tiles(ctx, dw, N, K, dtiles));
     }
-    ST_TRY(launch_q4k_matmul(ctx, dw, N, K, aq, M, dd, N, klass, dtiles));
+    ST_TRY(launch_q4k_matmul(ctx, tiles_only ? nullptr : dw, N, K, aq, M, dd, N, klass, dtiles));
     D2H(ctx, dst, dd, (size_t)M * N * 4);
     SYNC(ctx);
     return us.check();
@@ -524,6 +526,8 @@ int b200_bench_kq_matmul(b200_ctx* ctx, int kind, int M, int K, int N, int n_wei
 
 int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_weight_copies, int warmup, int iters, float* ms_out) {
     if (K % 256 || M <= 0 || N <= 0 || n_weight_copies <= 0 || iters <= 0) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad bench shape");
+    const bool tiles_only = klass == 7;  // the fast class as a model runs it: only the tile-major copy is given to the kernels
+    if (tiles_only) klass = 0;
     Tmp t;
     const size_t wb = (size_t)N * K / 256 * 144;
     uint8_t* dw; float *da, *dd; ActQ aq;
@@ -534,7 +538,7 @@ int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_w
     // up to 32 rows the fast class streams the tile-by-tile copy of the matrix a model makes at finalize
     uint8_t* dtiles = nullptr;
     const size_t tb = q4k_tiles_bytes(N, K);
-    if ((klass == 0 || klass == 5) && M <= 32) {
+    if (tiles_only || ((klass == 0 || klass == 5) && M <= 32)) {
         TMP_GET(ctx, t, dtiles, tb * n_weight_copies);
         for (int c = 0; c < n_weight_copies; c++) ST_TRY(launch_q4k_to_tiles(ctx, dw + (size_t)c * wb, N, K, dtiles + (size_t)c * tb));
     }
@@ -556,9 +560,10 @@ int b200_bench_q4k_matmul(b200_ctx* ctx, int M, int K, int N, int klass, int n_w
         ctx->x16_ready = reinterpret_cast<const __half*>(ctx->umma_scratch);
     }
     auto tiles_of = [&](int i) { return dtiles ? dtiles + (size_t)(i % n_weight_copies) * tb : nullptr; };
-    for (int i = 0; i < warmup; i++) ST_TRY(launch_q4k_matmul(ctx, dw + (size_t)(i % n_weight_copies) * wb, N, K, aq, M, dd, N, klass, tiles_of(i)));
+    auto rows_of = [&](int i) -> const uint8_t* { return tiles_only ? nullptr : dw + (size_t)(i % n_weight_copies) * wb; };
+    for (int i = 0; i < warmup; i++) ST_TRY(launch_q4k_matmul(ctx, rows_of(i), N, K, aq, M, dd, N, klass, tiles_of(i)));
     CUDA_TRY(ctx, cudaEventRecord(e0, ctx->stream));
-    for (int i = 0; i < iters; i++) ST_TRY(launch_q4k_matmul(ctx, dw + (size_t)(i % n_weight_copies) * wb, N, K, aq, M, dd, N, klass, tiles_of(i)));
+    for (int i = 0; i < iters; i++) ST_TRY(launch_q4k_matmul(ctx, rows_of(i), N, K, aq, M, dd, N, klass, tiles_of(i)));
     CUDA_TRY(ctx, cudaEventRecord(e1, ctx->stream));
     SYNC(ctx);
     float ms = 0;

@@ -96,8 +96,7 @@ def decode_tp(shape: str, batch: int, ctx_lo: int, ctx_hi: int, seed: int, steps
     ctx_all = np.random.default_rng(seed).integers(ctx_lo, ctx_hi + 1, batch).astype(np.int32)
     growth = steps + warmup + 8
     per_pos = 2 * sl.n_kv_heads * s.head_dim * 2 * L                       # this rank's KV bytes per position, all layers
-    # the Q4_K projections are held twice in the fast class (row-major and tile by tile for the small-batch kernel)
-    w_bytes = 2 * L * (s.hidden * (sl.n_heads + 2 * sl.n_kv_heads) * s.head_dim + s.hidden * sl.n_heads * s.head_dim
+    w_bytes = L * (s.hidden * (sl.n_heads + 2 * sl.n_kv_heads) * s.head_dim + s.hidden * sl.n_heads * s.head_dim
                        + 3 * s.hidden * sl.ffn) * 144 / 256 + (s.vocab + s.vocab // world) * s.hidden * 2
     budget = (kv_budget_gb * 1e9) if kv_budget_gb > 0 else (178e9 - w_bytes - 6e9)
     need = np.cumsum((np.ceil((ctx_all + growth) / 16) * 16) * per_pos)

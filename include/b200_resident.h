@@ -243,7 +243,8 @@ int b200_op_q4k_dequant(b200_ctx* ctx, const uint8_t* w, int rows, int cols, flo
 /* dst[M][N] = a[M][K] . W^T, W Q4_K [N][K]; activations quantized per 32 (actgroup.cu:311-355).
  * klass: 0 = library choice by M (fast class), 1 = exact kernels, 2 = the fast class's tcgen05 fp16 kernel at any M; for kernel
  * comparisons: 3 = the register-direct integer kernels, 4 = the streaming integer kernel in its one-chain form (the exact
- * class's bits), 5 = the small-batch fp16 kernel (M <= 32), 6 = the streaming integer kernel with K split. */
+ * class's bits), 5 = the small-batch fp16 kernel (M <= 32), 6 = the streaming integer kernel with K split, 7 = the fast class
+ * given only the tile-major copy of W, as a fast-class model keeps it after b200_finalize_weights. */
 int b200_op_q4k_matmul(b200_ctx* ctx, const uint8_t* w, const float* a, int M, int K, int N, int klass,
                        float* dst);
 /* dst[M][N] = a[M][K] . w[N][K]^T over f16 weights (the LM head's kind, decoder/forwardn.go:800-831): klass 0 picks by

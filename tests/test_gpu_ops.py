@@ -501,6 +501,29 @@ def test_a_bounded_device_wait_that_runs_out_reports_timeout_and_the_context_sta
     np.testing.assert_allclose(ops.f16_matmul(w, a, klass=2), want, atol=2e-4, rtol=1e-4)
 
 
+@pytest.mark.parametrize("M", [1, 2, 3, 20, 33, 100, 256, 300])
+def test_q4k_matmul_from_tile_major_copy_only(ops, oracle_lib, M):
+    """A fast-class model keeps only the tile-major copy of a Q4_K projection (klass 7 gives the kernels nothing else): the
+    one- and two-row dp4a kernel addresses it with a 2304-byte super-block stride, the small-batch kernel streams it, and the
+    tcgen05 kernel's loader fetches 2304 contiguous bytes per 16 rows instead of a tiled box. The last two must give the bits
+    the same kernel gives from the row-major matrix (same products, same order); the dp4a kernel over tiles partitions a row's
+    super-blocks over lanes and warps in another way, so its f32 sums are those of the row-major one to rounding. Ragged row
+    counts too (N not a multiple of 16 or of 128: the copy is padded with zero blocks to whole 16-row tiles, and 16-row
+    tiles past the matrix are not fetched)."""
+    rng = np.random.default_rng(170 + M)
+    for N, K in ((100, 256), (448 * 16 + 20, 512), (1000, 768), (4096, 2048), (130, 4096)):
+        raw = q4k.quantize(rng.normal(0, 0.02, (N, K)).astype(np.float32))
+        a = rng.normal(0, 1, (M, K)).astype(np.float32)
+        got = ops.q4k_matmul(raw, a, N, klass=7)
+        ref = oracle_lib.op_q4k_matmul_f64(raw, a, N)
+        if M <= 2:   # integer dots, f32 sums in another order
+            assert np.abs(got - ref).max() <= 2e-5 * np.abs(ref).max(), (N, K, np.abs(got - ref).max() / np.abs(ref).max())
+            assert np.array_equal(got, ops.q4k_matmul(raw, a, N, klass=7))
+        else:
+            assert np.array_equal(got, ops.q4k_matmul(raw, a, N, klass=0)), (N, K)
+            assert np.abs(got - ref).max() <= 4e-3 * np.abs(ref).max(), (N, K)
+
+
 @pytest.mark.parametrize("M", [1, 2, 3, 7, 8, 9, 16, 17, 25, 32])
 def test_q4k_matmul_small_batch_kernel(ops, oracle_lib, M):
     """The fast class's kernel for up to 32 rows (klass 5 forces it; klass 0 picks it from 3 rows): the matrix re-laid tile by
