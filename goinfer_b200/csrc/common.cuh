@@ -298,6 +298,49 @@ int flush_pending_parts(b200_ctx*);
 
 // tp.cu: collectives over the context's communicator, on its stream
 int tp_all_reduce_sum(b200_ctx*, float* buf, size_t n);
+// A model's peer-visible step buffers (tensor parallel on the GPUs of one host): one device block per rank, each mapped
+// into every other rank's process, so that one kernel can sum the ranks' partial o / down products over NVLink, add the
+// residual, apply the next RMSNorm, quantize per 32, and store the codes into every rank's activation buffer
+// (launch_tp_reduce_norm_quant). Offsets are the same on every rank.
+constexpr int kTpMaxRanks = 8;
+struct TpFused {
+    bool on = false;
+    int t = 1, rank = 0, max_rows = 0, H = 0;
+    uint8_t* base = nullptr;              // this rank's block (cudaMalloc)
+    uint8_t* peer[kTpMaxRanks] = {};      // every rank's block as mapped here; peer[rank] == base
+    size_t off_part = 0, off_stage = 0, off_h = 0, off_codes = 0, off_scales = 0, off_row_flags = 0, off_cta_flags = 0, bytes = 0;
+    unsigned seq = 0;                     // one more per launch, the same on every rank
+    // the flagless form (launch_tp_reduce_norm_quant_ll): staging, codes and scales twice, used in turn; a word that has not
+    // arrived yet holds a value no sender ever stores
+    size_t off_stage_ll[2] = {0, 0}, off_codes_ll[2] = {0, 0}, off_scales_ll[2] = {0, 0};
+    unsigned ll_calls = 0;                // the same on every rank
+    int armed[2] = {0, 0};                // leading rows of each codes/scales buffer known to hold the not-arrived value
+    bool use_ll = true;
+    long long wait_ns = 0;                // how long a rank waits for its peers before it gives up
+    long long* phase_ns = nullptr;        // measurement only: where CTA 0 stamps its clock at each stage (5 values)
+    float* part() const { return reinterpret_cast<float*>(base + off_part); }
+    float* h() const { return reinterpret_cast<float*>(base + off_h); }
+    int8_t* codes() const { return reinterpret_cast<int8_t*>(base + off_codes); }
+    float* scales() const { return reinterpret_cast<float*>(base + off_scales); }
+    ActQ aq_ll(int p) const { return ActQ{reinterpret_cast<int8_t*>(base + off_codes_ll[p]), reinterpret_cast<float*>(base + off_scales_ll[p])}; }
+};
+void tp_fused_layout(TpFused*, int t, int rank, int max_rows, int H);
+// tp.cu: allocates the block, trades the handles over the communicator and maps the peers' blocks; `on` stays false (and
+// the step keeps NCCL's all-reduce) when any rank could not, which every rank learns before it returns
+int tp_fused_setup(b200_ctx*, TpFused*, int max_rows, int H);
+void tp_fused_teardown(b200_ctx*, TpFused*);
+// tp_fused.cu. Rank r owns rows [r*ceil(T/t), ...): x = h + sum over ranks (rank order) of part; mode 0: h <- x on the
+// owner, RMSNorm(x)*w quantized per 32 into every rank's codes/scales; mode 1: x into every rank's h (no norm).
+// Every rank must launch it with the same T and mode, in the same order. phases (1 push, 2 reduce) and use_flags are for
+// the one-GPU emulation, which runs every rank's push before any reduce and needs no flags.
+int launch_tp_reduce_norm_quant(b200_ctx*, TpFused*, int T, const float* norm_w, float eps, int mode, int phases = 3, bool use_flags = true);
+// The same work as mode 0 without flags or fences: the data words announce themselves. Staging and activation buffers
+// start out filled with a value no sender stores (a NaN pattern for f32 words, byte -128 for codes); a reader polls a word
+// until it differs and, for staging, puts the value back. Buffers alternate between calls, so a buffer is rearmed a whole
+// call before it is written again. *out is the activation buffer this call filled (valid when the kernel has ended).
+// phases: 1 push, 2 reduce, 4 rearm + wait for every row's codes (7 = all; split only by the one-GPU emulation).
+int tp_fused_arm(b200_ctx*, TpFused*);  // fills the flagless form's buffers with the not-arrived values
+int launch_tp_reduce_norm_quant_ll(b200_ctx*, TpFused*, int T, const float* norm_w, float eps, ActQ* out, int phases = 7);
 int tp_all_gather_columns(b200_ctx*, const float* local, int rows, int w, float* gathered, float* full);
 
 // attention_prefill.cu: causal attention for a run of rows of one slot at consecutive positions pos0.. (fast class)

@@ -9,66 +9,9 @@
 //   residual     decoder/model_forward.go:98-119
 //   expert fold  decoder/mlp.go:729-745 (out += w*src, rank order, no contraction)
 #include "common.cuh"
+#include "rowquant.cuh"
 
 namespace {
-
-__device__ __forceinline__ double warp_sum_f64(double v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-
-// Quantizes one group of 32 values held one per lane. Lane 0 writes the scale and the group sum.
-__device__ __forceinline__ void quant_group_warp(float y, int8_t* codes_g, float* sc_out, float* asum_out, int lane) {
-    float ma = fabsf(y);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, o));
-    float sc = __fdiv_rn(ma, 127.f);
-    float inv = sc > 0.f ? __fdiv_rn(1.f, sc) : 0.f;
-    int q = __float2int_rn(__fmul_rn(y, inv));
-    q = max(-127, min(127, q));
-    int sum = q;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    codes_g[lane] = (int8_t)q;
-    if (lane == 0) {
-        *sc_out = sc;
-        *asum_out = __fmul_rn(sc, (float)sum);
-    }
-}
-
-// The same quantizer for a group held 8 values per lane by four consecutive lanes (q4 = lane & 3 is the lane's place in
-// its group). The maximum and the integer sum do not depend on the order they are taken in, so the codes, scale and sum
-// are those of quant_group_warp. Every lane of the warp must call it (lanes past the row pass zeros and `live` false).
-__device__ __forceinline__ void quant_group_quad(const float (&y)[8], int8_t* codes_g, float* sc_out, float* asum_out, int q4, bool live,
-                                                 float* deq = nullptr /* [8]: code * scale */) {
-    float ma = 0.f;
-#pragma unroll
-    for (int u = 0; u < 8; u++) ma = fmaxf(ma, fabsf(y[u]));
-    ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, 1));
-    ma = fmaxf(ma, __shfl_xor_sync(0xffffffffu, ma, 2));
-    const float sc = __fdiv_rn(ma, 127.f);
-    const float inv = sc > 0.f ? __fdiv_rn(1.f, sc) : 0.f;
-    int sum = 0;
-    unsigned w[2] = {0u, 0u};
-#pragma unroll
-    for (int u = 0; u < 8; u++) {
-        int q = __float2int_rn(__fmul_rn(y[u], inv));
-        q = max(-127, min(127, q));
-        sum += q;
-        w[u >> 2] |= (unsigned)(q & 0xff) << (8 * (u & 3));
-        if (deq) deq[u] = __fmul_rn((float)q, sc);
-    }
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    if (live) {
-        *reinterpret_cast<uint2*>(codes_g + 8 * q4) = make_uint2(w[0], w[1]);
-        if (q4 == 0) {
-            *sc_out = sc;
-            *asum_out = __fmul_rn(sc, (float)sum);
-        }
-    }
-}
 
 __global__ void embed_gather_kernel(const void* __restrict__ table, int kind, int n_rows, const int32_t* __restrict__ ids, int H,
                                     float scale, float* __restrict__ h) {

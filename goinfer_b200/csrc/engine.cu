@@ -303,6 +303,8 @@ struct b200_model {
     size_t x16_slot_bytes = 0;     // its two fp16 activation slots (0: the scratch has none)
     size_t umma_bytes = 0;
     int* err_flag = nullptr;       // raised by a bounded device-side wait that gave up
+    ActQ aq_h_local;               // the hidden-width activation buffers this GPU's own kernels fill (aq_h may point at a peer-filled pair)
+    TpFused tpf;                   // tensor parallel: the peer-visible h / partial-product / activation buffers (tpf.on) 
     float* exact_scores = nullptr;  // exact class: [MR*nH][ctx_cap]
     void* d_topk = nullptr;  // ForwardTopK's outputs: 1024 ids, 1024 logits, Z
     float *logits_local = nullptr, *logits_gather = nullptr;  // tensor parallel: [MLR][V/t] and the gathered [t][MLR][V/t]
@@ -520,12 +522,26 @@ int run_layers(b200_model* m, int T, int max_keys) {
         return x16_next_slot(ctx);
     };
     const float* delta = nullptr;  // pending residual add, fused into the next norm
+    m->aq_h = m->aq_h_local;
+    // tensor parallel on one host: sums the ranks' partial rows in m->att, adds them to the residual rows, norms with w and
+    // quantizes; m->aq_h then points at the activation buffers every rank's kernel filled
+    auto cross_rank_norm = [&](const float* w) -> int {
+        if (m->tpf.use_ll) return launch_tp_reduce_norm_quant_ll(ctx, &m->tpf, T, w, c.rms_eps, &m->aq_h);
+        ST_TRY(launch_tp_reduce_norm_quant(ctx, &m->tpf, T, w, c.rms_eps, 0));
+        m->aq_h = ActQ{m->tpf.codes(), m->tpf.scales()};
+        return B200_OK;
+    };
+    bool normed_ready = false;     // tensor parallel: the layer's attention norm was applied by the kernel that reduced across the ranks
     for (int l = 0; l < c.n_layers; l++) {
         LayerW& L = m->layers[l];
+        bool reduced = false;  // the down products were already added to the residual rows
         const bool q_in = is_kquant(L.qkv.kind);
-        __half* x16 = q_in ? x16_for(L.qkv) : nullptr;
-        ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, delta, L.attn_norm, T, H, c.rms_eps, q_in ? nullptr : m->normed,
-                                        q_in ? m->aq_h : none, nullptr, x16));
+        __half* x16 = (q_in && !normed_ready) ? x16_for(L.qkv) : nullptr;
+        if (!normed_ready) m->aq_h = m->aq_h_local;
+        if (!normed_ready)  // (tensor parallel: the kernel that summed the last layer's down products has normed and quantized already)
+            ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, delta, L.attn_norm, T, H, c.rms_eps, q_in ? nullptr : m->normed,
+                                            q_in ? m->aq_h : none, nullptr, x16));
+        normed_ready = false;
         // the consumers of the q|k|v, o and down products can add their K-split partials themselves (no reduce kernel)
         static const bool tap_env = getenv("B200_DEBUG_TAP") != nullptr || getenv("B200_NO_DEFER") != nullptr;
         const bool defer = c.tp_size <= 1 && !m->exact_scores && !tap_env;
@@ -573,12 +589,25 @@ int run_layers(b200_model* m, int T, int max_keys) {
         ST_TRY(matmul(m, L.wo, m->ctxb, m->aq_ctx, T, m->att, H));
         ctx->x16_ready = nullptr;
         ctx->defer_reduce = false;
-        if (c.tp_size > 1) ST_TRY(tp_all_reduce_sum(ctx, m->att, (size_t)T * H));  // o is split by input columns: partial sums
+        // o is split by input columns: the ranks hold partial sums. On one host one kernel sums them over peer memory, adds
+        // the residual, norms and quantizes (rows/t of the rows per rank, the codes stored to every rank); else NCCL sums.
+        if (c.tp_size > 1 && !m->tpf.on) ST_TRY(tp_all_reduce_sum(ctx, m->att, (size_t)T * H));
         if (c.n_experts == 0) {
             const bool g_q = is_kquant(L.gu.kind), d_q = is_kquant(L.down.kind);
-            __half* x16g = g_q ? x16_for(L.gu) : nullptr;
-            ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, m->att, L.ffn_norm, T, H, c.rms_eps, g_q ? nullptr : m->normed,
-                                            g_q ? m->aq_h : none, nullptr, x16g));
+            __half* x16g = nullptr;
+            if (m->tpf.on && g_q) {
+                ST_TRY(cross_rank_norm(L.ffn_norm));
+            } else {
+                m->aq_h = m->aq_h_local;
+                const float* add = m->att;
+                if (m->tpf.on) {  // the summed rows go to every rank's residual stream; the norm below then adds nothing
+                    ST_TRY(launch_tp_reduce_norm_quant(ctx, &m->tpf, T, nullptr, c.rms_eps, 1));
+                    add = nullptr;
+                }
+                x16g = g_q ? x16_for(L.gu) : nullptr;
+                ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, add, L.ffn_norm, T, H, c.rms_eps, g_q ? nullptr : m->normed,
+                                                g_q ? m->aq_h : none, nullptr, x16g));
+            }
             __half* x16d = d_q ? x16_for(L.down) : nullptr;   // the other slot: laid out by whoever quantizes silu(gate) * up
             bool fused = false;
             ctx->x16_ready = x16g;
@@ -601,7 +630,18 @@ int run_layers(b200_model* m, int T, int max_keys) {
             ST_TRY(matmul(m, L.down, m->mid, m->aq_mid, T, m->att, H));
             ctx->x16_ready = nullptr;
             ctx->defer_reduce = false;
-            if (c.tp_size > 1) ST_TRY(tp_all_reduce_sum(ctx, m->att, (size_t)T * H));
+            if (m->tpf.on) {
+                // the down products: summed, added and, when a quantized q|k|v follows, normed with the next layer's weight
+                if (l + 1 < c.n_layers && is_kquant(m->layers[l + 1].qkv.kind)) {
+                    ST_TRY(cross_rank_norm(m->layers[l + 1].attn_norm));
+                    normed_ready = true;
+                } else {
+                    ST_TRY(launch_tp_reduce_norm_quant(ctx, &m->tpf, T, nullptr, c.rms_eps, 1));  // every rank gets the updated rows
+                }
+                reduced = true;
+            } else if (c.tp_size > 1) {
+                ST_TRY(tp_all_reduce_sum(ctx, m->att, (size_t)T * H));
+            }
         } else {
             // routed experts (decoder/mlp.go:36-120): f32 router on the f32 normed row, top-k, grouped expert GEMMs,
             // fold in routing-rank order
@@ -637,10 +677,11 @@ int run_layers(b200_model* m, int T, int max_keys) {
             }
             ST_TRY(launch_fold_experts(ctx, m->eo, m->rw, slot_of, T, kk, H, m->att));
         }
-        delta = m->att;
+        delta = reduced ? nullptr : m->att;
     }
     if (delta) ST_TRY(launch_add(ctx, m->h, delta, (size_t)T * H));
     ST_TRY(flush_pending_parts(ctx));
+    m->aq_h = m->aq_h_local;
     return B200_OK;
 }
 
@@ -877,13 +918,23 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
     ST_TRY(m->dalloc((void**)&m->d_row_mask, (size_t)MR * 4, sb));
     ST_TRY(m->dalloc((void**)&m->d_ids, (size_t)MR * 4, sb));
     ST_TRY(m->dalloc((void**)&m->d_draws, (size_t)MR * sizeof(b200_draw), sb));
-    ST_TRY(m->dalloc((void**)&m->h, (size_t)MR * H * 4, sb));
+    // tensor parallel on one host: the residual rows, the o / down partial products and the activations that follow them
+    // live in a block the other ranks have mapped, for the kernel that sums, norms and quantizes across the ranks
+    if (c.tp_size > 1 && c.n_experts == 0) ST_TRY(tp_fused_setup(ctx, &m->tpf, MR, H));
+    if (m->tpf.on) {
+        m->h = m->tpf.h();
+        if (sb) *sb += m->tpf.bytes;
+    } else {
+        ST_TRY(m->dalloc((void**)&m->h, (size_t)MR * H * 4, sb));
+    }
     ST_TRY(m->dalloc((void**)&m->normed, (size_t)MR * H * 4, sb));
     ST_TRY(m->dalloc((void**)&m->qkv, (size_t)MR * ldq * 4, sb));
     ST_TRY(m->dalloc((void**)&m->ctxb, (size_t)MR * qd * 4, sb));
-    ST_TRY(m->dalloc((void**)&m->att, (size_t)MR * H * 4, sb));
+    if (m->tpf.on) m->att = m->tpf.part();
+    else ST_TRY(m->dalloc((void**)&m->att, (size_t)MR * H * 4, sb));
     ST_TRY(m->dalloc((void**)&m->aq_h.codes, (size_t)MR * H, sb));
     ST_TRY(m->dalloc((void**)&m->aq_h.scales, (size_t)MR * 2 * ceil_div(H, 32) * 4, sb));
+    m->aq_h_local = m->aq_h;
     ST_TRY(m->dalloc((void**)&m->aq_ctx.codes, (size_t)MR * qd, sb));
     ST_TRY(m->dalloc((void**)&m->aq_ctx.scales, (size_t)MR * 2 * ceil_div(qd, 32) * 4, sb));
     if (F) {
@@ -1002,6 +1053,7 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
 void b200_model_free(b200_model* m) {
     if (!m) return;
     cudaStreamSynchronize(m->ctx->stream);
+    tp_fused_teardown(m->ctx, &m->tpf);
     if (m->loop_graph) cudaGraphExecDestroy(m->loop_graph);
     for (void* p : m->allocs) cudaFree(p);
     if (m->p_desc) cudaFreeHost(m->p_desc);
@@ -1013,6 +1065,49 @@ void b200_model_free(b200_model* m) {
 }
 
 int b200_kv_slots(b200_model* m) { return m->c.n_slots; }
+int b200_tp_fused_active(b200_model* m) { return m && m->tpf.on ? 1 : 0; }
+
+int b200_bench_tp_reduce(b200_model* m, int T, int mode, int warmup, int iters, float* ms_out, float* stage_us_out) {
+    b200_ctx* ctx = m->ctx;
+    if (!m->finalized || !m->tpf.on || T < 1 || T > m->MR || iters < 1 || !ms_out) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the cross-rank kernel is not in use, or bad arguments");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    ctx->err_flag = m->err_flag;
+    const float* w = m->layers[0].ffn_norm;
+    auto one = [&]() -> int {  // the form the model's steps use
+        if (mode == 0 && m->tpf.use_ll) return launch_tp_reduce_norm_quant_ll(ctx, &m->tpf, T, w, m->c.rms_eps, nullptr);
+        return launch_tp_reduce_norm_quant(ctx, &m->tpf, T, w, m->c.rms_eps, mode);
+    };
+    for (int i = 0; i < warmup; i++) ST_TRY(one());
+    CUDA_TRY(ctx, cudaEventRecord(m->ev0, ctx->stream));
+    for (int i = 0; i < iters; i++) ST_TRY(one());
+    CUDA_TRY(ctx, cudaEventRecord(m->ev1, ctx->stream));
+    CUDA_TRY(ctx, cudaEventSynchronize(m->ev1));
+    float ms = 0.f;
+    CUDA_TRY(ctx, cudaEventElapsedTime(&ms, m->ev0, m->ev1));
+    *ms_out = ms / iters;
+    if (stage_us_out) {  // one more launch with CTA 0's clock stamped at each stage
+        long long* d_ns = nullptr;
+        long long ns[5] = {0, 0, 0, 0, 0};
+        CUDA_TRY(ctx, cudaMalloc((void**)&d_ns, sizeof ns));
+        CUDA_TRY(ctx, cudaMemsetAsync(d_ns, 0, sizeof ns, ctx->stream));
+        m->tpf.phase_ns = d_ns;
+        const int st = one();
+        m->tpf.phase_ns = nullptr;
+        if (st == B200_OK) cudaMemcpyAsync(ns, d_ns, sizeof ns, cudaMemcpyDeviceToHost, ctx->stream);
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(d_ns);
+        ST_TRY(st);
+        for (int i = 0; i < 4; i++) stage_us_out[i] = (float)(ns[i + 1] - ns[i]) * 1e-3f;
+    }
+    int gave_up = 0;
+    CUDA_TRY(ctx, cudaMemcpyAsync(&gave_up, m->err_flag, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (gave_up) {
+        cudaMemsetAsync(m->err_flag, 0, 4, ctx->stream);
+        B200_FAIL(ctx, B200_TIMEOUT, "a rank waited for its peers longer than its limit");
+    }
+    return B200_OK;
+}
 
 int b200_reset_slot(b200_model* m, int slot) {
     b200_ctx* ctx = m->ctx;

@@ -9,6 +9,7 @@
 #include <dlfcn.h>
 
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -115,6 +116,83 @@ int b200_tp_destroy(b200_ctx* ctx) {
     ctx->tp_rank = 0;
     if (r != 0) B200_FAIL(ctx, B200_NCCL_ERROR, "NCCL: %s (ncclCommDestroy)", api->error_string(r));
     return B200_OK;
+}
+
+// ---- the peer-visible step buffers of launch_tp_reduce_norm_quant ----
+// Every rank allocates its block, the 64-byte inter-process handles are traded with one all-gather on the communicator,
+// and each rank maps the others' blocks (which also turns peer access on). Whether every rank managed is then agreed
+// with one all-reduce, so that either all of them run the fused kernel or all of them keep NCCL's all-reduce.
+int tp_fused_setup(b200_ctx* ctx, TpFused* f, int max_rows, int H) {
+    f->on = false;
+    if (!ctx->tp_comm || ctx->tp_size < 2) return B200_OK;
+    NcclApi* api = nccl_api();
+    const int t = ctx->tp_size, rank = ctx->tp_rank;
+    // the same answer on every rank: the environment is the launcher's, the shape is the model's
+    bool want = t <= kTpMaxRanks && H % 256 == 0 && H <= 8192 && !getenv("B200_TP_NO_FUSED");
+    tp_fused_layout(f, t, rank, max_rows, H);
+    const char* wait_ms = getenv("B200_TP_WAIT_MS");
+    f->wait_ns = (long long)(wait_ms && atoi(wait_ms) > 0 ? atoi(wait_ms) : 5000) * 1000000ll;
+    if (!want) return B200_OK;
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    int ok = 1;
+    cudaIpcMemHandle_t mine{};
+    if (cudaMalloc((void**)&f->base, f->bytes) != cudaSuccess) { cudaGetLastError(); f->base = nullptr; ok = 0; }
+    // flags at zero and the flagless form's buffers armed, on the stream the handle exchange below runs on: no peer has
+    // this block's handle before these fills are done
+    if (ok && (cudaMemsetAsync(f->base, 0, f->bytes, ctx->stream) != cudaSuccess || tp_fused_arm(ctx, f) != B200_OK ||
+               cudaIpcGetMemHandle(&mine, f->base) != cudaSuccess)) { cudaGetLastError(); ok = 0; }
+    // trade the handles (a rank that failed sends zeros and says so in the agreement below)
+    uint8_t* d_all = nullptr;
+    float* d_ok = nullptr;
+    CUDA_TRY(ctx, cudaMalloc((void**)&d_all, (size_t)(t + 1) * sizeof mine));
+    CUDA_TRY(ctx, cudaMalloc((void**)&d_ok, 4));
+    CUDA_TRY(ctx, cudaMemcpyAsync(d_all + (size_t)t * sizeof mine, &mine, sizeof mine, cudaMemcpyHostToDevice, ctx->stream));
+    NCCL_TRY(ctx, api, api->all_gather(d_all + (size_t)t * sizeof mine, d_all, sizeof mine, kNcclUint8, ctx->tp_comm, ctx->stream));
+    std::vector<cudaIpcMemHandle_t> all(t);
+    CUDA_TRY(ctx, cudaMemcpyAsync(all.data(), d_all, (size_t)t * sizeof mine, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int k = 0; k < t && ok; k++) {
+        if (k == rank) { f->peer[k] = f->base; continue; }
+        void* p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, all[k], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); ok = 0; break; }
+        f->peer[k] = reinterpret_cast<uint8_t*>(p);
+    }
+    // the agreement: the sum of the ranks' "I can" is t or it is not
+    const float okf = ok ? 1.f : 0.f;
+    CUDA_TRY(ctx, cudaMemcpyAsync(d_ok, &okf, 4, cudaMemcpyHostToDevice, ctx->stream));
+    NCCL_TRY(ctx, api, api->all_reduce(d_ok, d_ok, 1, kNcclFloat32, kNcclSum, ctx->tp_comm, ctx->stream));
+    float sum = 0.f;
+    CUDA_TRY(ctx, cudaMemcpyAsync(&sum, d_ok, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    cudaFree(d_all);
+    cudaFree(d_ok);
+    if ((int)(sum + 0.5f) == t) {
+        f->on = true;
+        f->use_ll = !getenv("B200_TP_FLAGS");   // measurement: the form with flags and fences for every call
+        return B200_OK;
+    }
+    tp_fused_teardown(ctx, f);
+    return B200_OK;
+}
+
+// Unmaps the peers' blocks, waits (on the communicator, when it is still there) until every rank has, and frees this one's.
+void tp_fused_teardown(b200_ctx* ctx, TpFused* f) {
+    if (!f->base && !f->on) return;
+    cudaStreamSynchronize(ctx->stream);
+    for (int k = 0; k < f->t; k++)
+        if (k != f->rank && f->peer[k]) cudaIpcCloseMemHandle(f->peer[k]);
+    if (f->t > 1 && ctx->tp_comm) {  // every rank comes here (the ranks agreed on the outcome of the setup)
+        NcclApi* api = nccl_api();
+        float* d = nullptr;
+        if (cudaMalloc((void**)&d, 4) == cudaSuccess) {
+            cudaMemsetAsync(d, 0, 4, ctx->stream);
+            api->all_reduce(d, d, 1, kNcclFloat32, kNcclSum, ctx->tp_comm, ctx->stream);
+            cudaStreamSynchronize(ctx->stream);
+            cudaFree(d);
+        }
+    }
+    if (f->base) cudaFree(f->base);
+    *f = TpFused{};
 }
 
 // buf[n] <- sum over ranks, in place, on the context's stream

@@ -149,6 +149,13 @@ def decode_tp(shape: str, batch: int, ctx_lo: int, ctx_hi: int, seed: int, steps
     check(lib.b200_decode_loop_device(m, b_fit, p32(slot), p32(pos), p32(first), 2, 1, None, C.byref(ms)))
     lib.b200_profile_read(bctx, tag_ms, tag_n, 8)
     lib.b200_profile(bctx, 0)
+    alone_us = None
+    if lib.b200_tp_fused_active(m):   # the cross-rank kernel by itself, launches back to back on every rank at once
+        one, stages = C.c_float(), (C.c_float * 4)()
+        dist.barrier()
+        check(lib.b200_bench_tp_reduce(m, b_fit, 0, 5, 50, C.byref(one), stages))
+        alone_us = {"per_launch": one.value * 1e3, "first_cta": {"push": stages[0], "wait_and_reduce": stages[1], "stores_done_or_rearm": stages[2], "wait_for_peers": stages[3]},
+                    "form": "flags and fences" if os.environ.get("B200_TP_FLAGS") else "words that announce themselves"}
     names = ("attn_split", "attn_combine", "q4k_matmul", "head_matmul", "norm_quant", "rope_kvstore", "swiglu_quant", "collectives")
     out = None
     if rank == 0:
@@ -157,10 +164,13 @@ def decode_tp(shape: str, batch: int, ctx_lo: int, ctx_hi: int, seed: int, steps
                "tp": world, "layers": L, "batch": b_fit, "batch_asked": batch, "steps": steps, "warmup": warmup,
                "ms_per_step": dev_ms / steps, "tok_s": b_fit * steps / (dev_ms * 1e-3), "gpu_launches_per_rank": launches,
                "ranks_drew_the_same_ids": same, "kv_bytes_per_step_per_rank": keys * per_pos,
-               "all_reduce_bytes_per_step": 2 * L * b_fit * s.hidden * 4,
+               "cross_rank_sum_bytes_per_step": 2 * L * b_fit * s.hidden * 4,
                "memory_per_rank": {"weights_gb": caps.weight_bytes / 1e9, "kv_gb": caps.kv_bytes / 1e9, "scratch_gb": caps.scratch_bytes / 1e9},
                "hbm_floor_ms": (keys * per_pos + caps.weight_bytes) / 6540.5e9 * 1e3,
                "nvls": os.environ.get("NCCL_NVLS_ENABLE", "library default"),
+               "cross_rank_sum": ("one kernel over peer memory: sum of the ranks' partial rows + residual + RMSNorm + per-32 quantizer, rows/t per rank, "
+                                  "codes stored to every rank" if lib.b200_tp_fused_active(m) else "ncclAllReduce (f32) + the norm kernel on every rank"),
+               "cross_rank_sum_us_alone": alone_us,
                "breakdown_ms_per_step_rank0": {n: round(tag_ms[i] / 2, 4) for i, n in enumerate(names) if tag_n[i]}}
     dist.barrier()
     r.Close()

@@ -67,6 +67,26 @@ int b200_bench_prefill_attention(b200_ctx* ctx, int rows, int pos0, int n_heads,
  * the entry point that launched it reports B200_TIMEOUT. (0, -1) disarms. Nothing faults or spins without a limit. */
 int b200_debug_wait_fault(b200_ctx* ctx, int polls, int withhold_chunk);
 
+/* 1 when the model's tensor-parallel layers sum their partial products with the library's own kernel over peer memory
+ * (the ranks share a host and could map one another's buffers), 0 when they call NCCL's all-reduce. */
+int b200_tp_fused_active(b200_model* m);
+/* Average device milliseconds of that kernel alone on T rows of the model's width, `iters` launches back to back after
+ * `warmup` (mode 0: norm + quantize to every rank, 1: rows to every rank). Every rank must call it with the same arguments
+ * at the same point; it overwrites the model's step scratch. B200_BAD_ARGUMENT when the kernel is not in use.
+ * stage_us_out (4 floats, or NULL): from one more launch, how long the kernel's first CTA spent pushing partial rows to
+ * their owners, waiting for and reducing its own rows, completing its stores, and waiting for the peers' stores. */
+int b200_bench_tp_reduce(b200_model* m, int T, int mode, int warmup, int iters, float* ms_out, float* stage_us_out);
+
+/* Test hook for the tensor-parallel reduce + residual + RMSNorm + quantize kernel on ONE GPU: `t` blocks on this device
+ * stand for the ranks' peer-visible blocks, and the kernel is launched once per rank, one launch after the other, with its
+ * cross-rank waits left out (kernels that wait for one another must not share a GPU). parts [t][T][H] are the ranks'
+ * partial products, h [T][H] the residual rows every rank starts from, w [H] the norm weight. mode 0: every rank's view of
+ * the codes [t][T][H] and scales [t][T][2*H/32] and its residual rows h_out [t][T][H] (updated on the owner only);
+ * mode 1: h_out holds the summed rows on every rank; mode 2: mode 0's work in the form without flags (words that announce
+ * themselves), three calls in a row on the same inputs so that both buffer pairs are used, rearmed and used again. */
+int b200_debug_tp_reduce_emulated(b200_ctx* ctx, int t, int T, int H, const float* parts, const float* h, const float* w,
+                                  float eps, int mode, int8_t* codes_out, float* scales_out, float* h_out);
+
 #ifdef __cplusplus
 }
 #endif

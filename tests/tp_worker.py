@@ -23,8 +23,15 @@ def main():
     tensors = list(synth.host_weights(s, seed=3))
     rng = np.random.default_rng(8)
     prompts = [rng.integers(0, s.vocab, n).tolist() for n in (37, 9)]
-    for klass in (abi.CLASS_AUTO, abi.CLASS_EXACT):
+    # both kernel classes; the fast class also with the cross-rank sums left to NCCL's all-reduce instead of the library's
+    # own kernel over peer memory
+    for klass, own_kernel in ((abi.CLASS_AUTO, True), (abi.CLASS_EXACT, True), (abi.CLASS_AUTO, False)):
+        if own_kernel:
+            os.environ.pop("B200_TP_NO_FUSED", None)
+        else:
+            os.environ["B200_TP_NO_FUSED"] = "1"
         r = tp.build_rank(dist, s, synth.make_cfg(sl, 4, 128, 16, 0, 96, klass), dev, tensors)
+        assert bool(r.drv.fn("tp_fused_active")(r.m)) == own_kernel, "the ranks could not map one another's step buffers"
         outs = [r.PrefillLast(None, 0, i, tokens=p) for i, p in enumerate(prompts)]
         ids = []
         toks = [int(np.argmax(o)) for o in outs]
