@@ -340,7 +340,8 @@ int launch_tp_reduce_norm_quant(b200_ctx*, TpFused*, int T, const float* norm_w,
 // call before it is written again. *out is the activation buffer this call filled (valid when the kernel has ended).
 // phases: 1 push, 2 reduce, 4 rearm + wait for every row's codes (7 = all; split only by the one-GPU emulation).
 int tp_fused_arm(b200_ctx*, TpFused*);  // fills the flagless form's buffers with the not-arrived values
-int launch_tp_reduce_norm_quant_ll(b200_ctx*, TpFused*, int T, const float* norm_w, float eps, ActQ* out, int phases = 7);
+// given: this rank's product as K-split partials (else the ones the matmul left pending for the block's product, if any).
+int launch_tp_reduce_norm_quant_ll(b200_ctx*, TpFused*, int T, const float* norm_w, float eps, ActQ* out, int phases = 7, const Parts* given = nullptr);
 int tp_all_gather_columns(b200_ctx*, const float* local, int rows, int w, float* gathered, float* full);
 
 // attention_prefill.cu: causal attention for a run of rows of one slot at consecutive positions pos0.. (fast class)

@@ -544,7 +544,12 @@ int run_layers(b200_model* m, int T, int max_keys) {
         normed_ready = false;
         // the consumers of the q|k|v, o and down products can add their K-split partials themselves (no reduce kernel)
         static const bool tap_env = getenv("B200_DEBUG_TAP") != nullptr || getenv("B200_NO_DEFER") != nullptr;
-        const bool defer = c.tp_size <= 1 && !m->exact_scores && !tap_env;
+        // (tensor parallel: only where the cross-rank kernel, which adds them like the norm kernel does, is the consumer)
+        const bool can_defer = !m->exact_scores && !tap_env;
+        const bool tp_ll = m->tpf.on && m->tpf.use_ll;
+        const bool defer = can_defer && (c.tp_size <= 1 || m->tpf.on);
+        const bool defer_o = can_defer && (c.tp_size <= 1 || (tp_ll && c.n_experts == 0 && is_kquant(L.gu.kind)));
+        const bool defer_down = can_defer && (c.tp_size <= 1 || (tp_ll && l + 1 < c.n_layers && is_kquant(m->layers[l + 1].qkv.kind)));
         ctx->defer_reduce = defer;
         ctx->x16_ready = x16;
         ST_TRY(matmul(m, L.qkv, m->normed, m->aq_h, T, m->qkv, ldq));
@@ -584,7 +589,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
             }
         }
         ctx->x16_want = nullptr;
-        ctx->defer_reduce = defer;
+        ctx->defer_reduce = defer_o;
         ctx->x16_ready = (x16o && ctx->x16_done == T) ? x16o : nullptr;   // every context row was laid out
         ST_TRY(matmul(m, L.wo, m->ctxb, m->aq_ctx, T, m->att, H));
         ctx->x16_ready = nullptr;
@@ -625,7 +630,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
             if (!fused)
                 ST_TRY(launch_swiglu_quant(ctx, m->gu, T, c.ffn, 2 * c.ffn, d_q ? nullptr : m->mid, d_q ? m->aq_mid : none,
                                            c.kernel_class == B200_CLASS_EXACT, L.gu_il, x16d));
-            ctx->defer_reduce = defer;
+            ctx->defer_reduce = defer_down;
             ctx->x16_ready = x16d;
             ST_TRY(matmul(m, L.down, m->mid, m->aq_mid, T, m->att, H));
             ctx->x16_ready = nullptr;

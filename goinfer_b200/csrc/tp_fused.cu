@@ -222,13 +222,29 @@ __device__ __forceinline__ bool poll_v4(const void* p, unsigned none, long long 
     return true;
 }
 
+// eight values of this rank's partial product at element i: the matmul's output, or, when it left its K-split partials for
+// this kernel, their sum in split order starting from the first
+__device__ __forceinline__ void own_partial8(const float* __restrict__ part, const float* __restrict__ kparts, int n_kparts, size_t kpart_stride,
+                                             size_t i, float (&v)[8]) {
+    const float* src = n_kparts ? kparts + i : part + i;
+    float4 a = __ldcg(reinterpret_cast<const float4*>(src)), b = __ldcg(reinterpret_cast<const float4*>(src + 4));
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    for (int k = 1; k < n_kparts; k++) {
+        a = __ldcg(reinterpret_cast<const float4*>(src + (size_t)k * kpart_stride));
+        b = __ldcg(reinterpret_cast<const float4*>(src + (size_t)k * kpart_stride + 4));
+        v[0] = __fadd_rn(v[0], a.x); v[1] = __fadd_rn(v[1], a.y); v[2] = __fadd_rn(v[2], a.z); v[3] = __fadd_rn(v[3], a.w);
+        v[4] = __fadd_rn(v[4], b.x); v[5] = __fadd_rn(v[5], b.y); v[6] = __fadd_rn(v[6], b.z); v[7] = __fadd_rn(v[7], b.w);
+    }
+}
+
 struct TpLLOffsets {
     size_t part, h, stage, codes, scales, next_codes, next_scales;  // of this call's buffers and of the next call's
 };
 
 __global__ void __launch_bounds__(1024) tp_ll_reduce_norm_quant_kernel(TpPeers peers, TpLLOffsets off, int rank, int t, int T, int H,
                                                                        const float* __restrict__ w, float eps, int phases, long long wait_ns,
-                                                                       int* __restrict__ err_flag, long long* __restrict__ stage_ns) {
+                                                                       int* __restrict__ err_flag, long long* __restrict__ stage_ns,
+                                                                       const float* __restrict__ kparts, int n_kparts, size_t kpart_stride) {
     __shared__ double red[32];
     const int rows_per = (T + t - 1) / t, nG = H >> 5, c = threadIdx.x, nW = blockDim.x >> 5;
     const int q4 = threadIdx.x & 3, g = c >> 2;
@@ -246,9 +262,11 @@ __global__ void __launch_bounds__(1024) tp_ll_reduce_norm_quant_kernel(TpPeers p
         for (int r = blockIdx.x; r < T; r += gridDim.x) {
             const int o = r / rows_per, b = r - o * rows_per;
             if (o == rank) continue;
-            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(me + off.part) + (size_t)r * H + 8 * c);
             float* dst = reinterpret_cast<float*>(peers.p[o] + off.stage) + ((size_t)rank * rows_per + b) * H + 8 * c;
-            uint4 a0 = src[0], a1 = src[1];
+            float pv[8];
+            own_partial8(reinterpret_cast<const float*>(me + off.part), kparts, n_kparts, kpart_stride, (size_t)r * H + 8 * c, pv);
+            uint4 a0 = make_uint4(__float_as_uint(pv[0]), __float_as_uint(pv[1]), __float_as_uint(pv[2]), __float_as_uint(pv[3]));
+            uint4 a1 = make_uint4(__float_as_uint(pv[4]), __float_as_uint(pv[5]), __float_as_uint(pv[6]), __float_as_uint(pv[7]));
             a0.x = sendable(a0.x); a0.y = sendable(a0.y); a0.z = sendable(a0.z); a0.w = sendable(a0.w);
             a1.x = sendable(a1.x); a1.y = sendable(a1.y); a1.z = sendable(a1.z); a1.w = sendable(a1.w);
             st_volatile_v4(dst, a0);
@@ -264,8 +282,8 @@ __global__ void __launch_bounds__(1024) tp_ll_reduce_norm_quant_kernel(TpPeers p
             if (r >= T) break;
             float* hr = reinterpret_cast<float*>(me + off.h) + (size_t)r * H + 8 * c;
             const float4 h0 = *reinterpret_cast<const float4*>(hr), h1 = *reinterpret_cast<const float4*>(hr + 4);
-            const float* own = reinterpret_cast<const float*>(me + off.part) + (size_t)r * H + 8 * c;
-            const float4 p0 = __ldcg(reinterpret_cast<const float4*>(own)), p1 = __ldcg(reinterpret_cast<const float4*>(own + 4));
+            float pv[8];
+            own_partial8(reinterpret_cast<const float*>(me + off.part), kparts, n_kparts, kpart_stride, (size_t)r * H + 8 * c, pv);
             // the ranks' partial rows, added in rank order starting from rank 0's; a staged word is put back once it has been read
             float d[8];
 #pragma unroll
@@ -273,7 +291,8 @@ __global__ void __launch_bounds__(1024) tp_ll_reduce_norm_quant_kernel(TpPeers p
                 if (k < t) {
                     float v[8];
                     if (k == rank) {
-                        v[0] = p0.x; v[1] = p0.y; v[2] = p0.z; v[3] = p0.w; v[4] = p1.x; v[5] = p1.y; v[6] = p1.z; v[7] = p1.w;
+#pragma unroll
+                        for (int u = 0; u < 8; u++) v[u] = pv[u];
                     } else {
                         float* st = reinterpret_cast<float*>(me + off.stage) + ((size_t)k * rows_per + b) * H + 8 * c;
                         uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0;
@@ -370,7 +389,7 @@ int tp_fused_arm(b200_ctx* ctx, TpFused* f) {
     return B200_OK;
 }
 
-int launch_tp_reduce_norm_quant_ll(b200_ctx* ctx, TpFused* f, int T, const float* norm_w, float eps, ActQ* out, int phases) {
+int launch_tp_reduce_norm_quant_ll(b200_ctx* ctx, TpFused* f, int T, const float* norm_w, float eps, ActQ* out, int phases, const Parts* given) {
     if (!f->base || T < 1 || T > f->max_rows || f->H % 256 || f->H > 8192 || f->t < 1 || f->t > kTpMaxRanks || !norm_w)
         B200_FAIL(ctx, B200_BAD_ARGUMENT, "tensor-parallel reduce: %d rows of %d (at most %d), %d ranks", T, f->H, f->max_rows, f->t);
     if (!ctx->err_flag) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tensor-parallel reduce: the context has no error flag");
@@ -385,10 +404,19 @@ int launch_tp_reduce_norm_quant_ll(b200_ctx* ctx, TpFused* f, int T, const float
     for (int k = 0; k < kTpMaxRanks; k++) peers.p[k] = f->peer[k < f->t ? k : 0];
     const TpLLOffsets off{f->off_part, f->off_h, f->off_stage_ll[p], f->off_codes_ll[p], f->off_scales_ll[p], f->off_codes_ll[1 - p], f->off_scales_ll[1 - p]};
     const int grid = std::min(std::min(kTpMaxCtas, ctx->sm_count), T);
+    Parts pt{};
+    if (given) {
+        pt = *given;
+    } else if (ctx->pending.n > 0 && ctx->pending.dst == f->part() && ctx->pending.rows == T && ctx->pending.cols == f->H && !(ctx->pending.stride & 3)) {
+        pt = ctx->pending;  // the matmul left its K-split partials for this kernel to add
+        ctx->pending = Parts{};
+    } else {
+        ST_TRY(flush_pending_parts(ctx));
+    }
     {
         ProfScope ps(ctx, PROF_OTHER);  // counted with the collectives it replaces
         launch_pdl(tp_ll_reduce_norm_quant_kernel, dim3(grid), dim3(f->H / 8), 0, ctx->stream, peers, off, f->rank, f->t, T, f->H, norm_w, eps, phases,
-                   f->wait_ns, ctx->err_flag, f->phase_ns);
+                   f->wait_ns, ctx->err_flag, f->phase_ns, pt.p, pt.n, pt.stride);
     }
     LAUNCH_CHECK(ctx);
     if (phases & 4) {
@@ -407,6 +435,7 @@ int launch_tp_reduce_norm_quant(b200_ctx* ctx, TpFused* f, int T, const float* n
     TpPeers peers;
     for (int k = 0; k < kTpMaxRanks; k++) peers.p[k] = f->peer[k < f->t ? k : 0];
     const TpOffsets off{f->off_part, f->off_stage, f->off_h, f->off_codes, f->off_scales, f->off_row_flags, f->off_cta_flags};
+    ST_TRY(flush_pending_parts(ctx));  // this form reads the finished product
     if (phases & 1) ++f->seq;
     const int grid = std::min(std::min(kTpMaxCtas, ctx->sm_count), T);
     ProfScope ps(ctx, PROF_OTHER);  // counted with the collectives it replaces
@@ -417,15 +446,18 @@ int launch_tp_reduce_norm_quant(b200_ctx* ctx, TpFused* f, int T, const float* n
 }
 
 extern "C" int b200_debug_tp_reduce_emulated(b200_ctx* ctx, int t, int T, int H, const float* parts, const float* h, const float* w,
-                                             float eps, int mode, int8_t* codes_out, float* scales_out, float* h_out) {
+                                             float eps, int mode, int n_kparts, int8_t* codes_out, float* scales_out, float* h_out) {
     if (t < 1 || t > kTpMaxRanks || T < 1 || H < 256 || H % 256 || H > 8192) B200_FAIL(ctx, B200_BAD_ARGUMENT, "bad emulated shape");
     CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if (n_kparts < 0 || n_kparts > 8 || (n_kparts > 0 && mode != 2)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K-split partials go with mode 2");
     struct Blocks {
         TpFused f[kTpMaxRanks];
+        float* kp[kTpMaxRanks] = {};
         float* dw = nullptr;
         int* flag = nullptr;
         ~Blocks() {
             for (auto& x : f) cudaFree(x.base);
+            for (auto* x : kp) cudaFree(x);
             cudaFree(dw);
             cudaFree(flag);
         }
@@ -434,7 +466,12 @@ extern "C" int b200_debug_tp_reduce_emulated(b200_ctx* ctx, int t, int T, int H,
         tp_fused_layout(&bl.f[k], t, k, T, H);
         CUDA_TRY(ctx, cudaMalloc((void**)&bl.f[k].base, bl.f[k].bytes));
         CUDA_TRY(ctx, cudaMemsetAsync(bl.f[k].base, 0, bl.f[k].bytes, ctx->stream));
-        CUDA_TRY(ctx, cudaMemcpyAsync(bl.f[k].part(), parts + (size_t)k * T * H, (size_t)T * H * 4, cudaMemcpyHostToDevice, ctx->stream));
+        if (n_kparts > 0) {  // rank k's product as n_kparts partial matrices, T*H floats apart
+            CUDA_TRY(ctx, cudaMalloc((void**)&bl.kp[k], (size_t)n_kparts * T * H * 4));
+            CUDA_TRY(ctx, cudaMemcpyAsync(bl.kp[k], parts + (size_t)k * n_kparts * T * H, (size_t)n_kparts * T * H * 4, cudaMemcpyHostToDevice, ctx->stream));
+        } else {
+            CUDA_TRY(ctx, cudaMemcpyAsync(bl.f[k].part(), parts + (size_t)k * T * H, (size_t)T * H * 4, cudaMemcpyHostToDevice, ctx->stream));
+        }
         CUDA_TRY(ctx, cudaMemcpyAsync(bl.f[k].h(), h, (size_t)T * H * 4, cudaMemcpyHostToDevice, ctx->stream));
     }
     for (int k = 0; k < t; k++)
@@ -457,7 +494,10 @@ extern "C" int b200_debug_tp_reduce_emulated(b200_ctx* ctx, int t, int T, int H,
         for (int round = 0; round < 3 && st == B200_OK; round++) {
             for (int k = 0; k < t; k++) CUDA_TRY(ctx, cudaMemcpyAsync(bl.f[k].h(), h, (size_t)T * H * 4, cudaMemcpyHostToDevice, ctx->stream));
             for (int ph = 1; ph <= 4; ph *= 2)  // every rank's push, then every rank's reduce, then every rank's rearm + wait
-                for (int k = 0; k < t && st == B200_OK; k++) st = launch_tp_reduce_norm_quant_ll(ctx, &bl.f[k], T, bl.dw, eps, &got[k], ph);
+                for (int k = 0; k < t && st == B200_OK; k++) {
+                    const Parts given{bl.kp[k], (size_t)T * H, n_kparts, bl.f[k].part(), T, H};
+                    st = launch_tp_reduce_norm_quant_ll(ctx, &bl.f[k], T, bl.dw, eps, &got[k], ph, &given);
+                }
         }
     } else {
         for (int ph = 1; ph <= 2; ph++)  // every rank's push, then every rank's reduce

@@ -83,9 +83,11 @@ int b200_bench_tp_reduce(b200_model* m, int T, int mode, int warmup, int iters, 
  * partial products, h [T][H] the residual rows every rank starts from, w [H] the norm weight. mode 0: every rank's view of
  * the codes [t][T][H] and scales [t][T][2*H/32] and its residual rows h_out [t][T][H] (updated on the owner only);
  * mode 1: h_out holds the summed rows on every rank; mode 2: mode 0's work in the form without flags (words that announce
- * themselves), three calls in a row on the same inputs so that both buffer pairs are used, rearmed and used again. */
+ * themselves), three calls in a row on the same inputs so that both buffer pairs are used, rearmed and used again; with
+ * n_kparts > 0 (mode 2 only) parts is [t][n_kparts][T][H]: each rank's product as the K-split partials a matmul leaves
+ * for its consumer, which the kernel adds in split order. */
 int b200_debug_tp_reduce_emulated(b200_ctx* ctx, int t, int T, int H, const float* parts, const float* h, const float* w,
-                                  float eps, int mode, int8_t* codes_out, float* scales_out, float* h_out);
+                                  float eps, int mode, int n_kparts, int8_t* codes_out, float* scales_out, float* h_out);
 
 #ifdef __cplusplus
 }

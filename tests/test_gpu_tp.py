@@ -48,12 +48,12 @@ def test_reduce_norm_quant_kernel_with_emulated_ranks(ops, oracle_lib, t, T, H):
     x = h + s
     nG = H // 32
 
-    def run(mode):
+    def run(mode, given=parts, n_kparts=0):
         codes = np.zeros((t, T, H), np.int8)
         scales = np.zeros((t, T, 2 * nG), np.float32)
         h_out = np.zeros((t, T, H), np.float32)
         fp = lambda a: a.ctypes.data_as(C.POINTER(C.c_float))
-        st = ops.lib.b200_debug_tp_reduce_emulated(ops.ctx, t, T, H, fp(parts), fp(h), fp(w), C.c_float(1e-6), mode,
+        st = ops.lib.b200_debug_tp_reduce_emulated(ops.ctx, t, T, H, fp(given), fp(h), fp(w), C.c_float(1e-6), mode, n_kparts,
                                                    codes.ctypes.data_as(C.POINTER(C.c_int8)), fp(scales), fp(h_out))
         assert st == abi.OK, ops.lib.b200_last_error(ops.ctx)
         return codes, scales, h_out
@@ -70,6 +70,16 @@ def test_reduce_norm_quant_kernel_with_emulated_ranks(ops, oracle_lib, t, T, H):
             rest = np.ones(T, bool)
             rest[lo:hi] = False
             assert np.array_equal(h_out[k, rest], h[rest]), (mode, k)                                     # the others are left alone
+    # each rank's product given as three K-split partials, which the kernel adds in split order before anything else
+    kparts = rng.normal(0, 1, (t, 3, T, H)).astype(np.float32)
+    s3 = (kparts[:, 0] + kparts[:, 1]) + kparts[:, 2]
+    s = s3[0].copy()
+    for k in range(1, t):
+        s = s + s3[k]
+    want_codes, want_scales = oracle_lib.op_quant_g32(oracle_lib.op_rmsnorm(h + s, w, 1e-6))
+    codes, scales, _ = run(2, kparts, 3)
+    for k in range(t):
+        assert np.array_equal(codes[k], want_codes) and np.array_equal(scales[k].view(np.uint32), want_scales.view(np.uint32)), k
     _, _, h_all = run(1)
     for k in range(t):
         assert np.array_equal(h_all[k].view(np.uint32), x.view(np.uint32)), k
