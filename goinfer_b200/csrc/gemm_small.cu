@@ -460,12 +460,27 @@ int launch_q4k_matmul_small(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ 
     // two m-tiles a warp (half the activation traffic) where the matrix is tall enough to cover the SMs that way
     const int MT = (NT == 4 && ceil_div(N, 256) >= ctx->sm_count) ? 2 : 1;
     const int tiles = ceil_div(ceil_div(N, 16), kSmWarps * MT);
-    // K ranges: enough CTAs for two per SM, at least two super-blocks each; fewer while the partials' traffic (written and
-    // read back: 8 bytes per range, row and column) would pass a third of the weights' and the SMs stay covered
+    // K ranges. Two CTAs share an SM (their rings take 94 KB each), so the grid runs in waves of 2 * SMs CTAs and a wave
+    // that is a third full costs a whole one (a 24576 x 4096 matrix in two ranges: 384 CTAs on 296 places, 1.3 waves).
+    // Every count of ranges is priced as waves x (super-blocks per CTA + 2 for a CTA's fixed cost: ring fill, epilogue)
+    // and the cheapest is taken; a count whose partials (written and read back: 8 bytes per range, row and column)
+    // would pass a third of the weights' bytes is left out.
     const int kSbw = MT == 2 ? 1 : 2;   // SmallCfg<NT, MT>::kSbw
-    int splits = std::max(1, std::min(std::max(1, nSB / kSbw), ceil_div(2 * ctx->sm_count, tiles)));
+    const int places = 2 * ctx->sm_count;
     const double wbytes = (double)N * K * 0.5625;
-    while (splits > 1 && 8.0 * splits * T * N > 0.33 * wbytes && tiles * (splits - 1) >= ctx->sm_count) splits--;
+    int splits = 1;
+    double best = 1e30;
+    if (NT == 4) {  // 17 to 32 rows (one CTA an SM): enough CTAs for two per SM, fewer while the partials' traffic would pass a third of the weights'
+        splits = std::max(1, std::min(std::max(1, nSB / kSbw), ceil_div(2 * ctx->sm_count, tiles)));
+        while (splits > 1 && 8.0 * splits * T * N > 0.33 * wbytes && tiles * (splits - 1) >= ctx->sm_count) splits--;
+    }
+    for (int sp = 1; NT < 4 && sp <= std::max(1, nSB / kSbw); sp++) {
+        const int per = ceil_div(ceil_div(nSB, sp), kSbw) * kSbw, real = ceil_div(nSB, per);
+        if (real != sp) continue;
+        if (sp > 1 && 8.0 * sp * T * N > 0.33 * wbytes) break;
+        const double cost = (double)ceil_div(tiles * sp, places) * (per + 2);
+        if (cost < best - 1e-9) { best = cost; splits = sp; }
+    }
     static const int splits_env = getenv("B200_SMALL_SPLITS") ? atoi(getenv("B200_SMALL_SPLITS")) : 0;   // for measurements
     if (splits_env > 0) splits = std::min(splits_env, nSB);
     int sb_per_split = ceil_div(ceil_div(nSB, splits), kSbw) * kSbw;   // whole stages
