@@ -249,6 +249,12 @@ int launch_act_to_f16(b200_ctx*, ActQ aq, int T, int K, __half* out);  // the fp
 // uses the context's scratch like the tcgen05 matmul and takes the producers' activation tiles the same way
 // its weights are kept tile by tile ([row tile of 16][super-block][16 rows][144 B]: launch_q4k_to_tiles, q4k_tiles_bytes)
 int q4k_small_min_rows();
+bool q4k_small_grouped_supported(const uint8_t* W_all_tiles, int N, int K);
+// token rows -> expert-sorted slots: fp16 tiles + scales and group sums (what the grouped kernel below reads)
+int launch_gather_rows_x16(b200_ctx*, ActQ src, const int32_t* rows_tok, int n_rows, int K, __half* x16, float* scales_out);
+// routed experts on the same kernel: expert e's rows are offs[e] .. offs[e+1] of x16 / scales / dst (expert order)
+int launch_q4k_matmul_small_grouped(b200_ctx*, const uint8_t* W_all_tiles, int n_experts, int N, int K, const __half* x16, const float* scales,
+                                    const int32_t* offs, int n_rows, float* dst, int ldd);
 size_t q4k_tiles_bytes(int N, int K);
 int launch_q4k_to_tiles(b200_ctx*, const uint8_t* row_major, int N, int K, uint8_t* tiles);
 int launch_q4k_matmul_small(b200_ctx*, const uint8_t* W_tiles, int N, int K, ActQ aq, int T, float* dst, int ldd);

@@ -58,6 +58,7 @@ struct LayerW {
     std::vector<DevMat> egu;                // per expert gate|up
     const uint8_t** d_egu_ptrs = nullptr;   // device arrays of expert matrix pointers
     uint8_t *egu_all = nullptr, *ed_all = nullptr;  // Q4_K experts stacked: [n_experts][2F][.] and [n_experts][H][.]
+    uint8_t *egu_tiles = nullptr, *ed_tiles = nullptr;  // fast class: the stacks tile-major (every expert's matrix as launch_q4k_to_tiles lays it), the row-major stacks released
     const uint8_t** d_ed_ptrs = nullptr;
     double* inv_freq = nullptr;             // device, [rot_half]
     std::vector<double> h_inv_freq;
@@ -319,6 +320,7 @@ struct b200_model {
     float *rl = nullptr, *rw = nullptr, *egu_out = nullptr, *eo = nullptr, *emid = nullptr;
     int32_t *ridx = nullptr, *eoffs = nullptr, *erows = nullptr;
     ActQ aq_emid;
+    __half *x16_sorted = nullptr, *x16_emid = nullptr;  // routed experts, fast class: fp16 tiles of the sorted rows and of silu(gate)*up
     ActQ aq_sorted;  // routed experts: the layer's activation rows in expert-sorted order ([max_rows*top_k][hidden])
     // pinned host staging
     int32_t* p_desc = nullptr;
@@ -658,7 +660,14 @@ int run_layers(b200_model* m, int T, int max_keys) {
             ST_TRY(launch_group_experts(ctx, m->ridx, T, kk, nE, m->eoffs, m->erows));
             const int32_t* rows_tok = m->erows;
             const int32_t* slot_of = m->erows + (size_t)T * kk;
-            if (L.egu[0].kind == B200_K_Q4K) {
+            if (L.egu_tiles) {
+                // the experts' matmuls on the small-batch tensor-core kernel, grouped: token rows go to expert order as fp16
+                // tiles (with their scales and group sums), the SwiGLU lays out the down projection's tiles itself
+                ST_TRY(launch_gather_rows_x16(ctx, m->aq_h, rows_tok, T * kk, H, m->x16_sorted, m->aq_sorted.scales));
+                ST_TRY(launch_q4k_matmul_small_grouped(ctx, L.egu_tiles, nE, 2 * F, H, m->x16_sorted, m->aq_sorted.scales, m->eoffs, T * kk, m->egu_out, 2 * F));
+                ST_TRY(launch_swiglu_quant(ctx, m->egu_out, T * kk, F, 2 * F, nullptr, m->aq_emid, false, false, m->x16_emid));
+                ST_TRY(launch_q4k_matmul_small_grouped(ctx, L.ed_tiles, nE, H, F, m->x16_emid, m->aq_emid.scales, m->eoffs, T * kk, m->eo, H));
+            } else if (L.egu[0].kind == B200_K_Q4K) {
                 static const bool no_stream = getenv("B200_NO_STREAM") != nullptr;
                 if (L.egu_all && m->aq_sorted.codes && !no_stream && q4k_stream_grouped_supported(L.egu_all, 2 * F, H) &&
                     q4k_stream_grouped_supported(L.ed_all, H, F)) {
@@ -868,6 +877,22 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
                         pg[e] = (const uint8_t*)L.egu[e].p;
                         pd[e] = (const uint8_t*)L.ed[e].p;
                     }
+                    // fast class: the experts run on the small-batch tensor-core kernel in grouped form, which streams the
+                    // tile-major layout; the row-major stacks are released (one copy of 16 GB of experts, not two)
+                    const bool small_experts = (c.kernel_class == B200_CLASS_AUTO || c.kernel_class == 2) && !getenv("B200_NO_SMALL_EXPERTS") &&
+                                               c.hidden % 256 == 0 && c.moe_ffn % 256 == 0 && q4k_small_grouped_supported(L.egu_all, 2 * c.moe_ffn, c.hidden) &&
+                                               q4k_small_grouped_supported(L.ed_all, c.hidden, c.moe_ffn);
+                    if (small_experts) {
+                        ST_TRY(m->dalloc((void**)&L.egu_tiles, gb * c.n_experts, &m->weight_bytes));
+                        ST_TRY(launch_q4k_to_tiles(ctx, L.egu_all, c.n_experts * 2 * c.moe_ffn, c.hidden, L.egu_tiles));
+                        CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+                        m->dfree(L.egu_all); m->weight_bytes -= gb * c.n_experts; L.egu_all = nullptr;
+                        ST_TRY(m->dalloc((void**)&L.ed_tiles, db * c.n_experts, &m->weight_bytes));
+                        ST_TRY(launch_q4k_to_tiles(ctx, L.ed_all, c.n_experts * c.hidden, c.moe_ffn, L.ed_tiles));
+                        CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+                        m->dfree(L.ed_all); m->weight_bytes -= db * c.n_experts; L.ed_all = nullptr;
+                        for (int e = 0; e < c.n_experts; e++) { L.egu[e].p = nullptr; L.ed[e].p = nullptr; pg[e] = nullptr; pd[e] = nullptr; }
+                    }
                 }
             }
             ST_TRY(m->dalloc((void**)&L.d_egu_ptrs, c.n_experts * sizeof(void*), &m->weight_bytes));
@@ -960,6 +985,13 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
         if (H % 256 == 0) {
             ST_TRY(m->dalloc((void**)&m->aq_sorted.codes, (size_t)MR * kk * H, sb));
             ST_TRY(m->dalloc((void**)&m->aq_sorted.scales, (size_t)MR * kk * 2 * (H / 32) * 4, sb));
+        }
+        if (m->layers[0].egu_tiles) {   // rows padded to whole 256-row tiles with room for a 16-row pass past the last row
+            const size_t rows_pad = (size_t)ceil_div(MR * kk + 16, 256) * 256;
+            ST_TRY(m->dalloc((void**)&m->x16_sorted, rows_pad * H * 2, sb));
+            ST_TRY(m->dalloc((void**)&m->x16_emid, rows_pad * EF * 2, sb));
+            CUDA_TRY(ctx, cudaMemsetAsync(m->x16_sorted, 0, rows_pad * H * 2, ctx->stream));
+            CUDA_TRY(ctx, cudaMemsetAsync(m->x16_emid, 0, rows_pad * EF * 2, ctx->stream));
         }
         ST_TRY(m->dalloc((void**)&m->aq_emid.codes, (size_t)MR * kk * EF, sb));
         ST_TRY(m->dalloc((void**)&m->aq_emid.scales, (size_t)MR * kk * 2 * ceil_div(EF, 32) * 4, sb));

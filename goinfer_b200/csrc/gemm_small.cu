@@ -133,12 +133,17 @@ __device__ __forceinline__ RowScales row_scales(const uint4 hdr, int p) {
 }
 
 // grid (groups of 8*MT row tiles, K ranges); block 256. w16: the matrix tile by tile; n_tiles = ceil(N / 16).
-template <int NT, int MT>
+// GROUPED (routed experts): grid (groups of row tiles, 1, experts); w16 holds the experts' matrices one after the other
+// (n_tiles tiles each), x16 / scales / out rows are the token-expert pairs in expert order, and expert e owns rows
+// offs[e] .. offs[e+1]: the CTA walks them 8*NT at a time (the weights of a second pass come out of L2) and skips the
+// MMAs of 8-row groups past the expert's last row; an expert without rows costs its CTAs one load of offs.
+template <int NT, int MT, bool GROUPED>
 __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t* __restrict__ w16, int n_tiles,
                                                                                                const __half* __restrict__ x16,
                                                                                                const float* __restrict__ scales, int N, int nSB,
                                                                                                int sb_per_split, int T, float* __restrict__ out, int ldo,
-                                                                                               size_t split_stride, int* __restrict__ err_flag) {
+                                                                                               size_t split_stride, int* __restrict__ err_flag,
+                                                                                               const int32_t* __restrict__ offs) {
     using Cfg = SmallCfg<NT, MT>;
     constexpr int kSbw = Cfg::kSbw;
     pdl_trigger();
@@ -147,9 +152,10 @@ __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t*
     __shared__ int abort_s;
     uint8_t* smem = sm_raw + ((1024u - (smem_u32(sm_raw) & 1023u)) & 1023u);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, p = lane & 3;
-    const int tile0 = (blockIdx.x * kSmWarps + warp) * MT;          // first 16-row tile of this warp
-    const int row0 = tile0 * 16;
-    const int b_lo = blockIdx.y * sb_per_split, n_sb = max(0, min(nSB, b_lo + sb_per_split) - b_lo);
+    const int tile_l = (blockIdx.x * kSmWarps + warp) * MT;          // first 16-row tile of this warp (within its matrix)
+    const int tile0 = tile_l + (GROUPED ? (int)blockIdx.z * n_tiles : 0);
+    const int row0 = tile_l * 16;
+    const int b_lo = GROUPED ? 0 : blockIdx.y * sb_per_split, n_sb = max(0, min(nSB, b_lo + sb_per_split) - b_lo);
     const int n_it = (n_sb + kSbw - 1) / kSbw;                       // stages; the last may hold fewer super-blocks
     uint8_t* wring = smem + (size_t)warp * Cfg::kWDepth * Cfg::kWStage;
     uint8_t* aring = smem + (size_t)kSmWarps * Cfg::kWDepth * Cfg::kWStage;
@@ -166,6 +172,7 @@ __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t*
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
+    int rbase = 0;   // first activation / output row of the pass
 
     // stage i of this warp: super-blocks b_lo + kSbw i .. of its row tiles, one contiguous run per tile
     auto issue_w = [&](int i, int stage) {
@@ -173,36 +180,66 @@ __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t*
         const unsigned bar = smem_u32(&wfull[warp][stage]);
         int live = 0;
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++) live += (tile0 + mt < n_tiles) ? 1 : 0;
+        for (int mt = 0; mt < MT; mt++) live += (tile_l + mt < n_tiles) ? 1 : 0;
         mbar_arrive_expect_tx(bar, (unsigned)(live * nb * kTileBytes16));   // a warp past the matrix arrives with no bytes to wait for
 #pragma unroll
         for (int mt = 0; mt < MT; mt++)
-            if (tile0 + mt < n_tiles)
+            if (tile_l + mt < n_tiles)
                 bulk_g2s(smem_u32(wring + (size_t)stage * Cfg::kWStage + (size_t)mt * kSbw * kTileBytes16),
                          w16 + ((size_t)(tile0 + mt) * nSB + b) * kTileBytes16, (unsigned)(nb * kTileBytes16), bar);
     };
-    // the CTA's activation tiles of stage i: per super-block four 64-wide chunks of kTpad token rows
+    // the CTA's activation tiles of stage i: per super-block four 64-wide chunks of kTpad token rows from row rbase on (the
+    // fp16 matrix is [token tile of 256][chunk of 64 along K][256 rows][64]: a run of rows that crosses a token tile is two copies)
     auto issue_a = [&](int i, int stage) {
         const int b = b_lo + kSbw * i, nb = min(kSbw, b_lo + n_sb - b);
         const unsigned bar = smem_u32(&afull[stage]);
         mbar_arrive_expect_tx(bar, (unsigned)(nb * 4 * Cfg::kTpad * 128));
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(x16) + (size_t)(4 * b) * (256 * 128);
+        const int tt = rbase >> 8, r_in = rbase & 255, n1 = min(Cfg::kTpad, 256 - r_in);
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(x16) + ((size_t)tt * (4 * nSB) + 4 * b) * (256 * 128) + (size_t)r_in * 128;
         const unsigned dst = smem_u32(aring + (size_t)stage * Cfg::kAStage);
-        for (int c = 0; c < 4 * nb; c++) bulk_g2s(dst + c * Cfg::kChunk, src + (size_t)c * (256 * 128), Cfg::kTpad * 128, bar);
+        for (int c = 0; c < 4 * nb; c++) {
+            bulk_g2s(dst + c * Cfg::kChunk, src + (size_t)c * (256 * 128), n1 * 128, bar);
+            if (n1 < Cfg::kTpad)
+                bulk_g2s(dst + c * Cfg::kChunk + n1 * 128, src + ((size_t)(4 * nSB) + c) * (256 * 128) - (size_t)r_in * 128, (Cfg::kTpad - n1) * 128, bar);
+        }
     };
 
-    // weights are written by nobody: their first stages start before the wait on the kernel ahead of this one
+    // weights are written by nobody: their first stages start before the wait on the kernel ahead of this one (a routed
+    // expert's CTAs first have to learn whether the expert has rows at all)
     int w_issued = 0, a_issued = 0;
-    if (lane == 0)
+    if (!GROUPED && lane == 0)
         for (; w_issued < min(Cfg::kWDepth, n_it); w_issued++) issue_w(w_issued, w_issued);
     pdl_wait();
-    if (tid == 0)
-        for (; a_issued < min(Cfg::kADepth, n_it); a_issued++) issue_a(a_issued, a_issued);
+    int r_begin = 0, T_e = T;
+    if (GROUPED) {
+        r_begin = offs[blockIdx.z];
+        T_e = offs[blockIdx.z + 1] - r_begin;
+    }
+    const int sg = GROUPED ? ((gid + (r_begin & 7)) & 7) : gid;   // the activation rows' swizzle goes by their place in the whole matrix; passes are 8*NT rows apart
 
     // two accumulators per output tile where the registers allow: the low and the high sub-block of a pair feed different
     // ones, which halves the chain of dependent MMAs; they are added at the end
     constexpr bool kTwoAcc = MT * NT <= 2;
     constexpr int NA = kTwoAcc ? NT : 1, MA = kTwoAcc ? MT : 1;
+    const NibbleConsts kc{opaque(0x000F000Fu), opaque(0x64006400u), opaque(0x00F000F0u), opaque(0x54005400u)};
+    const float* asum_base = scales + (size_t)8 * nSB + 2 * p;
+    int ws = 0, as = 0;
+    unsigned wph = 0, aph = 0;   // ring positions and the phase parities of their barriers: they run on from pass to pass
+    const int n_pass = GROUPED ? (T_e + Cfg::kTpad - 1) / Cfg::kTpad : 1;
+#pragma unroll 1
+    for (int pass = 0; pass < n_pass; pass++) {
+    rbase = r_begin + pass * Cfg::kTpad;
+    const int Tc = min(Cfg::kTpad, T_e - pass * Cfg::kTpad), nt_live = (Tc + 7) >> 3;
+    const int ws0 = ws, as0 = as;
+    const unsigned wph0 = wph, aph0 = aph;
+    if (GROUPED || pass > 0) {   // (a dense launch started its first weight stages above)
+        w_issued = 0;
+        if (lane == 0)
+            for (; w_issued < min(Cfg::kWDepth, n_it); w_issued++) issue_w(w_issued, (ws0 + w_issued) % Cfg::kWDepth);
+    }
+    a_issued = 0;
+    if (tid == 0)
+        for (; a_issued < min(Cfg::kADepth, n_it); a_issued++) issue_a(a_issued, (as0 + a_issued) % Cfg::kADepth);
     float acc[MT][NT][4], acc2[MA][NA][4];
 #pragma unroll
     for (int mt = 0; mt < MT; mt++)
@@ -219,15 +256,14 @@ __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t*
 
     // group sums of this lane's token rows for sub-blocks 2p, 2p+1 of a super-block (the minimum term's operand); a stage's
     // sums are loaded while the stage before it is multiplied
-    const float* asum_base = scales + (size_t)8 * nSB + 2 * p;
     auto load_asum = [&](int i, unsigned (&dst)[kSbw][NT]) {
 #pragma unroll
         for (int u = 0; u < kSbw; u++) {
             const int b = b_lo + kSbw * i + u;
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const int t = 8 * nt + gid;
-                const float2 v = (t < T && b < b_lo + n_sb) ? __ldg(reinterpret_cast<const float2*>(asum_base + (size_t)t * 16 * nSB + 8 * b)) : make_float2(0.f, 0.f);
+                const int tl = 8 * nt + gid;
+                const float2 v = (tl < Tc && b < b_lo + n_sb) ? __ldg(reinterpret_cast<const float2*>(asum_base + (size_t)(rbase + tl) * 16 * nSB + 8 * b)) : make_float2(0.f, 0.f);
                 dst[u][nt] = as_u32(__floats2half2_rn(v.x, v.y));
             }
         }
@@ -235,9 +271,7 @@ __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t*
     unsigned asum[kSbw][NT], asum_next[kSbw][NT];
     load_asum(0, asum_next);
 
-    const NibbleConsts kc{opaque(0x000F000Fu), opaque(0x64006400u), opaque(0x00F000F0u), opaque(0x54005400u)};
-    int done = 0, ws = 0, as = 0;
-    unsigned wph = 0, aph = 0;   // ring positions and the phase parities of their barriers
+    int done = 0;
 #pragma unroll 1
     for (int i = 0; i < n_it; i++) {
 #pragma unroll
@@ -276,7 +310,8 @@ __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t*
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
 #pragma unroll
-                for (int mt = 0; mt < MT; mt++) mma_f16_k8(acc[mt][nt], rs[mt][0].neg_dm, rs[mt][1].neg_dm, asum[u][nt]);
+                for (int mt = 0; mt < MT; mt++)
+                    if (!GROUPED || nt < nt_live) mma_f16_k8(acc[mt][nt], rs[mt][0].neg_dm, rs[mt][1].neg_dm, asum[u][nt]);
             }
 #pragma unroll
             for (int jj = 0; jj < 4; jj++) {
@@ -285,8 +320,8 @@ __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t*
                 uint4 bl[NT], bh[NT];
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
-                    bl[nt] = *reinterpret_cast<const uint4*>(ast + (size_t)nt * (8 * 128) + ((jj ^ gid) << 4));
-                    bh[nt] = *reinterpret_cast<const uint4*>(ast + (size_t)nt * (8 * 128) + (((jj + 4) ^ gid) << 4));
+                    bl[nt] = *reinterpret_cast<const uint4*>(ast + (size_t)nt * (8 * 128) + ((jj ^ sg) << 4));
+                    bh[nt] = *reinterpret_cast<const uint4*>(ast + (size_t)nt * (8 * 128) + (((jj + 4) ^ sg) << 4));
                 }
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++) {
@@ -298,15 +333,17 @@ __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t*
                             const unsigned a0 = deq_lo(w0, rs[mt][0].ds_lo, rs[mt][0].c_lo, kc), a1 = deq_lo(w1, rs[mt][1].ds_lo, rs[mt][1].c_lo, kc);
                             const unsigned a2 = deq_lo(w0s, rs[mt][0].ds_lo, rs[mt][0].c_lo, kc), a3 = deq_lo(w1s, rs[mt][1].ds_lo, rs[mt][1].c_lo, kc);
 #pragma unroll
-                            for (int nt = 0; nt < NT; nt++) mma_f16(acc[mt][nt], a0, a1, a2, a3, hw ? bl[nt].z : bl[nt].x, hw ? bl[nt].w : bl[nt].y);
+                            for (int nt = 0; nt < NT; nt++)
+                                if (!GROUPED || nt < nt_live) mma_f16(acc[mt][nt], a0, a1, a2, a3, hw ? bl[nt].z : bl[nt].x, hw ? bl[nt].w : bl[nt].y);
                         }
                         {   // high nibbles: sub-block 2p + 1
                             const unsigned a0 = deq_hi(w0, rs[mt][0].ds_hi, rs[mt][0].c_hi, kc), a1 = deq_hi(w1, rs[mt][1].ds_hi, rs[mt][1].c_hi, kc);
                             const unsigned a2 = deq_hi(w0s, rs[mt][0].ds_hi, rs[mt][0].c_hi, kc), a3 = deq_hi(w1s, rs[mt][1].ds_hi, rs[mt][1].c_hi, kc);
 #pragma unroll
                             for (int nt = 0; nt < NT; nt++)
-                                mma_f16(kTwoAcc ? acc2[kTwoAcc ? mt : 0][kTwoAcc ? nt : 0] : acc[mt][nt], a0, a1, a2, a3, hw ? bh[nt].z : bh[nt].x,
-                                        hw ? bh[nt].w : bh[nt].y);
+                                if (!GROUPED || nt < nt_live)
+                                    mma_f16(kTwoAcc ? acc2[kTwoAcc ? mt : 0][kTwoAcc ? nt : 0] : acc[mt][nt], a0, a1, a2, a3, hw ? bh[nt].z : bh[nt].x,
+                                            hw ? bh[nt].w : bh[nt].y);
                         }
                     }
                 }
@@ -338,18 +375,20 @@ __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t*
     }
     if (*abort_v && lane == 0) {
         // copies this warp started and did not consume must land before the CTA may leave: bounded waits on their barriers
-        for (int k = done; k < w_issued; k++) mbar_wait(smem_u32(&wfull[warp][k % Cfg::kWDepth]), (unsigned)((k / Cfg::kWDepth) & 1));
+        for (int k = done; k < w_issued; k++)
+            mbar_wait(smem_u32(&wfull[warp][(ws0 + k) % Cfg::kWDepth]), wph0 ^ (unsigned)(((ws0 + k) / Cfg::kWDepth) & 1));
     }
-    __syncthreads();
+    __syncthreads();   // (also: every warp is done with both rings before the next pass refills them)
     if (abort_s) {
         if (tid == 0) {
             // activation stages nobody will read: the earliest unread one of any warp is not known here, so wait for all issued
-            for (int k = max(0, a_issued - Cfg::kADepth); k < a_issued; k++) mbar_wait(smem_u32(&afull[k % Cfg::kADepth]), (unsigned)((k / Cfg::kADepth) & 1));
+            for (int k = max(0, a_issued - Cfg::kADepth); k < a_issued; k++)
+                mbar_wait(smem_u32(&afull[(as0 + k) % Cfg::kADepth]), aph0 ^ (unsigned)(((as0 + k) / Cfg::kADepth) & 1));
             if (err_flag) atomicExch(err_flag, 1);
         }
         return;
     }
-    float* o = out + (size_t)blockIdx.y * split_stride;
+    float* o = out + (GROUPED ? (size_t)0 : (size_t)blockIdx.y * split_stride);
     if (kTwoAcc) {
 #pragma unroll
         for (int mt = 0; mt < MA; mt++)
@@ -364,16 +403,17 @@ __global__ void __launch_bounds__(kSmThreads, 2) q4k_small_kernel(const uint8_t*
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             const int t0 = 8 * nt + 2 * p, t1 = t0 + 1;
-            if (t0 < T) {
-                if (r0 < N) o[(size_t)t0 * ldo + r0] = acc[mt][nt][0];
-                if (r1 < N) o[(size_t)t0 * ldo + r1] = acc[mt][nt][2];
+            if (t0 < Tc) {
+                if (r0 < N) o[(size_t)(rbase + t0) * ldo + r0] = acc[mt][nt][0];
+                if (r1 < N) o[(size_t)(rbase + t0) * ldo + r1] = acc[mt][nt][2];
             }
-            if (t1 < T) {
-                if (r0 < N) o[(size_t)t1 * ldo + r0] = acc[mt][nt][1];
-                if (r1 < N) o[(size_t)t1 * ldo + r1] = acc[mt][nt][3];
+            if (t1 < Tc) {
+                if (r0 < N) o[(size_t)(rbase + t1) * ldo + r0] = acc[mt][nt][1];
+                if (r1 < N) o[(size_t)(rbase + t1) * ldo + r1] = acc[mt][nt][3];
             }
         }
     }
+    }   // pass
 }
 
 // [N][nSB][144] -> [ceil(N/16)][nSB][16][144]: one 16-byte piece per thread; rows past N become zero blocks (zero weights)
@@ -410,14 +450,15 @@ int run_small(b200_ctx* ctx, const uint8_t* W, int N, int nSB, const __half* x16
     using Cfg = SmallCfg<NT, MT>;
     static PerDeviceOnce attr_once;  // the attribute belongs to the device
     if (attr_once.first(ctx->device)) {
-        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_small_kernel<NT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_small_kernel<NT, MT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
     }
     const int n_tiles = ceil_div(N, 16);
     dim3 grid(ceil_div(n_tiles, kSmWarps * MT), splits);
     {
         ProfScope ps(ctx, PROF_Q4K_GEMM);
-        launch_pdl(q4k_small_kernel<NT, MT>, grid, dim3(kSmThreads), (size_t)Cfg::kSmem, ctx->stream, W, n_tiles, x16, scales, N, nSB, sb_per_split, T, out, ldo,
-                   stride, ctx->err_flag);
+        const int32_t* const no_offs = nullptr;
+        launch_pdl(q4k_small_kernel<NT, MT, false>, grid, dim3(kSmThreads), (size_t)Cfg::kSmem, ctx->stream, W, n_tiles, x16, scales, N, nSB, sb_per_split, T, out, ldo,
+                   stride, ctx->err_flag, no_offs);
     }
     LAUNCH_CHECK(ctx);
     return B200_OK;
@@ -518,5 +559,59 @@ int launch_q4k_matmul_small(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ 
             LAUNCH_CHECK(ctx);
         }
     }
+    return B200_OK;
+}
+
+// Routed experts' activations: sorted slot s takes token row rows_tok[s]: its fp16 tiles (code * scale, the layout the
+// kernels above read) and its scales and group sums. One block per slot.
+__global__ void gather_rows_x16_kernel(const int8_t* __restrict__ codes, const float* __restrict__ scales, const int32_t* __restrict__ rows_tok, int K,
+                                       __half* __restrict__ x16, float* __restrict__ scales_out) {
+    pdl_trigger();
+    pdl_wait();
+    const int s = blockIdx.x, r = rows_tok[s], nG = K >> 5;
+    for (int c = threadIdx.x; c < (K >> 3); c += blockDim.x) {
+        const int2 cw = *reinterpret_cast<const int2*>(codes + (size_t)r * K + 8 * c);
+        const float sc = scales[(size_t)r * 2 * nG + (c >> 2)];
+        const int8_t* cb = reinterpret_cast<const int8_t*>(&cw);
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = __fmul_rn((float)cb[u], sc);
+        x16_store8(x16, K, s, 8 * c, v);
+    }
+    for (int i = threadIdx.x; i < 2 * nG; i += blockDim.x) scales_out[(size_t)s * 2 * nG + i] = scales[(size_t)r * 2 * nG + i];
+}
+
+int launch_gather_rows_x16(b200_ctx* ctx, ActQ src, const int32_t* rows_tok, int n_rows, int K, __half* x16, float* scales_out) {
+    if (n_rows <= 0) return B200_OK;
+    if (K % 32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "K %% 32");
+    launch_pdl(gather_rows_x16_kernel, dim3(n_rows), dim3(128), 0, ctx->stream, (const int8_t*)src.codes, (const float*)src.scales, rows_tok, K, x16, scales_out);
+    LAUNCH_CHECK(ctx);
+    return B200_OK;
+}
+
+// Routed experts. W_all: the experts' matrices one after the other, each tile by tile (launch_q4k_to_tiles over the stacked
+// [n_experts * N][K] matrix gives exactly that when N is a multiple of 16). x16 / scales: the activation rows of the
+// token-expert pairs in expert order (expert e owns rows offs[e] .. offs[e+1], a device array), the fp16 tiles padded so
+// that rows up to n_rows + 16 can be read. dst rows are the same pairs.
+bool q4k_small_grouped_supported(const uint8_t* W_all, int N, int K) { return N % 16 == 0 && K % 256 == 0 && (reinterpret_cast<uintptr_t>(W_all) & 15) == 0; }
+
+int launch_q4k_matmul_small_grouped(b200_ctx* ctx, const uint8_t* W_all, int n_experts, int N, int K, const __half* x16, const float* scales,
+                                    const int32_t* offs, int n_rows, float* dst, int ldd) {
+    if (!q4k_small_grouped_supported(W_all, N, K)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "grouped small-batch matmul: N %% 16, K %% 256 or alignment");
+    if (n_rows <= 0) return B200_OK;
+    constexpr int NT = 2, MT = 1;   // passes of 16 rows: at 8 rows an expert on average, most experts take one
+    using Cfg = SmallCfg<NT, MT>;
+    static PerDeviceOnce attr_once;  // the attribute belongs to the device
+    if (attr_once.first(ctx->device)) {
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_small_kernel<NT, MT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+    }
+    const int n_tiles = N / 16, nSB = K / 256;
+    dim3 grid(ceil_div(n_tiles, kSmWarps * MT), 1, n_experts);
+    {
+        ProfScope ps(ctx, PROF_Q4K_GEMM);
+        launch_pdl(q4k_small_kernel<NT, MT, true>, grid, dim3(kSmThreads), (size_t)Cfg::kSmem, ctx->stream, W_all, n_tiles, x16, scales, N, nSB, nSB, n_rows, dst, ldd,
+                   (size_t)0, ctx->err_flag, offs);
+    }
+    LAUNCH_CHECK(ctx);
     return B200_OK;
 }
