@@ -59,6 +59,7 @@ EXPORTS = (
     "b200_open", "b200_close", "b200_last_error", "b200_model_create", "b200_upload_tensor", "b200_set_rope_inv_freq",
     "b200_model_finalize", "b200_model_free", "b200_kv_slots", "b200_reset_slot", "b200_reset", "b200_block_table",
     "b200_upload_kv", "b200_copy_kv", "b200_step_ragged", "b200_forward", "b200_forward_topk", "b200_prefill_last",
+    "b200_batch_open", "b200_batch_admit", "b200_batch_retire", "b200_batch_run", "b200_batch_close",
     "b200_stats", "b200_tp_unique_id", "b200_tp_init", "b200_tp_destroy",
     "b200_op_quant_g32", "b200_op_q4k_dequant", "b200_op_q4k_matmul", "b200_op_q4k_quantize", "b200_op_f16_matmul",
     "b200_op_rmsnorm", "b200_op_route", "b200_op_draw", "b200_op_topk", "b200_op_philox", "b200_op_attention",

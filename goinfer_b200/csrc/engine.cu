@@ -193,6 +193,50 @@ __global__ void advance_kernel(int32_t* tokens, const int32_t* ids, int32_t* pos
     if (advance_pos) pos_dev[i] += 1;
 }
 
+// ---- the device batch: a fixed set of seats that decode step after step with no per-step host packing ----
+// A seat is bound to a KV slot. A live seat holds a sequence (position, the token to feed, tokens left, its end-of-sequence
+// id); an empty seat runs a throw-away row at position 0 of the parking slot, so a step always has the same rows and a
+// finished sequence's KV stays as it was (for a follow-up turn or as a prefix donor). Commands are applied in order at a
+// step boundary; a seat retires itself when it draws its end-of-sequence id or runs out of tokens.
+struct SeatCmd {
+    int32_t op, seat, pos, token, max_new, eos;   // op 1: admit, 2: retire
+};
+struct SeatEvent {
+    int32_t seat, id, pos, flags;                 // flags bit 0: the seat was live in this step, bit 1: it retired after it
+};
+__global__ void seats_apply_kernel(const SeatCmd* __restrict__ cmds, int n, int32_t* desc_slot, int first_slot, int park_slot,
+                                   int32_t* live, int32_t* pos, int32_t* tokens, int32_t* remaining, int32_t* eos) {
+    if (threadIdx.x || blockIdx.x) return;
+    for (int k = 0; k < n; k++) {
+        const SeatCmd c = cmds[k];
+        if (c.op == 1) {
+            live[c.seat] = 1; pos[c.seat] = c.pos; tokens[c.seat] = c.token; remaining[c.seat] = c.max_new; eos[c.seat] = c.eos;
+            desc_slot[c.seat] = first_slot + c.seat;
+        } else {
+            live[c.seat] = 0; pos[c.seat] = 0; tokens[c.seat] = 0; remaining[c.seat] = 0;
+            desc_slot[c.seat] = park_slot;
+        }
+    }
+}
+__global__ void seats_advance_kernel(int S, const int32_t* __restrict__ ids, int32_t* desc_slot, int park_slot, int32_t* live, int32_t* pos,
+                                     int32_t* tokens, int32_t* remaining, const int32_t* __restrict__ eos, SeatEvent* __restrict__ events) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= S) return;
+    SeatEvent ev{i, -1, 0, 0};
+    if (live[i]) {
+        const int id = ids[i];
+        ev.id = id; ev.pos = pos[i]; ev.flags = 1;
+        tokens[i] = id;
+        pos[i] += 1;
+        if (--remaining[i] <= 0 || id == eos[i]) {   // the sequence is over: the seat goes back to the parking slot
+            ev.flags |= 2;
+            live[i] = 0; pos[i] = 0; tokens[i] = 0;
+            desc_slot[i] = park_slot;
+        }
+    }
+    events[i] = ev;
+}
+
 __global__ void synth_kv_kernel(__half* kpool, __half* vpool, const int32_t* table_row, int n_pos, int nKV, int hd,
                                 int block_rows, float sigma, uint64_t seed) {
     // element index over [pos][kvh][e]
@@ -316,6 +360,16 @@ struct b200_model {
     cudaGraphExec_t loop_graph = nullptr;
     int loop_graph_S = 0, loop_graph_splits = 0, loop_graph_adv = 0;
     int64_t loop_graph_launches = 0;
+    // the device batch (b200_batch_*): seats bound to slots first_slot.., empty seats park on park_slot
+    struct Seats {
+        int n = 0, first_slot = 0, park_slot = 0, max_steps = 0;
+        int32_t *live = nullptr, *remaining = nullptr, *eos = nullptr;   // device, [n]
+        int32_t *desc = nullptr, *pos = nullptr, *tokens = nullptr, *rows = nullptr;   // device: the seats' step descriptor, positions, tokens to feed, head rows
+        b200_draw* draws = nullptr;
+        void *cmds = nullptr, *events = nullptr;                         // device: SeatCmd[2n], SeatEvent[max_steps][n]
+        std::vector<int32_t> h_live, h_pos, h_end;                       // the host's view between runs (h_end: last position + 1 a seat may reach)
+        std::vector<int32_t> pending;                                    // commands not yet applied, 6 words each
+    } seats;
     // MoE
     float *rl = nullptr, *rw = nullptr, *egu_out = nullptr, *eo = nullptr, *emid = nullptr;
     int32_t *ridx = nullptr, *eoffs = nullptr, *erows = nullptr;
@@ -1674,6 +1728,182 @@ int b200_decode_loop_device(b200_model* m, int n_seqs, const int32_t* slot, cons
     m->stats.steps += steps;
     m->stats.rows += (int64_t)steps * S;
     m->stats.last_step_device_ms = ms / steps;
+    return B200_OK;
+}
+
+// ---- the device batch (scheduler.Admission's admit / retire mapped onto the device: internal/runtime/scheduler/admission.go:60-122) ----
+// b200_batch_open binds seats to slots; between runs the host prefills a seat's slot (b200_prefill_last / b200_step_ragged)
+// and admits the sequence at its next position with the token to feed; b200_batch_run then decodes `steps` greedy steps for
+// every seat with nothing packed or uploaded per step: commands are applied on the device at the first step's boundary,
+// ids are fed back, positions advance, a seat retires itself at its end-of-sequence id or token budget, and one record per
+// seat and step comes back. The blocks a seat's sequence can still take are reserved at admission, so a run cannot find
+// the pool empty.
+int b200_batch_open(b200_model* m, int n_seats, int first_slot, int park_slot, int max_steps) {
+    b200_ctx* ctx = m->ctx;
+    const b200_model_cfg& c = m->c;
+    auto& q = m->seats;
+    if (!m->finalized || q.n || n_seats < 1 || n_seats > m->MR || n_seats > m->MLR || first_slot < 0 || first_slot + n_seats > c.n_slots || park_slot < 0 ||
+        park_slot >= c.n_slots || (park_slot >= first_slot && park_slot < first_slot + n_seats) || max_steps < 1)
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "device batch: %d seats from slot %d, parking slot %d, %d steps a run", n_seats, first_slot, park_slot, max_steps);
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    size_t* sb = &m->scratch_bytes;
+    const int S = n_seats;
+    ST_TRY(m->dalloc((void**)&q.live, (size_t)S * 4, sb));
+    ST_TRY(m->dalloc((void**)&q.remaining, (size_t)S * 4, sb));
+    ST_TRY(m->dalloc((void**)&q.eos, (size_t)S * 4, sb));
+    ST_TRY(m->dalloc((void**)&q.desc, (size_t)(2 + 3 * S) * 4, sb));
+    ST_TRY(m->dalloc((void**)&q.pos, (size_t)S * 4, sb));
+    ST_TRY(m->dalloc((void**)&q.tokens, (size_t)S * 4, sb));
+    ST_TRY(m->dalloc((void**)&q.rows, (size_t)S * 4, sb));
+    ST_TRY(m->dalloc((void**)&q.draws, (size_t)S * sizeof(b200_draw), sb));
+    ST_TRY(m->dalloc(&q.cmds, (size_t)2 * S * sizeof(SeatCmd), sb));
+    ST_TRY(m->dalloc(&q.events, (size_t)max_steps * S * sizeof(SeatEvent), sb));
+    std::vector<int32_t> d(2 + 3 * S), iota(S);
+    std::vector<b200_draw> dr(S, b200_draw{B200_DRAW_GREEDY, 0, 0, 0, 0});
+    d[0] = S; d[1] = S;
+    for (int i = 0; i < S; i++) { d[2 + i] = park_slot; d[2 + S + i] = 0; d[2 + 2 * S + i] = 1; iota[i] = i; }
+    CUDA_TRY(ctx, cudaMemcpyAsync(q.desc, d.data(), d.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(q.rows, iota.data(), (size_t)S * 4, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(q.draws, dr.data(), (size_t)S * sizeof(b200_draw), cudaMemcpyHostToDevice, ctx->stream));
+    for (int32_t* z : {q.live, q.remaining, q.eos, q.pos, q.tokens}) CUDA_TRY(ctx, cudaMemsetAsync(z, 0, (size_t)S * 4, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    q.n = S; q.first_slot = first_slot; q.park_slot = park_slot; q.max_steps = max_steps;
+    q.h_live.assign(S, 0); q.h_pos.assign(S, 0); q.h_end.assign(S, 0);
+    q.pending.clear();
+    return B200_OK;
+}
+
+namespace {
+// blocks the seats' sequences (and the parking slot) may still take, seat `skip` left out
+int seats_reserved(b200_model* m, int skip) {
+    auto& q = m->seats;
+    int need = blocks_needed(m, q.park_slot, 1);
+    for (int i = 0; i < q.n; i++)
+        if (i != skip && q.h_live[i]) need += blocks_needed(m, q.first_slot + i, q.h_end[i]);
+    return need;
+}
+}  // namespace
+
+int b200_batch_admit(b200_model* m, int seat, int pos, int token, int max_new, int eos_id) {
+    b200_ctx* ctx = m->ctx;
+    const b200_model_cfg& c = m->c;
+    auto& q = m->seats;
+    if (!q.n || seat < 0 || seat >= q.n) B200_FAIL(ctx, B200_BAD_ARGUMENT, "device batch: no seat %d", seat);
+    const int slot = q.first_slot + seat, end = pos + max_new;
+    if (q.h_live[seat]) B200_FAIL(ctx, B200_BAD_ARGUMENT, "device batch: seat %d holds a sequence", seat);
+    if (pos < 0 || max_new < 1 || end > c.ctx_cap || pos > m->h_slot_len[slot] || token < 0 || token >= c.vocab)
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "device batch: seat %d cannot continue at position %d for %d tokens (its slot stores %d rows, capacity %d)", seat, pos,
+                  max_new, m->h_slot_len[slot], c.ctx_cap);
+    if ((int)q.pending.size() / 6 >= 2 * q.n) B200_FAIL(ctx, B200_BAD_ARGUMENT, "device batch: too many commands before a run");
+    // the blocks this sequence can still take (and the copies a shared block costs) must be there beside every other seat's
+    const int need = blocks_needed(m, slot, end) + m->h_cow_need(slot, pos, end);
+    if (need + seats_reserved(m, seat) > m->h_free) {
+        m->stats.kv_pool_full++;
+        B200_FAIL(ctx, B200_KV_POOL_FULL, "kv pool full: seat %d needs %d blocks, %d are reserved, %d free", seat, need, seats_reserved(m, seat), m->h_free);
+    }
+    ST_TRY(make_private(m, slot, pos, end));
+    q.h_live[seat] = 1; q.h_pos[seat] = pos; q.h_end[seat] = end;
+    const int32_t cmd[6] = {1, seat, pos, token, max_new, eos_id};
+    q.pending.insert(q.pending.end(), cmd, cmd + 6);
+    return B200_OK;
+}
+
+int b200_batch_retire(b200_model* m, int seat) {
+    b200_ctx* ctx = m->ctx;
+    auto& q = m->seats;
+    if (!q.n || seat < 0 || seat >= q.n) B200_FAIL(ctx, B200_BAD_ARGUMENT, "device batch: no seat %d", seat);
+    if ((int)q.pending.size() / 6 >= 2 * q.n) B200_FAIL(ctx, B200_BAD_ARGUMENT, "device batch: too many commands before a run");
+    q.h_live[seat] = 0;
+    const int32_t cmd[6] = {2, seat, 0, 0, 0, 0};
+    q.pending.insert(q.pending.end(), cmd, cmd + 6);
+    return B200_OK;
+}
+
+int b200_batch_run(b200_model* m, int steps, int32_t* events_out, int max_events, int32_t* n_events_out) {
+    b200_ctx* ctx = m->ctx;
+    const b200_model_cfg& c = m->c;
+    auto& q = m->seats;
+    const int S = q.n, H = c.hidden, V = c.vocab;
+    if (!S || steps < 1 || steps > q.max_steps || !n_events_out || (max_events > 0 && !events_out))
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "device batch: %d steps (at most %d a run)", steps, q.max_steps);
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    ctx->umma_scratch = m->umma_scratch;
+    ctx->umma_scratch_bytes = m->umma_bytes;
+    ctx->x16_slot_bytes = m->x16_slot_bytes;
+    ctx->err_flag = m->err_flag;
+    if (seats_reserved(m, -1) > m->h_free) {   // (other calls took blocks since the admissions)
+        m->stats.kv_pool_full++;
+        B200_FAIL(ctx, B200_KV_POOL_FULL, "kv pool full: the seats' sequences may take %d blocks, %d free", seats_reserved(m, -1), m->h_free);
+    }
+    const int n_cmd = (int)q.pending.size() / 6;
+    if (n_cmd) {
+        CUDA_TRY(ctx, cudaMemcpyAsync(q.cmds, q.pending.data(), q.pending.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+        seats_apply_kernel<<<1, 32, 0, ctx->stream>>>((const SeatCmd*)q.cmds, n_cmd, q.desc + 2, q.first_slot, q.park_slot, q.live, q.pos, q.tokens, q.remaining, q.eos);
+        LAUNCH_CHECK(ctx);
+        CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));   // the commands' host buffer is reused
+        q.pending.clear();
+    }
+    int max_keys = 1;
+    for (int i = 0; i < S; i++)
+        if (q.h_live[i]) max_keys = std::max(max_keys, std::min(q.h_end[i], q.h_pos[i] + steps));
+    CUDA_TRY(ctx, cudaEventRecord(m->ev0, ctx->stream));
+    for (int st = 0; st < steps; st++) {
+        prepare_step_kernel<<<1, 256, 0, ctx->stream>>>(q.desc, q.pos, 1, m->table, m->max_blocks, c.kv_block_rows, m->slot_mapped, m->free_stack,
+                                                        m->free_count, m->d_seq_row0, m->d_row_slot, m->d_row_pos, m->status, m->refs);
+        LAUNCH_CHECK(ctx);
+        ST_TRY(launch_embed_gather(ctx, m->embed.p, m->embed.kind, m->embed.rows, q.tokens, S, H, c.embed_scale, m->h));
+        ST_TRY(run_layers(m, S, max_keys));
+        const bool hq = is_kquant(m->head.kind);
+        ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, nullptr, m->final_norm, S, H, c.rms_eps, hq ? nullptr : m->hn, hq ? m->aq_h : ActQ{}, q.rows));
+        ST_TRY(head_logits(m, S));
+        if (c.final_softcap > 0.f) ST_TRY(launch_softcap(ctx, m->logits, (size_t)S * V, c.final_softcap));
+        ST_TRY(launch_draw(ctx, m->logits, S, V, q.draws, m->d_ids, nullptr));
+        seats_advance_kernel<<<ceil_div(S, 256), 256, 0, ctx->stream>>>(S, m->d_ids, q.desc + 2, q.park_slot, q.live, q.pos, q.tokens, q.remaining, q.eos,
+                                                                       (SeatEvent*)q.events + (size_t)st * S);
+        LAUNCH_CHECK(ctx);
+    }
+    CUDA_TRY(ctx, cudaEventRecord(m->ev1, ctx->stream));
+    std::vector<SeatEvent> ev((size_t)steps * S);
+    CUDA_TRY(ctx, cudaMemcpyAsync(ev.data(), q.events, ev.size() * sizeof(SeatEvent), cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids + m->MR, m->err_flag, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(m->p_ids + m->MR + 1, m->status, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    ST_TRY(check_device_flags(m, "a run of the device batch"));
+    // The mirror pops blocks in the order the device did (step by step, seat by seat), and the host's view of the seats
+    // follows the records.
+    int n_out = 0;
+    for (int st = 0; st < steps; st++)
+        for (int i = 0; i < S; i++) {
+            const SeatEvent& e = ev[(size_t)st * S + i];
+            if (e.flags & 1) {
+                m->h_append(q.first_slot + i, e.pos + 1);
+                q.h_pos[i] = e.pos + 1;
+                if (e.flags & 2) q.h_live[i] = 0;
+                if (n_out < max_events) {
+                    events_out[4 * n_out] = i; events_out[4 * n_out + 1] = e.id; events_out[4 * n_out + 2] = e.pos; events_out[4 * n_out + 3] = e.flags;
+                }
+                n_out++;
+                m->stats.rows++;
+            } else {
+                m->h_append(q.park_slot, 1);
+            }
+        }
+    *n_events_out = n_out;
+    float ms = 0;
+    cudaEventElapsedTime(&ms, m->ev0, m->ev1);
+    m->stats.steps += steps;
+    m->stats.last_step_device_ms = ms / steps;
+    if (n_out > max_events) B200_FAIL(ctx, B200_BAD_ARGUMENT, "device batch: %d records, room for %d", n_out, max_events);
+    return B200_OK;
+}
+
+int b200_batch_close(b200_model* m) {
+    auto& q = m->seats;
+    if (!q.n) return B200_OK;
+    cudaStreamSynchronize(m->ctx->stream);
+    for (void* p : {(void*)q.live, (void*)q.remaining, (void*)q.eos, (void*)q.desc, (void*)q.pos, (void*)q.tokens, (void*)q.rows, (void*)q.draws, q.cmds, q.events})
+        m->dfree(p);
+    q = b200_model::Seats{};
     return B200_OK;
 }
 

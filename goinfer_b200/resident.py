@@ -342,6 +342,29 @@ class Resident:
                                                      1 if advance else 0, _ptr(ids, C.c_int32), C.byref(ms)))
         return ids, ms.value
 
+    # ---- the device batch: seats bound to slots, admission and retirement applied on the device ----
+    def BatchOpen(self, n_seats: int, first_slot: int, park_slot: int, max_steps: int = 64):
+        self._check(self.drv.fn("batch_open")(self.m, n_seats, first_slot, park_slot, max_steps))
+        self._batch_seats, self._batch_steps = n_seats, max_steps
+
+    def BatchAdmit(self, seat: int, pos: int, token: int, max_new: int, eos_id: int = -1):
+        """The sequence in the seat's slot continues at `pos` by feeding `token` (its slot was prefilled up to there)."""
+        self._check(self.drv.fn("batch_admit")(self.m, seat, pos, token, max_new, eos_id))
+
+    def BatchRetire(self, seat: int):
+        self._check(self.drv.fn("batch_retire")(self.m, seat))
+
+    def BatchRun(self, steps: int):
+        """`steps` greedy steps for every seat. Returns the records (seat, id, pos, retired) of live seats in step order."""
+        cap = steps * self._batch_seats
+        ev = np.zeros((max(1, cap), 4), np.int32)
+        n = C.c_int32(0)
+        self._check(self.drv.fn("batch_run")(self.m, steps, _ptr(ev, C.c_int32), cap, C.byref(n)))
+        return [(int(s), int(i), int(p), bool(f & 2)) for s, i, p, f in ev[: n.value]]
+
+    def BatchClose(self):
+        self._check(self.drv.fn("batch_close")(self.m))
+
     def Stats(self) -> abi.Stats:
         s = abi.Stats()
         self._check(self.drv.fn("stats")(self.m, C.byref(s)))

@@ -454,6 +454,93 @@ def drive(r, sessions: List[_Session], max_active: int, chunk: int, time_scale: 
                             "RidePasses": st.RidePasses, "RideRows": st.RideRows, "StragglerRuns": st.StragglerRuns}}
 
 
+def drive_device_batch(r, sessions: List[_Session], seats: int, chunk: int, run_steps: int = 8, time_scale: float = 1.0,
+                       clock=time.perf_counter, sleep=time.sleep) -> dict:
+    """The same trace on the resident's DEVICE batch (BatchOpen / BatchAdmit / BatchRun): `seats` seats over slots
+    0..seats-1, slot `seats` as the parking slot. Admission is the same FIFO (scheduler.Admission); an admitted session's
+    prompt is prefilled in chunks through the ordinary entry point, its first id is taken from the last chunk's logits, and
+    it is seated; every run decodes `run_steps` greedy steps for all seats on the device (ids fed back, positions advanced,
+    a seat retired when its session's output length is reached) with nothing packed per step, and the records say which
+    session drew what. Ids equal drive()'s (greedy): the steps are the same kernels on the same rows."""
+    from .resident import RaggedPrefill, RaggedSeq
+    adm = Admission(seats)
+    free = list(range(seats - 1, -1, -1))
+    seated: dict = {}
+    waiting = deque(sessions)
+    finished: List[_Session] = []
+    r.BatchOpen(seats, 0, seats, max_steps=run_steps)
+    runs, run_ms, live_rows = 0, [], []
+    t0 = clock()
+    now = lambda: (clock() - t0) * time_scale if time_scale > 0 else float("inf")
+
+    def start(s: _Session):
+        seat = free.pop()
+        s.slot = seat
+        r.ResetSlot(seat)
+        done, lg = 0, None
+        for n in chunk_plan(len(s.prompt), chunk):
+            last = done + n == len(s.prompt)
+            o = r.StepRagged([RaggedSeq(seat, done, None, s.prompt[done:done + n], None, RaggedPrefill(len(s.prompt), last))])
+            if last:
+                lg = o[0].Logits[-1]
+            done += n
+        t = now() if time_scale > 0 else clock() - t0
+        s.last_id = int(np.argmax(lg))
+        s.out_ids.append(s.last_id)
+        s.generated = 1
+        s.t_first = s.t_last = t
+        if s.generated >= s.out_len:
+            finish(s, t)
+        else:
+            r.BatchAdmit(seat, len(s.prompt), s.last_id, s.out_len - 1)
+            seated[seat] = s
+
+    def finish(s: _Session, t: float):
+        s.t_end = t
+        finished.append(s)
+        free.append(s.slot)
+        nxt = adm.Release()
+        if nxt is not None:
+            start(nxt.payload)
+
+    while waiting or seated or adm.Load() > 0:
+        t = now()
+        while waiting and waiting[0].arrival <= t:
+            s = waiting.popleft()
+            if adm.Enter(Record(str(s.idx), None, s)):
+                start(s)
+        if not seated:
+            if not waiting:
+                break
+            gap = (waiting[0].arrival - t) / time_scale if time_scale > 0 else 0.0
+            if gap > 0:
+                sleep(min(gap, 0.05))
+            continue
+        ts = clock()
+        recs = r.BatchRun(run_steps)
+        te = clock()
+        t = (te - t0) * time_scale if time_scale > 0 else te - t0
+        runs += 1
+        run_ms.append((te - ts) * 1e3)
+        live_rows.append(len(recs))
+        for seat, tok, _pos, retired in recs:
+            s = seated[seat]
+            s.last_id = tok
+            s.out_ids.append(tok)
+            s.generated += 1
+            s.gaps.append(t - s.t_last)   # a run's ids arrive together: the gap is the run's, as a client of this driver would see it
+            s.t_last = t
+            if retired:
+                del seated[seat]
+                finish(s, t)
+    r.BatchClose()
+    makespan = clock() - t0
+    out_tok = sum(s.generated for s in finished)
+    return {"sessions": len(finished), "makespan_s": makespan, "output_tokens": out_tok, "output_tok_s": out_tok / makespan,
+            "runs": runs, "steps_per_run": run_steps, "mean_run_ms": float(np.mean(run_ms)) if run_ms else 0.0,
+            "mean_live_rows_per_run": float(np.mean(live_rows)) if live_rows else 0.0}
+
+
 def run_poisson(shape: str, n_sessions: int, rate: float, max_active: int, seed: int, prompt_lo: int, prompt_hi: int, out_lo: int,
                 out_hi: int, chunk: int = 512, device: int = 0, n_layers: int = 0, time_scale: float = 1.0, preamble: int = 0,
                 n_preambles: int = 1, prefix_reuse: bool = False) -> dict:

@@ -230,6 +230,31 @@ int b200_copy_kv(b200_model* m, int dst_slot, int src_slot, int n_rows);
 int b200_prefill_last(b200_model* m, int slot, int n, const float* embs, const int32_t* token_ids,
                       int start_pos, float* logits_out);
 
+/* ---- the device batch: admission and retirement applied on the device ------------------------------------------------
+ * The reference's serve loop admits a request when a session is free and retires it when its generation ends
+ * (scheduler.Admission, internal/runtime/scheduler/admission.go:60-122), and its coalescer packs every step's batch on the
+ * host (decoder/mc3_batch.go:358-446). Here a fixed set of SEATS lives on the device: seat i is bound to KV slot
+ * first_slot + i; an empty seat runs a throw-away row on `park_slot`, so every step has the same shape and a finished
+ * sequence's KV stays in its slot (a follow-up turn continues it, or it serves as a prefix donor).
+ *   b200_batch_open   binds the seats (n_seats <= max_rows; park_slot outside the seats' slots; max_steps bounds a run).
+ *   b200_batch_admit  after the host has prefilled the seat's slot up to `pos` (b200_prefill_last, b200_step_ragged,
+ *                     b200_copy_kv): the sequence continues at `pos` by feeding `token`, for at most `max_new` tokens or
+ *                     until it draws `eos_id` (-1: none). The blocks it can still take are reserved against the pool:
+ *                     B200_KV_POOL_FULL (nothing changed) when they are not there.
+ *   b200_batch_retire takes a sequence off its seat (a cancelled request).
+ *   b200_batch_run    applies the commands queued since the last run, in order, then decodes `steps` greedy steps for all
+ *                     seats: ids are fed back and positions advance on the device, a seat retires itself when its sequence
+ *                     ends, and nothing is packed or uploaded per step. events_out receives one record of four ints per
+ *                     live seat and step, in step order then seat order: seat, drawn id, the position that was decoded,
+ *                     flags (bit 1: the seat retired after this step). Each record's id is what StepBatch would have
+ *                     drawn for that sequence at that position with a Greedy draw.
+ * Between runs every other entry point may be used on any slot but a live seat's. */
+int b200_batch_open(b200_model* m, int n_seats, int first_slot, int park_slot, int max_steps);
+int b200_batch_admit(b200_model* m, int seat, int pos, int token, int max_new, int eos_id);
+int b200_batch_retire(b200_model* m, int seat);
+int b200_batch_run(b200_model* m, int steps, int32_t* events_out, int max_events, int32_t* n_events_out);
+int b200_batch_close(b200_model* m);
+
 int b200_stats(b200_model* m, b200_stats_t* out);
 /* ---- operator-level entry points (host buffers in, host buffers out) -------------------------------
  * The reference exposes its matmul as Backend.MatmulBT(a, b, dst, M, K, N) (decoder/backend.go:23-32)

@@ -129,6 +129,12 @@ var (
 	b200CopyKV      func(m unsafe.Pointer, dstSlot, srcSlot, nRows int32) int32
 	b200PrefillLast func(m unsafe.Pointer, slot, n int32, embs *float32, tokenIDs *int32, startPos int32, logitsOut *float32) int32
 	b200Stats       func(m unsafe.Pointer, out *statsC) int32
+	// the device batch: admission and retirement applied on the device, k steps a call
+	b200BatchOpen   func(m unsafe.Pointer, nSeats, firstSlot, parkSlot, maxSteps int32) int32
+	b200BatchAdmit  func(m unsafe.Pointer, seat, pos, token, maxNew, eosID int32) int32
+	b200BatchRetire func(m unsafe.Pointer, seat int32) int32
+	b200BatchRun    func(m unsafe.Pointer, steps int32, eventsOut *int32, maxEvents int32, nEventsOut *int32) int32
+	b200BatchClose  func(m unsafe.Pointer) int32
 	// operator-level entry points (host buffers in and out): what a kernel test on the Go side calls, the way
 	// backend/cuda/kernels/*_test.go call their kernels against host twins
 	b200OpQuantG32      func(ctx unsafe.Pointer, x *float32, rows, k int32, codes *int8, scales *float32) int32
@@ -180,6 +186,8 @@ func load() error {
 			{&b200Reset, "b200_reset"}, {&b200BlockTable, "b200_block_table"}, {&b200UploadKV, "b200_upload_kv"},
 			{&b200StepRagged, "b200_step_ragged"}, {&b200Forward, "b200_forward"}, {&b200ForwardTopK, "b200_forward_topk"},
 			{&b200CopyKV, "b200_copy_kv"}, {&b200PrefillLast, "b200_prefill_last"}, {&b200Stats, "b200_stats"},
+			{&b200BatchOpen, "b200_batch_open"}, {&b200BatchAdmit, "b200_batch_admit"}, {&b200BatchRetire, "b200_batch_retire"},
+			{&b200BatchRun, "b200_batch_run"}, {&b200BatchClose, "b200_batch_close"},
 			{&b200OpQuantG32, "b200_op_quant_g32"}, {&b200OpQ4KDequant, "b200_op_q4k_dequant"},
 			{&b200OpQ4KMatmul, "b200_op_q4k_matmul"}, {&b200OpF16Matmul, "b200_op_f16_matmul"},
 			{&b200OpQ4KQuantize, "b200_op_q4k_quantize"}, {&b200OpRMSNorm, "b200_op_rmsnorm"}, {&b200OpRoute, "b200_op_route"},

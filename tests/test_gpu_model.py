@@ -365,28 +365,31 @@ def test_prefix_reuse_shares_blocks_and_copies_on_write(oracle_lib):
     assert np.array_equal(g2.BlockTable(1), o2.BlockTable(1))
 
 
-def test_serve_driver_with_prefix_reuse_draws_the_same_ids():
+def test_serve_driver_with_prefix_reuse_draws_the_same_ids(oracle_lib):
     """The continuous-batching driver over prompts that share a preamble, with the prefix index on and off: in the exact
     class a row is the same bits whichever slot or pass wrote it, so every session draws the same ids, while most preamble
-    rows are taken by CopyKV or kept in place instead of prefilled."""
+    rows are taken by CopyKV or kept in place instead of prefilled. The same driver over the CPU oracle (prefix index on)
+    is the reference: the GPU's ids are the oracle's."""
     from goinfer_b200 import kvindex, serve
     s = synth.SHAPES["tiny-dense"]
 
-    def run(reuse):
+    def run(reuse, on_oracle=False):
         cfg = synth.make_cfg(s, 4, 400, 16, 1 + 4 * 25, 64 + 4, abi.CLASS_EXACT, 0)
-        r = Resident(cfg)
+        r = oracle_lib.OracleResident(cfg) if on_oracle else Resident(cfg)
         synth.load_host_weights([r], s, 5, 0)
         r.finalize()
         trace = serve.poisson_trace(10, 40.0, 3, 150, 330, 3, 12, s.vocab, preamble=140, n_preambles=2)
         kw = dict(index=kvindex.SlotIndex(4), root=kvindex.Root("tiny", Precision="f16"), class_map=kvindex.ClassMap()) if reuse else {}
         res = serve.drive(r, trace, max_active=4, chunk=64, time_scale=4.0, **kw)
-        st = r.Stats()
+        st = None if on_oracle else r.Stats()
         r.Close()
         return res, [x.out_ids for x in sorted(trace, key=lambda x: x.idx)], st
 
     base, ids0, st0 = run(False)
     res, ids1, st1 = run(True)
     assert ids0 == ids1
+    _, ids_oracle, _ = run(True, on_oracle=True)
+    assert ids1 == ids_oracle
     pr = res["prefix_reuse"]
     assert pr["copies"] >= 1 and pr["rows_reused"] >= 5 * 128
     assert st1.prefill_rows == st0.prefill_rows - pr["rows_reused"]
@@ -663,3 +666,111 @@ def test_decode_loop_leaves_the_host_block_mirror_in_the_device_order(oracle_lib
         ok, err = close_logits(g.Forward(None, n, dst, token=7), o.Forward(None, n, dst, token=7))
         assert ok, (src, err)
     g.Close()
+
+
+def test_device_batch_admits_and_retires_on_the_device(oracle_lib):
+    """The device batch: three seats over slots 0..2, slot 5 as the parking slot. Sequences are prefilled through the
+    ordinary entry points and admitted between runs; a run decodes several greedy steps with ids fed back, positions
+    advanced and finished seats retired on the device (token budget, an end-of-sequence id), with nothing packed per step.
+    Every record must be the id the oracle's host-driven StepBatch draws for that sequence at that position. A seat freed
+    in the middle of a run idles on the parking slot without touching its finished sequence's KV (the finished slot then
+    serves as a CopyKV donor whose rows are the oracle's, which also shows that the host's block mirror followed the
+    device); a new sequence takes the seat in the next run; a cancelled sequence stops where it was; and an admission the
+    pool cannot back is refused with nothing changed."""
+    g, o, s = build_pair(oracle_lib, "tiny-qknorm", n_slots=6, ctx_cap=96, seed=12, kv_pool_blocks=13)
+    rng = np.random.default_rng(4)
+    g.BatchOpen(3, 0, 5, max_steps=16)
+    state = {}   # seat -> dict(pos, tok, rem, eos, live): what the oracle-driven twin of the batch holds
+
+    def prefill(slot, prompt):
+        for r in (g, o):
+            r.ResetSlot(slot)
+        lg = g.PrefillLast(None, 0, slot, prompt)
+        o.PrefillLast(None, 0, slot, prompt)
+        return int(np.argmax(lg))
+
+    def admit(seat, pos, tok, max_new, eos=-1):
+        g.BatchAdmit(seat, pos, tok, max_new, eos)
+        state[seat] = dict(pos=pos, tok=tok, rem=max_new, eos=eos, live=True)
+
+    def run_and_check(steps):
+        got = g.BatchRun(steps)
+        want = []
+        for _ in range(steps):
+            live = sorted(k for k, v in state.items() if v["live"])
+            if not live:
+                continue
+            bo = o.StepBatch([BatchSeq(k, state[k]["pos"], None, state[k]["tok"], BatchDraw(Greedy=True)) for k in live])
+            for k, b in zip(live, bo):
+                v = state[k]
+                v["rem"] -= 1
+                done = v["rem"] <= 0 or b.ID == v["eos"]
+                want.append((k, b.ID, v["pos"], done))
+                v["pos"] += 1
+                v["tok"] = b.ID
+                v["live"] = not done
+        assert got == want, (got, want)
+        return got
+
+    prompts = [rng.integers(0, s.vocab, n).tolist() for n in (15, 9, 4, 21)]
+    admit(0, 15, prefill(0, prompts[0]), 5)          # ends by its budget in the middle of the first run
+    admit(1, 9, prefill(1, prompts[1]), 40)
+    run_and_check(8)                                  # seat 0 retires after 5 steps and idles on the parking slot for 3
+    assert not state[0]["live"] and state[1]["live"]
+    # the finished sequence's rows are intact and the host's block mirror followed the device: a prefix with a partial last
+    # block taken from slot 0 (the tail block's id comes from the mirror) reads slot 0's rows
+    for r in (g, o):
+        r.CopyKV(4, 0, 18)
+    ok, err = close_logits(g.Forward(None, 18, 4, token=3), o.Forward(None, 18, 4, token=3))
+    assert ok, err
+    # a new sequence on the freed seat and a third one, admitted between runs; seat 1 keeps going
+    admit(0, 21, prefill(0, prompts[3]), 40)
+    admit(2, 4, prefill(2, prompts[2]), 12)
+    first = run_and_check(12)                         # seat 2 uses up its 12 tokens exactly at the end of this run
+    ids2 = [i for (k, i, _, _) in first if k == 2]
+    assert len(ids2) == 12 and not state[2]["live"]
+    # the same prompt again with an end-of-sequence id: the fifth id it drew. It must stop at that id's first occurrence.
+    eos = ids2[4]
+    admit(2, 4, prefill(2, prompts[2]), 12, eos)
+    g.BatchRetire(1)                                  # and a cancelled request
+    state[1]["live"] = False
+    again = run_and_check(8)
+    got2 = [(i, d) for (k, i, _, d) in again if k == 2]
+    stop = ids2.index(eos)
+    assert [i for i, _ in got2] == ids2[: stop + 1] and got2[-1][1] and not any(k == 1 for k, *_ in again)
+    # the mirror again, after block edges were crossed in different steps by different seats
+    for r in (g, o):
+        r.CopyKV(4, 0, state[0]["pos"] - 3)
+    ok, err = close_logits(g.Forward(None, state[0]["pos"] - 3, 4, token=5), o.Forward(None, state[0]["pos"] - 3, 4, token=5))
+    assert ok, err
+    # an admission the pool cannot back (the whole capacity of a slot, beside what seat 0 may still take): nothing changes
+    free_before = g.Stats().kv_blocks_in_use
+    with pytest.raises(ResidentError) as e:
+        g.BatchAdmit(1, state[1]["pos"], 1, 96 - state[1]["pos"])
+    assert e.value.status == abi.KV_POOL_FULL, str(e.value)
+    assert g.Stats().kv_blocks_in_use == free_before
+    run_and_check(3)                                  # and the batch still runs
+    g.BatchClose()
+    g.Close()
+
+
+def test_serve_on_the_device_batch_draws_what_the_host_driven_driver_draws():
+    """A small trace (all sessions at t=0, more sessions than seats, prompts cut into chunks) through serve.drive (the host
+    packs every step) and through serve.drive_device_batch (seats, admission and retirement on the device, eight steps a
+    run): every session's ids must be the same, in the exact class where a row's bits do not depend on its batch."""
+    from goinfer_b200 import serve
+    s = synth.SHAPES["tiny-dense"]
+    outs = []
+    for which in ("host", "device"):
+        r = Resident(synth.make_cfg(s, 5, 160, 16, 0, 64, abi.CLASS_EXACT, 0))
+        synth.load_host_weights([r], s, 21, 0)
+        r.finalize()
+        trace = serve.poisson_trace(11, 50.0, 3, 5, 70, 1, 40, s.vocab)
+        if which == "host":
+            res = serve.drive(r, trace, 4, 32, time_scale=0.0)
+        else:
+            res = serve.drive_device_batch(r, trace, 4, 32, run_steps=8, time_scale=0.0)
+        assert res["sessions"] == 11
+        outs.append({t.idx: list(t.out_ids) for t in trace})
+        r.Close()
+    assert outs[0] == outs[1]
