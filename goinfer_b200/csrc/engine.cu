@@ -218,10 +218,14 @@ __global__ void seats_apply_kernel(const SeatCmd* __restrict__ cmds, int n, int3
         }
     }
 }
+// the step's records go to events[*step][.] (the count of steps lives on the device so that every step is the same launches:
+// a run replays one captured graph); seats_next_step_kernel moves it on
 __global__ void seats_advance_kernel(int S, const int32_t* __restrict__ ids, int32_t* desc_slot, int park_slot, int32_t* live, int32_t* pos,
-                                     int32_t* tokens, int32_t* remaining, const int32_t* __restrict__ eos, SeatEvent* __restrict__ events) {
+                                     int32_t* tokens, int32_t* remaining, const int32_t* __restrict__ eos, SeatEvent* __restrict__ events,
+                                     const int32_t* __restrict__ step) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= S) return;
+    events += (size_t)(*step) * S;
     SeatEvent ev{i, -1, 0, 0};
     if (live[i]) {
         const int id = ids[i];
@@ -236,6 +240,8 @@ __global__ void seats_advance_kernel(int S, const int32_t* __restrict__ ids, int
     }
     events[i] = ev;
 }
+
+__global__ void seats_next_step_kernel(int32_t* step) { *step += 1; }
 
 __global__ void synth_kv_kernel(__half* kpool, __half* vpool, const int32_t* table_row, int n_pos, int nKV, int hd,
                                 int block_rows, float sigma, uint64_t seed) {
@@ -366,6 +372,10 @@ struct b200_model {
         int32_t *live = nullptr, *remaining = nullptr, *eos = nullptr;   // device, [n]
         int32_t *desc = nullptr, *pos = nullptr, *tokens = nullptr, *rows = nullptr;   // device: the seats' step descriptor, positions, tokens to feed, head rows
         b200_draw* draws = nullptr;
+        int32_t* step = nullptr;                                         // device: steps done in the current run
+        cudaGraphExec_t graph = nullptr;                                 // one captured step and what it was captured for
+        int graph_splits = 0;
+        int64_t graph_launches = 0;
         void *cmds = nullptr, *events = nullptr;                         // device: SeatCmd[2n], SeatEvent[max_steps][n]
         std::vector<int32_t> h_live, h_pos, h_end;                       // the host's view between runs (h_end: last position + 1 a seat may reach)
         std::vector<int32_t> pending;                                    // commands not yet applied, 6 words each
@@ -1146,6 +1156,7 @@ void b200_model_free(b200_model* m) {
     cudaStreamSynchronize(m->ctx->stream);
     tp_fused_teardown(m->ctx, &m->tpf);
     if (m->loop_graph) cudaGraphExecDestroy(m->loop_graph);
+    if (m->seats.graph) cudaGraphExecDestroy(m->seats.graph);
     for (void* p : m->allocs) cudaFree(p);
     if (m->p_desc) cudaFreeHost(m->p_desc);
     if (m->p_ids) cudaFreeHost(m->p_ids);
@@ -1756,6 +1767,7 @@ int b200_batch_open(b200_model* m, int n_seats, int first_slot, int park_slot, i
     ST_TRY(m->dalloc((void**)&q.tokens, (size_t)S * 4, sb));
     ST_TRY(m->dalloc((void**)&q.rows, (size_t)S * 4, sb));
     ST_TRY(m->dalloc((void**)&q.draws, (size_t)S * sizeof(b200_draw), sb));
+    ST_TRY(m->dalloc((void**)&q.step, 4, sb));
     ST_TRY(m->dalloc(&q.cmds, (size_t)2 * S * sizeof(SeatCmd), sb));
     ST_TRY(m->dalloc(&q.events, (size_t)max_steps * S * sizeof(SeatEvent), sb));
     std::vector<int32_t> d(2 + 3 * S), iota(S);
@@ -1846,8 +1858,11 @@ int b200_batch_run(b200_model* m, int steps, int32_t* events_out, int max_events
     int max_keys = 1;
     for (int i = 0; i < S; i++)
         if (q.h_live[i]) max_keys = std::max(max_keys, std::min(q.h_end[i], q.h_pos[i] + steps));
+    // rounded up to whole attention splits, so that a captured step's arguments hold for every run with that split count
+    if (!m->exact_scores) max_keys = std::min(c.ctx_cap, ceil_div(max_keys, 512) * 512);
+    CUDA_TRY(ctx, cudaMemsetAsync(q.step, 0, 4, ctx->stream));
     CUDA_TRY(ctx, cudaEventRecord(m->ev0, ctx->stream));
-    for (int st = 0; st < steps; st++) {
+    auto one_step = [&]() -> int {
         prepare_step_kernel<<<1, 256, 0, ctx->stream>>>(q.desc, q.pos, 1, m->table, m->max_blocks, c.kv_block_rows, m->slot_mapped, m->free_stack,
                                                         m->free_count, m->d_seq_row0, m->d_row_slot, m->d_row_pos, m->status, m->refs);
         LAUNCH_CHECK(ctx);
@@ -1859,9 +1874,50 @@ int b200_batch_run(b200_model* m, int steps, int32_t* events_out, int max_events
         if (c.final_softcap > 0.f) ST_TRY(launch_softcap(ctx, m->logits, (size_t)S * V, c.final_softcap));
         ST_TRY(launch_draw(ctx, m->logits, S, V, q.draws, m->d_ids, nullptr));
         seats_advance_kernel<<<ceil_div(S, 256), 256, 0, ctx->stream>>>(S, m->d_ids, q.desc + 2, q.park_slot, q.live, q.pos, q.tokens, q.remaining, q.eos,
-                                                                       (SeatEvent*)q.events + (size_t)st * S);
+                                                                       (SeatEvent*)q.events, q.step);
         LAUNCH_CHECK(ctx);
+        seats_next_step_kernel<<<1, 1, 0, ctx->stream>>>(q.step);
+        LAUNCH_CHECK(ctx);
+        return B200_OK;
+    };
+    // Every step is the same launches (who is seated, positions, tokens and the step count live on the device), so from its
+    // second step on a run replays one captured CUDA graph, kept from run to run while the attention kernels' split count
+    // stays. Off while kernels are being event-profiled and under tensor parallel (the collectives stay eager).
+    static const bool no_graph = getenv("B200_NO_GRAPH") != nullptr;
+    const bool use_graph = steps >= 3 && ctx->prof_mask == 0 && c.tp_size <= 1 && !no_graph;
+    int done = 0;
+    if (use_graph) {
+        ST_TRY(one_step());  // eager: first-use set-up (function attributes, tensor maps) happens outside the capture
+        done = 1;
+        const int key_splits = m->exact_scores ? max_keys : ceil_div(max_keys, 512);
+        if (!q.graph || q.graph_splits != key_splits) {
+            if (q.graph) { cudaGraphExecDestroy(q.graph); q.graph = nullptr; }
+            const int64_t l0 = ctx->launches;
+            CUDA_TRY(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+            const int st_cap = one_step();
+            cudaGraph_t gr = nullptr;
+            const cudaError_t ce = cudaStreamEndCapture(ctx->stream, &gr);
+            if (st_cap != B200_OK) {
+                if (gr) cudaGraphDestroy(gr);
+                return st_cap;
+            }
+            if (ce != cudaSuccess || !gr) B200_FAIL(ctx, B200_CUDA_ERROR, "capturing the batch step failed: %s", cudaGetErrorString(ce));
+            q.graph_launches = ctx->launches - l0;
+            ctx->launches = l0;  // capturing launched nothing
+            const cudaError_t ie = cudaGraphInstantiate(&q.graph, gr, 0);
+            cudaGraphDestroy(gr);
+            if (ie != cudaSuccess) {
+                q.graph = nullptr;
+                B200_FAIL(ctx, B200_CUDA_ERROR, "instantiating the batch step's graph failed: %s", cudaGetErrorString(ie));
+            }
+            q.graph_splits = key_splits;
+        }
+        for (; done < steps; done++) {
+            CUDA_TRY(ctx, cudaGraphLaunch(q.graph, ctx->stream));
+            ctx->launches += q.graph_launches;
+        }
     }
+    for (; done < steps; done++) ST_TRY(one_step());
     CUDA_TRY(ctx, cudaEventRecord(m->ev1, ctx->stream));
     std::vector<SeatEvent> ev((size_t)steps * S);
     CUDA_TRY(ctx, cudaMemcpyAsync(ev.data(), q.events, ev.size() * sizeof(SeatEvent), cudaMemcpyDeviceToHost, ctx->stream));
@@ -1901,7 +1957,8 @@ int b200_batch_close(b200_model* m) {
     auto& q = m->seats;
     if (!q.n) return B200_OK;
     cudaStreamSynchronize(m->ctx->stream);
-    for (void* p : {(void*)q.live, (void*)q.remaining, (void*)q.eos, (void*)q.desc, (void*)q.pos, (void*)q.tokens, (void*)q.rows, (void*)q.draws, q.cmds, q.events})
+    if (q.graph) cudaGraphExecDestroy(q.graph);
+    for (void* p : {(void*)q.live, (void*)q.remaining, (void*)q.eos, (void*)q.desc, (void*)q.pos, (void*)q.tokens, (void*)q.rows, (void*)q.draws, (void*)q.step, q.cmds, q.events})
         m->dfree(p);
     q = b200_model::Seats{};
     return B200_OK;
