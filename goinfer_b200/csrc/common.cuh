@@ -244,6 +244,9 @@ int launch_q4k_matmul_umma(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, i
 int launch_q4k_matmul_umma_swiglu(b200_ctx*, const uint8_t* W_interleaved, int N, int K, ActQ aq, int T, float* dst, int ldd, void* scratch,
                                   size_t scratch_bytes, int* err_flag, ActQ swiglu_out, bool force, bool* fused, __half* swiglu_x16 = nullptr,
                                   const uint8_t* W_tiles = nullptr);
+// Q6_K (bodies + d: launch_q6k_repack) on the same pipeline: the codes are put together and scaled in the kernel
+int launch_q6k_matmul_umma(b200_ctx*, const uint8_t* W_bodies, int N, int K, ActQ aq, int T, float* dst, int ldd);
+bool q6k_umma_fits(int sm_count, size_t slot_bytes, size_t scratch_bytes, int N, int K, int T);
 int launch_act_to_f16(b200_ctx*, ActQ aq, int T, int K, __half* out);  // the fp16 activation tiles of quantized rows (what the producers otherwise lay out)
 // gemm_small.cu: the fast class's matmul for up to 32 rows (fp16 dequant in registers, mma.sync, weights streamed once);
 // uses the context's scratch like the tcgen05 matmul and takes the producers' activation tiles the same way
@@ -290,7 +293,7 @@ int launch_paged_attention(b200_ctx*, const float* q, int ldq, int T, int nH, in
 
 // gemm_umma.cu: the cached tensor map (a CUtensorMap, opaque here) of a Q4_K matrix seen as bytes [N][nSB*144], box of one
 // super-block x box_rows rows; null (and ctx->err) when the driver cannot encode it
-const struct CUtensorMap_st* q4k_weight_map(b200_ctx*, const uint8_t* W, int N, int nSB, int box_rows);
+const struct CUtensorMap_st* q4k_weight_map(b200_ctx*, const uint8_t* W, int N, int nSB, int box_rows, int sb_bytes = 144);
 // gemm_stream.cu: Q4_K x int8 for 4..64 rows, weights streamed through a TMA ring (exact arithmetic; split-K when splits > 1)
 int launch_q4k_matmul_stream(b200_ctx*, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd, bool allow_split);
 // the same kernel over experts stacked in one buffer ([n_experts*N][K]) and expert-sorted activation rows

@@ -101,13 +101,18 @@ __device__ __forceinline__ float umma_silu(float x) { return __fdividef(x, __fad
 // SWIGLU (NT = 2, no K split): the weight rows are gate|up interleaved by 128 (tile t = gate rows 128t.. then up rows 128t..),
 // so a thread of the epilogue holds, for its token, gate and up of the same 32 columns: it writes silu(gate) * up quantized
 // per 32 (codes [T][F], scales and group sums [T][2*F/32]) and the f32 gate|up matrix never exists.
-template <int NT, bool SWIGLU>
+// FMT 4: Q4_K rows (144-byte super-blocks). FMT 6: Q6_K rows as the device keeps them, 208-byte bodies (ql[128], qh[64],
+// sixteen int8 sub-scales) with the super-blocks' d values in `dvals` ([N][nSB] halves): w = d * sc * (q - 32), the six-bit
+// q put together from a nibble and two upper bits; (q - 32) is exact in fp16 and takes the one rounding of the product with
+// fp16(d * sc). The rest of the kernel (activation ring, MMAs, epilogue) does not know the format.
+template <int NT, bool SWIGLU, int FMT = 4>
 __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __grid_constant__ CUtensorMap wmap, int N, int nSB,
                                                                         const __half* __restrict__ X16, int T,
                                                                         float* __restrict__ dst, int ldd, size_t split_stride,
                                                                         int* __restrict__ err_flag, int8_t* __restrict__ sw_codes,
                                                                         float* __restrict__ sw_scales, __half* __restrict__ sw_x16,
-                                                                        const uint8_t* __restrict__ w16) {
+                                                                        const uint8_t* __restrict__ w16, const unsigned short* __restrict__ dvals) {
+    constexpr int RAW = FMT == 6 ? 208 : kRawRow;   // raw bytes of one super-block of a weight row
     pdl_trigger();  // the next kernel's blocks may be placed as ours retire; they wait for our completion before they touch data
     extern __shared__ __align__(1024) uint8_t umma_smem[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], raw_full, raw_empty;
@@ -156,8 +161,88 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
         // loader fetches the tile's next super-blocks into `raw` meanwhile.
         const int wr = NT == 2 ? tid : tid & 127, hf1 = (tid >> 7) & 1;
         const unsigned b_off = (unsigned)wr * 128u, sw = (unsigned)(wr & 7);
-        uint4 hdr, q[8];  // the current super-block: d, dmin, 12 scale bytes; 128 code bytes
         bool ok = true;
+        if constexpr (FMT == 6) {
+            uint4 q[13];      // the row's current super-block: ql (8 x 16 bytes), qh (4), sub-scales (1)
+            float d = 0.f, d_next = 0.f;
+            const bool row_in = n0 + wr < N;
+            const unsigned short* dp = dvals + (size_t)min(n0 + wr, N - 1) * nSB + sb0;
+            if (n_sb > 0 && row_in) d_next = __half2float(__ushort_as_half(dp[0]));
+            const unsigned k_nib = opaque_u(0x00F000F0u), k_up = opaque_u(0x03000300u), k_magic = opaque_u(0x54005400u);   // registers: one LOP3 per use
+            const __half2 k96 = __float2half2_rn(96.f);
+            auto step6 = [&](int it, int p) -> bool {  // p = it & 3, a literal at every call site
+                if (it > 1) {
+                    const bool w_ok = mbar_wait(smem_u32(&empty_bar[(it - 2) % kStages]), (unsigned)(((it - 2) / kStages) & 1), abort_v);
+                    if (!__all_sync(0xffffffffu, w_ok)) return false;
+                }
+                if (p == 0) {
+                    const int sb = it >> 2;
+                    const bool w_ok = mbar_wait(smem_u32(&raw_full), (unsigned)(sb & 1), abort_v);
+                    if (!__all_sync(0xffffffffu, w_ok)) return false;
+                    const uint4* rp = reinterpret_cast<const uint4*>(raw + (size_t)wr * RAW);
+#pragma unroll
+                    for (int i = 0; i < 13; i++) q[i] = rp[i];
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&raw_empty));
+                    d = d_next;
+                    if (sb + 1 < n_sb && row_in) d_next = __half2float(__ushort_as_half(dp[sb + 1]));
+                }
+                {
+                    // chunk p = elements 64 p .. 64 p + 63 of the block: half p >> 1 of the block; its first 32 elements take the
+                    // low (p even) or high (p odd) nibbles of ql[64 half + l] and bit pair (p & 1) * 2 of qh[32 half + l], the
+                    // other 32 those of ql[64 half + 32 + l] and the next bit pair; sub-scales 8 half + 4 (p & 1) + {0,1 | 2,3}
+                    const int half = p >> 1, odd = p & 1;
+                    uint8_t* rowp = bring + (size_t)(it & 1) * BSTAGE + b_off;
+                    const unsigned scw = (&q[12].x)[2 * half + odd];
+#pragma unroll
+                    for (int hf = 0; hf < 2; hf++) {
+                        if (NT == 1 && hf != hf1) continue;
+                        const uint4 la = q[4 * half + 2 * hf], lb = q[4 * half + 2 * hf + 1];   // ql of l = 0..15, 16..31
+                        const uint4 ua = q[8 + 2 * half], ub = q[8 + 2 * half + 1];               // qh of the same l
+                        const unsigned lw[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+                        const unsigned uw[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+                        const int ush = 4 * odd + 2 * hf;   // the bit pair's place in a qh byte
+#pragma unroll
+                        for (int ch = 0; ch < 4; ch++) {     // 8 elements a piece: l = 8 ch .. 8 ch + 7, sub-scale l / 16
+                            const int sc = (int)(signed char)((scw >> (8 * (2 * hf + (ch >> 1)))) & 0xffu);
+                            const __half2 ds = __half2half2(__float2half_rn(d * (float)sc));
+                            uint4 o;
+                            unsigned* ov = &o.x;
+#pragma unroll
+                            for (int wi = 0; wi < 2; wi++) {
+                                const unsigned w = lw[2 * ch + wi], u = uw[2 * ch + wi];
+#pragma unroll
+                                for (int b1 = 0; b1 < 2; b1++) {   // bytes (0,2) then (1,3) of the word: the tile's order inside every four
+                                    // nibble to bits [4,8) of each half, the two upper bits to [8,10): the half 64 + q
+                                    const int nfrom = 8 * b1 + 4 * odd;      // where the nibble starts in the 16-bit lane
+                                    const unsigned nsh = nfrom <= 4 ? (w << (4 - nfrom)) : (w >> (nfrom - 4));
+                                    const int ufrom = 8 * b1 + ush;
+                                    const unsigned us = ufrom <= 8 ? (u << (8 - ufrom)) : (u >> (ufrom - 8));
+                                    unsigned t = and_or_u(nsh, k_nib, k_magic);
+                                    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(us), "r"(k_up), "r"(t));   // (us & k_up) | t
+                                    const __half2 hq = __hsub2(*reinterpret_cast<__half2*>(&t), k96);   // q - 32, exact
+                                    const __half2 hv = __hmul2(hq, ds);
+                                    ov[2 * wi + b1] = *reinterpret_cast<const unsigned*>(&hv);
+                                }
+                            }
+                            *reinterpret_cast<uint4*>(rowp + (((unsigned)(4 * hf + ch) ^ sw) << 4)) = o;
+                        }
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&full_bar[it % kStages]));
+                return true;
+            };
+            for (int it = 0; it < n_it && ok; it += 4) {
+                ok = step6(it, 0);
+                if (ok) ok = step6(it + 1, 1);
+                if (ok) ok = step6(it + 2, 2);
+                if (ok) ok = step6(it + 3, 3);
+            }
+        } else {
+        uint4 hdr, q[8];  // the current super-block: d, dmin, 12 scale bytes; 128 code bytes
         const unsigned k_mask = opaque_u(0x03C003C0u), k_magic = opaque_u(0x4C004C00u);   // registers, so that mask-and-or is one LOP3
 
         auto step = [&](int it, int p) -> bool {  // p = it & 3, a literal at every call site
@@ -170,7 +255,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                 const int sb = it >> 2;
                 const bool w_ok = mbar_wait(smem_u32(&raw_full), (unsigned)(sb & 1), abort_v);
                 if (!__all_sync(0xffffffffu, w_ok)) return false;
-                const uint4* rp = reinterpret_cast<const uint4*>(raw + (size_t)wr * kRawRow);
+                const uint4* rp = reinterpret_cast<const uint4*>(raw + (size_t)wr * RAW);
                 hdr = rp[0];
 #pragma unroll
                 for (int i = 0; i < 8; i++) q[i] = rp[1 + i];
@@ -212,6 +297,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
             if (ok) ok = step(it + 1, 1);
             if (ok) ok = step(it + 2, 2);
             if (ok) ok = step(it + 3, 3);
+        }
         }
         if (!ok) abort_s = 1;
     } else if (warp == kProducerWarps && lane == 0) {
@@ -274,8 +360,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                     bulk_g2s(smem_u32(raw + (size_t)i * 16 * kRawRow), w16 + ((size_t)(tile0 + i) * nSB + sb0 + sb) * (16 * kRawRow), 16 * kRawRow,
                              smem_u32(&raw_full));
             } else {
-                mbar_arrive_expect_tx(smem_u32(&raw_full), (unsigned)(128 * NT * kRawRow));
-                tensor_g2s_2d(smem_u32(raw), &wmap, (sb0 + sb) * kRawRow, n0, smem_u32(&raw_full));
+                mbar_arrive_expect_tx(smem_u32(&raw_full), (unsigned)(128 * NT * RAW));
+                tensor_g2s_2d(smem_u32(raw), &wmap, (sb0 + sb) * RAW, n0, smem_u32(&raw_full));
             }
             issued = sb + 1;
         }
@@ -442,22 +528,22 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, size_t spli
 // The tensor map of a weight matrix seen as bytes, [N rows][nSB * 144], with a box of one super-block x box_rows rows. A map
 // depends only on its key, so the cache never goes stale. cuTensorMapEncodeTiled is reached through the runtime's
 // driver-entry-point lookup.
-const CUtensorMap* q4k_weight_map(b200_ctx* ctx, const uint8_t* W, int N, int nSB, int box_rows) {
+const CUtensorMap* q4k_weight_map(b200_ctx* ctx, const uint8_t* W, int N, int nSB, int box_rows, int sb_bytes) {
     static std::mutex mu;
-    static std::map<std::tuple<const void*, int, int, int>, CUtensorMap*> cache;
+    static std::map<std::tuple<const void*, int, int, int, int>, CUtensorMap*> cache;
     std::lock_guard<std::mutex> lock(mu);
     const tensor_map_encode_fn encode = tensor_map_encoder();
     if (!encode) {
         ctx->err = "cuTensorMapEncodeTiled is not available from this driver";
         return nullptr;
     }
-    const auto key = std::make_tuple((const void*)W, N, nSB, box_rows);
+    const auto key = std::make_tuple((const void*)W, N, nSB, box_rows, sb_bytes);
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
     CUtensorMap* m = new CUtensorMap;
-    const cuuint64_t dims[2] = {(cuuint64_t)nSB * 144, (cuuint64_t)N};
-    const cuuint64_t strides[1] = {(cuuint64_t)nSB * 144};
-    const cuuint32_t box[2] = {(cuuint32_t)144, (cuuint32_t)box_rows};
+    const cuuint64_t dims[2] = {(cuuint64_t)nSB * sb_bytes, (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)nSB * sb_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)sb_bytes, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(W), dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -551,7 +637,7 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     }
     static const CUtensorMap no_map{};  // the tile-major copy is fetched with plain bulk copies
-    const CUtensorMap* wmap = W_tiles ? &no_map : q4k_weight_map(ctx, W, N, nSB, 128 * NT);
+    const CUtensorMap* wmap = W_tiles ? &no_map : q4k_weight_map(ctx, W, N, nSB, 128 * NT, kRawRow);
     if (!wmap) return B200_CUDA_ERROR;
     dim3 grid(n_tiles, t_tiles, splits);
     float* out = splits > 1 ? part : dst;
@@ -562,14 +648,90 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
         int8_t* const no_codes = nullptr;
         float* const no_scales = nullptr;
         __half* const no_x16 = nullptr;
-        if (fuse) launch_pdl(q4k_umma_gemm_kernel<2, true>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, sw.codes, sw.scales, sw_x16, W_tiles);
-        else if (NT == 2) launch_pdl(q4k_umma_gemm_kernel<2, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16, W_tiles);
-        else launch_pdl(q4k_umma_gemm_kernel<1, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16, W_tiles);
+        const unsigned short* const no_d = nullptr;
+        if (fuse) launch_pdl(q4k_umma_gemm_kernel<2, true>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, sw.codes, sw.scales, sw_x16, W_tiles, no_d);
+        else if (NT == 2) launch_pdl(q4k_umma_gemm_kernel<2, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16, W_tiles, no_d);
+        else launch_pdl(q4k_umma_gemm_kernel<1, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16, W_tiles, no_d);
     }
     LAUNCH_CHECK(ctx);
     if (fuse && fused) *fused = true;
     if (splits > 1) {
         if (ctx->defer_reduce && ldd == N) {  // the consumer adds the partials (same order, same bits)
+            ctx->pending = Parts{part, stride, splits, dst, T, N};
+        } else {
+            launch_pdl(splitk_reduce_kernel, dim3((unsigned)(((size_t)T * N + 255) / 256)), dim3(256), 0, ctx->stream, part, stride, splits, T, N, dst, ldd);
+            LAUNCH_CHECK(ctx);
+        }
+    }
+    return B200_OK;
+}
+
+// Q6_K weights (208-byte bodies row by row, d values behind them: launch_q6k_repack) x the per-32 activations as fp16
+// tiles, on the same tcgen05 pipeline: the producers put the six-bit codes together and scale them in registers, so no
+// dequantized copy of the matrix exists. From 32 rows in the fast class.
+size_t q6k_umma_smem_bytes() { return (size_t)kStages * 2 * kTileBytes + 2 * 2 * kTileBytes + (size_t)kProducers * 208 + 1024; }
+
+// whether T rows of an [N][K] Q6_K matrix fit a scratch of `scratch_bytes` whose first 2 * slot_bytes hold activation slots
+bool q6k_umma_fits(int sm_count, size_t slot_bytes, size_t scratch_bytes, int N, int K, int T) {
+    if (K % 256 || T < 1 || !scratch_bytes) return false;
+    const int nSB = K / 256, t_tiles = ceil_div(T, 256);
+    const int max_splits = std::max(1, std::min(4, nSB / 2));
+    const int NT = ceil_div(N, 256) * t_tiles * max_splits >= sm_count * 3 / 4 ? 2 : 1;
+    const int n_tiles = ceil_div(N, 128 * NT);
+    const int splits = std::max(1, std::min(max_splits, sm_count / std::max(1, n_tiles * t_tiles)));
+    const size_t x_bytes = (size_t)t_tiles * 256 * K * 2;
+    const size_t part_bytes = splits > 1 ? (size_t)splits * T * N * 4 : 0;
+    const size_t part_off = slot_bytes ? 2 * slot_bytes : ((x_bytes + 255) & ~(size_t)255);
+    return !(slot_bytes && x_bytes > slot_bytes) && part_off + part_bytes + 256 <= scratch_bytes;
+}
+
+int launch_q6k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd) {
+    ST_TRY(flush_pending_parts(ctx));  // the scratch is about to be reused
+    if (K % 256 || (reinterpret_cast<uintptr_t>(W) & 15)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q6_K needs K %% 256 == 0 and 16-byte aligned weights");
+    if (!ctx->umma_scratch) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the tcgen05 matmul needs the fast class's scratch");
+    const int nSB = K / 256, t_tiles = ceil_div(T, 256);
+    const int max_splits = std::max(1, std::min(4, nSB / 2));
+    const int NT = ceil_div(N, 256) * t_tiles * max_splits >= ctx->sm_count * 3 / 4 ? 2 : 1;
+    const int n_tiles = ceil_div(N, 128 * NT);
+    const int splits = std::max(1, std::min(max_splits, ctx->sm_count / std::max(1, n_tiles * t_tiles)));
+    const size_t x_bytes = (size_t)t_tiles * 256 * K * 2;
+    const size_t part_bytes = splits > 1 ? (size_t)splits * T * N * 4 : 0;
+    const bool slots = ctx->x16_slot_bytes > 0;
+    const size_t part_off = slots ? 2 * ctx->x16_slot_bytes : ((x_bytes + 255) & ~(size_t)255);
+    if ((slots && x_bytes > ctx->x16_slot_bytes) || part_off + part_bytes + 256 > ctx->umma_scratch_bytes)
+        B200_FAIL(ctx, B200_BAD_ARGUMENT, "tcgen05 matmul scratch too small");
+    float* part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ctx->umma_scratch) + part_off);
+    const __half* x16 = slots ? ctx->x16_ready : nullptr;
+    if (!x16) {
+        __half* mine = slots ? x16_next_slot(ctx) : reinterpret_cast<__half*>(ctx->umma_scratch);
+        ST_TRY(launch_act_to_f16(ctx, aq, T, K, mine));
+        x16 = mine;
+    }
+    const int smem = (int)q6k_umma_smem_bytes();
+    static PerDeviceOnce attr_once;  // the attribute belongs to the device
+    if (attr_once.first(ctx->device)) {
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<1, false, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, false, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    }
+    const CUtensorMap* wmap = q4k_weight_map(ctx, W, N, nSB, 128 * NT, 208);
+    if (!wmap) return B200_CUDA_ERROR;
+    const unsigned short* dvals = reinterpret_cast<const unsigned short*>(W + (size_t)N * nSB * 208);
+    dim3 grid(n_tiles, t_tiles, splits);
+    float* out = splits > 1 ? part : dst;
+    const int out_ld = splits > 1 ? N : ldd;
+    const size_t stride = splits > 1 ? (size_t)T * N : 0;
+    {
+        ProfScope ps(ctx, PROF_Q4K_GEMM);
+        int8_t* const no_codes = nullptr;
+        float* const no_scales = nullptr;
+        __half* const no_x16 = nullptr;
+        const uint8_t* const no_tiles = nullptr;
+        if (NT == 2) launch_pdl(q4k_umma_gemm_kernel<2, false, 6>, grid, dim3(kUmmaThreads), (size_t)smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, ctx->err_flag, no_codes, no_scales, no_x16, no_tiles, dvals);
+        else launch_pdl(q4k_umma_gemm_kernel<1, false, 6>, grid, dim3(kUmmaThreads), (size_t)smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, ctx->err_flag, no_codes, no_scales, no_x16, no_tiles, dvals);
+    }
+    LAUNCH_CHECK(ctx);
+    if (splits > 1) {
+        if (ctx->defer_reduce && ldd == N) {
             ctx->pending = Parts{part, stride, splits, dst, T, N};
         } else {
             launch_pdl(splitk_reduce_kernel, dim3((unsigned)(((size_t)T * N + 255) / 256)), dim3(256), 0, ctx->stream, part, stride, splits, T, N, dst, ldd);

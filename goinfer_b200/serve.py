@@ -543,7 +543,7 @@ def drive_device_batch(r, sessions: List[_Session], seats: int, chunk: int, run_
 
 def run_poisson(shape: str, n_sessions: int, rate: float, max_active: int, seed: int, prompt_lo: int, prompt_hi: int, out_lo: int,
                 out_hi: int, chunk: int = 512, device: int = 0, n_layers: int = 0, time_scale: float = 1.0, preamble: int = 0,
-                n_preambles: int = 1, prefix_reuse: bool = False) -> dict:
+                n_preambles: int = 1, prefix_reuse: bool = False, device_batch: int = 0) -> dict:
     """Builds the synthetic model, runs the trace, returns one result dict. time_scale > 1 compresses the arrival clock;
     0 makes every session arrive at once (the closed-loop capacity of the engine at `max_active`). preamble > 0 gives the
     prompts shared leading runs; prefix_reuse serves them from the slots that already hold them."""
@@ -552,7 +552,8 @@ def run_poisson(shape: str, n_sessions: int, rate: float, max_active: int, seed:
     s = synth.SHAPES[shape]
     cap = prompt_hi + out_hi + 1
     blocks = 1 + max_active * ((cap + 15) // 16)
-    cfg = synth.make_cfg(s, max_active, cap, 16, blocks, chunk + max_active, abi.CLASS_AUTO, n_layers)
+    # (the device batch parks its empty seats on one more slot)
+    cfg = synth.make_cfg(s, max_active + (1 if device_batch else 0), cap, 16, blocks + 1, chunk + max_active, abi.CLASS_AUTO, n_layers)
     r = Resident(cfg, device=device)
     synth.load_device_weights(r, s, seed=seed, n_layers=n_layers)
     r.finalize()
@@ -565,7 +566,12 @@ def run_poisson(shape: str, n_sessions: int, rate: float, max_active: int, seed:
         caps = r.ResidentCaps()
         kw = dict(index=kvindex.SlotIndex(max_active), root=kvindex.Root(Model=f"{shape}/q4k/b200", Precision="f16"),
                   class_map=kvindex.ClassMap(Floor=caps.fast_prefill_floor, MinRows=16) if caps.has_fast_prefill else kvindex.ClassMap())
-    res = drive(r, trace, max_active, chunk, time_scale, **kw)
+    if device_batch:
+        res = drive_device_batch(r, trace, max_active, chunk, run_steps=device_batch, time_scale=time_scale)
+    else:
+        res = drive(r, trace, max_active, chunk, time_scale, **kw)
+    res["driver"] = (f"device batch: seats and retirement on the device, {device_batch} steps a run, prompts prefilled between runs" if device_batch
+                     else "host-driven: a ragged step packed per step, prefill chunks riding the decode runs")
     res["workload"] = (f"{shape}: {n_sessions} sessions, Poisson {rate}/s seed {seed}"
                        f"{'' if time_scale == 1.0 else f' (arrival clock x{time_scale})' if time_scale > 0 else ' (all at t=0)'}, "
                        f"prompts U[{prompt_lo},{prompt_hi}]{f' sharing {n_preambles} preamble(s) of {preamble}' if preamble else ''}"

@@ -218,6 +218,7 @@ def main():
     v.add_argument("--preamble", type=int, default=0, help="leading tokens every prompt shares with one of --n-preambles runs")
     v.add_argument("--n-preambles", type=int, default=1)
     v.add_argument("--prefix-reuse", action="store_true", help="serve shared prefixes from the slots that hold them (CopyKV)")
+    v.add_argument("--device-batch", type=int, default=0, help="k > 0: decode on the device batch, k steps a run (admission and retirement on the device)")
     args = ap.parse_args()
     if args.what == "decode":
         print(json.dumps(decode(args.shape, args.batch, args.ctx_lo, args.ctx_hi, args.seed, args.steps, args.warmup,
@@ -232,7 +233,7 @@ def main():
         print(json.dumps(run_poisson(args.shape, args.sessions, args.rate, args.max_active, args.seed, args.prompt_lo,
                                      args.prompt_hi, args.out_lo, args.out_hi, args.chunk, n_layers=args.layers,
                                      time_scale=args.time_scale, preamble=args.preamble, n_preambles=args.n_preambles,
-                                     prefix_reuse=args.prefix_reuse)))
+                                     prefix_reuse=args.prefix_reuse, device_batch=args.device_batch)))
 
 
 if __name__ == "__main__":

@@ -67,6 +67,10 @@ int b200_bench_prefill_attention(b200_ctx* ctx, int rows, int pos0, int n_heads,
  * the entry point that launched it reports B200_TIMEOUT. (0, -1) disarms. Nothing faults or spins without a limit. */
 int b200_debug_wait_fault(b200_ctx* ctx, int polls, int withhold_chunk);
 
+/* Test hook: dst[M][N] = a . W^T for W Q6_K given as the file's 210-byte blocks, on the tcgen05 kernel that assembles and
+ * scales the six-bit codes itself (what a fast-class model runs for Q6_K tensors from 32 rows), at any M. */
+int b200_debug_q6k_matmul_umma(b200_ctx* ctx, const uint8_t* w_host, const float* a_host, int M, int K, int N, float* dst_host);
+
 /* 1 when the model's tensor-parallel layers sum their partial products with the library's own kernel over peer memory
  * (the ranks share a host and could map one another's buffers), 0 when they call NCCL's all-reduce. */
 int b200_tp_fused_active(b200_model* m);
