@@ -125,7 +125,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
     // split-K ranges are whole super-blocks (4 chunks of 64)
     const int splits = gridDim.z, sb0 = (int)((long long)nSB * blockIdx.z / splits),
               sb1 = (int)((long long)nSB * (blockIdx.z + 1) / splits);
-    const int n_sb = sb1 - sb0, n_it = 4 * n_sb, K = nSB * 256;
+    const int n_sb = sb1 - sb0, n_it = 4 * n_sb;
+    // token tiles of 128 this CTA really has: with 128 rows or fewer left, the second tile's copies, MMAs and epilogue are left out
+    const int mt_count = (T - t0 > 128) ? 2 : 1;
     // the swizzle atoms want 1024-byte aligned tiles; the launch reserves 1024 spare bytes for this round-up
     uint8_t* smem = umma_smem + ((1024u - (smem_u32(umma_smem) & 1023u)) & 1023u);
     uint8_t* bring = smem + (size_t)kStages * STAGE;  // 2 B stages of BSTAGE bytes
@@ -311,11 +313,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
             const unsigned a0 = smem_u32(smem + (size_t)(it % kStages) * STAGE), b0 = smem_u32(bring + (size_t)(it & 1) * BSTAGE);
             // one instruction spans all 128*NT weight rows (N = 128*NT): the token tile is fetched once for them
 #pragma unroll
-            for (int mt = 0; mt < 2; mt++)
+            for (int mt = 0; mt < 2; mt++) {
+                if (mt >= mt_count) break;
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++)
                     umma_f16(tmem_base + mt * 128 * NT, umma_desc(a0 + mt * kTileBytes + ks * 32), umma_desc(b0 + ks * 32),
                              idesc_for(128 * NT), (it > 0 || ks > 0) ? 1u : 0u);
+            }
             umma_commit(smem_u32(&empty_bar[it % kStages]));
         }
         // all MMAs done: the last commit covers every earlier one. Only this thread waits for it; everyone else
@@ -335,8 +339,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                 break;
             }
             const unsigned bar = smem_u32(&full_bar[it % kStages]);
-            mbar_arrive_expect_tx(bar, STAGE);
-            bulk_g2s(smem_u32(smem + (size_t)(it % kStages) * STAGE), src + (size_t)it * STAGE, STAGE, bar);
+            const unsigned a_bytes = (unsigned)(mt_count * kTileBytes);   // rows 0..127 of a 256-row tile are its first half
+            mbar_arrive_expect_tx(bar, a_bytes);
+            bulk_g2s(smem_u32(smem + (size_t)(it % kStages) * STAGE), src + (size_t)it * STAGE, a_bytes, bar);
             issued = it + 1;
         }
         if (abort_s) {  // copies still in flight must land before the CTA may leave: bounded waits on their barriers
@@ -373,7 +378,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     if (abort_s) {
         if (tid == 0 && err_flag) atomicExch(err_flag, 1);
-    } else if (n_it > 0 && warp < kProducerWarps) {
+    } else if (n_it > 0 && warp < kProducerWarps && (warp >> 2) < mt_count) {
         // warp w reads TMEM lanes 32*(w%4).. of token tile mt = w/4, all 128*NT columns:
         // tokens t0 + 128*mt + 32*(w%4) + lane, output columns n0 + column
         float* out = dst + (size_t)blockIdx.z * split_stride;
