@@ -365,9 +365,8 @@ def run_gpu(args):
         extra["c1"] = workloads.decode("c1-1.1b", 64, 32, 1280, 1, steps=8, warmup=3, device=local)
     if world > 1 and not args.no_extra:
         # the 70B-class shape split over these same ranks (its own communicator; the largest batch whose KV fits)
-        from goinfer_b200 import workloads
         barrier()
-        tp_c5 = workloads.decode_tp("c5-70b", 256, 1024, 32768, 4, steps=4, warmup=2)
+        tp_c5 = tp_leg(rank)
         if tp_c5 is not None:
             extra["tp_c5"] = tp_c5
 
@@ -429,6 +428,44 @@ def run_gpu(args):
             line[name] = {"weight_mb": gb * 1e3, "read_floor_ms": floor_ms, "read_floor_frac_of_measured_peak": gb / (floor_ms * 1e-3) / peak,
                           "rows": rows}
     print(json.dumps(line), flush=True)
+
+
+def tp_leg(rank: int):
+    """The tensor-parallel leg: every rank starts a child process (python -m goinfer_b200.workloads decode-tp) that joins a
+    process group of its own on the next port, so that a failure or a stall of that leg costs the leg and not the
+    benchmark's line; rank 0 returns the child's result (or what went wrong), the others None."""
+    import subprocess
+    env = dict(os.environ)
+    env["MASTER_PORT"] = str(int(env.get("MASTER_PORT", "29500")) + 23)
+    env["NCCL_NVLS_ENABLE"] = "0"   # the leg's sums across ranks run on the library's own kernel; its few NCCL calls need no multicast
+    for k in [k for k in env if k.startswith("TORCHELASTIC_")]:
+        env.pop(k)
+    torch_cache_clear()
+    cmd = [sys.executable, "-m", "goinfer_b200.workloads", "decode-tp", "--shape", "c5-70b", "--batch", "256", "--ctx-lo", "1024",
+           "--ctx-hi", "32768", "--seed", "4", "--steps", "4", "--warmup", "2"]
+    p = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, env=env, cwd=ROOT, text=True)
+    try:
+        out, err = p.communicate(timeout=480)
+    except subprocess.TimeoutExpired:
+        p.kill()
+        out, err = p.communicate()
+        return {"error": "the tensor-parallel leg did not finish in 480 s"} if rank == 0 else None
+    if rank != 0:
+        return None
+    for line in reversed(out.splitlines()):
+        if line.startswith("{"):
+            try:
+                return json.loads(line)
+            except ValueError:
+                break
+    return {"error": f"the tensor-parallel leg exited with code {p.returncode}", "stderr_tail": err[-600:]}
+
+
+def torch_cache_clear():
+    import gc
+    import torch
+    gc.collect()
+    torch.cuda.empty_cache()
 
 
 def main():

@@ -99,6 +99,11 @@ def decode_tp(shape: str, batch: int, ctx_lo: int, ctx_hi: int, seed: int, steps
     w_bytes = L * (s.hidden * (sl.n_heads + 2 * sl.n_kv_heads) * s.head_dim + s.hidden * sl.n_heads * s.head_dim
                        + 3 * s.hidden * sl.ffn) * 144 / 256 + (s.vocab + s.vocab // world) * s.hidden * 2
     budget = (kv_budget_gb * 1e9) if kv_budget_gb > 0 else (178e9 - w_bytes - 6e9)
+    # what is really free on the ranks' GPUs (a parent process may hold a context): the smallest figure decides for all
+    free = torch.tensor([float(torch.cuda.mem_get_info(dev)[0])], dtype=torch.float64, device=("cuda:%d" % dev) if on_gpu else "cpu")
+    dist.all_reduce(free, op=dist.ReduceOp.MIN)
+    if kv_budget_gb <= 0:
+        budget = min(budget, float(free.cpu()[0]) - w_bytes - 6e9)
     need = np.cumsum((np.ceil((ctx_all + growth) / 16) * 16) * per_pos)
     b_fit = int(np.searchsorted(need, budget, side="right"))
     b_fit = max(2, min(batch, b_fit))
