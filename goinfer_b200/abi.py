@@ -70,6 +70,6 @@ EXPORTS = (
 BENCH_EXPORTS = (
     "b200_launch_count", "b200_synth_tensor", "b200_synth_kv", "b200_decode_loop_device", "b200_debug_read_hidden",
     "b200_profile", "b200_profile_read", "b200_bench_read", "b200_bench_kq_matmul", "b200_bench_q4k_matmul",
-    "b200_bench_f16_matmul", "b200_bench_attention", "b200_bench_prefill_attention", "b200_debug_wait_fault", "b200_tp_fused_active", "b200_bench_tp_reduce", "b200_debug_q6k_matmul_umma",
+    "b200_bench_f16_matmul", "b200_bench_attention", "b200_bench_prefill_attention", "b200_debug_wait_fault", "b200_tp_fused_active", "b200_bench_tp_reduce", "b200_debug_q6k_matmul_umma", "b200_debug_kq_matmul_umma",
     "b200_debug_tp_reduce_emulated",
 )

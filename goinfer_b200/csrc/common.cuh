@@ -246,6 +246,7 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx*, const uint8_t* W_interleaved, int N
                                   const uint8_t* W_tiles = nullptr);
 // Q6_K (bodies + d: launch_q6k_repack) on the same pipeline: the codes are put together and scaled in the kernel
 int launch_q6k_matmul_umma(b200_ctx*, const uint8_t* W_bodies, int N, int K, ActQ aq, int T, float* dst, int ldd);
+int launch_kq_matmul_umma(b200_ctx*, int kind, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd);  // Q5_K (file blocks) or Q6_K
 bool q6k_umma_fits(int sm_count, size_t slot_bytes, size_t scratch_bytes, int N, int K, int T);
 int launch_act_to_f16(b200_ctx*, ActQ aq, int T, int K, __half* out);  // the fp16 activation tiles of quantized rows (what the producers otherwise lay out)
 // gemm_small.cu: the fast class's matmul for up to 32 rows (fp16 dequant in registers, mma.sync, weights streamed once);

@@ -526,10 +526,10 @@ int matmul(b200_model* m, const DevMat& W, const float* xf, ActQ xq, int T, floa
         // from 32 rows in the fast class: fp16 copy of the weights x (code * scale) activations on the tensor cores (the
         // dp4a lane re-reads the matrix for every four rows); the weights are then within 2^-11 of their values
         static const bool no_umma = getenv("B200_NO_UMMA") != nullptr, q6_copy = getenv("B200_Q6K_F16_COPY") != nullptr;
-        // Q6_K: the tcgen05 kernel puts the codes together itself (no dequantized copy of the matrix)
-        if (W.kind == B200_K_Q6K && !q6_copy && T >= 32 && m->c.kernel_class != B200_CLASS_EXACT && !no_umma && ctx->umma_scratch &&
+        // Q5_K / Q6_K: the tcgen05 kernel puts the codes together itself (no dequantized copy of the matrix)
+        if ((W.kind == B200_K_Q6K || W.kind == B200_K_Q5K) && !q6_copy && T >= 32 && m->c.kernel_class != B200_CLASS_EXACT && !no_umma && ctx->umma_scratch &&
             q6k_umma_fits(ctx->sm_count, ctx->x16_slot_bytes, ctx->umma_scratch_bytes, W.rows, W.cols, T) && !(reinterpret_cast<uintptr_t>(W.p) & 15))
-            return launch_q6k_matmul_umma(ctx, (const uint8_t*)W.p, W.rows, W.cols, xq, T, dst, ldd);
+            return launch_kq_matmul_umma(ctx, W.kind, (const uint8_t*)W.p, W.rows, W.cols, xq, T, dst, ldd);
         if (W.f16 && m->kq_act && T >= 32 && m->c.kernel_class != B200_CLASS_EXACT && !no_umma && ctx->umma_scratch &&
             f16w_umma_supported(W.f16, W.rows, W.cols) && f16w_umma_scratch_bytes(T, W.cols) <= ctx->umma_scratch_bytes) {
             ST_TRY(launch_act_dequant(ctx, xq, T, W.cols, m->kq_act));
@@ -1104,13 +1104,13 @@ int b200_model_finalize(b200_model* m, b200_caps* out) {
             }
             ST_TRY(to_tiles(&m->head, MLR));
         }
-        // Q5_K / W8A8 tensors: fp16 copies for the tensor-core matmul from 32 rows on. Q6_K tensors need none: the tcgen05
+        // W8A8 tensors: fp16 copies for the tensor-core matmul from 32 rows on. Q5_K and Q6_K tensors need none: the tcgen05
         // kernel takes their blocks as they are (a copy is made only where the scratch cannot hold the matrix's partials)
         std::vector<DevMat*> kq;
         const size_t scratch_now = m->umma_bytes;
         auto wants_copy = [&](const DevMat* d, int rows_max) {
             if (!d->p || !is_lane_kind(d->kind)) return false;
-            if (d->kind != B200_K_Q6K || getenv("B200_Q6K_F16_COPY")) return true;
+            if ((d->kind != B200_K_Q6K && d->kind != B200_K_Q5K) || getenv("B200_Q6K_F16_COPY")) return true;
             return !q6k_umma_fits(ctx->sm_count, m->x16_slot_bytes, scratch_now, d->rows, d->cols, rows_max) || (reinterpret_cast<uintptr_t>(d->p) & 15);
         };
         for (int l = 0; l < c.n_layers; l++) {

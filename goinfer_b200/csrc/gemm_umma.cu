@@ -104,7 +104,9 @@ __device__ __forceinline__ float umma_silu(float x) { return __fdividef(x, __fad
 // FMT 4: Q4_K rows (144-byte super-blocks). FMT 6: Q6_K rows as the device keeps them, 208-byte bodies (ql[128], qh[64],
 // sixteen int8 sub-scales) with the super-blocks' d values in `dvals` ([N][nSB] halves): w = d * sc * (q - 32), the six-bit
 // q put together from a nibble and two upper bits; (q - 32) is exact in fp16 and takes the one rounding of the product with
-// fp16(d * sc). The rest of the kernel (activation ring, MMAs, epilogue) does not know the format.
+// fp16(d * sc). FMT 5: Q5_K rows as in the file (176-byte super-blocks: d, dmin, the 12 scale bytes of Q4_K, qh[32], qs[128]):
+// Q4_K's nibbles with a fifth bit from qh, the five-bit code placed in the mantissa of the half 32 + q.
+// The rest of the kernel (activation ring, MMAs, epilogue) does not know the format.
 template <int NT, bool SWIGLU, int FMT = 4>
 __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __grid_constant__ CUtensorMap wmap, int N, int nSB,
                                                                         const __half* __restrict__ X16, int T,
@@ -112,7 +114,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                                                                         int* __restrict__ err_flag, int8_t* __restrict__ sw_codes,
                                                                         float* __restrict__ sw_scales, __half* __restrict__ sw_x16,
                                                                         const uint8_t* __restrict__ w16, const unsigned short* __restrict__ dvals) {
-    constexpr int RAW = FMT == 6 ? 208 : kRawRow;   // raw bytes of one super-block of a weight row
+    constexpr int RAW = FMT == 6 ? 208 : (FMT == 5 ? 176 : kRawRow);   // raw bytes of one super-block of a weight row
     pdl_trigger();  // the next kernel's blocks may be placed as ours retire; they wait for our completion before they touch data
     extern __shared__ __align__(1024) uint8_t umma_smem[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], raw_full, raw_empty;
@@ -242,6 +244,77 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                 if (ok) ok = step6(it + 1, 1);
                 if (ok) ok = step6(it + 2, 2);
                 if (ok) ok = step6(it + 3, 3);
+            }
+        } else if constexpr (FMT == 5) {
+            uint4 hdr, uq[2], q[8];   // the row's current super-block: d, dmin, scale bytes; the fifth bits; the nibbles
+            const unsigned k_nib = opaque_u(0x01E001E0u), k_bit = opaque_u(0x02000200u), k_magic = opaque_u(0x50005000u);
+            auto step5 = [&](int it, int p) -> bool {  // p = it & 3, a literal at every call site
+                if (it > 1) {
+                    const bool w_ok = mbar_wait(smem_u32(&empty_bar[(it - 2) % kStages]), (unsigned)(((it - 2) / kStages) & 1), abort_v);
+                    if (!__all_sync(0xffffffffu, w_ok)) return false;
+                }
+                if (p == 0) {
+                    const int sb = it >> 2;
+                    const bool w_ok = mbar_wait(smem_u32(&raw_full), (unsigned)(sb & 1), abort_v);
+                    if (!__all_sync(0xffffffffu, w_ok)) return false;
+                    const uint4* rp = reinterpret_cast<const uint4*>(raw + (size_t)wr * RAW);
+                    hdr = rp[0];
+                    uq[0] = rp[1]; uq[1] = rp[2];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) q[i] = rp[3 + i];
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&raw_empty));
+                }
+                {   // sub-blocks 2p (low nibbles of code bytes 32p.., bit 2p of qh[l]) and 2p+1 (high nibbles, bit 2p+1)
+                    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
+                    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+                    uint8_t* rowp = bring + (size_t)(it & 1) * BSTAGE + b_off;
+                    const uint4 qa = q[2 * p], qb = q[2 * p + 1];
+                    const unsigned wq[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                    const unsigned uw[8] = {uq[0].x, uq[0].y, uq[0].z, uq[0].w, uq[1].x, uq[1].y, uq[1].z, uq[1].w};
+                    unsigned scs, ms;
+                    pair_scale_min(hdr, p, &scs, &ms);
+#pragma unroll
+                    for (int hf = 0; hf < 2; hf++) {
+                        if (NT == 1 && hf != hf1) continue;
+                        const int sc = (int)((scs >> (8 * hf)) & 0xffu), mn = (int)((ms >> (8 * hf)) & 0xffu);
+                        const __half dsh = __float2half_rn(d * (float)sc);
+                        const __half2 ds = __half2half2(dsh), c = __float2half2_rn(-(32.f * __half2float(dsh) + dmin * (float)mn));
+                        const int bit = 2 * p + hf;
+#pragma unroll
+                        for (int ch = 0; ch < 4; ch++) {
+                            uint4 o;
+                            unsigned* ov = &o.x;
+#pragma unroll
+                            for (int wi = 0; wi < 2; wi++) {
+                                const unsigned w = wq[2 * ch + wi], u = uw[2 * ch + wi];
+#pragma unroll
+                                for (int b1 = 0; b1 < 2; b1++) {   // bytes (0,2) then (1,3): the tile's order inside every four
+                                    const int nfrom = 8 * b1 + 4 * hf;   // the nibble's first bit in the 16-bit lane; it goes to bit 5
+                                    const unsigned nsh = nfrom <= 5 ? (w << (5 - nfrom)) : (w >> (nfrom - 5));
+                                    const int ufrom = 8 * b1 + bit;      // the fifth bit's place; it goes to bit 9
+                                    const unsigned us = ufrom <= 9 ? (u << (9 - ufrom)) : (u >> (ufrom - 9));
+                                    unsigned t = and_or_u(nsh, k_nib, k_magic);
+                                    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(us), "r"(k_bit), "r"(t));   // (us & k_bit) | t
+                                    const __half2 hv = __hfma2(*reinterpret_cast<__half2*>(&t), ds, c);
+                                    ov[2 * wi + b1] = *reinterpret_cast<const unsigned*>(&hv);
+                                }
+                            }
+                            *reinterpret_cast<uint4*>(rowp + (((unsigned)(4 * hf + ch) ^ sw) << 4)) = o;
+                        }
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&full_bar[it % kStages]));
+                return true;
+            };
+            for (int it = 0; it < n_it && ok; it += 4) {
+                ok = step5(it, 0);
+                if (ok) ok = step5(it + 1, 1);
+                if (ok) ok = step5(it + 2, 2);
+                if (ok) ok = step5(it + 3, 3);
             }
         } else {
         uint4 hdr, q[8];  // the current super-block: d, dmin, 12 scale bytes; 128 code bytes
@@ -691,8 +764,15 @@ bool q6k_umma_fits(int sm_count, size_t slot_bytes, size_t scratch_bytes, int N,
 }
 
 int launch_q6k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd) {
+    return launch_kq_matmul_umma(ctx, B200_K_Q6K, W, N, K, aq, T, dst, ldd);
+}
+
+// kind B200_K_Q5K (the file's 176-byte blocks) or B200_K_Q6K (208-byte bodies + d values)
+int launch_kq_matmul_umma(b200_ctx* ctx, int kind, const uint8_t* W, int N, int K, ActQ aq, int T, float* dst, int ldd) {
     ST_TRY(flush_pending_parts(ctx));  // the scratch is about to be reused
-    if (K % 256 || (reinterpret_cast<uintptr_t>(W) & 15)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q6_K needs K %% 256 == 0 and 16-byte aligned weights");
+    if (kind != B200_K_Q5K && kind != B200_K_Q6K) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the K-quant tcgen05 matmul takes Q5_K or Q6_K");
+    const int sb_bytes = kind == B200_K_Q6K ? 208 : 176;
+    if (K % 256 || (reinterpret_cast<uintptr_t>(W) & 15)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "Q5_K / Q6_K need K %% 256 == 0 and 16-byte aligned weights");
     if (!ctx->umma_scratch) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the tcgen05 matmul needs the fast class's scratch");
     const int nSB = K / 256, t_tiles = ceil_div(T, 256);
     const int max_splits = std::max(1, std::min(4, nSB / 2));
@@ -717,10 +797,12 @@ int launch_q6k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ a
     if (attr_once.first(ctx->device)) {
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<1, false, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, false, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<1, false, 5>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, false, 5>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     }
-    const CUtensorMap* wmap = q4k_weight_map(ctx, W, N, nSB, 128 * NT, 208);
+    const CUtensorMap* wmap = q4k_weight_map(ctx, W, N, nSB, 128 * NT, sb_bytes);
     if (!wmap) return B200_CUDA_ERROR;
-    const unsigned short* dvals = reinterpret_cast<const unsigned short*>(W + (size_t)N * nSB * 208);
+    const unsigned short* dvals = kind == B200_K_Q6K ? reinterpret_cast<const unsigned short*>(W + (size_t)N * nSB * 208) : nullptr;
     dim3 grid(n_tiles, t_tiles, splits);
     float* out = splits > 1 ? part : dst;
     const int out_ld = splits > 1 ? N : ldd;
@@ -731,8 +813,10 @@ int launch_q6k_matmul_umma(b200_ctx* ctx, const uint8_t* W, int N, int K, ActQ a
         float* const no_scales = nullptr;
         __half* const no_x16 = nullptr;
         const uint8_t* const no_tiles = nullptr;
-        if (NT == 2) launch_pdl(q4k_umma_gemm_kernel<2, false, 6>, grid, dim3(kUmmaThreads), (size_t)smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, ctx->err_flag, no_codes, no_scales, no_x16, no_tiles, dvals);
-        else launch_pdl(q4k_umma_gemm_kernel<1, false, 6>, grid, dim3(kUmmaThreads), (size_t)smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, ctx->err_flag, no_codes, no_scales, no_x16, no_tiles, dvals);
+#define KQ_LAUNCH(NTV, FMTV) launch_pdl(q4k_umma_gemm_kernel<NTV, false, FMTV>, grid, dim3(kUmmaThreads), (size_t)smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, ctx->err_flag, no_codes, no_scales, no_x16, no_tiles, dvals)
+        if (kind == B200_K_Q6K) { if (NT == 2) KQ_LAUNCH(2, 6); else KQ_LAUNCH(1, 6); }
+        else { if (NT == 2) KQ_LAUNCH(2, 5); else KQ_LAUNCH(1, 5); }
+#undef KQ_LAUNCH
     }
     LAUNCH_CHECK(ctx);
     if (splits > 1) {

@@ -202,18 +202,22 @@ int b200_op_kq_matmul(b200_ctx* ctx, int kind, const uint8_t* w, const float* a,
 // Test hook: the Q6_K matmul on the tcgen05 kernel that puts the codes together itself (what a fast-class model runs from
 // 32 rows), at any M, on the file's 210-byte blocks.
 int b200_debug_q6k_matmul_umma(b200_ctx* ctx, const uint8_t* w, const float* a, int M, int K, int N, float* dst) {
-    if (K % 256 || M < 1 || N < 1) B200_FAIL(ctx, B200_BAD_ARGUMENT, "a Q6_K matrix with K %% 256 == 0");
+    return b200_debug_kq_matmul_umma(ctx, B200_K_Q6K, w, a, M, K, N, dst);
+}
+
+int b200_debug_kq_matmul_umma(b200_ctx* ctx, int kind, const uint8_t* w, const float* a, int M, int K, int N, float* dst) {
+    if (K % 256 || M < 1 || N < 1 || (kind != B200_K_Q5K && kind != B200_K_Q6K)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "a Q5_K or Q6_K matrix with K %% 256 == 0");
     Tmp t;
-    const size_t nb = (size_t)N * K / 256, wb = nb * 210;
+    const size_t nb = (size_t)N * K / 256, wb = nb * (kind == B200_K_Q6K ? 210 : 176);
     uint8_t *dw, *dp; float *da, *dd; ActQ aq;
     TMP_GET(ctx, t, dw, wb); TMP_GET(ctx, t, dp, wb); TMP_GET(ctx, t, da, (size_t)M * K); TMP_GET(ctx, t, dd, (size_t)M * N);
     TMP_GET(ctx, t, aq.codes, (size_t)M * K); TMP_GET(ctx, t, aq.scales, (size_t)M * 2 * (K / 32));
     H2D(ctx, dw, w, wb); H2D(ctx, da, a, (size_t)M * K * 4);
-    ST_TRY(launch_q6k_repack(ctx, dw, nb, dp));
+    if (kind == B200_K_Q6K) ST_TRY(launch_q6k_repack(ctx, dw, nb, dp));
     ST_TRY(launch_quant_g32(ctx, da, M, K, aq));
     UmmaScratch us(ctx);
     ST_TRY(us.ensure(t, M, K, N));
-    ST_TRY(launch_q6k_matmul_umma(ctx, dp, N, K, aq, M, dd, N));
+    ST_TRY(launch_kq_matmul_umma(ctx, kind, kind == B200_K_Q6K ? dp : dw, N, K, aq, M, dd, N));
     D2H(ctx, dst, dd, (size_t)M * N * 4);
     SYNC(ctx);
     return us.check();

@@ -70,6 +70,8 @@ int b200_debug_wait_fault(b200_ctx* ctx, int polls, int withhold_chunk);
 /* Test hook: dst[M][N] = a . W^T for W Q6_K given as the file's 210-byte blocks, on the tcgen05 kernel that assembles and
  * scales the six-bit codes itself (what a fast-class model runs for Q6_K tensors from 32 rows), at any M. */
 int b200_debug_q6k_matmul_umma(b200_ctx* ctx, const uint8_t* w_host, const float* a_host, int M, int K, int N, float* dst_host);
+/* The same for kind B200_K_Q5K (176-byte blocks) or B200_K_Q6K. */
+int b200_debug_kq_matmul_umma(b200_ctx* ctx, int kind, const uint8_t* w_host, const float* a_host, int M, int K, int N, float* dst_host);
 
 /* 1 when the model's tensor-parallel layers sum their partial products with the library's own kernel over peer memory
  * (the ranks share a host and could map one another's buffers), 0 when they call NCCL's all-reduce. */

@@ -189,10 +189,11 @@ def test_q5k_q6k_matmul_within_the_reference_bar(ops, oracle_lib, kind):
     assert worst < 1e-5
 
 
+@pytest.mark.parametrize("kind", [abi.K_Q6K, abi.K_Q5K])
 @pytest.mark.parametrize("M", [1, 32, 100, 256, 300])
-def test_q6k_matmul_on_the_tcgen05_kernel(ops, oracle_lib, M):
-    """Q6_K weights on the tcgen05 kernel whose producers put the six-bit codes together and scale them in registers (what a
-    fast-class model runs for Q6_K tensors from 32 rows, with no dequantized copy of the matrix). fp16 operands (the
+def test_q6k_matmul_on_the_tcgen05_kernel(ops, oracle_lib, M, kind):
+    """Q6_K (and Q5_K) weights on the tcgen05 kernel whose producers put the codes together and scale them in registers (what
+    a fast-class model runs for these tensors from 32 rows, with no dequantized copy of the matrix). fp16 operands (the
     sub-scale d*sc and the activation code*scale are rounded to fp16, q - 32 is exact), fp32 accumulation in tensor memory:
     held to the Q4_K tcgen05 matmul's tolerance against the f64 product of the dequantized rows, on ragged row counts
     (rows past N read as zero blocks), one, two and many super-blocks, with and without a K split; and every planted
@@ -202,20 +203,20 @@ def test_q6k_matmul_on_the_tcgen05_kernel(ops, oracle_lib, M):
     rng = np.random.default_rng(600 + M)
     for N, nSB in ((8 * 3 + 5, 1), (300, 2), (129, 6), (1000, 12), (4096, 8)):
         K = 256 * nSB
-        raw = random_blocks(rng, abi.K_Q6K, N, K)
+        raw = random_blocks(rng, kind, N, K)
         a = rng.normal(0, 1, (M, K)).astype(np.float32)
         a[:, rng.integers(0, K, 3)] *= 30.0    # outliers
         got = np.zeros((M, N), np.float32)
-        st = ops.lib.b200_debug_q6k_matmul_umma(ops.ctx, raw.ctypes.data_as(C.POINTER(C.c_uint8)), a.ctypes.data_as(C.POINTER(C.c_float)),
+        st = ops.lib.b200_debug_kq_matmul_umma(ops.ctx, kind, raw.ctypes.data_as(C.POINTER(C.c_uint8)), a.ctypes.data_as(C.POINTER(C.c_float)),
                                                 M, K, N, got.ctypes.data_as(C.POINTER(C.c_float)))
         assert st == abi.OK, ops.lib.b200_last_error(ops.ctx)
-        want, bar = oracle_lib.op_kq_matmul_f64(abi.K_Q6K, raw, a, N)
+        want, bar = oracle_lib.op_kq_matmul_f64(kind, raw, a, N)
         scale = np.abs(want).max()
         assert np.all(np.isfinite(got)) and np.abs(got - want).max() <= 4e-3 * scale, (N, nSB, np.abs(got - want).max() / scale)
         rel = np.linalg.norm(got - want) / np.linalg.norm(want)
         assert rel <= 2.5e-3, (N, nSB, rel)
-        for plant in (2, 3) + ((4,) if nSB > 1 else ()):
-            bad, _ = oracle_lib.op_kq_matmul_f64(abi.K_Q6K, raw, a, N, plant)
+        for plant in ((2, 3) if kind == abi.K_Q6K else (1,)) + ((4,) if nSB > 1 else ()):
+            bad, _ = oracle_lib.op_kq_matmul_f64(kind, raw, a, N, plant)
             assert np.linalg.norm(got - bad) / np.linalg.norm(want) > 0.05, (N, nSB, plant)
 
 
