@@ -8,6 +8,10 @@ The hashes here are computed over the reference's canonical byte encoding (key.g
 
 The device side of a hit is `Resident.CopyKV(dst, src, rows)`: whole device blocks are shared by reference, so a hit
 costs no KV bytes. This module never touches the device; the serve driver (serve.py `drive`) connects the two.
+
+Standing: a mirror for this repository's Python serve driver and its tests, not part of the library. A Go host keeps its
+own kvmgr and only calls `b200_copy_kv`; the parts of the key this backend cannot exercise (image spans, adapter ids,
+windowed layers) are carried only so that hashes and the reference's own test tables agree.
 """
 from __future__ import annotations
 

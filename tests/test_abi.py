@@ -74,3 +74,12 @@ def test_every_programmatically_launched_kernel_waits():
         end = all_text.find("__global__", m.end())
         body = all_text[m.end():end if end > 0 else len(all_text)]
         assert "pdl_wait()" in body and "pdl_trigger()" in body, name
+        # ... and before the first dependent access: no pointer parameter is subscripted ahead of the wait. (Weights, which no
+        # kernel writes, may be fetched earlier; the kernels that do so go through copy helpers or casts, not subscripts.)
+        sig = body[:body.index(")")]
+        params = re.findall(r"\*\s*(?:__restrict__\s+)?([A-Za-z_][A-Za-z_0-9]*)\s*(?:,|$)", sig)
+        kernel_body = body[body.index("{"):]
+        before = kernel_body[:kernel_body.index("pdl_wait()")]
+        before = re.sub(r"//[^\n]*", "", before)
+        for prm in params:
+            assert not re.search(r"\b" + prm + r"\s*\[", before), (name, prm)
