@@ -351,7 +351,9 @@ int launch_tp_reduce_norm_quant(b200_ctx*, TpFused*, int T, const float* norm_w,
 // phases: 1 push, 2 reduce, 4 rearm + wait for every row's codes (7 = all; split only by the one-GPU emulation).
 int tp_fused_arm(b200_ctx*, TpFused*);  // fills the flagless form's buffers with the not-arrived values
 // given: this rank's product as K-split partials (else the ones the matmul left pending for the block's product, if any).
-int launch_tp_reduce_norm_quant_ll(b200_ctx*, TpFused*, int T, const float* norm_w, float eps, ActQ* out, int phases = 7, const Parts* given = nullptr);
+// x16: also lay the rows out as the fp16 tiles the matmul after this kernel reads (local rows 0..T-1 of that slot).
+int launch_tp_reduce_norm_quant_ll(b200_ctx*, TpFused*, int T, const float* norm_w, float eps, ActQ* out, int phases = 7, const Parts* given = nullptr,
+                                   __half* x16 = nullptr);
 int tp_all_gather_columns(b200_ctx*, const float* local, int rows, int w, float* gathered, float* full);
 
 // attention_prefill.cu: causal attention for a run of rows of one slot at consecutive positions pos0.. (fast class)

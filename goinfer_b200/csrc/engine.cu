@@ -595,18 +595,20 @@ int run_layers(b200_model* m, int T, int max_keys) {
     m->aq_h = m->aq_h_local;
     // tensor parallel on one host: sums the ranks' partial rows in m->att, adds them to the residual rows, norms with w and
     // quantizes; m->aq_h then points at the activation buffers every rank's kernel filled
-    auto cross_rank_norm = [&](const float* w) -> int {
-        if (m->tpf.use_ll) return launch_tp_reduce_norm_quant_ll(ctx, &m->tpf, T, w, c.rms_eps, &m->aq_h);
+    auto cross_rank_norm = [&](const float* w, __half* x16_out) -> int {
+        if (m->tpf.use_ll) return launch_tp_reduce_norm_quant_ll(ctx, &m->tpf, T, w, c.rms_eps, &m->aq_h, 7, nullptr, x16_out);
         ST_TRY(launch_tp_reduce_norm_quant(ctx, &m->tpf, T, w, c.rms_eps, 0));
         m->aq_h = ActQ{m->tpf.codes(), m->tpf.scales()};
         return B200_OK;
     };
     bool normed_ready = false;     // tensor parallel: the layer's attention norm was applied by the kernel that reduced across the ranks
+    __half* x16_carry = nullptr;   // ... and these are the fp16 tiles it laid out for the layer's q|k|v
     for (int l = 0; l < c.n_layers; l++) {
         LayerW& L = m->layers[l];
         bool reduced = false;  // the down products were already added to the residual rows
         const bool q_in = is_kquant(L.qkv.kind);
-        __half* x16 = (q_in && !normed_ready) ? x16_for(L.qkv) : nullptr;
+        __half* x16 = (q_in && !normed_ready) ? x16_for(L.qkv) : x16_carry;   // (or the tiles the cross-rank kernel laid out after the last layer)
+        x16_carry = nullptr;
         if (!normed_ready) m->aq_h = m->aq_h_local;
         if (!normed_ready)  // (tensor parallel: the kernel that summed the last layer's down products has normed and quantized already)
             ST_TRY(launch_add_rmsnorm_quant(ctx, m->h, delta, L.attn_norm, T, H, c.rms_eps, q_in ? nullptr : m->normed,
@@ -671,7 +673,8 @@ int run_layers(b200_model* m, int T, int max_keys) {
             const bool g_q = is_kquant(L.gu.kind), d_q = is_kquant(L.down.kind);
             __half* x16g = nullptr;
             if (m->tpf.on && g_q) {
-                ST_TRY(cross_rank_norm(L.ffn_norm));
+                x16g = m->tpf.use_ll ? x16_for(L.gu) : nullptr;   // laid out by the cross-rank kernel as the codes arrive
+                ST_TRY(cross_rank_norm(L.ffn_norm, x16g));
             } else {
                 m->aq_h = m->aq_h_local;
                 const float* add = m->att;
@@ -708,7 +711,8 @@ int run_layers(b200_model* m, int T, int max_keys) {
             if (m->tpf.on) {
                 // the down products: summed, added and, when a quantized q|k|v follows, normed with the next layer's weight
                 if (l + 1 < c.n_layers && is_kquant(m->layers[l + 1].qkv.kind)) {
-                    ST_TRY(cross_rank_norm(m->layers[l + 1].attn_norm));
+                    x16_carry = m->tpf.use_ll ? x16_for(m->layers[l + 1].qkv) : nullptr;
+                    ST_TRY(cross_rank_norm(m->layers[l + 1].attn_norm, x16_carry));
                     normed_ready = true;
                 } else {
                     ST_TRY(launch_tp_reduce_norm_quant(ctx, &m->tpf, T, nullptr, c.rms_eps, 1));  // every rank gets the updated rows

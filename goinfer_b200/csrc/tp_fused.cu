@@ -23,6 +23,8 @@
 //
 // The arithmetic is the row kernels' (elementwise.cu): f64 sum of squares, y = (x*inv)*w, the quantizer of rowquant.cuh.
 #include <algorithm>
+#include <cstring>
+#include <vector>
 
 #include "common.cuh"
 #include "rowquant.cuh"
@@ -244,7 +246,8 @@ struct TpLLOffsets {
 __global__ void __launch_bounds__(1024) tp_ll_reduce_norm_quant_kernel(TpPeers peers, TpLLOffsets off, int rank, int t, int T, int H,
                                                                        const float* __restrict__ w, float eps, int phases, long long wait_ns,
                                                                        int* __restrict__ err_flag, long long* __restrict__ stage_ns,
-                                                                       const float* __restrict__ kparts, int n_kparts, size_t kpart_stride) {
+                                                                       const float* __restrict__ kparts, int n_kparts, size_t kpart_stride,
+                                                                       __half* __restrict__ x16) {
     __shared__ double red[32];
     const int rows_per = (T + t - 1) / t, nG = H >> 5, c = threadIdx.x, nW = blockDim.x >> 5;
     const int q4 = threadIdx.x & 3, g = c >> 2;
@@ -348,9 +351,35 @@ __global__ void __launch_bounds__(1024) tp_ll_reduce_norm_quant_kernel(TpPeers p
             reinterpret_cast<uint4*>(me + off.next_codes)[i] = make_uint4(kNoCodes, kNoCodes, kNoCodes, kNoCodes);
         for (size_t i = tid; i < n_scales16; i += nthr) reinterpret_cast<uint4*>(me + off.next_scales)[i] = make_uint4(kNoF32, kNoF32, kNoF32, kNoF32);
         if (stamp) stage_ns[3] = global_ns();
-        // ---- wait until every row's codes and scales, from every owner, are here ----
+        // ---- wait until every row's codes and scales, from every owner, are here; with x16 set, the thread that saw 16
+        // codes arrive also lays them out as the fp16 tiles (code * scale) the matmul after this kernel reads, so no
+        // conversion kernel runs between the two ----
         uint4 v;
-        for (size_t i = tid; i < n_codes16 && ok; i += nthr) ok = poll_v4(me + off.codes + i * 16, kNoCodes, wait_ns, &v);
+        for (size_t i = tid; i < n_codes16 && ok; i += nthr) {
+            ok = poll_v4(me + off.codes + i * 16, kNoCodes, wait_ns, &v);
+            if (x16 && ok) {
+                const int r = (int)(i / (size_t)(H >> 4)), k16 = (int)(i % (size_t)(H >> 4)) << 4;
+                const unsigned* scp = reinterpret_cast<const unsigned*>(me + off.scales) + (size_t)r * 2 * nG + (k16 >> 5);
+                unsigned sb = *reinterpret_cast<const volatile unsigned*>(scp);
+                if (sb == kNoF32) {   // the group's scale has not landed yet (bounded like every wait)
+                    const long long t0 = global_ns();
+                    while ((sb = *reinterpret_cast<const volatile unsigned*>(scp)) == kNoF32) {
+                        if (global_ns() - t0 > wait_ns) { ok = false; break; }
+                    }
+                }
+                if (ok) {
+                    const float sc = __uint_as_float(sb);
+                    const unsigned cw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int hh = 0; hh < 2; hh++) {
+                        float f[8];
+#pragma unroll
+                        for (int u = 0; u < 8; u++) f[u] = __fmul_rn((float)(int)(signed char)((cw[2 * hh + (u >> 2)] >> (8 * (u & 3))) & 0xffu), sc);
+                        x16_store8(x16, H, r, k16 + 8 * hh, f);
+                    }
+                }
+            }
+        }
         for (size_t i = tid; i < n_scales16 && ok; i += nthr) ok = poll_v4(me + off.scales + i * 16, kNoF32, wait_ns, &v);
     }
     if (!ok) atomicExch(err_flag, 1);
@@ -389,7 +418,8 @@ int tp_fused_arm(b200_ctx* ctx, TpFused* f) {
     return B200_OK;
 }
 
-int launch_tp_reduce_norm_quant_ll(b200_ctx* ctx, TpFused* f, int T, const float* norm_w, float eps, ActQ* out, int phases, const Parts* given) {
+int launch_tp_reduce_norm_quant_ll(b200_ctx* ctx, TpFused* f, int T, const float* norm_w, float eps, ActQ* out, int phases, const Parts* given,
+                                   __half* x16) {
     if (!f->base || T < 1 || T > f->max_rows || f->H % 256 || f->H > 8192 || f->t < 1 || f->t > kTpMaxRanks || !norm_w)
         B200_FAIL(ctx, B200_BAD_ARGUMENT, "tensor-parallel reduce: %d rows of %d (at most %d), %d ranks", T, f->H, f->max_rows, f->t);
     if (!ctx->err_flag) B200_FAIL(ctx, B200_BAD_ARGUMENT, "tensor-parallel reduce: the context has no error flag");
@@ -416,7 +446,7 @@ int launch_tp_reduce_norm_quant_ll(b200_ctx* ctx, TpFused* f, int T, const float
     {
         ProfScope ps(ctx, PROF_OTHER);  // counted with the collectives it replaces
         launch_pdl(tp_ll_reduce_norm_quant_kernel, dim3(grid), dim3(f->H / 8), 0, ctx->stream, peers, off, f->rank, f->t, T, f->H, norm_w, eps, phases,
-                   f->wait_ns, ctx->err_flag, f->phase_ns, pt.p, pt.n, pt.stride);
+                   f->wait_ns, ctx->err_flag, f->phase_ns, pt.p, pt.n, pt.stride, x16);
     }
     LAUNCH_CHECK(ctx);
     if (phases & 4) {
@@ -453,11 +483,13 @@ extern "C" int b200_debug_tp_reduce_emulated(b200_ctx* ctx, int t, int T, int H,
     struct Blocks {
         TpFused f[kTpMaxRanks];
         float* kp[kTpMaxRanks] = {};
+        __half* x16[kTpMaxRanks] = {};
         float* dw = nullptr;
         int* flag = nullptr;
         ~Blocks() {
             for (auto& x : f) cudaFree(x.base);
             for (auto* x : kp) cudaFree(x);
+            for (auto* x : x16) cudaFree(x);
             cudaFree(dw);
             cudaFree(flag);
         }
@@ -491,13 +523,31 @@ extern "C" int b200_debug_tp_reduce_emulated(b200_ctx* ctx, int t, int T, int H,
             bl.f[k].wait_ns = 50ll * 1000000ll;
             st = tp_fused_arm(ctx, &bl.f[k]);
         }
+        const size_t x_bytes = (size_t)ceil_div(T, 256) * 256 * H * 2;
+        for (int k = 0; k < t; k++) {
+            CUDA_TRY(ctx, cudaMalloc((void**)&bl.x16[k], 2 * x_bytes));   // what the kernel lays out | what the conversion kernel makes of the codes
+            CUDA_TRY(ctx, cudaMemsetAsync(bl.x16[k], 0, 2 * x_bytes, ctx->stream));
+        }
         for (int round = 0; round < 3 && st == B200_OK; round++) {
             for (int k = 0; k < t; k++) CUDA_TRY(ctx, cudaMemcpyAsync(bl.f[k].h(), h, (size_t)T * H * 4, cudaMemcpyHostToDevice, ctx->stream));
             for (int ph = 1; ph <= 4; ph *= 2)  // every rank's push, then every rank's reduce, then every rank's rearm + wait
                 for (int k = 0; k < t && st == B200_OK; k++) {
                     const Parts given{bl.kp[k], (size_t)T * H, n_kparts, bl.f[k].part(), T, H};
-                    st = launch_tp_reduce_norm_quant_ll(ctx, &bl.f[k], T, bl.dw, eps, &got[k], ph, &given);
+                    st = launch_tp_reduce_norm_quant_ll(ctx, &bl.f[k], T, bl.dw, eps, &got[k], ph, &given, bl.x16[k]);
                 }
+        }
+        // the fp16 tiles every rank laid out as the codes arrived are the conversion kernel's, bit for bit
+        std::vector<uint8_t> ha(x_bytes), hb(x_bytes);
+        for (int k = 0; k < t && st == B200_OK; k++) {
+            st = launch_act_to_f16(ctx, got[k], T, H, bl.x16[k] + x_bytes / 2);
+            if (st != B200_OK) break;
+            CUDA_TRY(ctx, cudaMemcpyAsync(ha.data(), bl.x16[k], x_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+            CUDA_TRY(ctx, cudaMemcpyAsync(hb.data(), bl.x16[k] + x_bytes / 2, x_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+            CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            if (memcmp(ha.data(), hb.data(), x_bytes)) {
+                ctx->err_flag = saved;
+                B200_FAIL(ctx, B200_CUDA_ERROR, "rank %d: the fp16 tiles laid out by the cross-rank kernel differ from the conversion kernel's", k);
+            }
         }
     } else {
         for (int ph = 1; ph <= 2; ph++)  // every rank's push, then every rank's reduce
