@@ -38,7 +38,14 @@
 
 namespace {
 
-constexpr int kStages = 3;   // A ring (and barriers); the B ring has 2 stages
+constexpr int kStages = 3;    // barrier slots: a chunk's full / empty barriers are slot it % kStages
+#ifndef B200_UMMA_A_STAGES
+#define B200_UMMA_A_STAGES 3
+#define B200_UMMA_B_STAGES 2
+#endif
+constexpr int kAStages = B200_UMMA_A_STAGES;   // the activation ring (bulk copies)
+constexpr int kBStages = B200_UMMA_B_STAGES;   // the dequantized weight ring (written by the producers)
+static_assert(kAStages <= kStages && kBStages <= kStages, "a ring cannot be deeper than the barrier slots");
 
 // 8 weights of one 16-byte chunk (nibbles of words w0, w1) -> fp16, two at a time in half2 arithmetic. A nibble q is
 // placed at mantissa bits [6,10) of the half 16.0 (0x4C00), which makes the half 16 + q with no int->float conversion, and
@@ -132,8 +139,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
     const int mt_count = (T - t0 > 128) ? 2 : 1;
     // the swizzle atoms want 1024-byte aligned tiles; the launch reserves 1024 spare bytes for this round-up
     uint8_t* smem = umma_smem + ((1024u - (smem_u32(umma_smem) & 1023u)) & 1023u);
-    uint8_t* bring = smem + (size_t)kStages * STAGE;  // 2 B stages of BSTAGE bytes
-    uint8_t* raw = bring + 2 * BSTAGE;                // the raw super-block (144 bytes) of each of the tile's 128*NT weight rows
+    uint8_t* bring = smem + (size_t)kAStages * STAGE;  // kBStages B stages of BSTAGE bytes
+    uint8_t* raw = bring + kBStages * BSTAGE;                // the raw super-block (144 bytes) of each of the tile's 128*NT weight rows
 
     if (tid == 0) {
         for (int s = 0; s < kStages; s++) {
@@ -175,8 +182,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
             const unsigned k_nib = opaque_u(0x00F000F0u), k_up = opaque_u(0x03000300u), k_magic = opaque_u(0x54005400u);   // registers: one LOP3 per use
             const __half2 k96 = __float2half2_rn(96.f);
             auto step6 = [&](int it, int p) -> bool {  // p = it & 3, a literal at every call site
-                if (it > 1) {
-                    const bool w_ok = mbar_wait(smem_u32(&empty_bar[(it - 2) % kStages]), (unsigned)(((it - 2) / kStages) & 1), abort_v);
+                if (it >= kBStages) {
+                    const bool w_ok = mbar_wait(smem_u32(&empty_bar[(it - kBStages) % kStages]), (unsigned)(((it - kBStages) / kStages) & 1), abort_v);
                     if (!__all_sync(0xffffffffu, w_ok)) return false;
                 }
                 if (p == 0) {
@@ -197,7 +204,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                     // low (p even) or high (p odd) nibbles of ql[64 half + l] and bit pair (p & 1) * 2 of qh[32 half + l], the
                     // other 32 those of ql[64 half + 32 + l] and the next bit pair; sub-scales 8 half + 4 (p & 1) + {0,1 | 2,3}
                     const int half = p >> 1, odd = p & 1;
-                    uint8_t* rowp = bring + (size_t)(it & 1) * BSTAGE + b_off;
+                    uint8_t* rowp = bring + (size_t)(it % kBStages) * BSTAGE + b_off;
                     const unsigned scw = (&q[12].x)[2 * half + odd];
 #pragma unroll
                     for (int hf = 0; hf < 2; hf++) {
@@ -249,8 +256,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
             uint4 hdr, uq[2], q[8];   // the row's current super-block: d, dmin, scale bytes; the fifth bits; the nibbles
             const unsigned k_nib = opaque_u(0x01E001E0u), k_bit = opaque_u(0x02000200u), k_magic = opaque_u(0x50005000u);
             auto step5 = [&](int it, int p) -> bool {  // p = it & 3, a literal at every call site
-                if (it > 1) {
-                    const bool w_ok = mbar_wait(smem_u32(&empty_bar[(it - 2) % kStages]), (unsigned)(((it - 2) / kStages) & 1), abort_v);
+                if (it >= kBStages) {
+                    const bool w_ok = mbar_wait(smem_u32(&empty_bar[(it - kBStages) % kStages]), (unsigned)(((it - kBStages) / kStages) & 1), abort_v);
                     if (!__all_sync(0xffffffffu, w_ok)) return false;
                 }
                 if (p == 0) {
@@ -269,7 +276,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                 {   // sub-blocks 2p (low nibbles of code bytes 32p.., bit 2p of qh[l]) and 2p+1 (high nibbles, bit 2p+1)
                     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
                     const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-                    uint8_t* rowp = bring + (size_t)(it & 1) * BSTAGE + b_off;
+                    uint8_t* rowp = bring + (size_t)(it % kBStages) * BSTAGE + b_off;
                     const uint4 qa = q[2 * p], qb = q[2 * p + 1];
                     const unsigned wq[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
                     const unsigned uw[8] = {uq[0].x, uq[0].y, uq[0].z, uq[0].w, uq[1].x, uq[1].y, uq[1].z, uq[1].w};
@@ -322,8 +329,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
 
         auto step = [&](int it, int p) -> bool {  // p = it & 3, a literal at every call site
             // B stage it%2 was last read by the MMAs of chunk it-2
-            if (it > 1) {  // the answer is made warp-uniform: the lanes meet in __syncwarp below
-                const bool w_ok = mbar_wait(smem_u32(&empty_bar[(it - 2) % kStages]), (unsigned)(((it - 2) / kStages) & 1), abort_v);
+            if (it >= kBStages) {  // the answer is made warp-uniform: the lanes meet in __syncwarp below
+                const bool w_ok = mbar_wait(smem_u32(&empty_bar[(it - kBStages) % kStages]), (unsigned)(((it - kBStages) / kStages) & 1), abort_v);
                 if (!__all_sync(0xffffffffu, w_ok)) return false;
             }
             if (p == 0) {  // take the row's next super-block out of `raw`, then hand `raw` back to the weight loader
@@ -342,7 +349,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
             {   // dequantize the chunk's sub-blocks 2p (low nibbles of code bytes 32p..32p+31) and 2p+1 (high nibbles)
                 const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
                 const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-                uint8_t* rowp = bring + (size_t)(it & 1) * BSTAGE + b_off;
+                uint8_t* rowp = bring + (size_t)(it % kBStages) * BSTAGE + b_off;
                 const uint4 qa = q[2 * p], qb = q[2 * p + 1];
                 const unsigned wq[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
                 unsigned scs, ms;
@@ -383,7 +390,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const unsigned a0 = smem_u32(smem + (size_t)(it % kStages) * STAGE), b0 = smem_u32(bring + (size_t)(it & 1) * BSTAGE);
+            const unsigned a0 = smem_u32(smem + (size_t)(it % kAStages) * STAGE), b0 = smem_u32(bring + (size_t)(it % kBStages) * BSTAGE);
             // one instruction spans all 128*NT weight rows (N = 128*NT): the token tile is fetched once for them
 #pragma unroll
             for (int mt = 0; mt < 2; mt++) {
@@ -407,18 +414,18 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
         const uint8_t* src = reinterpret_cast<const uint8_t*>(X16) + ((size_t)blockIdx.y * (size_t)(4 * nSB) + (size_t)(4 * sb0)) * STAGE;
         int issued = 0;
         for (int it = 0; it < n_it; it++) {
-            if (it >= kStages && !mbar_wait(smem_u32(&empty_bar[(it - kStages) % kStages]), (unsigned)(((it - kStages) / kStages) & 1), abort_v)) {
+            if (it >= kAStages && !mbar_wait(smem_u32(&empty_bar[(it - kAStages) % kStages]), (unsigned)(((it - kAStages) / kStages) & 1), abort_v)) {
                 abort_s = 1;
                 break;
             }
             const unsigned bar = smem_u32(&full_bar[it % kStages]);
             const unsigned a_bytes = (unsigned)(mt_count * kTileBytes);   // rows 0..127 of a 256-row tile are its first half
             mbar_arrive_expect_tx(bar, a_bytes);
-            bulk_g2s(smem_u32(smem + (size_t)(it % kStages) * STAGE), src + (size_t)it * STAGE, a_bytes, bar);
+            bulk_g2s(smem_u32(smem + (size_t)(it % kAStages) * STAGE), src + (size_t)it * STAGE, a_bytes, bar);
             issued = it + 1;
         }
         if (abort_s) {  // copies still in flight must land before the CTA may leave: bounded waits on their barriers
-            for (int it = max(0, issued - kStages); it < issued; it++) mbar_wait(smem_u32(&full_bar[it % kStages]), (unsigned)((it / kStages) & 1));
+            for (int it = max(0, issued - kAStages); it < issued; it++) mbar_wait(smem_u32(&full_bar[it % kStages]), (unsigned)((it / kStages) & 1));
         }
     } else if (warp == kProducerWarps + 2 && lane == 0) {
         // ---- the weight loader: one thread. From the row-major matrix, one tiled copy per super-block: 144 raw bytes of
@@ -707,7 +714,7 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
     }
     if (sw_x16 && sw_x16 == x16) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the epilogue's activation slot is the one this matmul reads");
     // A ring + B ring (sized for NT = 2) + one raw super-block per producer thread + round-up room
-    constexpr int smem = kStages * 2 * kTileBytes + 2 * 2 * kTileBytes + kProducers * kRawRow + 1024;
+    constexpr int smem = kAStages * 2 * kTileBytes + kBStages * 2 * kTileBytes + kProducers * kRawRow + 1024;
     static PerDeviceOnce attr_once;  // the attribute belongs to the device
     if (attr_once.first(ctx->device)) {
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -747,7 +754,7 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
 // Q6_K weights (208-byte bodies row by row, d values behind them: launch_q6k_repack) x the per-32 activations as fp16
 // tiles, on the same tcgen05 pipeline: the producers put the six-bit codes together and scale them in registers, so no
 // dequantized copy of the matrix exists. From 32 rows in the fast class.
-size_t q6k_umma_smem_bytes() { return (size_t)kStages * 2 * kTileBytes + 2 * 2 * kTileBytes + (size_t)kProducers * 208 + 1024; }
+size_t q6k_umma_smem_bytes() { return (size_t)kAStages * 2 * kTileBytes + (size_t)kBStages * 2 * kTileBytes + (size_t)kProducers * 208 + 1024; }
 
 // whether T rows of an [N][K] Q6_K matrix fit a scratch of `scratch_bytes` whose first 2 * slot_bytes hold activation slots
 bool q6k_umma_fits(int sm_count, size_t slot_bytes, size_t scratch_bytes, int N, int K, int T) {
