@@ -14,8 +14,9 @@ One JSON line on stdout (rank 0). `value` is tok/s with everything resident in H
 device; `e2e` is the same metric through the C ABI's step call with host buffers (embedding rows in, ids out, every step).
 Beside them, on one GPU: `parity` (the timed kernel class against the CPU oracle on a 256-sequence step of this shape),
 `exact_class` (the same workload in the exact kernel class), `c4` and `c1` (the routed-expert and the 1.1B-shape decode
-configurations), the Q4_K small-batch matmul sweep and the CPU baseline; on N >= 2 GPUs, after the replica legs, `tp_c5`:
-the 70B-class shape tensor-parallel over the N ranks.
+configurations), `c2_serve` (a small serve trace through the host-driven driver and the device batch), the Q4_K small-batch
+matmul sweep and the CPU baseline; on N >= 2 GPUs, after the replica legs, `tp_c5`: the 70B-class shape tensor-parallel
+over the N ranks.
 """
 import argparse
 import ctypes as C
@@ -363,6 +364,17 @@ def run_gpu(args):
         extra["exact_class"] = exact_class_leg(local, stream)
         extra["c4"] = workloads.decode("c4-moe", 128, 256, 4096, 3, steps=4, warmup=2, device=local)
         extra["c1"] = workloads.decode("c1-1.1b", 64, 32, 1280, 1, steps=8, warmup=3, device=local)
+        # configuration 2 in small: a serve trace (all sessions at t=0, 64 admitted at a time) through the host-driven driver
+        # (a ragged step packed per step, prefill chunks riding the decode runs) and through the device batch (seats,
+        # admission and retirement on the device, 8 steps a run)
+        from goinfer_b200.serve import run_poisson
+        keep = ("sessions", "makespan_s", "output_tokens", "output_tok_s", "total_tok_s", "steps", "runs", "mean_step_ms", "mean_run_ms",
+                "ttft_ms", "inter_token_ms", "driver")
+        extra["c2_serve"] = {}
+        for name, db in (("host_driven", 0), ("device_batch", 8)):
+            res = run_poisson("c1-1.1b", 128, 40.0, 64, 1, 32, 1024, 16, 128, chunk=512, device=local, time_scale=0.0, device_batch=db)
+            extra["c2_serve"][name] = {k: res[k] for k in keep if k in res}
+        extra["c2_serve"]["workload"] = "c1-1.1b shape: 128 sessions at t=0, prompts U[32,1024], outputs U[16,128], <= 64 admitted, greedy"
     if world > 1 and not args.no_extra:
         # the 70B-class shape split over these same ranks (its own communicator; the largest batch whose KV fits)
         barrier()
