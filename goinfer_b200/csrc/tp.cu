@@ -8,7 +8,9 @@
 // host process already loaded, e.g. PyTorch's, is the one found), so a single-GPU host needs no NCCL at all.
 #include <dlfcn.h>
 
+#include <chrono>
 #include <mutex>
+#include <thread>
 #include <vector>
 
 #include "common.cuh"
@@ -181,15 +183,28 @@ void tp_fused_teardown(b200_ctx* ctx, TpFused* f) {
     cudaStreamSynchronize(ctx->stream);
     for (int k = 0; k < f->t; k++)
         if (k != f->rank && f->peer[k]) cudaIpcCloseMemHandle(f->peer[k]);
+    bool peers_done = true;
     if (f->t > 1 && ctx->tp_comm) {  // every rank comes here (the ranks agreed on the outcome of the setup)
         NcclApi* api = nccl_api();
         float* d = nullptr;
         if (cudaMalloc((void**)&d, 4) == cudaSuccess) {
             cudaMemsetAsync(d, 0, 4, ctx->stream);
             api->all_reduce(d, d, 1, kNcclFloat32, kNcclSum, ctx->tp_comm, ctx->stream);
-            cudaStreamSynchronize(ctx->stream);
-            cudaFree(d);
+            // a rank that is gone never joins: the wait is bounded, and a block whose peers may still have it mapped is
+            // left to the process's exit rather than freed under them
+            const auto t0 = std::chrono::steady_clock::now();
+            cudaError_t q;
+            while ((q = cudaStreamQuery(ctx->stream)) == cudaErrorNotReady) {
+                if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(10)) { peers_done = false; break; }
+                std::this_thread::sleep_for(std::chrono::milliseconds(1));
+            }
+            if (q != cudaSuccess && q != cudaErrorNotReady) cudaGetLastError();
+            if (peers_done) cudaFree(d);
         }
+    }
+    if (!peers_done) {
+        *f = TpFused{};
+        return;
     }
     if (f->base) cudaFree(f->base);
     *f = TpFused{};
