@@ -691,6 +691,31 @@ __global__ void __launch_bounds__(256) dense_matmul_f64_kernel(const WT* __restr
     if (lane == 0) dst[(size_t)t * ldd + n] = (float)s;
 }
 
+// The same sums for four tokens a warp (f32 weights: the router): a weight is loaded once for the four, and every
+// output keeps the kernel above's order of additions (lane-strided partial sums in f64, then the xor fold), hence its bits.
+__global__ void __launch_bounds__(256) dense_matmul_f64_tok4_kernel(const float* __restrict__ W, int N, int K, const float* __restrict__ x, int T,
+                                                                    float* __restrict__ dst, int ldd) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), t0 = blockIdx.y * 4;
+    if (n >= N) return;
+    const float* w = W + (size_t)n * K;
+    const float* xr[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) xr[i] = x + (size_t)min(t0 + i, T - 1) * K;
+    double s[4] = {0, 0, 0, 0};
+    for (int k = lane; k < K; k += 32) {
+        const double wv = (double)w[k];
+#pragma unroll
+        for (int i = 0; i < 4; i++) s[i] += (double)xr[i][k] * wv;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s[i] += __shfl_xor_sync(0xffffffffu, s[i], o);
+        if (lane == 0 && t0 + i < T) dst[(size_t)(t0 + i) * ldd + n] = (float)s[i];
+    }
+}
+
 __global__ void __launch_bounds__(256) dense_matmul_f64_grouped_kernel(const float* const* __restrict__ Wptrs, int N, int K,
                                                                        const float* __restrict__ x,
                                                                        const int32_t* __restrict__ offs,
@@ -917,6 +942,11 @@ int launch_f16w_matmul(b200_ctx* ctx, const __half* W, int N, int K, const float
 }
 
 int launch_f32w_matmul(b200_ctx* ctx, const float* W, int N, int K, const float* x, int T, float* dst, int ldd) {
+    if (T >= 4) {
+        dense_matmul_f64_tok4_kernel<<<dim3(ceil_div(N, 8), ceil_div(T, 4)), 256, 0, ctx->stream>>>(W, N, K, x, T, dst, ldd);
+        LAUNCH_CHECK(ctx);
+        return B200_OK;
+    }
     dim3 grid(ceil_div(N, 8), T);
     dense_matmul_f64_kernel<float><<<grid, 256, 0, ctx->stream>>>(W, N, K, x, dst, ldd);
     LAUNCH_CHECK(ctx);

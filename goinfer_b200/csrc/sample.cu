@@ -416,33 +416,44 @@ __global__ void __launch_bounds__(32) route_kernel(const float* __restrict__ log
             if (idx[(size_t)r * k + j] >= 0) wts[(size_t)r * k + j] = __fdiv_rn(wts[(size_t)r * k + j], wsum);
 }
 
-// One block; thread e owns expert e. offs[nE+1]; rows_tok[s] = token row of sorted slot s; slot_of[a] = sorted
-// slot of assignment a = row*k + rank (-1 when the rank is empty).
-__global__ void group_experts_kernel(const int32_t* __restrict__ idx, int n_assign, int k, int nE, int32_t* __restrict__ offs,
-                                     int32_t* __restrict__ rows_tok, int32_t* __restrict__ slot_of, int n_staged) {
-    extern __shared__ int s_cnt[];     // nE counts, then the first n_staged assignments (all of them when they fit)
+// One block; a warp owns an expert at a time (expert w, w + warps, ...) and walks the assignments 32 at a time with a
+// ballot, so an expert's rows keep the order of their assignments. offs[nE+1]; rows_tok[s] = token row of sorted slot s;
+// slot_of[a] = sorted slot of assignment a = row*k + rank (-1 when the rank is empty).
+__global__ void __launch_bounds__(1024) group_experts_kernel(const int32_t* __restrict__ idx, int n_assign, int k, int nE, int32_t* __restrict__ offs,
+                                                             int32_t* __restrict__ rows_tok, int32_t* __restrict__ slot_of, int n_staged) {
+    extern __shared__ int s_cnt[];     // nE counts (then offsets), then the first n_staged assignments (all of them when they fit)
     int* s_idx = s_cnt + nE;
-    const int e = threadIdx.x;
-    for (int a = e; a < n_staged; a += blockDim.x) s_idx[a] = idx[a];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+    for (int a = tid; a < n_staged; a += blockDim.x) s_idx[a] = idx[a];
     __syncthreads();
-    auto at = [&](int a) { return a < n_staged ? s_idx[a] : idx[a]; };
-    int c = 0;
-    if (e < nE)
-        for (int a = 0; a < n_assign; a++) c += at(a) == e;
-    if (e < nE) s_cnt[e] = c;
+    auto at = [&](int a) { return a < n_assign ? (a < n_staged ? s_idx[a] : idx[a]) : -2; };
+    for (int e = warp; e < nE; e += n_warps) {
+        int c = 0;
+        for (int base = 0; base < n_assign; base += 32) c += __popc(__ballot_sync(0xffffffffu, at(base + lane) == e));
+        if (lane == 0) s_cnt[e] = c;
+    }
     __syncthreads();
-    if (e == 0) {
+    if (tid == 0) {
         int run = 0;
-        for (int i = 0; i < nE; i++) { offs[i] = run; run += s_cnt[i]; }
+        for (int i = 0; i < nE; i++) { const int c = s_cnt[i]; offs[i] = run; s_cnt[i] = run; run += c; }
         offs[nE] = run;
     }
     __syncthreads();
-    if (e < nE) {
-        int s = offs[e];
-        for (int a = 0; a < n_assign; a++)
-            if (at(a) == e) { rows_tok[s] = a / k; slot_of[a] = s; s++; }
+    for (int e = warp; e < nE; e += n_warps) {
+        int s = s_cnt[e];
+        for (int base = 0; base < n_assign; base += 32) {
+            const int a = base + lane;
+            const bool mine = at(a) == e;
+            const unsigned m = __ballot_sync(0xffffffffu, mine);
+            if (mine) {
+                const int slot = s + __popc(m & ((1u << lane) - 1u));
+                rows_tok[slot] = a / k;
+                slot_of[a] = slot;
+            }
+            s += __popc(m);
+        }
     }
-    for (int a = e; a < n_assign; a += blockDim.x)
+    for (int a = tid; a < n_assign; a += blockDim.x)
         if (at(a) < 0) slot_of[a] = -1;
 }
 
@@ -484,7 +495,7 @@ int launch_group_experts(b200_ctx* ctx, const int32_t* idx, int T, int k, int nE
     // rows holds rows_tok[T*k] followed by slot_of[T*k]
     // the assignments are scanned once per expert: from shared memory as far as they fit (40 KB), the rest from global
     const int n_staged = std::min(T * k, 10240);
-    group_experts_kernel<<<1, max(32, ((nE + 31) / 32) * 32), (nE + n_staged) * sizeof(int), ctx->stream>>>(
+    group_experts_kernel<<<1, 1024, (nE + n_staged) * sizeof(int), ctx->stream>>>(
         idx, T * k, k, nE, offs, rows, rows + (size_t)T * k, n_staged);
     LAUNCH_CHECK(ctx);
     return B200_OK;
