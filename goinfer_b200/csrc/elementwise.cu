@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float* __restri
 template <bool F64>
 __global__ void __launch_bounds__(256) swiglu_quant_vec_kernel(const float* __restrict__ gate_up, int F, int ld, float* __restrict__ mid,
                                                                int8_t* __restrict__ codes, float* __restrict__ scales, int il,
-                                                               __half* __restrict__ x16) {
+                                                               __half* __restrict__ x16, int n_parts, size_t part_stride) {
     pdl_trigger();
     pdl_wait();
     const int r = blockIdx.y, nG = F >> 5, nC = F >> 3;
@@ -292,7 +292,18 @@ __global__ void __launch_bounds__(256) swiglu_quant_vec_kernel(const float* __re
         const float* gp = gate_up + (size_t)r * ld + (il ? (size_t)(f >> 7) * 256 + (f & 127) : (size_t)f);
         const float4 g0 = *reinterpret_cast<const float4*>(gp), g1 = *reinterpret_cast<const float4*>(gp + 4);
         const float4 u0 = *reinterpret_cast<const float4*>(gp + up_off), u1 = *reinterpret_cast<const float4*>(gp + up_off + 4);
-        const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+        float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+        for (int k = 1; k < n_parts; k++) {  // gate_up is the first of the matmul's K-split partials: added in their order
+            const float* pp = gp + (size_t)k * part_stride;
+            const float4 a0 = *reinterpret_cast<const float4*>(pp), a1 = *reinterpret_cast<const float4*>(pp + 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(pp + up_off), b1 = *reinterpret_cast<const float4*>(pp + up_off + 4);
+            const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                gv[u] = __fadd_rn(gv[u], av[u]);
+                uv[u] = __fadd_rn(uv[u], bv[u]);
+            }
+        }
 #pragma unroll
         for (int u = 0; u < 8; u++) y[u] = __fmul_rn(F64 ? silu_f64(gv[u]) : silu_f32(gv[u]), uv[u]);
         if (mid) {
@@ -390,9 +401,10 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvstore_kernel(
     }
 }
 
-// The same for head_dim 128 with two heads per warp and sixteen per block (grid.y walks the heads): a lane keeps four
-// consecutive values of a head, the loads of both heads (and of every K-split partial) are in flight while the block's
+// The same for head_dim 128 or 64 with two heads per warp and sixteen per block (grid.y walks the heads): a lane keeps
+// HD/32 consecutive values of a head, the loads of both heads (and of every K-split partial) are in flight while the block's
 // cos/sin table is computed, and the rotation partner comes by shuffle. Same arithmetic, expression by expression.
+template <int HD>
 __global__ void __launch_bounds__(256) qknorm_rope_kvstore_vec_kernel(
     float* __restrict__ qkv, int ld, int nH, int nKV, int half, const double* __restrict__ inv_freq,
     const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, const int32_t* __restrict__ row_slot,
@@ -401,27 +413,34 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvstore_vec_kernel(
     size_t part_stride) {
     pdl_trigger();
     pdl_wait();
-    constexpr int hd = 128;
+    constexpr int hd = HD, V = HD / 32;   // values a lane
     __shared__ double cs[2 * 64];  // [half] cos, [half] sin
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_heads = nH + 2 * nKV;
     const int pos = row_pos[r], slot = row_slot[r];
-    float x[2][4];
+    float x[2][V];
     const float* base = n_parts ? parts : qkv;
     const int np = n_parts ? n_parts : 1;
+    auto load = [&](const float* p, float (&o)[V]) {
+        if constexpr (V == 4) {
+            const float4 a = *reinterpret_cast<const float4*>(p);
+            o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
+        } else {
+            const float2 a = *reinterpret_cast<const float2*>(p);
+            o[0] = a.x; o[1] = a.y;
+        }
+    };
 #pragma unroll
     for (int u = 0; u < 2; u++) {
         const int hh = blockIdx.y * 16 + 2 * warp + u;
-        x[u][0] = x[u][1] = x[u][2] = x[u][3] = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; i++) x[u][i] = 0.f;
         if (hh < n_heads) {
-            const size_t off = (size_t)r * ld + (size_t)hh * hd + 4 * lane;
+            const size_t off = (size_t)r * ld + (size_t)hh * hd + V * lane;
             for (int k = 0; k < np; k++) {
-                const float4 a = *reinterpret_cast<const float4*>(base + (size_t)k * part_stride + off);
-                if (k == 0) {
-                    x[u][0] = a.x; x[u][1] = a.y; x[u][2] = a.z; x[u][3] = a.w;
-                } else {
-                    x[u][0] = __fadd_rn(x[u][0], a.x); x[u][1] = __fadd_rn(x[u][1], a.y);
-                    x[u][2] = __fadd_rn(x[u][2], a.z); x[u][3] = __fadd_rn(x[u][3], a.w);
-                }
+                float a[V];
+                load(base + (size_t)k * part_stride + off, a);
+#pragma unroll
+                for (int i = 0; i < V; i++) x[u][i] = k == 0 ? a[i] : __fadd_rn(x[u][i], a[i]);
             }
         }
     }
@@ -435,29 +454,32 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvstore_vec_kernel(
     __syncthreads();
     const int blk = table[(size_t)slot * max_blocks + pos / block_rows];
     const int rib = pos % block_rows;
-    const int e0 = 4 * lane;                       // this lane's first element
+    const int e0 = V * lane;                       // this lane's first element
     const bool first = e0 < half, second = !first && e0 < 2 * half;
-    const int partner = first ? lane + half / 4 : lane - half / 4;
+    const int partner = first ? lane + half / V : lane - half / V;
 #pragma unroll
     for (int u = 0; u < 2; u++) {
         const int hh = blockIdx.y * 16 + 2 * warp + u;
         if (hh >= n_heads) break;  // uniform over the warp
         const bool is_q = hh < nH, is_k = !is_q && hh < nH + nKV;
         const float* nw = is_q ? q_norm : (is_k ? k_norm : nullptr);
-        float v[4] = {x[u][0], x[u][1], x[u][2], x[u][3]};
+        float v[V];
+#pragma unroll
+        for (int i = 0; i < V; i++) v[i] = x[u][i];
         if (nw) {
             double ss = 0;
 #pragma unroll
-            for (int i = 0; i < 4; i++) ss += (double)v[i] * (double)v[i];
+            for (int i = 0; i < V; i++) ss += (double)v[i] * (double)v[i];
             ss = warp_sum_f64(ss);
             const float inv = (float)(1.0 / sqrt(ss / (double)hd + (double)eps));
-            const float4 wv = *reinterpret_cast<const float4*>(nw + e0);
-            v[0] = __fmul_rn(__fmul_rn(v[0], inv), wv.x); v[1] = __fmul_rn(__fmul_rn(v[1], inv), wv.y);
-            v[2] = __fmul_rn(__fmul_rn(v[2], inv), wv.z); v[3] = __fmul_rn(__fmul_rn(v[3], inv), wv.w);
+            float wv[V];
+            load(nw + e0, wv);
+#pragma unroll
+            for (int i = 0; i < V; i++) v[i] = __fmul_rn(__fmul_rn(v[i], inv), wv[i]);
         }
         if (is_q || is_k) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
+            for (int i = 0; i < V; i++) {
                 const float other = __shfl_sync(0xffffffffu, v[i], partner & 31);
                 if (first) {
                     const double x1 = v[i], x2 = other, c = cs[e0 + i], sn = cs[half + e0 + i];
@@ -469,12 +491,19 @@ __global__ void __launch_bounds__(256) qknorm_rope_kvstore_vec_kernel(
             }
         }
         if (is_q) {
-            *reinterpret_cast<float4*>(qkv + (size_t)r * ld + (size_t)hh * hd + e0) = make_float4(v[0], v[1], v[2], v[3]);
+            float* dq = qkv + (size_t)r * ld + (size_t)hh * hd + e0;
+            if constexpr (V == 4) *reinterpret_cast<float4*>(dq) = make_float4(v[0], v[1], v[2], v[3]);
+            else *reinterpret_cast<float2*>(dq) = make_float2(v[0], v[1]);
         } else {
             const int kvh = is_k ? hh - nH : hh - nH - nKV;
             __half* dst = (is_k ? kpool : vpool) + (((size_t)blk * nKV + kvh) * block_rows + rib) * hd + e0;
-            const __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
-            *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const unsigned*>(&h0), *reinterpret_cast<const unsigned*>(&h1));
+            const __half2 h0 = __floats2half2_rn(v[0], v[1]);
+            if constexpr (V == 4) {
+                const __half2 h1 = __floats2half2_rn(v[2], v[3]);
+                *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const unsigned*>(&h0), *reinterpret_cast<const unsigned*>(&h1));
+            } else {
+                *reinterpret_cast<unsigned*>(dst) = *reinterpret_cast<const unsigned*>(&h0);
+            }
         }
     }
 }
@@ -558,14 +587,25 @@ int launch_swiglu_quant(b200_ctx* ctx, const float* gate_up, int T, int F, int l
     ProfScope ps(ctx, PROF_SWIGLU);
     const int il = interleaved128 ? 1 : 0;
     if (il && (!aq.codes || F % 128)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "interleaved gate|up needs a quantized output and F %% 128 == 0");
+    const bool vec = aq.codes && F % 32 == 0 &&
+                     !((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(mid) | (uintptr_t)((size_t)ld * 4)) & 15) &&
+                     !(reinterpret_cast<uintptr_t>(aq.codes) & 7);
+    Parts pt{};
+    if (ctx->pending.n > 0 && ctx->pending.dst == gate_up) {  // the matmul left its K-split partials
+        if (vec && ld == ctx->pending.cols && !((reinterpret_cast<uintptr_t>(ctx->pending.p) | (uintptr_t)(ctx->pending.stride * 4)) & 15)) {
+            pt = ctx->pending;
+            ctx->pending = Parts{};
+        } else {
+            ST_TRY(flush_pending_parts(ctx));
+        }
+    }
     if (aq.codes) {
         if (F % 32) B200_FAIL(ctx, B200_BAD_ARGUMENT, "F must be a multiple of 32");
-        const bool vec = !((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(mid) | (uintptr_t)((size_t)ld * 4)) & 15) &&
-                         !(reinterpret_cast<uintptr_t>(aq.codes) & 7);
         if (vec) {
             dim3 grid(ceil_div(F / 8, 256), T);
-            if (f64_silu) launch_pdl(swiglu_quant_vec_kernel<true>, grid, dim3(256), 0, ctx->stream, gate_up, F, ld, mid, aq.codes, aq.scales, il, x16);
-            else launch_pdl(swiglu_quant_vec_kernel<false>, grid, dim3(256), 0, ctx->stream, gate_up, F, ld, mid, aq.codes, aq.scales, il, x16);
+            const float* src = pt.n ? pt.p : gate_up;
+            if (f64_silu) launch_pdl(swiglu_quant_vec_kernel<true>, grid, dim3(256), 0, ctx->stream, src, F, ld, mid, aq.codes, aq.scales, il, x16, pt.n, pt.stride);
+            else launch_pdl(swiglu_quant_vec_kernel<false>, grid, dim3(256), 0, ctx->stream, src, F, ld, mid, aq.codes, aq.scales, il, x16, pt.n, pt.stride);
         } else {
             if (x16) B200_FAIL(ctx, B200_BAD_ARGUMENT, "fp16 activation tiles are laid out by the vector kernel only (aligned buffers)");
             dim3 grid(ceil_div(F / 32, 8), T);
@@ -615,14 +655,18 @@ int launch_qknorm_rope_kvstore(b200_ctx* ctx, float* qkv, int ld, int T, int nH,
         pt = ctx->pending;
         ctx->pending = Parts{};
     }
-    const bool vec = hd == 128 && rot_half % 4 == 0 && rot_half <= 64 && ld % 4 == 0 &&
+    const bool vec = (hd == 128 || hd == 64) && rot_half % (hd / 32) == 0 && rot_half <= 64 && ld % 4 == 0 &&
                      !((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(pt.p) | (uintptr_t)(pt.stride * 4) |
                         reinterpret_cast<uintptr_t>(q_norm) | reinterpret_cast<uintptr_t>(k_norm)) & 15) &&
                      !((reinterpret_cast<uintptr_t>(kv.k) | reinterpret_cast<uintptr_t>(kv.v)) & 7);
     if (vec) {
         dim3 grid(T, ceil_div(nH + 2 * nKV, 16));
-        launch_pdl(qknorm_rope_kvstore_vec_kernel, grid, dim3(256), 0, ctx->stream, qkv, ld, nH, nKV, rot_half, inv_freq, q_norm, k_norm, eps, row_slot,
-                   row_pos, kv.k, kv.v, kv.table, kv.max_blocks, kv.block_rows, pt.p, pt.n, pt.stride);
+        if (hd == 128)
+            launch_pdl(qknorm_rope_kvstore_vec_kernel<128>, grid, dim3(256), 0, ctx->stream, qkv, ld, nH, nKV, rot_half, inv_freq, q_norm, k_norm, eps, row_slot,
+                       row_pos, kv.k, kv.v, kv.table, kv.max_blocks, kv.block_rows, pt.p, pt.n, pt.stride);
+        else
+            launch_pdl(qknorm_rope_kvstore_vec_kernel<64>, grid, dim3(256), 0, ctx->stream, qkv, ld, nH, nKV, rot_half, inv_freq, q_norm, k_norm, eps, row_slot,
+                       row_pos, kv.k, kv.v, kv.table, kv.max_blocks, kv.block_rows, pt.p, pt.n, pt.stride);
     } else
     qknorm_rope_kvstore_kernel<<<T, 256, smem, ctx->stream>>>(qkv, ld, nH, nKV, hd, rot_half, inv_freq, q_norm, k_norm, eps,
                                                               row_slot, row_pos, kv.k, kv.v, kv.table, kv.max_blocks,

@@ -689,6 +689,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
             __half* x16d = d_q ? x16_for(L.down) : nullptr;   // the other slot: laid out by whoever quantizes silu(gate) * up
             bool fused = false;
             ctx->x16_ready = x16g;
+            ctx->defer_reduce = can_defer && d_q;   // the SwiGLU kernel adds the gate|up partials (each rank's columns are whole)
             static const bool no_umma_env = getenv("B200_NO_UMMA") != nullptr, no_fuse_env = getenv("B200_NO_FUSED_SWIGLU") != nullptr;
             if (L.gu_il && d_q && T >= 33 && !tap_env && !no_umma_env && ctx->umma_scratch &&
                 q4k_umma_scratch_bytes(T, H, 2 * c.ffn) <= ctx->umma_scratch_bytes) {
@@ -700,6 +701,7 @@ int run_layers(b200_model* m, int T, int max_keys) {
                 ST_TRY(matmul(m, L.gu, m->normed, m->aq_h, T, m->gu, 2 * c.ffn));
             }
             ctx->x16_ready = nullptr;
+            ctx->defer_reduce = false;
             if (!fused)
                 ST_TRY(launch_swiglu_quant(ctx, m->gu, T, c.ffn, 2 * c.ffn, d_q ? nullptr : m->mid, d_q ? m->aq_mid : none,
                                            c.kernel_class == B200_CLASS_EXACT, L.gu_il, x16d));
