@@ -38,7 +38,7 @@
 
 namespace {
 
-constexpr int kStages = 3;    // barrier slots: a chunk's full / empty barriers are slot it % kStages
+constexpr int kStages = 4;    // barrier slots: a chunk's full / empty barriers are slot it % kStages (four: a chunk's slot is its place in its super-block)
 #ifndef B200_UMMA_A_STAGES
 #define B200_UMMA_A_STAGES 3
 #define B200_UMMA_B_STAGES 2
@@ -326,15 +326,21 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
         } else {
         uint4 hdr, q[8];  // the current super-block: d, dmin, 12 scale bytes; 128 code bytes
         const unsigned k_mask = opaque_u(0x03C003C0u), k_magic = opaque_u(0x4C004C00u);   // registers, so that mask-and-or is one LOP3
+        static_assert(kStages == 4, "a chunk's barrier slot is its place p in its super-block");
+        // where this thread's eight 16-byte pieces of a row go inside a B stage (the 128-byte swizzle), computed once
+        uint8_t* piece[8];
+#pragma unroll
+        for (int c8 = 0; c8 < 8; c8++) piece[c8] = bring + b_off + (((unsigned)c8 ^ sw) << 4);
 
-        auto step = [&](int it, int p) -> bool {  // p = it & 3, a literal at every call site
-            // B stage it%2 was last read by the MMAs of chunk it-2
+        auto step = [&](int sb, int p) -> bool {  // chunk it = 4 * sb + p; p is a literal at every call site, so slots and stages are too
+            const int it = 4 * sb + p;
+            // the B stage was last read by the MMAs of chunk it - kBStages
             if (it >= kBStages) {  // the answer is made warp-uniform: the lanes meet in __syncwarp below
-                const bool w_ok = mbar_wait(smem_u32(&empty_bar[(it - kBStages) % kStages]), (unsigned)(((it - kBStages) / kStages) & 1), abort_v);
+                const int back = p - kBStages;   // negative: a chunk of the super-block before
+                const bool w_ok = mbar_wait(smem_u32(&empty_bar[back & 3]), (unsigned)((sb + (back >> 2)) & 1), abort_v);
                 if (!__all_sync(0xffffffffu, w_ok)) return false;
             }
             if (p == 0) {  // take the row's next super-block out of `raw`, then hand `raw` back to the weight loader
-                const int sb = it >> 2;
                 const bool w_ok = mbar_wait(smem_u32(&raw_full), (unsigned)(sb & 1), abort_v);
                 if (!__all_sync(0xffffffffu, w_ok)) return false;
                 const uint4* rp = reinterpret_cast<const uint4*>(raw + (size_t)wr * RAW);
@@ -349,7 +355,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
             {   // dequantize the chunk's sub-blocks 2p (low nibbles of code bytes 32p..32p+31) and 2p+1 (high nibbles)
                 const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
                 const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-                uint8_t* rowp = bring + (size_t)(it % kBStages) * BSTAGE + b_off;
+                const int stage_off = (kBStages == 2 ? (p & 1) : it % kBStages) * BSTAGE;
                 const uint4 qa = q[2 * p], qb = q[2 * p + 1];
                 const unsigned wq[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
                 unsigned scs, ms;
@@ -365,20 +371,20 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                     for (int ch = 0; ch < 4; ch++) {
                         const uint4 v = hf ? dequant8<true>(wq[2 * ch], wq[2 * ch + 1], ds, c, k_mask, k_magic)
                                            : dequant8<false>(wq[2 * ch], wq[2 * ch + 1], ds, c, k_mask, k_magic);
-                        *reinterpret_cast<uint4*>(rowp + (((unsigned)(4 * hf + ch) ^ sw) << 4)) = v;
+                        *reinterpret_cast<uint4*>(piece[4 * hf + ch] + stage_off) = v;
                     }
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy stores -> visible to the tensor core
             __syncwarp();  // every lane's stores are fenced: one arrival stands for the warp
-            if (lane == 0) mbar_arrive(smem_u32(&full_bar[it % kStages]));
+            if (lane == 0) mbar_arrive(smem_u32(&full_bar[p]));
             return true;
         };
-        for (int it = 0; it < n_it && ok; it += 4) {  // n_it is a multiple of 4
-            ok = step(it, 0);
-            if (ok) ok = step(it + 1, 1);
-            if (ok) ok = step(it + 2, 2);
-            if (ok) ok = step(it + 3, 3);
+        for (int sb = 0; sb < n_sb && ok; sb++) {
+            ok = step(sb, 0);
+            if (ok) ok = step(sb, 1);
+            if (ok) ok = step(sb, 2);
+            if (ok) ok = step(sb, 3);
         }
         }
         if (!ok) abort_s = 1;
