@@ -576,9 +576,14 @@ int run_layers(b200_model* m, int T, int max_keys) {
     ctx->err_flag = m->err_flag;
     ctx->x16_slot_bytes = m->x16_slot_bytes;
     ctx->x16_ready = nullptr;
-    struct X16Guard {  // no request or hand-off outlives this call, whichever way it returns
+    struct X16Guard {  // no request, hand-off, deferral or unsummed partial outlives this call, whichever way it returns
         b200_ctx* c;
-        ~X16Guard() { c->x16_want = nullptr; c->x16_ready = nullptr; }
+        ~X16Guard() {
+            c->x16_want = nullptr;
+            c->x16_ready = nullptr;
+            c->defer_reduce = false;
+            c->pending = Parts{};   // (the ordinary return has summed them already; an error return abandons the step's results)
+        }
     } x16_guard{ctx};
     ctx->x16_want = nullptr;
     // A producer lays out the fp16 activation tiles of the tcgen05 matmul that follows it (no conversion kernel) when that
