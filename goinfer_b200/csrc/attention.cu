@@ -691,6 +691,7 @@ __global__ void __launch_bounds__(256) attn_exact_av_tile_kernel(const float* __
     constexpr int DG = HD / 8, KL = 256 / DG, CH = 256;
     static_assert(KL <= 32, "the key lanes of a dim group are lanes of one warp");
     __shared__ double ws[G][CH];
+    __shared__ int vrow[CH];   // the chunk's keys as rows of the pool (block id and row in the block resolved once a chunk)
     const int kvh = blockIdx.x, r = blockIdx.y;
     const int nkeys = min(row_pos[r] + 1, max_blocks * block_rows);
     const int kl = threadIdx.x % KL, dg = threadIdx.x / KL;
@@ -706,11 +707,13 @@ __global__ void __launch_bounds__(256) attn_exact_av_tile_kernel(const float* __
             const int g = i / CH, kk = i % CH;
             ws[g][kk] = kc + kk < nkeys ? (double)w[((size_t)r * nH + kvh * G + g) * ld + kc + kk] : 0.0;
         }
+        {
+            const int key = min(kc + (int)threadIdx.x, nkeys - 1);   // (CH == the block's 256 threads)
+            vrow[threadIdx.x] = (tbl[key / block_rows] * nKV + kvh) * block_rows + key % block_rows;
+        }
         __syncthreads();
         const int n = min(CH, nkeys - kc);
-        for (int kk = kl; kk < n; kk += KL) {
-            const int key = kc + kk;
-            const uint4 v = *reinterpret_cast<const uint4*>(vpool + (((size_t)tbl[key / block_rows] * nKV + kvh) * block_rows + key % block_rows) * HD + 8 * dg);
+        auto fold = [&](const uint4& v, int kk) {
             const __half2* hv = reinterpret_cast<const __half2*>(&v);
             double vd[8];
 #pragma unroll
@@ -725,7 +728,17 @@ __global__ void __launch_bounds__(256) attn_exact_av_tile_kernel(const float* __
 #pragma unroll
                 for (int j = 0; j < 8; j++) acc[g][j] = fma(wg, vd[j], acc[g][j]);
             }
+        };
+        // four keys' loads in flight per thread (ascending keys, the same chain of sums)
+        int kk = kl;
+        for (; kk + 3 * KL < n; kk += 4 * KL) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u] = *reinterpret_cast<const uint4*>(vpool + (size_t)vrow[kk + u * KL] * HD + 8 * dg);
+#pragma unroll
+            for (int u = 0; u < 4; u++) fold(v[u], kk + u * KL);
         }
+        for (; kk < n; kk += KL) fold(*reinterpret_cast<const uint4*>(vpool + (size_t)vrow[kk] * HD + 8 * dg), kk);
     }
     // fold the KL key lanes
 #pragma unroll
