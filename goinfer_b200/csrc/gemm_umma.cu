@@ -10,11 +10,12 @@
 // One CTA owns a [256 tokens] x [128*NT weight rows] output tile: per token tile an accumulator of 128*NT fp32 columns x
 // 128 lanes (NT = 2: all of the SM's tensor memory; NT = 1 when that is what it takes to cover the SMs). K is walked in
 // chunks of 64 (one sub-block pair of a super-block):
-//   A ring (3 stages): 2 x [128 tokens][64] fp16. The fp16 activation matrix is written tile by tile in the MMA's
-//            swizzled order by act_to_f16_kernel, so a stage is ONE contiguous 32 KB bulk copy, issued by one thread.
+//   A ring (5 slots of one token tile: [128 tokens][64] fp16, two slots a chunk when the CTA has two token tiles). The fp16
+//            activation matrix is written tile by tile in the MMA's swizzled order by the kernels that quantize
+//            activations, so a slot is ONE contiguous 16 KB bulk copy, issued by one thread.
 //   raw weights: the 144-byte super-blocks of the tile's rows, one tiled TMA copy (box 144 B x 128*NT rows) per
 //            super-block, issued by one thread; each producer thread keeps its row's super-block in registers.
-//   B ring (2 stages): [128*NT weight rows][64] fp16, dequantized by eight producer warps (a thread = a weight row;
+//   B ring (3 stages): [128*NT weight rows][64] fp16, dequantized by eight producer warps (a thread = a weight row;
 //            nibbles become fp16 by a mantissa trick, three instructions per pair of weights).
 // The producers arrive on a `full` mbarrier per chunk (the activation copy's bytes are counted on the same barrier); the
 // MMA warp's elected thread waits for it, issues the chunk's 8 tcgen05.mma (M128, N = 128*NT, K = 16 each) and a
@@ -39,13 +40,18 @@
 namespace {
 
 constexpr int kStages = 4;    // barrier slots: a chunk's full / empty barriers are slot it % kStages (four: a chunk's slot is its place in its super-block)
-#ifndef B200_UMMA_A_STAGES
-#define B200_UMMA_A_STAGES 3
+#ifndef B200_UMMA_A_SLOTS
+#define B200_UMMA_A_SLOTS 6
 #define B200_UMMA_B_STAGES 2
+#define B200_UMMA_RAW_SLOTS 1
 #endif
-constexpr int kAStages = B200_UMMA_A_STAGES;   // the activation ring (bulk copies)
-constexpr int kBStages = B200_UMMA_B_STAGES;   // the dequantized weight ring (written by the producers)
-static_assert(kAStages <= kStages && kBStages <= kStages, "a ring cannot be deeper than the barrier slots");
+// The activation ring is counted in token tiles of 16 KB (a chunk with two token tiles takes two slots, with one tile one), the
+// dequantized weight ring in stages of 128*NT rows, the raw super-blocks in slots of 128*NT x 144 bytes. Build parameters, for
+// measurement: 5 slots + 3 weight stages, 5 + 2 with two raw slots and 6 + 2 + 1 all run a 256-row launch on 24576 x 4096 in
+// 57-59 us and a 2048-row one in 358-374 us; 4 activation slots lose 6-10 % at 2048 rows.
+constexpr int kASlotsQ4 = B200_UMMA_A_SLOTS, kBStagesQ4 = B200_UMMA_B_STAGES, kRawSlotsQ4 = B200_UMMA_RAW_SLOTS;
+constexpr int kASlotsKQ = 6, kBStagesKQ = 2;
+static_assert(kBStagesQ4 <= kStages && kBStagesKQ <= kStages, "a ring cannot be deeper than the barrier slots");
 
 // 8 weights of one 16-byte chunk (nibbles of words w0, w1) -> fp16, two at a time in half2 arithmetic. A nibble q is
 // placed at mantissa bits [6,10) of the half 16.0 (0x4C00), which makes the half 16 + q with no int->float conversion, and
@@ -124,10 +130,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
     constexpr int RAW = FMT == 6 ? 208 : (FMT == 5 ? 176 : kRawRow);   // raw bytes of one super-block of a weight row
     pdl_trigger();  // the next kernel's blocks may be placed as ours retire; they wait for our completion before they touch data
     extern __shared__ __align__(1024) uint8_t umma_smem[];
-    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], raw_full, raw_empty;
+    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], raw_full[2], raw_empty[2];
     __shared__ unsigned tmem_base_s;
     __shared__ int abort_s;
-    constexpr int STAGE = 2 * kTileBytes;       // an A stage = two token tiles
+    constexpr int STAGE = 2 * kTileBytes;       // a chunk of the activation matrix in global memory: two token tiles
+    constexpr int kASlots = FMT == 4 ? kASlotsQ4 : kASlotsKQ, kBStages = FMT == 4 ? kBStagesQ4 : kBStagesKQ;
+    constexpr int RAWST = FMT == 4 ? kRawSlotsQ4 : 1, RAWSLOT = 128 * NT * RAW;   // slots of raw super-blocks (beside the one in registers)
+    static_assert(RAWST <= 2, "two barriers for the raw slots");
     constexpr int BSTAGE = NT * kTileBytes;     // a B stage = NT weight tiles, contiguous: one K-major tile of 128*NT rows
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * 128 * NT, t0 = blockIdx.y * 256;
@@ -139,7 +148,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
     const int mt_count = (T - t0 > 128) ? 2 : 1;
     // the swizzle atoms want 1024-byte aligned tiles; the launch reserves 1024 spare bytes for this round-up
     uint8_t* smem = umma_smem + ((1024u - (smem_u32(umma_smem) & 1023u)) & 1023u);
-    uint8_t* bring = smem + (size_t)kAStages * STAGE;  // kBStages B stages of BSTAGE bytes
+    uint8_t* bring = smem + (size_t)kASlots * kTileBytes;  // kBStages B stages of BSTAGE bytes
     uint8_t* raw = bring + kBStages * BSTAGE;                // the raw super-block (144 bytes) of each of the tile's 128*NT weight rows
 
     if (tid == 0) {
@@ -148,8 +157,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
             mbar_init(smem_u32(&full_bar[s]), kProducerWarps + 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);  // one tcgen05.commit
         }
-        mbar_init(smem_u32(&raw_full), 1);                 // the weight loader's announcement (+ the box's bytes)
-        mbar_init(smem_u32(&raw_empty), kProducerWarps);   // every producer warp has taken its rows out
+        for (int s = 0; s < RAWST; s++) {
+            mbar_init(smem_u32(&raw_full[s]), 1);                 // the weight loader's announcement (+ the box's bytes)
+            mbar_init(smem_u32(&raw_empty[s]), kProducerWarps);   // every producer warp has taken its rows out
+        }
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -188,14 +199,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                 }
                 if (p == 0) {
                     const int sb = it >> 2;
-                    const bool w_ok = mbar_wait(smem_u32(&raw_full), (unsigned)(sb & 1), abort_v);
+                    const bool w_ok = mbar_wait(smem_u32(&raw_full[0]), (unsigned)(sb & 1), abort_v);
                     if (!__all_sync(0xffffffffu, w_ok)) return false;
                     const uint4* rp = reinterpret_cast<const uint4*>(raw + (size_t)wr * RAW);
 #pragma unroll
                     for (int i = 0; i < 13; i++) q[i] = rp[i];
                     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&raw_empty));
+                    if (lane == 0) mbar_arrive(smem_u32(&raw_empty[0]));
                     d = d_next;
                     if (sb + 1 < n_sb && row_in) d_next = __half2float(__ushort_as_half(dp[sb + 1]));
                 }
@@ -262,7 +273,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                 }
                 if (p == 0) {
                     const int sb = it >> 2;
-                    const bool w_ok = mbar_wait(smem_u32(&raw_full), (unsigned)(sb & 1), abort_v);
+                    const bool w_ok = mbar_wait(smem_u32(&raw_full[0]), (unsigned)(sb & 1), abort_v);
                     if (!__all_sync(0xffffffffu, w_ok)) return false;
                     const uint4* rp = reinterpret_cast<const uint4*>(raw + (size_t)wr * RAW);
                     hdr = rp[0];
@@ -271,7 +282,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                     for (int i = 0; i < 8; i++) q[i] = rp[3 + i];
                     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&raw_empty));
+                    if (lane == 0) mbar_arrive(smem_u32(&raw_empty[0]));
                 }
                 {   // sub-blocks 2p (low nibbles of code bytes 32p.., bit 2p of qh[l]) and 2p+1 (high nibbles, bit 2p+1)
                     const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
@@ -340,17 +351,18 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                 const bool w_ok = mbar_wait(smem_u32(&empty_bar[back & 3]), (unsigned)((sb + (back >> 2)) & 1), abort_v);
                 if (!__all_sync(0xffffffffu, w_ok)) return false;
             }
-            if (p == 0) {  // take the row's next super-block out of `raw`, then hand `raw` back to the weight loader
-                const bool w_ok = mbar_wait(smem_u32(&raw_full), (unsigned)(sb & 1), abort_v);
+            if (p == 0) {  // take the row's next super-block out of its raw slot, then hand the slot back to the weight loader
+                const int slot = sb % RAWST;
+                const bool w_ok = mbar_wait(smem_u32(&raw_full[slot]), (unsigned)((sb / RAWST) & 1), abort_v);
                 if (!__all_sync(0xffffffffu, w_ok)) return false;
-                const uint4* rp = reinterpret_cast<const uint4*>(raw + (size_t)wr * RAW);
+                const uint4* rp = reinterpret_cast<const uint4*>(raw + (size_t)slot * RAWSLOT + (size_t)wr * RAW);
                 hdr = rp[0];
 #pragma unroll
                 for (int i = 0; i < 8; i++) q[i] = rp[1 + i];
                 // these reads are ordered before the copy engine's writes of the refill
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&raw_empty));
+                if (lane == 0) mbar_arrive(smem_u32(&raw_empty[slot]));
             }
             {   // dequantize the chunk's sub-blocks 2p (low nibbles of code bytes 32p..32p+31) and 2p+1 (high nibbles)
                 const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
@@ -396,14 +408,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const unsigned a0 = smem_u32(smem + (size_t)(it % kAStages) * STAGE), b0 = smem_u32(bring + (size_t)(it % kBStages) * BSTAGE);
+            const unsigned b0 = smem_u32(bring + (size_t)(it % kBStages) * BSTAGE);
             // one instruction spans all 128*NT weight rows (N = 128*NT): the token tile is fetched once for them
 #pragma unroll
             for (int mt = 0; mt < 2; mt++) {
                 if (mt >= mt_count) break;
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++)
-                    umma_f16(tmem_base + mt * 128 * NT, umma_desc(a0 + mt * kTileBytes + ks * 32), umma_desc(b0 + ks * 32),
+                    umma_f16(tmem_base + mt * 128 * NT, umma_desc(smem_u32(smem + (size_t)((mt_count * it + mt) % kASlots) * kTileBytes) + ks * 32), umma_desc(b0 + ks * 32),
                              idesc_for(128 * NT), (it > 0 || ks > 0) ? 1u : 0u);
             }
             umma_commit(smem_u32(&empty_bar[it % kStages]));
@@ -419,19 +431,23 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
         // tile by tile ([token tile][chunk of K][256 rows][64]) in the swizzled order of the MMA tiles. ----
         const uint8_t* src = reinterpret_cast<const uint8_t*>(X16) + ((size_t)blockIdx.y * (size_t)(4 * nSB) + (size_t)(4 * sb0)) * STAGE;
         int issued = 0;
-        for (int it = 0; it < n_it; it++) {
-            if (it >= kAStages && !mbar_wait(smem_u32(&empty_bar[(it - kAStages) % kStages]), (unsigned)(((it - kAStages) / kStages) & 1), abort_v)) {
-                abort_s = 1;
-                break;
-            }
+        for (int it = 0; it < n_it && !abort_s; it++) {
             const unsigned bar = smem_u32(&full_bar[it % kStages]);
-            const unsigned a_bytes = (unsigned)(mt_count * kTileBytes);   // rows 0..127 of a 256-row tile are its first half
-            mbar_arrive_expect_tx(bar, a_bytes);
-            bulk_g2s(smem_u32(smem + (size_t)(it % kAStages) * STAGE), src + (size_t)it * STAGE, a_bytes, bar);
+            for (int mt = 0; mt < mt_count; mt++) {
+                // the slot's last tenant was token tile flat - kASlots, a tile of chunk (flat - kASlots) / mt_count; and the chunk's
+                // `full` barrier must have finished the phase of chunk it - kStages before anything of this chunk arrives on it
+                const int flat = mt_count * it + mt, prev = max(flat >= kASlots ? (flat - kASlots) / mt_count : -1, it - kStages);
+                if (prev >= 0 && !mbar_wait(smem_u32(&empty_bar[prev % kStages]), (unsigned)((prev / kStages) & 1), abort_v)) {
+                    abort_s = 1;
+                    break;
+                }
+                if (mt == 0) mbar_arrive_expect_tx(bar, (unsigned)(mt_count * kTileBytes));   // rows 0..127 of a 256-row tile are its first half
+                bulk_g2s(smem_u32(smem + (size_t)(flat % kASlots) * kTileBytes), src + (size_t)it * STAGE + (size_t)mt * kTileBytes, kTileBytes, bar);
+            }
             issued = it + 1;
         }
         if (abort_s) {  // copies still in flight must land before the CTA may leave: bounded waits on their barriers
-            for (int it = max(0, issued - kAStages); it < issued; it++) mbar_wait(smem_u32(&full_bar[it % kStages]), (unsigned)((it / kStages) & 1));
+            for (int it = max(0, issued - 4); it < issued; it++) mbar_wait(smem_u32(&full_bar[it % kStages]), (unsigned)((it / kStages) & 1));
         }
     } else if (warp == kProducerWarps + 2 && lane == 0) {
         // ---- the weight loader: one thread. From the row-major matrix, one tiled copy per super-block: 144 raw bytes of
@@ -441,23 +457,26 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
         int issued = 0;
         const int tile0 = n0 / 16, live = min(8 * NT, (N + 15) / 16 - tile0);
         for (int sb = 0; sb < n_sb; sb++) {
-            if (sb > 0 && !mbar_wait(smem_u32(&raw_empty), (unsigned)((sb - 1) & 1), abort_v)) {
+            const int slot = sb % RAWST;
+            if (sb >= RAWST && !mbar_wait(smem_u32(&raw_empty[slot]), (unsigned)((sb / RAWST - 1) & 1), abort_v)) {
                 abort_s = 1;
                 break;
             }
+            uint8_t* rslot = raw + (size_t)slot * RAWSLOT;
             if (w16) {
-                mbar_arrive_expect_tx(smem_u32(&raw_full), (unsigned)(live * 16 * kRawRow));
+                mbar_arrive_expect_tx(smem_u32(&raw_full[slot]), (unsigned)(live * 16 * kRawRow));
                 for (int i = 0; i < live; i++)
-                    bulk_g2s(smem_u32(raw + (size_t)i * 16 * kRawRow), w16 + ((size_t)(tile0 + i) * nSB + sb0 + sb) * (16 * kRawRow), 16 * kRawRow,
-                             smem_u32(&raw_full));
+                    bulk_g2s(smem_u32(rslot + (size_t)i * 16 * kRawRow), w16 + ((size_t)(tile0 + i) * nSB + sb0 + sb) * (16 * kRawRow), 16 * kRawRow,
+                             smem_u32(&raw_full[slot]));
             } else {
-                mbar_arrive_expect_tx(smem_u32(&raw_full), (unsigned)(128 * NT * RAW));
-                tensor_g2s_2d(smem_u32(raw), &wmap, (sb0 + sb) * RAW, n0, smem_u32(&raw_full));
+                mbar_arrive_expect_tx(smem_u32(&raw_full[slot]), (unsigned)RAWSLOT);
+                tensor_g2s_2d(smem_u32(rslot), &wmap, (sb0 + sb) * RAW, n0, smem_u32(&raw_full[slot]));
             }
             issued = sb + 1;
         }
-        // a copy still in flight must land before the CTA may leave: a bounded wait on its barrier
-        if (abort_s && issued > 0) mbar_wait(smem_u32(&raw_full), (unsigned)((issued - 1) & 1));
+        // copies still in flight must land before the CTA may leave: bounded waits on their barriers
+        if (abort_s)
+            for (int sb = max(0, issued - RAWST); sb < issued; sb++) mbar_wait(smem_u32(&raw_full[sb % RAWST]), (unsigned)((sb / RAWST) & 1));
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
@@ -720,7 +739,8 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
     }
     if (sw_x16 && sw_x16 == x16) B200_FAIL(ctx, B200_BAD_ARGUMENT, "the epilogue's activation slot is the one this matmul reads");
     // A ring + B ring (sized for NT = 2) + one raw super-block per producer thread + round-up room
-    constexpr int smem = kAStages * 2 * kTileBytes + kBStages * 2 * kTileBytes + kProducers * kRawRow + 1024;
+    constexpr int smem = kASlotsQ4 * kTileBytes + kBStagesQ4 * 2 * kTileBytes + kRawSlotsQ4 * kProducers * kRawRow + 1024;
+    static_assert(smem <= 227 * 1024, "a CTA's shared memory");
     static PerDeviceOnce attr_once;  // the attribute belongs to the device
     if (attr_once.first(ctx->device)) {
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -760,7 +780,7 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
 // Q6_K weights (208-byte bodies row by row, d values behind them: launch_q6k_repack) x the per-32 activations as fp16
 // tiles, on the same tcgen05 pipeline: the producers put the six-bit codes together and scale them in registers, so no
 // dequantized copy of the matrix exists. From 32 rows in the fast class.
-size_t q6k_umma_smem_bytes() { return (size_t)kAStages * 2 * kTileBytes + (size_t)kBStages * 2 * kTileBytes + (size_t)kProducers * 208 + 1024; }
+size_t q6k_umma_smem_bytes() { return (size_t)kASlotsKQ * kTileBytes + (size_t)kBStagesKQ * 2 * kTileBytes + (size_t)kProducers * 208 + 1024; }
 
 // whether T rows of an [N][K] Q6_K matrix fit a scratch of `scratch_bytes` whose first 2 * slot_bytes hold activation slots
 bool q6k_umma_fits(int sm_count, size_t slot_bytes, size_t scratch_bytes, int N, int K, int T) {
