@@ -599,17 +599,28 @@ int launch_q4k_matmul_small_grouped(b200_ctx* ctx, const uint8_t* W_all, int n_e
                                     const int32_t* offs, int n_rows, float* dst, int ldd) {
     if (!q4k_small_grouped_supported(W_all, N, K)) B200_FAIL(ctx, B200_BAD_ARGUMENT, "grouped small-batch matmul: N %% 16, K %% 256 or alignment");
     if (n_rows <= 0) return B200_OK;
-    constexpr int NT = 2, MT = 1;   // passes of 16 rows: at 8 rows an expert on average, most experts take one
-    using Cfg = SmallCfg<NT, MT>;
-    static PerDeviceOnce attr_once;  // the attribute belongs to the device
-    if (attr_once.first(ctx->device)) {
-        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_small_kernel<NT, MT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
-    }
+    // passes of 16 rows (NT = 2): at 8 rows an expert on average, most experts take one. A warp takes two row tiles (MT = 2) where
+    // the matrix has enough of them: an expert's share of a launch is small (a 1536 x 2048 gate|up stack is 1.8 MB), so fewer,
+    // longer CTAs spend less of their time on set-up and on the first copies' latency.
+    static const int mt_env = getenv("B200_EXPERT_MT") ? atoi(getenv("B200_EXPERT_MT")) : 0;
     const int n_tiles = N / 16, nSB = K / 256;
-    dim3 grid(ceil_div(n_tiles, kSmWarps * MT), 1, n_experts);
-    {
-        ProfScope ps(ctx, PROF_Q4K_GEMM);
-        launch_pdl(q4k_small_kernel<NT, MT, true>, grid, dim3(kSmThreads), (size_t)Cfg::kSmem, ctx->stream, W_all, n_tiles, x16, scales, N, nSB, nSB, n_rows, dst, ldd,
+    const int MTsel = mt_env ? mt_env : (n_tiles >= 32 ? 2 : 1);
+    ProfScope ps(ctx, PROF_Q4K_GEMM);
+    if (MTsel == 2) {
+        using Cfg = SmallCfg<2, 2>;
+        static PerDeviceOnce attr_once;  // the attribute belongs to the device
+        if (attr_once.first(ctx->device))
+            CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_small_kernel<2, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+        dim3 grid(ceil_div(n_tiles, kSmWarps * 2), 1, n_experts);
+        launch_pdl(q4k_small_kernel<2, 2, true>, grid, dim3(kSmThreads), (size_t)Cfg::kSmem, ctx->stream, W_all, n_tiles, x16, scales, N, nSB, nSB, n_rows, dst, ldd,
+                   (size_t)0, ctx->err_flag, offs);
+    } else {
+        using Cfg = SmallCfg<2, 1>;
+        static PerDeviceOnce attr_once;
+        if (attr_once.first(ctx->device))
+            CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_small_kernel<2, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem));
+        dim3 grid(ceil_div(n_tiles, kSmWarps), 1, n_experts);
+        launch_pdl(q4k_small_kernel<2, 1, true>, grid, dim3(kSmThreads), (size_t)Cfg::kSmem, ctx->stream, W_all, n_tiles, x16, scales, N, nSB, nSB, n_rows, dst, ldd,
                    (size_t)0, ctx->err_flag, offs);
     }
     LAUNCH_CHECK(ctx);

@@ -416,45 +416,71 @@ __global__ void __launch_bounds__(32) route_kernel(const float* __restrict__ log
             if (idx[(size_t)r * k + j] >= 0) wts[(size_t)r * k + j] = __fdiv_rn(wts[(size_t)r * k + j], wsum);
 }
 
-// One block; a warp owns an expert at a time (expert w, w + warps, ...) and walks the assignments 32 at a time with a
-// ballot, so an expert's rows keep the order of their assignments. offs[nE+1]; rows_tok[s] = token row of sorted slot s;
-// slot_of[a] = sorted slot of assignment a = row*k + rank (-1 when the rank is empty).
+// One block of 1024 threads: a counting sort that keeps an expert's rows in the order of their assignments. The experts'
+// totals come from shared-memory atomics (a count does not depend on the order), their offsets from a warp scan; then the
+// assignments are walked 1024 at a time, a thread each: lanes that name the same expert find one another with match_any (a
+// lane's place among them is its rank in the warp), the warps' counts per expert are scanned over the 32 warps by a thread
+// per expert, and slot = the expert's running offset + the warps before + the rank. offs[nE+1]; rows_tok[s] = token row of
+// sorted slot s; slot_of[a] = sorted slot of assignment a = row*k + rank (-1 when the rank is empty).
+// Dynamic shared memory: 33 * nE ints.
 __global__ void __launch_bounds__(1024) group_experts_kernel(const int32_t* __restrict__ idx, int n_assign, int k, int nE, int32_t* __restrict__ offs,
-                                                             int32_t* __restrict__ rows_tok, int32_t* __restrict__ slot_of, int n_staged) {
-    extern __shared__ int s_cnt[];     // nE counts (then offsets), then the first n_staged assignments (all of them when they fit)
-    int* s_idx = s_cnt + nE;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
-    for (int a = tid; a < n_staged; a += blockDim.x) s_idx[a] = idx[a];
+                                                             int32_t* __restrict__ rows_tok, int32_t* __restrict__ slot_of) {
+    extern __shared__ int s_base[];    // nE running offsets, then [32 warps][nE] counts
+    int* wcnt = s_base + nE;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int e = tid; e < nE; e += 1024) s_base[e] = 0;
     __syncthreads();
-    auto at = [&](int a) { return a < n_assign ? (a < n_staged ? s_idx[a] : idx[a]) : -2; };
-    for (int e = warp; e < nE; e += n_warps) {
-        int c = 0;
-        for (int base = 0; base < n_assign; base += 32) c += __popc(__ballot_sync(0xffffffffu, at(base + lane) == e));
-        if (lane == 0) s_cnt[e] = c;
+    for (int a = tid; a < n_assign; a += 1024) {
+        const int e = idx[a];
+        if (e >= 0) atomicAdd(&s_base[e], 1);
     }
     __syncthreads();
-    if (tid == 0) {
-        int run = 0;
-        for (int i = 0; i < nE; i++) { const int c = s_cnt[i]; offs[i] = run; s_cnt[i] = run; run += c; }
-        offs[nE] = run;
-    }
-    __syncthreads();
-    for (int e = warp; e < nE; e += n_warps) {
-        int s = s_cnt[e];
-        for (int base = 0; base < n_assign; base += 32) {
-            const int a = base + lane;
-            const bool mine = at(a) == e;
-            const unsigned m = __ballot_sync(0xffffffffu, mine);
-            if (mine) {
-                const int slot = s + __popc(m & ((1u << lane) - 1u));
-                rows_tok[slot] = a / k;
-                slot_of[a] = slot;
+    if (warp == 0) {
+        int carry = 0;
+        for (int e0 = 0; e0 < nE; e0 += 32) {
+            const int c = e0 + lane < nE ? s_base[e0 + lane] : 0;
+            int v = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += u;
             }
-            s += __popc(m);
+            if (e0 + lane < nE) {
+                offs[e0 + lane] = carry + v - c;
+                s_base[e0 + lane] = carry + v - c;
+            }
+            carry += __shfl_sync(0xffffffffu, v, 31);
         }
+        if (lane == 0) offs[nE] = carry;
     }
-    for (int a = tid; a < n_assign; a += blockDim.x)
-        if (at(a) < 0) slot_of[a] = -1;
+    __syncthreads();
+    for (int a0 = 0; a0 < n_assign; a0 += 1024) {
+        const int a = a0 + tid, e = a < n_assign ? idx[a] : -1;
+        for (int i = tid; i < 32 * nE; i += 1024) wcnt[i] = 0;
+        __syncthreads();
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        if (e >= 0 && rank == 0) wcnt[warp * nE + e] = __popc(peers);
+        __syncthreads();
+        for (int ee = tid; ee < nE; ee += 1024) {   // the warps' counts become the warps' first slots; the expert's offset moves on
+            int run = s_base[ee];
+            for (int w = 0; w < 32; w++) {
+                const int c = wcnt[w * nE + ee];
+                wcnt[w * nE + ee] = run;
+                run += c;
+            }
+            s_base[ee] = run;
+        }
+        __syncthreads();
+        if (e >= 0) {
+            const int slot = wcnt[warp * nE + e] + rank;
+            rows_tok[slot] = a / k;
+            slot_of[a] = slot;
+        } else if (a < n_assign) {
+            slot_of[a] = -1;
+        }
+        __syncthreads();
+    }
 }
 
 }  // namespace
@@ -493,10 +519,12 @@ int launch_route(b200_ctx* ctx, const float* logits, int T, int nE, int k, int n
 
 int launch_group_experts(b200_ctx* ctx, const int32_t* idx, int T, int k, int nE, int32_t* offs, int32_t* rows) {
     // rows holds rows_tok[T*k] followed by slot_of[T*k]
-    // the assignments are scanned once per expert: from shared memory as far as they fit (40 KB), the rest from global
-    const int n_staged = std::min(T * k, 10240);
-    group_experts_kernel<<<1, 1024, (nE + n_staged) * sizeof(int), ctx->stream>>>(
-        idx, T * k, k, nE, offs, rows, rows + (size_t)T * k, n_staged);
+    if (nE > 512) B200_FAIL(ctx, B200_DECLINED, "expert grouping: more than 512 experts");
+    const size_t smem = (size_t)33 * nE * sizeof(int);
+    static PerDeviceOnce attr_once;  // the attribute belongs to the device
+    if (attr_once.first(ctx->device))
+        CUDA_TRY(ctx, cudaFuncSetAttribute(group_experts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 33 * 512 * (int)sizeof(int)));
+    group_experts_kernel<<<1, 1024, smem, ctx->stream>>>(idx, T * k, k, nE, offs, rows, rows + (size_t)T * k);
     LAUNCH_CHECK(ctx);
     return B200_OK;
 }
