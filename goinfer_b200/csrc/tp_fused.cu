@@ -262,7 +262,12 @@ __global__ void __launch_bounds__(1024) tp_ll_reduce_norm_quant_kernel(TpPeers p
     bool ok = true;
     // ---- push: this rank's partial rows into their owners' staging ([source rank][owner's row][H]) ----
     if (phases & 1) {
-        for (int r = blockIdx.x; r < T; r += gridDim.x) {
+        // the rows are walked from the next rank's on (rank s starts with the rows of rank s + 1), so that at any moment the
+        // ranks send to different owners instead of all to the owners of the first rows
+        for (int r0 = blockIdx.x; r0 < t * rows_per; r0 += gridDim.x) {
+            int r = r0 + (rank + 1) * rows_per;
+            if (r >= t * rows_per) r -= t * rows_per;
+            if (r >= T) continue;
             const int o = r / rows_per, b = r - o * rows_per;
             if (o == rank) continue;
             float* dst = reinterpret_cast<float*>(peers.p[o] + off.stage) + ((size_t)rank * rows_per + b) * H + 8 * c;
