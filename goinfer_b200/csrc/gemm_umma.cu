@@ -51,6 +51,7 @@ constexpr int kStages = 4;    // barrier slots: a chunk's full / empty barriers 
 // 57-59 us and a 2048-row one in 358-374 us; 4 activation slots lose 6-10 % at 2048 rows.
 constexpr int kASlotsQ4 = B200_UMMA_A_SLOTS, kBStagesQ4 = B200_UMMA_B_STAGES, kRawSlotsQ4 = B200_UMMA_RAW_SLOTS;
 constexpr int kASlotsKQ = 6, kBStagesKQ = 2;
+constexpr int kOneASlots = 3, kOneBStages = 3, kOneRawSlots = 2;   // launches of 128 rows or fewer (Q4_K)
 static_assert(kBStagesQ4 <= kStages && kBStagesKQ <= kStages, "a ring cannot be deeper than the barrier slots");
 
 // 8 weights of one 16-byte chunk (nibbles of words w0, w1) -> fp16, two at a time in half2 arithmetic. A nibble q is
@@ -120,7 +121,9 @@ __device__ __forceinline__ float umma_silu(float x) { return __fdividef(x, __fad
 // fp16(d * sc). FMT 5: Q5_K rows as in the file (176-byte super-blocks: d, dmin, the 12 scale bytes of Q4_K, qh[32], qs[128]):
 // Q4_K's nibbles with a fifth bit from qh, the five-bit code placed in the mantissa of the half 32 + q.
 // The rest of the kernel (activation ring, MMAs, epilogue) does not know the format.
-template <int NT, bool SWIGLU, int FMT = 4>
+// ONE (Q4_K, launches of 128 rows or fewer: every CTA has one token tile): the shared memory the second token tile's slots
+// would take goes to a third weight stage and a second slot of raw super-blocks (3 activation slots + 3 + 2).
+template <int NT, bool SWIGLU, int FMT = 4, bool ONE = false>
 __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __grid_constant__ CUtensorMap wmap, int N, int nSB,
                                                                         const __half* __restrict__ X16, int T,
                                                                         float* __restrict__ dst, int ldd, size_t split_stride,
@@ -134,8 +137,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
     __shared__ unsigned tmem_base_s;
     __shared__ int abort_s;
     constexpr int STAGE = 2 * kTileBytes;       // a chunk of the activation matrix in global memory: two token tiles
-    constexpr int kASlots = FMT == 4 ? kASlotsQ4 : kASlotsKQ, kBStages = FMT == 4 ? kBStagesQ4 : kBStagesKQ;
-    constexpr int RAWST = FMT == 4 ? kRawSlotsQ4 : 1, RAWSLOT = 128 * NT * RAW;   // slots of raw super-blocks (beside the one in registers)
+    static_assert(!ONE || FMT == 4, "the one-token-tile rings are the Q4_K kernel's");
+    constexpr int kASlots = ONE ? kOneASlots : (FMT == 4 ? kASlotsQ4 : kASlotsKQ), kBStages = ONE ? kOneBStages : (FMT == 4 ? kBStagesQ4 : kBStagesKQ);
+    constexpr int RAWST = ONE ? kOneRawSlots : (FMT == 4 ? kRawSlotsQ4 : 1), RAWSLOT = 128 * NT * RAW;   // slots of raw super-blocks (beside the one in registers)
     static_assert(RAWST <= 2, "two barriers for the raw slots");
     constexpr int BSTAGE = NT * kTileBytes;     // a B stage = NT weight tiles, contiguous: one K-major tile of 128*NT rows
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -145,7 +149,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) q4k_umma_gemm_kernel(const __
               sb1 = (int)((long long)nSB * (blockIdx.z + 1) / splits);
     const int n_sb = sb1 - sb0, n_it = 4 * n_sb;
     // token tiles of 128 this CTA really has: with 128 rows or fewer left, the second tile's copies, MMAs and epilogue are left out
-    const int mt_count = (T - t0 > 128) ? 2 : 1;
+    const int mt_count = (!ONE && T - t0 > 128) ? 2 : 1;
     // the swizzle atoms want 1024-byte aligned tiles; the launch reserves 1024 spare bytes for this round-up
     uint8_t* smem = umma_smem + ((1024u - (smem_u32(umma_smem) & 1023u)) & 1023u);
     uint8_t* bring = smem + (size_t)kASlots * kTileBytes;  // kBStages B stages of BSTAGE bytes
@@ -741,11 +745,18 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
     // A ring + B ring (sized for NT = 2) + one raw super-block per producer thread + round-up room
     constexpr int smem = kASlotsQ4 * kTileBytes + kBStagesQ4 * 2 * kTileBytes + kRawSlotsQ4 * kProducers * kRawRow + 1024;
     static_assert(smem <= 227 * 1024, "a CTA's shared memory");
+    constexpr int smem_one = kOneASlots * kTileBytes + kOneBStages * 2 * kTileBytes + kOneRawSlots * kProducers * kRawRow + 1024;
+    static_assert(smem_one <= 227 * 1024, "a CTA's shared memory");
+    static const bool no_one_env = getenv("B200_UMMA_NO_ONE") != nullptr;   // measurement: the general rings at every row count
+    const bool one = T <= 128 && !no_one_env;
     static PerDeviceOnce attr_once;  // the attribute belongs to the device
     if (attr_once.first(ctx->device)) {
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<1, false, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_one));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, false, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_one));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(q4k_umma_gemm_kernel<2, true, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_one));
     }
     static const CUtensorMap no_map{};  // the tile-major copy is fetched with plain bulk copies
     const CUtensorMap* wmap = W_tiles ? &no_map : q4k_weight_map(ctx, W, N, nSB, 128 * NT, kRawRow);
@@ -760,7 +771,10 @@ int launch_q4k_matmul_umma_swiglu(b200_ctx* ctx, const uint8_t* W, int N, int K,
         float* const no_scales = nullptr;
         __half* const no_x16 = nullptr;
         const unsigned short* const no_d = nullptr;
-        if (fuse) launch_pdl(q4k_umma_gemm_kernel<2, true>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, sw.codes, sw.scales, sw_x16, W_tiles, no_d);
+        if (one && fuse) launch_pdl(q4k_umma_gemm_kernel<2, true, 4, true>, grid, dim3(kUmmaThreads), smem_one, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, sw.codes, sw.scales, sw_x16, W_tiles, no_d);
+        else if (one && NT == 2) launch_pdl(q4k_umma_gemm_kernel<2, false, 4, true>, grid, dim3(kUmmaThreads), smem_one, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16, W_tiles, no_d);
+        else if (one) launch_pdl(q4k_umma_gemm_kernel<1, false, 4, true>, grid, dim3(kUmmaThreads), smem_one, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16, W_tiles, no_d);
+        else if (fuse) launch_pdl(q4k_umma_gemm_kernel<2, true>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, sw.codes, sw.scales, sw_x16, W_tiles, no_d);
         else if (NT == 2) launch_pdl(q4k_umma_gemm_kernel<2, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16, W_tiles, no_d);
         else launch_pdl(q4k_umma_gemm_kernel<1, false>, grid, dim3(kUmmaThreads), smem, ctx->stream, *wmap, N, nSB, x16, T, out, out_ld, stride, err_flag, no_codes, no_scales, no_x16, W_tiles, no_d);
     }
