@@ -717,7 +717,7 @@ __global__ void __launch_bounds__(256) dense_matmul_f64_tok4_kernel(const float*
 }
 
 // The same sums again for a tile of TT tokens x 16 weight rows a block: the tokens' rows are brought into shared memory once
-// as f64 (exact), a warp takes two of the 16 weight rows one after the other and reads each weight once for the TT tokens. A
+// as f64 (exact), a warp takes two of the 16 weight rows and reads each weight once for the TT tokens. A
 // 128 x 128 router product over K = 2048 moves 25 MB through L2 instead of the 164 MB of the four-tokens-a-warp kernel.
 // Dynamic shared memory: TT * K doubles.
 template <int TT>
@@ -726,30 +726,61 @@ __global__ void __launch_bounds__(256) dense_matmul_f64_tile_kernel(const float*
     extern __shared__ double xs[];   // [TT][K]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t0 = blockIdx.y * TT;
-    for (int i = threadIdx.x; i < TT * K; i += 256) {
-        const int tt = i / K, k = i - tt * K;
-        xs[i] = (double)x[(size_t)min(t0 + tt, T - 1) * K + k];
+    for (int tt = warp; tt < TT; tt += 8) {   // a warp brings a token's row in, several loads in flight a lane
+        const float* xr = x + (size_t)min(t0 + tt, T - 1) * K;
+        double* xd = xs + (size_t)tt * K;
+#pragma unroll 8
+        for (int k = lane; k < K; k += 32) xd[k] = (double)__ldg(xr + k);
     }
     __syncthreads();
-#pragma unroll 1
-    for (int j = 0; j < 2; j++) {
-        const int n = blockIdx.x * 16 + 2 * warp + j;
-        if (n >= N) break;
-        const float* w = W + (size_t)n * K;
-        double s[TT];
+    // the warp's two weight rows side by side, four steps of K's loads in flight (a lane's weights are 128 bytes apart: the
+    // loads' latency, not their count, is what a lane waits for)
+    const int n0 = blockIdx.x * 16 + 2 * warp;
+    if (n0 >= N) return;
+    const bool two = n0 + 1 < N;
+    const float* w0 = W + (size_t)n0 * K;
+    const float* w1 = W + (size_t)(two ? n0 + 1 : n0) * K;
+    double s0[TT], s1[TT];
 #pragma unroll
-        for (int i = 0; i < TT; i++) s[i] = 0;
-#pragma unroll 2
-        for (int k = lane; k < K; k += 32) {
-            const double wv = (double)w[k];
+    for (int i = 0; i < TT; i++) s0[i] = s1[i] = 0;
+    int k = lane;
+    for (; k + 96 < K; k += 128) {
+        float a[4], b[4];
 #pragma unroll
-            for (int i = 0; i < TT; i++) s[i] += xs[i * K + k] * wv;
+        for (int u = 0; u < 4; u++) {
+            a[u] = __ldg(w0 + k + 32 * u);
+            b[u] = __ldg(w1 + k + 32 * u);
         }
 #pragma unroll
-        for (int i = 0; i < TT; i++) {
+        for (int u = 0; u < 4; u++) {
+            const double av = (double)a[u], bv = (double)b[u];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s[i] += __shfl_xor_sync(0xffffffffu, s[i], o);
-            if (lane == 0 && t0 + i < T) dst[(size_t)(t0 + i) * ldd + n] = (float)s[i];
+            for (int i = 0; i < TT; i++) {
+                const double xv = xs[i * K + k + 32 * u];
+                s0[i] += xv * av;
+                s1[i] += xv * bv;
+            }
+        }
+    }
+    for (; k < K; k += 32) {
+        const double av = (double)w0[k], bv = (double)w1[k];
+#pragma unroll
+        for (int i = 0; i < TT; i++) {
+            const double xv = xs[i * K + k];
+            s0[i] += xv * av;
+            s1[i] += xv * bv;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TT; i++) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            s0[i] += __shfl_xor_sync(0xffffffffu, s0[i], o);
+            s1[i] += __shfl_xor_sync(0xffffffffu, s1[i], o);
+        }
+        if (lane == 0 && t0 + i < T) {
+            dst[(size_t)(t0 + i) * ldd + n0] = (float)s0[i];
+            if (two) dst[(size_t)(t0 + i) * ldd + n0 + 1] = (float)s1[i];
         }
     }
 }
