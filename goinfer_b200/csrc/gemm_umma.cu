@@ -10,13 +10,17 @@
 // One CTA owns a [256 tokens] x [128*NT weight rows] output tile: per token tile an accumulator of 128*NT fp32 columns x
 // 128 lanes (NT = 2: all of the SM's tensor memory; NT = 1 when that is what it takes to cover the SMs). K is walked in
 // chunks of 64 (one sub-block pair of a super-block):
-//   A ring (5 slots of one token tile: [128 tokens][64] fp16, two slots a chunk when the CTA has two token tiles). The fp16
-//            activation matrix is written tile by tile in the MMA's swizzled order by the kernels that quantize
-//            activations, so a slot is ONE contiguous 16 KB bulk copy, issued by one thread.
-//   raw weights: the 144-byte super-blocks of the tile's rows, one tiled TMA copy (box 144 B x 128*NT rows) per
-//            super-block, issued by one thread; each producer thread keeps its row's super-block in registers.
-//   B ring (3 stages): [128*NT weight rows][64] fp16, dequantized by eight producer warps (a thread = a weight row;
-//            nibbles become fp16 by a mantissa trick, three instructions per pair of weights).
+//   A ring: slots of one token tile ([128 tokens][64] fp16; a chunk takes two slots when the CTA has two token tiles,
+//            else one): 6 slots, 3 in a launch of 128 rows or fewer. The fp16 activation matrix is written tile by tile
+//            in the MMA's swizzled order by the kernels that quantize activations, so a slot is ONE contiguous 16 KB
+//            bulk copy, issued by one thread.
+//   raw weights: the 144-byte super-blocks of the tile's rows, per super-block one bulk copy of 2304 contiguous bytes
+//            per 16 rows of the tile-major copy (or one tiled TMA copy, box 144 B x 128*NT rows, of the row-major matrix),
+//            issued by one thread into a slot (two slots in a launch of 128 rows or fewer); each producer thread keeps
+//            its row's current super-block in registers.
+//   B ring: stages of [128*NT weight rows][64] fp16 (2; 3 in a launch of 128 rows or fewer), dequantized by eight
+//            producer warps (a thread = a weight row; nibbles become fp16 by a mantissa trick, three instructions per
+//            pair of weights).
 // The producers arrive on a `full` mbarrier per chunk (the activation copy's bytes are counted on the same barrier); the
 // MMA warp's elected thread waits for it, issues the chunk's 8 tcgen05.mma (M128, N = 128*NT, K = 16 each) and a
 // tcgen05.commit that arrives on the `empty` mbarrier producers and loaders wait on before they reuse a stage. Nothing
