@@ -729,8 +729,17 @@ __global__ void __launch_bounds__(256) dense_matmul_f64_tile_kernel(const float*
     for (int tt = warp; tt < TT; tt += 8) {   // a warp brings a token's row in, several loads in flight a lane
         const float* xr = x + (size_t)min(t0 + tt, T - 1) * K;
         double* xd = xs + (size_t)tt * K;
+        if ((K & 3) == 0 && (reinterpret_cast<uintptr_t>(xr) & 15) == 0) {
 #pragma unroll 8
-        for (int k = lane; k < K; k += 32) xd[k] = (double)__ldg(xr + k);
+            for (int k = 4 * lane; k < K; k += 128) {
+                const float4 v = __ldg(reinterpret_cast<const float4*>(xr + k));
+                *reinterpret_cast<double2*>(xd + k) = make_double2((double)v.x, (double)v.y);
+                *reinterpret_cast<double2*>(xd + k + 2) = make_double2((double)v.z, (double)v.w);
+            }
+        } else {
+#pragma unroll 8
+            for (int k = lane; k < K; k += 32) xd[k] = (double)__ldg(xr + k);
+        }
     }
     __syncthreads();
     // the warp's two weight rows side by side, four steps of K's loads in flight (a lane's weights are 128 bytes apart: the
@@ -744,12 +753,22 @@ __global__ void __launch_bounds__(256) dense_matmul_f64_tile_kernel(const float*
 #pragma unroll
     for (int i = 0; i < TT; i++) s0[i] = s1[i] = 0;
     int k = lane;
-    for (; k + 96 < K; k += 128) {
-        float a[4], b[4];
+    float a[4], b[4], an[4], bn[4];   // this batch of four steps' weights and the next one's, already on their way
+    if (k + 96 < K) {
 #pragma unroll
         for (int u = 0; u < 4; u++) {
             a[u] = __ldg(w0 + k + 32 * u);
             b[u] = __ldg(w1 + k + 32 * u);
+        }
+    }
+    for (; k + 96 < K; k += 128) {
+        const bool more = k + 128 + 96 < K;
+        if (more) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                an[u] = __ldg(w0 + k + 128 + 32 * u);
+                bn[u] = __ldg(w1 + k + 128 + 32 * u);
+            }
         }
 #pragma unroll
         for (int u = 0; u < 4; u++) {
@@ -759,6 +778,13 @@ __global__ void __launch_bounds__(256) dense_matmul_f64_tile_kernel(const float*
                 const double xv = xs[i * K + k + 32 * u];
                 s0[i] += xv * av;
                 s1[i] += xv * bv;
+            }
+        }
+        if (more) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                a[u] = an[u];
+                b[u] = bn[u];
             }
         }
     }
