@@ -85,3 +85,17 @@ def test_every_programmatically_launched_kernel_waits():
         before = re.sub(r"//[^\n]*", "", before)
         for prm in params:
             assert not re.search(r"\b" + prm + r"\s*\[", before), (name, prm)
+
+
+def test_go_shim_binds_every_product_symbol():
+    """integration/b200/lib.go (source only: no Go toolchain here) registers one function per symbol of the product header,
+    no more and no fewer, and checks the struct sizes this file pins."""
+    import os
+    import re
+    from goinfer_b200 import abi
+    text = open(os.path.join(os.path.dirname(__file__), "..", "integration", "b200", "lib.go")).read()
+    bound = re.findall(r'\{&\w+,\s*"(b200_[a-z0-9_]+)"\}', text)
+    assert len(bound) == len(set(bound))
+    assert set(bound) == set(abi.EXPORTS), (sorted(set(abi.EXPORTS) - set(bound)), sorted(set(bound) - set(abi.EXPORTS)))
+    for size in ("116", "24", "56"):
+        assert re.search(r"unsafe\.Sizeof\(\w+\{\}\) != " + size, text), size
